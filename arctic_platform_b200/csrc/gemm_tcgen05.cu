@@ -1,0 +1,443 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in
+// tensor memory), operands staged by TMA into a 128-byte-swizzled shared
+// memory ring.  One persistent CTA per SM, three warp roles:
+//   warp 0      TMA producer (one lane)
+//   warp 1      MMA issuer (one lane), owns the TMEM allocation
+//   warps 2..5  epilogue: TMEM -> registers -> global, one accumulator row per thread
+// Two accumulator buffers in TMEM let the epilogue of tile i overlap the main
+// loop of tile i+1.  Every wait is bounded (see common.cuh).
+//
+// D[M,N] = A[M,K] * B[N,K]^T with either operand optionally "MN-major"
+// (A stored as [K,M], B stored as [K,N]); this covers the forward, the
+// data-gradient and the weight-gradient products of a linear layer without
+// transposes in memory.  Stands in for the cuBLAS GEMMs behind every
+// nn.Linear of the reference (arctic_platform/model/patches/liger.py:25-36
+// keeps them on cuBLAS).
+#include "common.cuh"
+#include "host_utils.cuh"
+
+namespace apb {
+
+enum GemmEpilogue : int {
+  kEpiBf16 = 0,        // C(bf16) = alpha * acc (+ bias[n])
+  kEpiF32 = 1,         // C(f32)  = alpha * acc
+  kEpiF32Atomic = 2,   // C(f32) += alpha * acc  (red.add; split-K or shared accumulation)
+  kEpiF32Accum = 3,    // C(f32) += alpha * acc  (plain read-modify-write, one writer)
+  kEpiSwiGLU = 4,      // columns interleaved (gate, up): C2(bf16)[m, n/2] = silu(g) * u; C(bf16) = acc if C != null
+};
+
+struct GemmParams {
+  int M, N, K;
+  int a_mn, b_mn;
+  int epi;
+  int splits;
+  void* C;
+  long long ldc;
+  void* C2;
+  long long ldc2;
+  const __nv_bfloat16* bias;
+  float alpha;
+  // Optional tile table for grouped problems: {m0, m_end, b_row_offset, n_tile}.
+  const int4* tile_map;
+  int num_map_tiles;
+  int* status;
+};
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kTmemCols = 2 * BN;
+};
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* empty_bar = full_bar + Cfg::kStages;
+  uint64_t* tfull_bar = empty_bar + Cfg::kStages;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (p.M + kBM - 1) / kBM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int mn_tiles = p.tile_map ? p.num_map_tiles : tiles_m * tiles_n;
+  const int total_tiles = mn_tiles * p.splits;
+  const int k_blocks = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  // Tile decode shared by all roles.  Consecutive tile ids walk 8 m-tiles of
+  // one n-band before moving on, so CTAs running at the same time share B in L2.
+  auto decode = [&](int t, int& m0, int& m_end, int& b_row, int& n0, int& kb0, int& kb1) {
+    const int split = t / mn_tiles;
+    const int tt = t - split * mn_tiles;
+    kb0 = static_cast<int>((static_cast<long long>(k_blocks) * split) / p.splits);
+    kb1 = static_cast<int>((static_cast<long long>(k_blocks) * (split + 1)) / p.splits);
+    if (p.tile_map) {
+      const int4 e = p.tile_map[tt];
+      m0 = e.x;
+      m_end = e.y;
+      n0 = e.w * BN;
+      b_row = e.z + n0;
+    } else {
+      constexpr int G = 8;
+      const int per_group = G * tiles_n;
+      const int g = tt / per_group;
+      const int first_m = g * G;
+      const int gsize = min(tiles_m - first_m, G);
+      const int r = tt - g * per_group;
+      const int mi = first_m + r % gsize;
+      const int ni = r / gsize;
+      m0 = mi * kBM;
+      m_end = p.M;
+      n0 = ni * BN;
+      b_row = n0;
+    }
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int m0, m_end, b_row, n0, kb0, kb1;
+        decode(t, m0, m_end, b_row, n0, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kTimeoutEmpty)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          uint8_t* sb = sa + Cfg::kABytes;
+          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          if (!p.a_mn) {
+            tma_load_2d(sa, &tma_a, &full_bar[stage], kb * kBK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c)
+              tma_load_2d(sa + c * (64 * kBK * 2), &tma_a, &full_bar[stage], m0 + c * 64, kb * kBK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sb, &tma_b, &full_bar[stage], kb * kBK, b_row);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (64 * kBK * 2), &tma_b, &full_bar[stage], b_row + c * 64, kb * kBK);
+          }
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // Give copies already issued time to land before shared memory is released.
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 100000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(kBM, BN, p.a_mn, p.b_mn);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        int m0, m_end, b_row, n0, kb0, kb1;
+        decode(t, m0, m_end, b_row, n0, kb0, kb1);
+        const int buf = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[buf], acc_phase ^ 1, p.status, kTimeoutTmemEmpty)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status, kTimeoutFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t sb = sa + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t da = p.a_mn ? umma_smem_desc(sa + k * 2048, 64 * kBK * 2, 1024)
+                                       : umma_smem_desc(sa + k * 32, 0, 1024);
+            const uint64_t db = p.b_mn ? umma_smem_desc(sb + k * 2048, 64 * kBK * 2, 1024)
+                                       : umma_smem_desc(sb + k * 32, 0, 1024);
+            umma_bf16_ss(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == Cfg::kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(&tfull_bar[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // TMEM lanes this warp may read
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      int m0, m_end, b_row, n0, kb0, kb1;
+      decode(t, m0, m_end, b_row, n0, kb0, kb1);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[buf], acc_phase, p.status, kTimeoutTmemFull)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const bool row_ok = row < m_end;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        if (p.epi == kEpiBf16 || (p.epi == kEpiSwiGLU && p.C != nullptr)) {
+          if (p.bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+          }
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (col0 + q * 8 < p.N) {
+              uint4 o;
+              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              *reinterpret_cast<uint4*>(dst + q * 8) = o;
+            }
+          }
+        }
+        if (p.epi == kEpiSwiGLU) {
+          __nv_bfloat16* dst =
+              static_cast<__nv_bfloat16*>(p.C2) + static_cast<long long>(row) * p.ldc2 + (col0 >> 1);
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            if (col0 + q * 16 < p.N) {
+              float a[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) a[j] = silu_f(v[q * 16 + 2 * j]) * v[q * 16 + 2 * j + 1];
+              uint4 o;
+              o.x = pack_bf16x2(a[0], a[1]);
+              o.y = pack_bf16x2(a[2], a[3]);
+              o.z = pack_bf16x2(a[4], a[5]);
+              o.w = pack_bf16x2(a[6], a[7]);
+              *reinterpret_cast<uint4*>(dst + q * 8) = o;
+            }
+          }
+        } else if (p.epi == kEpiF32 || p.epi == kEpiF32Accum) {
+          float* dst = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            if (col0 + q * 4 < p.N) {
+              float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+              if (p.epi == kEpiF32Accum) {
+                const float4 old = *reinterpret_cast<const float4*>(dst + q * 4);
+                o.x += old.x;
+                o.y += old.y;
+                o.z += old.z;
+                o.w += old.w;
+              }
+              *reinterpret_cast<float4*>(dst + q * 4) = o;
+            }
+          }
+        } else if (p.epi == kEpiF32Atomic) {
+          float* dst = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            if (col0 + q * 4 < p.N)
+              atomicAdd(reinterpret_cast<float4*>(dst + q * 4),
+                        make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+}  // namespace apb
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+namespace apb {
+
+static int sm_count() {
+  static int n[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+  return n[dev] > 0 ? n[dev] : 148;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_ctas,
+                       cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured[dev & 63] = true;
+  }
+  const int tiles_m = (p.M + kBM - 1) / kBM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int mn_tiles = p.tile_map ? p.num_map_tiles : tiles_m * tiles_n;
+  const long long total = static_cast<long long>(mn_tiles) * p.splits;
+  int grid = static_cast<int>(total < sm_count() ? total : sm_count());
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  if (grid <= 0) return 0;
+  gemm_bf16_kernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace apb
+
+extern "C" {
+
+// D = alpha * op(A) * op(B)^T (+ epilogue).  bf16 operands.
+//   a_mn = 0: A is [M,K] row-major (lda >= K);  a_mn = 1: A is stored [K,M] (lda >= M)
+//   b_mn = 0: B is [N,K] row-major (ldb >= K);  b_mn = 1: B is stored [K,N] (ldb >= N)
+// All leading dimensions and N must be multiples of 8; bases 16-byte aligned.
+// tile_map (device, optional) has `num_map_tiles` int4 {m0, m_end, b_row_offset, n_tile}
+// entries and turns the launch into a grouped GEMM over row ranges of A/C with
+// per-group B row offsets (b_rows = total rows of the stacked B).
+// bn = 0 picks the tile width; splits > 1 needs an atomic fp32 epilogue.
+// max_ctas > 0 caps the grid (leaves SMs free for a concurrent kernel).
+int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                  long long ldc, int a_mn, int b_mn, int epi, int splits, float alpha, const void* bias,
+                  void* C2, long long ldc2, const void* tile_map, int num_map_tiles, long long b_rows, int bn,
+                  int max_ctas, cudaStream_t stream) {
+  using namespace apb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (N % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15))
+    return kBadArgument;
+  if (epi == kEpiBf16 || epi == kEpiSwiGLU) {
+    if (C && (ldc % 8)) return kBadArgument;
+  } else if (ldc % 4) {
+    return kBadArgument;
+  }
+  if (epi == kEpiSwiGLU && (!C2 || (ldc2 % 8) || (N % 16))) return kBadArgument;
+  const int k_blocks = (K + kBK - 1) / kBK;
+  if (splits < 1) splits = 1;
+  if (splits > k_blocks) splits = k_blocks;
+  if (splits > 1 && epi != kEpiF32Atomic) return kBadArgument;
+  if (bn == 0) {
+    const long long t256 = static_cast<long long>((M + kBM - 1) / kBM) * ((N + 255) / 256) * splits;
+    bn = (N >= 256 && t256 >= sm_count()) ? 256 : 128;
+    if (tile_map) bn = 128;
+  }
+  if (bn != 128 && bn != 256) return kBadArgument;
+
+  CUtensorMap ta, tb;
+  int rc;
+  if (!a_mn)
+    rc = make_tmap_2d(&ta, A, 2, static_cast<uint64_t>(M), static_cast<uint64_t>(K), lda, 64, kBM);
+  else
+    rc = make_tmap_2d(&ta, A, 2, static_cast<uint64_t>(K), static_cast<uint64_t>(M), lda, 64, 64);
+  if (rc) return 1000 + rc;
+  const uint64_t brows = b_rows > 0 ? static_cast<uint64_t>(b_rows) : static_cast<uint64_t>(N);
+  if (!b_mn)
+    rc = make_tmap_2d(&tb, B, 2, brows, static_cast<uint64_t>(K), ldb, 64, bn);
+  else
+    rc = make_tmap_2d(&tb, B, 2, static_cast<uint64_t>(K), brows, ldb, 64, 64);
+  if (rc) return 2000 + rc;
+
+  GemmParams p;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.a_mn = a_mn;
+  p.b_mn = b_mn;
+  p.epi = epi;
+  p.splits = splits;
+  p.C = C;
+  p.ldc = ldc;
+  p.C2 = C2;
+  p.ldc2 = ldc2;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.alpha = alpha;
+  p.tile_map = static_cast<const int4*>(tile_map);
+  p.num_map_tiles = num_map_tiles;
+  p.status = status_device_ptr();
+  return bn == 256 ? launch_gemm<256>(ta, tb, p, max_ctas, stream) : launch_gemm<128>(ta, tb, p, max_ctas, stream);
+}
+}

@@ -1,0 +1,28 @@
+// Host-side helpers shared by the .cu files: the kernel status word, the
+// driver entry point for tensor-map encoding and a 2-D bf16/fp8 tensor-map
+// builder with 128-byte swizzle.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace apb {
+
+// Device status word shared by every kernel of the library.  Defined once in
+// status.cu; kernels receive its device address as a parameter.
+int* status_device_ptr();
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn();
+
+// Row-major 2-D tensor [rows, cols] with `ld` elements between rows; box is
+// box_cols x box_rows elements, 128-byte swizzle (box_cols * elem_bytes must
+// be 128).  Returns 0 on success.
+int make_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
+                 uint32_t box_cols, uint32_t box_rows);
+
+}  // namespace apb

@@ -1,0 +1,166 @@
+"""ctypes access to the two native libraries.
+
+``cuda_lib()`` returns ``libapb200.so`` (kernels), ``rt_lib()`` returns
+``libapb200_rt.so`` (host runtime).  Both are built in-tree by
+:mod:`arctic_platform_b200._build`; if the shared object is missing and a
+compiler is present it is built on first use.  On a machine with a GPU a
+missing kernel library is an error, never a silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+import torch
+
+from .. import _build
+
+_lock = threading.Lock()
+_cuda = None
+_rt = None
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+class KernelError(RuntimeError):
+    """A kernel launch returned a non-zero code or the status word is set."""
+
+
+def _load(path: Path, builder):
+    if not path.exists():
+        try:
+            builder()
+        except Exception as exc:  # pragma: no cover - depends on toolchain
+            raise NativeLibraryError(f"{path.name} is missing and could not be built: {exc}") from exc
+    try:
+        return ctypes.CDLL(str(path))
+    except OSError as exc:
+        raise NativeLibraryError(f"cannot load {path}: {exc}") from exc
+
+
+def cuda_lib() -> ctypes.CDLL:
+    global _cuda
+    if _cuda is None:
+        with _lock:
+            if _cuda is None:
+                lib = _load(_build.CUDA_LIB, _build.build_cuda)
+                _declare_cuda(lib)
+                _cuda = lib
+    return _cuda
+
+
+def rt_lib() -> ctypes.CDLL:
+    global _rt
+    if _rt is None:
+        with _lock:
+            if _rt is None:
+                lib = _load(_build.RT_LIB, _build.build_runtime)
+                _declare_rt(lib)
+                _rt = lib
+    return _rt
+
+
+def cuda_available() -> bool:
+    return torch.cuda.is_available()
+
+
+def stream_ptr(stream=None) -> ctypes.c_void_p:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return ctypes.c_void_p(s.cuda_stream)
+
+
+def ptr(t) -> ctypes.c_void_p:
+    if t is None:
+        return ctypes.c_void_p(0)
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what} failed with code {code}")
+
+
+def status_read() -> int:
+    return int(cuda_lib().apb_status_read())
+
+
+def status_clear() -> None:
+    cuda_lib().apb_status_clear()
+
+
+def check_status(what: str = "kernel") -> None:
+    """Synchronises and raises if any kernel recorded an error (e.g. a bounded wait ran out)."""
+    torch.cuda.synchronize()
+    st = status_read()
+    if st != 0:
+        status_clear()
+        raise KernelError(f"{what}: device status word = {st}")
+
+
+c_vp = ctypes.c_void_p
+c_i = ctypes.c_int
+c_ll = ctypes.c_longlong
+c_f = ctypes.c_float
+c_sz = ctypes.c_size_t
+
+
+def _sig(lib, name, argtypes, restype=ctypes.c_int):
+    fn = getattr(lib, name, None)
+    if fn is None:
+        return
+    fn.argtypes = argtypes
+    fn.restype = restype
+
+
+def _declare_cuda(lib) -> None:
+    _sig(lib, "apb_status_read", [])
+    _sig(lib, "apb_status_clear", [])
+    _sig(lib, "apb_version", [])
+    _sig(lib, "apb_fill_u32", [c_vp, c_sz, ctypes.c_uint32, c_vp])
+    _sig(lib, "apb_gemm_bf16",
+         [c_vp, c_vp, c_vp, c_i, c_i, c_i, c_ll, c_ll, c_ll, c_i, c_i, c_i, c_i, c_f, c_vp,
+          c_vp, c_ll, c_vp, c_i, c_ll, c_i, c_i, c_vp])
+    _sig(lib, "apb_rmsnorm_fwd", [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i, c_i, c_f, c_f, c_vp])
+    _sig(lib, "apb_rmsnorm_bwd", [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i, c_i, c_f, c_vp])
+    _sig(lib, "apb_qknorm_rope_fwd",
+         [c_vp, c_ll, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i, c_i, c_i, c_i, c_i, c_f, c_vp])
+    _sig(lib, "apb_qknorm_rope_bwd",
+         [c_vp, c_ll, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_ll, c_vp, c_vp,
+          c_i, c_i, c_i, c_i, c_i, c_f, c_vp])
+    _sig(lib, "apb_swiglu_fwd", [c_vp, c_vp, c_ll, c_ll, c_vp])
+    _sig(lib, "apb_swiglu_bwd", [c_vp, c_vp, c_vp, c_ll, c_ll, c_vp])
+    # later kernels declare themselves from their wrapper modules through declare()
+
+
+def declare(name: str, argtypes, restype=ctypes.c_int):
+    """Declares the signature of an exported kernel entry point and returns it."""
+    lib = cuda_lib()
+    fn = getattr(lib, name, None)
+    if fn is None:
+        raise NativeLibraryError(f"{name} is not exported by {_build.CUDA_LIB.name}; rebuild the library")
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+def _declare_rt(lib) -> None:
+    i32p = ctypes.POINTER(ctypes.c_int32)
+    i64p = ctypes.POINTER(ctypes.c_int64)
+    f64p = ctypes.POINTER(ctypes.c_double)
+    _sig(lib, "apb_rt_pages_create", [ctypes.c_int32], c_vp)
+    _sig(lib, "apb_rt_pages_destroy", [c_vp], None)
+    _sig(lib, "apb_rt_pages_free_count", [c_vp], ctypes.c_int32)
+    _sig(lib, "apb_rt_pages_alloc", [c_vp, ctypes.c_int32, i32p], ctypes.c_int32)
+    _sig(lib, "apb_rt_pages_retain", [c_vp, ctypes.c_int32, i32p], ctypes.c_int32)
+    _sig(lib, "apb_rt_pages_release", [c_vp, ctypes.c_int32, i32p], ctypes.c_int32)
+    _sig(lib, "apb_rt_pages_refcount", [c_vp, ctypes.c_int32], ctypes.c_int32)
+    _sig(lib, "apb_rt_ffd_pack", [i64p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, i32p],
+         ctypes.c_int32)
+    _sig(lib, "apb_rt_group_prompts", [i64p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, i32p],
+         ctypes.c_int32)
+    _sig(lib, "apb_rt_balance_groups", [f64p, i32p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, i32p],
+         ctypes.c_int32)
+    _sig(lib, "apb_rt_version", [], ctypes.c_int32)
