@@ -89,8 +89,9 @@ def test_grouped_tile_map():
     _lib.check_status("gemm grouped")
     row = 0
     for e, c in enumerate(counts):
-        ref = x[row:row + c].float() @ w[e * N:(e + 1) * N].float().t()
-        _close(out[row:row + c], ref, K)
+        if c:
+            ref = x[row:row + c].float() @ w[e * N:(e + 1) * N].float().t()
+            _close(out[row:row + c], ref, K)
         row += c
 
 
