@@ -322,11 +322,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       tc_fence_before();
       mbar_arrive(dq_read);
     }
-    // dK / dV of this block
+    // dK / dV of this block.  The TMEM loads are warp collectives: every lane runs them, only the
+    // global stores are predicated on the row being inside the block.
+    ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
     if (ok) {
       if (n_iter > 0) ok = mbar_wait(dkv_full, 0, p.status, kTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
       tc_fence_after();
-      if (ok && row_ok) {
+      if (ok) {
         __nv_bfloat16* dkp = p.dk + (static_cast<long long>(kv_row0) + r) * p.ld_dk + static_cast<long long>(kvh) * D;
         __nv_bfloat16* dvp = p.dv + (static_cast<long long>(kv_row0) + r) * p.ld_dv + static_cast<long long>(kvh) * D;
 #pragma unroll 1
@@ -336,21 +339,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 #pragma unroll 1
           for (int h = 0; h < D / 32; ++h) {
             uint32_t v[32];
-            if (n_iter > 0) {
+            if (n_iter > 0) {  // uniform across the CTA
               tmem_ld_32x32(tmem_base + lane_off + col0 + h * 32, v);
               tmem_ld_wait();
             } else {
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] = 0u;
             }
+            if (row_ok) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-              o.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-              o.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-              o.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
-              *reinterpret_cast<uint4*>(dst + h * 32 + q * 8) = o;
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack_bf16x2(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+                o.y = pack_bf16x2(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+                o.z = pack_bf16x2(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+                o.w = pack_bf16x2(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+                *reinterpret_cast<uint4*>(dst + h * 32 + q * 8) = o;
+              }
             }
           }
         }

@@ -24,6 +24,8 @@ enum GemmEpilogue : int {
   kEpiF32Atomic = 2,   // C(f32) += alpha * acc  (red.add; split-K or shared accumulation)
   kEpiF32Accum = 3,    // C(f32) += alpha * acc  (plain read-modify-write, one writer)
   kEpiSwiGLU = 4,      // columns interleaved (gate, up): C2(bf16)[m, n/2] = silu(g) * u; C(bf16) = acc if C != null
+  kEpiLogprobPartial = 5,  // per row and 128-column tile: (max, sum exp, sum exp*z, label z) of z = acc*alpha*row_scale
+  kEpiDlogits = 6,         // C(bf16) = d loss / d acc for log-prob / entropy heads (see lm-head section below)
 };
 
 struct GemmParams {
@@ -41,6 +43,14 @@ struct GemmParams {
   const int4* tile_map;
   int num_map_tiles;
   int* status;
+  // log-prob epilogues
+  const float* row_scale;  // [M] per-row multiplier of the logits (inverse temperature) or null
+  const int* labels;       // [M]
+  float* partial;          // [M][tiles_n][4]
+  const float* row_lse;    // [M] log-sum-exp of the scaled logits
+  const float* row_ent;    // [M] entropy
+  const float* row_glp;    // [M] upstream gradient of the log-prob
+  const float* row_gent;   // [M] upstream gradient of the entropy, or null
 };
 
 constexpr int kBM = 128;
@@ -240,6 +250,92 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < m_end;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+      if (p.epi == kEpiLogprobPartial) {
+        // BN == 128 here: one partial record per row and tile
+        const float rs = p.alpha * ((p.row_scale && row_ok) ? p.row_scale[row] : 1.f);
+        const int label = row_ok ? p.labels[row] : -1;
+        float m_run = -INFINITY, s_run = 0.f, e_run = 0.f, lab = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          float z[32];
+          float cm = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            z[j] = (col0 + j < p.N) ? __uint_as_float(r[j]) * rs : -INFINITY;
+            cm = fmaxf(cm, z[j]);
+            if (col0 + j == label) lab = z[j];
+          }
+          const float m_new = fmaxf(m_run, cm);
+          const float corr = __expf(m_run - m_new);
+          float cs = 0.f, ce = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float ex = (col0 + j < p.N) ? __expf(z[j] - m_new) : 0.f;
+            cs += ex;
+            ce += (col0 + j < p.N) ? ex * z[j] : 0.f;
+          }
+          s_run = s_run * corr + cs;
+          e_run = e_run * corr + ce;
+          m_run = m_new;
+        }
+        if (row_ok) {
+          const int tiles_n_ = (p.N + BN - 1) / BN;
+          float4* dst = reinterpret_cast<float4*>(p.partial) + static_cast<long long>(row) * tiles_n_ + n0 / BN;
+          *dst = make_float4(m_run, s_run, e_run, lab);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+        continue;
+      }
+      if (p.epi == kEpiDlogits) {
+        const float it = (p.row_scale && row_ok) ? p.row_scale[row] : 1.f;
+        const float rs = p.alpha * it;
+        const int label = row_ok ? p.labels[row] : -1;
+        const float lse = row_ok ? p.row_lse[row] : 0.f;
+        const float ent = row_ok ? p.row_ent[row] : 0.f;
+        const float glp = row_ok ? p.row_glp[row] : 0.f;
+        const float gent = (row_ok && p.row_gent) ? p.row_gent[row] : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (!row_ok) continue;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float z = __uint_as_float(r[j]) * rs;
+            const float pj = __expf(z - lse);
+            float g = -glp * pj - gent * pj * (z - lse + ent);
+            if (col0 + j == label) g += glp;
+            v[j] = g * rs;
+          }
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (col0 + q * 8 < p.N) {
+              uint4 o;
+              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+              *reinterpret_cast<uint4*>(dst + q * 8) = o;
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = n0 + c * 32;
@@ -438,6 +534,128 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   p.tile_map = static_cast<const int4*>(tile_map);
   p.num_map_tiles = num_map_tiles;
   p.status = status_device_ptr();
+  p.row_scale = nullptr;
+  p.labels = nullptr;
+  p.partial = nullptr;
+  p.row_lse = p.row_ent = p.row_glp = p.row_gent = nullptr;
   return bn == 256 ? launch_gemm<256>(ta, tb, p, max_ctas, stream) : launch_gemm<128>(ta, tb, p, max_ctas, stream);
+}
+}
+
+// ---------------------------------------------------------------------------
+// lm_head + log-softmax + label gather + entropy
+// ---------------------------------------------------------------------------
+namespace apb {
+
+// Combines the per-tile partials of one row: lse, log-prob of the label, entropy = lse - E[z].
+__global__ void lmhead_combine_kernel(const float4* __restrict__ partial, int tiles, float* __restrict__ lp,
+                                      float* __restrict__ ent, float* __restrict__ lse_out, int M) {
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const float4* pr = partial + static_cast<long long>(row) * tiles;
+  float m = -INFINITY, s = 0.f, e = 0.f, lab = -INFINITY;
+  for (int t = lane; t < tiles; t += 32) {
+    const float4 v = pr[t];
+    const float mn = fmaxf(m, v.x);
+    const float c0 = (m == -INFINITY) ? 0.f : __expf(m - mn);
+    const float c1 = (v.x == -INFINITY) ? 0.f : __expf(v.x - mn);
+    s = s * c0 + v.y * c1;
+    e = e * c0 + v.z * c1;
+    m = mn;
+    lab = fmaxf(lab, v.w);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+    const float s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    const float e2 = __shfl_xor_sync(0xffffffffu, e, o);
+    const float l2 = __shfl_xor_sync(0xffffffffu, lab, o);
+    const float mn = fmaxf(m, m2);
+    const float c0 = (m == -INFINITY) ? 0.f : __expf(m - mn);
+    const float c1 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
+    s = s * c0 + s2 * c1;
+    e = e * c0 + e2 * c1;
+    m = mn;
+    lab = fmaxf(lab, l2);
+  }
+  if (lane == 0) {
+    const float lse = m + logf(s);
+    lse_out[row] = lse;
+    lp[row] = lab - lse;
+    ent[row] = lse - e / s;
+  }
+}
+
+static int lmhead_launch(const void* hidden, const void* weight, int M, int V, int H, long long ldh, long long ldw,
+                         GemmParams& p, int bn, cudaStream_t stream) {
+  if ((ldh % 8) || (ldw % 8) || (V % 8)) return kBadArgument;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, hidden, 2, M, H, ldh, 64, kBM);
+  if (rc) return 1000 + rc;
+  rc = make_tmap_2d(&tb, weight, 2, V, H, ldw, 64, bn);
+  if (rc) return 2000 + rc;
+  p.M = M;
+  p.N = V;
+  p.K = H;
+  p.a_mn = 0;
+  p.b_mn = 0;
+  p.splits = 1;
+  p.C2 = nullptr;
+  p.ldc2 = 0;
+  p.bias = nullptr;
+  p.tile_map = nullptr;
+  p.num_map_tiles = 0;
+  p.status = status_device_ptr();
+  return bn == 256 ? launch_gemm<256>(ta, tb, p, 0, stream) : launch_gemm<128>(ta, tb, p, 0, stream);
+}
+
+}  // namespace apb
+
+extern "C" {
+
+// hidden [M,H] bf16, weight [V,H] bf16, labels [M] int32, row_scale [M] fp32 or null (then `scale` applies).
+// partial: fp32 scratch [M][ceil(V/128)][4].  Outputs lp/ent/lse fp32 [M].
+int apb_lmhead_logprob_fwd(const void* hidden, const void* weight, const int* labels, const float* row_scale,
+                           float* partial, float* lp, float* ent, float* lse, int M, int V, int H, long long ldh,
+                           long long ldw, float scale, cudaStream_t stream) {
+  using namespace apb;
+  if (M <= 0) return 0;
+  GemmParams p{};
+  p.epi = kEpiLogprobPartial;
+  p.alpha = scale;
+  p.C = nullptr;
+  p.ldc = 0;
+  p.row_scale = row_scale;
+  p.labels = labels;
+  p.partial = partial;
+  int rc = lmhead_launch(hidden, weight, M, V, H, ldh, ldw, p, 128, stream);
+  if (rc) return rc;
+  const int tiles = (V + 127) / 128;
+  const int grid = (M * 32 + 255) / 256;
+  lmhead_combine_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float4*>(partial), tiles, lp, ent, lse, M);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// dlogits [M,V] bf16 (row stride ldd) = d loss / d (hidden @ weight^T) given upstream g_lp, g_ent (null = 0).
+int apb_lmhead_dlogits(const void* hidden, const void* weight, const int* labels, const float* row_scale,
+                       const float* lse, const float* ent, const float* g_lp, const float* g_ent, void* dlogits,
+                       int M, int V, int H, long long ldh, long long ldw, long long ldd, float scale,
+                       cudaStream_t stream) {
+  using namespace apb;
+  if (M <= 0) return 0;
+  if (ldd % 8) return kBadArgument;
+  GemmParams p{};
+  p.epi = kEpiDlogits;
+  p.alpha = scale;
+  p.C = dlogits;
+  p.ldc = ldd;
+  p.row_scale = row_scale;
+  p.labels = labels;
+  p.row_lse = lse;
+  p.row_ent = ent;
+  p.row_glp = g_lp;
+  p.row_gent = g_ent;
+  return lmhead_launch(hidden, weight, M, V, H, ldh, ldw, p, 256, stream);
 }
 }

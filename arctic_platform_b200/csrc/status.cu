@@ -80,5 +80,20 @@ int apb_fill_u32(void* buf, size_t bytes, uint32_t value, cudaStream_t stream) {
   return static_cast<int>(cudaGetLastError());
 }
 
+// Makes `dev` the current device of the calling thread for this library's CUDA runtime instance.
+// The Python wrappers call it before every launch: autograd worker threads and freshly started
+// threads have no device bound in this (statically linked) runtime, and tensor-map encoding needs
+// a current context.
+int apb_bind_device(int dev) {
+  static thread_local int bound = -1;
+  if (bound == dev) return 0;
+  cudaError_t e = cudaSetDevice(dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaFree(0);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  bound = dev;
+  return 0;
+}
+
 int apb_version() { return 1; }
 }

@@ -1,0 +1,149 @@
+"""Model architecture descriptions.
+
+``DecoderConfig`` covers the Qwen3 dense family and the Qwen3-MoE family (the
+architectures named by the benchmark configurations); ``from_hf_dict`` reads a
+Hugging Face ``config.json`` so HF safetensors checkpoints load without the
+``transformers`` model classes.  The reference resolves models through
+``AutoModelForCausalLM`` (arctic_platform/model/loaders/huggingface.py:26-43) and a
+Qwen3.5-MoE carve-out (arctic_platform/model/loaders/qwen3_5_moe.py:93-123).
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+from typing import Any, Dict, Optional
+
+
+@dataclass
+class DecoderConfig:
+    vocab_size: int = 151936
+    hidden_size: int = 2560
+    intermediate_size: int = 9728
+    num_layers: int = 36
+    num_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    tie_word_embeddings: bool = True
+    qk_norm: bool = True
+    max_position_embeddings: int = 40960
+    # mixture of experts (0 experts = dense)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    model_type: str = "qwen3"
+    name: str = "qwen3"
+
+    @property
+    def q_size(self) -> int:
+        return self.num_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    @property
+    def qkv_size(self) -> int:
+        return self.q_size + 2 * self.kv_size
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def num_parameters(self, include_embeddings: bool = True) -> int:
+        H, L = self.hidden_size, self.num_layers
+        attn = self.qkv_size * H + H * self.q_size + (2 * self.head_dim if self.qk_norm else 0)
+        if self.is_moe:
+            mlp = self.num_experts * 3 * H * self.moe_intermediate_size + self.num_experts * H
+        else:
+            mlp = 3 * H * self.intermediate_size
+        per_layer = attn + mlp + 2 * H
+        total = L * per_layer + H
+        if include_embeddings:
+            total += self.vocab_size * H * (1 if self.tie_word_embeddings else 2)
+        return total
+
+    def flops_per_token(self, seq_len: int = 0, backward: bool = True) -> float:
+        """Matmul FLOPs per token (2 x active weights) plus causal attention at ``seq_len``; x3 with backward."""
+        H, L = self.hidden_size, self.num_layers
+        attn_w = self.qkv_size * H + H * self.q_size
+        mlp_w = (self.num_experts_per_tok * 3 * H * self.moe_intermediate_size if self.is_moe
+                 else 3 * H * self.intermediate_size)
+        dense = 2.0 * (L * (attn_w + mlp_w) + self.vocab_size * H)
+        attn = 2.0 * 2.0 * L * self.num_heads * self.head_dim * seq_len / 2.0
+        return (dense + attn) * (3.0 if backward else 1.0)
+
+    def to_dict(self) -> Dict[str, Any]:
+        return asdict(self)
+
+    @staticmethod
+    def from_hf_dict(d: Dict[str, Any], name: str = "") -> "DecoderConfig":
+        mt = d.get("model_type", "qwen3")
+        heads = d["num_attention_heads"]
+        return DecoderConfig(
+            vocab_size=d["vocab_size"], hidden_size=d["hidden_size"],
+            intermediate_size=d.get("intermediate_size", 0), num_layers=d["num_hidden_layers"],
+            num_heads=heads, num_kv_heads=d.get("num_key_value_heads", heads),
+            head_dim=d.get("head_dim", d["hidden_size"] // heads), rms_norm_eps=d.get("rms_norm_eps", 1e-6),
+            rope_theta=float(d.get("rope_theta", 1e6)), tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
+            qk_norm=mt.startswith("qwen3"), max_position_embeddings=d.get("max_position_embeddings", 40960),
+            num_experts=d.get("num_experts", 0) or 0, num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
+            moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0,
+            norm_topk_prob=bool(d.get("norm_topk_prob", True)), model_type=mt, name=name or mt)
+
+    def to_hf_dict(self) -> Dict[str, Any]:
+        d = {
+            "architectures": ["Qwen3MoeForCausalLM" if self.is_moe else "Qwen3ForCausalLM"],
+            "model_type": "qwen3_moe" if self.is_moe else "qwen3",
+            "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+            "intermediate_size": self.intermediate_size, "num_hidden_layers": self.num_layers,
+            "num_attention_heads": self.num_heads, "num_key_value_heads": self.num_kv_heads,
+            "head_dim": self.head_dim, "rms_norm_eps": self.rms_norm_eps, "rope_theta": self.rope_theta,
+            "tie_word_embeddings": self.tie_word_embeddings, "max_position_embeddings": self.max_position_embeddings,
+            "hidden_act": "silu", "torch_dtype": "bfloat16", "attention_bias": False,
+        }
+        if self.is_moe:
+            d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
+                     moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob)
+        return d
+
+
+PRESETS: Dict[str, DecoderConfig] = {
+    # CPU plumbing model of the first benchmark configuration
+    "qwen3-tiny": DecoderConfig(vocab_size=32000, hidden_size=256, intermediate_size=688, num_layers=2, num_heads=4,
+                                num_kv_heads=2, head_dim=64, name="qwen3-tiny"),
+    # same proportions with head_dim 128 so the GPU attention backward applies
+    "qwen3-tiny-d128": DecoderConfig(vocab_size=32000, hidden_size=256, intermediate_size=688, num_layers=2,
+                                     num_heads=4, num_kv_heads=2, head_dim=128, name="qwen3-tiny-d128"),
+    "qwen3-0.6b": DecoderConfig(hidden_size=1024, intermediate_size=3072, num_layers=28, num_heads=16, num_kv_heads=8,
+                                name="qwen3-0.6b"),
+    "qwen3-1.7b": DecoderConfig(hidden_size=2048, intermediate_size=6144, num_layers=28, num_heads=16, num_kv_heads=8,
+                                name="qwen3-1.7b"),
+    "qwen3-4b": DecoderConfig(hidden_size=2560, intermediate_size=9728, num_layers=36, num_heads=32, num_kv_heads=8,
+                              name="qwen3-4b"),
+    "qwen3-8b": DecoderConfig(hidden_size=4096, intermediate_size=12288, num_layers=36, num_heads=32, num_kv_heads=8,
+                              tie_word_embeddings=False, name="qwen3-8b"),
+    "qwen3-32b": DecoderConfig(hidden_size=5120, intermediate_size=25600, num_layers=64, num_heads=64, num_kv_heads=8,
+                               tie_word_embeddings=False, name="qwen3-32b"),
+    "qwen3-30b-a3b": DecoderConfig(hidden_size=2048, intermediate_size=6144, num_layers=48, num_heads=32,
+                                   num_kv_heads=4, tie_word_embeddings=False, num_experts=128, num_experts_per_tok=8,
+                                   moe_intermediate_size=768, model_type="qwen3_moe", name="qwen3-30b-a3b"),
+    "qwen3-moe-tiny": DecoderConfig(vocab_size=32000, hidden_size=256, intermediate_size=688, num_layers=2,
+                                    num_heads=4, num_kv_heads=2, head_dim=128, num_experts=8, num_experts_per_tok=2,
+                                    moe_intermediate_size=128, model_type="qwen3_moe", name="qwen3-moe-tiny"),
+}
+
+
+def resolve_config(model_name_or_path: str) -> DecoderConfig:
+    """Preset name (case-insensitive, with or without an ``org/`` prefix) or a directory with ``config.json``."""
+    p = Path(model_name_or_path)
+    if p.is_dir() and (p / "config.json").exists():
+        return DecoderConfig.from_hf_dict(json.loads((p / "config.json").read_text()), name=p.name)
+    key = model_name_or_path.split("/")[-1].lower()
+    if key in PRESETS:
+        return PRESETS[key]
+    raise ValueError(f"unknown model {model_name_or_path!r}: give a preset ({sorted(PRESETS)}) or a directory "
+                     "containing config.json")

@@ -1,0 +1,186 @@
+"""Qwen3-style decoder on the packed token axis.
+
+The model never sees a padded ``[B, S]`` batch: it takes ``input_ids [T]``,
+``positions [T]`` and an :class:`~arctic_platform_b200.ops.attention.AttnLayout`
+that says which rows attend to which key ranges.  Plain packed batches and
+ZoRRo prompt-deduplicated batches differ only in that layout, so there is no
+model patching step (the reference monkey-patches every attention module and the
+backbone forward: arctic_platform/rl/zorro_train/qwen_model_patcher.py:255-717).
+
+Weights are kept in the fused layouts the kernels want -- ``wqkv`` (q|k|v rows),
+``wgu`` (gate/up rows interleaved so SwiGLU runs in the GEMM epilogue) -- and are
+converted from / to Hugging Face names in :mod:`arctic_platform_b200.models.hf_io`.
+On CPU tensors every op falls through to its fp32 PyTorch expression, which makes
+this same module the numerical oracle.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Iterator, List, Optional, Tuple
+
+import torch
+from torch import nn
+
+from ..ops import gemm, norm
+from ..ops.attention import AttnLayout, segment_attention
+from .config import DecoderConfig
+
+
+class _GateUpSwiGLUFn(torch.autograd.Function):
+    """act = silu(x Wg^T) * (x Wu^T) with Wg/Wu rows interleaved in ``wgu``; the activation is
+    produced by the GEMM epilogue, the pre-activations are kept for the backward."""
+
+    @staticmethod
+    def forward(ctx, x, wgu):
+        gu, act = gemm.gate_up_swiglu(x, wgu, keep_gu=True)
+        ctx.save_for_backward(x, wgu, gu)
+        return act
+
+    @staticmethod
+    def backward(ctx, dact):
+        x, wgu, gu = ctx.saved_tensors
+        from ..ops import _lib
+        dact = dact.contiguous()
+        dgu = torch.empty_like(gu)
+        T, I2 = gu.shape
+        _lib.check(_lib.cuda_lib().apb_swiglu_bwd(_lib.ptr(gu), _lib.ptr(dact), _lib.ptr(dgu), T, I2 // 2,
+                                                  _lib.stream_ptr()), "swiglu_bwd")
+        dx = gemm.matmul_nn(dgu, wgu) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            acc = getattr(wgu, "grad_f32", None)
+            if acc is not None:
+                gemm.matmul_tn(dgu, x, out=acc, accumulate=True)
+            else:
+                dw = gemm.matmul_tn(dgu, x)
+        return dx, dw
+
+
+def gate_up_act(x: torch.Tensor, wgu: torch.Tensor) -> torch.Tensor:
+    if not x.is_cuda:
+        gu = x @ wgu.t()
+        return torch.nn.functional.silu(gu[..., 0::2]) * gu[..., 1::2]
+    return _GateUpSwiGLUFn.apply(x, wgu)
+
+
+class DecoderBlock(nn.Module):
+    def __init__(self, cfg: DecoderConfig, layer_idx: int, device, dtype):
+        super().__init__()
+        self.cfg = cfg
+        self.layer_idx = layer_idx
+        H, D = cfg.hidden_size, cfg.head_dim
+        mk = lambda *s: nn.Parameter(torch.empty(*s, device=device, dtype=dtype))
+        self.ln1 = mk(H)
+        self.wqkv = mk(cfg.qkv_size, H)
+        self.q_norm = mk(D) if cfg.qk_norm else None
+        self.k_norm = mk(D) if cfg.qk_norm else None
+        self.wo = mk(H, cfg.q_size)
+        self.ln2 = mk(H)
+        if cfg.is_moe:
+            from .moe import MoEFeedForward
+            self.mlp = MoEFeedForward(cfg, device, dtype)
+            self.wgu = self.wdown = None
+        else:
+            self.mlp = None
+            self.wgu = mk(2 * cfg.intermediate_size, H)
+            self.wdown = mk(H, cfg.intermediate_size)
+
+    def forward(self, x, stream, positions, layout: AttnLayout, rope):
+        """``x`` is the previous sublayer output, ``stream`` the residual stream before adding it
+        (None for the first block).  Returns the MLP output and the updated stream."""
+        cfg = self.cfg
+        h, stream = norm.rmsnorm(x, self.ln1, cfg.rms_norm_eps, stream)
+        qkv = gemm.linear(h, self.wqkv)
+        q, k, v = norm.qknorm_rope(qkv, self.q_norm, self.k_norm, rope[0], rope[1], positions, cfg.num_heads,
+                                   cfg.num_kv_heads, cfg.head_dim, cfg.rms_norm_eps)
+        a = segment_attention(q, k, v, layout)
+        o = gemm.linear(a.reshape(a.shape[0], -1), self.wo)
+        h2, stream = norm.rmsnorm(o, self.ln2, cfg.rms_norm_eps, stream)
+        if self.mlp is not None:
+            d = self.mlp(h2)
+        else:
+            d = gemm.linear(gate_up_act(h2, self.wgu), self.wdown)
+        return d, stream
+
+
+class DecoderLM(nn.Module):
+    def __init__(self, cfg: DecoderConfig, device="cpu", dtype=torch.float32, max_positions: Optional[int] = None):
+        super().__init__()
+        self.cfg = cfg
+        H = cfg.hidden_size
+        self.embed = nn.Parameter(torch.empty(cfg.vocab_size, H, device=device, dtype=dtype))
+        self.blocks = nn.ModuleList([DecoderBlock(cfg, i, device, dtype) for i in range(cfg.num_layers)])
+        self.final_norm = nn.Parameter(torch.empty(H, device=device, dtype=dtype))
+        self.lm_head = None if cfg.tie_word_embeddings else nn.Parameter(
+            torch.empty(cfg.vocab_size, H, device=device, dtype=dtype))
+        self._rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+        self._rope_len = max_positions or min(cfg.max_position_embeddings, 40960)
+        self.gradient_checkpointing = False
+
+    # ------------------------------------------------------------------ init
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0, std: float = 0.02) -> "DecoderLM":
+        """Deterministic normal(0, std) init keyed by parameter name, so the values do not depend on
+        how the model is later sharded (norm weights are ones)."""
+        for name, p in self.named_parameters():
+            if p.dim() == 1 and not name.endswith("router_bias"):
+                p.fill_(1.0)
+                continue
+            g = torch.Generator(device="cpu")
+            g.manual_seed((hash_name(name) + seed) % (2 ** 31))
+            chunk = 1 << 24
+            flat = p.data.view(-1)
+            for s in range(0, flat.numel(), chunk):
+                n = min(chunk, flat.numel() - s)
+                flat[s:s + n].copy_((torch.randn(n, generator=g, dtype=torch.float32) * std).to(p.dtype))
+        return self
+
+    def rope(self, device) -> Tuple[torch.Tensor, torch.Tensor]:
+        if self._rope is None or self._rope[0].device != torch.device(device):
+            self._rope = norm.rope_tables(self._rope_len, self.cfg.head_dim, self.cfg.rope_theta, device)
+        return self._rope
+
+    @property
+    def output_weight(self) -> torch.Tensor:
+        return self.embed if self.lm_head is None else self.lm_head
+
+    # --------------------------------------------------------------- forward
+    def forward_hidden(self, input_ids: torch.Tensor, positions: torch.Tensor, layout: AttnLayout) -> torch.Tensor:
+        """Final-norm hidden states ``[T, H]`` for packed ``input_ids [T]``."""
+        x = torch.nn.functional.embedding(input_ids, self.embed)
+        rope = self.rope(x.device)
+        positions = positions.to(torch.int32) if x.is_cuda else positions
+        stream = None
+        for blk in self.blocks:
+            if self.gradient_checkpointing and torch.is_grad_enabled():
+                from torch.utils.checkpoint import checkpoint
+                x, stream = checkpoint(blk, x, stream, positions, layout, rope, use_reentrant=False)
+            else:
+                x, stream = blk(x, stream, positions, layout, rope)
+        h, _ = norm.rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, stream)
+        return h
+
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        """Full logits ``[N, V]`` in fp32 -- small inputs / tests only; training and scoring use
+        :func:`arctic_platform_b200.ops.logprob.lm_head_logprobs` which never forms this tensor."""
+        if hidden.is_cuda:
+            return gemm.matmul_nt(hidden.contiguous(), self.output_weight, out_dtype=torch.float32)
+        return hidden.float() @ self.output_weight.float().t()
+
+
+def hash_name(name: str) -> int:
+    h = 2166136261
+    for ch in name.encode():
+        h = ((h ^ ch) * 16777619) & 0xFFFFFFFF
+    return h
+
+
+def token_logprobs(model: DecoderLM, packed, inv_temperature=1.0, with_entropy: bool = True):
+    """Log-probabilities (and entropies) of ``packed.labels`` under ``model``; ``packed`` is a
+    :class:`~arctic_platform_b200.rl.zorro_train.layout.PackedBatch` already on the model's device.
+    Returns fp32 tensors of shape ``[N]`` in original sample order."""
+    from ..ops.logprob import lm_head_logprobs
+
+    hidden = model.forward_hidden(packed.input_ids, packed.positions, packed.layout)
+    pred = hidden.index_select(0, packed.pred_index)
+    return lm_head_logprobs(pred, model.output_weight, packed.labels, inv_temperature, with_entropy)

@@ -1,0 +1,240 @@
+"""Hugging Face weight names <-> the fused layouts of :class:`DecoderLM`.
+
+On disk and on the trainer->sampler sync path weights travel under their Hugging Face
+names (``model.layers.N.self_attn.q_proj.weight`` ...), the same contract the reference
+keeps for checkpoints (``save_pretrained(..., safe_serialization=True)``,
+arctic_platform/common/deepspeed_worker.py:602-636) and for weight sync (310 tensors
+for Qwen3-1.7B, arctic_platform/integrations/verl/README.md:96-98).  In memory the
+kernels want fused tensors: ``wqkv`` = rows [q | k | v], ``wgu`` = gate and up rows
+interleaved (row 2j = gate_j, row 2j+1 = up_j).  This module is the table between the two.
+"""
+from __future__ import annotations
+
+import json
+import struct
+from pathlib import Path
+from typing import Callable, Dict, Iterator, List, Optional, Tuple
+
+import torch
+
+from .config import DecoderConfig
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    return torch.stack([gate, up], dim=1).reshape(2 * gate.shape[0], *gate.shape[1:])
+
+
+def split_gate_up(wgu: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    return wgu[0::2], wgu[1::2]
+
+
+def hf_param_names(cfg: DecoderConfig) -> List[str]:
+    """Every Hugging Face tensor name of the architecture, in layer order."""
+    names = ["model.embed_tokens.weight"]
+    for i in range(cfg.num_layers):
+        p = f"model.layers.{i}."
+        names += [p + "input_layernorm.weight", p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight",
+                  p + "self_attn.v_proj.weight"]
+        if cfg.qk_norm:
+            names += [p + "self_attn.q_norm.weight", p + "self_attn.k_norm.weight"]
+        names += [p + "self_attn.o_proj.weight", p + "post_attention_layernorm.weight"]
+        if cfg.is_moe:
+            names.append(p + "mlp.gate.weight")
+            for e in range(cfg.num_experts):
+                names += [p + f"mlp.experts.{e}.gate_proj.weight", p + f"mlp.experts.{e}.up_proj.weight",
+                          p + f"mlp.experts.{e}.down_proj.weight"]
+        else:
+            names += [p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight", p + "mlp.down_proj.weight"]
+    names.append("model.norm.weight")
+    if not cfg.tie_word_embeddings:
+        names.append("lm_head.weight")
+    return names
+
+
+def iter_hf_tensors(model) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Yields ``(hf_name, tensor)`` views/slices of the fused parameters (no copies except the
+    de-interleave of gate/up)."""
+    cfg: DecoderConfig = model.cfg
+    yield "model.embed_tokens.weight", model.embed.data
+    qs, ks = cfg.q_size, cfg.kv_size
+    for i, blk in enumerate(model.blocks):
+        p = f"model.layers.{i}."
+        yield p + "input_layernorm.weight", blk.ln1.data
+        w = blk.wqkv.data
+        yield p + "self_attn.q_proj.weight", w[:qs]
+        yield p + "self_attn.k_proj.weight", w[qs:qs + ks]
+        yield p + "self_attn.v_proj.weight", w[qs + ks:]
+        if cfg.qk_norm:
+            yield p + "self_attn.q_norm.weight", blk.q_norm.data
+            yield p + "self_attn.k_norm.weight", blk.k_norm.data
+        yield p + "self_attn.o_proj.weight", blk.wo.data
+        yield p + "post_attention_layernorm.weight", blk.ln2.data
+        if cfg.is_moe:
+            yield p + "mlp.gate.weight", blk.mlp.router.data
+            for e in range(cfg.num_experts):
+                g, u = split_gate_up(blk.mlp.wgu.data[e])
+                yield p + f"mlp.experts.{e}.gate_proj.weight", g
+                yield p + f"mlp.experts.{e}.up_proj.weight", u
+                yield p + f"mlp.experts.{e}.down_proj.weight", blk.mlp.wdown.data[e]
+        else:
+            g, u = split_gate_up(blk.wgu.data)
+            yield p + "mlp.gate_proj.weight", g
+            yield p + "mlp.up_proj.weight", u
+            yield p + "mlp.down_proj.weight", blk.wdown.data
+    yield "model.norm.weight", model.final_norm.data
+    if model.lm_head is not None:
+        yield "lm_head.weight", model.lm_head.data
+
+
+@torch.no_grad()
+def load_hf_tensor(model, name: str, tensor: torch.Tensor) -> None:
+    """Copies one Hugging Face tensor into its place inside the fused parameters."""
+    cfg: DecoderConfig = model.cfg
+    qs, ks = cfg.q_size, cfg.kv_size
+
+    def put(dst, src):
+        if dst.shape != src.shape:
+            raise ValueError(f"{name}: shape {tuple(src.shape)} does not fit {tuple(dst.shape)}")
+        dst.copy_(src.to(device=dst.device, dtype=dst.dtype))
+
+    if name == "model.embed_tokens.weight":
+        return put(model.embed.data, tensor)
+    if name == "model.norm.weight":
+        return put(model.final_norm.data, tensor)
+    if name == "lm_head.weight":
+        if model.lm_head is None:
+            return None  # tied: the embedding already carries it
+        return put(model.lm_head.data, tensor)
+    parts = name.split(".")
+    if len(parts) < 5 or parts[0] != "model" or parts[1] != "layers":
+        raise KeyError(f"unexpected tensor name {name!r}")
+    blk = model.blocks[int(parts[2])]
+    rest = ".".join(parts[3:])
+    if rest == "input_layernorm.weight":
+        return put(blk.ln1.data, tensor)
+    if rest == "post_attention_layernorm.weight":
+        return put(blk.ln2.data, tensor)
+    if rest == "self_attn.q_proj.weight":
+        return put(blk.wqkv.data[:qs], tensor)
+    if rest == "self_attn.k_proj.weight":
+        return put(blk.wqkv.data[qs:qs + ks], tensor)
+    if rest == "self_attn.v_proj.weight":
+        return put(blk.wqkv.data[qs + ks:], tensor)
+    if rest == "self_attn.q_norm.weight":
+        return put(blk.q_norm.data, tensor)
+    if rest == "self_attn.k_norm.weight":
+        return put(blk.k_norm.data, tensor)
+    if rest == "self_attn.o_proj.weight":
+        return put(blk.wo.data, tensor)
+    if rest == "mlp.gate_proj.weight":
+        return put(blk.wgu.data[0::2], tensor)
+    if rest == "mlp.up_proj.weight":
+        return put(blk.wgu.data[1::2], tensor)
+    if rest == "mlp.down_proj.weight":
+        return put(blk.wdown.data, tensor)
+    if rest == "mlp.gate.weight":
+        return put(blk.mlp.router.data, tensor)
+    if parts[3] == "mlp" and parts[4] == "experts":
+        e = int(parts[5])
+        which = parts[6]
+        if which == "gate_proj":
+            return put(blk.mlp.wgu.data[e][0::2], tensor)
+        if which == "up_proj":
+            return put(blk.mlp.wgu.data[e][1::2], tensor)
+        if which == "down_proj":
+            return put(blk.mlp.wdown.data[e], tensor)
+    raise KeyError(f"unexpected tensor name {name!r}")
+
+
+# ----------------------------------------------------------------------- safetensors files
+_ST_DTYPES = {"F32": torch.float32, "F16": torch.float16, "BF16": torch.bfloat16, "I64": torch.int64,
+              "I32": torch.int32, "U8": torch.uint8, "F64": torch.float64, "BOOL": torch.bool, "I8": torch.int8,
+              "I16": torch.int16}
+_ST_NAMES = {v: k for k, v in _ST_DTYPES.items()}
+
+
+def read_safetensors(path) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Streams tensors out of a ``.safetensors`` file through one memory map (no whole-file read)."""
+    import numpy as np
+
+    path = Path(path)
+    with open(path, "rb") as f:
+        (hlen,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(hlen))
+    header.pop("__metadata__", None)
+    mm = np.memmap(path, dtype=np.uint8, mode="r", offset=8 + hlen)
+    for name, info in header.items():
+        lo, hi = info["data_offsets"]
+        dt = _ST_DTYPES[info["dtype"]]
+        buf = torch.from_numpy(np.array(mm[lo:hi]))  # owned copy of just this tensor
+        yield name, buf.view(dt).reshape(info["shape"])
+
+
+def write_safetensors(path, tensors: Dict[str, torch.Tensor], metadata: Optional[Dict[str, str]] = None) -> None:
+    header: Dict[str, object] = {}
+    if metadata:
+        header["__metadata__"] = metadata
+    off = 0
+    items = []
+    for name, t in tensors.items():
+        t = t.detach().cpu().contiguous()
+        n = t.numel() * t.element_size()
+        header[name] = {"dtype": _ST_NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + n]}
+        off += n
+        items.append(t)
+    hb = json.dumps(header, separators=(",", ":")).encode()
+    hb += b" " * ((-len(hb)) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hb)))
+        f.write(hb)
+        for t in items:
+            if t.numel():
+                f.write(t.view(torch.uint8).reshape(-1).numpy().tobytes())
+
+
+def save_hf_checkpoint(model, out_dir, max_shard_bytes: int = 4 << 30, tensors=None) -> List[str]:
+    """Writes ``config.json``, sharded ``model-XXXXX-of-YYYYY.safetensors`` and the index file.
+    ``tensors`` overrides the source of ``(name, tensor)`` pairs (e.g. gathered ZeRO shards)."""
+    out = Path(out_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    (out / "config.json").write_text(json.dumps(model.cfg.to_hf_dict(), indent=2))
+    shards: List[Dict[str, torch.Tensor]] = [{}]
+    size = 0
+    for name, t in (tensors if tensors is not None else iter_hf_tensors(model)):
+        n = t.numel() * t.element_size()
+        if size + n > max_shard_bytes and shards[-1]:
+            shards.append({})
+            size = 0
+        shards[-1][name] = t.detach().to("cpu").contiguous().clone()
+        size += n
+    files, weight_map = [], {}
+    for i, sh in enumerate(shards):
+        fn = "model.safetensors" if len(shards) == 1 else f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+        write_safetensors(out / fn, sh, {"format": "pt"})
+        files.append(fn)
+        for k in sh:
+            weight_map[k] = fn
+    if len(shards) > 1:
+        (out / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+    return files
+
+
+def load_hf_checkpoint(model, ckpt_dir, strict: bool = True) -> int:
+    """Loads every ``*.safetensors`` under ``ckpt_dir`` into ``model``; returns the tensor count."""
+    d = Path(ckpt_dir)
+    files = sorted(d.glob("*.safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no .safetensors files in {d}")
+    expected = set(hf_param_names(model.cfg))
+    seen = set()
+    for f in files:
+        for name, t in read_safetensors(f):
+            if name not in expected:
+                if strict and not (name == "lm_head.weight" and model.lm_head is None):
+                    raise KeyError(f"{f.name}: unexpected tensor {name!r}")
+                continue
+            load_hf_tensor(model, name, t)
+            seen.add(name)
+    if strict and seen != expected:
+        raise KeyError(f"checkpoint is missing {sorted(expected - seen)[:5]} ...")
+    return len(seen)

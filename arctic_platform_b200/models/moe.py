@@ -1,0 +1,152 @@
+"""Token-choice top-k mixture of experts (Qwen3-MoE layout).
+
+Router: fp32 softmax over ``E`` logits, top-k, optional renormalisation of the kept
+probabilities (arctic_platform/model/implementations/qwen35/models/layers/moe.py:226-269
+in the reference).  Experts: SwiGLU FFNs stacked as ``wgu [E, 2*I, H]`` (gate/up rows
+interleaved) and ``wdown [E, H, I]``.
+
+Single-GPU / data-parallel execution sorts the routed (token, expert) pairs by expert and
+runs ONE grouped tcgen05 GEMM per projection through the GEMM kernel's tile table (the
+reference calls ``torch._grouped_mm`` three times, ``moe.py:133-148``).  Expert-parallel
+execution (experts sharded over ranks, dispatch/combine over NVLink) lives in
+:mod:`arctic_platform_b200.parallel.expert_parallel` and reuses :func:`grouped_ffn`.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+from torch import nn
+
+from ..ops import gemm
+from .config import DecoderConfig
+
+
+def route_topk(logits: torch.Tensor, k: int, renorm: bool) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fp32 softmax + top-k.  Returns ``(weights [T,k] fp32, experts [T,k] int64)``."""
+    probs = torch.softmax(logits.float(), dim=-1)
+    w, idx = torch.topk(probs, k, dim=-1)
+    if renorm:
+        w = w / w.sum(-1, keepdim=True)
+    return w, idx
+
+
+def build_group_tiles(counts: torch.Tensor, n_out: int, bn: int = 128) -> torch.Tensor:
+    """Tile table ``[n, 4] = (m0, m_end, b_row_offset, n_tile)`` for a grouped GEMM whose group ``e``
+    owns ``counts[e]`` consecutive rows and the ``e``-th ``n_out``-row slab of the stacked B."""
+    counts_l = counts.tolist()
+    tiles = []
+    row = 0
+    n_tiles = (n_out + bn - 1) // bn
+    for e, c in enumerate(counts_l):
+        for m0 in range(row, row + c, 128):
+            for nt in range(n_tiles):
+                tiles.append((m0, row + c, e * n_out, nt))
+        row += c
+    if not tiles:
+        return torch.zeros((0, 4), dtype=torch.int32, device=counts.device)
+    return torch.tensor(tiles, dtype=torch.int32).to(counts.device)
+
+
+class _GroupedFFNFn(torch.autograd.Function):
+    """y[r] = W_down[e(r)] (silu(W_g[e(r)] x[r]) * (W_u[e(r)] x[r])) for rows sorted by expert."""
+
+    @staticmethod
+    def forward(ctx, x, wgu, wdown, counts):
+        E, I2, H = wgu.shape
+        I = I2 // 2
+        R = x.shape[0]
+        t1 = build_group_tiles(counts, I2)
+        t2 = build_group_tiles(counts, H)
+        gu = torch.empty((R, I2), device=x.device, dtype=x.dtype)
+        act = torch.empty((R, I), device=x.device, dtype=x.dtype)
+        y = torch.empty((R, H), device=x.device, dtype=x.dtype)
+        if R > 0:
+            gemm.gemm_raw(x, wgu.view(E * I2, H), gu, M=R, N=I2, K=H, epi=gemm.EPI_SWIGLU, out2=act, tile_map=t1,
+                          b_rows=E * I2, bn=128)
+            gemm.gemm_raw(act, wdown.view(E * H, I), y, M=R, N=H, K=I, tile_map=t2, b_rows=E * H, bn=128)
+        ctx.save_for_backward(x, wgu, wdown, gu, act, counts)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import _lib
+        x, wgu, wdown, gu, act, counts = ctx.saved_tensors
+        E, I2, H = wgu.shape
+        I = I2 // 2
+        R = x.shape[0]
+        dy = dy.contiguous()
+        dx = torch.zeros_like(x)
+        acc_gu = getattr(wgu, "grad_f32", None)
+        acc_dn = getattr(wdown, "grad_f32", None)
+        dwgu = acc_gu if acc_gu is not None else torch.zeros(wgu.shape, device=x.device, dtype=torch.float32)
+        dwdn = acc_dn if acc_dn is not None else torch.zeros(wdown.shape, device=x.device, dtype=torch.float32)
+        if R > 0:
+            # d act = dy @ Wdown[e]   (grouped, B stored [H, I] per expert -> MN-major B over the stacked rows)
+            dact = torch.empty_like(act)
+            dgu = torch.empty_like(gu)
+            row = 0
+            for e, c in enumerate(counts.tolist()):
+                if c == 0:
+                    continue
+                sl = slice(row, row + c)
+                gemm.matmul_nn(dy[sl], wdown[e], out=dact[sl])
+                gemm.matmul_tn(dy[sl], act[sl], out=dwdn[e], accumulate=True)
+                row += c
+            _lib.check(_lib.cuda_lib().apb_swiglu_bwd(_lib.ptr(gu), _lib.ptr(dact), _lib.ptr(dgu), R, I,
+                                                      _lib.stream_ptr()), "swiglu_bwd")
+            row = 0
+            for e, c in enumerate(counts.tolist()):
+                if c == 0:
+                    continue
+                sl = slice(row, row + c)
+                gemm.matmul_nn(dgu[sl], wgu[e], out=dx[sl])
+                gemm.matmul_tn(dgu[sl], x[sl], out=dwgu[e], accumulate=True)
+                row += c
+        return (dx, None if acc_gu is not None else dwgu.to(wgu.dtype),
+                None if acc_dn is not None else dwdn.to(wdown.dtype), None)
+
+
+def grouped_ffn(x_sorted: torch.Tensor, wgu: torch.Tensor, wdown: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+    """Expert FFN over rows already sorted by expert; ``counts [E]`` rows per expert (CPU or GPU int64)."""
+    if not x_sorted.is_cuda:
+        outs, row = [], 0
+        for e, c in enumerate(counts.tolist()):
+            xe = x_sorted[row:row + c]
+            gu = xe @ wgu[e].t()
+            outs.append((torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ wdown[e].t())
+            row += c
+        return torch.cat(outs) if outs else x_sorted.new_zeros((0, wdown.shape[1]))
+    return _GroupedFFNFn.apply(x_sorted.contiguous(), wgu, wdown, counts.cpu())
+
+
+class MoEFeedForward(nn.Module):
+    def __init__(self, cfg: DecoderConfig, device, dtype):
+        super().__init__()
+        self.cfg = cfg
+        E, H, I = cfg.num_experts, cfg.hidden_size, cfg.moe_intermediate_size
+        self.router = nn.Parameter(torch.empty(E, H, device=device, dtype=dtype))
+        self.wgu = nn.Parameter(torch.empty(E, 2 * I, H, device=device, dtype=dtype))
+        self.wdown = nn.Parameter(torch.empty(E, H, I, device=device, dtype=dtype))
+        self.ep = None  # set by parallel.expert_parallel.attach() when experts are sharded over ranks
+        self.last_tokens_per_expert: Optional[torch.Tensor] = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        cfg = self.cfg
+        T, H = x.shape
+        logits = gemm.linear(x, self.router)
+        w, idx = route_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
+        if self.ep is not None:
+            return self.ep.forward(self, x, w, idx)
+        k = cfg.num_experts_per_tok
+        flat_e = idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        counts = torch.bincount(flat_e, minlength=cfg.num_experts)
+        self.last_tokens_per_expert = counts.detach()
+        src_tok = torch.div(order, k, rounding_mode="floor")
+        xs = x.index_select(0, src_tok)
+        ys = grouped_ffn(xs, self.wgu, self.wdown, counts)
+        wflat = w.reshape(-1).index_select(0, order).to(ys.dtype)
+        out = torch.zeros((T, H), device=x.device, dtype=torch.float32 if x.is_cuda else x.dtype)
+        out.index_add_(0, src_tok, (ys * wflat[:, None]).to(out.dtype))
+        return out.to(x.dtype)

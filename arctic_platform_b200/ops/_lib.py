@@ -68,7 +68,12 @@ def cuda_available() -> bool:
 
 
 def stream_ptr(stream=None) -> ctypes.c_void_p:
+    """Raw handle of the launch stream.  Also binds the library's runtime to torch's current device
+    in this thread (autograd worker threads start without one)."""
     s = stream if stream is not None else torch.cuda.current_stream()
+    code = cuda_lib().apb_bind_device(s.device.index if s.device.index is not None else torch.cuda.current_device())
+    if code != 0:
+        raise KernelError(f"apb_bind_device failed with code {code}")
     return ctypes.c_void_p(s.cuda_stream)
 
 
@@ -119,6 +124,7 @@ def _declare_cuda(lib) -> None:
     _sig(lib, "apb_status_read", [])
     _sig(lib, "apb_status_clear", [])
     _sig(lib, "apb_version", [])
+    _sig(lib, "apb_bind_device", [c_i])
     _sig(lib, "apb_fill_u32", [c_vp, c_sz, ctypes.c_uint32, c_vp])
     _sig(lib, "apb_gemm_bf16",
          [c_vp, c_vp, c_vp, c_i, c_i, c_i, c_ll, c_ll, c_ll, c_i, c_i, c_i, c_i, c_f, c_vp,

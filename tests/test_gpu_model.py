@@ -1,0 +1,66 @@
+"""The bf16 GPU model (all kernels) against the same module in fp32 on CPU, and ZoRRo equivalence on GPU."""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _batch():
+    from tests.test_zorro_equivalence_cpu import make_grpo_batch
+    return make_grpo_batch(n_prompts=3, n_samples=4, p_rng=(100, 300), r_rng=(10, 150))
+
+
+def _models(name="qwen3-tiny-d128"):
+    from arctic_platform_b200.models.config import PRESETS
+    from arctic_platform_b200.models.decoder import DecoderLM
+    cfg = PRESETS[name]
+    ref = DecoderLM(cfg, "cpu", torch.float32).init_weights(seed=3)
+    gpu = DecoderLM(cfg, "cuda", torch.bfloat16)
+    with torch.no_grad():
+        for (n, p), (_, q) in zip(gpu.named_parameters(), ref.named_parameters()):
+            p.copy_(q.to(torch.bfloat16))
+            q.copy_(p.float().cpu())          # reference uses the bf16-rounded weights
+    return cfg, ref, gpu
+
+
+@pytest.mark.parametrize("name", ["qwen3-tiny-d128", "qwen3-moe-tiny"])
+def test_model_forward_backward_vs_fp32(name):
+    from arctic_platform_b200.models.decoder import token_logprobs
+    from arctic_platform_b200.ops import _lib
+    from arctic_platform_b200.rl.zorro_train.layout import build_packed_batch
+    cfg, ref, gpu = _models(name)
+    ids, mask, R = _batch()
+    pb = build_packed_batch(ids, mask, R, dedup=True)
+    adv = torch.randn(pb.labels.shape[0])
+    lp_r, ent_r = token_logprobs(ref, pb, 1.0)
+    ((lp_r * adv).sum() / adv.numel()).backward()
+    pbg = copy.copy(pb).to("cuda")
+    lp_g, ent_g = token_logprobs(gpu, pbg, 1.0)
+    ((lp_g * adv.cuda()).sum() / adv.numel()).backward()
+    _lib.check_status("model")
+    assert (lp_g.cpu() - lp_r).abs().max() < 0.25          # the reference's own gate vs HF (LOGPROB_ATOL)
+    assert (lp_g.cpu() - lp_r).abs().mean() < 0.02
+    assert (ent_g.cpu() - ent_r).abs().mean() < 0.02
+    gr = dict(ref.named_parameters())
+    for n, p in gpu.named_parameters():
+        if "router" in n:
+            continue
+        a, b = p.grad.float().cpu().flatten(), gr[n].grad.flatten()
+        cos = torch.nn.functional.cosine_similarity(a, b, dim=0)
+        assert cos > 0.98, f"{n}: cosine {cos}"
+
+
+def test_zorro_equals_full_on_gpu():
+    from arctic_platform_b200.models.decoder import token_logprobs
+    from arctic_platform_b200.ops import _lib
+    from arctic_platform_b200.rl.zorro_train.layout import build_packed_batch
+    cfg, ref, gpu = _models()
+    ids, mask, R = _batch()
+    with torch.no_grad():
+        lp_d, _ = token_logprobs(gpu, build_packed_batch(ids, mask, R, dedup=True).to("cuda"))
+        lp_f, _ = token_logprobs(gpu, build_packed_batch(ids, mask, R, dedup=False).to("cuda"))
+    _lib.check_status("zorro gpu")
+    assert (lp_d - lp_f).abs().max() < 0.05
+    assert (lp_d - lp_f).abs().mean() < 5e-3
