@@ -1,0 +1,282 @@
+// Gradient reduce-scatter + clip + partitioned AdamW + parameter all-gather, as
+// two kernels that talk to the other GPUs through peer-mapped (symmetric) buffers
+// over NVLink instead of calling a collective library:
+//
+//   phase A  zero_reduce_kernel : this rank's shard of the fp32 gradient bucket is
+//            summed over every rank's bucket with P2P loads (or one
+//            multimem.ld_reduce through the switch when a multicast mapping is
+//            given), scaled, written to the local reduced shard, and its sum of
+//            squares is accumulated for the global gradient norm.
+//   phase B  zero_adamw_kernel  : AdamW on the fp32 master shard with the clip
+//            coefficient derived on the device from the global sum of squares,
+//            then the updated bf16 values are stored into EVERY rank's parameter
+//            buffer (P2P stores or multimem.st), which is the all-gather.
+//
+// With one rank both kernels degenerate to a fused local cast/clip/AdamW.  The
+// reference leaves these steps to DeepSpeed's ZeRO reduce-scatter, its
+// multi-tensor FusedAdam and a parameter all-gather
+// (arctic_platform/common/deepspeed_worker.py:208-300).
+//
+// Cross-rank ordering uses epoch flags in symmetric memory: a kernel first
+// announces its epoch to every peer and waits (bounded) until all peers have
+// announced theirs, i.e. their earlier work on the stream -- the writes this kernel
+// is about to read -- has completed.
+#include "common.cuh"
+#include "host_utils.cuh"
+
+namespace apb {
+
+constexpr int kMaxRanks = 16;
+
+struct PeerPtrs {
+  void* p[kMaxRanks];
+};
+
+// Announce `epoch` in slot `rank` of every peer's flag array, then wait until every
+// slot of the local flag array has reached `epoch`.  Every block waits by itself so
+// no grid-wide barrier is needed; only block 0 announces.
+__device__ __forceinline__ bool epoch_barrier(const PeerPtrs& flags, int rank, int world, int epoch, int* status) {
+  if (world <= 1) return true;
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    flag_store_release(static_cast<int*>(flags.p[threadIdx.x]) + rank, epoch);
+  }
+  if (threadIdx.x < world) {
+    if (!flag_wait_ge(static_cast<const int*>(flags.p[rank]) + threadIdx.x, epoch, status, kTimeoutFlag)) ok_s = 0;
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_ptr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_ptr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_b128(void* mc_ptr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_ptr),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+// grads: per-rank base pointers of the fp32 bucket (symmetric layout); this rank owns
+// elements [shard_off, shard_off + n).  n % 4 == 0.
+__global__ void __launch_bounds__(256)
+zero_reduce_kernel(PeerPtrs grads, const float* mc_grads, PeerPtrs flags, int rank, int world, int epoch,
+                   long long shard_off, long long n, float scale, float* __restrict__ reduced,
+                   double* __restrict__ sumsq, int* status) {
+  if (!epoch_barrier(flags, rank, world, epoch, status)) return;
+  double acc = 0.0;
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4 s;
+    if (mc_grads) {
+      s = multimem_ld_reduce_f32x4(mc_grads + shard_off + i * 4);
+    } else {
+      s = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < world; ++r) {
+        const int src = (rank + r) % world;  // start at the local copy, spread peers over links
+        const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[src]) + shard_off + i * 4);
+        s.x += v.x;
+        s.y += v.y;
+        s.z += v.z;
+        s.w += v.w;
+      }
+    }
+    s.x *= scale;
+    s.y *= scale;
+    s.z *= scale;
+    s.w *= scale;
+    *reinterpret_cast<float4*>(reduced + i * 4) = s;
+    acc += static_cast<double>(s.x) * s.x + static_cast<double>(s.y) * s.y + static_cast<double>(s.z) * s.z +
+           static_cast<double>(s.w) * s.w;
+  }
+  // block reduction of the sum of squares
+  __shared__ double red[8];
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < blockDim.x / 32; ++w) t += red[w];
+    atomicAdd(sumsq, t);
+  }
+}
+
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay;
+  float bias1, bias2;       // 1 - beta^t
+  float max_grad_norm;      // <= 0 : no clipping
+};
+
+// params: per-rank base pointers of the bf16 parameter bucket; every rank receives the
+// updated values of this rank's shard [shard_off, shard_off + n).  n % 8 == 0.
+__global__ void __launch_bounds__(256)
+zero_adamw_kernel(PeerPtrs params, void* mc_params, PeerPtrs flags, int rank, int world, int epoch,
+                  long long shard_off, long long n, const float* __restrict__ grad, float* __restrict__ master,
+                  float* __restrict__ m, float* __restrict__ v, const double* __restrict__ total_sumsq,
+                  AdamArgs a, int* status) {
+  if (!epoch_barrier(flags, rank, world, epoch, status)) return;
+  float clip = 1.f;
+  if (a.max_grad_norm > 0.f && total_sumsq) {
+    const float nrm = static_cast<float>(sqrt(*total_sumsq));
+    clip = fminf(1.f, a.max_grad_norm / (nrm + 1e-6f));
+  }
+  const long long n8 = n >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float out[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const long long e = i * 8 + h * 4;
+      float4 g = *reinterpret_cast<const float4*>(grad + e);
+      float4 w = *reinterpret_cast<const float4*>(master + e);
+      float4 mm = *reinterpret_cast<const float4*>(m + e);
+      float4 vv = *reinterpret_cast<const float4*>(v + e);
+      float* gp = &g.x;
+      float* wp = &w.x;
+      float* mp = &mm.x;
+      float* vp = &vv.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float gj = gp[j] * clip;
+        mp[j] = a.beta1 * mp[j] + (1.f - a.beta1) * gj;
+        vp[j] = a.beta2 * vp[j] + (1.f - a.beta2) * gj * gj;
+        const float mh = mp[j] / a.bias1;
+        const float vh = vp[j] / a.bias2;
+        wp[j] = wp[j] * (1.f - a.lr * a.weight_decay) - a.lr * mh / (sqrtf(vh) + a.eps);
+        out[h * 4 + j] = wp[j];
+      }
+      *reinterpret_cast<float4*>(master + e) = w;
+      *reinterpret_cast<float4*>(m + e) = mm;
+      *reinterpret_cast<float4*>(v + e) = vv;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(out[0], out[1]);
+    o.y = pack_bf16x2(out[2], out[3]);
+    o.z = pack_bf16x2(out[4], out[5]);
+    o.w = pack_bf16x2(out[6], out[7]);
+    const long long e = shard_off + i * 8;
+    if (mc_params) {
+      multimem_st_b128(static_cast<__nv_bfloat16*>(mc_params) + e, o);
+    } else {
+      for (int r = 0; r < world; ++r) {
+        const int dst = (rank + r) % world;
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[dst]) + e) = o;
+      }
+    }
+  }
+}
+
+// Waits until every peer has announced `epoch` (completion of the peers' stores into
+// this rank's buffers before dependent work starts).
+__global__ void epoch_wait_kernel(PeerPtrs flags, int rank, int world, int epoch, int* status) {
+  epoch_barrier(flags, rank, world, epoch, status);
+}
+
+// All-gather of bf16 shards by pulling: dst[r*n .. ] = peer r's shard (n elements, n % 8 == 0).
+__global__ void __launch_bounds__(256)
+gather_shards_kernel(PeerPtrs shards, PeerPtrs flags, int rank, int world, int epoch, long long n,
+                     __nv_bfloat16* __restrict__ dst, int* status) {
+  if (!epoch_barrier(flags, rank, world, epoch, status)) return;
+  const long long n8 = n >> 3;
+  const long long total = n8 * world;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int rr = static_cast<int>(i / n8);
+    const int src = (rank + rr) % world;
+    const long long off = (i - static_cast<long long>(rr) * n8) * 8;
+    const uint4 val = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(shards.p[src]) + off);
+    *reinterpret_cast<uint4*>(dst + static_cast<long long>(src) * n + off) = val;
+  }
+}
+
+__global__ void sumsq_f32_kernel(const float* __restrict__ x, long long n, double* __restrict__ out) {
+  double acc = 0.0;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    acc += static_cast<double>(x[i]) * x[i];
+  __shared__ double red[8];
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < blockDim.x / 32; ++w) t += red[w];
+    atomicAdd(out, t);
+  }
+}
+
+}  // namespace apb
+
+extern "C" {
+using namespace apb;
+
+static PeerPtrs to_peers(void* const* ptrs, int world) {
+  PeerPtrs p;
+  for (int i = 0; i < kMaxRanks; ++i) p.p[i] = i < world ? ptrs[i] : nullptr;
+  return p;
+}
+static int grid_for(long long work_items) {
+  long long g = (work_items + 255) / 256;
+  if (g < 1) g = 1;
+  return static_cast<int>(g < 148 * 8 ? g : 148 * 8);
+}
+
+// Phase A.  grad_ptrs[world]: every rank's fp32 bucket base (peer-mapped); flag_ptrs[world]: every rank's
+// int flag array (>= world ints).  mc_grads: multicast address of the bucket or null.
+int apb_zero_reduce(void* const* grad_ptrs, const float* mc_grads, void* const* flag_ptrs, int rank, int world,
+                    int epoch, long long shard_off, long long n, float scale, float* reduced, double* sumsq,
+                    cudaStream_t s) {
+  if (world > kMaxRanks || (n % 4) || (shard_off % 4)) return kBadArgument;
+  if (n == 0 && world <= 1) return 0;
+  zero_reduce_kernel<<<grid_for(n / 4), 256, 0, s>>>(to_peers(grad_ptrs, world), mc_grads, to_peers(flag_ptrs, world),
+                                                     rank, world, epoch, shard_off, n, scale, reduced, sumsq,
+                                                     status_device_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Phase B.  param_ptrs[world]: every rank's bf16 parameter bucket base; mc_params: multicast address or null.
+int apb_zero_adamw(void* const* param_ptrs, void* mc_params, void* const* flag_ptrs, int rank, int world, int epoch,
+                   long long shard_off, long long n, const float* grad, float* master, float* m, float* v,
+                   const double* total_sumsq, float lr, float beta1, float beta2, float eps, float weight_decay,
+                   float bias1, float bias2, float max_grad_norm, cudaStream_t s) {
+  if (world > kMaxRanks || (n % 8) || (shard_off % 8)) return kBadArgument;
+  if (n == 0 && world <= 1) return 0;
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias1, bias2, max_grad_norm};
+  zero_adamw_kernel<<<grid_for(n / 8), 256, 0, s>>>(to_peers(param_ptrs, world), mc_params,
+                                                    to_peers(flag_ptrs, world), rank, world, epoch, shard_off, n, grad,
+                                                    master, m, v, total_sumsq, a, status_device_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+int apb_epoch_wait(void* const* flag_ptrs, int rank, int world, int epoch, cudaStream_t s) {
+  if (world > kMaxRanks) return kBadArgument;
+  if (world <= 1) return 0;
+  epoch_wait_kernel<<<1, 32, 0, s>>>(to_peers(flag_ptrs, world), rank, world, epoch, status_device_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+int apb_gather_shards(void* const* shard_ptrs, void* const* flag_ptrs, int rank, int world, int epoch, long long n,
+                      void* dst, cudaStream_t s) {
+  if (world > kMaxRanks || (n % 8)) return kBadArgument;
+  gather_shards_kernel<<<grid_for(n / 8 * world), 256, 0, s>>>(to_peers(shard_ptrs, world), to_peers(flag_ptrs, world),
+                                                               rank, world, epoch, n,
+                                                               static_cast<__nv_bfloat16*>(dst), status_device_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+int apb_sumsq_f32(const float* x, long long n, double* out, cudaStream_t s) {
+  if (n <= 0) return 0;
+  sumsq_f32_kernel<<<grid_for(n), 256, 0, s>>>(x, n, out);
+  return static_cast<int>(cudaGetLastError());
+}
+}

@@ -31,7 +31,7 @@ def route_topk(logits: torch.Tensor, k: int, renorm: bool) -> Tuple[torch.Tensor
     return w, idx
 
 
-def build_group_tiles(counts: torch.Tensor, n_out: int, bn: int = 128) -> torch.Tensor:
+def build_group_tiles(counts: torch.Tensor, n_out: int, device, bn: int = 128) -> torch.Tensor:
     """Tile table ``[n, 4] = (m0, m_end, b_row_offset, n_tile)`` for a grouped GEMM whose group ``e``
     owns ``counts[e]`` consecutive rows and the ``e``-th ``n_out``-row slab of the stacked B."""
     counts_l = counts.tolist()
@@ -44,8 +44,8 @@ def build_group_tiles(counts: torch.Tensor, n_out: int, bn: int = 128) -> torch.
                 tiles.append((m0, row + c, e * n_out, nt))
         row += c
     if not tiles:
-        return torch.zeros((0, 4), dtype=torch.int32, device=counts.device)
-    return torch.tensor(tiles, dtype=torch.int32).to(counts.device)
+        return torch.zeros((0, 4), dtype=torch.int32, device=device)
+    return torch.tensor(tiles, dtype=torch.int32).to(device)
 
 
 class _GroupedFFNFn(torch.autograd.Function):
@@ -56,8 +56,8 @@ class _GroupedFFNFn(torch.autograd.Function):
         E, I2, H = wgu.shape
         I = I2 // 2
         R = x.shape[0]
-        t1 = build_group_tiles(counts, I2)
-        t2 = build_group_tiles(counts, H)
+        t1 = build_group_tiles(counts, I2, x.device)
+        t2 = build_group_tiles(counts, H, x.device)
         gu = torch.empty((R, I2), device=x.device, dtype=x.dtype)
         act = torch.empty((R, I), device=x.device, dtype=x.dtype)
         y = torch.empty((R, H), device=x.device, dtype=x.dtype)

@@ -80,6 +80,8 @@ def stream_ptr(stream=None) -> ctypes.c_void_p:
 def ptr(t) -> ctypes.c_void_p:
     if t is None:
         return ctypes.c_void_p(0)
+    if not t.is_cuda:
+        raise KernelError(f"a kernel argument lives on {t.device}, not on a CUDA device")
     return ctypes.c_void_p(t.data_ptr())
 
 
