@@ -1,0 +1,385 @@
+// Sampler-side kernels: paged KV cache writes, paged (split-KV) decode attention with
+// an LSE-weighted merge that also serves forest-cascade decode, and token sampling.
+// These take the place of the vLLM / ArcticInference kernels the reference drives
+// through ReplicaPool (arctic_platform/common/ray_server.py:197-201,921-933; forest
+// cascade attention is switched on by `use_fca`, common/utils/server_models.py:123-132).
+//
+// KV cache layout: [num_pages, Hkv, 16, D] bf16 -- the 16 tokens of one (page, head)
+// are one contiguous 4 KB tile (D = 128).
+#include "common.cuh"
+#include "host_utils.cuh"
+
+namespace apb {
+
+constexpr int kPage = 16;
+
+// k, v: [T, Hkv, D] (row stride ld elements); slots[t] = page * 16 + offset, or < 0 to skip.
+__global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ k, long long ldk,
+                                      const __nv_bfloat16* __restrict__ v, long long ldv,
+                                      const int* __restrict__ slots, __nv_bfloat16* __restrict__ kcache,
+                                      __nv_bfloat16* __restrict__ vcache, int T, int Hkv, int D) {
+  const int vec_per_row = Hkv * D / 8;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+       i < static_cast<long long>(T) * vec_per_row; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / vec_per_row);
+    const int e = static_cast<int>(i % vec_per_row) * 8;
+    const int slot = slots[t];
+    if (slot < 0) continue;
+    const int h = e / D, d = e % D;
+    const long long dst = ((static_cast<long long>(slot / kPage) * Hkv + h) * kPage + slot % kPage) * D + d;
+    *reinterpret_cast<uint4*>(kcache + dst) = *reinterpret_cast<const uint4*>(k + t * ldk + e);
+    *reinterpret_cast<uint4*>(vcache + dst) = *reinterpret_cast<const uint4*>(v + t * ldv + e);
+  }
+}
+
+// Paged decode attention.  One CTA = (query group, kv head, kv split); a query group is
+// `nq` consecutive query rows that share one page list (nq = 1: ordinary decode; nq > 1:
+// one node of the prefix forest, whose KV is read ONCE for all descendant sequences).
+//   q        [Bq, Hq, D]
+//   q_start  [G]        first query row of group g;  q_count [G] rows in the group (<= kMaxNq)
+//   pages    [G, max_pages]  page ids of the group's KV range;  kv_len [G] tokens in it
+//   out_o    [Bq, Hq, splits, D] fp32 partial numerators (un-normalised), out_ml [Bq,Hq,splits,2] (max, sum)
+// Scores use base-2 exponentials with scale_log2 = softmax_scale * log2(e).
+constexpr int kDecThreads = 128;
+constexpr int kMaxNq = 16;
+
+template <int R, int D>
+__global__ void __launch_bounds__(kDecThreads)
+paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const int* __restrict__ q_start,
+                    const int* __restrict__ q_count, const int* __restrict__ pages, int max_pages,
+                    const int* __restrict__ kv_len, const __nv_bfloat16* __restrict__ kcache,
+                    const __nv_bfloat16* __restrict__ vcache, float* __restrict__ out_o, float* __restrict__ out_ml,
+                    int Hq, int Hkv, int splits, float scale_log2) {
+  static_assert(D == 128, "head_dim 128");
+  const int g = blockIdx.x / Hkv;
+  const int kvh = blockIdx.x % Hkv;
+  const int split = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = q_count[g];
+  const int qs = q_start[g];
+  const int len = kv_len[g];
+  const int n_pages = (len + kPage - 1) / kPage;
+  const int per = (n_pages + splits - 1) / splits;
+  const int p0 = split * per, p1 = min(n_pages, p0 + per);
+
+  __shared__ float q_s[R][D];
+  __shared__ float p_s[4][R][kPage];
+  __shared__ float red_m[4][R], red_l[4][R];
+  __shared__ float red_o[4][R][D];
+
+  const int tok = lane & 15, half = lane >> 4;
+  for (int qi = 0; qi < nq; ++qi) {
+    const int row = qs + qi;
+    __syncthreads();
+    for (int i = threadIdx.x; i < R * D; i += kDecThreads) {
+      const int r = i / D, d = i % D;
+      q_s[r][d] = __bfloat162float(q[(static_cast<long long>(row) * Hq + kvh * R + r) * D + d]) * scale_log2;
+    }
+    __syncthreads();
+    float m[R], l[R], acc[R][4];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      m[r] = -INFINITY;
+      l[r] = 0.f;
+      acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+    }
+    for (int pi = p0 + warp; pi < p1; pi += 4) {
+      const int page = pages[static_cast<long long>(g) * max_pages + pi];
+      const __nv_bfloat16* kp = kcache + ((static_cast<long long>(page) * Hkv + kvh) * kPage + tok) * D + half * 64;
+      float dot[R];
+#pragma unroll
+      for (int r = 0; r < R; ++r) dot[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(kp + i * 8);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float kf[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h2[e]);
+          kf[2 * e] = f.x;
+          kf[2 * e + 1] = f.y;
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float* qr = &q_s[r][half * 64 + i * 8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dot[r] += kf[e] * qr[e];
+        }
+      }
+      const bool valid = pi * kPage + tok < len;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float s = dot[r] + __shfl_xor_sync(0xffffffffu, dot[r], 16);
+        if (!valid) s = -INFINITY;
+        float mx = s;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float m_new = fmaxf(m[r], mx);
+        const float pv = valid ? exp2f(s - m_new) : 0.f;
+        float ps = pv;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+        const float alpha = (m[r] == -INFINITY) ? 0.f : exp2f(m[r] - m_new);
+        l[r] = l[r] * alpha + ps;
+        m[r] = m_new;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[r][e] *= alpha;
+        if (half == 0) p_s[warp][r][tok] = pv;
+      }
+      __syncwarp();
+      const __nv_bfloat16* vp = vcache + ((static_cast<long long>(page) * Hkv + kvh) * kPage) * D + lane * 4;
+#pragma unroll
+      for (int t = 0; t < kPage; ++t) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(vp + t * D);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const float pw = p_s[warp][r][t];
+          acc[r][0] += pw * a.x;
+          acc[r][1] += pw * a.y;
+          acc[r][2] += pw * b.x;
+          acc[r][3] += pw * b.y;
+        }
+      }
+      __syncwarp();
+    }
+    // merge the four warps
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (lane == 0) {
+        red_m[warp][r] = m[r];
+        red_l[warp][r] = l[r];
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) red_o[warp][r][lane * 4 + e] = acc[r][e];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < R * D; i += kDecThreads) {
+      const int r = i / D, d = i % D;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_m[w][r]);
+      float o = 0.f, ll = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float sc = (red_m[w][r] == -INFINITY) ? 0.f : exp2f(red_m[w][r] - mm);
+        o += red_o[w][r][d] * sc;
+        ll += red_l[w][r] * sc;
+      }
+      const long long base = (static_cast<long long>(row) * Hq + kvh * R + r) * splits + split;
+      out_o[base * D + d] = o;
+      if (d == 0) {
+        out_ml[base * 2] = mm;
+        out_ml[base * 2 + 1] = ll;
+      }
+    }
+  }
+}
+
+// Merges `n_src` sets of partials per (row, head): sets s = 0..n_src-1 are [rows, Hq, splits_s, D] blocks
+// given by pointer tables (cascade levels: shared prefix nodes + per-sequence suffix), producing
+// normalised bf16 output [rows, Hq, D].  One warp per (row, head).
+struct MergeSrc {
+  const float* o[4];
+  const float* ml[4];
+  int splits[4];
+  int n;
+};
+__global__ void decode_merge_kernel(MergeSrc src, __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out,
+                                    int rows, int Hq, int D) {
+  const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= static_cast<long long>(rows) * Hq) return;
+  float mm = -INFINITY;
+  for (int s = 0; s < src.n; ++s)
+    for (int k = 0; k < src.splits[s]; ++k) mm = fmaxf(mm, src.ml[s][(gw * src.splits[s] + k) * 2]);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float ll = 0.f;
+  for (int s = 0; s < src.n; ++s)
+    for (int k = 0; k < src.splits[s]; ++k) {
+      const long long b = gw * src.splits[s] + k;
+      const float m = src.ml[s][b * 2];
+      const float sc = (m == -INFINITY) ? 0.f : exp2f(m - mm);
+      ll += src.ml[s][b * 2 + 1] * sc;
+      const float4 v = *reinterpret_cast<const float4*>(src.o[s] + b * D + lane * 4);
+      acc[0] += v.x * sc;
+      acc[1] += v.y * sc;
+      acc[2] += v.z * sc;
+      acc[3] += v.w * sc;
+    }
+  const float inv = ll > 0.f ? 1.f / ll : 0.f;
+  uint2 o;
+  o.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
+  o.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
+  *reinterpret_cast<uint2*>(out + gw * D + lane * 4) = o;
+  if (lse_out && lane == 0) lse_out[gw] = ll > 0.f ? (mm + log2f(ll)) * 0.6931471805599453f : -INFINITY;
+}
+
+// ---------------------------------------------------------------------------- sampling
+__device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
+  x ^= x >> 16;
+  x *= 0x7feb352dU;
+  x ^= x >> 15;
+  x *= 0x846ca68bU;
+  x ^= x >> 16;
+  return x;
+}
+// One block per row.  logits [B, V] fp32 (row stride ldl).  temperature[b] <= 0 -> greedy.
+// Gumbel-max sampling: argmax(z + g), z = logit / T.  Also returns log softmax(z)[token].
+__global__ void __launch_bounds__(1024)
+sample_kernel(const float* __restrict__ logits, long long ldl, const float* __restrict__ temperature, int V,
+              uint32_t seed, const int* __restrict__ step_dev, int* __restrict__ tokens,
+              float* __restrict__ logprobs) {
+  const int b = blockIdx.x;
+  const uint32_t step = step_dev ? static_cast<uint32_t>(*step_dev) : 0u;
+  const float T = temperature[b];
+  const bool greedy = !(T > 0.f);
+  const float invT = greedy ? 1.f : 1.f / T;
+  const float* row = logits + b * ldl;
+  float best = -INFINITY, best_z = 0.f;
+  int best_i = 0;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float z = row[i] * invT;
+    float key = z;
+    if (!greedy) {
+      const uint32_t h = hash_u32(hash_u32(seed ^ (step * 0x9E3779B9u)) ^ hash_u32(static_cast<uint32_t>(b) * 0x85ebca6bU + i));
+      const float u = (static_cast<float>(h >> 8) + 0.5f) * (1.f / 16777216.f);
+      key = z - __logf(-__logf(u));
+    }
+    if (key > best) {
+      best = key;
+      best_i = i;
+      best_z = z;
+    }
+    const float mn = fmaxf(m, z);
+    s = s * __expf(m - mn) + __expf(z - mn);
+    m = mn;
+  }
+  __shared__ float sb[32], sz[32], sm[32], ss[32];
+  __shared__ int si[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    const float oz = __shfl_xor_sync(0xffffffffu, best_z, o);
+    if (ob > best || (ob == best && oi < best_i)) {
+      best = ob;
+      best_i = oi;
+      best_z = oz;
+    }
+    const float om = __shfl_xor_sync(0xffffffffu, m, o);
+    const float os = __shfl_xor_sync(0xffffffffu, s, o);
+    const float mn = fmaxf(m, om);
+    s = (m == -INFINITY ? 0.f : s * __expf(m - mn)) + (om == -INFINITY ? 0.f : os * __expf(om - mn));
+    m = mn;
+  }
+  if (lane == 0) {
+    sb[warp] = best;
+    si[warp] = best_i;
+    sz[warp] = best_z;
+    sm[warp] = m;
+    ss[warp] = s;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    best = lane < nw ? sb[lane] : -INFINITY;
+    best_i = lane < nw ? si[lane] : 0x7fffffff;
+    best_z = lane < nw ? sz[lane] : 0.f;
+    m = lane < nw ? sm[lane] : -INFINITY;
+    s = lane < nw ? ss[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      const float oz = __shfl_xor_sync(0xffffffffu, best_z, o);
+      if (ob > best || (ob == best && oi < best_i)) {
+        best = ob;
+        best_i = oi;
+        best_z = oz;
+      }
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const float os = __shfl_xor_sync(0xffffffffu, s, o);
+      const float mn = fmaxf(m, om);
+      s = (m == -INFINITY ? 0.f : s * __expf(m - mn)) + (om == -INFINITY ? 0.f : os * __expf(om - mn));
+      m = mn;
+    }
+    if (lane == 0) {
+      tokens[b] = best_i;
+      logprobs[b] = best_z - (m + __logf(s));
+    }
+  }
+}
+
+}  // namespace apb
+
+extern "C" {
+using namespace apb;
+
+int apb_kv_cache_write(const void* k, long long ldk, const void* v, long long ldv, const int* slots, void* kcache,
+                       void* vcache, int T, int Hkv, int D, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if ((D % 8) || (ldk % 8) || (ldv % 8)) return kBadArgument;
+  const long long n = static_cast<long long>(T) * Hkv * D / 8;
+  const int grid = static_cast<int>((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  kv_cache_write_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(k), ldk,
+                                             static_cast<const __nv_bfloat16*>(v), ldv, slots,
+                                             static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache),
+                                             T, Hkv, D);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Partial attention of G query groups (see paged_decode_kernel).  out_o / out_ml are fp32 scratch
+// [Bq, Hq, splits, D] and [Bq, Hq, splits, 2].
+int apb_paged_decode_partial(const void* q, const int* q_start, const int* q_count, const int* pages, int max_pages,
+                             const int* kv_len, const void* kcache, const void* vcache, float* out_o, float* out_ml,
+                             int G, int Hq, int Hkv, int D, int splits, float scale, cudaStream_t s) {
+  if (G <= 0) return 0;
+  if (D != 128 || Hq % Hkv || splits < 1) return kBadArgument;
+  const int R = Hq / Hkv;
+  const dim3 grid(G * Hkv, splits);
+  const float sl2 = scale * 1.4426950408889634f;
+#define APB_DEC(RR)                                                                                           \
+  paged_decode_kernel<RR, 128><<<grid, kDecThreads, 0, s>>>(                                                  \
+      static_cast<const __nv_bfloat16*>(q), q_start, q_count, pages, max_pages, kv_len,                      \
+      static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache), out_o, out_ml, Hq, \
+      Hkv, splits, sl2)
+  if (R == 1) APB_DEC(1);
+  else if (R == 2) APB_DEC(2);
+  else if (R == 4) APB_DEC(4);
+  else if (R == 8) APB_DEC(8);
+  else return kBadArgument;
+#undef APB_DEC
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Merges up to 4 partial sets into out [rows, Hq, D] bf16 (+ optional natural-log LSE [rows, Hq]).
+int apb_decode_merge(const float* const* o_ptrs, const float* const* ml_ptrs, const int* splits, int n_src, void* out,
+                     float* lse, int rows, int Hq, int D, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (n_src < 1 || n_src > 4 || D != 128) return kBadArgument;
+  MergeSrc src;
+  src.n = n_src;
+  for (int i = 0; i < 4; ++i) {
+    src.o[i] = i < n_src ? o_ptrs[i] : nullptr;
+    src.ml[i] = i < n_src ? ml_ptrs[i] : nullptr;
+    src.splits[i] = i < n_src ? splits[i] : 0;
+  }
+  const long long warps = static_cast<long long>(rows) * Hq;
+  const int grid = static_cast<int>((warps * 32 + 255) / 256);
+  decode_merge_kernel<<<grid, 256, 0, s>>>(src, static_cast<__nv_bfloat16*>(out), lse, rows, Hq, D);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// step_dev: device int holding the decode step (read by the kernel, so a captured graph sees new values).
+int apb_sample(const float* logits, long long ldl, const float* temperature, int B, int V, unsigned seed,
+               const int* step_dev, int* tokens, float* logprobs, cudaStream_t s) {
+  if (B <= 0) return 0;
+  sample_kernel<<<B, 1024, 0, s>>>(logits, ldl, temperature, V, seed, step_dev, tokens, logprobs);
+  return static_cast<int>(cudaGetLastError());
+}
+}

@@ -62,7 +62,7 @@ struct GemmCfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
   static constexpr int kTmemCols = 2 * BN;
 };
@@ -497,11 +497,15 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   if (splits > k_blocks) splits = k_blocks;
   if (splits > 1 && epi != kEpiF32Atomic) return kBadArgument;
   if (bn == 0) {
-    const long long t256 = static_cast<long long>((M + kBM - 1) / kBM) * ((N + 255) / 256) * splits;
+    const long long tm = (M + kBM - 1) / kBM;
+    const long long t256 = tm * ((N + 255) / 256) * splits;
+    const long long t128 = tm * ((N + 127) / 128) * splits;
     bn = (N >= 256 && t256 >= sm_count()) ? 256 : 128;
+    // skinny problems (decode): narrower tiles put more SMs on the weight stream
+    if (bn == 128 && t128 * 10 < sm_count() * 7 && N >= 128) bn = 64;
     if (tile_map) bn = 128;
   }
-  if (bn != 128 && bn != 256) return kBadArgument;
+  if (bn != 64 && bn != 128 && bn != 256) return kBadArgument;
 
   CUtensorMap ta, tb;
   int rc;
@@ -538,6 +542,7 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   p.labels = nullptr;
   p.partial = nullptr;
   p.row_lse = p.row_ent = p.row_glp = p.row_gent = nullptr;
+  if (bn == 64) return launch_gemm<64>(ta, tb, p, max_ctas, stream);
   return bn == 256 ? launch_gemm<256>(ta, tb, p, max_ctas, stream) : launch_gemm<128>(ta, tb, p, max_ctas, stream);
 }
 }

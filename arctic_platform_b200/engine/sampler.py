@@ -1,0 +1,596 @@
+"""Rollout engine: paged KV cache, prefix-sharing prefill, CUDA-graph decode, forest-cascade attention.
+
+The reference delegates generation to vLLM replicas managed by ArcticInference's ``ReplicaPool``
+(arctic_platform/common/ray_server.py:197-201,375-404,921-933) and only flips ``use_fca`` for
+forest cascade attention (common/utils/server_models.py:123-132).  This module is a from-scratch
+engine for the same contract -- ``generate(prompts, sampling_params)`` returning per-sample records
+``{token_ids, finish_reason, logprobs, prompt_len}`` -- built on this package's kernels:
+
+* prefill runs the training-side tcgen05 attention over the packed prompts; every DISTINCT prompt
+  is prefilled once and its full KV pages are shared (reference counted) by all of its rollouts;
+* decode is one CUDA graph per batch-size bucket: embedding, the tcgen05 GEMMs (narrow tiles for
+  skinny problems), fused q/k-norm+RoPE, paged split-KV attention, SwiGLU epilogue, lm-head and a
+  Gumbel-max sampling kernel; sequence lengths, positions and page tables live in device buffers
+  that the graph reads, so the host only looks at finished flags every ``sync_interval`` steps;
+* with ``cascade=True`` decode attention is two passes merged by log-sum-exp: one pass per prompt
+  group over the shared prompt pages (KV read once for all rollouts of the group), one pass per
+  sequence over its private pages.
+
+Pages for a sequence's maximum length are reserved at admission, which keeps the decode loop free
+of host-side allocation.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..models.config import DecoderConfig
+from ..models.decoder import DecoderLM
+from ..ops import _lib, gemm, norm
+from ..ops.attention import AttnLayout, attention_fwd_cuda
+
+PAGE = 16
+MAX_NQ = 16
+
+
+@dataclass
+class SamplingParams:
+    n: int = 1
+    temperature: float = 1.0
+    max_tokens: int = 16
+    top_p: float = 1.0
+    top_k: int = -1
+    stop_token_ids: Tuple[int, ...] = ()
+    ignore_eos: bool = False
+    logprobs: Optional[int] = None
+    seed: Optional[int] = None
+
+    @staticmethod
+    def from_dict(d: Optional[dict]) -> "SamplingParams":
+        d = dict(d or {})
+        sp = SamplingParams()
+        for k in ("n", "temperature", "max_tokens", "top_p", "top_k", "ignore_eos", "logprobs", "seed"):
+            if k in d and d[k] is not None:
+                setattr(sp, k, d[k])
+        if d.get("stop_token_ids"):
+            sp.stop_token_ids = tuple(int(x) for x in d["stop_token_ids"])
+        return sp
+
+
+class PageAllocator:
+    """Reference-counted KV pages (C++ runtime, ``runtime.cpp``)."""
+
+    def __init__(self, num_pages: int):
+        self.rt = _lib.rt_lib()
+        self.h = self.rt.apb_rt_pages_create(num_pages)
+        self.num_pages = num_pages
+
+    def free_count(self) -> int:
+        return self.rt.apb_rt_pages_free_count(self.h)
+
+    def alloc(self, n: int) -> Optional[np.ndarray]:
+        out = np.empty(max(n, 1), dtype=np.int32)
+        if n == 0:
+            return out[:0]
+        rc = self.rt.apb_rt_pages_alloc(self.h, n, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int32)))
+        return out[:n] if rc == 0 else None
+
+    def retain(self, pages: np.ndarray) -> None:
+        if len(pages):
+            p = np.ascontiguousarray(pages, dtype=np.int32)
+            if self.rt.apb_rt_pages_retain(self.h, len(p), p.ctypes.data_as(ctypes.POINTER(ctypes.c_int32))) != 0:
+                raise RuntimeError("retain of a page that is not allocated")
+
+    def release(self, pages: np.ndarray) -> None:
+        if len(pages):
+            p = np.ascontiguousarray(pages, dtype=np.int32)
+            if self.rt.apb_rt_pages_release(self.h, len(p), p.ctypes.data_as(ctypes.POINTER(ctypes.c_int32))) < 0:
+                raise RuntimeError("release of a page that is not allocated")
+
+    def __del__(self):
+        try:
+            self.rt.apb_rt_pages_destroy(self.h)
+        except Exception:
+            pass
+
+
+@dataclass
+class _Seq:
+    req: int                     # index of the prompt in the generate() call
+    sample: int                  # rollout index within the prompt
+    prompt_len: int
+    max_new: int
+    shared_pages: np.ndarray     # full prompt pages shared with the group
+    private_pages: np.ndarray    # prompt tail + response pages owned by this sequence
+    group: int
+    out: List[int] = field(default_factory=list)
+    lps: List[float] = field(default_factory=list)
+    finish: Optional[str] = None
+
+
+_FN: Dict[str, object] = {}
+
+
+def _fn(name: str):
+    if not _FN:
+        c = ctypes
+        vp, i, ll, f, u = c.c_void_p, c.c_int, c.c_longlong, c.c_float, c.c_uint
+        _FN["kvw"] = _lib.declare("apb_kv_cache_write", [vp, ll, vp, ll, vp, vp, vp, i, i, i, vp])
+        _FN["dec"] = _lib.declare("apb_paged_decode_partial", [vp, vp, vp, vp, i, vp, vp, vp, vp, vp, i, i, i, i, i, f, vp])
+        _FN["merge"] = _lib.declare("apb_decode_merge", [vp, vp, vp, i, vp, vp, i, i, i, vp])
+        _FN["sample"] = _lib.declare("apb_sample", [vp, ll, vp, i, i, u, vp, vp, vp, vp])
+    return _FN[name]
+
+
+class SamplerEngine:
+    def __init__(self, cfg: DecoderConfig, device="cuda", model: Optional[DecoderLM] = None,
+                 kv_cache_tokens: int = 1 << 20, max_batch: int = 256, max_seq_len: int = 8192,
+                 cascade: bool = True, sync_interval: int = 16, use_cuda_graph: bool = True, seed: int = 0,
+                 eos_token_id: Optional[int] = None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.model = model if model is not None else DecoderLM(cfg, self.device, torch.bfloat16)
+        self.max_batch = max_batch
+        self.max_seq_len = max_seq_len
+        self.cascade = cascade
+        self.sync_interval = sync_interval
+        self.use_cuda_graph = use_cuda_graph
+        self.seed = seed
+        self.eos = eos_token_id
+        self.num_pages = max(64, kv_cache_tokens // PAGE)
+        self.max_pages = (max_seq_len + PAGE - 1) // PAGE + 1
+        self._alloc_cache()
+        self.pages = PageAllocator(self.num_pages)
+        self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self._step_count = 0
+        self._asleep = False
+        self._alloc_state()
+
+    # ------------------------------------------------------------------ memory
+    def _alloc_cache(self) -> None:
+        c = self.cfg
+        shape = (c.num_layers, self.num_pages, c.num_kv_heads, PAGE, c.head_dim)
+        self.kcache = torch.empty(shape, device=self.device, dtype=torch.bfloat16)
+        self.vcache = torch.empty(shape, device=self.device, dtype=torch.bfloat16)
+
+    def _alloc_state(self) -> None:
+        B, dev, c = self.max_batch, self.device, self.cfg
+        i32 = dict(device=dev, dtype=torch.int32)
+        self.d_tokens = torch.zeros(B, **i32)
+        self.d_pos = torch.zeros(B, **i32)
+        self.d_len = torch.zeros(B, **i32)            # tokens in cache incl. the current one (0 = inactive slot)
+        self.d_active = torch.zeros(B, **i32)
+        self.d_max_len = torch.zeros(B, **i32)
+        self.d_finished = torch.zeros(B, **i32)
+        self.d_temp = torch.ones(B, device=dev, dtype=torch.float32)
+        self.d_page_table = torch.zeros((B, self.max_pages), **i32)       # all pages of the sequence, in order
+        self.d_priv_table = torch.zeros((B, self.max_pages), **i32)       # private pages only
+        self.d_priv_len = torch.zeros(B, **i32)
+        self.d_shared_tokens = torch.zeros(B, **i32)
+        self.d_q_start = torch.arange(B, **i32)
+        self.d_q_one = torch.ones(B, **i32)
+        # prefix groups (cascade): rows of one group are consecutive slots
+        self.d_g_start = torch.zeros(B, **i32)
+        self.d_g_count = torch.zeros(B, **i32)
+        self.d_g_pages = torch.zeros((B, self.max_pages), **i32)
+        self.d_g_len = torch.zeros(B, **i32)
+        self.out_cap = 0
+        self.d_out_tokens = None
+        self.d_out_lps = None
+        self.d_out_idx = torch.zeros((B, 1), device=dev, dtype=torch.int64)   # tokens emitted so far per slot
+        self.d_step = torch.zeros(1, **i32)                                   # global decode step (RNG stream)
+        self.d_stop = torch.full((8,), -1, **i32)
+        self.splits = 4
+        Hq, D = c.num_heads, c.head_dim
+        f32 = dict(device=dev, dtype=torch.float32)
+        self.part_o = [torch.empty((B, Hq, self.splits, D), **f32) for _ in range(2)]
+        self.part_ml = [torch.empty((B, Hq, self.splits, 2), **f32) for _ in range(2)]
+        self.d_logits = torch.empty((B, c.vocab_size), **f32)
+        self.d_new_tok = torch.zeros(B, **i32)
+        self.d_new_lp = torch.zeros(B, **f32)
+
+    def kv_bytes(self) -> int:
+        return 2 * self.kcache.numel() * 2
+
+    # ------------------------------------------------------------------ layers (no autograd)
+    @torch.no_grad()
+    def _block(self, li: int, x, stream, positions, slots, attn_fn):
+        c = self.cfg
+        blk = self.model.blocks[li]
+        h, stream = norm.rmsnorm(x, blk.ln1, c.rms_norm_eps, stream)
+        qkv = gemm.matmul_nt(h, blk.wqkv)
+        q, k, v = norm.qknorm_rope(qkv, blk.q_norm, blk.k_norm, *self.model.rope(self.device), positions, c.num_heads,
+                                   c.num_kv_heads, c.head_dim, c.rms_norm_eps)
+        _lib.check(_fn("kvw")(_lib.ptr(k), k.stride(0), _lib.ptr(v), v.stride(0), _lib.ptr(slots),
+                              _lib.ptr(self.kcache[li]), _lib.ptr(self.vcache[li]), k.shape[0], c.num_kv_heads,
+                              c.head_dim, _lib.stream_ptr()), "kv_cache_write")
+        a = attn_fn(li, q, k, v)
+        o = gemm.matmul_nt(a.reshape(a.shape[0], -1), blk.wo)
+        h2, stream = norm.rmsnorm(o, blk.ln2, c.rms_norm_eps, stream)
+        if blk.mlp is not None:
+            d = blk.mlp(h2)
+        else:
+            _, act = gemm.gate_up_swiglu(h2, blk.wgu, keep_gu=False)
+            d = gemm.matmul_nt(act, blk.wdown)
+        return d, stream
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def _prefill(self, prompts: List[np.ndarray], page_lists: List[np.ndarray]) -> torch.Tensor:
+        """Runs the packed prompts through the model, fills their KV pages and returns the final-norm
+        hidden state of each prompt's last token ``[len(prompts), H]``."""
+        lens = np.array([len(p) for p in prompts], dtype=np.int64)
+        cu = np.concatenate([[0], np.cumsum(lens)])
+        T = int(cu[-1])
+        ids = torch.from_numpy(np.concatenate(prompts).astype(np.int64)).to(self.device)
+        pos_np = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+        slots_np = np.concatenate([pl[np.arange(n) // PAGE] * PAGE + np.arange(n) % PAGE
+                                   for n, pl in zip(lens, page_lists)]).astype(np.int32)
+        positions = torch.from_numpy(pos_np).to(self.device)
+        slots = torch.from_numpy(slots_np).to(self.device)
+        layout = AttnLayout.from_cu_seqlens(cu)
+        scale = 1.0 / math.sqrt(self.cfg.head_dim)
+
+        def attn(li, q, k, v):
+            o, _ = attention_fwd_cuda(q, k, v.contiguous() if v.stride(1) != v.shape[2] else v, layout, scale,
+                                      need_lse=False)
+            return o
+
+        x = torch.nn.functional.embedding(ids, self.model.embed)
+        stream = None
+        for li in range(self.cfg.num_layers):
+            x, stream = self._block(li, x, stream, positions, slots, attn)
+        last = torch.from_numpy((cu[1:] - 1).astype(np.int64)).to(self.device)
+        xl = x.index_select(0, last)
+        sl = stream.index_select(0, last)
+        h, _ = norm.rmsnorm(xl, self.model.final_norm, self.cfg.rms_norm_eps, sl)
+        return h
+
+    # ------------------------------------------------------------------ decode step
+    @torch.no_grad()
+    def _decode_attention(self, li: int, q: torch.Tensor, B: int) -> torch.Tensor:
+        c = self.cfg
+        scale = 1.0 / math.sqrt(c.head_dim)
+        s = _lib.stream_ptr()
+        dec, merge = _fn("dec"), _fn("merge")
+        kc, vc = self.kcache[li], self.vcache[li]
+        out = torch.empty((B, c.num_heads, c.head_dim), device=self.device, dtype=torch.bfloat16)
+        if self.cascade:
+            _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_g_start), _lib.ptr(self.d_g_count), _lib.ptr(self.d_g_pages),
+                           self.max_pages, _lib.ptr(self.d_g_len), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(self.part_o[0]),
+                           _lib.ptr(self.part_ml[0]), B, c.num_heads, c.num_kv_heads, c.head_dim, self.splits, scale, s),
+                       "paged_decode(prefix)")
+            _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_q_start), _lib.ptr(self.d_active), _lib.ptr(self.d_priv_table),
+                           self.max_pages, _lib.ptr(self.d_priv_len), _lib.ptr(kc), _lib.ptr(vc),
+                           _lib.ptr(self.part_o[1]), _lib.ptr(self.part_ml[1]), B, c.num_heads, c.num_kv_heads,
+                           c.head_dim, self.splits, scale, s), "paged_decode(private)")
+            n_src = 2
+        else:
+            _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_q_start), _lib.ptr(self.d_active), _lib.ptr(self.d_page_table),
+                           self.max_pages, _lib.ptr(self.d_len), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(self.part_o[0]),
+                           _lib.ptr(self.part_ml[0]), B, c.num_heads, c.num_kv_heads, c.head_dim, self.splits, scale, s),
+                       "paged_decode")
+            n_src = 1
+        o_ptrs = (ctypes.c_void_p * 4)(*[self.part_o[i].data_ptr() if i < n_src else 0 for i in range(4)])
+        ml_ptrs = (ctypes.c_void_p * 4)(*[self.part_ml[i].data_ptr() if i < n_src else 0 for i in range(4)])
+        sp = (ctypes.c_int * 4)(*[self.splits if i < n_src else 0 for i in range(4)])
+        _lib.check(merge(o_ptrs, ml_ptrs, sp, n_src, _lib.ptr(out), None, B, c.num_heads, c.head_dim, s), "decode_merge")
+        return out
+
+    @torch.no_grad()
+    def _decode_step(self, B: int) -> None:
+        """One token for slots [0, B).  Reads and updates device state only, so the whole step can be
+        captured in a CUDA graph and replayed."""
+        c = self.cfg
+        act = self.d_active[:B] > 0
+        positions = self.d_pos[:B]
+        pidx = torch.div(positions, PAGE, rounding_mode="floor").long()
+        page = self.d_page_table[:B].gather(1, pidx[:, None]).squeeze(1)
+        slots = torch.where(act, page * PAGE + positions % PAGE, torch.full_like(page, -1)).int()
+        x = torch.nn.functional.embedding(self.d_tokens[:B].long(), self.model.embed)
+        stream = None
+        attn = lambda li, q, k, v: self._decode_attention(li, q, B)
+        for li in range(c.num_layers):
+            x, stream = self._block(li, x, stream, positions, slots, attn)
+        h, _ = norm.rmsnorm(x, self.model.final_norm, c.rms_norm_eps, stream)
+        logits = self.d_logits[:B]
+        gemm.matmul_nt(h, self.model.output_weight, out=logits)
+        _lib.check(_fn("sample")(_lib.ptr(logits), logits.stride(0), _lib.ptr(self.d_temp), B, c.vocab_size,
+                                 ctypes.c_uint(self.seed & 0xFFFFFFFF), _lib.ptr(self.d_step), _lib.ptr(self.d_new_tok),
+                                 _lib.ptr(self.d_new_lp), _lib.stream_ptr()), "sample")
+        new_tok, new_lp = self.d_new_tok[:B], self.d_new_lp[:B]
+        idx = self.d_out_idx[:B].clamp(max=self.out_cap - 1)
+        self.d_out_tokens[:B].scatter_(1, idx, torch.where(act, new_tok, self.d_out_tokens[:B].gather(1, idx).squeeze(1))[:, None])
+        self.d_out_lps[:B].scatter_(1, idx, torch.where(act, new_lp, self.d_out_lps[:B].gather(1, idx).squeeze(1))[:, None])
+        self.d_out_idx[:B] += act.long()[:, None]
+        newlen = self.d_len[:B] + act.int()
+        stop = (new_tok[:, None] == self.d_stop[None, :]).any(1)
+        done = act & (stop | (newlen >= self.d_max_len[:B]))
+        self.d_finished[:B] |= done.int()
+        still = act & ~done
+        self.d_active[:B] = still.int()
+        self.d_tokens[:B] = torch.where(still, new_tok, self.d_tokens[:B])
+        self.d_pos[:B] += still.int()
+        self.d_len[:B] = torch.where(still, newlen, self.d_len[:B])
+        self.d_priv_len[:B] += still.int()
+        self.d_step += 1
+
+    def _run_steps(self, B: int, n: int) -> None:
+        if not self.use_cuda_graph or self.cfg.is_moe:
+            for _ in range(n):
+                self._decode_step(B)
+            return
+        g = self._graphs.get(B)
+        if g is None:
+            # the first steps run eagerly (kernel attribute set-up, device binding, allocator warm-up)
+            self._decode_step(B)
+            n -= 1
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._decode_step(B)
+            self._graphs[B] = g
+        for _ in range(n):
+            g.replay()
+
+    # ------------------------------------------------------------------ public API
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[Sequence[int]], sampling_params=None) -> List[dict]:
+        """Generates ``n`` samples per prompt.  Returns one record per sample, prompt-major:
+        ``{"token_ids", "logprobs", "finish_reason", "prompt_len", "prompt_index", "text"}``."""
+        sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
+        if self._asleep:
+            raise RuntimeError("sampler is asleep; call wake() first")
+        if sp.top_k not in (-1, 0) or sp.top_p < 1.0:
+            raise NotImplementedError("top-k / top-p filtering is not implemented in the sampling kernel")
+        prompts_np = [np.asarray(p, dtype=np.int64) for p in prompts]
+        for p in prompts_np:
+            if len(p) == 0:
+                raise ValueError("empty prompt")
+            if len(p) + sp.max_tokens > self.max_seq_len:
+                raise ValueError(f"prompt ({len(p)}) + max_tokens ({sp.max_tokens}) exceeds max_seq_len {self.max_seq_len}")
+        stops = list(sp.stop_token_ids)
+        if self.eos is not None and not sp.ignore_eos:
+            stops.append(self.eos)
+        stops = stops[:8]
+        self.d_stop.fill_(-1)
+        if stops:
+            self.d_stop[:len(stops)] = torch.tensor(stops, dtype=torch.int32, device=self.device)
+        if self.out_cap < sp.max_tokens:
+            self.out_cap = sp.max_tokens
+            self.d_out_tokens = torch.zeros((self.max_batch, self.out_cap), device=self.device, dtype=torch.int32)
+            self.d_out_lps = torch.zeros((self.max_batch, self.out_cap), device=self.device, dtype=torch.float32)
+            self._graphs.clear()
+        if sp.seed is not None:
+            self.seed = int(sp.seed)
+        results: List[Optional[dict]] = [None] * (len(prompts_np) * sp.n)
+        # work queue: one entry per prompt; a prompt's n rollouts are admitted together (one prefix group)
+        queue = list(range(len(prompts_np)))
+        slots_free = list(range(self.max_batch))
+        live: Dict[int, _Seq] = {}
+        group_prompt_pages: Dict[int, np.ndarray] = {}
+        group_members: Dict[int, List[int]] = {}
+        next_group = 0
+        while queue or live:
+            # ---- admission: as many whole prompts as fit in slots and pages
+            admitted: List[Tuple[int, List[int]]] = []
+            while queue and len(slots_free) >= sp.n:
+                r = queue[0]
+                P = len(prompts_np[r])
+                n_full = P // PAGE
+                tail = P - n_full * PAGE
+                priv_pages = (tail + sp.max_tokens + PAGE - 1) // PAGE
+                need = n_full + sp.n * priv_pages
+                if self.pages.free_count() < need:
+                    break
+                queue.pop(0)
+                shared = self.pages.alloc(n_full)
+                gid = next_group
+                next_group += 1
+                group_prompt_pages[gid] = shared
+                mem = []
+                slots_free.sort()
+                for si in range(sp.n):
+                    slot = slots_free.pop(0)
+                    priv = self.pages.alloc(priv_pages)
+                    if si > 0:
+                        self.pages.retain(shared)
+                    live[slot] = _Seq(req=r, sample=si, prompt_len=P, max_new=sp.max_tokens, shared_pages=shared,
+                                      private_pages=priv, group=gid)
+                    mem.append(slot)
+                group_members[gid] = mem
+                admitted.append((gid, mem))
+            if not admitted and not live:
+                raise RuntimeError("KV cache too small for a single prompt group; raise kv_cache_tokens")
+            if admitted:
+                self._admit(admitted, prompts_np, live, sp)
+            # ---- decode until the next look at the finished flags
+            B = max(live) + 1 if live else 0
+            bucket = next((b for b in (8, 16, 32, 64, 128, 256, 512, 1024) if b >= B), self.max_batch)
+            bucket = min(bucket, self.max_batch)
+            if B > 0:
+                self._set_groups(group_members, live)
+                self._run_steps(bucket, self.sync_interval)
+            # ---- harvest
+            fin = self.d_finished[:max(B, 1)].cpu().numpy() if B else np.zeros(0, dtype=np.int32)
+            done_slots = [s for s in list(live) if fin[s]]
+            if done_slots:
+                nout = self.d_out_idx[:B, 0].cpu().numpy()
+                toks = self.d_out_tokens[:B].cpu().numpy()
+                lps = self.d_out_lps[:B].cpu().numpy()
+                for s in done_slots:
+                    sq = live.pop(s)
+                    k = int(nout[s])
+                    out = toks[s, :k].tolist()
+                    reason = "stop" if (out and out[-1] in stops) else "length"
+                    results[sq.req * sp.n + sq.sample] = {
+                        "token_ids": out, "logprobs": lps[s, :k].tolist(), "finish_reason": reason,
+                        "prompt_len": sq.prompt_len, "prompt_index": sq.req, "text": None}
+                    self.pages.release(sq.private_pages)
+                    self.pages.release(sq.shared_pages)
+                    group_members[sq.group].remove(s)
+                    if not group_members[sq.group]:
+                        del group_members[sq.group]
+                        del group_prompt_pages[sq.group]
+                    slots_free.append(s)
+                    self.d_finished[s] = 0
+                    self.d_len[s] = 0
+                    self.d_priv_len[s] = 0
+        return results  # type: ignore[return-value]
+
+    # ------------------------------------------------------------------ admission
+    @torch.no_grad()
+    def _admit(self, admitted, prompts_np, live: Dict[int, _Seq], sp: SamplingParams,
+               token_budget: int = 32768) -> None:
+        """Prefills each admitted prompt ONCE, copies its partial tail page to every rollout's private
+        page, samples the first token of every rollout and initialises the slot state."""
+        c = self.cfg
+        # batches of prompts under the token budget
+        batches: List[List[Tuple[int, List[int]]]] = [[]]
+        tok = 0
+        for gid, mem in admitted:
+            P = live[mem[0]].prompt_len
+            if batches[-1] and tok + P > token_budget:
+                batches.append([])
+                tok = 0
+            batches[-1].append((gid, mem))
+            tok += P
+        for batch in batches:
+            prompts, page_lists = [], []
+            for gid, mem in batch:
+                s0 = live[mem[0]]
+                tail = s0.prompt_len % PAGE
+                pl = s0.shared_pages if tail == 0 else np.concatenate([s0.shared_pages, s0.private_pages[:1]])
+                prompts.append(prompts_np[s0.req])
+                page_lists.append(pl.astype(np.int64))
+            h = self._prefill(prompts, page_lists)
+            # tail page copies for rollouts 1..n-1
+            src, dst = [], []
+            for gid, mem in batch:
+                s0 = live[mem[0]]
+                if s0.prompt_len % PAGE:
+                    for slot in mem[1:]:
+                        src.append(int(s0.private_pages[0]))
+                        dst.append(int(live[slot].private_pages[0]))
+            if src:
+                si = torch.tensor(src, device=self.device)
+                di = torch.tensor(dst, device=self.device)
+                self.kcache[:, di] = self.kcache[:, si]
+                self.vcache[:, di] = self.vcache[:, si]
+            # first token of every rollout
+            rows = [gi for gi, (_, mem) in enumerate(batch) for _ in mem]
+            slots = [slot for _, mem in batch for slot in mem]
+            hrep = h.index_select(0, torch.tensor(rows, device=self.device))
+            logits = gemm.matmul_nt(hrep.contiguous(), self.model.output_weight, out_dtype=torch.float32)
+            n = len(slots)
+            temp = torch.full((n,), float(sp.temperature), device=self.device, dtype=torch.float32)
+            tok0 = torch.empty(n, device=self.device, dtype=torch.int32)
+            lp0 = torch.empty(n, device=self.device, dtype=torch.float32)
+            _lib.check(_fn("sample")(_lib.ptr(logits), logits.stride(0), _lib.ptr(temp), n, c.vocab_size,
+                                     ctypes.c_uint((self.seed * 2654435761 + 12345) & 0xFFFFFFFF), _lib.ptr(self.d_step),
+                                     _lib.ptr(tok0), _lib.ptr(lp0), _lib.stream_ptr()), "sample")
+            self.d_step += 1
+            st = torch.tensor(slots, device=self.device, dtype=torch.long)
+            P_t = torch.tensor([live[s].prompt_len for s in slots], device=self.device, dtype=torch.int32)
+            stop_hit = (tok0[:, None] == self.d_stop[None, :]).any(1)
+            fin = stop_hit | (sp.max_tokens <= 1)
+            self.d_tokens[st] = tok0
+            self.d_pos[st] = P_t
+            self.d_len[st] = P_t + 1
+            self.d_max_len[st] = P_t + int(sp.max_tokens)
+            self.d_active[st] = (~fin).int()
+            self.d_finished[st] = fin.int()
+            self.d_temp[st] = temp
+            self.d_out_tokens[st, 0] = tok0
+            self.d_out_lps[st, 0] = lp0
+            self.d_out_idx[st, 0] = 1
+            pt = np.zeros((n, self.max_pages), dtype=np.int32)
+            pv = np.zeros((n, self.max_pages), dtype=np.int32)
+            plen = np.zeros(n, dtype=np.int32)
+            sh = np.zeros(n, dtype=np.int32)
+            for i, s in enumerate(slots):
+                sq = live[s]
+                allp = np.concatenate([sq.shared_pages, sq.private_pages])
+                pt[i, :len(allp)] = allp
+                pv[i, :len(sq.private_pages)] = sq.private_pages
+                sh[i] = len(sq.shared_pages) * PAGE
+                plen[i] = sq.prompt_len - sh[i] + 1
+            self.d_page_table[st] = torch.from_numpy(pt).to(self.device)
+            self.d_priv_table[st] = torch.from_numpy(pv).to(self.device)
+            self.d_priv_len[st] = torch.from_numpy(plen).to(self.device)
+            self.d_shared_tokens[st] = torch.from_numpy(sh).to(self.device)
+
+    def _set_groups(self, group_members: Dict[int, List[int]], live: Dict[int, _Seq]) -> None:
+        """Prefix-forest tables for cascade decode: runs of consecutive slots (at most 16) that share
+        one prompt become one query group over the prompt's shared pages."""
+        if not self.cascade:
+            return
+        B = self.max_batch
+        g_start = np.zeros(B, dtype=np.int32)
+        g_count = np.zeros(B, dtype=np.int32)
+        g_len = np.zeros(B, dtype=np.int32)
+        g_pages = np.zeros((B, self.max_pages), dtype=np.int32)
+        k = 0
+        for gid, mem in group_members.items():
+            mem = sorted(mem)
+            shared = live[mem[0]].shared_pages
+            i = 0
+            while i < len(mem):
+                j = i
+                while j + 1 < len(mem) and mem[j + 1] == mem[j] + 1 and j + 1 - i < MAX_NQ:
+                    j += 1
+                g_start[k] = mem[i]
+                g_count[k] = j - i + 1
+                g_len[k] = len(shared) * PAGE
+                g_pages[k, :len(shared)] = shared
+                k += 1
+                i = j + 1
+        self.d_g_start.copy_(torch.from_numpy(g_start))
+        self.d_g_count.copy_(torch.from_numpy(g_count))
+        self.d_g_len.copy_(torch.from_numpy(g_len))
+        self.d_g_pages.copy_(torch.from_numpy(g_pages))
+
+    # ------------------------------------------------------------------ weights / sleep / wake
+    @torch.no_grad()
+    def load_weights(self, named_tensors) -> int:
+        """Copies ``(hf_name, tensor)`` pairs into the engine's fused parameters; returns the count."""
+        from ..models.hf_io import load_hf_tensor
+        n = 0
+        for name, t in named_tensors:
+            load_hf_tensor(self.model, name, t)
+            n += 1
+        return n
+
+    def weight_norm(self) -> Dict[str, float]:
+        sq = torch.zeros((), dtype=torch.float64, device=self.device)
+        n = 0
+        for p in self.model.parameters():
+            sq += p.data.double().pow(2).sum()
+            n += p.numel()
+        return {"norm": float(sq.sqrt().item()), "sq_sum": float(sq.item()), "num_params": n}
+
+    def reset_prefix_cache(self) -> None:
+        """Pages are released at the end of every ``generate`` call, so nothing outlives a weight sync."""
+        return None
+
+    def sleep(self, level: int = 1) -> None:
+        """Level 1 frees the KV cache and the captured graphs; level 2 also drops the weights (they come
+        back with the next weight sync)."""
+        self._graphs.clear()
+        self.kcache = self.vcache = None
+        if level >= 2:
+            for p in self.model.parameters():
+                p.data = torch.empty(0, device=self.device, dtype=p.dtype)
+        self._asleep = True
+        torch.cuda.empty_cache()
+
+    def wake(self, tags: Optional[Sequence[str]] = None) -> None:
+        tags = set(tags or ("weights", "kv_cache"))
+        if "kv_cache" in tags and self.kcache is None:
+            self._alloc_cache()
+            self._asleep = False

@@ -1,0 +1,413 @@
+"""Training engine: flat parameter/gradient buffers, ZeRO partitioning, fused step.
+
+What DeepSpeed provides to the reference (``deepspeed.initialize`` + ZeRO + FusedAdam,
+arctic_platform/common/deepspeed_worker.py:198-300) is implemented here directly:
+
+* all parameters live in ONE flat bf16 buffer and all gradients in ONE flat fp32 buffer
+  (``param.grad_f32`` views; the kernels' weight-gradient GEMMs accumulate straight into
+  it), cut into *units* (embedding, one per decoder block, final norm) whose lengths are
+  padded so every rank owns an equal, 16-byte aligned shard of every unit;
+* ``step()`` runs two kernels per unit (``optim.cu``): gradient reduce-scatter over NVLink
+  peer loads fused with scaling and the sum of squares, then clip + AdamW on the fp32
+  master shard fused with the bf16 parameter all-gather by peer stores;
+* the same code path serves one rank (no communication, still fused clip + AdamW);
+* ``impl="collective"`` does the same math with ``torch.distributed`` collectives and
+  PyTorch ops -- the NCCL baseline on GPUs and the only path on CPU/gloo.
+
+Gradients are fp32 and averaged over data-parallel ranks, gradient accumulation sums
+micro-batches without rescaling (``scale_wrt_gas=False`` in the reference,
+arctic_platform/rl/processors/pipeline.py:441-457), ``step()`` reports ``last_lr`` and
+``grad_norm`` (``deepspeed_worker.py:555-576``).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass, field
+from typing import Any, Dict, Iterable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..models.decoder import DecoderLM
+from ..ops import _lib
+from ..parallel.symm import EpochFlags, SymmetricBuffer
+
+
+# ----------------------------------------------------------------------------- configuration
+@dataclass
+class SchedulerConfig:
+    type: str = "constant"          # constant | warmup | cosine
+    warmup_steps: int = 0
+    total_steps: int = 0
+    min_lr_ratio: float = 0.0
+
+
+@dataclass
+class EngineConfig:
+    lr: float = 1e-5
+    betas: Tuple[float, float] = (0.9, 0.999)
+    eps: float = 1e-8
+    weight_decay: float = 0.0
+    max_grad_norm: float = 0.0
+    gradient_accumulation_steps: int = 1
+    zero_stage: int = 1
+    scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
+    impl: str = "fused"             # fused | collective
+    offload_optimizer: bool = False
+    gradient_checkpointing: bool = False
+
+    @staticmethod
+    def from_ds_config(ds_config: Optional[dict], training_config: Optional[dict] = None) -> "EngineConfig":
+        """Reads the DeepSpeed-style dict the clients send (and the higher-level ``training_config``
+        that takes precedence, with the same field names the reference accepts)."""
+        ds = dict(ds_config or {})
+        cfg = EngineConfig()
+        opt = (ds.get("optimizer") or {}).get("params", {})
+        if training_config is not None:
+            o = training_config.get("optimizer", {}) or {}
+            betas = o.get("betas") or [o.get("beta1", 0.9), o.get("beta2", 0.999)]
+            opt = {"lr": o.get("lr", 1e-5), "betas": list(betas), "eps": o.get("eps", 1e-8),
+                   "weight_decay": o.get("weight_decay", 0.0)}
+            if "gradient_accumulation_steps" in training_config:
+                ds["gradient_accumulation_steps"] = training_config["gradient_accumulation_steps"]
+            for src, key in ((o, "gradient_clipping"), (training_config, "gradient_clipping"), (o, "max_grad_norm")):
+                if key in src:
+                    ds["gradient_clipping"] = src[key]
+                    break
+            sched = training_config.get("lr_scheduler")
+            horizon = int(training_config.get("training_horizon", 0) or 0)
+            if sched is not None and horizon > 0:
+                warm = round(float(sched["warmup_steps"])) if "warmup_steps" in sched else round(
+                    float(sched.get("warmup_ratio", 0.0)) * horizon)
+                if sched.get("type", "constant") == "cosine":
+                    cfg.scheduler = SchedulerConfig("cosine", warm, horizon, float(sched.get("min_lr_ratio") or 0.0))
+                elif warm > 0:
+                    cfg.scheduler = SchedulerConfig("warmup", warm, horizon, 0.0)
+        elif "scheduler" in ds:
+            sp = ds["scheduler"].get("params", {})
+            kind = {"WarmupCosineLR": "cosine", "WarmupLR": "warmup"}.get(ds["scheduler"].get("type"), "constant")
+            cfg.scheduler = SchedulerConfig(kind, int(sp.get("warmup_num_steps", 0)), int(sp.get("total_num_steps", 0)),
+                                            float(sp.get("cos_min_ratio", 0.0)))
+        cfg.lr = float(opt.get("lr", 1e-5))
+        b = opt.get("betas", [0.9, 0.999])
+        cfg.betas = (float(b[0]), float(b[1]))
+        cfg.eps = float(opt.get("eps", 1e-8))
+        cfg.weight_decay = float(opt.get("weight_decay", 0.0))
+        cfg.max_grad_norm = float(ds.get("gradient_clipping", 0.0) or 0.0)
+        cfg.gradient_accumulation_steps = int(ds.get("gradient_accumulation_steps", 1))
+        zero = ds.get("zero_optimization", {}) or {}
+        cfg.zero_stage = int(zero.get("stage", 1))
+        cfg.offload_optimizer = (zero.get("offload_optimizer") or {}).get("device", "none") == "cpu"
+        cfg.impl = ds.get("b200_impl", "fused")
+        return cfg
+
+
+def lr_at(cfg: EngineConfig, step: int) -> float:
+    """Learning rate for optimizer step number ``step`` (0-based)."""
+    s = cfg.scheduler
+    if s.type == "constant":
+        return cfg.lr
+    if s.warmup_steps > 0 and step < s.warmup_steps:
+        return cfg.lr * (step + 1) / s.warmup_steps if s.type == "warmup" else cfg.lr * step / s.warmup_steps
+    if s.type == "warmup":
+        return cfg.lr
+    span = max(1, s.total_steps - s.warmup_steps)
+    prog = min(1.0, max(0.0, (step - s.warmup_steps) / span))
+    cos = 0.5 * (1.0 + math.cos(math.pi * prog))
+    return cfg.lr * (s.min_lr_ratio + (1.0 - s.min_lr_ratio) * cos)
+
+
+# ----------------------------------------------------------------------------- flat layout
+@dataclass
+class Unit:
+    name: str
+    params: List[Tuple[str, torch.nn.Parameter]]
+    offset: int = 0      # element offset of the unit in the flat buffers
+    length: int = 0      # padded element count (multiple of 8 * world)
+
+
+def model_units(model: DecoderLM) -> List[Unit]:
+    units = [Unit("embed", [("embed", model.embed)] + ([("lm_head", model.lm_head)] if model.lm_head is not None else []))]
+    for i, blk in enumerate(model.blocks):
+        units.append(Unit(f"block{i}", [(f"blocks.{i}.{n}", p) for n, p in blk.named_parameters()]))
+    units.append(Unit("final", [("final_norm", model.final_norm)]))
+    return units
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class TrainEngine:
+    def __init__(self, model: DecoderLM, cfg: EngineConfig, group=None, forward_only: bool = False):
+        self.model = model
+        self.cfg = cfg
+        self.group = group
+        self.forward_only = forward_only
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        p0 = next(model.parameters())
+        self.device = p0.device
+        self.param_dtype = p0.dtype
+        self.on_cuda = self.device.type == "cuda"
+        self.impl = cfg.impl if self.on_cuda else "collective"
+        self.global_steps = 0
+        self.micro_steps = 0
+        self.last_grad_norm = 0.0
+        model.gradient_checkpointing = cfg.gradient_checkpointing
+        self._build_flat()
+
+    # ------------------------------------------------------------------ layout
+    def _build_flat(self) -> None:
+        W = self.world
+        self.units = model_units(self.model)
+        off = 0
+        self.param_slices: Dict[str, Tuple[int, int, torch.Size]] = {}
+        for u in self.units:
+            u.offset = off
+            cur = off
+            for name, p in u.params:
+                self.param_slices[name] = (cur, p.numel(), p.shape)
+                cur = _round_up(cur + p.numel(), 8)
+            u.length = _round_up(cur - off, 8 * W)
+            off += u.length
+        self.total = off
+        use_symm = self.impl == "fused" and W > 1
+        self.param_buf = (SymmetricBuffer(self.total, self.param_dtype, self.device, self.group) if use_symm
+                          else SymmetricBuffer(self.total, self.param_dtype, self.device, False))
+        flat = self.param_buf.tensor
+        with torch.no_grad():
+            for u in self.units:
+                for name, p in u.params:
+                    o, n, shape = self.param_slices[name]
+                    view = flat[o:o + n].view(shape)
+                    view.copy_(p.data)
+                    p.data = view
+        if self.forward_only:
+            return
+        self.grad_buf = (SymmetricBuffer(self.total, torch.float32, self.device, self.group) if use_symm
+                         else SymmetricBuffer(self.total, torch.float32, self.device, False))
+        gflat = self.grad_buf.tensor
+        for u in self.units:
+            for name, p in u.params:
+                o, n, shape = self.param_slices[name]
+                p.grad_f32 = gflat[o:o + n].view(shape)
+        self.flags = EpochFlags(self.device, self.group if use_symm else False) if self.on_cuda else None
+        # optimizer shards: for every unit this rank owns [offset + rank*len/W, +len/W)
+        self.shard_total = self.total // W
+        self.unit_shard_off: List[int] = []
+        acc = 0
+        for u in self.units:
+            self.unit_shard_off.append(acc)
+            acc += u.length // W
+        opt_dev = "cpu" if (self.cfg.offload_optimizer and not self.on_cuda) else self.device
+        self.master = torch.empty(self.shard_total, dtype=torch.float32, device=opt_dev)
+        for u, so in zip(self.units, self.unit_shard_off):
+            n = u.length // W
+            s = u.offset + self.rank * n
+            self.master[so:so + n].copy_(flat[s:s + n].float())
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+        # W == 1: the reduced gradient is the gradient buffer itself (in place)
+        self.reduced = gflat if W == 1 else torch.empty(self.shard_total, dtype=torch.float32, device=self.device)
+        self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self._offloaded: Dict[str, torch.Tensor] = {}
+
+    # ------------------------------------------------------------------ training loop pieces
+    def zero_grad(self) -> None:
+        self.grad_buf.tensor.zero_()
+        for p in self.model.parameters():
+            p.grad = None
+
+    def gradient_accumulation_steps(self) -> int:
+        return self.cfg.gradient_accumulation_steps
+
+    def backward(self, loss: torch.Tensor) -> None:
+        loss.backward()
+        self.collect_autograd_grads()
+        self.micro_steps += 1
+
+    def collect_autograd_grads(self) -> None:
+        """Gradients that autograd produced as ``p.grad`` (CPU ops, embedding lookup) are folded
+        into the flat fp32 buffer; kernels with ``grad_f32`` support have written there already."""
+        for p in self.model.parameters():
+            if p.grad is not None:
+                p.grad_f32.add_(p.grad.to(torch.float32))
+                p.grad = None
+
+    def is_gradient_accumulation_boundary(self) -> bool:
+        return self.micro_steps % self.cfg.gradient_accumulation_steps == 0
+
+    # ------------------------------------------------------------------ optimizer step
+    def step(self) -> Dict[str, float]:
+        cfg = self.cfg
+        lr = lr_at(cfg, self.global_steps)
+        t = self.global_steps + 1
+        bias1 = 1.0 - cfg.betas[0] ** t
+        bias2 = 1.0 - cfg.betas[1] ** t
+        self.sumsq.zero_()
+        if self.impl == "fused":
+            self._step_fused(lr, bias1, bias2)
+        else:
+            self._step_collective(lr, bias1, bias2)
+        self.global_steps += 1
+        self.zero_grad()
+        self.last_lr = lr
+        return {"last_lr": lr, "grad_norm": self._grad_norm_tensor}
+
+    def grad_norm_value(self) -> float:
+        g = self._grad_norm_tensor
+        return float(g.item()) if torch.is_tensor(g) else float(g)
+
+    def _step_fused(self, lr, bias1, bias2) -> None:
+        lib = _lib.cuda_lib()
+        fn_r = _fused_fns()["reduce"]
+        fn_a = _fused_fns()["adamw"]
+        fn_w = _fused_fns()["wait"]
+        W, r = self.world, self.rank
+        s = _lib.stream_ptr()
+        flags_tbl = self.flags.ptr_table()
+        cfg = self.cfg
+        for u, so in zip(self.units, self.unit_shard_off):
+            n = u.length // W
+            shard_off = r * n
+            gp = self.grad_buf.ptr_table(u.offset * 4)
+            red_ptr = (self.grad_buf.tensor.data_ptr() + u.offset * 4) if W == 1 else (self.reduced.data_ptr() + so * 4)
+            mc = self.grad_buf.mc_ptr(u.offset * 4)
+            _lib.check(fn_r(gp, mc, flags_tbl, r, W, self.flags.next(), shard_off, n, 1.0 / W,
+                            ctypes.c_void_p(red_ptr), _lib.ptr(self.sumsq), s), "apb_zero_reduce")
+        if W > 1:
+            dist.all_reduce(self.sumsq, group=self.group)
+        self._grad_norm_tensor = self.sumsq.sqrt().float().clone()
+        for u, so in zip(self.units, self.unit_shard_off):
+            n = u.length // W
+            shard_off = r * n
+            pp = self.param_buf.ptr_table(u.offset * 2)
+            mc = self.param_buf.mc_ptr(u.offset * 2)
+            red_ptr = (self.grad_buf.tensor.data_ptr() + u.offset * 4) if W == 1 else (self.reduced.data_ptr() + so * 4)
+            _lib.check(fn_a(pp, mc, flags_tbl, r, W, self.flags.next(), shard_off, n, ctypes.c_void_p(red_ptr),
+                            ctypes.c_void_p(self.master.data_ptr() + so * 4),
+                            ctypes.c_void_p(self.exp_avg.data_ptr() + so * 4),
+                            ctypes.c_void_p(self.exp_avg_sq.data_ptr() + so * 4), _lib.ptr(self.sumsq),
+                            lr, cfg.betas[0], cfg.betas[1], cfg.eps, cfg.weight_decay, bias1, bias2,
+                            cfg.max_grad_norm, s), "apb_zero_adamw")
+        if W > 1:
+            _lib.check(fn_w(flags_tbl, r, W, self.flags.next(), s), "apb_epoch_wait")
+
+    def _step_collective(self, lr, bias1, bias2) -> None:
+        W, r = self.world, self.rank
+        cfg = self.cfg
+        gflat = self.grad_buf.tensor
+        shards = []
+        for u in self.units:
+            n = u.length // W
+            g = gflat[u.offset:u.offset + u.length]
+            if W > 1:
+                if self.on_cuda:
+                    out = torch.empty(n, dtype=torch.float32, device=self.device)
+                    dist.reduce_scatter_tensor(out, g, op=dist.ReduceOp.SUM, group=self.group)
+                    out.div_(W)
+                else:
+                    dist.all_reduce(g, group=self.group)
+                    out = g[r * n:(r + 1) * n] / W
+            else:
+                out = g[:n]
+            shards.append(out)
+        sq = sum((s.double() ** 2).sum() for s in shards)
+        sq = sq.reshape(1).to(self.device)
+        if W > 1:
+            dist.all_reduce(sq, group=self.group)
+        norm = sq.sqrt().float()
+        self._grad_norm_tensor = norm.reshape(())
+        clip = torch.clamp(cfg.max_grad_norm / (norm + 1e-6), max=1.0) if cfg.max_grad_norm > 0 else None
+        flat = self.param_buf.tensor
+        for u, so, g in zip(self.units, self.unit_shard_off, shards):
+            n = u.length // W
+            g = g.to(self.master.device)
+            if clip is not None:
+                g = g * clip.to(g.device)
+            m = self.exp_avg[so:so + n]
+            v = self.exp_avg_sq[so:so + n]
+            w = self.master[so:so + n]
+            m.mul_(cfg.betas[0]).add_(g, alpha=1 - cfg.betas[0])
+            v.mul_(cfg.betas[1]).addcmul_(g, g, value=1 - cfg.betas[1])
+            w.mul_(1 - lr * cfg.weight_decay)
+            w.addcdiv_(m / bias1, (v / bias2).sqrt_().add_(cfg.eps), value=-lr)
+            new = w.to(self.param_dtype).to(self.device)
+            dst = flat[u.offset:u.offset + u.length]
+            if W > 1:
+                dist.all_gather_into_tensor(dst, new.contiguous(), group=self.group) if self.on_cuda else \
+                    _gloo_all_gather(dst, new, W, self.group)
+            else:
+                dst[:n].copy_(new)
+
+    # ------------------------------------------------------------------ introspection
+    def iter_hf_tensors(self):
+        from ..models.hf_io import iter_hf_tensors
+        return iter_hf_tensors(self.model)
+
+    @torch.no_grad()
+    def weight_norm(self) -> Dict[str, float]:
+        """Global L2 norm over the real (unpadded) parameters in fp64, as the reference's weight-sync
+        check computes it (arctic_platform/common/deepspeed_worker.py:685-704)."""
+        sq = torch.zeros((), dtype=torch.float64, device=self.device)
+        n = 0
+        for p in self.model.parameters():
+            sq += p.data.double().pow(2).sum()
+            n += p.numel()
+        return {"norm": float(sq.sqrt().item()), "sq_sum": float(sq.item()), "num_params": n}
+
+    # ------------------------------------------------------------------ sleep / wake
+    def offload_states(self, include: Iterable[str] = ("optimizer", "grads", "params")) -> None:
+        """Moves the selected state to pinned host memory and frees the device copies.  ``params`` can
+        only be offloaded when they are not in symmetric memory (their addresses are registered with peers)."""
+        if not self.on_cuda:
+            return
+        for key in include:
+            if key == "optimizer" and not self.forward_only:
+                for nm in ("master", "exp_avg", "exp_avg_sq"):
+                    t = getattr(self, nm)
+                    if t.is_cuda:
+                        host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+                        host.copy_(t, non_blocking=True)
+                        self._offloaded[nm] = host
+            elif key == "grads" and not self.forward_only and self.world == 1:
+                self._offloaded["grads"] = None
+        torch.cuda.synchronize(self.device)
+        for nm in list(self._offloaded):
+            if nm in ("master", "exp_avg", "exp_avg_sq"):
+                setattr(self, nm, torch.empty(0, device=self.device))
+        torch.cuda.empty_cache()
+
+    def reload_states(self) -> None:
+        if not self.on_cuda:
+            return
+        for nm, host in list(self._offloaded.items()):
+            if host is not None:
+                setattr(self, nm, host.to(self.device, non_blocking=True))
+        self._offloaded.clear()
+        torch.cuda.synchronize(self.device)
+
+
+def _gloo_all_gather(dst: torch.Tensor, shard: torch.Tensor, world: int, group) -> None:
+    parts = [torch.empty_like(shard) for _ in range(world)]
+    dist.all_gather(parts, shard.contiguous(), group=group)
+    n = shard.numel()
+    for i, p in enumerate(parts):
+        dst[i * n:(i + 1) * n].copy_(p)
+
+
+_FUSED: Dict[str, Any] = {}
+
+
+def _fused_fns():
+    if not _FUSED:
+        c = ctypes
+        vp, i, ll, f = c.c_void_p, c.c_int, c.c_longlong, c.c_float
+        _FUSED["reduce"] = _lib.declare("apb_zero_reduce", [vp, vp, vp, i, i, i, ll, ll, f, vp, vp, vp])
+        _FUSED["adamw"] = _lib.declare("apb_zero_adamw",
+                                       [vp, vp, vp, i, i, i, ll, ll, vp, vp, vp, vp, vp, f, f, f, f, f, f, f, f, vp])
+        _FUSED["wait"] = _lib.declare("apb_epoch_wait", [vp, i, i, i, vp])
+        _FUSED["gather"] = _lib.declare("apb_gather_shards", [vp, vp, i, i, i, ll, vp, vp])
+    return _FUSED
