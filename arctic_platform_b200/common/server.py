@@ -1,0 +1,345 @@
+"""Job server core: what sits behind the HTTP routes, the Ray methods and the in-process client.
+
+A *job* is a set of engine workers of one kind -- ``training``, ``sampling`` or ``log_prob`` -- created by
+``initialize(job_config)``; every later call names a job id.  The method set and the return shapes follow
+the reference's servers (arctic_platform/common/ray_server.py:551-1209, common/http_server.py:140-970):
+``forward_backward -> {job_id, metrics, avg_loss}``, ``forward -> {job_id, batch, metrics, avg_loss}``,
+``step -> {job_id, metrics: {last_lr, grad_norm}, batch}``, ``generate -> {results: [...]}``,
+``weight_norm``, ``weight_sync``, ``sleep/wake`` for each engine kind, ``status`` / ``get_job_status``.
+
+Workers are reached through a tiny actor interface (``call(method, *args)``) with three implementations:
+in-process (this file), spawned local processes (``local_actors.py``) and Ray actors when Ray is
+importable.  Failure handling is host-side: a worker that raises during ``initialize`` makes the server
+destroy every worker it already created for that job (all-or-nothing, as
+arctic_platform/common/deepspeed_worker.py:89-104), heartbeats mark a job ``FAILED``.
+"""
+from __future__ import annotations
+
+import itertools
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional
+
+import torch
+
+from .utils.batch import merge_dict_shards, restore_batch_order, split_batch_for_ranks
+from .utils.metrics import finalize_fwd_bwd_metrics
+
+
+class JobError(RuntimeError):
+    """Carries an HTTP-like status code: 404 unknown job, 409 conflicting state, 400 bad request."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(message)
+        self.status = status
+
+
+class InProcessActor:
+    """Actor facade over an object living in this process."""
+
+    def __init__(self, obj):
+        self.obj = obj
+
+    def call(self, method: str, *args, **kwargs):
+        return getattr(self.obj, method)(*args, **kwargs)
+
+    def kill(self) -> None:
+        try:
+            self.obj.destroy()
+        except Exception:
+            pass
+
+
+@dataclass
+class Job:
+    job_id: int
+    job_type: str
+    config: Dict[str, Any]
+    workers: List[Any]
+    status: str = "RUNNING"
+    created: float = field(default_factory=time.time)
+    last_heartbeat: float = field(default_factory=time.time)
+    info: Dict[str, Any] = field(default_factory=dict)
+
+
+def default_worker_factory(job_config: Dict[str, Any], rank: int, world: int):
+    from ..engine.worker import EngineWorker
+    return InProcessActor(EngineWorker())
+
+
+class ArcticRLServerCore:
+    def __init__(self, worker_factory: Callable = default_worker_factory, training_gpus: int = 0,
+                 sampling_gpus: int = 0, log_prob_gpus: int = 0, colocate: bool = False,
+                 heartbeat_timeout: float = 0.0):
+        self.worker_factory = worker_factory
+        self.gpus = {"training": training_gpus, "sampling": sampling_gpus, "log_prob": log_prob_gpus}
+        self.colocate = colocate
+        self.jobs: Dict[int, Job] = {}
+        self._ids = itertools.count(1)
+        self._lock = threading.RLock()
+        self.heartbeat_timeout = heartbeat_timeout
+
+    # ------------------------------------------------------------------ lifecycle
+    def initialize(self, job_config: Dict[str, Any]) -> Dict[str, Any]:
+        job_type = job_config.get("job_type", "training")
+        if job_type not in ("training", "sampling", "log_prob"):
+            raise JobError(400, f"unknown job_type {job_type!r}")
+        n = int(job_config.get("num_devices") or self.gpus.get(job_type) or 1)
+        with self._lock:
+            for j in self.jobs.values():
+                if j.job_type == job_type and j.status == "RUNNING" and not job_config.get("allow_multiple"):
+                    raise JobError(409, f"a {job_type} job is already running (job {j.job_id})")
+            job_id = next(self._ids)
+        workers: List[Any] = []
+        try:
+            for rank in range(n):
+                w = self.worker_factory(job_config, rank, n)
+                workers.append(w)
+            for w in workers:
+                ok = w.call("initialize", job_config)
+                if ok is False:
+                    raise RuntimeError("worker.initialize returned False")
+        except Exception as exc:
+            for w in workers:          # all-or-nothing: no half-initialised job survives
+                try:
+                    w.kill()
+                except Exception:
+                    pass
+            raise JobError(500, f"{job_type} job failed to initialise: {exc}") from exc
+        ckpt = job_config.get("checkpoint_path")
+        info = {"job_id": job_id, "job_type": job_type, "model_name": job_config.get("model_name"),
+                "status": "RUNNING", "num_devices": n,
+                "checkpoint_path": f"{ckpt}/arctic_rl_job_{job_id}" if ckpt else None,
+                "cuda_ipc": bool(job_config.get("cuda_ipc")), "low_memory": bool(job_config.get("low_memory")),
+                "engine": "b200"}
+        with self._lock:
+            self.jobs[job_id] = Job(job_id, job_type, dict(job_config), workers, info=info)
+        return info
+
+    def destroy(self, job_id: Optional[int] = None) -> Dict[str, Any]:
+        with self._lock:
+            ids = [job_id] if job_id is not None else list(self.jobs)
+            jobs = [self.jobs.pop(i) for i in ids if i in self.jobs]
+        if job_id is not None and not jobs:
+            raise JobError(404, f"unknown job {job_id}")
+        for j in jobs:
+            for w in j.workers:
+                w.kill()
+            j.status = "DESTROYED"
+        return {"destroyed": [j.job_id for j in jobs]}
+
+    def _job(self, job_id: int, kinds=None) -> Job:
+        with self._lock:
+            j = self.jobs.get(int(job_id)) if job_id is not None else None
+        if j is None:
+            raise JobError(404, f"unknown job {job_id}")
+        if j.status != "RUNNING":
+            raise JobError(409, f"job {job_id} is {j.status}")
+        if kinds and j.job_type not in kinds:
+            raise JobError(400, f"job {job_id} is a {j.job_type} job, expected one of {kinds}")
+        if self.heartbeat_timeout and time.time() - j.last_heartbeat > self.heartbeat_timeout:
+            j.status = "FAILED"
+            raise JobError(409, f"job {job_id} missed its heartbeat deadline")
+        return j
+
+    def heartbeat(self, job_id: int) -> None:
+        with self._lock:
+            if job_id in self.jobs:
+                self.jobs[job_id].last_heartbeat = time.time()
+
+    def find_job(self, job_type: str) -> Optional[Job]:
+        with self._lock:
+            for j in self.jobs.values():
+                if j.job_type == job_type and j.status == "RUNNING":
+                    return j
+        return None
+
+    # ------------------------------------------------------------------ training / scoring
+    def _fan_out(self, job: Job, method: str, payload: Dict[str, Any]) -> List[Dict[str, Any]]:
+        batch = payload.get("batch")
+        meta = dict(payload.get("meta") or {})
+        processing = payload.get("processing")
+        shards, order = split_batch_for_ranks(batch, meta, len(job.workers))
+        results = [w.call(method, shard, meta, processing) for w, shard in zip(job.workers, shards)]
+        return results, order
+
+    def forward_backward(self, job_id: int, payload: Dict[str, Any]) -> Dict[str, Any]:
+        job = self._job(job_id, ("training",))
+        results, _ = self._fan_out(job, "forward_backward", payload)
+        metrics, avg_loss = finalize_fwd_bwd_metrics(results)
+        return {"job_id": job.job_id, "metrics": metrics, "avg_loss": avg_loss}
+
+    def forward(self, job_id: int, payload: Dict[str, Any]) -> Dict[str, Any]:
+        job = self._job(job_id, ("training", "log_prob"))
+        results, order = self._fan_out(job, "forward_no_grad", payload)
+        metrics, avg_loss = finalize_fwd_bwd_metrics(results)
+        merged = merge_dict_shards([r.get("batch") or {} for r in results])
+        if order is not None:
+            merged = restore_batch_order(merged, order)
+        return {"job_id": job.job_id, "batch": merged, "metrics": metrics, "avg_loss": avg_loss}
+
+    def step(self, job_id: int, learning_rate: Optional[float] = None) -> Dict[str, Any]:
+        job = self._job(job_id, ("training",))
+        outs = [w.call("step", learning_rate) for w in job.workers]
+        return {"job_id": job.job_id, "metrics": outs[0]["metrics"], "batch": {}}
+
+    def empty_training_cache(self, job_id: int) -> Dict[str, Any]:
+        job = self._job(job_id, ("training", "log_prob"))
+        for w in job.workers:
+            w.call("empty_cache")
+        return {"job_id": job.job_id, "status": "ok"}
+
+    # ------------------------------------------------------------------ checkpoints
+    def save(self, job_id: int, path: Optional[str] = None, step: Optional[int] = None, export_hf: bool = False,
+             save_total_limit: Optional[int] = None) -> Dict[str, Any]:
+        from .utils.checkpoint import prune_checkpoint_dirs, resolve_checkpoint_save_paths
+        job = self._job(job_id, ("training",))
+        root = path or job.info.get("checkpoint_path")
+        if not root:
+            raise JobError(400, "no checkpoint path configured")
+        save_dir, tag = resolve_checkpoint_save_paths(root, step)
+        outs = [w.call("save_checkpoint", save_dir, tag, export_hf) for w in job.workers]
+        if save_total_limit:
+            prune_checkpoint_dirs(save_dir, save_total_limit)
+        return {"job_id": job.job_id, "path": save_dir, "tag": tag, "files": outs[0].get("files", [])}
+
+    def load_checkpoint(self, job_id: int, path: Optional[str] = None, step: Optional[int] = None) -> Dict[str, Any]:
+        job = self._job(job_id, ("training",))
+        root = path or job.info.get("checkpoint_path")
+        if not root:
+            raise JobError(400, "no checkpoint path configured")
+        tag = f"checkpoint-{step}" if step is not None else None
+        steps = [w.call("load_checkpoint", root, tag) for w in job.workers]
+        return {"job_id": job.job_id, "global_steps": int(steps[0] or 0)}
+
+    # ------------------------------------------------------------------ rollout
+    def generate(self, job_id: int, prompts, sampling_params=None, routing_key=None, strict: bool = False):
+        job = self._job(job_id, ("sampling",))
+        n = len(job.workers)
+        if n == 1:
+            return {"job_id": job.job_id, "results": job.workers[0].call("generate", prompts, sampling_params)}
+        # replica data parallelism: contiguous slices keep the rollouts of one prompt on one replica
+        per = (len(prompts) + n - 1) // n
+        results: List[dict] = []
+        for i, w in enumerate(job.workers):
+            part = prompts[i * per:(i + 1) * per]
+            if part:
+                out = w.call("generate", part, sampling_params)
+                for o in out:
+                    o["prompt_index"] += i * per
+                results.extend(out)
+        return {"job_id": job.job_id, "results": results}
+
+    def log_probs(self, job_id: int, prompts, completions, top_k: int = 1) -> Dict[str, Any]:
+        job = self._job(job_id, ("sampling", "log_prob", "training"))
+        if job.job_type == "sampling":
+            raise JobError(400, "log-probs are served by a log_prob or training job in this build")
+        rows = []
+        P = max(len(p) for p in prompts)
+        R = max(len(c) for c in completions)
+        ids = torch.zeros((len(prompts), P + R), dtype=torch.int64)
+        mask = torch.zeros_like(ids)
+        for i, (p, c) in enumerate(zip(prompts, completions)):
+            ids[i, P - len(p):P] = torch.tensor(p)
+            mask[i, P - len(p):P] = 1
+            ids[i, P:P + len(c)] = torch.tensor(c)
+            mask[i, P:P + len(c)] = 1
+        out = self.forward(job.job_id, {"batch": {"input_ids": ids, "attention_mask": mask, "response_mask": mask[:, P:]},
+                                        "meta": {"response_length": R, "zorro_train_enable": True}})
+        lp = out["batch"]["log_probs"]
+        for i, c in enumerate(completions):
+            rows.append(lp[i, :len(c)].tolist())
+        return {"job_id": job.job_id, "log_probs": rows}
+
+    # ------------------------------------------------------------------ weights
+    def weight_sync(self, source_job_id: int, target_job_ids: List[int], cuda_ipc: Optional[bool] = None,
+                    low_memory: Optional[bool] = None) -> Dict[str, Any]:
+        src = self._job(source_job_id, ("training",))
+        t0 = time.perf_counter()
+        total = 0
+        for tid in target_job_ids:
+            dst = self._job(tid, ("sampling", "log_prob"))
+            for i, dw in enumerate(dst.workers):
+                sw = src.workers[i % len(src.workers)]
+                total += self._sync_pair(sw, dw)
+        return {"status": "ok", "num_tensors": total, "seconds": time.perf_counter() - t0}
+
+    def _sync_pair(self, sw, dw) -> int:
+        s_obj = getattr(sw, "obj", None)
+        d_obj = getattr(dw, "obj", None)
+        if s_obj is not None and d_obj is not None:
+            return s_obj.sync_weights_to(d_obj)
+        # different processes: stream named tensors through the actor interface
+        names = sw.call("get_parameter_names")
+        for name in names:
+            dw.call("load_named_weight", name, sw.call("get_named_weight", name))
+        return len(names)
+
+    def weight_norm(self, training_job_id: Optional[int] = None, sampling_job_id: Optional[int] = None) -> Dict[str, Any]:
+        out: Dict[str, Any] = {}
+        if training_job_id is not None:
+            r = self._job(training_job_id).workers[0].call("weight_norm")
+            out["training_norm"], out["training_num_params"] = r["norm"], r["num_params"]
+        if sampling_job_id is not None:
+            r = self._job(sampling_job_id).workers[0].call("weight_norm")
+            out["sampling_norm"], out["sampling_num_params"] = r["norm"], r["num_params"]
+        return out
+
+    # ------------------------------------------------------------------ sleep / wake
+    def sleep_inference(self, job_id: int, level: int = 1) -> Dict[str, Any]:
+        job = self._job(job_id, ("sampling",))
+        for w in job.workers:
+            w.call("sleep_inference", level)
+        return {"job_id": job.job_id, "status": "sleeping"}
+
+    def wake_inference(self, job_id: int, tags=None) -> Dict[str, Any]:
+        job = self._job(job_id, ("sampling",))
+        for w in job.workers:
+            w.call("wake_inference", tags)
+        return {"job_id": job.job_id, "status": "awake"}
+
+    def reset_prefix_cache(self, job_id: int) -> Dict[str, Any]:
+        job = self._job(job_id, ("sampling",))
+        for w in job.workers:
+            w.call("reset_prefix_cache")
+        return {"job_id": job.job_id, "status": "ok"}
+
+    def sleep_training(self, job_id: int, mode: str = "all") -> Dict[str, Any]:
+        job = self._job(job_id, ("training", "log_prob"))
+        method = {"all": "offload_to_cpu", "non_lp": "offload_non_lp_states", "lp_params": "offload_lp_params"}.get(mode)
+        if method is None:
+            raise JobError(400, f"unknown sleep mode {mode!r}")
+        for w in job.workers:
+            w.call(method)
+        return {"job_id": job.job_id, "status": "sleeping", "mode": mode}
+
+    def wake_training(self, job_id: int) -> Dict[str, Any]:
+        job = self._job(job_id, ("training", "log_prob"))
+        for w in job.workers:
+            w.call("backload_to_gpu")
+        return {"job_id": job.job_id, "status": "awake"}
+
+    def operation(self, operation_type: str, sub_job_id: int, payload: Optional[dict] = None) -> Dict[str, Any]:
+        payload = payload or {}
+        if operation_type == "weight-sync":
+            return self.weight_sync(payload.get("source_sub_job_id", sub_job_id), payload.get("target_sub_job_ids", []))
+        if operation_type == "reset-prefix-cache":
+            return self.reset_prefix_cache(sub_job_id)
+        if operation_type == "sleep-inference":
+            return self.sleep_inference(sub_job_id, payload.get("level", 1))
+        if operation_type == "wake-inference":
+            return self.wake_inference(sub_job_id, payload.get("tags"))
+        raise JobError(400, f"unknown operation {operation_type!r}")
+
+    # ------------------------------------------------------------------ status
+    def status(self) -> Dict[str, Any]:
+        with self._lock:
+            return {"jobs": [dict(j.info, status=j.status) for j in self.jobs.values()]}
+
+    def get_job_status(self, job_id: int) -> Dict[str, Any]:
+        with self._lock:
+            j = self.jobs.get(int(job_id))
+        if j is None:
+            raise JobError(404, f"unknown job {job_id}")
+        return dict(j.info, status=j.status)

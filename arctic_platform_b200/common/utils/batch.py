@@ -1,0 +1,121 @@
+"""Splitting a global batch over data-parallel workers and merging their answers.
+
+``split_batch_for_ranks`` cuts every tensor along dim 0 (``torch.chunk`` semantics), injects the global
+quantities each shard needs to normalise its loss (``dp_size``, ``batch_num_tokens``,
+``global_batch_size``), rebuilds ``position_ids`` when the client dropped them to save bandwidth and,
+when ``meta['load_balancer']`` is set, first reorders the samples so every rank gets whole prompt groups
+of similar cost (ZoRRo load balancer).  The answers are merged in rank order and un-permuted.
+Contract of arctic_platform/common/utils/batch.py:39-492 in the reference.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+
+def tensorize(obj: Any) -> Any:
+    """Lists of numbers -> tensors (recursively through dicts), everything else untouched."""
+    if isinstance(obj, dict):
+        return {k: tensorize(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)) and obj and all(isinstance(x, (int, float, list, tuple)) for x in obj):
+        try:
+            return torch.tensor(obj)
+        except (ValueError, TypeError):
+            return obj
+    return obj
+
+
+def detensorize(obj: Any) -> Any:
+    """Tensors -> Python numbers / lists so a metrics dict is JSON-serialisable."""
+    if torch.is_tensor(obj):
+        return obj.item() if obj.numel() == 1 else obj.tolist()
+    if isinstance(obj, dict):
+        return {k: detensorize(v) for k, v in obj.items()}
+    if isinstance(obj, (list, tuple)):
+        return [detensorize(v) for v in obj]
+    return obj
+
+
+def reconstruct_position_ids_(batch: Dict[str, torch.Tensor]) -> None:
+    """``position_ids = cumsum(attention_mask) - 1`` clipped at 0, in place, when missing."""
+    if "position_ids" in batch or "attention_mask" not in batch:
+        return
+    m = batch["attention_mask"].long()
+    batch["position_ids"] = (m.cumsum(-1) - 1).clamp_min(0) * m
+
+
+def split_dict(batch: Dict[str, Any], n: int) -> List[Dict[str, Any]]:
+    outs: List[Dict[str, Any]] = [dict() for _ in range(n)]
+    for k, v in batch.items():
+        if torch.is_tensor(v) and v.dim() > 0:
+            parts = list(torch.chunk(v, n, dim=0))
+            while len(parts) < n:
+                parts.append(v[:0])
+            for o, p in zip(outs, parts):
+                o[k] = p
+        else:
+            for o in outs:
+                o[k] = v
+    return outs
+
+
+def merge_dict_shards(shards: Sequence[Dict[str, Any]]) -> Dict[str, Any]:
+    out: Dict[str, Any] = {}
+    keys = []
+    for s in shards:
+        for k in s:
+            if k not in keys:
+                keys.append(k)
+    for k in keys:
+        vals = [s[k] for s in shards if k in s]
+        if all(torch.is_tensor(v) for v in vals):
+            if vals[0].dim() == 0:
+                out[k] = torch.stack(vals)
+            else:
+                width = max(v.shape[1] for v in vals) if vals[0].dim() > 1 else None
+                if width is not None and any(v.shape[1] != width for v in vals):
+                    vals = [torch.nn.functional.pad(v, (0, width - v.shape[1])) for v in vals]
+                out[k] = torch.cat(vals, 0)
+        elif all(isinstance(v, list) for v in vals):
+            out[k] = [x for v in vals for x in v]
+        else:
+            out[k] = vals[0]
+    return out
+
+
+def restore_batch_order(batch: Dict[str, Any], order: torch.Tensor) -> Dict[str, Any]:
+    """Inverse of the permutation applied before splitting: row ``i`` of the result is the sample that was
+    at position ``i`` of the client's batch."""
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(order.numel())
+    out = {}
+    for k, v in batch.items():
+        out[k] = v[inv] if torch.is_tensor(v) and v.dim() > 0 and v.shape[0] == order.numel() else v
+    return out
+
+
+def shard_token_stats(shards: Sequence[Dict[str, Any]]) -> List[int]:
+    return [int(s["attention_mask"].sum()) if "attention_mask" in s else 0 for s in shards]
+
+
+def split_batch_for_ranks(batch, meta: Dict[str, Any], n: int) -> Tuple[List[Any], Optional[torch.Tensor]]:
+    """Returns ``(shards, order)``; ``order`` is the permutation applied to the samples (or None).
+    ``meta`` is updated in place with ``dp_size`` and the global normalisers."""
+    meta.setdefault("dp_size", n)
+    if isinstance(batch, (list, tuple)):
+        # client-side micro-batches: each micro-batch is split on its own, rank r gets the list of its parts
+        per_mb = [split_batch_for_ranks(mb, dict(meta), n)[0] for mb in batch]
+        return [[mb[r] for mb in per_mb] for r in range(n)], None
+    batch = dict(batch)
+    if meta.get("drop_position_ids"):
+        reconstruct_position_ids_(batch)
+    if "response_mask" in batch and meta.get("batch_num_tokens") is None:
+        meta["batch_num_tokens"] = float(batch["response_mask"].sum())
+    if "input_ids" in batch and meta.get("global_batch_size") is None:
+        meta["global_batch_size"] = float(batch["input_ids"].shape[0])
+    order = None
+    if n > 1 and meta.get("load_balancer") and "input_ids" in batch:
+        from ...rl.zorro_train.seqlen_balancing import reorg_global_batch
+        batch, order = reorg_global_batch(batch, meta, n)
+    return split_dict(batch, n), order

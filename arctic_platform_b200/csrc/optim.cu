@@ -280,3 +280,136 @@ int apb_sumsq_f32(const float* x, long long n, double* out, cudaStream_t s) {
   return static_cast<int>(cudaGetLastError());
 }
 }
+
+// ---------------------------------------------------------------------------
+// Trainer -> sampler weight synchronisation
+// ---------------------------------------------------------------------------
+namespace apb {
+
+struct SyncUnits {
+  // up to 160 units (embedding, one per block, final norm); offsets/lengths in elements
+  long long offset[160];
+  long long length[160];
+  int n;
+};
+
+// dst[e] = source element e of the flat parameter space, read from the rank that owns it.
+//   sharded = 0: every rank holds the whole flat buffer (src.p[rank] is read);
+//   sharded = 1: rank r holds, for every unit u, elements [r*len_u/W, (r+1)*len_u/W) packed back to back
+//                (the ZeRO shard layout); the owner is computed per element and read through its peer mapping.
+// One pass, 16 bytes per thread per iteration; this is the whole "gather ZeRO shards + reshard to the
+// sampler layout" step when both sides use the same fused layout.
+__global__ void __launch_bounds__(256)
+sync_weights_flat_kernel(PeerPtrs src, PeerPtrs flags, int rank, int world, int epoch, int sharded, SyncUnits units,
+                         __nv_bfloat16* __restrict__ dst, long long total, int* status) {
+  if (!epoch_barrier(flags, rank, world, epoch, status)) return;
+  const long long n8 = total >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long e = i * 8;
+    const __nv_bfloat16* sp;
+    if (!sharded) {
+      sp = static_cast<const __nv_bfloat16*>(src.p[rank]) + e;
+    } else {
+      int u = 0;
+      long long shard_base = 0;  // start of unit u inside a rank's packed shard buffer
+      while (u + 1 < units.n && e >= units.offset[u + 1]) {
+        shard_base += units.length[u] / world;
+        ++u;
+      }
+      const long long per = units.length[u] / world;
+      const long long in_unit = e - units.offset[u];
+      const int owner = static_cast<int>(in_unit / per);
+      sp = static_cast<const __nv_bfloat16*>(src.p[owner]) + shard_base + (in_unit - owner * per);
+    }
+    *reinterpret_cast<uint4*>(dst + e) = *reinterpret_cast<const uint4*>(sp);
+  }
+}
+
+// Block-scaled fp8 (e4m3) requantisation of a [rows, cols] bf16 weight with one fp32 scale per
+// 128 x 128 block: scale = amax / 448, q = w / scale.  One CTA per block.
+__global__ void __launch_bounds__(256)
+quant_fp8_block128_kernel(const __nv_bfloat16* __restrict__ w, long long ldw, int rows, int cols,
+                          uint8_t* __restrict__ q, long long ldq, float* __restrict__ scales, int scale_ld) {
+  const int bx = blockIdx.x, by = blockIdx.y;
+  const int r0 = by * 128, c0 = bx * 128;
+  __shared__ float red[8];
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < 128 * 16; i += 256) {
+    const int r = r0 + i / 16, c = c0 + (i % 16) * 8;
+    if (r < rows && c < cols) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(w + r * ldw + c);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h2[k]);
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) amax = fmaxf(amax, red[k]);
+  const float scale = amax > 0.f ? amax / 448.f : 1.f;
+  const float inv = 1.f / scale;
+  if (threadIdx.x == 0) scales[by * scale_ld + bx] = scale;
+  for (int i = threadIdx.x; i < 128 * 16; i += 256) {
+    const int r = r0 + i / 16, c = c0 + (i % 16) * 8;
+    if (r < rows && c < cols) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(w + r * ldw + c);
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      uint32_t out[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const float2 a = __bfloat1622float2(h2[2 * k]);
+        const float2 b = __bfloat1622float2(h2[2 * k + 1]);
+        uint16_t lo, hi;
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(a.y * inv), "f"(a.x * inv));
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(b.y * inv), "f"(b.x * inv));
+        out[k] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+      }
+      *reinterpret_cast<uint2*>(q + r * ldq + c) = make_uint2(out[0], out[1]);
+    }
+  }
+}
+
+}  // namespace apb
+
+extern "C" {
+
+// src_ptrs[world]: per-rank source base pointers (full flat buffer if sharded == 0, packed ZeRO shards if 1).
+// unit_offset / unit_length: n_units entries describing the flat parameter space (elements).
+int apb_sync_weights_flat(void* const* src_ptrs, void* const* flag_ptrs, int rank, int world, int epoch, int sharded,
+                          const long long* unit_offset, const long long* unit_length, int n_units, void* dst,
+                          long long total, cudaStream_t s) {
+  using namespace apb;
+  if (world > kMaxRanks || n_units > 160 || (total % 8)) return kBadArgument;
+  SyncUnits u;
+  u.n = n_units;
+  for (int i = 0; i < n_units; ++i) {
+    u.offset[i] = unit_offset[i];
+    u.length[i] = unit_length[i];
+    if (sharded && (unit_length[i] % (8LL * world))) return kBadArgument;
+  }
+  sync_weights_flat_kernel<<<grid_for(total / 8), 256, 0, s>>>(to_peers(src_ptrs, world), to_peers(flag_ptrs, world),
+                                                              rank, world, epoch, sharded, u,
+                                                              static_cast<__nv_bfloat16*>(dst), total,
+                                                              status_device_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+// w [rows, cols] bf16 -> q [rows, cols] e4m3 + scales [ceil(rows/128), ceil(cols/128)] fp32.  cols % 8 == 0.
+int apb_quant_fp8_block128(const void* w, long long ldw, int rows, int cols, void* q, long long ldq, float* scales,
+                           cudaStream_t s) {
+  using namespace apb;
+  if (rows <= 0 || cols <= 0) return 0;
+  if ((cols % 8) || (ldw % 8) || (ldq % 8)) return kBadArgument;
+  const dim3 grid((cols + 127) / 128, (rows + 127) / 128);
+  quant_fp8_block128_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(w), ldw, rows, cols,
+                                                 static_cast<uint8_t*>(q), ldq, scales, (cols + 127) / 128);
+  return static_cast<int>(cudaGetLastError());
+}
+}

@@ -147,6 +147,7 @@ class SamplerEngine:
         self._alloc_cache()
         self.pages = PageAllocator(self.num_pages)
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self._graph_launches: Dict[int, int] = {}
         self._step_count = 0
         self._asleep = False
         self._alloc_state()
@@ -332,11 +333,15 @@ class SamplerEngine:
             n -= 1
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
+            before = _lib.launch_count()
             with torch.cuda.graph(g):
                 self._decode_step(B)
+            self._graph_launches[B] = _lib.launch_count() - before
+            _lib.add_launches(-self._graph_launches[B])       # capture records, it does not launch
             self._graphs[B] = g
         for _ in range(n):
             g.replay()
+        _lib.add_launches(n * self._graph_launches[B])
 
     # ------------------------------------------------------------------ public API
     @torch.no_grad()

@@ -1,0 +1,232 @@
+"""Per-GPU engine worker: the object a server drives for one rank of a job.
+
+It plays the role of the reference's ``DeepSpeedWorker`` Ray actor
+(arctic_platform/common/deepspeed_worker.py:107-1135) for ``training`` and ``log_prob`` jobs and of an
+ArcticInference replica for ``sampling`` jobs, with the same method names and return shapes
+(``{"metrics", "avg_loss", "batch"}`` for forward passes, ``{"metrics": {"last_lr", "grad_norm"}, "batch": {}}``
+for ``step``).  One process owns one GPU; data-parallel ranks are peers of one ``torch.distributed`` group and
+meet inside ``TrainEngine.step`` (fused NVLink kernels) -- the server only fans requests out.
+"""
+from __future__ import annotations
+
+import time
+from typing import Any, Dict, Iterable, List, Optional
+
+import torch
+
+from ..common.utils.metrics import combine_metric_microbatches
+from ..models.config import DecoderConfig, resolve_config
+from ..models.decoder import DecoderLM
+from ..rl.processors.pipeline import run_pipeline
+from .trainer import EngineConfig, TrainEngine
+
+
+def split_microbatches(batch: Dict[str, torch.Tensor], n: int) -> List[Dict[str, torch.Tensor]]:
+    """Splits every tensor of the batch along dim 0 into ``n`` chunks (``torch.chunk`` semantics)."""
+    if n <= 1:
+        return [batch]
+    outs: List[Dict[str, Any]] = [dict() for _ in range(n)]
+    for k, v in batch.items():
+        if torch.is_tensor(v) and v.dim() > 0:
+            parts = torch.chunk(v, n, dim=0)
+            if len(parts) != n:
+                raise ValueError(f"cannot split {k} with {v.shape[0]} rows into {n} micro-batches")
+            for o, p in zip(outs, parts):
+                o[k] = p
+        else:
+            for o in outs:
+                o[k] = v
+    return outs
+
+
+class EngineWorker:
+    def __init__(self, device=None):
+        self.device = torch.device(device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
+        self.job_type: Optional[str] = None
+        self.engine: Optional[TrainEngine] = None
+        self.sampler = None
+        self.model_cfg: Optional[DecoderConfig] = None
+        self.job_config: Dict[str, Any] = {}
+
+    # ------------------------------------------------------------------ lifecycle
+    def initialize(self, job_config: Dict[str, Any], model: Optional[DecoderLM] = None) -> bool:
+        """``job_config`` has the fields of the server-side ``JobConfig`` (model_name, job_type, ds_config,
+        training_config, log_prob_config, ds_worker_config, vllm_config, seed, ...)."""
+        self.job_config = dict(job_config)
+        self.job_type = job_config.get("job_type", "training")
+        seed = job_config.get("seed")
+        seed = 42 if seed is None else int(seed)
+        if job_config.get("full_determinism"):
+            from ..utils.debug import enable_full_determinism
+            enable_full_determinism(seed)
+        self.model_cfg = model.cfg if model is not None else resolve_config(job_config["model_name"])
+        dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        if self.job_type == "sampling":
+            from .sampler import SamplerEngine
+            vc = dict(job_config.get("vllm_config") or {})
+            m = model if model is not None else self._load_model(job_config, dtype, seed)
+            self.sampler = SamplerEngine(
+                self.model_cfg, self.device, model=m,
+                kv_cache_tokens=int(vc.get("kv_cache_tokens", 1 << 20)), max_batch=int(vc.get("max_num_seqs", 256)),
+                max_seq_len=int(vc.get("max_model_len", 8192)),
+                cascade=bool((job_config.get("arctic_inference_config") or {}).get("zorro_inference", {}).get("enable", True)),
+                seed=seed, eos_token_id=vc.get("eos_token_id"))
+            return True
+        m = model if model is not None else self._load_model(job_config, dtype, seed)
+        if self.job_type == "log_prob":
+            ecfg = EngineConfig.from_ds_config(job_config.get("log_prob_config") or job_config.get("ds_config"))
+            self.engine = TrainEngine(m, ecfg, forward_only=True)
+        else:
+            ecfg = EngineConfig.from_ds_config(job_config.get("ds_config"), job_config.get("training_config"))
+            wc = job_config.get("ds_worker_config") or {}
+            ecfg.gradient_checkpointing = bool(wc.get("gradient_checkpointing", False))
+            self.engine = TrainEngine(m, ecfg)
+        return True
+
+    def _load_model(self, job_config, dtype, seed) -> DecoderLM:
+        from pathlib import Path
+        from ..models.hf_io import load_hf_checkpoint
+        m = DecoderLM(self.model_cfg, self.device, dtype)
+        path = Path(str(job_config["model_name"]))
+        if path.is_dir() and any(path.glob("*.safetensors")):
+            load_hf_checkpoint(m, path)
+        else:
+            m.init_weights(seed=seed)     # no checkpoint on disk: deterministic random initialisation
+        return m
+
+    def destroy(self) -> None:
+        self.engine = None
+        self.sampler = None
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    # ------------------------------------------------------------------ forward / backward / step
+    def _forward_maybe_backward(self, batch, meta, processing, backward: bool) -> Dict[str, Any]:
+        if self.engine is None:
+            raise RuntimeError("worker has no training/log-prob engine")
+        t0 = time.perf_counter()
+        if isinstance(batch, (list, tuple)):
+            mbs = list(batch)                               # client-side gradient-accumulation split
+        else:
+            n_mb = int((meta or {}).get("num_micro_batches", 1) or 1)
+            mbs = split_microbatches(batch, n_mb)
+        per_mb, outs = [], []
+        for mb in mbs:
+            r = run_pipeline(self.engine, mb, meta, processing, self.device, backward=backward, return_tensors=True)
+            per_mb.append(r["metrics"])
+            outs.append(r)
+        metrics = combine_metric_microbatches(per_mb)
+        result: Dict[str, Any] = {"metrics": metrics, "avg_loss": sum(o["avg_loss"] for o in outs)}
+        if not backward:
+            keys = outs[0].get("batch", {}).keys()
+            result["batch"] = {k: torch.cat([o["batch"][k] for o in outs], 0) for k in keys}
+        metrics["_profile_ms"] = {"fwd_bwd" if backward else "fwd": (time.perf_counter() - t0) * 1e3}
+        return result
+
+    def forward_backward(self, batch, meta=None, processing=None) -> Dict[str, Any]:
+        return self._forward_maybe_backward(batch, meta, processing, backward=True)
+
+    def forward_no_grad(self, batch, meta=None, processing=None) -> Dict[str, Any]:
+        processing = {"post": ["compute_entropy_and_logprobs"], "loss_fn": None, **(processing or {})}
+        return self._forward_maybe_backward(batch, meta, processing, backward=False)
+
+    def step(self, learning_rate: Optional[float] = None) -> Dict[str, Any]:
+        if learning_rate is not None:
+            self.engine.cfg.lr = float(learning_rate)
+        out = self.engine.step()
+        return {"metrics": {"last_lr": out["last_lr"], "grad_norm": float(out["grad_norm"])}, "batch": {}}
+
+    def compute_log_probs(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """``log softmax(logits)[next token]`` for every position of unpadded ``input_ids [B, S]``:
+        a ``[B, S-1]`` CPU tensor (arctic_platform/common/deepspeed_worker.py:638-652 in the reference)."""
+        batch = {"input_ids": input_ids, "attention_mask": torch.ones_like(input_ids)}
+        r = run_pipeline(self.engine, batch, {"plain_packing": True}, {"loss_fn": None, "post": []}, self.device,
+                         backward=False)
+        return r["batch"]["log_probs"][:, 1:]
+
+    # ------------------------------------------------------------------ rollout
+    def generate(self, prompts, sampling_params=None) -> List[dict]:
+        if self.sampler is None:
+            raise RuntimeError("worker has no sampling engine")
+        return self.sampler.generate(prompts, sampling_params)
+
+    # ------------------------------------------------------------------ weights
+    def iter_weights(self):
+        return self.engine.iter_hf_tensors()
+
+    def get_parameter_names(self) -> List[str]:
+        from ..models.hf_io import hf_param_names
+        return hf_param_names(self.model_cfg)
+
+    def weight_norm(self) -> Dict[str, float]:
+        return self.sampler.weight_norm() if self.sampler is not None else self.engine.weight_norm()
+
+    def get_named_weight(self, name: str) -> torch.Tensor:
+        for n, t in self.engine.iter_hf_tensors():
+            if n == name:
+                return t.detach().to("cpu")
+        raise KeyError(name)
+
+    def load_named_weight(self, name: str, tensor: torch.Tensor) -> None:
+        from ..models.hf_io import load_hf_tensor
+        model = self.sampler.model if self.sampler is not None else self.engine.model
+        load_hf_tensor(model, name, tensor)
+
+    def sync_weights_to(self, dst: "EngineWorker") -> int:
+        """Pushes this (training) worker's parameters into ``dst`` (a sampling or log-prob worker of the
+        same process).  Same device and layout: one flat-gather kernel; otherwise tensor by tensor under
+        their Hugging Face names.  Returns the number of tensors covered."""
+        from ..models.hf_io import hf_param_names
+        from ..parallel import weight_sync
+        dst_model = dst.sampler.model if dst.sampler is not None else dst.engine.model
+        n_names = len(hf_param_names(self.model_cfg))
+        if self.engine.on_cuda and next(dst_model.parameters()).device == self.device:
+            flat = getattr(dst_model, "_flat_params", None)
+            if flat is None or flat.numel() != self.engine.total:
+                flat = weight_sync.flatten_like(dst_model, self.engine)
+            weight_sync.sync_flat(self.engine, flat)
+            return n_names
+        return weight_sync.sync_state_dict(((n, t.detach()) for n, t in self.engine.iter_hf_tensors()), dst_model)
+
+    def sleep_inference(self, level: int = 1) -> None:
+        if self.sampler is not None:
+            self.sampler.sleep(level)
+
+    def wake_inference(self, tags=None) -> None:
+        if self.sampler is not None:
+            self.sampler.wake(tags)
+
+    def reset_prefix_cache(self) -> None:
+        if self.sampler is not None:
+            self.sampler.reset_prefix_cache()
+
+    # ------------------------------------------------------------------ sleep / wake
+    def offload_to_cpu(self) -> None:
+        if self.engine is not None:
+            self.engine.offload_states(("optimizer", "grads"))
+
+    def offload_non_lp_states(self) -> None:
+        if self.engine is not None:
+            self.engine.offload_states(("optimizer",))
+
+    def offload_lp_params(self) -> None:
+        return None
+
+    def backload_to_gpu(self) -> None:
+        if self.engine is not None:
+            self.engine.reload_states()
+
+    def empty_cache(self) -> None:
+        if self.device.type == "cuda":
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+
+    # ------------------------------------------------------------------ checkpoints
+    def save_checkpoint(self, path: str, tag: Optional[str] = None, export_hf: bool = False) -> Dict[str, Any]:
+        from .checkpoint import save_checkpoint
+        return save_checkpoint(self.engine, path, tag, export_hf=export_hf)
+
+    def load_checkpoint(self, path: str, tag: Optional[str] = None) -> int:
+        from .checkpoint import load_checkpoint
+        return load_checkpoint(self.engine, path, tag)

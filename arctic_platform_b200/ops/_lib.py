@@ -85,9 +85,26 @@ def ptr(t) -> ctypes.c_void_p:
     return ctypes.c_void_p(t.data_ptr())
 
 
+_LAUNCHES = 0
+
+
 def check(code: int, what: str) -> None:
+    """Raises on a non-zero launch code; also counts the call as one launch of this library's kernels."""
+    global _LAUNCHES
     if code != 0:
         raise KernelError(f"{what} failed with code {code}")
+    _LAUNCHES += 1
+
+
+def launch_count() -> int:
+    """Kernel entry points of this library called so far in this process (graph replays add the number
+    recorded while the graph was captured)."""
+    return _LAUNCHES
+
+
+def add_launches(n: int) -> None:
+    global _LAUNCHES
+    _LAUNCHES += int(n)
 
 
 def status_read() -> int:

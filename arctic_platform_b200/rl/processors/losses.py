@@ -1,0 +1,199 @@
+"""Registered loss functions.
+
+Each loss has the signature ``fn(model_outputs, batch, meta, config, device) -> (loss, metrics)``:
+``model_outputs`` carries per-token ``logprobs`` (and ``entropy``) on the packed axis together with the
+:class:`PackedBatch` that maps tokens back to the padded ``[B, R]`` response grid; ``batch`` holds the
+client's padded tensors.  Metrics are emitted as ``{name}.sum`` / ``{name}.tokens`` pairs so that the
+server can form global token means (see ``common/utils/metrics.py``).
+
+* ``verl_grpo`` -- verl-shaped PPO/GRPO actor loss (dual-clip, optional entropy bonus and KL-to-reference
+  penalty), the loss the reference runs in production
+  (arctic_platform/integrations/verl/grpo_loss.py:415-522).
+* ``grpo``      -- decoupled-PPO variant with a proximal policy, behaviour-importance cap and the same
+  aggregation modes (arctic_platform/rl/processors/grpo.py:195-394).
+* ``sft`` / ``sft_ce`` -- next-token cross entropy with global-token normalisation
+  (arctic_platform/sft/processor.py:95-292).
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Tuple
+
+import torch
+
+from ...common.registry import register_loss_fn
+from .functional import agg_loss, kl_penalty, masked_sum, ppo_clip_token_loss
+
+
+def _global_info(meta: dict) -> dict:
+    return {"dp_size": int(meta.get("dp_size", 1) or 1), "batch_num_tokens": meta.get("batch_num_tokens"),
+            "global_batch_size": meta.get("global_batch_size")}
+
+
+def _token_views(model_outputs: dict, batch: dict, device):
+    """Per-token views (packed order) of the padded client tensors."""
+    packed = model_outputs["packed"]
+    R = packed.response_length
+
+    def take(name, default=None):
+        t = batch.get(name)
+        if t is None:
+            return default
+        return packed.gather_from_grid(t.to(device)).float()
+
+    mask_grid = batch.get("response_mask")
+    if mask_grid is None:
+        mask = torch.ones_like(model_outputs["logprobs"], dtype=torch.bool)
+    else:
+        mask = packed.gather_from_grid(mask_grid.to(device)).bool()
+    seq_ids = torch.div(packed.out_index.to(device), R, rounding_mode="floor")
+    return packed, take, mask, seq_ids
+
+
+@register_loss_fn("verl_grpo")
+def verl_grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, device) -> Tuple[torch.Tensor, dict]:
+    actor = meta.get("actor_config", {}) or {}
+    agg_mode = actor.get("loss_agg_mode", "token-mean")
+    entropy_coeff = float(actor.get("entropy_coeff", 0.0) or 0.0)
+    packed, take, mask, seq_ids = _token_views(model_outputs, batch, device)
+    info = _global_info(meta)
+    info.update(seq_ids=seq_ids, num_seqs=packed.batch_size)
+    lp = model_outputs["logprobs"].float()
+    old = take("old_log_probs")
+    adv = take("advantages")
+    if old is None or adv is None:
+        raise KeyError("verl_grpo needs batch['old_log_probs'] and batch['advantages']")
+    # the clip constants are fixed in the reference implementation (0.2 / 0.2 / 3.0) whatever the config says
+    tok_loss, neg_kl, clipped, lower = ppo_clip_token_loss(lp, old, adv, 0.2, 0.2, 3.0)
+    is_w = meta.get("rollout_is_weights")
+    if is_w is not None:
+        tok_loss = tok_loss * packed.gather_from_grid(is_w.to(device)).float()
+    loss = agg_loss(tok_loss, mask, agg_mode, **info)
+    mf = mask.float()
+    sums = torch.stack([mf.sum(), (clipped.float() * mf).sum(), (-neg_kl * mf).sum(), (lower.float() * mf).sum(),
+                        (tok_loss * mf).sum()]).detach()
+    extra = []
+    entropy = model_outputs.get("entropy")
+    if entropy is not None:
+        entropy = entropy.float()
+        loss = loss - entropy_coeff * agg_loss(entropy, mask, agg_mode, **info)
+        extra.append((entropy * mf).sum().detach())
+    use_kl = bool(actor.get("use_kl_loss", False))
+    if use_kl:
+        ref = take("ref_log_prob")
+        if ref is None:
+            raise KeyError("use_kl_loss needs batch['ref_log_prob']")
+        kld = kl_penalty(lp, ref, actor.get("kl_loss_type", "low_var_kl"))
+        kl_coef = float(actor.get("kl_loss_coef", 0.001))
+        loss = loss + kl_coef * agg_loss(kld, mask, agg_mode, **info)
+        extra.append((kld * mf).sum().detach())
+    vals = torch.cat([sums, torch.stack(extra)]) if extra else sums
+    vals = vals.cpu().tolist()                      # the one device->host sync of the loss
+    ntok, clip_s, kl_s, lower_s, pg_s = vals[:5]
+    metrics: Dict[str, Any] = {}
+    for name, v in (("actor/pg_clipfrac", clip_s), ("actor/ppo_kl", kl_s), ("actor/pg_clipfrac_lower", lower_s),
+                    ("actor/pg_loss", pg_s)):
+        metrics[name + ".sum"] = v
+        metrics[name + ".tokens"] = ntok
+    loss_sum = pg_s
+    k = 5
+    if entropy is not None:
+        metrics["actor/entropy_loss.sum"] = vals[k]
+        metrics["actor/entropy_loss.tokens"] = ntok
+        loss_sum -= entropy_coeff * vals[k]
+        k += 1
+    if use_kl:
+        metrics["kl_loss.sum"] = vals[k]
+        metrics["kl_loss.tokens"] = ntok
+        metrics["kl_coef"] = kl_coef
+        loss_sum += kl_coef * vals[k]
+    metrics["loss.sum"] = loss_sum
+    metrics["loss.tokens"] = ntok
+    return loss, metrics
+
+
+@register_loss_fn("grpo")
+def grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, device) -> Tuple[torch.Tensor, dict]:
+    """Decoupled PPO: the clip is taken against a proximal policy (``prox_log_probs``, defaulting to the
+    behaviour policy) and the behaviour mismatch enters as a capped importance weight."""
+    cfg = {**(meta.get("actor_config") or {}), **(config or {})}
+    eps = float(cfg.get("eps_clip", cfg.get("clip_ratio", 0.2)))
+    eps_hi = float(cfg.get("eps_clip_higher", eps) or eps)
+    c_clip = cfg.get("c_clip")
+    cap = cfg.get("behav_imp_weight_cap")
+    agg_mode = cfg.get("loss_agg_mode", "token-mean")
+    packed, take, mask, seq_ids = _token_views(model_outputs, batch, device)
+    info = _global_info(meta)
+    info.update(seq_ids=seq_ids, num_seqs=packed.batch_size)
+    lp = model_outputs["logprobs"].float()
+    old = take("old_log_probs")
+    adv = take("advantages")
+    prox = take("prox_log_probs", old)
+    ratio = torch.exp(torch.clamp(lp - prox, -20, 20))
+    clipped_ratio = torch.clamp(ratio, 1 - eps, 1 + eps_hi)
+    l1, l2 = -adv * ratio, -adv * clipped_ratio
+    tok = torch.maximum(l1, l2)
+    clip_mask = l2 > l1
+    if c_clip is not None:
+        l3 = -adv * float(c_clip)
+        tok = torch.where(adv < 0, torch.minimum(l3, tok), tok)
+    behav_w = torch.exp(torch.clamp(prox - old, -20, 20))
+    if cap is not None:
+        keep = behav_w <= float(cap)
+        mask = mask & keep
+    tok = tok * behav_w.detach()
+    loss = agg_loss(tok, mask, agg_mode, **info)
+    ent_coef = float(cfg.get("entropy_coeff", 0.0) or 0.0)
+    entropy = model_outputs.get("entropy")
+    if entropy is not None and ent_coef:
+        loss = loss - ent_coef * agg_loss(entropy.float(), mask, agg_mode, **info)
+    kl_coef = float(cfg.get("kl_ctl", cfg.get("kl_loss_coef", 0.0)) or 0.0)
+    ref = take("ref_log_prob")
+    if kl_coef and ref is not None:
+        loss = loss + kl_coef * agg_loss(kl_penalty(lp, ref, cfg.get("kl_loss_type", "k3")), mask, agg_mode, **info)
+    mf = mask.float()
+    vals = torch.stack([mf.sum(), (tok * mf).sum(), (clip_mask.float() * mf).sum(),
+                        ((lp - old) * mf).sum(), (behav_w * mf).sum()]).detach().cpu().tolist()
+    n = vals[0]
+    metrics = {"loss.sum": vals[1], "loss.tokens": n, "actor/pg_loss.sum": vals[1], "actor/pg_loss.tokens": n,
+               "actor/pg_clipfrac.sum": vals[2], "actor/pg_clipfrac.tokens": n,
+               "actor/approx_kl.sum": -vals[3], "actor/approx_kl.tokens": n,
+               "actor/behav_imp_weight.sum": vals[4], "actor/behav_imp_weight.tokens": n}
+    return loss, metrics
+
+
+def _sft_core(model_outputs: dict, batch: dict, meta: dict, device):
+    packed = model_outputs["packed"]
+    lp = model_outputs["logprobs"].float()
+    lm = batch.get("loss_mask")
+    if lm is None and batch.get("labels") is not None:
+        lm = (batch["labels"] != -100)
+    mask = (packed.gather_from_grid(lm.to(device)).bool() if lm is not None
+            else torch.ones_like(lp, dtype=torch.bool))
+    ce_sum = -masked_sum(lp, mask)
+    ntok = mask.sum()
+    return ce_sum, ntok
+
+
+@register_loss_fn("sft_ce")
+def sft_ce_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, device):
+    """Cross entropy summed over this shard's tokens, divided by the GLOBAL token count and multiplied by
+    ``dp_size`` (gradients are averaged over ranks afterwards); all-masked shards contribute zero."""
+    ce_sum, ntok = _sft_core(model_outputs, batch, meta, device)
+    dp = int(meta.get("dp_size", 1) or 1)
+    t_global = meta.get("batch_num_tokens")
+    denom = float(t_global) if t_global else ntok.clamp_min(1).float()
+    loss = ce_sum / denom * dp
+    s, n = torch.stack([ce_sum.detach(), ntok.float()]).cpu().tolist()
+    return loss, {"loss.sum": s, "loss.tokens": n}
+
+
+@register_loss_fn("sft")
+def sft_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, device):
+    """Mean next-token cross entropy of the shard (the Hugging Face ``outputs.loss`` convention)."""
+    ce_sum, ntok = _sft_core(model_outputs, batch, meta, device)
+    loss = ce_sum / ntok.clamp_min(1).float()
+    s, n = torch.stack([ce_sum.detach(), ntok.float()]).cpu().tolist()
+    return loss, {"loss.sum": s, "loss.tokens": n}
+
+
+SFT_LOSS_FNS = {"sft", "sft_ce"}

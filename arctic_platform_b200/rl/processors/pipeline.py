@@ -1,0 +1,109 @@
+"""One forward (and backward) pass of a worker over its shard of the batch.
+
+``run_pipeline`` takes the client's padded tensors, builds the packed (optionally prompt-deduplicated)
+layout on the host in one pass, runs the model once, evaluates the registered loss and, when asked,
+back-propagates into the engine's flat gradient buffer.  Outputs go back padded to ``[B, R]``.
+
+The reference's pipeline (arctic_platform/rl/processors/pipeline.py:222-499) un-pads 2-D side tensors to
+1-D, calls a monkey-patched HF model, collects logits/log-probs through post-processors and re-pads; here
+the model is packed-native and log-probs/entropy come straight out of the fused lm-head kernel, so the
+post-processors reduce to the entropy switch and the temperature.
+"""
+from __future__ import annotations
+
+import time
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from ...common.registry import LOSS_FNS, POST_PROCESSORS, register_post_processor, resolve_fn
+from ...models.decoder import token_logprobs
+from ..zorro_train.layout import PackedBatch, build_packed_batch, build_plain_packed
+from . import losses as _losses  # noqa: F401  (registers the built-in losses)
+
+DEFAULT_PROCESSING = {"pre": [], "post": ["compute_entropy_and_logprobs"], "loss_fn": "verl_grpo", "loss_kwargs": {}}
+
+
+@register_post_processor("identity")
+def _identity(model_outputs, batch, meta, config, device):
+    return model_outputs
+
+
+@register_post_processor("compute_entropy_and_logprobs")
+def _entropy_and_logprobs(model_outputs, batch, meta, config, device):
+    """Log-probs and entropy are produced by the fused lm-head kernel; nothing left to compute."""
+    return model_outputs
+
+
+@register_post_processor("compute_entropy")
+def _entropy(model_outputs, batch, meta, config, device):
+    return model_outputs
+
+
+@register_post_processor("apply_temperature")
+def _temperature(model_outputs, batch, meta, config, device):
+    """Temperature is folded into the lm-head epilogue (``meta['temperature']``)."""
+    return model_outputs
+
+
+def response_length_of(batch: dict, meta: dict) -> int:
+    for key in ("responses", "response_mask", "old_log_probs", "advantages"):
+        t = batch.get(key)
+        if torch.is_tensor(t) and t.dim() == 2:
+            return int(t.shape[1])
+    if meta.get("response_length"):
+        return int(meta["response_length"])
+    raise KeyError("cannot infer the response length: send 'responses'/'response_mask' or meta['response_length']")
+
+
+def pack_for_model(batch: dict, meta: dict, sft: bool) -> PackedBatch:
+    ids = batch["input_ids"]
+    mask = batch.get("attention_mask")
+    if mask is None:
+        mask = torch.ones_like(ids)
+    if sft:
+        return build_plain_packed(ids, mask)
+    return build_packed_batch(ids, mask, response_length_of(batch, meta),
+                              dedup=bool(meta.get("zorro_train_enable", True)))
+
+
+def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = None,
+                 processing: Optional[dict] = None, device=None, backward: bool = True,
+                 return_tensors: bool = True) -> Dict[str, Any]:
+    meta = dict(meta or {})
+    processing = {**DEFAULT_PROCESSING, **(processing or {})}
+    model = engine.model
+    device = device or next(model.parameters()).device
+    loss_name = processing.get("loss_fn")
+    sft = loss_name in _losses.SFT_LOSS_FNS or bool(meta.get("plain_packing"))
+    t0 = time.perf_counter()
+    packed = pack_for_model(batch, meta, sft).to(device)
+    actor = meta.get("actor_config", {}) or {}
+    want_entropy = bool(actor.get("entropy_coeff", 0.0)) or bool(meta.get("compute_entropy", not backward))
+    temperature = float(meta.get("temperature", 1.0) or 1.0)
+    model.train(backward)
+    ctx = torch.enable_grad() if backward else torch.no_grad()
+    with ctx:
+        lp, ent = token_logprobs(model, packed, 1.0 / temperature, with_entropy=want_entropy)
+        outputs: Dict[str, Any] = {"logprobs": lp, "entropy": ent, "packed": packed}
+        for name in processing.get("post") or []:
+            outputs = resolve_fn(name, POST_PROCESSORS)(outputs, batch, meta, processing, device)
+        loss = None
+        metrics: Dict[str, Any] = {}
+        if loss_name:
+            loss_fn = resolve_fn(loss_name, LOSS_FNS)
+            loss, metrics = loss_fn(outputs, batch, meta, processing.get("loss_kwargs") or {}, device)
+        if backward:
+            if loss is None:
+                raise ValueError("backward needs a loss_fn")
+            engine.backward(loss)
+    result: Dict[str, Any] = {"metrics": metrics, "avg_loss": float(loss.detach()) if loss is not None else 0.0}
+    metrics.setdefault("perf/packed_tokens", float(packed.total_tokens))
+    metrics.setdefault("perf/dedup_redundancy", float(packed.redundancy))
+    metrics["perf/pipeline_ms"] = (time.perf_counter() - t0) * 1e3
+    if return_tensors:
+        out_batch = {"log_probs": packed.scatter_to_grid(lp.detach().float()).cpu()}
+        if ent is not None:
+            out_batch["entropy"] = packed.scatter_to_grid(ent.detach().float()).cpu()
+        result["batch"] = out_batch
+    return result

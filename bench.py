@@ -1,0 +1,281 @@
+"""GRPO step benchmark: Qwen3-4B, colocated trainer + sampler on every GPU, synthetic data, random-init weights.
+
+One step = sync_weights -> rollout (n samples per prompt, temperature 1.0, fixed response budget) ->
+reference log-probs -> forward/backward (ZoRRo prompt-deduplicated, verl-style GRPO loss) -> AdamW.
+Weak scaling: every GPU holds ``--prompts-per-gpu`` prompts x ``--samples`` rollouts (the named
+configuration, 64 prompts x 16 samples on 8 GPUs, is 8 prompts per GPU).  The headline metric is
+whole-job tokens/s = global (prompt + response) tokens of a step / step time, as the reference's verl
+integration reports (arctic_platform/integrations/verl/README.md:100-109).
+
+Two timed regions of ``--steps`` steps each, both bracketed by barrier + synchronize, timed with CUDA
+events, max over ranks:
+  * ``value``: the engines driven directly;
+  * ``e2e``:   the same step through the public client API (``create_arctic_rl_client``), where every
+               step copies its inputs from pinned host memory to the device and reads its results back.
+
+    python bench.py [--gpus N --steps K --warmup W]          # N > 1 under torch.distributed.run
+    python bench.py --impl reference                          # the reference's own stack, if installable
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen3-4b")
+    ap.add_argument("--prompts-per-gpu", type=int, default=8)
+    ap.add_argument("--samples", type=int, default=16)
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--response-len", type=int, default=2048)
+    ap.add_argument("--rollouts-per-microbatch", type=int, default=4,
+                    help="rollouts of one prompt per training micro-batch (prompt KV is recomputed per micro-batch)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--lr", type=float, default=1e-6)
+    return ap.parse_args()
+
+
+def reference_arm(args) -> None:
+    """The reference needs deepspeed, ray, arctic_inference and deep_ep (pyproject.toml:111-131 of the reference);
+    none is installed here or in the offline wheelhouse, and its build backend (hatchling) is missing too."""
+    why = "reference not installable offline: build backend hatchling and hard deps deepspeed/ray/arctic_inference/deep_ep are absent from the image and /opt/wheelhouse"
+    try:
+        sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
+        import arctic_platform  # noqa: F401
+        import deepspeed  # noqa: F401
+        import ray  # noqa: F401
+        why = "reference imports, but no reference runner is wired because its engines (DeepSpeed/vLLM/ArcticInference) are unavailable"
+    except Exception:
+        pass
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons of this process's GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.stop_flag = threading.Event()
+
+    def run(self):
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                parts = [p.strip() for p in out.split(",")]
+                if len(parts) >= 7:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self.stop_flag.wait(0.5)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        reasons = []
+        for i, name in enumerate(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")):
+            if any(s[3 + i].lower().startswith("active") for s in self.samples):
+                reasons.append(name)
+        busy = sorted(sm)[len(sm) // 4:] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    if args.gpus != world and rank == 0 and world > 1:
+        print(f"[bench] --gpus {args.gpus} but WORLD_SIZE {world}; using {world}", file=sys.stderr)
+
+    from arctic_platform_b200.engine.sampler import SamplingParams
+    from arctic_platform_b200.engine.trainer import EngineConfig, TrainEngine
+    from arctic_platform_b200.engine.worker import EngineWorker
+    from arctic_platform_b200.models.config import resolve_config
+    from arctic_platform_b200.ops import _lib
+    from arctic_platform_b200.rl import ArcticRLClientConfig, create_arctic_rl_client
+
+    cfg = resolve_config(args.model)
+    P, R, NP, NS = args.prompt_len, args.response_len, args.prompts_per_gpu, args.samples
+    B = NP * NS
+    kv_tokens = NP * (P + 64) + B * (R + 64) + 4096
+    client_cfg = ArcticRLClientConfig(
+        comm_protocol="local", model_name=args.model, training_gpus=world, sampling_gpus=world, log_prob_gpus=world,
+        colocate=True, seed=1234,
+        ds_config={"zero_optimization": {"stage": 2}, "gradient_clipping": 1.0,
+                   "optimizer": {"type": "AdamW", "params": {"lr": args.lr, "betas": [0.9, 0.999], "eps": 1e-8,
+                                                             "weight_decay": 0.01}}},
+        vllm_config={"kv_cache_tokens": kv_tokens, "max_num_seqs": max(8, B), "max_model_len": P + R + 16},
+        arctic_inference_config={"zorro_inference": {"enable": True}})
+    client = create_arctic_rl_client(client_cfg)
+    server = client.get_server_state()
+    train_w = server.find_job("training").workers[0].obj
+    samp_w = server.find_job("sampling").workers[0].obj
+    ref_w = server.find_job("log_prob").workers[0].obj
+
+    gen = torch.Generator().manual_seed(99 + rank)
+    sp = {"n": NS, "temperature": 1.0, "max_tokens": R, "ignore_eos": True}
+    n_mb = max(1, NS // max(1, args.rollouts_per_microbatch))
+    meta = {"zorro_train_enable": True, "temperature": 1.0, "dp_size": world,
+            "batch_num_tokens": float(B * R * world), "global_batch_size": float(B * world),
+            "actor_config": {"loss_agg_mode": "token-mean", "use_kl_loss": True, "kl_loss_coef": 0.001,
+                             "kl_loss_type": "low_var_kl", "entropy_coeff": 0.0}}
+
+    def make_prompts():
+        return [torch.randint(1, cfg.vocab_size, (P,), generator=gen).tolist() for _ in range(NP)]
+
+    def build_batches(prompts, results):
+        """Padded RL batch on pinned host memory, split so that each micro-batch holds every prompt with a
+        slice of its rollouts (the prompt is deduplicated inside a micro-batch)."""
+        ids = torch.zeros((B, P + R), dtype=torch.int64).pin_memory()
+        old = torch.zeros((B, R), dtype=torch.float32).pin_memory()
+        for i, r in enumerate(results):
+            ids[i, :P] = torch.tensor(prompts[r["prompt_index"]])
+            ids[i, P:P + len(r["token_ids"])] = torch.tensor(r["token_ids"])
+            old[i, :len(r["logprobs"])] = torch.tensor(r["logprobs"])
+        mask = torch.ones_like(ids)
+        rewards = torch.randn(NP, NS, generator=gen)
+        adv = ((rewards - rewards.mean(1, keepdim=True)) / (rewards.std(1, keepdim=True) + 1e-6)).reshape(B, 1)
+        full = {"input_ids": ids, "attention_mask": mask, "response_mask": mask[:, P:].contiguous(),
+                "old_log_probs": old, "advantages": adv.expand(B, R).contiguous()}
+        per = NS // n_mb
+        mbs = []
+        for m in range(n_mb):
+            rows = torch.tensor([p * NS + m * per + j for p in range(NP) for j in range(per)])
+            mbs.append({k: v[rows].contiguous().pin_memory() for k, v in full.items()})
+        return mbs
+
+    def in_bytes(mbs, prompts):
+        return sum(t.numel() * t.element_size() for mb in mbs for t in mb.values()) + sum(len(p) for p in prompts) * 8
+
+    counters = {"h2d": 0, "d2h": 0}
+
+    def step_direct():
+        """Engines driven directly (no client / server layer)."""
+        prompts = make_prompts()
+        train_w.sync_weights_to(samp_w)
+        samp_w.sampler.wake(["kv_cache"])
+        results = samp_w.generate(prompts, sp)
+        samp_w.sampler.sleep(1)
+        mbs = build_batches(prompts, results)
+        for mb in mbs:
+            ref = ref_w.forward_no_grad(mb, dict(meta), None)
+            mb["ref_log_prob"] = ref["batch"]["log_probs"]
+        out = train_w.forward_backward(mbs, dict(meta), {"loss_fn": "verl_grpo"})
+        st = train_w.step()
+        return out["avg_loss"], st["metrics"]["grad_norm"]
+
+    def step_client():
+        """The same step through the public client API; inputs start in pinned host memory."""
+        prompts = make_prompts()
+        client.call("sync_weights")
+        results = client.call("generate", prompts, sp)
+        client.call("sleep_inference", 1)
+        mbs = build_batches(prompts, results)
+        counters["h2d"] = 2 * in_bytes(mbs, prompts)          # every micro-batch goes to the device twice (ref + train)
+        d2h = sum(len(r["token_ids"]) * 8 for r in results)
+        for mb in mbs:
+            ref = client.call("fwd_no_grad", {"batch": mb, "meta": dict(meta)}, reference_model=True)
+            mb["ref_log_prob"] = ref["batch"]["log_probs"]
+            d2h += ref["batch"]["log_probs"].numel() * 4
+        out = client.call("fwd_bwd", {"batch": mbs, "meta": dict(meta)}, {"loss_fn": "verl_grpo"})
+        st = client.call("step")
+        counters["d2h"] = d2h + 8 * (len(out["metrics"]) + 2)
+        return out["avg_loss"], st["metrics"]["grad_norm"]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    def timed(fn, k):
+        barrier()
+        st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = _lib.launch_count()
+        st.record()
+        for _ in range(k):
+            fn()
+        en.record()
+        barrier()
+        ms = st.elapsed_time(en)
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / k, _lib.launch_count() - l0
+
+    for _ in range(args.warmup):
+        step_direct()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms_direct, launches = timed(step_direct, args.steps)
+    e2e = None
+    if not args.no_e2e:
+        step_client()                                        # client path warm-up (separate caches / graphs)
+        ms_client, _ = timed(step_client, args.steps)
+        tokens = B * (P + R) * world
+        e2e = {"value": tokens / (ms_client / 1e3), "unit": "tokens/s", "ms_per_step": ms_client,
+               "h2d_bytes_per_step": counters["h2d"], "d2h_bytes_per_step": counters["d2h"]}
+    sampler.stop_flag.set()
+    sampler.join(timeout=3)
+    _lib.check_status("bench")
+    if rank == 0:
+        tokens = B * (P + R) * world
+        line = {
+            "metric": "grpo_step_tokens_per_s", "value": tokens / (ms_direct / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_direct,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "ours",
+            "config": {"model": args.model, "global_batch": B * world, "prompts": NP * world, "samples_per_prompt": NS,
+                       "seq_len": P + R, "prompt_len": P, "response_len": R,
+                       "parallelism": f"dp{world}-zero2-fused + sampler tp1 x{world} replicas, colocated",
+                       "l2_policy": "inputs larger than L2 (new random prompts and rollouts every step)",
+                       "step": "sync_weights+rollout+ref_logprob+fwd_bwd+adamw", "lr": args.lr,
+                       "train_microbatches": n_mb},
+            "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches,
+            "rollout_tokens_per_step": B * R * world,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
