@@ -136,8 +136,11 @@ class DecoderLM(nn.Module):
         return self
 
     def rope(self, device) -> Tuple[torch.Tensor, torch.Tensor]:
-        if self._rope is None or self._rope[0].device != torch.device(device):
-            self._rope = norm.rope_tables(self._rope_len, self.cfg.head_dim, self.cfg.rope_theta, device)
+        dev = torch.device(device)
+        if dev.type == "cuda" and dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        if self._rope is None or self._rope[0].device != dev:
+            self._rope = norm.rope_tables(self._rope_len, self.cfg.head_dim, self.cfg.rope_theta, dev)
         return self._rope
 
     @property

@@ -1,0 +1,85 @@
+"""Metric reducers, batch split/merge, checkpoint path helpers, registry."""
+import os
+
+import pytest
+import torch
+
+from arctic_platform_b200.common import registry
+from arctic_platform_b200.common.utils import batch as B
+from arctic_platform_b200.common.utils.checkpoint import prune_checkpoint_dirs, resolve_checkpoint_save_paths
+from arctic_platform_b200.common.utils.metrics import (combine_metric_microbatches, combine_metric_shards,
+                                                       finalize_fwd_bwd_metrics)
+
+
+def test_shards_collapse_to_global_token_mean():
+    shards = [{"loss.sum": 10.0, "loss.tokens": 4, "lr": 1e-3, "tag": "a", "ok": True},
+              {"loss.sum": 2.0, "loss.tokens": 8, "lr": 3e-3}]
+    out = combine_metric_shards(shards)
+    assert out["loss"] == pytest.approx(1.0) and out["lr"] == pytest.approx(2e-3)
+    assert out["tag"] == "a" and out["ok"] is True and "loss.sum" not in out
+    assert combine_metric_shards([{"x.sum": 1.0, "x.tokens": 0}])["x"] == 0.0
+    assert combine_metric_shards([]) == {}
+    # an unpaired .sum is an ordinary number
+    assert combine_metric_shards([{"y.sum": 2.0}, {"y.sum": 4.0}])["y.sum"] == pytest.approx(3.0)
+
+
+def test_microbatches_keep_pairs_and_average_rest():
+    out = combine_metric_microbatches([{"a.sum": 1.0, "a.tokens": 2, "g": 4.0}, {"a.sum": 3.0, "a.tokens": 2, "g": 2.0}])
+    assert out == {"a.sum": 4.0, "a.tokens": 4.0, "g": 3.0}
+
+
+def test_finalize_prefers_global_loss():
+    m, loss = finalize_fwd_bwd_metrics([{"metrics": {"loss.sum": 6.0, "loss.tokens": 3}, "avg_loss": 100.0},
+                                        {"metrics": {"loss.sum": 0.0, "loss.tokens": 3}, "avg_loss": 100.0}])
+    assert loss == pytest.approx(1.0) and m["loss"] == pytest.approx(1.0)
+    _, loss2 = finalize_fwd_bwd_metrics([{"metrics": {}, "avg_loss": 0.5}, {"avg_loss": 0.25}])
+    assert loss2 == pytest.approx(0.75)
+
+
+def test_split_merge_restore_order():
+    batch = {"input_ids": torch.arange(24).view(6, 4), "attention_mask": torch.ones(6, 4, dtype=torch.long),
+             "response_mask": torch.ones(6, 2), "note": "x"}
+    meta = {}
+    shards, order = B.split_batch_for_ranks(batch, meta, 3)
+    assert order is None and len(shards) == 3 and shards[1]["input_ids"].shape == (2, 4) and shards[2]["note"] == "x"
+    assert meta["dp_size"] == 3 and meta["batch_num_tokens"] == 12.0 and meta["global_batch_size"] == 6.0
+    merged = B.merge_dict_shards([{"lp": s["input_ids"].float()} for s in shards])
+    assert torch.equal(merged["lp"], batch["input_ids"].float())
+    perm = torch.tensor([2, 0, 1])
+    shuffled = {"v": torch.tensor([30.0, 10.0, 20.0])}          # row i holds original sample perm[i]
+    assert torch.equal(B.restore_batch_order(shuffled, perm)["v"], torch.tensor([10.0, 20.0, 30.0]))
+    mbs, _ = B.split_batch_for_ranks([batch, batch], {}, 2)
+    assert len(mbs) == 2 and len(mbs[0]) == 2 and mbs[1][0]["input_ids"].shape == (3, 4)
+
+
+def test_position_ids_reconstruction():
+    b = {"attention_mask": torch.tensor([[0, 0, 1, 1, 1], [1, 1, 1, 0, 0]])}
+    B.reconstruct_position_ids_(b)
+    assert b["position_ids"].tolist() == [[0, 0, 0, 1, 2], [0, 1, 2, 0, 0]]
+
+
+def test_checkpoint_paths_and_pruning(tmp_path):
+    assert resolve_checkpoint_save_paths("/x/y", 12) == ("/x/y", "checkpoint-12")
+    assert resolve_checkpoint_save_paths("/x/y", None) == ("/x/y", None)
+    for s in (1, 5, 10, 20):
+        (tmp_path / f"checkpoint-{s}").mkdir()
+    (tmp_path / "hf").mkdir()
+    (tmp_path / "checkpoint-abc").mkdir()
+    removed = prune_checkpoint_dirs(str(tmp_path), 2)
+    assert sorted(os.path.basename(r) for r in removed) == ["checkpoint-1", "checkpoint-5"]
+    assert sorted(p.name for p in tmp_path.iterdir()) == ["checkpoint-10", "checkpoint-20", "checkpoint-abc", "hf"]
+    assert prune_checkpoint_dirs(str(tmp_path), 0) == [] and prune_checkpoint_dirs(str(tmp_path / "nope"), 1) == []
+
+
+def test_registry_lookup_and_dotted_fallback():
+    @registry.register_loss_fn("_unit_loss")
+    def f(*a):
+        return 1
+
+    assert registry.resolve_fn("_unit_loss", registry.LOSS_FNS) is f
+    assert registry.resolve_fn(f, registry.LOSS_FNS) is f
+    assert registry.resolve_fn("math.sqrt", registry.LOSS_FNS)(4) == 2
+    with pytest.raises(KeyError):
+        registry.resolve_fn("nope", registry.LOSS_FNS)
+    with pytest.raises(KeyError):
+        registry.resolve_fn("math.nope", registry.LOSS_FNS)
