@@ -1,0 +1,126 @@
+"""Checkpoints in the DeepSpeed directory layout, written without DeepSpeed.
+
+``save_checkpoint(engine, save_dir, tag)`` produces what ``engine.save_checkpoint(save_dir, tag)`` of a
+DeepSpeed bf16 ZeRO engine leaves on disk (the reference saves exactly that,
+arctic_platform/common/deepspeed_worker.py:578-600)::
+
+    <save_dir>/latest                                            text file with the tag
+    <save_dir>/<tag>/mp_rank_00_model_states.pt                  rank 0: module weights + engine state
+    <save_dir>/<tag>/bf16_zero_pp_rank_<r>_mp_rank_00_optim_states.pt   every rank: its optimizer partition
+    <save_dir>/hf/                                               optional Hugging Face safetensors export
+
+The model-states file keeps the DeepSpeed keys (``module``, ``param_shapes``, ``global_steps``,
+``dp_world_size``, ``mp_world_size``, ``ds_config``, ``ds_version``, ``lr_scheduler``...), with the module
+stored under Hugging Face parameter names; the optimizer file keeps ``optimizer_state_dict`` with
+``zero_stage``, ``partition_count``, ``base_optimizer_state`` (``exp_avg`` / ``exp_avg_sq`` / ``step``) and
+``single_partition_of_fp32_groups``.  The flat partition follows THIS engine's unit layout (recorded under
+``b200_layout``), which is what makes a resume bit-exact; the HF export is the interchange format.
+"""
+from __future__ import annotations
+
+import os
+from collections import OrderedDict
+from pathlib import Path
+from typing import Any, Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+DS_VERSION = "0.19.2+b200"
+
+
+def _barrier(engine) -> None:
+    if engine.world > 1 and dist.is_initialized():
+        dist.barrier(group=engine.group)
+
+
+def save_checkpoint(engine, save_dir: str, tag: Optional[str] = None, export_hf: bool = False) -> Dict[str, Any]:
+    tag = tag or f"global_step{engine.global_steps}"
+    root = Path(save_dir)
+    d = root / tag
+    d.mkdir(parents=True, exist_ok=True)
+    files = []
+    if engine.rank == 0:
+        module = OrderedDict((n, t.detach().to("cpu").clone()) for n, t in engine.iter_hf_tensors())
+        state = {
+            "module": module, "buffer_names": [], "optimizer": None,
+            "param_shapes": [OrderedDict((n, t.shape) for n, t in module.items())],
+            "frozen_param_shapes": None, "frozen_param_fragments": None, "shared_params": {},
+            "lr_scheduler": {"type": engine.cfg.scheduler.type, "warmup_steps": engine.cfg.scheduler.warmup_steps,
+                             "total_steps": engine.cfg.scheduler.total_steps,
+                             "min_lr_ratio": engine.cfg.scheduler.min_lr_ratio, "last_step": engine.global_steps},
+            "data_sampler": None, "random_ltd": None, "sparse_tensor_module_names": [],
+            "skipped_steps": 0, "global_steps": engine.global_steps, "global_samples": 0,
+            "micro_steps": engine.micro_steps,
+            "dp_world_size": engine.world, "mp_world_size": 1,
+            "ds_config": {"zero_optimization": {"stage": engine.cfg.zero_stage}, "bf16": {"enabled": True},
+                          "gradient_accumulation_steps": engine.cfg.gradient_accumulation_steps,
+                          "gradient_clipping": engine.cfg.max_grad_norm},
+            "ds_version": DS_VERSION,
+            "b200_layout": {"total": engine.total, "units": [(u.name, u.offset, u.length) for u in engine.units],
+                            "param_slices": {k: (o, n, tuple(s)) for k, (o, n, s) in engine.param_slices.items()}},
+        }
+        f = d / "mp_rank_00_model_states.pt"
+        torch.save(state, f)
+        files.append(str(f))
+    if not engine.forward_only:
+        host = lambda t: t.detach().to("cpu").clone()
+        optim = {
+            "optimizer_state_dict": {
+                "zero_stage": engine.cfg.zero_stage, "partition_count": [engine.world], "loss_scaler": None,
+                "dynamic_loss_scale": False, "overflow": False, "clip_grad": engine.cfg.max_grad_norm,
+                "base_optimizer_state": {
+                    "state": {0: {"exp_avg": host(engine.exp_avg), "exp_avg_sq": host(engine.exp_avg_sq),
+                                  "step": engine.global_steps}},
+                    "param_groups": [{"lr": engine.cfg.lr, "betas": tuple(engine.cfg.betas), "eps": engine.cfg.eps,
+                                      "weight_decay": engine.cfg.weight_decay, "params": [0]}]},
+                "single_partition_of_fp32_groups": [host(engine.master)],
+                "group_paddings": [0],
+            },
+            "ds_config": {"zero_optimization": {"stage": engine.cfg.zero_stage}},
+            "ds_version": DS_VERSION,
+        }
+        f = d / f"bf16_zero_pp_rank_{engine.rank}_mp_rank_00_optim_states.pt"
+        torch.save(optim, f)
+        files.append(str(f))
+    _barrier(engine)
+    if engine.rank == 0:
+        (root / "latest").write_text(tag)
+        if export_hf:
+            from ..models.hf_io import save_hf_checkpoint
+            files += [str(root / "hf" / x) for x in save_hf_checkpoint(engine.model, root / "hf")]
+    _barrier(engine)
+    return {"path": str(d), "tag": tag, "files": files}
+
+
+def load_checkpoint(engine, load_dir: str, tag: Optional[str] = None) -> int:
+    """Restores module weights, optimizer partition and step counters; returns ``global_steps`` (0 when the
+    directory has no checkpoint)."""
+    root = Path(load_dir)
+    if tag is None:
+        latest = root / "latest"
+        if not latest.exists():
+            return 0
+        tag = latest.read_text().strip()
+    d = root / tag
+    ms = d / "mp_rank_00_model_states.pt"
+    if not ms.exists():
+        raise FileNotFoundError(f"{ms} not found")
+    state = torch.load(ms, map_location="cpu", weights_only=False)
+    if state.get("dp_world_size", 1) != engine.world and not engine.forward_only:
+        raise ValueError(f"checkpoint was written with {state.get('dp_world_size')} data-parallel ranks, this job has "
+                         f"{engine.world}; use the hf/ export to change the world size")
+    from ..models.hf_io import load_hf_tensor
+    for name, t in state["module"].items():
+        load_hf_tensor(engine.model, name, t)
+    engine.global_steps = int(state.get("global_steps", 0))
+    engine.micro_steps = int(state.get("micro_steps", 0))
+    if not engine.forward_only:
+        f = d / f"bf16_zero_pp_rank_{engine.rank}_mp_rank_00_optim_states.pt"
+        osd = torch.load(f, map_location="cpu", weights_only=False)["optimizer_state_dict"]
+        base = osd["base_optimizer_state"]["state"][0]
+        engine.master.copy_(osd["single_partition_of_fp32_groups"][0])
+        engine.exp_avg.copy_(base["exp_avg"])
+        engine.exp_avg_sq.copy_(base["exp_avg_sq"])
+    _barrier(engine)
+    return engine.global_steps

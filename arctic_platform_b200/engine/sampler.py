@@ -373,6 +373,7 @@ class SamplerEngine:
             self._graphs.clear()
         if sp.seed is not None:
             self.seed = int(sp.seed)
+            self.d_step.zero_()            # a seeded call restarts the random stream
         results: List[Optional[dict]] = [None] * (len(prompts_np) * sp.n)
         # work queue: one entry per prompt; a prompt's n rollouts are admitted together (one prefix group)
         queue = list(range(len(prompts_np)))
