@@ -664,3 +664,4 @@ int apb_lmhead_dlogits(const void* hidden, const void* weight, const int* labels
   return lmhead_launch(hidden, weight, M, V, H, ldh, ldw, p, 256, stream);
 }
 }
+

@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--rollouts-per-microbatch", type=int, default=4,
                     help="rollouts of one prompt per training micro-batch (prompt KV is recomputed per micro-batch)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--phases", action="store_true", help="print per-phase wall times of the direct step to stderr")
     ap.add_argument("--lr", type=float, default=1e-6)
     return ap.parse_args()
 
@@ -187,19 +188,34 @@ def main():
 
     counters = {"h2d": 0, "d2h": 0}
 
+    phase_ms = {}
+
+    def mark(name, t0):
+        if args.phases:
+            torch.cuda.synchronize(dev)
+            phase_ms[name] = phase_ms.get(name, 0.0) + (time.perf_counter() - t0) * 1e3
+        return time.perf_counter()
+
     def step_direct():
         """Engines driven directly (no client / server layer)."""
+        t = time.perf_counter()
         prompts = make_prompts()
         train_w.sync_weights_to(samp_w)
         samp_w.sampler.wake(["kv_cache"])
+        t = mark("sync_weights", t)
         results = samp_w.generate(prompts, sp)
+        t = mark("rollout", t)
         samp_w.sampler.sleep(1)
         mbs = build_batches(prompts, results)
+        t = mark("build_batch", t)
         for mb in mbs:
             ref = ref_w.forward_no_grad(mb, dict(meta), None)
             mb["ref_log_prob"] = ref["batch"]["log_probs"]
+        t = mark("ref_logprob", t)
         out = train_w.forward_backward(mbs, dict(meta), {"loss_fn": "verl_grpo"})
+        t = mark("fwd_bwd", t)
         st = train_w.step()
+        t = mark("optimizer", t)
         return out["avg_loss"], st["metrics"]["grad_norm"]
 
     def step_client():
@@ -245,7 +261,11 @@ def main():
         step_direct()
     sampler = ClockSampler(local_rank)
     sampler.start()
+    phase_ms.clear()
     ms_direct, launches = timed(step_direct, args.steps)
+    if args.phases and rank == 0:
+        print("[bench] phases ms/step: " + json.dumps({k: round(v / args.steps, 1) for k, v in phase_ms.items()}),
+              file=sys.stderr, flush=True)
     e2e = None
     if not args.no_e2e:
         step_client()                                        # client path warm-up (separate caches / graphs)
