@@ -665,3 +665,50 @@ int apb_lmhead_dlogits(const void* hidden, const void* weight, const int* labels
 }
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the fused lm-head log-prob forward (see apb_noalloc.h)
+// ---------------------------------------------------------------------------
+#include "apb_noalloc.h"
+
+namespace apb {
+// Per-tile reduction records (max, sum-exp, sum exp*z, label logit) for the no-alloc entry point.
+// File-scope device storage: its size is fixed at build time and every device that loads the
+// library carries it.  In host code this name is only a handle for cudaGetSymbolAddress.
+static __device__ __align__(256) float4 g_noalloc_partials[APB_NOALLOC_MAX_TILE_RECORDS];
+}  // namespace apb
+
+extern "C" int apb_lmhead_logprob_fwd_noalloc(const void* hidden, const void* weight, const int* labels,
+                                               const float* row_scale, float* lp, float* ent, float* lse, int M,
+                                               int V, int H, long long ldh, long long ldw, float scale,
+                                               cudaStream_t stream) {
+  using namespace apb;
+  if (M <= 0) return 0;
+  if (V <= 0 || H <= 0) return kBadArgument;
+  const long long tiles = (static_cast<long long>(V) + 127) / 128;
+  if (static_cast<long long>(M) * tiles > APB_NOALLOC_MAX_TILE_RECORDS) return APB_NOALLOC_TOO_LARGE;
+  // One-time set-up per device (with that device current): resolve the device address of the scratch.
+  static float4* scratch_ptr[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return APB_NOALLOC_SETUP_FAILED;
+  if (!scratch_ptr[dev]) {
+    float4* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_partials) != cudaSuccess || !p)
+      return APB_NOALLOC_SETUP_FAILED;
+    scratch_ptr[dev] = p;
+  }
+  float* partial = reinterpret_cast<float*>(scratch_ptr[dev]);
+  GemmParams p{};
+  p.epi = kEpiLogprobPartial;
+  p.alpha = scale;
+  p.C = nullptr;
+  p.ldc = 0;
+  p.row_scale = row_scale;
+  p.labels = labels;
+  p.partial = partial;
+  int rc = lmhead_launch(hidden, weight, M, V, H, ldh, ldw, p, 128, stream);
+  if (rc) return rc;
+  const int grid = (M * 32 + 255) / 256;
+  lmhead_combine_kernel<<<grid, 256, 0, stream>>>(reinterpret_cast<const float4*>(partial), static_cast<int>(tiles),
+                                                  lp, ent, lse, M);
+  return static_cast<int>(cudaGetLastError());
+}
