@@ -45,6 +45,7 @@ def parse_args():
     ap.add_argument("--response-len", type=int, default=2048)
     ap.add_argument("--rollouts-per-microbatch", type=int, default=4,
                     help="rollouts of one prompt per training micro-batch (prompt KV is recomputed per micro-batch)")
+    ap.add_argument("--prompts-per-microbatch", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="print per-phase wall times of the direct step to stderr")
     ap.add_argument("--lr", type=float, default=1e-6)
@@ -153,7 +154,9 @@ def main():
 
     gen = torch.Generator().manual_seed(99 + rank)
     sp = {"n": NS, "temperature": 1.0, "max_tokens": R, "ignore_eos": True}
-    n_mb = max(1, NS // max(1, args.rollouts_per_microbatch))
+    rpm = max(1, min(NS, args.rollouts_per_microbatch))
+    ppm = max(1, min(NP, args.prompts_per_microbatch))
+    n_mb = ((NS + rpm - 1) // rpm) * ((NP + ppm - 1) // ppm)
     meta = {"zorro_train_enable": True, "temperature": 1.0, "dp_size": world,
             "batch_num_tokens": float(B * R * world), "global_batch_size": float(B * world),
             "actor_config": {"loss_agg_mode": "token-mean", "use_kl_loss": True, "kl_loss_coef": 0.001,
@@ -176,11 +179,12 @@ def main():
         adv = ((rewards - rewards.mean(1, keepdim=True)) / (rewards.std(1, keepdim=True) + 1e-6)).reshape(B, 1)
         full = {"input_ids": ids, "attention_mask": mask, "response_mask": mask[:, P:].contiguous(),
                 "old_log_probs": old, "advantages": adv.expand(B, R).contiguous()}
-        per = NS // n_mb
         mbs = []
-        for m in range(n_mb):
-            rows = torch.tensor([p * NS + m * per + j for p in range(NP) for j in range(per)])
-            mbs.append({k: v[rows].contiguous().pin_memory() for k, v in full.items()})
+        for p0 in range(0, NP, ppm):
+            for r0 in range(0, NS, rpm):
+                rows = torch.tensor([p * NS + j for p in range(p0, min(NP, p0 + ppm))
+                                     for j in range(r0, min(NS, r0 + rpm))])
+                mbs.append({k: v[rows].contiguous().pin_memory() for k, v in full.items()})
         return mbs
 
     def in_bytes(mbs, prompts):
