@@ -83,16 +83,40 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const int* __restrict__
       l[r] = 0.f;
       acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
     }
+    // K of the page being processed sits in registers; the next page's K and this page's V are
+    // requested before the arithmetic so that three pages of loads are in flight per warp.
+    uint4 kreg[8];
+    {
+      const int pi0 = p0 + warp;
+      if (pi0 < p1) {
+        const int page = pages[static_cast<long long>(g) * max_pages + pi0];
+        const __nv_bfloat16* kp = kcache + ((static_cast<long long>(page) * Hkv + kvh) * kPage + tok) * D + half * 64;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) kreg[i] = *reinterpret_cast<const uint4*>(kp + i * 8);
+      }
+    }
+#pragma unroll 1
     for (int pi = p0 + warp; pi < p1; pi += 4) {
       const int page = pages[static_cast<long long>(g) * max_pages + pi];
-      const __nv_bfloat16* kp = kcache + ((static_cast<long long>(page) * Hkv + kvh) * kPage + tok) * D + half * 64;
+      uint4 knext[8];
+      if (pi + 4 < p1) {
+        const int pn = pages[static_cast<long long>(g) * max_pages + pi + 4];
+        const __nv_bfloat16* kp = kcache + ((static_cast<long long>(pn) * Hkv + kvh) * kPage + tok) * D + half * 64;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) knext[i] = *reinterpret_cast<const uint4*>(kp + i * 8);
+      }
+      uint2 vreg[kPage];
+      {
+        const __nv_bfloat16* vp = vcache + ((static_cast<long long>(page) * Hkv + kvh) * kPage) * D + lane * 4;
+#pragma unroll
+        for (int t = 0; t < kPage; ++t) vreg[t] = *reinterpret_cast<const uint2*>(vp + t * D);
+      }
       float dot[R];
 #pragma unroll
       for (int r = 0; r < R; ++r) dot[r] = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(kp + i * 8);
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&kreg[i]);
         float kf[8];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -128,12 +152,10 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const int* __restrict__
         if (half == 0) p_s[warp][r][tok] = pv;
       }
       __syncwarp();
-      const __nv_bfloat16* vp = vcache + ((static_cast<long long>(page) * Hkv + kvh) * kPage) * D + lane * 4;
 #pragma unroll
       for (int t = 0; t < kPage; ++t) {
-        const uint2 raw = *reinterpret_cast<const uint2*>(vp + t * D);
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vreg[t].x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vreg[t].y));
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           const float pw = p_s[warp][r][t];
@@ -144,6 +166,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const int* __restrict__
         }
       }
       __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 8; ++i) kreg[i] = knext[i];
     }
     // merge the four warps
 #pragma unroll

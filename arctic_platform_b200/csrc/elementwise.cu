@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int T, int H, float eps,
-                   float w_offset) {
+                   float w_offset, float* __restrict__ x_f32) {
   __shared__ float scratch[32];
   const int nvec = H / 8;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
@@ -60,7 +60,17 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     for (int i = 0; i < kNormMaxVec; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
       if (v < nvec) {
-        load8(x + base + v * 8, vals[i]);
+        if (x_f32) {
+          // split-K accumulator: read the fp32 sums and leave zeros behind for the next GEMM
+          float4* xp = reinterpret_cast<float4*>(x_f32 + base + v * 8);
+          const float4 a = xp[0], b = xp[1];
+          vals[i][0] = a.x; vals[i][1] = a.y; vals[i][2] = a.z; vals[i][3] = a.w;
+          vals[i][4] = b.x; vals[i][5] = b.y; vals[i][6] = b.z; vals[i][7] = b.w;
+          xp[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+          xp[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+          load8(x + base + v * 8, vals[i]);
+        }
         if (res) {
           float r[8];
           load8(res + base + v * 8, r);
@@ -381,7 +391,20 @@ int apb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void
   rmsnorm_fwd_kernel<<<grid, kNormThreads, 0, s>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
       static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(res_out),
-      rstd, T, H, eps, w_offset);
+      rstd, T, H, eps, w_offset, nullptr);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Same as apb_rmsnorm_fwd with the input taken from an fp32 buffer (split-K GEMM sums) that is reset to
+// zero as it is read; res_out is required (it receives x + res in bf16, or x alone when res is null).
+int apb_rmsnorm_fwd_f32in(float* x_f32, const void* res, const void* w, void* y, void* res_out, int T, int H, float eps,
+                          float w_offset, cudaStream_t s) {
+  if (T <= 0) return 0;
+  if (H % 8 || H > kNormThreads * 8 * kNormMaxVec || !res_out) return kBadArgument;
+  const int grid = T < 148 * 8 ? T : 148 * 8;
+  rmsnorm_fwd_kernel<<<grid, kNormThreads, 0, s>>>(
+      nullptr, static_cast<const __nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(w),
+      static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(res_out), nullptr, T, H, eps, w_offset, x_f32);
   return static_cast<int>(cudaGetLastError());
 }
 

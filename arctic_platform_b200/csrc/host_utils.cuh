@@ -25,4 +25,9 @@ EncodeTiledFn encode_tiled_fn();
 int make_tmap_2d(CUtensorMap* map, const void* base, int elem_bytes, uint64_t rows, uint64_t cols, uint64_t ld,
                  uint32_t box_cols, uint32_t box_rows);
 
+// General tiled tensor map (rank <= 5), 128-byte swizzle.  dims/box innermost first; strides in BYTES for
+// dimensions 1..rank-1 (dimension 0 is contiguous).
+int make_tmap_nd(CUtensorMap* map, const void* base, int elem_bytes, int rank, const uint64_t* dims,
+                 const uint64_t* strides_bytes, const uint32_t* box);
+
 }  // namespace apb

@@ -124,6 +124,9 @@ def _fn(name: str):
         _FN["dec"] = _lib.declare("apb_paged_decode_partial", [vp, vp, vp, vp, i, vp, vp, vp, vp, vp, i, i, i, i, i, f, vp])
         _FN["merge"] = _lib.declare("apb_decode_merge", [vp, vp, vp, i, vp, vp, i, i, i, vp])
         _FN["sample"] = _lib.declare("apb_sample", [vp, ll, vp, i, i, u, vp, vp, vp, vp])
+        _FN["prefix_tc"] = _lib.declare("apb_decode_prefix_tc",
+                                        [vp, i, vp, vp, vp, i, vp, vp, vp, ll, vp, vp, i, i, i, i, i, f, vp])
+        _FN["norm32"] = _lib.declare("apb_rmsnorm_fwd_f32in", [vp, vp, vp, vp, vp, i, i, f, f, vp])
     return _FN[name]
 
 
@@ -131,7 +134,7 @@ class SamplerEngine:
     def __init__(self, cfg: DecoderConfig, device="cuda", model: Optional[DecoderLM] = None,
                  kv_cache_tokens: int = 1 << 20, max_batch: int = 256, max_seq_len: int = 8192,
                  cascade: bool = True, sync_interval: int = 16, use_cuda_graph: bool = True, seed: int = 0,
-                 eos_token_id: Optional[int] = None):
+                 eos_token_id: Optional[int] = None, prefix_on_tensor_cores: bool = True, split_k: bool = True):
         self.cfg = cfg
         self.device = torch.device(device)
         self.model = model if model is not None else DecoderLM(cfg, self.device, torch.bfloat16)
@@ -142,6 +145,8 @@ class SamplerEngine:
         self.use_cuda_graph = use_cuda_graph
         self.seed = seed
         self.eos = eos_token_id
+        self.prefix_on_tensor_cores = prefix_on_tensor_cores
+        self.split_k = split_k
         self.num_pages = max(64, kv_cache_tokens // PAGE)
         self.max_pages = (max_seq_len + PAGE - 1) // PAGE + 1
         self._alloc_cache()
@@ -192,6 +197,9 @@ class SamplerEngine:
         self.part_o = [torch.empty((B, Hq, self.splits, D), **f32) for _ in range(2)]
         self.part_ml = [torch.empty((B, Hq, self.splits, 2), **f32) for _ in range(2)]
         self.d_logits = torch.empty((B, c.vocab_size), **f32)
+        # fp32 split-K accumulators of the two skinny projections (kept zero between uses by the norm kernel)
+        self.acc_o = torch.zeros((B, c.hidden_size), **f32)
+        self.acc_d = torch.zeros((B, c.hidden_size), **f32)
         self.d_new_tok = torch.zeros(B, **i32)
         self.d_new_lp = torch.zeros(B, **f32)
 
@@ -262,10 +270,18 @@ class SamplerEngine:
         kc, vc = self.kcache[li], self.vcache[li]
         out = torch.empty((B, c.num_heads, c.head_dim), device=self.device, dtype=torch.bfloat16)
         if self.cascade:
-            _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_g_start), _lib.ptr(self.d_g_count), _lib.ptr(self.d_g_pages),
-                           self.max_pages, _lib.ptr(self.d_g_len), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(self.part_o[0]),
-                           _lib.ptr(self.part_ml[0]), B, c.num_heads, c.num_kv_heads, c.head_dim, self.splits, scale, s),
-                       "paged_decode(prefix)")
+            R = c.num_heads // c.num_kv_heads
+            if self.prefix_on_tensor_cores and c.head_dim == 128 and R * MAX_NQ <= 128 and 128 % R == 0:
+                _lib.check(_fn("prefix_tc")(_lib.ptr(q), B, _lib.ptr(self.d_g_start), _lib.ptr(self.d_g_count),
+                                            _lib.ptr(self.d_g_pages), self.max_pages, _lib.ptr(self.d_g_len),
+                                            _lib.ptr(kc), _lib.ptr(vc), self.num_pages, _lib.ptr(self.part_o[0]),
+                                            _lib.ptr(self.part_ml[0]), B, c.num_heads, c.num_kv_heads, c.head_dim,
+                                            self.splits, scale, s), "decode_prefix_tc")
+            else:
+                _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_g_start), _lib.ptr(self.d_g_count),
+                               _lib.ptr(self.d_g_pages), self.max_pages, _lib.ptr(self.d_g_len), _lib.ptr(kc),
+                               _lib.ptr(vc), _lib.ptr(self.part_o[0]), _lib.ptr(self.part_ml[0]), B, c.num_heads,
+                               c.num_kv_heads, c.head_dim, self.splits, scale, s), "paged_decode(prefix)")
             _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_q_start), _lib.ptr(self.d_active), _lib.ptr(self.d_priv_table),
                            self.max_pages, _lib.ptr(self.d_priv_len), _lib.ptr(kc), _lib.ptr(vc),
                            _lib.ptr(self.part_o[1]), _lib.ptr(self.part_ml[1]), B, c.num_heads, c.num_kv_heads,
@@ -296,9 +312,12 @@ class SamplerEngine:
         x = torch.nn.functional.embedding(self.d_tokens[:B].long(), self.model.embed)
         stream = None
         attn = lambda li, q, k, v: self._decode_attention(li, q, B)
-        for li in range(c.num_layers):
-            x, stream = self._block(li, x, stream, positions, slots, attn)
-        h, _ = norm.rmsnorm(x, self.model.final_norm, c.rms_norm_eps, stream)
+        if self.split_k and not c.is_moe:
+            h = self._decode_layers_splitk(x, positions, slots, B)
+        else:
+            for li in range(c.num_layers):
+                x, stream = self._block(li, x, stream, positions, slots, attn)
+            h, _ = norm.rmsnorm(x, self.model.final_norm, c.rms_norm_eps, stream)
         logits = self.d_logits[:B]
         gemm.matmul_nt(h, self.model.output_weight, out=logits)
         _lib.check(_fn("sample")(_lib.ptr(logits), logits.stride(0), _lib.ptr(self.d_temp), B, c.vocab_size,
@@ -320,6 +339,47 @@ class SamplerEngine:
         self.d_len[:B] = torch.where(still, newlen, self.d_len[:B])
         self.d_priv_len[:B] += still.int()
         self.d_step += 1
+
+    def _norm_f32(self, acc: torch.Tensor, w: torch.Tensor, res: torch.Tensor):
+        """RMSNorm whose input is an fp32 split-K accumulator (reset to zero as it is read)."""
+        T, H = acc.shape
+        y = torch.empty((T, H), device=self.device, dtype=torch.bfloat16)
+        stream = torch.empty((T, H), device=self.device, dtype=torch.bfloat16)
+        _lib.check(_fn("norm32")(_lib.ptr(acc), _lib.ptr(res), _lib.ptr(w), _lib.ptr(y), _lib.ptr(stream), T, H,
+                                 self.cfg.rms_norm_eps, 0.0, _lib.stream_ptr()), "rmsnorm_f32in")
+        return y, stream
+
+    def _decode_layers_splitk(self, x: torch.Tensor, positions, slots, B: int) -> torch.Tensor:
+        """Decoder stack for one decode step.  The two projections with few output columns (o_proj, down_proj)
+        run as split-K GEMMs with fp32 ``red.add`` epilogues so that every SM streams weights; the norm that
+        follows reads the fp32 sums directly."""
+        c = self.cfg
+        H = c.hidden_size
+        acc_o, acc_d = self.acc_o[:B], self.acc_d[:B]
+        tiles = (H + 127) // 128
+        so = max(1, min(148 // tiles, (c.q_size + 63) // 64))
+        sd = max(1, min(148 // tiles, (c.intermediate_size + 63) // 64))
+        stream = None
+        for li in range(c.num_layers):
+            blk = self.model.blocks[li]
+            if li == 0:
+                h, stream = norm.rmsnorm(x, blk.ln1, c.rms_norm_eps, None)
+            else:
+                h, stream = self._norm_f32(acc_d, blk.ln1, stream)
+            qkv = gemm.matmul_nt(h, blk.wqkv)
+            q, k, v = norm.qknorm_rope(qkv, blk.q_norm, blk.k_norm, *self.model.rope(self.device), positions,
+                                       c.num_heads, c.num_kv_heads, c.head_dim, c.rms_norm_eps)
+            _lib.check(_fn("kvw")(_lib.ptr(k), k.stride(0), _lib.ptr(v), v.stride(0), _lib.ptr(slots),
+                                  _lib.ptr(self.kcache[li]), _lib.ptr(self.vcache[li]), B, c.num_kv_heads, c.head_dim,
+                                  _lib.stream_ptr()), "kv_cache_write")
+            a = self._decode_attention(li, q, B).reshape(B, -1)
+            gemm.gemm_raw(a, blk.wo, acc_o, M=B, N=H, K=c.q_size, epi=gemm.EPI_F32_ATOMIC, splits=so, bn=128)
+            h2, stream = self._norm_f32(acc_o, blk.ln2, stream)
+            _, act = gemm.gate_up_swiglu(h2, blk.wgu, keep_gu=False)
+            gemm.gemm_raw(act, blk.wdown, acc_d, M=B, N=H, K=c.intermediate_size, epi=gemm.EPI_F32_ATOMIC, splits=sd,
+                          bn=128)
+        h, _ = self._norm_f32(acc_d, self.model.final_norm, stream)
+        return h
 
     def _run_steps(self, B: int, n: int) -> None:
         if not self.use_cuda_graph or self.cfg.is_moe:

@@ -6,25 +6,27 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _engine(cascade, graph, max_batch=16):
+def _engine(cascade, graph, max_batch=16, **kw):
     from arctic_platform_b200.engine.sampler import SamplerEngine
     from arctic_platform_b200.models.config import PRESETS
     from arctic_platform_b200.models.decoder import DecoderLM
     cfg = PRESETS["qwen3-tiny-d128"]
     model = DecoderLM(cfg, "cuda", torch.bfloat16).init_weights(seed=5, std=0.05)
     eng = SamplerEngine(cfg, "cuda", model=model, kv_cache_tokens=1 << 14, max_batch=max_batch, max_seq_len=512,
-                        cascade=cascade, sync_interval=4, use_cuda_graph=graph)
+                        cascade=cascade, sync_interval=4, use_cuda_graph=graph, **kw)
     return cfg, model, eng
 
 
-@pytest.mark.parametrize("cascade,graph", [(False, False), (True, False), (True, True)])
-def test_generate_logprobs_match_scoring(cascade, graph):
+@pytest.mark.parametrize("cascade,graph,kw", [
+    (False, False, {"split_k": False}), (True, False, {"prefix_on_tensor_cores": False, "split_k": False}),
+    (True, False, {}), (True, True, {})])
+def test_generate_logprobs_match_scoring(cascade, graph, kw):
     """Greedy rollouts: every reported log-prob must equal the model's own log-prob of that token when the
     whole sequence is scored in one packed forward pass, and the token must be the arg-max there."""
     from arctic_platform_b200.models.decoder import token_logprobs
     from arctic_platform_b200.ops import _lib
     from arctic_platform_b200.rl.zorro_train.layout import build_packed_batch
-    cfg, model, eng = _engine(cascade, graph)
+    cfg, model, eng = _engine(cascade, graph, **kw)
     rng = np.random.default_rng(0)
     prompts = [rng.integers(1, cfg.vocab_size, size=n).tolist() for n in (37, 64, 5)]
     outs = eng.generate(prompts, {"n": 3, "temperature": 0.0, "max_tokens": 21})
