@@ -375,7 +375,9 @@ class SamplerEngine:
             a = self._decode_attention(li, q, B).reshape(B, -1)
             gemm.gemm_raw(a, blk.wo, acc_o, M=B, N=H, K=c.q_size, epi=gemm.EPI_F32_ATOMIC, splits=so, bn=128)
             h2, stream = self._norm_f32(acc_o, blk.ln2, stream)
-            _, act = gemm.gate_up_swiglu(h2, blk.wgu, keep_gu=False)
+            act = torch.empty((B, c.intermediate_size), device=self.device, dtype=torch.bfloat16)
+            gemm.gemm_raw(h2, blk.wgu, None, M=B, N=2 * c.intermediate_size, K=H, epi=gemm.EPI_SWIGLU, out2=act,
+                          bn=256 if B <= 128 else 0)
             gemm.gemm_raw(act, blk.wdown, acc_d, M=B, N=H, K=c.intermediate_size, epi=gemm.EPI_F32_ATOMIC, splits=sd,
                           bn=128)
         h, _ = self._norm_f32(acc_d, self.model.final_norm, stream)
