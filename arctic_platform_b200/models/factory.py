@@ -1,0 +1,181 @@
+"""Model specification, loader registry and patch pipeline.
+
+``ModelSpec`` -> ``build_model(spec)`` mirrors arctic_platform/model/{config,factory,loader,patch}.py in the
+reference (``ModelSpec``, ``register_loader``, ``resolve_loader_name``, ``LoadedModel``, ``PATCH_ORDER``), but
+the patches are *switches on a native model* rather than monkey patches of Hugging Face modules:
+
+* ``liger``        -> the fused RMSNorm / RoPE / SwiGLU kernels are always on for CUDA tensors (no-op here),
+* ``zorro_train``  -> recorded on the model (``model.zorro``) and consumed by the pipeline's layout builder,
+* ``gradient_checkpointing`` -> ``model.gradient_checkpointing = True``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from .config import DecoderConfig, resolve_config
+from .decoder import DecoderLM
+
+PATCH_ORDER = ("liger", "zorro_train", "gradient_checkpointing")
+
+
+@dataclass
+class ZorroTrainPatch:
+    response_len: int = 0
+    max_token_len: int = 0
+    rollout_n: int = 1
+    temperature: float = 1.0
+    use_unpad: bool = True
+    world_size: int = 1
+    logits_optimization: str = "memory"          # none | memory | compute (all map to the fused lm-head kernel)
+    logits_optimization_peak_mem_size_in_gib: float = 4.0
+    logits_compute_from_fp32_inputs: bool = False
+    logits_compute_in_fp32: bool = True
+
+    def __post_init__(self):
+        if self.logits_optimization not in ("none", "memory", "compute"):
+            raise ValueError(f"logits_optimization must be none|memory|compute, got {self.logits_optimization!r}")
+
+
+@dataclass
+class ParallelismConfig:
+    expert_parallel: int = 1
+    sequence_parallel: int = 1
+
+
+@dataclass
+class Patches:
+    liger: bool = True
+    zorro_train: Optional[ZorroTrainPatch] = None
+    gradient_checkpointing: bool = False
+
+
+@dataclass
+class ModelSpec:
+    model_path_or_name: str
+    dtype: str = "bfloat16"
+    attn_implementation: Optional[str] = None       # accepted for compatibility; attention is always the tcgen05 kernel
+    loader: Optional[str] = None
+    parallelism: ParallelismConfig = field(default_factory=ParallelismConfig)
+    patches: Patches = field(default_factory=Patches)
+    loader_options: Dict[str, Any] = field(default_factory=dict)
+
+    @staticmethod
+    def from_ds_worker_config(model_name: str, ds_worker_config: Optional[dict]) -> "ModelSpec":
+        """Bridge from the free-form worker config dict: gradient checkpointing defaults to on, ``zorro_train``
+        sub-dict becomes a :class:`ZorroTrainPatch`."""
+        wc = dict(ds_worker_config or {})
+        z = wc.get("zorro_train")
+        patches = Patches(liger=bool(wc.get("liger", True)),
+                          zorro_train=ZorroTrainPatch(**{k: v for k, v in z.items() if k != "enable"})
+                          if isinstance(z, dict) and z.get("enable", True) else None,
+                          gradient_checkpointing=bool(wc.get("gradient_checkpointing", True)))
+        par = ParallelismConfig(expert_parallel=int(wc.get("expert_parallel", 1)),
+                                sequence_parallel=int(wc.get("sequence_parallel", 1)))
+        return ModelSpec(model_name, dtype=wc.get("dtype", "bfloat16"), attn_implementation=wc.get("attn_implementation"),
+                         parallelism=par, patches=patches, loader_options=dict(wc.get("loader_options") or {}))
+
+
+@dataclass
+class LoaderContext:
+    spec: ModelSpec
+    _cfg: Optional[DecoderConfig] = None
+
+    @property
+    def hf_config(self) -> DecoderConfig:
+        if self._cfg is None:
+            self._cfg = resolve_config(self.spec.model_path_or_name)
+        return self._cfg
+
+
+@dataclass
+class LoadedModel:
+    model: DecoderLM
+    applied_patches: List[str] = field(default_factory=list)
+
+
+_LOADERS: Dict[str, Tuple[Callable, Optional[Callable], bool]] = {}
+
+
+def register_loader(name: str, matches: Optional[Callable[[LoaderContext], bool]] = None, default: bool = False):
+    def deco(fn):
+        _LOADERS[name] = (fn, matches, default)
+        return fn
+    return deco
+
+
+def resolve_loader_name(ctx: LoaderContext) -> str:
+    if ctx.spec.loader:
+        if ctx.spec.loader not in _LOADERS:
+            raise KeyError(f"unknown loader {ctx.spec.loader!r} (known: {sorted(_LOADERS)})")
+        return ctx.spec.loader
+    hits = [n for n, (_, m, _) in _LOADERS.items() if m is not None and m(ctx)]
+    if len(hits) == 1:
+        return hits[0]
+    if len(hits) > 1:
+        raise ValueError(f"several loaders match this model: {hits}; set ModelSpec.loader")
+    defaults = [n for n, (_, _, d) in _LOADERS.items() if d]
+    if not defaults:
+        raise ValueError("no loader matches and no default loader is registered")
+    return defaults[0]
+
+
+def _torch_dtype(name: str) -> torch.dtype:
+    return {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}[name]
+
+
+@register_loader("dense", default=True)
+def _load_dense(ctx: LoaderContext, device, seed: int) -> DecoderLM:
+    if ctx.spec.parallelism.expert_parallel > 1:
+        raise ValueError("the dense loader does not take expert_parallel > 1")
+    return _instantiate(ctx, device, seed)
+
+
+@register_loader("moe", matches=lambda c: c.hf_config.is_moe)
+def _load_moe(ctx: LoaderContext, device, seed: int) -> DecoderLM:
+    model = _instantiate(ctx, device, seed)
+    if ctx.spec.parallelism.expert_parallel > 1:
+        from ..parallel.expert_parallel import attach_expert_parallel
+        attach_expert_parallel(model, ctx.spec.parallelism.expert_parallel)
+    return model
+
+
+def _instantiate(ctx: LoaderContext, device, seed: int) -> DecoderLM:
+    from pathlib import Path
+    from .hf_io import load_hf_checkpoint
+    dev = torch.device(device)
+    dtype = _torch_dtype(ctx.spec.dtype) if dev.type == "cuda" else torch.float32
+    model = DecoderLM(ctx.hf_config, dev, dtype)
+    p = Path(ctx.spec.model_path_or_name)
+    if p.is_dir() and any(p.glob("*.safetensors")):
+        load_hf_checkpoint(model, p)
+    else:
+        model.init_weights(seed=seed)
+    return model
+
+
+def apply_patches(model: DecoderLM, patches: Patches) -> List[str]:
+    """Applies the enabled switches in ``PATCH_ORDER``; idempotent (a second call adds nothing)."""
+    done = list(getattr(model, "_applied_patches", []))
+    for name in PATCH_ORDER:
+        if name in done:
+            continue
+        if name == "liger" and patches.liger:
+            done.append(name)
+        elif name == "zorro_train" and patches.zorro_train is not None:
+            model.zorro = patches.zorro_train
+            done.append(name)
+        elif name == "gradient_checkpointing" and patches.gradient_checkpointing:
+            model.gradient_checkpointing = True
+            done.append(name)
+    model._applied_patches = done
+    return done
+
+
+def build_model(spec: ModelSpec, parallel_groups: Optional[dict] = None, device="cpu", seed: int = 42) -> LoadedModel:
+    ctx = LoaderContext(spec)
+    fn, _, _ = _LOADERS[resolve_loader_name(ctx)]
+    model = fn(ctx, device, seed)
+    return LoadedModel(model, apply_patches(model, spec.patches))

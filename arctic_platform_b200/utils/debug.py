@@ -1,0 +1,205 @@
+"""Debug and profiling helpers: memory reports, rank-filtered printing, synchronised timers, a profiler
+context and full-determinism switch (arctic_platform/common/utils/debug.py:56-483 in the reference)."""
+from __future__ import annotations
+
+import contextlib
+import cProfile
+import fcntl
+import gc
+import io
+import os
+import pstats
+import random
+import time
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+DISABLE_DEBUG = os.environ.get("APB_DEBUG", "0") != "1"
+
+
+def get_mem_metrics() -> Dict[str, float]:
+    """Torch allocator, device (NVML via torch) and host RSS figures in GiB."""
+    out: Dict[str, float] = {}
+    if torch.cuda.is_available():
+        gib = 2 ** 30
+        out["torch_allocated_gib"] = torch.cuda.memory_allocated() / gib
+        out["torch_max_allocated_gib"] = torch.cuda.max_memory_allocated() / gib
+        out["torch_reserved_gib"] = torch.cuda.memory_reserved() / gib
+        free, total = torch.cuda.mem_get_info()
+        out["device_used_gib"] = (total - free) / gib
+        out["device_total_gib"] = total / gib
+    try:
+        import psutil
+        out["host_rss_gib"] = psutil.Process().memory_info().rss / 2 ** 30
+    except Exception:
+        pass
+    return out
+
+
+def see_memory_usage(message: str, force: bool = False, ranks=(0,)) -> Optional[Dict[str, float]]:
+    if DISABLE_DEBUG and not force:
+        return None
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    if ranks is not None and rank not in ranks:
+        return None
+    gc.collect()
+    m = get_mem_metrics()
+    print(f"[mem][rank {rank}] {message}: " + " ".join(f"{k}={v:.2f}" for k, v in m.items()), flush=True)
+    return m
+
+
+def printflock(*args, **kwargs) -> None:
+    """print() under an exclusive file lock so lines of concurrent ranks do not interleave."""
+    with open(__file__, "r") as fh:
+        fcntl.flock(fh, fcntl.LOCK_EX)
+        try:
+            print(*args, **kwargs, flush=True)
+        finally:
+            fcntl.flock(fh, fcntl.LOCK_UN)
+
+
+def pr(*args, force: bool = False, **kwargs) -> None:
+    if DISABLE_DEBUG and not force:
+        return
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    printflock(f"[{rank}]", *args, **kwargs)
+
+
+def pr0(*args, force: bool = False, **kwargs) -> None:
+    if (dist.get_rank() if dist.is_initialized() else 0) == 0:
+        pr(*args, force=force, **kwargs)
+
+
+def debug_gathered_tensor(t: torch.Tensor, name: str = "", group=None) -> Dict[str, float]:
+    """Norm / min / max of a tensor, all-reduced so every rank reports the same numbers."""
+    stats = torch.tensor([t.float().pow(2).sum(), t.float().min(), -t.float().max()], dtype=torch.float64,
+                         device=t.device)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        sq = stats[:1].clone()
+        dist.all_reduce(sq, group=group)
+        mm = stats[1:].clone()
+        dist.all_reduce(mm, op=dist.ReduceOp.MIN, group=group)
+        stats = torch.cat([sq, mm])
+    out = {"norm": float(stats[0].sqrt()), "min": float(stats[1]), "max": float(-stats[2])}
+    pr0(f"{name}: {out}")
+    return out
+
+
+class SynchronizedWallClockTimer:
+    """Named timers that synchronise the device around start/stop so wall time brackets GPU work."""
+
+    def __init__(self, enabled: bool = True):
+        self.enabled = enabled
+        self._start: Dict[str, float] = {}
+        self.elapsed_ms: Dict[str, float] = {}
+        self.counts: Dict[str, int] = {}
+
+    @staticmethod
+    def _sync() -> None:
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+
+    def start(self, name: str) -> str:
+        if self.enabled:
+            self._sync()
+            self._start[name] = time.perf_counter()
+        return name
+
+    def stop(self, name: str) -> float:
+        if not self.enabled or name not in self._start:
+            return 0.0
+        self._sync()
+        ms = (time.perf_counter() - self._start.pop(name)) * 1e3
+        self.elapsed_ms[name] = self.elapsed_ms.get(name, 0.0) + ms
+        self.counts[name] = self.counts.get(name, 0) + 1
+        return ms
+
+    def stop_and_print_elapsed(self, name: str) -> float:
+        ms = self.stop(name)
+        if self.enabled:
+            pr0(f"{name}: {ms:.2f} ms", force=True)
+        return ms
+
+    def summary(self, reset: bool = False) -> Dict[str, float]:
+        out = dict(self.elapsed_ms)
+        if reset:
+            self.elapsed_ms.clear()
+            self.counts.clear()
+        return out
+
+
+class SynchronizedWallClockTimerDummy:
+    """Drop-in no-op used when timers are switched off."""
+
+    def __getattr__(self, _name):
+        return lambda *a, **k: 0.0
+
+
+@contextlib.contextmanager
+def nvtx_range(name: str, enabled: bool = True):
+    on = enabled and torch.cuda.is_available()
+    if on:
+        torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        if on:
+            torch.cuda.nvtx.range_pop()
+
+
+class ProfilerContext:
+    """``type="torch"`` -> torch.profiler (CPU + CUDA activities, trace written to ``out_dir``),
+    ``type="c"`` -> cProfile (top functions printed on exit), ``type="none"`` -> nothing."""
+
+    def __init__(self, type: str = "none", out_dir: str = "/tmp/apb-prof", name: str = "trace", top: int = 30):
+        if type not in ("none", "c", "torch"):
+            raise ValueError(f"unknown profiler type {type!r}")
+        self.type, self.out_dir, self.name, self.top = type, out_dir, name, top
+        self._prof = None
+        self.report: Optional[str] = None
+
+    def __enter__(self):
+        if self.type == "c":
+            self._prof = cProfile.Profile()
+            self._prof.enable()
+        elif self.type == "torch":
+            acts = [torch.profiler.ProfilerActivity.CPU]
+            if torch.cuda.is_available():
+                acts.append(torch.profiler.ProfilerActivity.CUDA)
+            self._prof = torch.profiler.profile(activities=acts, with_stack=True)
+            self._prof.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self.type == "c":
+            self._prof.disable()
+            buf = io.StringIO()
+            pstats.Stats(self._prof, stream=buf).sort_stats("cumulative").print_stats(self.top)
+            self.report = buf.getvalue()
+        elif self.type == "torch":
+            self._prof.__exit__(*exc)
+            os.makedirs(self.out_dir, exist_ok=True)
+            path = os.path.join(self.out_dir, f"{self.name}.json")
+            self._prof.export_chrome_trace(path)
+            self.report = path
+        return False
+
+
+def enable_full_determinism(seed: int, warn_only: bool = True) -> None:
+    """Seeds every RNG and switches PyTorch to deterministic algorithms."""
+    random.seed(seed)
+    try:
+        import numpy as np
+        np.random.seed(seed)
+    except Exception:
+        pass
+    torch.manual_seed(seed)
+    if torch.cuda.is_available():
+        torch.cuda.manual_seed_all(seed)
+    os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+    os.environ["PYTHONHASHSEED"] = str(seed)
+    torch.use_deterministic_algorithms(True, warn_only=warn_only)
+    torch.backends.cudnn.deterministic = True
+    torch.backends.cudnn.benchmark = False

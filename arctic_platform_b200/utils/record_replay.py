@@ -1,0 +1,73 @@
+"""Deterministic rollout record / replay for reproducing a failing training step without the sampler.
+
+``@record_replay_generation`` wraps an async or sync ``generate``-like function.  Controlled by
+``REPLAY_GENERATION_DIR`` (where the tape lives), ``REPLAY_GENERATION_MODE`` (``record`` | ``replay`` | unset)
+and ``REPLAY_START_RECORD`` (first call index to put on tape); call ``i`` is stored as ``generate-{i}.json``.
+Same switches as arctic_platform/common/utils/record_replay.py:26-183, with a JSON tape instead of pickle so a
+tape is never executed on load."""
+from __future__ import annotations
+
+import asyncio
+import functools
+import json
+import os
+from pathlib import Path
+from typing import Any, Callable
+
+
+class ReplayMiss(RuntimeError):
+    pass
+
+
+def _settings():
+    d = os.environ.get("REPLAY_GENERATION_DIR")
+    mode = os.environ.get("REPLAY_GENERATION_MODE", "")
+    if os.environ.get("REPLAY_GENERATION") == "1" and not mode:
+        mode = "replay"
+    start = int(os.environ.get("REPLAY_START_RECORD", "0") or 0)
+    return (Path(d) if d else None), mode, start
+
+
+def record_replay_generation(fn: Callable) -> Callable:
+    counter = {"i": 0}
+
+    def _path(d: Path, i: int) -> Path:
+        return d / f"generate-{i}.json"
+
+    def _before(args, kwargs):
+        d, mode, start = _settings()
+        i = counter["i"]
+        counter["i"] += 1
+        if d is None or mode not in ("record", "replay"):
+            return None, None, i
+        if mode == "replay":
+            p = _path(d, i)
+            if not p.exists():
+                raise ReplayMiss(f"no recorded generation for call {i} under {d}")
+            return json.loads(p.read_text())["result"], None, i
+        return None, (d if i >= start else None), i
+
+    def _after(d, i, result):
+        if d is not None:
+            d.mkdir(parents=True, exist_ok=True)
+            _path(d, i).write_text(json.dumps({"call": i, "result": result}))
+        return result
+
+    if asyncio.iscoroutinefunction(fn):
+        @functools.wraps(fn)
+        async def awrapper(*args, **kwargs):
+            replayed, d, i = _before(args, kwargs)
+            if replayed is not None:
+                return replayed
+            return _after(d, i, await fn(*args, **kwargs))
+        awrapper._replay_counter = counter
+        return awrapper
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        replayed, d, i = _before(args, kwargs)
+        if replayed is not None:
+            return replayed
+        return _after(d, i, fn(*args, **kwargs))
+    wrapper._replay_counter = counter
+    return wrapper
