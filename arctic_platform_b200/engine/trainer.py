@@ -173,7 +173,7 @@ class TrainEngine:
             u.length = _round_up(cur - off, 8 * W)
             off += u.length
         self.total = off
-        use_symm = self.impl == "fused" and W > 1
+        use_symm = self.impl == "fused" and W > 1 and not self.forward_only
         self.param_buf = (SymmetricBuffer(self.total, self.param_dtype, self.device, self.group) if use_symm
                           else SymmetricBuffer(self.total, self.param_dtype, self.device, False))
         flat = self.param_buf.tensor
