@@ -63,7 +63,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const int* __restrict__
   const int p0 = split * per, p1 = min(n_pages, p0 + per);
 
   __shared__ float q_s[R][D];
-  __shared__ float p_s[4][R][kPage];
+  __shared__ __align__(16) float p_s[4][R][kPage];
   __shared__ float red_m[4][R], red_l[4][R];
   __shared__ float red_o[4][R][D];
 
@@ -153,16 +153,23 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const int* __restrict__
       }
       __syncwarp();
 #pragma unroll
-      for (int t = 0; t < kPage; ++t) {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vreg[t].x));
-        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vreg[t].y));
+      for (int t4 = 0; t4 < kPage / 4; ++t4) {
+        float4 pw4[R];  // probabilities of four tokens per head, one 16-byte shared load each
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          const float pw = p_s[warp][r][t];
-          acc[r][0] += pw * a.x;
-          acc[r][1] += pw * a.y;
-          acc[r][2] += pw * b.x;
-          acc[r][3] += pw * b.y;
+        for (int r = 0; r < R; ++r) pw4[r] = *reinterpret_cast<const float4*>(&p_s[warp][r][t4 * 4]);
+#pragma unroll
+        for (int tt = 0; tt < 4; ++tt) {
+          const int t = t4 * 4 + tt;
+          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vreg[t].x));
+          const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vreg[t].y));
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            const float pw = tt == 0 ? pw4[r].x : tt == 1 ? pw4[r].y : tt == 2 ? pw4[r].z : pw4[r].w;
+            acc[r][0] += pw * a.x;
+            acc[r][1] += pw * a.y;
+            acc[r][2] += pw * b.x;
+            acc[r][3] += pw * b.y;
+          }
         }
       }
       __syncwarp();

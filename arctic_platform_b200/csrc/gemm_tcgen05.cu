@@ -15,6 +15,7 @@
 // keeps them on cuBLAS).
 #include "common.cuh"
 #include "host_utils.cuh"
+#include "peer.cuh"
 
 namespace apb {
 
@@ -26,6 +27,13 @@ enum GemmEpilogue : int {
   kEpiSwiGLU = 4,      // columns interleaved (gate, up): C2(bf16)[m, n/2] = silu(g) * u; C(bf16) = acc if C != null
   kEpiLogprobPartial = 5,  // per row and 128-column tile: (max, sum exp, sum exp*z, label z) of z = acc*alpha*row_scale
   kEpiDlogits = 6,         // C(bf16) = d loss / d acc for log-prob / entropy heads (see lm-head section below)
+  kEpiF32AtomicPeer = 7,   // GEMM -> reduce-scatter: red.add of the partial row into the fp32 buffer of the rank
+                           // that owns the row (owner = row / rows_per_rank), over its NVLink peer mapping
+  kEpiBf16ScatterPeer = 8, // GEMM -> all-to-all: bf16 row stored to (peer, row) = row_map[m] (MoE combine)
+};
+
+struct PeerTensorMaps {
+  CUtensorMap m[8];
 };
 
 struct GemmParams {
@@ -51,6 +59,12 @@ struct GemmParams {
   const float* row_ent;    // [M] entropy
   const float* row_glp;    // [M] upstream gradient of the log-prob
   const float* row_gent;   // [M] upstream gradient of the entropy, or null
+  // peer-aware modes
+  void* c_peers[8];        // per-rank output base pointers (symmetric buffers)
+  int rows_per_rank;       // kEpiF32AtomicPeer: rows owned by each rank
+  const int2* row_map;     // kEpiBf16ScatterPeer: (rank, destination row) per output row, rank < 0 = drop
+  int a_peer_rows;         // > 0: A is row-sharded over ranks, this many rows each, read through per-rank maps
+  int world;
 };
 
 constexpr int kBM = 128;
@@ -70,9 +84,8 @@ struct GemmCfg {
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 
 template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const GemmParams p) {
+__device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtensorMap& tma_b,
+                                          const CUtensorMap* a_peer_maps, const GemmParams& p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -161,7 +174,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
           mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
-          if (!p.a_mn) {
+          if (a_peer_maps != nullptr && p.a_peer_rows > 0) {
+            // all-gather fused into the operand fetch: each slab of the A tile comes from the rank that owns
+            // those rows, by a plain (non-multicast) TMA load from its peer mapping
+            const int br = min(kBM, p.a_peer_rows);
+            for (int i = 0; i < kBM / br; ++i) {
+              const int row = m0 + i * br;
+              const int peer = min(row / p.a_peer_rows, p.world - 1);
+              tma_load_2d(sa + i * br * 128, &a_peer_maps[peer], &full_bar[stage], kb * kBK,
+                          row - peer * p.a_peer_rows);
+            }
+          } else if (!p.a_mn) {
             tma_load_2d(sa, &tma_a, &full_bar[stage], kb * kBK, m0);
           } else {
 #pragma unroll
@@ -399,6 +422,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               *reinterpret_cast<float4*>(dst + q * 4) = o;
             }
           }
+        } else if (p.epi == kEpiF32AtomicPeer) {
+          const int owner = min(row / p.rows_per_rank, p.world - 1);
+          float* dst = static_cast<float*>(p.c_peers[owner]) +
+                       static_cast<long long>(row - owner * p.rows_per_rank) * p.ldc + col0;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            if (col0 + q * 4 < p.N)
+              atomicAdd(reinterpret_cast<float4*>(dst + q * 4),
+                        make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
+          }
+        } else if (p.epi == kEpiBf16ScatterPeer) {
+          const int2 to = p.row_map[row];
+          if (to.x >= 0) {
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c_peers[to.x]) + static_cast<long long>(to.y) * p.ldc + col0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (col0 + q * 8 < p.N) {
+                uint4 o;
+                o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
+                o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
+                o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
+                o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
+                *reinterpret_cast<uint4*>(dst + q * 8) = o;
+              }
+            }
+          }
         } else if (p.epi == kEpiF32Atomic) {
           float* dst = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
 #pragma unroll
@@ -422,6 +471,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                 const GemmParams p) {
+  gemm_body<BN>(tma_a, tma_b, nullptr, p);
+}
+
+// Variant whose A operand is gathered from the other ranks' memory tile by tile (all-gather -> GEMM).
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_ag_kernel(const __grid_constant__ PeerTensorMaps a_maps, const __grid_constant__ CUtensorMap tma_b,
+                    const GemmParams p) {
+  gemm_body<BN>(a_maps.m[0], tma_b, a_maps.m, p);
 }
 
 }  // namespace apb
