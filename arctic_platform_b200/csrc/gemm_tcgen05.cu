@@ -776,3 +776,166 @@ extern "C" int apb_lmhead_logprob_fwd_noalloc(const void* hidden, const void* we
                                                   lp, ent, lse, M);
   return static_cast<int>(cudaGetLastError());
 }
+
+// ---------------------------------------------------------------------------
+// Tensor-parallel fused GEMM + collective entry points
+// ---------------------------------------------------------------------------
+namespace apb {
+
+// After a GEMM -> reduce-scatter: wait until every rank has finished adding into this rank's fp32 slice,
+// then convert the slice to bf16 and clear it for its next use.
+__global__ void __launch_bounds__(256)
+tp_finalize_kernel(PeerPtrs flags, int rank, int world, int epoch, float* __restrict__ acc,
+                   __nv_bfloat16* __restrict__ out, long long n, int* status) {
+  if (!epoch_barrier(flags, rank, world, epoch, status)) return;
+  const long long n8 = n >> 3;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4* a = reinterpret_cast<float4*>(acc + i * 8);
+    const float4 x = a[0], y = a[1];
+    uint4 o;
+    o.x = pack_bf16x2(x.x, x.y);
+    o.y = pack_bf16x2(x.z, x.w);
+    o.z = pack_bf16x2(y.x, y.y);
+    o.w = pack_bf16x2(y.z, y.w);
+    *reinterpret_cast<uint4*>(out + i * 8) = o;
+    a[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    a[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+template <int BN>
+static int launch_gemm_ag(const PeerTensorMaps& maps, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_ag_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured[dev & 63] = true;
+  }
+  const long long total = static_cast<long long>((p.M + kBM - 1) / kBM) * ((p.N + BN - 1) / BN);
+  const int grid = static_cast<int>(total < sm_count() ? total : sm_count());
+  gemm_bf16_ag_kernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(maps, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace apb
+
+extern "C" {
+
+// All-gather -> GEMM.  The activation is row-sharded: rank r holds rows [r*rows, (r+1)*rows) of A in its own
+// buffer a_ptrs[r] ([rows, K] bf16, row stride lda, all mapped into this process).  Computes
+// C[M = world*rows, N] = A_full @ B[N,K]^T on this rank; every A tile is fetched from its owner's memory by
+// plain TMA loads while earlier tiles are multiplied.  The caller orders this launch after the peers' writes
+// (apb_epoch_wait).  rows must be a multiple of 8 and either >= 128 with rows % 128 == 0, or a divisor of 128.
+int apb_gemm_ag(void* const* a_ptrs, int world, int rows, const void* B, void* C, int N, int K, long long lda,
+                long long ldb, long long ldc, int bn, cudaStream_t stream) {
+  using namespace apb;
+  if (world < 1 || world > 8 || rows <= 0 || (rows % 8)) return kBadArgument;
+  if (rows >= kBM ? (rows % kBM) : (kBM % rows)) return kBadArgument;
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8)) return kBadArgument;
+  PeerTensorMaps maps;
+  const int br = rows < kBM ? rows : kBM;
+  for (int r = 0; r < 8; ++r) {
+    const int src = r < world ? r : 0;
+    int rc = make_tmap_2d(&maps.m[r], a_ptrs[src], 2, rows, K, lda, 64, br);
+    if (rc) return 1000 + rc;
+  }
+  if (bn == 0) bn = 128;
+  if (bn != 64 && bn != 128 && bn != 256) return kBadArgument;
+  CUtensorMap tb;
+  int rc = make_tmap_2d(&tb, B, 2, N, K, ldb, 64, bn);
+  if (rc) return 2000 + rc;
+  GemmParams p{};
+  p.M = world * rows;
+  p.N = N;
+  p.K = K;
+  p.epi = kEpiBf16;
+  p.splits = 1;
+  p.C = C;
+  p.ldc = ldc;
+  p.alpha = 1.f;
+  p.status = status_device_ptr();
+  p.a_peer_rows = rows;
+  p.world = world;
+  if (bn == 64) return launch_gemm_ag<64>(maps, tb, p, stream);
+  return bn == 256 ? launch_gemm_ag<256>(maps, tb, p, stream) : launch_gemm_ag<128>(maps, tb, p, stream);
+}
+
+// GEMM -> reduce-scatter.  Every rank computes its partial P = A[M,K_local] @ B[N,K_local]^T and adds each
+// row into the fp32 accumulator of the rank that owns it (acc_ptrs[r]: [M/world, N] fp32, zero on entry),
+// straight from the GEMM epilogue over the NVLink peer mappings.  Follow with apb_tp_finalize.
+int apb_gemm_rs(const void* A, const void* B, void* const* acc_ptrs, int world, int M, int N, int K, long long lda,
+                long long ldb, long long ld_acc, int bn, cudaStream_t stream) {
+  using namespace apb;
+  if (world < 1 || world > 8 || M % world || (lda % 8) || (ldb % 8) || (ld_acc % 4) || (N % 8)) return kBadArgument;
+  if (bn == 0) bn = 128;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, A, 2, M, K, lda, 64, kBM);
+  if (rc) return 1000 + rc;
+  rc = make_tmap_2d(&tb, B, 2, N, K, ldb, 64, bn);
+  if (rc) return 2000 + rc;
+  GemmParams p{};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.epi = kEpiF32AtomicPeer;
+  p.splits = 1;
+  p.ldc = ld_acc;
+  p.alpha = 1.f;
+  p.status = status_device_ptr();
+  p.rows_per_rank = M / world;
+  p.world = world;
+  for (int r = 0; r < 8; ++r) p.c_peers[r] = r < world ? acc_ptrs[r] : nullptr;
+  if (bn == 64) return launch_gemm<64>(ta, tb, p, 0, stream);
+  return bn == 256 ? launch_gemm<256>(ta, tb, p, 0, stream) : launch_gemm<128>(ta, tb, p, 0, stream);
+}
+
+// Grouped GEMM whose output rows are scattered to other ranks: row m of the result goes to
+// out_ptrs[row_map[m].x] + row_map[m].y * ldc (bf16).  Used as the fused "expert GEMM 2 + combine" of
+// expert-parallel MoE.  tile_map as in apb_gemm_bf16.
+int apb_gemm_scatter(const void* A, const void* B, void* const* out_ptrs, int world, const void* row_map, int M, int N,
+                     int K, long long lda, long long ldb, long long ldc, const void* tile_map, int num_map_tiles,
+                     long long b_rows, cudaStream_t stream) {
+  using namespace apb;
+  if (M <= 0) return 0;
+  if (world < 1 || world > 8 || (lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8)) return kBadArgument;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_2d(&ta, A, 2, M, K, lda, 64, kBM);
+  if (rc) return 1000 + rc;
+  rc = make_tmap_2d(&tb, B, 2, b_rows > 0 ? b_rows : N, K, ldb, 64, 128);
+  if (rc) return 2000 + rc;
+  GemmParams p{};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.epi = kEpiBf16ScatterPeer;
+  p.splits = 1;
+  p.ldc = ldc;
+  p.alpha = 1.f;
+  p.tile_map = static_cast<const int4*>(tile_map);
+  p.num_map_tiles = num_map_tiles;
+  p.status = status_device_ptr();
+  p.row_map = static_cast<const int2*>(row_map);
+  p.world = world;
+  for (int r = 0; r < 8; ++r) p.c_peers[r] = r < world ? out_ptrs[r] : nullptr;
+  return launch_gemm<128>(ta, tb, p, 0, stream);
+}
+
+int apb_tp_finalize(void* const* flag_ptrs, int rank, int world, int epoch, float* acc, void* out, long long n,
+                    cudaStream_t stream) {
+  using namespace apb;
+  if (world > kMaxRanks || (n % 8)) return kBadArgument;
+  if (n <= 0) return 0;
+  PeerPtrs f;
+  for (int i = 0; i < kMaxRanks; ++i) f.p[i] = i < world ? flag_ptrs[i] : nullptr;
+  long long g = (n / 8 + 255) / 256;
+  const int grid = static_cast<int>(g < 1 ? 1 : (g < 148 * 8 ? g : 148 * 8));
+  tp_finalize_kernel<<<grid, 256, 0, stream>>>(f, rank, world, epoch, acc, static_cast<__nv_bfloat16*>(out), n,
+                                               status_device_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+}

@@ -374,3 +374,50 @@ int apb_quant_fp8_block128(const void* w, long long ldw, int rows, int cols, voi
   return static_cast<int>(cudaGetLastError());
 }
 }
+
+// ---------------------------------------------------------------------------
+// Expert-parallel dispatch / return: rows moved between ranks by P2P stores
+// ---------------------------------------------------------------------------
+namespace apb {
+
+// For every routed pair e: copy row src[src_row[e]] (H bf16) into dst_ptrs[dst_rank[e]] at row dst_row[e]
+// and, when meta_ptrs is given, write (this rank, tag[e]) beside it so the receiver can send the result back.
+// One warp per pair.  dst_rank[e] < 0 skips the pair.
+__global__ void __launch_bounds__(256)
+ep_scatter_rows_kernel(const __nv_bfloat16* __restrict__ src, long long ld_src, const int* __restrict__ src_row,
+                       const int* __restrict__ dst_rank, const int* __restrict__ dst_row, const int* __restrict__ tag,
+                       PeerPtrs dst_ptrs, long long ld_dst, PeerPtrs meta_ptrs, int rank, int n_pairs, int H) {
+  const int lane = threadIdx.x & 31;
+  const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long e = wid; e < n_pairs; e += nw) {
+    const int dr = dst_rank[e];
+    if (dr < 0) continue;
+    const __nv_bfloat16* s = src + static_cast<long long>(src_row[e]) * ld_src;
+    __nv_bfloat16* d = static_cast<__nv_bfloat16*>(dst_ptrs.p[dr]) + static_cast<long long>(dst_row[e]) * ld_dst;
+    for (int i = lane * 8; i < H; i += 256) *reinterpret_cast<uint4*>(d + i) = *reinterpret_cast<const uint4*>(s + i);
+    if (meta_ptrs.p[dr] != nullptr && lane == 0)
+      static_cast<int2*>(meta_ptrs.p[dr])[dst_row[e]] = make_int2(rank, tag ? tag[e] : static_cast<int>(e));
+  }
+}
+
+}  // namespace apb
+
+extern "C" {
+
+// dst_ptrs / meta_ptrs: per-rank base pointers (meta may be null).  H % 8 == 0.
+int apb_ep_scatter_rows(const void* src, long long ld_src, const int* src_row, const int* dst_rank, const int* dst_row,
+                        const int* tag, void* const* dst_ptrs, long long ld_dst, void* const* meta_ptrs, int rank,
+                        int world, int n_pairs, int H, cudaStream_t s) {
+  using namespace apb;
+  if (n_pairs <= 0) return 0;
+  if (world > kMaxRanks || (H % 8) || (ld_src % 8) || (ld_dst % 8)) return kBadArgument;
+  PeerPtrs meta;
+  for (int i = 0; i < kMaxRanks; ++i) meta.p[i] = (meta_ptrs && i < world) ? meta_ptrs[i] : nullptr;
+  const long long g = (static_cast<long long>(n_pairs) * 32 + 255) / 256;
+  const int grid = static_cast<int>(g < 148 * 16 ? g : 148 * 16);
+  ep_scatter_rows_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src), ld_src, src_row, dst_rank, dst_row,
+                                              tag, to_peers(dst_ptrs, world), ld_dst, meta, rank, n_pairs, H);
+  return static_cast<int>(cudaGetLastError());
+}
+}

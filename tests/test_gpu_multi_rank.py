@@ -68,3 +68,93 @@ def test_fused_step_matches_collectives_on_two_gpus():
     assert all(abs(a - b) <= 2e-2 * abs(b) + 1e-4 for a, b in zip(nf, nc)), (nf, nc)
     assert (r0["fused"][1] - r0["collective"][1]).abs().max() < 5e-3
     assert (r0["fused"][0] - r0["collective"][0]).abs().max() < 2e-2
+
+
+def _tp_ep_main(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from arctic_platform_b200.models.config import PRESETS
+        from arctic_platform_b200.models.moe import MoEFeedForward
+        from arctic_platform_b200.ops import _lib
+        from arctic_platform_b200.parallel import tensor_parallel as tp
+        from arctic_platform_b200.parallel.expert_parallel import ExpertParallel
+        dev = torch.device("cuda", rank)
+        res = {}
+        # ---- tensor parallel: all-gather -> GEMM and GEMM -> reduce-scatter fused kernels vs NCCL + matmul
+        ctx = tp.TPContext(dev, None, max_rows=512, max_cols=4096)
+        g = torch.Generator(device="cuda").manual_seed(5)
+        for rows in (64, 256):
+            K, N = 512, 768
+            x_full = torch.randn(world * rows, K, device=dev, generator=g).bfloat16()
+            w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+            x_local = x_full[rank * rows:(rank + 1) * rows].contiguous()
+            for _ in range(2):                                   # twice: buffers and epochs are reused
+                got = tp.ag_gemm(ctx, x_local, w)
+            ref = tp.ag_gemm_collective(x_local, w)
+            res[f"ag{rows}"] = float((got.float() - ref.float()).abs().max())
+            M = world * rows
+            xk = torch.randn(M, K, device=dev, generator=torch.Generator(device="cuda").manual_seed(7 + rank)).bfloat16()
+            for _ in range(3):
+                got = tp.gemm_rs(ctx, xk, w)
+            ref = tp.gemm_rs_collective(xk, w)
+            res[f"rs{rows}"] = float((got.float() - ref.float()).abs().max())
+            res[f"rs{rows}_scale"] = float(ref.float().abs().max())
+        # ---- expert parallel: fused dispatch/combine (training path and fused-epilogue inference path)
+        cfg = PRESETS["qwen3-moe-tiny"]
+        torch.manual_seed(0)
+        full = MoEFeedForward(cfg, dev, torch.bfloat16)
+        with torch.no_grad():
+            for p in full.parameters():
+                p.normal_(0, 0.05)
+        El = cfg.num_experts // world
+        ep_moe = MoEFeedForward(cfg, dev, torch.bfloat16)
+        with torch.no_grad():
+            ep_moe.router.copy_(full.router)
+            ep_moe.wgu = torch.nn.Parameter(full.wgu.data[rank * El:(rank + 1) * El].clone())
+            ep_moe.wdown = torch.nn.Parameter(full.wdown.data[rank * El:(rank + 1) * El].clone())
+        ep_moe.ep = ExpertParallel(cfg.hidden_size, cfg.num_experts, None, dev, max_recv_rows=4096, max_pairs=4096)
+        x = torch.randn(300 + 40 * rank, cfg.hidden_size, device=dev,
+                        generator=torch.Generator(device="cuda").manual_seed(20 + rank)).bfloat16()
+        gy = torch.randn_like(x)
+        x1 = x.clone().requires_grad_()
+        y_ep = ep_moe(x1)
+        y_ep.backward(gy)
+        x2 = x.clone().requires_grad_()
+        y_full = full(x2)
+        y_full.backward(gy)
+        with torch.no_grad():
+            y_inf = ep_moe(x)                                      # GEMM-2 epilogue scatters to the source ranks
+        res["ep_y"] = float((y_ep.float() - y_full.float()).abs().max())
+        res["ep_inf"] = float((y_inf.float() - y_full.float()).abs().max())
+        res["ep_dx"] = float((x1.grad.float() - x2.grad.float()).abs().max())
+        res["ep_scale"] = float(y_full.float().abs().max())
+        # expert weight gradients: this rank's shard must equal the sum over ranks of the full model's gradient
+        gfull = full.wdown.grad.float().clone()
+        dist.all_reduce(gfull)
+        res["ep_dw"] = float((ep_moe.wdown.grad.float() - gfull[rank * El:(rank + 1) * El]).abs().max())
+        res["ep_dw_scale"] = float(gfull.abs().max())
+        _lib.check_status("tp/ep")
+        torch.save(res, os.path.join(out_dir, f"t{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_tensor_parallel_and_expert_parallel_fused_kernels():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_tp_ep_main, args=(2, _free_port(), d), nprocs=2, join=True)
+        res = [torch.load(os.path.join(d, f"t{r}.pt"), weights_only=False) for r in range(2)]
+    for r in res:
+        for rows in (64, 256):
+            assert r[f"ag{rows}"] < 0.05, r
+            assert r[f"rs{rows}"] < 0.02 * r[f"rs{rows}_scale"] + 0.05, r
+        assert r["ep_y"] < 0.03 * r["ep_scale"] + 0.02, r
+        assert r["ep_inf"] < 0.03 * r["ep_scale"] + 0.02, r
+        assert r["ep_dx"] < 0.05, r
+        assert r["ep_dw"] < 0.03 * r["ep_dw_scale"] + 0.02, r
