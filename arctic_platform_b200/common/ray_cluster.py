@@ -1,0 +1,95 @@
+"""Ray cluster bring-up for the Ray protocol (arctic_platform/common/ray_cluster.py:88-270 in the reference).
+
+``init_ray_cluster(auto_attach)`` attaches to a running Ray cluster only if it has GPUs; otherwise it starts a
+head node on free ports with a private temp dir, fans ``ray start --address`` out to the peers listed in
+``/job/hostfile`` (via ``pdsh`` when present) and registers an ``atexit`` hook that stops only the cluster it
+started.  Ray is optional in this build: without it the function reports ``{"ray": False}`` and the clients
+fall back to in-process / spawned actors.
+"""
+from __future__ import annotations
+
+import atexit
+import os
+import shutil
+import socket
+import subprocess
+import tempfile
+import uuid
+from typing import Dict, List, Optional
+
+from ..rl.config import primary_ip  # noqa: F401  (re-exported for callers of the reference API)
+
+_started: Dict[str, Optional[str]] = {"temp_dir": None}
+
+
+def free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("", 0))
+        return s.getsockname()[1]
+
+
+def read_hostfile(path: str = "/job/hostfile") -> List[str]:
+    if not os.path.exists(path):
+        return []
+    hosts = []
+    for line in open(path):
+        line = line.strip()
+        if line and not line.startswith("#"):
+            hosts.append(line.split()[0])
+    return hosts
+
+
+def ray_available() -> bool:
+    try:
+        import ray  # noqa: F401
+        return True
+    except Exception:
+        return False
+
+
+def init_ray_cluster(auto_attach: bool = True) -> Dict[str, object]:
+    if not ray_available():
+        return {"ray": False, "reason": "ray is not installed; using local actors"}
+    import ray
+    if ray.is_initialized():
+        return {"ray": True, "attached": True}
+    if auto_attach:
+        try:
+            ray.init(address="auto", ignore_reinit_error=True)
+            if ray.cluster_resources().get("GPU", 0) > 0:
+                return {"ray": True, "attached": True}
+            ray.shutdown()                       # a CPU-only cluster is not ours to use
+        except Exception:
+            pass
+    temp_dir = os.environ.get("ARL_RAY_TEMP_DIR") or os.path.join(tempfile.gettempdir(), f"arl-ray-{uuid.uuid4().hex[:8]}")
+    port = int(os.environ.get("RAY_PORT", 0)) or free_port()
+    dash = int(os.environ.get("RAY_DASHBOARD_PORT", 0)) or free_port()
+    cmd = ["ray", "start", "--head", f"--port={port}", f"--dashboard-port={dash}", f"--temp-dir={temp_dir}"]
+    lo, hi = os.environ.get("ARL_RAY_MIN_WORKER_PORT"), os.environ.get("ARL_RAY_MAX_WORKER_PORT")
+    if lo and hi:
+        cmd += [f"--min-worker-port={lo}", f"--max-worker-port={hi}"]
+    subprocess.run(cmd, check=True, capture_output=True)
+    _started["temp_dir"] = temp_dir
+    atexit.register(shutdown_own_cluster)
+    head = f"{primary_ip()}:{port}"
+    peers = [h for h in read_hostfile() if h not in (socket.gethostname(), primary_ip())]
+    if peers and shutil.which("pdsh"):
+        subprocess.run(["pdsh", "-w", ",".join(peers), f"ray start --address={head}"], check=False, capture_output=True)
+    ray.init(address=head, ignore_reinit_error=True)
+    return {"ray": True, "attached": False, "address": head, "temp_dir": temp_dir, "peers": peers}
+
+
+def shutdown_own_cluster() -> None:
+    """Stops the Ray cluster this process started (identified by its temp dir), nothing else."""
+    temp_dir = _started.get("temp_dir")
+    if not temp_dir:
+        return
+    try:
+        import ray
+        if ray.is_initialized():
+            ray.shutdown()
+    except Exception:
+        pass
+    subprocess.run(["ray", "stop", "--force"], check=False, capture_output=True,
+                   env={**os.environ, "RAY_TMPDIR": temp_dir})
+    _started["temp_dir"] = None

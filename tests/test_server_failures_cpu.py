@@ -1,0 +1,126 @@
+"""Host-side failure handling: all-or-nothing initialisation, heartbeats, spawned actors that die or raise,
+placement arithmetic.  No GPU involved; failures are injected with fake workers."""
+import os
+import time
+
+import pytest
+
+from arctic_platform_b200.common.local_actors import ActorDied, ActorError, SpawnedActor
+from arctic_platform_b200.common.server import ArcticRLServerCore, JobError
+from arctic_platform_b200.common.utils.ray_pg import (ColocatePlacement, gpu_fraction, pg_scheduling_options,
+                                                      plan_colocate_placement)
+
+
+class FakeWorker:
+    created = []
+
+    def __init__(self, fail_init=False):
+        self.fail_init = fail_init
+        self.killed = False
+        self.calls = []
+        FakeWorker.created.append(self)
+
+    def call(self, method, *args, **kwargs):
+        self.calls.append(method)
+        if method == "initialize" and self.fail_init:
+            raise RuntimeError("boom")
+        if method == "step":
+            return {"metrics": {"last_lr": 1e-5, "grad_norm": 1.0}, "batch": {}}
+        return True
+
+    def kill(self):
+        self.killed = True
+
+
+def test_initialize_is_all_or_nothing():
+    FakeWorker.created = []
+    core = ArcticRLServerCore(worker_factory=lambda cfg, r, n: FakeWorker(fail_init=(r == 2)))
+    with pytest.raises(JobError) as e:
+        core.initialize({"model_name": "m", "job_type": "training", "num_devices": 4})
+    assert e.value.status == 500 and len(FakeWorker.created) == 4
+    assert all(w.killed for w in FakeWorker.created)            # nothing of the failed job survives
+    assert core.status()["jobs"] == []
+    # a second attempt is not blocked by the failed one
+    core2 = ArcticRLServerCore(worker_factory=lambda cfg, r, n: FakeWorker())
+    info = core2.initialize({"model_name": "m", "job_type": "training", "num_devices": 2})
+    assert info["status"] == "RUNNING" and info["num_devices"] == 2
+    with pytest.raises(JobError) as e2:
+        core2.initialize({"model_name": "m", "job_type": "training"})
+    assert e2.value.status == 409
+    with pytest.raises(JobError) as e3:
+        core2.step(999)
+    assert e3.value.status == 404
+    with pytest.raises(JobError) as e4:
+        core2.generate(info["job_id"], [[1]])
+    assert e4.value.status == 400
+    assert core2.step(info["job_id"])["metrics"]["grad_norm"] == 1.0
+    core2.destroy(info["job_id"])
+    assert all(w.killed for w in FakeWorker.created[-2:])
+
+
+def test_missed_heartbeat_fails_the_job():
+    core = ArcticRLServerCore(worker_factory=lambda cfg, r, n: FakeWorker(), heartbeat_timeout=0.05)
+    info = core.initialize({"model_name": "m", "job_type": "training"})
+    core.heartbeat(info["job_id"])
+    assert core.step(info["job_id"])["job_id"] == info["job_id"]
+    time.sleep(0.1)
+    with pytest.raises(JobError) as e:
+        core.step(info["job_id"])
+    assert e.value.status == 409 and core.get_job_status(info["job_id"])["status"] == "FAILED"
+
+
+class _Echo:
+    def ping(self, x):
+        return x + 1
+
+    def pid(self):
+        return os.getpid()
+
+    def fail(self):
+        raise ValueError("bad input")
+
+    def die(self):
+        os._exit(3)
+
+    def env(self, k):
+        return os.environ.get(k)
+
+
+def _bad_factory():
+    raise RuntimeError("cannot build")
+
+
+def test_spawned_actor_rpc_errors_and_death():
+    a = SpawnedActor(_Echo, env={"APB_TEST_VAR": "7"})
+    try:
+        assert a.call("ping", 41) == 42 and a.call("pid") != os.getpid() and a.call("env", "APB_TEST_VAR") == "7"
+        assert a.heartbeat()
+        with pytest.raises(ActorError, match="bad input"):
+            a.call("fail")
+        assert a.call("ping", 1) == 2                      # an exception does not kill the actor
+        with pytest.raises(ActorDied):
+            a.call("die", timeout=10)
+        assert not a.heartbeat()
+        with pytest.raises(ActorDied):
+            a.call("ping", 1)
+    finally:
+        a.kill()
+    with pytest.raises(ActorError, match="cannot build"):
+        SpawnedActor(_bad_factory)
+
+
+def test_placement_arithmetic():
+    plan = plan_colocate_placement(12, 8)
+    assert plan.gpus_per_node == [8, 4] and plan.total == 12
+    assert plan.locate(0) == (0, 0) and plan.locate(7) == (0, 7) and plan.locate(8) == (1, 0)
+    with pytest.raises(IndexError):
+        plan.locate(12)
+    assert plan.tp_layout(3, 4) == [[0, 1, 2, 3], [4, 5, 6, 7], [8, 9, 10, 11]]
+    assert ColocatePlacement([8, 8]).tp_layout(2, 8) == [list(range(8)), list(range(8, 16))]
+    # a TP-3 replica may not straddle the node boundary: bundles 6,7 stay unused on node 0
+    assert ColocatePlacement([8, 8]).tp_layout(4, 3) == [[0, 1, 2], [3, 4, 5], [8, 9, 10], [11, 12, 13]]
+    with pytest.raises(ValueError):
+        ColocatePlacement([4]).tp_layout(2, 4)
+    assert gpu_fraction("training", True) == 0.34 and gpu_fraction("sampling", False) == 1.0
+    opts = pg_scheduling_options(plan, 9, "log_prob", True)
+    assert opts["num_gpus"] == 0.33
