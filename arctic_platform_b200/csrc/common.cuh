@@ -23,6 +23,7 @@ enum StatusCode : int {
   kTimeoutTmemEmpty = 104, // MMA warp waited for the epilogue to release TMEM
   kTimeoutFlag = 105,      // wait on a global-memory flag (peer or local)
   kBadArgument = 201,
+  kBadRouting = 202,       // a (rank, row) routing entry outside the group: the store was skipped
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

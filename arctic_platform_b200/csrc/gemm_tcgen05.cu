@@ -434,7 +434,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
           }
         } else if (p.epi == kEpiBf16ScatterPeer) {
           const int2 to = p.row_map[row];
-          if (to.x >= 0) {
+          if (to.x >= p.world || to.y < 0) {
+            atomicCAS(p.status, 0, kBadRouting);
+          } else if (to.x >= 0) {
             __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c_peers[to.x]) + static_cast<long long>(to.y) * p.ldc + col0;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -585,7 +587,7 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
     rc = make_tmap_2d(&tb, B, 2, static_cast<uint64_t>(K), brows, ldb, 64, 64);
   if (rc) return 2000 + rc;
 
-  GemmParams p;
+  GemmParams p{};  // zero: the peer-mode fields must read 0 in the plain path
   p.M = M;
   p.N = N;
   p.K = K;

@@ -386,13 +386,18 @@ namespace apb {
 __global__ void __launch_bounds__(256)
 ep_scatter_rows_kernel(const __nv_bfloat16* __restrict__ src, long long ld_src, const int* __restrict__ src_row,
                        const int* __restrict__ dst_rank, const int* __restrict__ dst_row, const int* __restrict__ tag,
-                       PeerPtrs dst_ptrs, long long ld_dst, PeerPtrs meta_ptrs, int rank, int n_pairs, int H) {
+                       PeerPtrs dst_ptrs, long long ld_dst, PeerPtrs meta_ptrs, int rank, int world, int n_pairs,
+                       int H, int* status) {
   const int lane = threadIdx.x & 31;
   const long long wid = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const long long nw = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   for (long long e = wid; e < n_pairs; e += nw) {
     const int dr = dst_rank[e];
     if (dr < 0) continue;
+    if (dr >= world || dst_row[e] < 0) {  // corrupt routing table: record it and skip the store
+      if (lane == 0) atomicCAS(status, 0, kBadRouting);
+      continue;
+    }
     const __nv_bfloat16* s = src + static_cast<long long>(src_row[e]) * ld_src;
     __nv_bfloat16* d = static_cast<__nv_bfloat16*>(dst_ptrs.p[dr]) + static_cast<long long>(dst_row[e]) * ld_dst;
     for (int i = lane * 8; i < H; i += 256) *reinterpret_cast<uint4*>(d + i) = *reinterpret_cast<const uint4*>(s + i);
@@ -417,7 +422,8 @@ int apb_ep_scatter_rows(const void* src, long long ld_src, const int* src_row, c
   const long long g = (static_cast<long long>(n_pairs) * 32 + 255) / 256;
   const int grid = static_cast<int>(g < 148 * 16 ? g : 148 * 16);
   ep_scatter_rows_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src), ld_src, src_row, dst_rank, dst_row,
-                                              tag, to_peers(dst_ptrs, world), ld_dst, meta, rank, n_pairs, H);
+                                              tag, to_peers(dst_ptrs, world), ld_dst, meta, rank, world, n_pairs, H,
+                                              status_device_ptr());
   return static_cast<int>(cudaGetLastError());
 }
 }

@@ -137,8 +137,11 @@ class ExpertParallel:
             return out
         meta = self.meta.tensor[: r.recv_rows * 2].view(r.recv_rows, 2)
         src_row = torch.arange(r.recv_rows, device=rows.device, dtype=torch.int32)
-        _lib.check(_fns()["scatter"](_lib.ptr(rows), rows.stride(0), _lib.ptr(src_row), _lib.ptr(meta[:, 0].contiguous()),
-                                     _lib.ptr(meta[:, 1].contiguous()), None, self.comb.ptr_table(), H, None, self.rank,
+        # named tensors: a temporary handed to ptr() would be freed (and its block reused) before the launch
+        to_rank = meta[:, 0].contiguous()
+        to_row = meta[:, 1].contiguous()
+        _lib.check(_fns()["scatter"](_lib.ptr(rows), rows.stride(0), _lib.ptr(src_row), _lib.ptr(to_rank),
+                                     _lib.ptr(to_row), None, self.comb.ptr_table(), H, None, self.rank,
                                      self.world, r.recv_rows, H, _lib.stream_ptr()), "apb_ep_scatter_rows")
         self._barrier()
         return self.comb.tensor[: r.num_pairs * H].view(r.num_pairs, H).clone()
