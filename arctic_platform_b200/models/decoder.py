@@ -93,7 +93,11 @@ class DecoderBlock(nn.Module):
         qkv = gemm.linear(h, self.wqkv)
         q, k, v = norm.qknorm_rope(qkv, self.q_norm, self.k_norm, rope[0], rope[1], positions, cfg.num_heads,
                                    cfg.num_kv_heads, cfg.head_dim, cfg.rms_norm_eps)
-        a = segment_attention(q, k, v, layout)
+        if getattr(self, "sp_group", None) is not None:
+            from ..parallel.ulysses import ulysses_attention
+            a = ulysses_attention(q, k, v, layout, self.sp_group)
+        else:
+            a = segment_attention(q, k, v, layout)
         o = gemm.linear(a.reshape(a.shape[0], -1), self.wo)
         h2, stream = norm.rmsnorm(o, self.ln2, cfg.rms_norm_eps, stream)
         if self.mlp is not None:
