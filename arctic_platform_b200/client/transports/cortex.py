@@ -54,9 +54,10 @@ class CortexTransport(Transport):
     def _http(self, method: str, path: str, **kw):
         delay = 0.5
         last: Any = None
+        extra_headers = kw.pop("headers", {})        # popped once: a retry must carry the same headers
         for attempt in range(self.backend.max_retries + 1):
             try:
-                resp = self.session.request(method, self.base + path, headers={**self.headers, **kw.pop("headers", {})},
+                resp = self.session.request(method, self.base + path, headers={**self.headers, **extra_headers},
                                             timeout=self.config.request_timeout, **kw)
                 if resp.status_code not in TRANSIENT:
                     if resp.status_code >= 400:

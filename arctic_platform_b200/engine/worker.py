@@ -65,6 +65,8 @@ class EngineWorker:
             from .sampler import SamplerEngine
             vc = dict(job_config.get("vllm_config") or {})
             m = model if model is not None else self._load_model(job_config, dtype, seed)
+            if self.device.type != "cuda":
+                from .reference_sampler import ReferenceSampler as SamplerEngine   # noqa: F811  (CPU: recompute sampler)
             self.sampler = SamplerEngine(
                 self.model_cfg, self.device, model=m,
                 kv_cache_tokens=int(vc.get("kv_cache_tokens", 1 << 20)), max_batch=int(vc.get("max_num_seqs", 256)),

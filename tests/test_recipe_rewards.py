@@ -25,4 +25,4 @@ def test_long_context_qa_reward():
     assert long_context_qa_reward("... \\boxed{The Eiffel Tower}", ["Eiffel Tower"]) == 1.0
     assert 0.0 < long_context_qa_reward("Answer: tower in Paris", ["Eiffel Tower"]) < 1.0
     assert long_context_qa_reward("Answer: tower in Paris", ["Eiffel Tower"], em_only=True) == 0.0
-    assert long_context_qa_reward("nothing", ["x"]) == 0.0 and abs(f1_score("a b c", "b c d") - 2 / 3) < 1e-9
+    assert long_context_qa_reward("nothing", ["x"]) == 0.0 and abs(f1_score("x b c", "b c d") - 2 / 3) < 1e-9
