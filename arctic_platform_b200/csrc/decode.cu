@@ -209,6 +209,251 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const int* __restrict__
   }
 }
 
+// ---------------------------------------------------------------------------
+// Paged decode on warp-level tensor-core MMAs (m16n8k16): the per-sequence pass.
+//
+// A decode query group has at most a handful of rows per KV head (R query heads of ONE token), far below the
+// 64/128-row tile of the tcgen05 path used for shared prefixes, and the kernel is bound by streaming KV pages, not
+// by math.  So: each warp owns every 4th page of the CTA's range, copies K and V pages with cp.async into a
+// 3-deep shared-memory ring (XOR-swizzled 16-byte chunks), reads fragments with ldmatrix and runs S = Q K^T and
+// O += P V as m16n8k16 MMAs whose 16 rows hold up to 16 / R queries x R heads.  Per page that is 32 MMAs and 16
+// ldmatrix instead of ~850 scalar instructions, which leaves the load pipeline as the only limiter.
+// Output format is the same un-normalised (numerator, max, sum) partial as the scalar kernel.
+// ---------------------------------------------------------------------------
+constexpr int kMmaStages = 3;
+constexpr int kMmaPageBytes = kPage * 128 * 2;                    // one K or V page of one head
+constexpr int kMmaWarpBytes = kMmaStages * 2 * kMmaPageBytes;     // K+V ring of one warp
+constexpr int kMmaSmem = 4 * kMmaWarpBytes;                       // 96 KB
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// One page (K and V, 4 KB each, contiguous in the cache) -> one ring stage; chunk c of row t lands at
+// t * 256 + ((c ^ (t & 7)) * 16) so that the 8 rows of an ldmatrix tile hit 8 different bank groups.
+__device__ __forceinline__ void decode_issue_page(uint32_t stage_addr, const __nv_bfloat16* kpage,
+                                                  const __nv_bfloat16* vpage, int lane) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = i * 32 + lane;  // 16-byte chunk 0..255 of the page
+    const int t = c >> 4, col = c & 15;
+    const uint32_t off = static_cast<uint32_t>(t * 256 + ((col ^ (t & 7)) << 4));
+    cp_async16(stage_addr + off, reinterpret_cast<const uint8_t*>(kpage) + c * 16);
+    cp_async16(stage_addr + kMmaPageBytes + off, reinterpret_cast<const uint8_t*>(vpage) + c * 16);
+  }
+}
+
+__global__ void __launch_bounds__(kDecThreads)
+paged_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const int* __restrict__ q_start,
+                        const int* __restrict__ q_count, const int* __restrict__ pages, int max_pages,
+                        const int* __restrict__ kv_len, const __nv_bfloat16* __restrict__ kcache,
+                        const __nv_bfloat16* __restrict__ vcache, float* __restrict__ out_o, float* __restrict__ out_ml,
+                        int Hq, int Hkv, int splits, float scale_log2) {
+  constexpr int D = 128;
+  extern __shared__ __align__(128) uint8_t dec_smem[];
+  const int g = blockIdx.x / Hkv;
+  const int kvh = blockIdx.x % Hkv;
+  const int split = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int R = Hq / Hkv;
+  const int nq = q_count[g];
+  const int qs = q_start[g];
+  const int len = kv_len[g];
+  const int n_pages = (len + kPage - 1) / kPage;
+  const int per = (n_pages + splits - 1) / splits;
+  const int p0 = split * per, p1 = min(n_pages, p0 + per);
+  const int* my_pages = pages + static_cast<long long>(g) * max_pages;
+  const uint32_t ring = smem_u32(dec_smem) + warp * kMmaWarpBytes;
+  const int n_my = (p1 - p0 - warp + 3) / 4;  // pages p0 + warp, p0 + warp + 4, ... (<= 0: none)
+  const int q_per_pass = 16 / R;              // queries whose R heads fit the 16 MMA rows
+  const int quad_row = lane >> 2, quad_col = (lane & 3) * 2;
+
+  for (int q0 = 0; q0 < nq; q0 += q_per_pass) {
+    const int rows_valid = min(q_per_pass, nq - q0) * R;
+    // ---- Q fragments (A operand), rows >= rows_valid are zero
+    uint32_t qa[8][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int rr = quad_row + 8 * h;
+      const bool ok = rr < rows_valid;
+      const long long qrow = qs + q0 + rr / R;
+      const __nv_bfloat16* qp = q + (qrow * Hq + kvh * R + rr % R) * D + quad_col;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        qa[ks][h] = ok ? *reinterpret_cast<const uint32_t*>(qp + ks * 16) : 0u;
+        qa[ks][2 + h] = ok ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8) : 0u;
+      }
+    }
+    float o[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    // ---- prologue: first kMmaStages-1 pages of this warp
+#pragma unroll
+    for (int j = 0; j < kMmaStages - 1; ++j) {
+      if (j < n_my) {
+        const long long page = my_pages[p0 + warp + 4 * j];
+        const __nv_bfloat16* kp = kcache + (page * Hkv + kvh) * (kPage * D);
+        const __nv_bfloat16* vp = vcache + (page * Hkv + kvh) * (kPage * D);
+        decode_issue_page(ring + (j % kMmaStages) * 2 * kMmaPageBytes, kp, vp, lane);
+      }
+      cp_async_commit();
+    }
+#pragma unroll 1
+    for (int j = 0; j < n_my; ++j) {
+      {
+        const int jn = j + kMmaStages - 1;
+        if (jn < n_my) {
+          const long long page = my_pages[p0 + warp + 4 * jn];
+          const __nv_bfloat16* kp = kcache + (page * Hkv + kvh) * (kPage * D);
+          const __nv_bfloat16* vp = vcache + (page * Hkv + kvh) * (kPage * D);
+          decode_issue_page(ring + (jn % kMmaStages) * 2 * kMmaPageBytes, kp, vp, lane);
+        }
+        cp_async_commit();
+      }
+      cp_async_wait<kMmaStages - 1>();
+      __syncwarp();
+      const uint32_t ks_addr = ring + (j % kMmaStages) * 2 * kMmaPageBytes;
+      const uint32_t vs_addr = ks_addr + kMmaPageBytes;
+      // ---- S = Q K^T : two 8-token tiles
+      float sc[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+      {
+        const int mat = lane >> 3, rowin = lane & 7;
+        const int tok = rowin + 8 * (mat >> 1);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const int chunk = ks * 2 + (mat & 1);
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4(ks_addr + tok * 256 + ((chunk ^ (tok & 7)) << 4), b0, b1, b2, b3);
+          mma_16816(sc[0], qa[ks], b0, b1);
+          mma_16816(sc[1], qa[ks], b2, b3);
+        }
+      }
+      // ---- online softmax for rows quad_row (h = 0) and quad_row + 8 (h = 1)
+      const int tok_base = (p0 + warp + 4 * j) * kPage + quad_col;
+      uint32_t pa[4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        if (h == 1 && rows_valid <= 8) {  // uniform: the upper 8 rows are padding
+          pa[1] = pa[3] = 0u;
+          continue;
+        }
+        float sv[4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const bool valid = tok_base + nt * 8 + e < len;
+            sv[nt * 2 + e] = valid ? sc[nt][2 * h + e] * scale_log2 : -INFINITY;
+          }
+        float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[h], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = exp2f(m_run[h] - m_use);  // m_run = -inf -> 0
+        float pv[4], ps = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          pv[i] = exp2f(sv[i] - m_use);  // masked: exp2(-inf) = 0
+          ps += pv[i];
+        }
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        l_run[h] = l_run[h] * alpha + ps;
+        m_run[h] = m_new;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          o[i][2 * h] *= alpha;
+          o[i][2 * h + 1] *= alpha;
+        }
+        pa[h] = pack_bf16x2(pv[0], pv[1]);
+        pa[2 + h] = pack_bf16x2(pv[2], pv[3]);
+      }
+      // ---- O += P V : sixteen 8-dim tiles, V fragments via transposed ldmatrix
+      {
+        const int mat = lane >> 3, rowin = lane & 7;
+        const int tok = rowin + 8 * (mat & 1);
+#pragma unroll
+        for (int dp = 0; dp < 8; ++dp) {
+          const int chunk = dp * 2 + (mat >> 1);
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_t(vs_addr + tok * 256 + ((chunk ^ (tok & 7)) << 4), b0, b1, b2, b3);
+          mma_16816(o[2 * dp], pa, b0, b1);
+          mma_16816(o[2 * dp + 1], pa, b2, b3);
+        }
+      }
+      __syncwarp();
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // every warp is done with its ring: reuse it for the cross-warp merge
+    float* red_o = reinterpret_cast<float*>(dec_smem);                 // [4][16][D]
+    float* red_m = red_o + 4 * 16 * D;                                 // [4][16]
+    float* red_l = red_m + 4 * 16;                                     // [4][16]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int rr = quad_row + 8 * h;
+      if ((lane & 3) == 0) {
+        red_m[warp * 16 + rr] = m_run[h];
+        red_l[warp * 16 + rr] = l_run[h];
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float2 v2 = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+        *reinterpret_cast<float2*>(&red_o[(warp * 16 + rr) * D + i * 8 + quad_col]) = v2;
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rows_valid * D; i += kDecThreads) {
+      const int rr = i / D, d = i % D;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_m[w * 16 + rr]);
+      float ov = 0.f, ll = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float mw = red_m[w * 16 + rr];
+        const float scw = (mw == -INFINITY) ? 0.f : exp2f(mw - mm);
+        ov += red_o[(w * 16 + rr) * D + d] * scw;
+        ll += red_l[w * 16 + rr] * scw;
+      }
+      const long long qrow = qs + q0 + rr / R;
+      const long long base = ((qrow * Hq + kvh * R + rr % R) * splits + split);
+      out_o[base * D + d] = ov;
+      if (d == 0) {
+        out_ml[base * 2] = mm;
+        out_ml[base * 2 + 1] = ll;
+      }
+    }
+    __syncthreads();  // the ring is written again by the next pass
+  }
+}
+
 // Merges `n_src` sets of partials per (row, head): sets s = 0..n_src-1 are [rows, Hq, splits_s, D] blocks
 // given by pointer tables (cascade levels: shared prefix nodes + per-sequence suffix), producing
 // normalised bf16 output [rows, Hq, D].  One warp per (row, head).
@@ -364,6 +609,10 @@ int apb_kv_cache_write(const void* k, long long ldk, const void* v, long long ld
   return static_cast<int>(cudaGetLastError());
 }
 
+// Selects the scalar (CUDA-core) paged decode kernel instead of the MMA one: numerics cross-check and A/B timing.
+static int g_decode_scalar = 0;
+void apb_decode_use_scalar(int on) { g_decode_scalar = on; }
+
 // Partial attention of G query groups (see paged_decode_kernel).  out_o / out_ml are fp32 scratch
 // [Bq, Hq, splits, D] and [Bq, Hq, splits, 2].
 int apb_paged_decode_partial(const void* q, const int* q_start, const int* q_count, const int* pages, int max_pages,
@@ -374,6 +623,21 @@ int apb_paged_decode_partial(const void* q, const int* q_start, const int* q_cou
   const int R = Hq / Hkv;
   const dim3 grid(G * Hkv, splits);
   const float sl2 = scale * 1.4426950408889634f;
+  if (16 % R == 0 && !g_decode_scalar) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured[dev & 63]) {
+      cudaError_t e = cudaFuncSetAttribute(paged_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      configured[dev & 63] = true;
+    }
+    paged_decode_mma_kernel<<<grid, kDecThreads, kMmaSmem, s>>>(
+        static_cast<const __nv_bfloat16*>(q), q_start, q_count, pages, max_pages, kv_len,
+        static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache), out_o, out_ml, Hq, Hkv,
+        splits, sl2);
+    return static_cast<int>(cudaGetLastError());
+  }
 #define APB_DEC(RR)                                                                                           \
   paged_decode_kernel<RR, 128><<<grid, kDecThreads, 0, s>>>(                                                  \
       static_cast<const __nv_bfloat16*>(q), q_start, q_count, pages, max_pages, kv_len,                      \

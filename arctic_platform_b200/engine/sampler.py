@@ -23,6 +23,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -161,8 +162,9 @@ class SamplerEngine:
     def _alloc_cache(self) -> None:
         c = self.cfg
         shape = (c.num_layers, self.num_pages, c.num_kv_heads, PAGE, c.head_dim)
-        self.kcache = torch.empty(shape, device=self.device, dtype=torch.bfloat16)
-        self.vcache = torch.empty(shape, device=self.device, dtype=torch.bfloat16)
+        # zero-filled: the unwritten tail of a last page is multiplied by probability 0 and must be finite
+        self.kcache = torch.zeros(shape, device=self.device, dtype=torch.bfloat16)
+        self.vcache = torch.zeros(shape, device=self.device, dtype=torch.bfloat16)
 
     def _alloc_state(self) -> None:
         B, dev, c = self.max_batch, self.device, self.cfg
@@ -192,6 +194,7 @@ class SamplerEngine:
         self.d_step = torch.zeros(1, **i32)                                   # global decode step (RNG stream)
         self.d_stop = torch.full((8,), -1, **i32)
         self.splits = 4
+        self.n_groups = B            # groups in the prefix tables (a power-of-two bucket bounds the prefix grid)
         Hq, D = c.num_heads, c.head_dim
         f32 = dict(device=dev, dtype=torch.float32)
         self.part_o = [torch.empty((B, Hq, self.splits, D), **f32) for _ in range(2)]
@@ -269,35 +272,49 @@ class SamplerEngine:
         dec, merge = _fn("dec"), _fn("merge")
         kc, vc = self.kcache[li], self.vcache[li]
         out = torch.empty((B, c.num_heads, c.head_dim), device=self.device, dtype=torch.bfloat16)
+        # per-sequence pass: one CTA per (sequence, kv head) already fills the GPU at rollout batch sizes, so the
+        # KV range is split only when there are fewer CTAs than two waves of SMs
+        seq_splits = max(1, min(self.splits, 296 // max(1, B * c.num_kv_heads)))
+        if os.environ.get("APB_DECODE_SEQ_SPLITS"):               # tuning knob for A/B timing
+            seq_splits = max(1, min(self.splits, int(os.environ["APB_DECODE_SEQ_SPLITS"])))
         if self.cascade:
             R = c.num_heads // c.num_kv_heads
+            G = min(B, self._group_bucket())          # groups are packed at the front of the tables
             if self.prefix_on_tensor_cores and c.head_dim == 128 and R * MAX_NQ <= 128 and 128 % R == 0:
                 _lib.check(_fn("prefix_tc")(_lib.ptr(q), B, _lib.ptr(self.d_g_start), _lib.ptr(self.d_g_count),
                                             _lib.ptr(self.d_g_pages), self.max_pages, _lib.ptr(self.d_g_len),
                                             _lib.ptr(kc), _lib.ptr(vc), self.num_pages, _lib.ptr(self.part_o[0]),
-                                            _lib.ptr(self.part_ml[0]), B, c.num_heads, c.num_kv_heads, c.head_dim,
+                                            _lib.ptr(self.part_ml[0]), G, c.num_heads, c.num_kv_heads, c.head_dim,
                                             self.splits, scale, s), "decode_prefix_tc")
             else:
                 _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_g_start), _lib.ptr(self.d_g_count),
                                _lib.ptr(self.d_g_pages), self.max_pages, _lib.ptr(self.d_g_len), _lib.ptr(kc),
-                               _lib.ptr(vc), _lib.ptr(self.part_o[0]), _lib.ptr(self.part_ml[0]), B, c.num_heads,
+                               _lib.ptr(vc), _lib.ptr(self.part_o[0]), _lib.ptr(self.part_ml[0]), G, c.num_heads,
                                c.num_kv_heads, c.head_dim, self.splits, scale, s), "paged_decode(prefix)")
             _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_q_start), _lib.ptr(self.d_active), _lib.ptr(self.d_priv_table),
                            self.max_pages, _lib.ptr(self.d_priv_len), _lib.ptr(kc), _lib.ptr(vc),
                            _lib.ptr(self.part_o[1]), _lib.ptr(self.part_ml[1]), B, c.num_heads, c.num_kv_heads,
-                           c.head_dim, self.splits, scale, s), "paged_decode(private)")
+                           c.head_dim, seq_splits, scale, s), "paged_decode(private)")
             n_src = 2
+            src_splits = [self.splits, seq_splits]
         else:
             _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_q_start), _lib.ptr(self.d_active), _lib.ptr(self.d_page_table),
                            self.max_pages, _lib.ptr(self.d_len), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(self.part_o[0]),
-                           _lib.ptr(self.part_ml[0]), B, c.num_heads, c.num_kv_heads, c.head_dim, self.splits, scale, s),
+                           _lib.ptr(self.part_ml[0]), B, c.num_heads, c.num_kv_heads, c.head_dim, seq_splits, scale, s),
                        "paged_decode")
             n_src = 1
+            src_splits = [seq_splits]
         o_ptrs = (ctypes.c_void_p * 4)(*[self.part_o[i].data_ptr() if i < n_src else 0 for i in range(4)])
         ml_ptrs = (ctypes.c_void_p * 4)(*[self.part_ml[i].data_ptr() if i < n_src else 0 for i in range(4)])
-        sp = (ctypes.c_int * 4)(*[self.splits if i < n_src else 0 for i in range(4)])
+        sp = (ctypes.c_int * 4)(*[src_splits[i] if i < n_src else 0 for i in range(4)])
         _lib.check(merge(o_ptrs, ml_ptrs, sp, n_src, _lib.ptr(out), None, B, c.num_heads, c.head_dim, s), "decode_merge")
         return out
+
+    def _group_bucket(self) -> int:
+        """Number of prefix groups rounded up to a power of two: the grid of the shared-prefix pass (and the key of
+        the captured graph) changes only when the count crosses a bucket."""
+        n = max(1, int(self.n_groups))
+        return 1 << (n - 1).bit_length()
 
     @torch.no_grad()
     def _decode_step(self, B: int) -> None:
@@ -388,7 +405,8 @@ class SamplerEngine:
             for _ in range(n):
                 self._decode_step(B)
             return
-        g = self._graphs.get(B)
+        key = (B, self._group_bucket() if self.cascade else 0)
+        g = self._graphs.get(key)
         if g is None:
             # the first steps run eagerly (kernel attribute set-up, device binding, allocator warm-up)
             self._decode_step(B)
@@ -398,12 +416,12 @@ class SamplerEngine:
             before = _lib.launch_count()
             with torch.cuda.graph(g):
                 self._decode_step(B)
-            self._graph_launches[B] = _lib.launch_count() - before
-            _lib.add_launches(-self._graph_launches[B])       # capture records, it does not launch
-            self._graphs[B] = g
+            self._graph_launches[key] = _lib.launch_count() - before
+            _lib.add_launches(-self._graph_launches[key])     # capture records, it does not launch
+            self._graphs[key] = g
         for _ in range(n):
             g.replay()
-        _lib.add_launches(n * self._graph_launches[B])
+        _lib.add_launches(n * self._graph_launches[key])
 
     # ------------------------------------------------------------------ public API
     @torch.no_grad()
@@ -618,6 +636,7 @@ class SamplerEngine:
                 g_pages[k, :len(shared)] = shared
                 k += 1
                 i = j + 1
+        self.n_groups = k
         self.d_g_start.copy_(torch.from_numpy(g_start))
         self.d_g_count.copy_(torch.from_numpy(g_count))
         self.d_g_len.copy_(torch.from_numpy(g_len))

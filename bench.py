@@ -46,6 +46,8 @@ def parse_args():
     ap.add_argument("--rollouts-per-microbatch", type=int, default=4,
                     help="rollouts of one prompt per training micro-batch (prompt KV is recomputed per micro-batch)")
     ap.add_argument("--prompts-per-microbatch", type=int, default=1)
+    ap.add_argument("--ref-microbatch-merge", type=int, default=4,
+                    help="training micro-batches scored together in one reference (no-grad) forward")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="print per-phase wall times of the direct step to stderr")
     ap.add_argument("--lr", type=float, default=1e-6)
@@ -187,6 +189,25 @@ def main():
                 mbs.append({k: v[rows].contiguous().pin_memory() for k, v in full.items()})
         return mbs
 
+    def ref_groups(mbs):
+        """Scoring needs no activations for backward, so the reference pass runs on larger micro-batches: all the
+        rollouts of a prompt together (the prompt is stored and attended once for the 16 of them)."""
+        k = max(1, min(len(mbs), args.ref_microbatch_merge))
+        out = []
+        for i in range(0, len(mbs), k):
+            part = mbs[i:i + k]
+            keys = ("input_ids", "attention_mask", "response_mask")
+            batch = part[0] if len(part) == 1 else {kk: torch.cat([m[kk] for m in part]).pin_memory() for kk in keys}
+            out.append({"batch": {kk: batch[kk] for kk in keys}, "parts": part})
+        return out
+
+    def scatter_ref(grp, logp):
+        r0 = 0
+        for m in grp["parts"]:
+            n = m["input_ids"].shape[0]
+            m["ref_log_prob"] = logp[r0:r0 + n]
+            r0 += n
+
     def in_bytes(mbs, prompts):
         return sum(t.numel() * t.element_size() for mb in mbs for t in mb.values()) + sum(len(p) for p in prompts) * 8
 
@@ -212,9 +233,9 @@ def main():
         samp_w.sampler.sleep(1)
         mbs = build_batches(prompts, results)
         t = mark("build_batch", t)
-        for mb in mbs:
-            ref = ref_w.forward_no_grad(mb, dict(meta), None)
-            mb["ref_log_prob"] = ref["batch"]["log_probs"]
+        for grp in ref_groups(mbs):
+            ref = ref_w.forward_no_grad(grp["batch"], dict(meta), None)
+            scatter_ref(grp, ref["batch"]["log_probs"])
         t = mark("ref_logprob", t)
         out = train_w.forward_backward(mbs, dict(meta), {"loss_fn": "verl_grpo"})
         t = mark("fwd_bwd", t)
@@ -231,9 +252,9 @@ def main():
         mbs = build_batches(prompts, results)
         counters["h2d"] = 2 * in_bytes(mbs, prompts)          # every micro-batch goes to the device twice (ref + train)
         d2h = sum(len(r["token_ids"]) * 8 for r in results)
-        for mb in mbs:
-            ref = client.call("fwd_no_grad", {"batch": mb, "meta": dict(meta)}, reference_model=True)
-            mb["ref_log_prob"] = ref["batch"]["log_probs"]
+        for grp in ref_groups(mbs):
+            ref = client.call("fwd_no_grad", {"batch": grp["batch"], "meta": dict(meta)}, reference_model=True)
+            scatter_ref(grp, ref["batch"]["log_probs"])
             d2h += ref["batch"]["log_probs"].numel() * 4
         out = client.call("fwd_bwd", {"batch": mbs, "meta": dict(meta)}, {"loss_fn": "verl_grpo"})
         st = client.call("step")

@@ -72,3 +72,69 @@ def test_more_sequences_than_slots_and_stop_tokens():
     first = outs[0]["token_ids"]
     outs2 = eng.generate(prompts[:1], {"n": 1, "temperature": 0.0, "max_tokens": 9, "stop_token_ids": [first[3]]})
     assert outs2[0]["finish_reason"] == "stop" and outs2[0]["token_ids"] == first[:first.index(first[3]) + 1]
+
+
+@pytest.mark.parametrize("Hq,Hkv,nq,splits", [(32, 8, 1, 1), (32, 8, 1, 3), (32, 8, 3, 2), (16, 8, 5, 1), (8, 8, 1, 2),
+                                              (32, 2, 2, 1)])
+def test_paged_decode_mma_kernel_matches_reference_and_scalar_kernel(Hq, Hkv, nq, splits):
+    """The tensor-core (m16n8k16) paged decode pass against a dense fp32 reference and against the scalar kernel:
+    ragged lengths (including an empty range), shuffled pages, query groups of several rows, KV splits."""
+    import ctypes
+    import math
+    from arctic_platform_b200.engine.sampler import _fn
+    from arctic_platform_b200.ops import _lib
+    dev, D, PAGE = "cuda", 128, 16
+    g = torch.Generator(device=dev).manual_seed(Hq * 100 + nq * 10 + splits)
+    lens = [0, 1, 15, 16, 17, 333, 1024, 700]
+    G = len(lens)
+    max_pages = 80
+    num_pages = G * max_pages + 7
+    kc = torch.randn(num_pages, Hkv, PAGE, D, device=dev, generator=g).bfloat16()
+    vc = torch.randn(num_pages, Hkv, PAGE, D, device=dev, generator=g).bfloat16()
+    perm = torch.randperm(num_pages, device=dev, generator=g)[:G * max_pages].to(torch.int32).view(G, max_pages)
+    Bq = G * nq
+    q = torch.randn(Bq, Hq, D, device=dev, generator=g).bfloat16()
+    q_start = (torch.arange(G, device=dev, dtype=torch.int32) * nq).contiguous()
+    q_count = torch.full((G,), nq, device=dev, dtype=torch.int32)
+    kv_len = torch.tensor(lens, device=dev, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(D)
+
+    def run(scalar):
+        _lib.cuda_lib().apb_decode_use_scalar(int(scalar))
+        po = torch.zeros(Bq, Hq, splits, D, device=dev, dtype=torch.float32)
+        pml = torch.zeros(Bq, Hq, splits, 2, device=dev, dtype=torch.float32)
+        _lib.check(_fn("dec")(_lib.ptr(q), _lib.ptr(q_start), _lib.ptr(q_count), _lib.ptr(perm), max_pages,
+                              _lib.ptr(kv_len), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(po), _lib.ptr(pml), G, Hq, Hkv, D,
+                              splits, scale, _lib.stream_ptr()), "paged_decode")
+        out = torch.empty(Bq, Hq, D, device=dev, dtype=torch.bfloat16)
+        lse = torch.empty(Bq, Hq, device=dev, dtype=torch.float32)
+        o_ptrs = (ctypes.c_void_p * 4)(po.data_ptr(), 0, 0, 0)
+        ml_ptrs = (ctypes.c_void_p * 4)(pml.data_ptr(), 0, 0, 0)
+        sp = (ctypes.c_int * 4)(splits, 0, 0, 0)
+        _lib.check(_fn("merge")(o_ptrs, ml_ptrs, sp, 1, _lib.ptr(out), _lib.ptr(lse), Bq, Hq, D, _lib.stream_ptr()), "merge")
+        _lib.check_status("paged decode")
+        return out.float(), lse
+
+    try:
+        out_mma, lse_mma = run(False)
+        out_sc, lse_sc = run(True) if Hq // Hkv in (1, 2, 4, 8) and nq <= 16 else (None, None)
+    finally:
+        _lib.cuda_lib().apb_decode_use_scalar(0)
+    R = Hq // Hkv
+    for gi, L in enumerate(lens):
+        if L == 0:
+            continue
+        n_pg = (L + PAGE - 1) // PAGE
+        pg = perm[gi, :n_pg].long()
+        K = kc[pg].permute(1, 0, 2, 3).reshape(Hkv, n_pg * PAGE, D)[:, :L].float()
+        V = vc[pg].permute(1, 0, 2, 3).reshape(Hkv, n_pg * PAGE, D)[:, :L].float()
+        for qi in range(nq):
+            row = gi * nq + qi
+            qq = q[row].float().view(Hkv, R, D)
+            s = torch.einsum("hrd,hld->hrl", qq, K) * scale
+            ref = torch.einsum("hrl,hld->hrd", torch.softmax(s, -1), V).reshape(Hq, D)
+            ref_lse = torch.logsumexp(s, -1).reshape(Hq)
+            assert (out_mma[row] - ref).abs().max() < 0.03, (gi, L, float((out_mma[row] - ref).abs().max()))
+            assert (lse_mma[row] - ref_lse).abs().max() < 0.02
+            if out_sc is not None:
+                assert (out_mma[row] - out_sc[row]).abs().max() < 0.03
