@@ -105,11 +105,14 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 }
 
 // dx = rstd * (g - xhat * mean(g * xhat)) [+ dres], g = dy * w ; dw += sum_t dy * xhat
-__global__ void __launch_bounds__(kNormThreads)
+// NV = 8-element vectors per thread (registers scale with it, so narrow rows keep more CTAs per SM).
+template <int NV>
+__global__ void __launch_bounds__(kNormThreads, NV <= 2 ? 3 : 1)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                    float* __restrict__ dw, int T, int H, float w_offset) {
+  constexpr int kNormMaxVec = NV;  // shadows the file-level bound inside this kernel
   __shared__ float scratch[32];
   const int nvec = H / 8;
   float dw_acc[kNormMaxVec][8];
@@ -175,6 +178,39 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         for (int j = 0; j < 8; ++j) atomicAdd(dw + v * 8 + j, dw_acc[i][j]);
       }
     }
+  }
+}
+
+// N consecutive bf16 (N = 1, 2 or 4) as one 2-, 4- or 8-byte access.
+template <int N>
+__device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float (&out)[N]) {
+  if constexpr (N == 1) {
+    out[0] = __bfloat162float(p[0]);
+  } else if constexpr (N == 2) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    out[0] = f.x;
+    out[1] = f.y;
+  } else {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    out[0] = f0.x;
+    out[1] = f0.y;
+    out[2] = f1.x;
+    out[3] = f1.y;
+  }
+}
+template <int N>
+__device__ __forceinline__ void store_vec(__nv_bfloat16* p, const float (&v)[N]) {
+  if constexpr (N == 1) {
+    p[0] = __float2bfloat16(v[0]);
+  } else if constexpr (N == 2) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+  } else {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = raw;
   }
 }
 
@@ -251,47 +287,53 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_qkv,
                        const __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dqkv, long long ld_dqkv,
                        float* __restrict__ dwq, float* __restrict__ dwk, int T, int Hq, int Hkv, int rot,
                        float eps) {
-  constexpr int E2 = D / 64;
+  constexpr int E2 = D / 64;  // elements per lane in each half of the head
   const int lane = threadIdx.x & 31;
   const int heads = Hq + Hkv;
   const long long nwarps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  float dwa[E2], dwb[E2];
+  // Every warp walks (token, head) pairs of BOTH classes (q heads and k heads) so the work is balanced whatever
+  // the GQA ratio; the two weight-gradient accumulators live in registers side by side.
+  float dwa[2][E2], dwb[2][E2];
+  float wa[2][E2], wb[2][E2];
 #pragma unroll
-  for (int j = 0; j < E2; ++j) dwa[j] = dwb[j] = 0.f;
-  // Warps stride over (token, head) pairs of ONE head class so dw stays in registers:
-  // even global warps take q heads, odd ones k heads.
-  const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
-  const bool is_q = (gw & 1) == 0;
-  const int nh = is_q ? Hq : Hkv;
-  const __nv_bfloat16* w = is_q ? wq : wk;
-  const long long items = static_cast<long long>(T) * nh;
-  for (long long it = gw >> 1; it < items; it += (nwarps_total + 1) >> 1) {
-    const int t = static_cast<int>(it / nh);
-    const int hh = static_cast<int>(it % nh);
-    const int h = is_q ? hh : Hq + hh;
-    const __nv_bfloat16* src = qkv + t * ld_qkv + static_cast<long long>(h) * D;
-    const __nv_bfloat16* g = is_q ? dq + (static_cast<long long>(t) * Hq + hh) * D
-                                  : dk + (static_cast<long long>(t) * Hkv + hh) * D;
-    __nv_bfloat16* dst = dqkv + t * ld_dqkv + static_cast<long long>(h) * D;
-    const int p = pos[t];
-    const int half = rot / 2;
-    float ga[E2], gb[E2], xa[E2], xb[E2];
+  for (int c = 0; c < 2; ++c) {
+    const __nv_bfloat16* w = c == 0 ? wq : wk;
 #pragma unroll
     for (int j = 0; j < E2; ++j) {
-      const int i = lane * E2 + j;
-      const float da = __bfloat162float(g[i]), db = __bfloat162float(g[D / 2 + i]);
-      if (rot == D) {
-        const float c = cos_t[static_cast<long long>(p) * half + i], s = sin_t[static_cast<long long>(p) * half + i];
-        ga[j] = da * c + db * s;   // transpose of the rotation
-        gb[j] = db * c - da * s;
-      } else {
-        ga[j] = da;
-        gb[j] = db;
-      }
-      xa[j] = __bfloat162float(src[i]);
-      xb[j] = __bfloat162float(src[D / 2 + i]);
+      dwa[c][j] = dwb[c][j] = 0.f;
+      wa[c][j] = w ? __bfloat162float(w[lane * E2 + j]) : 1.f;
+      wb[c][j] = w ? __bfloat162float(w[D / 2 + lane * E2 + j]) : 1.f;
     }
-    if (w) {
+  }
+  const bool has_w = wq != nullptr;
+  const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const long long items = static_cast<long long>(T) * heads;
+  const int half = rot / 2;
+  for (long long it = gw; it < items; it += nwarps_total) {
+    const int t = static_cast<int>(it / heads);
+    const int h = static_cast<int>(it % heads);
+    const bool is_q = h < Hq;
+    const __nv_bfloat16* src = qkv + t * ld_qkv + static_cast<long long>(h) * D;
+    const __nv_bfloat16* g = is_q ? dq + (static_cast<long long>(t) * Hq + h) * D
+                                  : dk + (static_cast<long long>(t) * Hkv + (h - Hq)) * D;
+    __nv_bfloat16* dst = dqkv + t * ld_dqkv + static_cast<long long>(h) * D;
+    const int p = pos[t];
+    float ga[E2], gb[E2], xa[E2], xb[E2];
+    load_vec<E2>(g + lane * E2, ga);
+    load_vec<E2>(g + D / 2 + lane * E2, gb);
+    load_vec<E2>(src + lane * E2, xa);
+    load_vec<E2>(src + D / 2 + lane * E2, xb);
+    if (rot == D) {
+#pragma unroll
+      for (int j = 0; j < E2; ++j) {
+        const int i = lane * E2 + j;
+        const float c = cos_t[static_cast<long long>(p) * half + i], sn = sin_t[static_cast<long long>(p) * half + i];
+        const float da = ga[j], db = gb[j];
+        ga[j] = da * c + db * sn;  // transpose of the rotation
+        gb[j] = db * c - da * sn;
+      }
+    }
+    if (has_w) {
       float ss = 0.f;
 #pragma unroll
       for (int j = 0; j < E2; ++j) ss += xa[j] * xa[j] + xb[j] * xb[j];
@@ -300,14 +342,18 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_qkv,
       float dot = 0.f;
 #pragma unroll
       for (int j = 0; j < E2; ++j) {
-        const int i = lane * E2 + j;
-        const float wa = __bfloat162float(w[i]), wb = __bfloat162float(w[D / 2 + i]);
         xa[j] *= rstd;
         xb[j] *= rstd;
-        dwa[j] += ga[j] * xa[j];
-        dwb[j] += gb[j] * xb[j];
-        ga[j] *= wa;
-        gb[j] *= wb;
+        const float pa = ga[j] * xa[j], pb = gb[j] * xb[j];
+        if (is_q) {
+          dwa[0][j] += pa;
+          dwb[0][j] += pb;
+        } else {
+          dwa[1][j] += pa;
+          dwb[1][j] += pb;
+        }
+        ga[j] *= is_q ? wa[0][j] : wa[1][j];
+        gb[j] *= is_q ? wb[0][j] : wb[1][j];
         dot += ga[j] * xa[j] + gb[j] * xb[j];
       }
       dot = warp_sum(dot) / D;
@@ -317,19 +363,19 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_qkv,
         gb[j] = rstd * (gb[j] - xb[j] * dot);
       }
     }
-#pragma unroll
-    for (int j = 0; j < E2; ++j) {
-      const int i = lane * E2 + j;
-      dst[i] = __float2bfloat16(ga[j]);
-      dst[D / 2 + i] = __float2bfloat16(gb[j]);
-    }
+    store_vec<E2>(dst + lane * E2, ga);
+    store_vec<E2>(dst + D / 2 + lane * E2, gb);
   }
-  float* dwp = is_q ? dwq : dwk;
-  if (w && dwp) {
+  if (has_w) {
 #pragma unroll
-    for (int j = 0; j < E2; ++j) {
-      atomicAdd(dwp + lane * E2 + j, dwa[j]);
-      atomicAdd(dwp + D / 2 + lane * E2 + j, dwb[j]);
+    for (int c = 0; c < 2; ++c) {
+      float* dwp = c == 0 ? dwq : dwk;
+      if (!dwp) continue;
+#pragma unroll
+      for (int j = 0; j < E2; ++j) {
+        atomicAdd(dwp + lane * E2 + j, dwa[c][j]);
+        atomicAdd(dwp + D / 2 + lane * E2 + j, dwb[c][j]);
+      }
     }
   }
 }
@@ -413,11 +459,18 @@ int apb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
                     float* dw, int T, int H, float w_offset, cudaStream_t s) {
   if (T <= 0) return 0;
   if (H % 8 || H > kNormThreads * 8 * kNormMaxVec) return kBadArgument;
-  const int grid = T < 148 * 2 ? T : 148 * 2;
-  rmsnorm_bwd_kernel<<<grid, kNormThreads, 0, s>>>(
-      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
-      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres),
-      static_cast<__nv_bfloat16*>(dx), dw, T, H, w_offset);
+  const int nv = (H / 8 + kNormThreads - 1) / kNormThreads;
+  const int per_sm = nv <= 2 ? 3 : 1;
+  const int grid = T < 148 * per_sm ? T : 148 * per_sm;
+#define APB_NORM_BWD(NV)                                                                                     \
+  rmsnorm_bwd_kernel<NV><<<grid, kNormThreads, 0, s>>>(                                                       \
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),                            \
+      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<const __nv_bfloat16*>(dres),                    \
+      static_cast<__nv_bfloat16*>(dx), dw, T, H, w_offset)
+  if (nv <= 1) APB_NORM_BWD(1);
+  else if (nv <= 2) APB_NORM_BWD(2);
+  else APB_NORM_BWD(4);
+#undef APB_NORM_BWD
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -449,7 +502,7 @@ int apb_qknorm_rope_bwd(const void* qkv, long long ld_qkv, const void* wq, const
                         float eps, cudaStream_t s) {
   if (T <= 0) return 0;
   if (rot != 0 && rot != D) return kBadArgument;
-  const int grid = 148 * 4;
+  const int grid = 148 * 8;
 #define APB_LAUNCH_QKB(DD)                                                                                  \
   qknorm_rope_bwd_kernel<DD><<<grid, 256, 0, s>>>(                                                          \
       static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<const __nv_bfloat16*>(wq),               \

@@ -71,22 +71,24 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kGemmThreads = 192;
 
-template <int BN>
+// ST = 0 picks the deepest ring that fits one CTA per SM; ST = 3 is the "two CTAs per SM" variant for skinny
+// (decode) problems whose tile count falls between one and two waves of SMs.
+template <int BN, int ST = 0>
 struct GemmCfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+  static constexpr int kStages = ST ? ST : (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
   static constexpr int kTmemCols = 2 * BN;
 };
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 
-template <int BN>
+template <int BN, int ST = 0>
 __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtensorMap& tma_b,
                                           const CUtensorMap* a_peer_maps, const GemmParams& p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, ST>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
@@ -482,6 +484,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   gemm_body<BN>(tma_a, tma_b, nullptr, p);
 }
 
+// Two CTAs per SM with a 3-stage ring each (see GemmCfg).
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 2)
+gemm_bf16_x2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const GemmParams p) {
+  gemm_body<BN, 3>(tma_a, tma_b, nullptr, p);
+}
+
 // Variant whose A operand is gathered from the other ranks' memory tile by tile (all-gather -> GEMM).
 template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -530,6 +540,29 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   return static_cast<int>(cudaGetLastError());
 }
 
+template <int BN>
+static int launch_gemm_x2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN, 3>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_x2_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured[dev & 63] = true;
+  }
+  const int tiles_m = (p.M + kBM - 1) / kBM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int mn_tiles = p.tile_map ? p.num_map_tiles : tiles_m * tiles_n;
+  const long long total = static_cast<long long>(mn_tiles) * p.splits;
+  const int cap = 2 * sm_count();
+  const int grid = static_cast<int>(total < cap ? total : cap);
+  if (grid <= 0) return 0;
+  gemm_bf16_x2_kernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 }  // namespace apb
 
 extern "C" {
@@ -571,7 +604,11 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
     if (bn == 128 && t128 * 10 < sm_count() * 7 && N >= 128) bn = 64;
     if (tile_map) bn = 128;
   }
+  // bn = 1000 + width: the two-CTAs-per-SM variant (widths 64 and 128)
+  const bool x2 = bn > 1000;
+  if (x2) bn -= 1000;
   if (bn != 64 && bn != 128 && bn != 256) return kBadArgument;
+  if (x2 && bn == 256) return kBadArgument;
 
   CUtensorMap ta, tb;
   int rc;
@@ -608,6 +645,7 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   p.labels = nullptr;
   p.partial = nullptr;
   p.row_lse = p.row_ent = p.row_glp = p.row_gent = nullptr;
+  if (x2) return bn == 64 ? launch_gemm_x2<64>(ta, tb, p, stream) : launch_gemm_x2<128>(ta, tb, p, stream);
   if (bn == 64) return launch_gemm<64>(ta, tb, p, max_ctas, stream);
   return bn == 256 ? launch_gemm<256>(ta, tb, p, max_ctas, stream) : launch_gemm<128>(ta, tb, p, max_ctas, stream);
 }

@@ -366,6 +366,16 @@ class SamplerEngine:
                                  self.cfg.rms_norm_eps, 0.0, _lib.stream_ptr()), "rmsnorm_f32in")
         return y, stream
 
+    def _gate_up_bn(self, B: int) -> int:
+        """Tile choice of the gate/up projection in decode: when 128-wide tiles make between one and two waves of
+        SMs, run two CTAs per SM so that every tile streams its weights at the same time."""
+        if os.environ.get("APB_GATE_UP_BN"):
+            return int(os.environ["APB_GATE_UP_BN"])
+        if B > 128:
+            return 0
+        tiles = (2 * self.cfg.intermediate_size + 127) // 128
+        return gemm.BN_X2 + 128 if 148 < tiles <= 296 else 256
+
     def _decode_layers_splitk(self, x: torch.Tensor, positions, slots, B: int) -> torch.Tensor:
         """Decoder stack for one decode step.  The two projections with few output columns (o_proj, down_proj)
         run as split-K GEMMs with fp32 ``red.add`` epilogues so that every SM streams weights; the norm that
@@ -394,7 +404,7 @@ class SamplerEngine:
             h2, stream = self._norm_f32(acc_o, blk.ln2, stream)
             act = torch.empty((B, c.intermediate_size), device=self.device, dtype=torch.bfloat16)
             gemm.gemm_raw(h2, blk.wgu, None, M=B, N=2 * c.intermediate_size, K=H, epi=gemm.EPI_SWIGLU, out2=act,
-                          bn=256 if B <= 128 else 0)
+                          bn=self._gate_up_bn(B))
             gemm.gemm_raw(act, blk.wdown, acc_d, M=B, N=H, K=c.intermediate_size, epi=gemm.EPI_F32_ATOMIC, splits=sd,
                           bn=128)
         h, _ = self._norm_f32(acc_d, self.model.final_norm, stream)

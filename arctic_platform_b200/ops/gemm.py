@@ -28,6 +28,9 @@ def _check2d(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must be bfloat16, got {t.dtype}")
 
 
+BN_X2 = 1000   # add to a tile width (64 / 128): 3-stage ring, two CTAs per SM -- for skinny problems between one and two waves
+
+
 def gemm_raw(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor], *, M: int, N: int, K: int,
              a_mn: bool = False, b_mn: bool = False, epi: int = EPI_BF16, splits: int = 1,
              alpha: float = 1.0, bias: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None,

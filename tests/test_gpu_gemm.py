@@ -109,3 +109,26 @@ def test_linear_autograd():
     _close(y, yr.detach(), 256)
     _close(x.grad, xr.grad, 384)
     _close(w.grad, wr.grad, 260)
+
+
+@pytest.mark.parametrize("bn", [64, 128])
+@pytest.mark.parametrize("epi", ["bf16", "swiglu"])
+def test_two_ctas_per_sm_variant_matches_reference(bn, epi):
+    """The 3-stage, two-CTAs-per-SM kernel (decode-shaped problems between one and two waves of tiles)."""
+    from arctic_platform_b200.ops import _lib, gemm
+    torch.manual_seed(bn)
+    M, N, K = 128, 19456 if bn == 128 else 12800, 512
+    a = torch.randn(M, K, device="cuda").bfloat16()
+    b = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    ref = a.float() @ b.float().t()
+    if epi == "bf16":
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        gemm.gemm_raw(a, b, out, M=M, N=N, K=K, bn=gemm.BN_X2 + bn)
+        _lib.check_status("x2 gemm")
+        assert (out.float() - ref).abs().max() < 0.05
+    else:
+        act = torch.empty(M, N // 2, device="cuda", dtype=torch.bfloat16)
+        gemm.gemm_raw(a, b, None, M=M, N=N, K=K, epi=gemm.EPI_SWIGLU, out2=act, bn=gemm.BN_X2 + bn)
+        _lib.check_status("x2 gemm swiglu")
+        want = torch.nn.functional.silu(ref[:, 0::2]) * ref[:, 1::2]
+        assert (act.float() - want).abs().max() < 0.05
