@@ -14,6 +14,10 @@
 // to shared memory once and is read by two products (K-major for dK, MN-major for
 // dQ^T).  dQ^T is added to an fp32 accumulator in global memory with coalesced
 // red.add (lanes = head-dim index).
+//
+// Two gradient warpgroups take alternate query tiles, so the tensor core works on tile i+1 while the other group is
+// still in the exponentials / dS of tile i.  Tensor memory (512 columns): per group one 64-column slot that holds
+// S^T, then P^T, then dQ^T of its tile, and one 64-column slot for dP^T; dK and dV take 128 columns each.
 #include "common.cuh"
 #include "host_utils.cuh"
 
@@ -34,7 +38,7 @@ struct AttnBwdParams {
   int* status;
 };
 
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;  // producer, MMA issuer, two gradient groups of four warps
 constexpr int kBwdQTile = 64;
 constexpr int kBwdStages = 3;
 constexpr int kBigDiag = 1 << 27;
@@ -67,13 +71,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   uint64_t* full = bars;                    // [stages]
   uint64_t* empty = full + kBwdStages;      // [stages]
   uint64_t* kv_full = empty + kBwdStages;   // 1
-  uint64_t* s_full = kv_full + 1;           // [2]
-  uint64_t* dp_full = s_full + 2;           // 1
-  uint64_t* p_full = dp_full + 1;           // 1 (128 arrivals)
-  uint64_t* ds_full = p_full + 1;           // 1 (128 arrivals)
-  uint64_t* dq_full = ds_full + 1;          // 1
-  uint64_t* dq_read = dq_full + 1;          // 1 (128 arrivals)
-  uint64_t* dkv_full = dq_read + 1;         // 1
+  uint64_t* s_full = kv_full + 1;           // [2]  S^T of a tile is in its group's slot
+  uint64_t* dp_full = s_full + 2;           // [2]  dP^T likewise
+  uint64_t* p_full = dp_full + 2;           // [2]  (128 arrivals) P^T written
+  uint64_t* ds_full = p_full + 2;           // [2]  (128 arrivals) dS^T in shared memory, dP^T slot free
+  uint64_t* dq_full = ds_full + 2;          // [2]  dQ^T of the tile is in the slot
+  uint64_t* dq_read = dq_full + 2;          // [2]  (128 arrivals) slot free again
+  uint64_t* dkv_full = dq_read + 2;         // 1
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(dkv_full + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -89,13 +93,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       mbar_init(&empty[s], 1);
     }
     mbar_init(kv_full, 1);
-    mbar_init(&s_full[0], 1);
-    mbar_init(&s_full[1], 1);
-    mbar_init(dp_full, 1);
-    mbar_init(p_full, 128);
-    mbar_init(ds_full, 128);
-    mbar_init(dq_full, 1);
-    mbar_init(dq_read, 128);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&s_full[g], 1);
+      mbar_init(&dp_full[g], 1);
+      mbar_init(&p_full[g], 128);
+      mbar_init(&ds_full[g], 128);
+      mbar_init(&dq_full[g], 1);
+      mbar_init(&dq_read[g], 128);
+    }
     mbar_init(dkv_full, 1);
     mbar_fence_init();
   }
@@ -107,7 +112,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 192, kColDK = 256, kColDV = 384;
+  constexpr uint32_t kColSlot = 0, kColDP = 128, kColDK = 256, kColDV = 384;  // slot / dP: + 64 * group
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer (whole warp)
@@ -177,64 +182,68 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         }
       };
       bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutFull);
-      if (ok) ok = mbar_wait(&full[0], 0, p.status, kTimeoutFull);
-      if (ok) {
+      // S^T and dP^T of the first tile of each group
+      for (int j = 0; j < 2 && j < n_iter && ok; ++j) {
+        ok = mbar_wait(&full[j % kBwdStages], 0, p.status, kTimeoutFull);
+        if (!ok) break;
         tc_fence_after();
-        issue_st(ka, stage_q(0), kColS);
-        tc_commit(&s_full[0]);
-        issue_st(va, stage_q(0) + Cfg::kQTileBytes, kColDP);
-        tc_commit(dp_full);
+        issue_st(ka, stage_q(j % kBwdStages), kColSlot + j * 64);
+        tc_commit(&s_full[j]);
+        issue_st(va, stage_q(j % kBwdStages) + Cfg::kQTileBytes, kColDP + j * 64);
+        tc_commit(&dp_full[j]);
       }
       for (int it = 0; it < n_iter && ok; ++it) {
         const int s = it % kBwdStages;
+        const int g = it & 1;
+        const uint32_t par = (it >> 1) & 1;
         const uint32_t sq = stage_q(s), sdo = sq + Cfg::kQTileBytes;
-        const bool more = it + 1 < n_iter;
+        const uint32_t slot = tmem_base + kColSlot + g * 64;
         // dV += P^T dO
-        if (!mbar_wait(p_full, it & 1, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
+        if (!mbar_wait(&p_full[g], par, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < kBwdQTile / 16; ++k)
-          umma_bf16_ts(tmem_base + kColDV, tmem_base + kColS + (it & 1) * 64 + k * 8,
-                       umma_smem_desc(sdo + k * 2048, QCH, 1024), idesc_dv, (it > 0 || k > 0) ? 1u : 0u);
-        // next S^T
-        if (more) {
-          const int s1 = (it + 1) % kBwdStages;
-          if (!mbar_wait(&full[s1], ((it + 1) / kBwdStages) & 1, p.status, kTimeoutFull)) { ok = false; break; }
+          umma_bf16_ts(tmem_base + kColDV, slot + k * 8, umma_smem_desc(sdo + k * 2048, QCH, 1024), idesc_dv,
+                       (it > 0 || k > 0) ? 1u : 0u);
+        // S^T and dP^T of the other group's next tile (its slot is free once dQ^T of tile it-1 has been read)
+        if (it >= 1 && it + 1 < n_iter) {
+          const int it1 = it + 1, g1 = g ^ 1, s1 = it1 % kBwdStages;
+          if (!mbar_wait(&dq_read[g1], ((it - 1) >> 1) & 1, p.status, kTimeoutTmemEmpty) ||
+              !mbar_wait(&full[s1], (it1 / kBwdStages) & 1, p.status, kTimeoutFull)) { ok = false; break; }
           tc_fence_after();
-          issue_st(ka, stage_q(s1), kColS + ((it + 1) & 1) * 64);
-          tc_commit(&s_full[(it + 1) & 1]);
+          issue_st(ka, stage_q(s1), kColSlot + g1 * 64);
+          tc_commit(&s_full[g1]);
+          issue_st(va, stage_q(s1) + Cfg::kQTileBytes, kColDP + g1 * 64);
+          tc_commit(&dp_full[g1]);
         }
-        // dK += dS^T Q ; dQ^T = K^T dS^T
-        if (!mbar_wait(ds_full, it & 1, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
-        if (it > 0 && !mbar_wait(dq_read, (it - 1) & 1, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
+        // dK += dS^T Q ; dQ^T = K^T dS^T (into the slot, whose P^T the dV product above has consumed: the
+        // tensor core executes one CTA's MMAs in issue order)
+        if (!mbar_wait(&ds_full[g], par, p.status, kTimeoutTmemEmpty)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t dsa = smem_u32(smem_ds + (it & 1) * Cfg::kDsBytes);
+        const uint32_t dsa = smem_u32(smem_ds + g * Cfg::kDsBytes);
 #pragma unroll
         for (int k = 0; k < kBwdQTile / 16; ++k)
           umma_bf16_ss(tmem_base + kColDK, umma_smem_desc(dsa + k * 32, 0, 1024),
                        umma_smem_desc(sq + k * 2048, QCH, 1024), idesc_dv, (it > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < 128 / 16; ++k)
-          umma_bf16_ss(tmem_base + kColDQ, umma_smem_desc(ka + k * 2048, 16384, 1024),
-                       umma_smem_desc(dsa + k * 2048, 0, 1024), idesc_dq, k > 0 ? 1u : 0u);
-        tc_commit(dq_full);
+          umma_bf16_ss(slot, umma_smem_desc(ka + k * 2048, 16384, 1024), umma_smem_desc(dsa + k * 2048, 0, 1024),
+                       idesc_dq, k > 0 ? 1u : 0u);
+        tc_commit(&dq_full[g]);
         tc_commit(&empty[s]);
-        if (more) {
-          const int s1 = (it + 1) % kBwdStages;
-          issue_st(va, stage_q(s1) + Cfg::kQTileBytes, kColDP);
-          tc_commit(dp_full);
-        }
       }
       if (ok) tc_commit(dkv_full);
     }
   } else {
     // ---------------------------------------------------------------- softmax / gradient group
     const int quarter = warp & 3;
+    const int grp = (warp - 2) >> 2;    // gradient group: tiles grp, grp + 2, ...
     const int r = quarter * 32 + lane;  // key row of the block (and head-dim index for dQ^T)
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const bool row_ok = r < kv_valid;
     bool ok = true;
-    for (int it = 0; it < n_iter; ++it) {
+    for (int it = grp; it < n_iter; it += 2) {
+      const uint32_t par = (it >> 1) & 1;
       const int s = it % kBwdStages;
       const int* e = p.list + static_cast<long long>(list_off + it / ratio) * 4;
       const int q_row0 = e[0], q_valid = e[1], diag = e[2];
@@ -242,12 +251,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       const int c_min = (diag >= kBigDiag) ? 0 : max(0, r - diag);
       const float* st = smem_stat + s * 128;
       if (!mbar_wait(&full[s], (it / kBwdStages) & 1, p.status, kTimeoutFull) ||
-          !mbar_wait(&s_full[it & 1], (it >> 1) & 1, p.status, kTimeoutTmemFull)) {
+          !mbar_wait(&s_full[grp], par, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const uint32_t t_s = tmem_base + lane_off + kColS + (it & 1) * 64;
+      const uint32_t t_s = tmem_base + lane_off + kColSlot + grp * 64;
       float pr[kBwdQTile];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -267,18 +276,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[grp]);
       // dS^T
-      if (!mbar_wait(dp_full, it & 1, p.status, kTimeoutTmemFull)) {
+      if (!mbar_wait(&dp_full[grp], par, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      uint8_t* ds_row = smem_ds + (it & 1) * Cfg::kDsBytes + r * 128;
+      uint8_t* ds_row = smem_ds + grp * Cfg::kDsBytes + r * 128;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem_base + lane_off + kColDP + h * 32, v);
+        tmem_ld_32x32(tmem_base + lane_off + kColDP + grp * 64 + h * 32, v);
         tmem_ld_wait();
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -298,9 +307,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(ds_full);
+      mbar_arrive(&ds_full[grp]);
       // dQ^T -> global accumulator (this thread holds head-dim index r for 64 query rows)
-      if (!mbar_wait(dq_full, it & 1, p.status, kTimeoutTmemFull)) {
+      if (!mbar_wait(&dq_full[grp], par, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
@@ -309,7 +318,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t v[32];
-        tmem_ld_32x32(tmem_base + lane_off + kColDQ + h * 32, v);
+        tmem_ld_32x32(t_s + h * 32, v);
         tmem_ld_wait();
         if (r < D) {
 #pragma unroll
@@ -320,7 +329,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
         }
       }
       tc_fence_before();
-      mbar_arrive(dq_read);
+      mbar_arrive(&dq_read[grp]);
     }
     // dK / dV of this block.  The TMEM loads are warp collectives: every lane runs them, only the
     // global stores are predicated on the row being inside the block.
@@ -332,8 +341,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant
       if (ok) {
         __nv_bfloat16* dkp = p.dk + (static_cast<long long>(kv_row0) + r) * p.ld_dk + static_cast<long long>(kvh) * D;
         __nv_bfloat16* dvp = p.dv + (static_cast<long long>(kv_row0) + r) * p.ld_dv + static_cast<long long>(kvh) * D;
-#pragma unroll 1
-        for (int which = 0; which < 2; ++which) {
+        {
+          const int which = grp;  // group 0 stores dK, group 1 stores dV
           __nv_bfloat16* dst = which ? dvp : dkp;
           const uint32_t col0 = which ? kColDV : kColDK;
 #pragma unroll 1
