@@ -147,7 +147,8 @@ __global__ void epoch_wait_kernel(PeerPtrs flags, int rank, int world, int epoch
 __global__ void __launch_bounds__(256)
 gather_shards_kernel(PeerPtrs shards, PeerPtrs flags, int rank, int world, int epoch, long long n,
                      __nv_bfloat16* __restrict__ dst, int* status) {
-  if (!epoch_barrier(flags, rank, world, epoch, status)) return;
+  // epoch <= 0: the caller guarantees the shards are final (they only change at optimizer steps)
+  if (epoch > 0 && !epoch_barrier(flags, rank, world, epoch, status)) return;
   const long long n8 = n >> 3;
   const long long total = n8 * world;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;

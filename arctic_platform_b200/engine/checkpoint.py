@@ -40,8 +40,14 @@ def save_checkpoint(engine, save_dir: str, tag: Optional[str] = None, export_hf:
     d = root / tag
     d.mkdir(parents=True, exist_ok=True)
     files = []
+    module = None
+    if getattr(engine, "zero3", None) is not None:
+        # stage 3: materialising the weights is a collective gather -- every rank takes part, rank 0 keeps the result
+        gathered = ((n, t.detach().to("cpu").clone() if engine.rank == 0 else None) for n, t in engine.iter_hf_tensors())
+        module = OrderedDict(gathered)
     if engine.rank == 0:
-        module = OrderedDict((n, t.detach().to("cpu").clone()) for n, t in engine.iter_hf_tensors())
+        if module is None:
+            module = OrderedDict((n, t.detach().to("cpu").clone()) for n, t in engine.iter_hf_tensors())
         state = {
             "module": module, "buffer_names": [], "optimizer": None,
             "param_shapes": [OrderedDict((n, t.shape) for n, t in module.items())],
@@ -88,7 +94,8 @@ def save_checkpoint(engine, save_dir: str, tag: Optional[str] = None, export_hf:
         (root / "latest").write_text(tag)
         if export_hf:
             from ..models.hf_io import save_hf_checkpoint
-            files += [str(root / "hf" / x) for x in save_hf_checkpoint(engine.model, root / "hf")]
+            tensors = module.items() if getattr(engine, "zero3", None) is not None else None   # gathered above
+            files += [str(root / "hf" / x) for x in save_hf_checkpoint(engine.model, root / "hf", tensors=tensors)]
     _barrier(engine)
     return {"path": str(d), "tag": tag, "files": files}
 
@@ -111,8 +118,26 @@ def load_checkpoint(engine, load_dir: str, tag: Optional[str] = None) -> int:
         raise ValueError(f"checkpoint was written with {state.get('dp_world_size')} data-parallel ranks, this job has "
                          f"{engine.world}; use the hf/ export to change the world size")
     from ..models.hf_io import load_hf_tensor
-    for name, t in state["module"].items():
-        load_hf_tensor(engine.model, name, t)
+    if getattr(engine, "zero3", None) is not None:
+        # stage 3: load into a temporary full buffer, then cut this rank's shard out of it
+        full = torch.empty(engine.total, dtype=engine.param_dtype, device=engine.device)
+        saved = {}
+        for u in engine.units:
+            for name, p in u.params:
+                o, n, shape = engine.param_slices[name]
+                saved[name] = p.data
+                p.data = full[o:o + n].view(shape)
+        try:
+            for name, t in state["module"].items():
+                load_hf_tensor(engine.model, name, t)
+        finally:
+            for u in engine.units:
+                for name, p in u.params:
+                    p.data = saved[name]
+        engine.load_full_flat(full)
+    else:
+        for name, t in state["module"].items():
+            load_hf_tensor(engine.model, name, t)
     engine.global_steps = int(state.get("global_steps", 0))
     engine.micro_steps = int(state.get("micro_steps", 0))
     if not engine.forward_only:

@@ -156,6 +156,9 @@ class TrainEngine:
         self.micro_steps = 0
         self.last_grad_norm = 0.0
         model.gradient_checkpointing = cfg.gradient_checkpointing
+        # stage 3: bf16 parameters exist only as per-rank shards and are gathered unit by unit (engine/zero3.py)
+        self.zero3 = None
+        self._zero3_wanted = cfg.zero_stage >= 3 and self.world > 1
         self._build_flat()
 
     # ------------------------------------------------------------------ layout
@@ -173,6 +176,9 @@ class TrainEngine:
             u.length = _round_up(cur - off, 8 * W)
             off += u.length
         self.total = off
+        if self._zero3_wanted:
+            self._build_zero3()
+            return
         use_symm = self.impl == "fused" and W > 1 and not self.forward_only
         self.param_buf = (SymmetricBuffer(self.total, self.param_dtype, self.device, self.group) if use_symm
                           else SymmetricBuffer(self.total, self.param_dtype, self.device, False))
@@ -213,6 +219,29 @@ class TrainEngine:
         self.reduced = gflat if W == 1 else torch.empty(self.shard_total, dtype=torch.float32, device=self.device)
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
         self._offloaded: Dict[str, torch.Tensor] = {}
+
+    def _build_zero3(self) -> None:
+        from .zero3 import Zero3State
+        use_symm = self.impl == "fused" and self.on_cuda
+        self.flags = EpochFlags(self.device, self.group if use_symm else False) if self.on_cuda else None
+        self.zero3 = Zero3State(self)           # re-points the parameters, fills the shard buffer
+        self.param_buf = self.zero3.shard_buf   # what peers can read of this rank's parameters
+        if self.forward_only:
+            return
+        self.grad_buf = (SymmetricBuffer(self.total, torch.float32, self.device, self.group) if use_symm
+                         else SymmetricBuffer(self.total, torch.float32, self.device, False))
+        gflat = self.grad_buf.tensor
+        for u in self.units:
+            for name, p in u.params:
+                o, n, shape = self.param_slices[name]
+                p.grad_f32 = gflat[o:o + n].view(shape)
+        opt_dev = "cpu" if (self.cfg.offload_optimizer and not self.on_cuda) else self.device
+        self.master = self.zero3.shard_buf.tensor.float().to(opt_dev)
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+        self.reduced = torch.empty(self.shard_total, dtype=torch.float32, device=self.device)
+        self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self._offloaded = {}
 
     # ------------------------------------------------------------------ training loop pieces
     def zero_grad(self) -> None:
@@ -269,6 +298,8 @@ class TrainEngine:
         s = _lib.stream_ptr()
         flags_tbl = self.flags.ptr_table()
         cfg = self.cfg
+        if self.zero3 is not None:
+            return self._step_fused_zero3(lr, bias1, bias2, fn_r, fn_a, fn_w, flags_tbl, s)
         for u, so in zip(self.units, self.unit_shard_off):
             n = u.length // W
             shard_off = r * n
@@ -295,7 +326,57 @@ class TrainEngine:
         if W > 1:
             _lib.check(fn_w(flags_tbl, r, W, self.flags.next(), s), "apb_epoch_wait")
 
+    def _step_fused_zero3(self, lr, bias1, bias2, fn_r, fn_a, fn_w, flags_tbl, s) -> None:
+        """Stage 3: every parameter piece is reduced from all ranks into the owner's shard layout, then ONE AdamW
+        launch per unit updates master, moments and this rank's bf16 shard (no all-gather: peers pull what they need
+        when they materialise a unit)."""
+        cfg = self.cfg
+        z = self.zero3
+        z.reduce_pieces_fused(fn_r, flags_tbl, s)
+        dist.all_reduce(self.sumsq, group=self.group)
+        self._grad_norm_tensor = self.sumsq.sqrt().float().clone()
+        own = (ctypes.c_void_p * 1)()
+        for ui, so in enumerate(self.unit_shard_off):
+            n = z.unit_shard_len[ui]
+            own[0] = z.shard_buf.tensor.data_ptr() + so * 2
+            _lib.check(fn_a(own, ctypes.c_void_p(0), flags_tbl, 0, 1, 0, 0, n, ctypes.c_void_p(self.reduced.data_ptr() + so * 4),
+                            ctypes.c_void_p(self.master.data_ptr() + so * 4),
+                            ctypes.c_void_p(self.exp_avg.data_ptr() + so * 4),
+                            ctypes.c_void_p(self.exp_avg_sq.data_ptr() + so * 4), _lib.ptr(self.sumsq),
+                            lr, cfg.betas[0], cfg.betas[1], cfg.eps, cfg.weight_decay, bias1, bias2,
+                            cfg.max_grad_norm, s), "apb_zero_adamw")
+        # every rank's shard is final before anyone gathers from it
+        _lib.check(fn_w(flags_tbl, self.rank, self.world, self.flags.next(), s), "apb_epoch_wait")
+        z.invalidate()
+
+    def _step_collective_zero3(self, lr, bias1, bias2) -> None:
+        cfg = self.cfg
+        z = self.zero3
+        shards = z.reduced_pieces_collective()
+        sq = sum((g.double() ** 2).sum() for g in shards).reshape(1).to(self.device)
+        dist.all_reduce(sq, group=self.group)
+        norm = sq.sqrt().float()
+        self._grad_norm_tensor = norm.reshape(())
+        clip = torch.clamp(cfg.max_grad_norm / (norm + 1e-6), max=1.0) if cfg.max_grad_norm > 0 else None
+        for ui, (so, g) in enumerate(zip(self.unit_shard_off, shards)):
+            n = z.unit_shard_len[ui]
+            g = g.to(self.master.device)
+            if clip is not None:
+                g = g * clip.to(g.device)
+            m, v, w = self.exp_avg[so:so + n], self.exp_avg_sq[so:so + n], self.master[so:so + n]
+            m.mul_(cfg.betas[0]).add_(g, alpha=1 - cfg.betas[0])
+            v.mul_(cfg.betas[1]).addcmul_(g, g, value=1 - cfg.betas[1])
+            w.mul_(1 - lr * cfg.weight_decay)
+            w.addcdiv_(m / bias1, (v / bias2).sqrt_().add_(cfg.eps), value=-lr)
+            z.shard_buf.tensor[so:so + n].copy_(w.to(self.param_dtype))
+        if self.on_cuda:
+            torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        z.invalidate()
+
     def _step_collective(self, lr, bias1, bias2) -> None:
+        if self.zero3 is not None:
+            return self._step_collective_zero3(lr, bias1, bias2)
         W, r = self.world, self.rank
         cfg = self.cfg
         gflat = self.grad_buf.tensor
@@ -343,19 +424,70 @@ class TrainEngine:
                 dst[:n].copy_(new)
 
     # ------------------------------------------------------------------ introspection
+    def full_flat_params(self) -> torch.Tensor:
+        """All parameters in one flat buffer with the engine's parameter-major layout.  Stages 0-2: the live
+        buffer itself; stage 3: a fresh gather of every unit."""
+        if self.zero3 is None:
+            return self.param_buf.tensor
+        full = torch.empty(self.total, dtype=self.param_dtype, device=self.device)
+        self.zero3.gather_all_into(full)
+        return full
+
     def iter_hf_tensors(self):
         from ..models.hf_io import iter_hf_tensors
-        return iter_hf_tensors(self.model)
+        if self.zero3 is None:
+            return iter_hf_tensors(self.model)
+        return self._iter_hf_tensors_zero3()
+
+    def _iter_hf_tensors_zero3(self):
+        """Stage 3: gathers the parameters into a temporary full buffer, yields the Hugging Face views, then points
+        the parameters back at their gather slots."""
+        from ..models.hf_io import iter_hf_tensors
+        full = self.full_flat_params()
+        saved = {}
+        try:
+            for u in self.units:
+                for name, p in u.params:
+                    o, n, shape = self.param_slices[name]
+                    saved[name] = p.data
+                    p.data = full[o:o + n].view(shape)
+            yield from iter_hf_tensors(self.model)
+        finally:
+            for u in self.units:
+                for name, p in u.params:
+                    if name in saved:
+                        p.data = saved[name]
+
+    @torch.no_grad()
+    def load_full_flat(self, full: torch.Tensor) -> None:
+        """Stage 3: re-shards a full parameter-major buffer into this rank's shard (and the fp32 master copy)."""
+        z = self.zero3
+        r = self.rank
+        for ui, u in enumerate(self.units):
+            base = self.unit_shard_off[ui]
+            for _name, fo, pl, so in z.pieces[ui]:
+                src = full[u.offset + fo + r * pl:u.offset + fo + (r + 1) * pl]
+                z.shard_buf.tensor[base + so:base + so + pl].copy_(src)
+        if not self.forward_only:
+            self.master.copy_(z.shard_buf.tensor.float())
+        if self.on_cuda:
+            torch.cuda.synchronize(self.device)
+        if dist.is_initialized():
+            dist.barrier(group=self.group)
+        z.invalidate()
 
     @torch.no_grad()
     def weight_norm(self) -> Dict[str, float]:
         """Global L2 norm over the real (unpadded) parameters in fp64, as the reference's weight-sync
         check computes it (arctic_platform/common/deepspeed_worker.py:685-704)."""
         sq = torch.zeros((), dtype=torch.float64, device=self.device)
-        n = 0
-        for p in self.model.parameters():
-            sq += p.data.double().pow(2).sum()
-            n += p.numel()
+        n = sum(p.numel() for p in self.model.parameters())
+        if self.zero3 is not None:                       # sum of squares of the shards, added over ranks
+            sq += self.zero3.shard_buf.tensor.double().pow(2).sum()
+            dist.all_reduce(sq, group=self.group)
+        else:
+            for p in self.model.parameters():
+                sq += p.data.double().pow(2).sum()
         return {"norm": float(sq.sqrt().item()), "sq_sum": float(sq.item()), "num_params": n}
 
     # ------------------------------------------------------------------ sleep / wake

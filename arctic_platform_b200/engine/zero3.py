@@ -1,0 +1,229 @@
+"""ZeRO stage 3 for the training engine: bf16 parameters live ONLY as per-rank shards.
+
+Layout.  Every parameter is cut into ``world`` equal flat pieces (row blocks of a weight matrix); rank ``r`` keeps
+piece ``r`` of every parameter of a unit back to back in its shard buffer, which sits in symmetric memory so that
+peers can read it.  The fp32 master weights and Adam moments have the same per-rank layout, so the fused optimizer
+kernel updates master, moments and the bf16 shard in one pass without any all-gather.
+
+Materialisation.  A unit (one decoder block) is rebuilt just in time by ``gather_shards_kernel``: every rank PULLS the
+peers' pieces over NVLink with plain loads into one of two alternating gather slots; a side stream prefetches the next
+unit (forward: i+1, backward: i-1) while the current one computes, and module pre-hooks (forward and backward) wait
+for the slot.  Parameters of unit ``i`` are permanent views into slot ``i % 2``, so tensors autograd saved in the
+forward point at the right bytes again once the backward hook has re-gathered the unit.  The embedding / lm-head
+and the final norm stay gathered (they are touched at both ends of every pass).
+
+Gradients stay full-size in fp32 (accumulated locally over micro-batches); at the step every piece is reduced from
+all ranks by ``zero_reduce_kernel`` straight into the owner's shard layout (reduce-scatter by P2P loads).
+
+CPU / gloo runs use the same bookkeeping with ``all_gather`` / ``all_reduce``, which is what the equivalence test
+against stage 1 exercises.  The reference delegates all of this to DeepSpeed (``zero_optimization.stage: 3``,
+arctic_platform/common/deepspeed_worker.py:208-324).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..parallel.symm import SymmetricBuffer
+
+
+class Zero3State:
+    def __init__(self, engine):
+        self.e = engine
+        W, r = engine.world, engine.rank
+        dev, dt = engine.device, engine.param_dtype
+        self.fused = engine.impl == "fused" and engine.on_cuda
+        # ---- piece tables
+        self.pieces: List[List[Tuple[str, int, int, int]]] = []     # per unit: (name, full_rel_off, piece_len, shard_rel_off)
+        self.unit_shard_len: List[int] = []
+        for u in engine.units:
+            rows, off = [], 0
+            for name, p in u.params:
+                n = p.numel()
+                if n % (8 * W):
+                    raise ValueError(f"ZeRO-3: parameter {name} has {n} elements, not a multiple of 8 x world ({8 * W})")
+                full_off = engine.param_slices[name][0] - u.offset
+                rows.append((name, full_off, n // W, off))
+                off += n // W
+            self.pieces.append(rows)
+            self.unit_shard_len.append(off)
+        engine.unit_shard_off = []
+        acc = 0
+        for n in self.unit_shard_len:
+            engine.unit_shard_off.append(acc)
+            acc += n
+        engine.shard_total = acc
+        # ---- shard buffer (peers read it) filled from the model's current parameters
+        self.shard_buf = SymmetricBuffer(acc, dt, dev, engine.group if self.fused else False)
+        with torch.no_grad():
+            for ui, u in enumerate(engine.units):
+                base = engine.unit_shard_off[ui]
+                pmap = dict(u.params)
+                for name, _fo, pl, so in self.pieces[ui]:
+                    self.shard_buf.tensor[base + so:base + so + pl].copy_(pmap[name].data.reshape(-1)[r * pl:(r + 1) * pl])
+        # ---- gather slots: blocks alternate between two, everything else stays resident
+        self.is_block = [u.name.startswith("block") for u in engine.units]
+        max_block = max([u.length for u, b in zip(engine.units, self.is_block) if b] or [8])
+        self.slots = [torch.empty(max_block, dtype=dt, device=dev) for _ in range(2)]
+        self.slot_content = [-1, -1]
+        self.resident: Dict[int, torch.Tensor] = {}
+        self.block_rank: Dict[int, int] = {}
+        k = 0
+        for ui, u in enumerate(engine.units):
+            if self.is_block[ui]:
+                self.block_rank[ui] = k
+                buf = self.slots[k % 2]
+                k += 1
+            else:
+                buf = torch.empty(u.length, dtype=dt, device=dev)
+                self.resident[ui] = buf
+            for name, p in u.params:
+                o, n, shape = engine.param_slices[name]
+                p.data = buf[o - u.offset:o - u.offset + n].view(shape)
+        self.side = torch.cuda.Stream(device=dev) if engine.on_cuda else None
+        self.ready: List[Optional[torch.cuda.Event]] = [None, None]
+        self.gathers = 0
+        for ui in self.resident:
+            self._gather(ui, self.resident[ui])
+        self._install_hooks()
+
+    # ------------------------------------------------------------------ gather
+    def _gather(self, ui: int, buf: torch.Tensor) -> None:
+        """All pieces of unit ``ui`` from every rank into ``buf`` (full parameter-major layout of the unit)."""
+        e = self.e
+        W = e.world
+        base = e.unit_shard_off[ui]
+        self.gathers += 1
+        if self.fused:
+            fn = _fused_gather()
+            flags = e.flags.ptr_table()
+            s = _lib.stream_ptr()
+            for _name, fo, pl, so in self.pieces[ui]:
+                tbl = self.shard_buf.ptr_table((base + so) * 2)
+                _lib.check(fn(tbl, flags, e.rank, W, 0, pl, ctypes.c_void_p(buf.data_ptr() + fo * 2), s),
+                           "apb_gather_shards")
+            return
+        for _name, fo, pl, so in self.pieces[ui]:
+            mine = self.shard_buf.tensor[base + so:base + so + pl].contiguous()
+            dst = buf[fo:fo + pl * W]
+            if e.on_cuda:
+                dist.all_gather_into_tensor(dst, mine, group=e.group)
+            else:
+                parts = [torch.empty_like(mine) for _ in range(W)]
+                dist.all_gather(parts, mine, group=e.group)
+                for i, p in enumerate(parts):
+                    dst[i * pl:(i + 1) * pl].copy_(p)
+
+    def gather_all_into(self, dst_flat: torch.Tensor) -> None:
+        """Every unit into a full flat buffer with the engine's parameter-major layout (weight sync, checkpoints)."""
+        for ui, u in enumerate(self.e.units):
+            self._gather(ui, dst_flat[u.offset:u.offset + u.length])
+
+    def ensure(self, ui: int) -> None:
+        """Unit ``ui`` is in its slot when this returns (on the current stream)."""
+        if not self.is_block[ui]:
+            return
+        k = self.block_rank[ui] % 2
+        if self.slot_content[k] == ui:
+            if self.ready[k] is not None:
+                torch.cuda.current_stream(self.e.device).wait_event(self.ready[k])
+                self.ready[k] = None
+            return
+        if self.ready[k] is not None:      # an unconsumed prefetch may still be writing this slot
+            torch.cuda.current_stream(self.e.device).wait_event(self.ready[k])
+        self._gather(ui, self.slots[k])
+        self.slot_content[k] = ui
+        self.ready[k] = None
+
+    def prefetch(self, ui: int) -> None:
+        """Starts gathering unit ``ui`` on the side stream; its slot may still be read by work already queued on the
+        main stream (the unit two positions away), so the side stream first waits for the main stream."""
+        if ui < 0 or ui >= len(self.e.units) or not self.is_block[ui]:
+            return
+        k = self.block_rank[ui] % 2
+        if self.slot_content[k] == ui:
+            return
+        if self.side is None or not self.fused:
+            return                       # collectives stay on the main stream: ensure() gathers on demand
+        main = torch.cuda.current_stream(self.e.device)
+        self.side.wait_stream(main)
+        with torch.cuda.stream(self.side):
+            self._gather(ui, self.slots[k])
+            ev = torch.cuda.Event()
+            ev.record(self.side)
+        self.slot_content[k] = ui
+        self.ready[k] = ev
+
+    def invalidate(self) -> None:
+        """After an optimizer step the shards changed: slots are stale, resident units are gathered again."""
+        self.slot_content = [-1, -1]
+        self.ready = [None, None]
+        for ui, buf in self.resident.items():
+            self._gather(ui, buf)
+
+    # ------------------------------------------------------------------ hooks
+    def _install_hooks(self) -> None:
+        blocks = self.e.model.blocks
+        unit_of_block = [ui for ui, b in enumerate(self.is_block) if b]
+
+        def fwd_pre(i):
+            def hook(_mod, _args):
+                ui = unit_of_block[i]
+                self.ensure(ui)
+                if i + 1 < len(unit_of_block):
+                    self.prefetch(unit_of_block[i + 1])
+            return hook
+
+        def bwd_pre(i):
+            def hook(_mod, _grad_out):
+                ui = unit_of_block[i]
+                self.ensure(ui)
+                if i - 1 >= 0:
+                    self.prefetch(unit_of_block[i - 1])
+            return hook
+
+        for i, blk in enumerate(blocks):
+            blk.register_forward_pre_hook(fwd_pre(i))
+            if not self.e.forward_only:
+                blk.register_full_backward_pre_hook(bwd_pre(i))
+
+    # ------------------------------------------------------------------ optimizer step
+    def reduce_pieces_fused(self, fn_r, flags_tbl, s) -> None:
+        e = self.e
+        W, r = e.world, e.rank
+        for ui, u in enumerate(e.units):
+            base = e.unit_shard_off[ui]
+            for _name, fo, pl, so in self.pieces[ui]:
+                gp = e.grad_buf.ptr_table((u.offset + fo) * 4)
+                mc = e.grad_buf.mc_ptr((u.offset + fo) * 4)
+                out = e.reduced.data_ptr() + (base + so) * 4
+                _lib.check(fn_r(gp, mc, flags_tbl, r, W, e.flags.next(), r * pl, pl, 1.0 / W, ctypes.c_void_p(out),
+                                _lib.ptr(e.sumsq), s), "apb_zero_reduce")
+
+    def reduced_pieces_collective(self) -> List[torch.Tensor]:
+        """Per unit: this rank's shard of the averaged gradient (shard layout)."""
+        e = self.e
+        W, r = e.world, e.rank
+        g = e.grad_buf.tensor
+        dist.all_reduce(g, group=e.group)
+        out = []
+        for ui, u in enumerate(e.units):
+            parts = [g[u.offset + fo + r * pl:u.offset + fo + (r + 1) * pl] for _n, fo, pl, _so in self.pieces[ui]]
+            out.append(torch.cat(parts) / W)
+        return out
+
+
+_GATHER = None
+
+
+def _fused_gather():
+    global _GATHER
+    if _GATHER is None:
+        c = ctypes
+        _GATHER = _lib.declare("apb_gather_shards", [c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_longlong,
+                                                      c.c_void_p, c.c_void_p])
+    return _GATHER

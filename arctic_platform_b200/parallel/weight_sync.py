@@ -60,6 +60,13 @@ def flatten_like(model, engine) -> torch.Tensor:
 def sync_flat(engine, dst_flat: torch.Tensor, stream=None) -> int:
     """One-kernel sync from the training engine's parameter buffer into ``dst_flat`` (same layout).
     Returns the number of bytes written."""
+    if getattr(engine, "zero3", None) is not None:
+        # stage 3: the gather of every rank's shards IS the sync -- each unit is pulled from the owners straight
+        # into the sampler's buffer (same parameter-major layout), no intermediate full copy on the trainer
+        if dst_flat.numel() != engine.total or dst_flat.dtype != engine.param_dtype:
+            raise ValueError("destination buffer does not have the trainer's flat layout")
+        engine.zero3.gather_all_into(dst_flat)
+        return dst_flat.numel() * dst_flat.element_size()
     if not dst_flat.is_cuda:
         dst_flat.copy_(engine.param_buf.tensor.to(dst_flat.dtype))
         return dst_flat.numel() * dst_flat.element_size()

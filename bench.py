@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--prompts-per-microbatch", type=int, default=1)
     ap.add_argument("--ref-microbatch-merge", type=int, default=4,
                     help="training micro-batches scored together in one reference (no-grad) forward")
+    ap.add_argument("--zero-stage", type=int, default=3,
+                    help="3: bf16 parameters sharded over ranks and gathered unit by unit; 2: replicated parameters")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--phases", action="store_true", help="print per-phase wall times of the direct step to stderr")
     ap.add_argument("--lr", type=float, default=1e-6)
@@ -143,7 +145,7 @@ def main():
     client_cfg = ArcticRLClientConfig(
         comm_protocol="local", model_name=args.model, training_gpus=world, sampling_gpus=world, log_prob_gpus=world,
         colocate=True, seed=1234,
-        ds_config={"zero_optimization": {"stage": 2}, "gradient_clipping": 1.0,
+        ds_config={"zero_optimization": {"stage": args.zero_stage}, "gradient_clipping": 1.0,
                    "optimizer": {"type": "AdamW", "params": {"lr": args.lr, "betas": [0.9, 0.999], "eps": 1e-8,
                                                              "weight_decay": 0.01}}},
         vllm_config={"kv_cache_tokens": kv_tokens, "max_num_seqs": max(8, B), "max_model_len": P + R + 16},
@@ -310,7 +312,7 @@ def main():
             "impl": "ours",
             "config": {"model": args.model, "global_batch": B * world, "prompts": NP * world, "samples_per_prompt": NS,
                        "seq_len": P + R, "prompt_len": P, "response_len": R,
-                       "parallelism": f"dp{world}-zero2-fused + sampler tp1 x{world} replicas, colocated",
+                       "parallelism": f"dp{world}-zero{args.zero_stage}-fused + sampler tp1 x{world} replicas, colocated",
                        "l2_policy": "inputs larger than L2 (new random prompts and rollouts every step)",
                        "step": "sync_weights+rollout+ref_logprob+fwd_bwd+adamw", "lr": args.lr,
                        "train_microbatches": n_mb},

@@ -158,3 +158,70 @@ def test_tensor_parallel_and_expert_parallel_fused_kernels():
         assert r["ep_inf"] < 0.03 * r["ep_scale"] + 0.02, r
         assert r["ep_dx"] < 0.05, r
         assert r["ep_dw"] < 0.03 * r["ep_dw_scale"] + 0.02, r
+
+
+def _zero3_main(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from arctic_platform_b200.engine.trainer import EngineConfig, TrainEngine
+        from arctic_platform_b200.models.config import PRESETS
+        from arctic_platform_b200.models.decoder import DecoderLM, token_logprobs
+        from arctic_platform_b200.ops import _lib
+        from arctic_platform_b200.parallel.weight_sync import sync_flat
+        from arctic_platform_b200.rl.zorro_train.layout import build_packed_batch
+        from tests.test_zorro_equivalence_cpu import make_grpo_batch
+        ids, mask, R = make_grpo_batch(n_prompts=4, n_samples=4, p_rng=(40, 200), r_rng=(10, 80), seed=9)
+        B = ids.shape[0]
+        sl = slice(rank * B // world, (rank + 1) * B // world)
+        half = (sl.stop - sl.start) // 2
+        mbs = [build_packed_batch(ids[m], mask[m], R).to("cuda")
+               for m in (slice(sl.start, sl.start + half), slice(sl.start + half, sl.stop))]
+        res = {}
+        for name, stage, impl in (("z1", 1, "fused"), ("z3", 3, "fused"), ("z3c", 3, "collective")):
+            model = DecoderLM(PRESETS["qwen3-tiny-d128"], "cuda", torch.bfloat16).init_weights(seed=11)
+            eng = TrainEngine(model, EngineConfig(lr=1e-3, weight_decay=0.01, max_grad_norm=0.5, impl=impl, zero_stage=stage))
+            norms, losses = [], []
+            for _step in range(2):
+                for i, pb in enumerate(mbs):                      # two micro-batches per step (slots are re-gathered)
+                    a = torch.randn(pb.labels.shape[0], generator=torch.Generator().manual_seed(2 + rank + 10 * i)).cuda()
+                    lp, _ = token_logprobs(eng.model, pb, 1.0)
+                    loss = -(lp * a).mean()
+                    eng.backward(loss)
+                    losses.append(float(loss))
+                norms.append(float(eng.step()["grad_norm"]))
+            with torch.no_grad():
+                lp_after, _ = token_logprobs(eng.model, mbs[0], 1.0)
+            full = eng.full_flat_params().float().cpu()
+            if stage == 3:
+                dst = torch.zeros(eng.total, dtype=torch.bfloat16, device="cuda")
+                sync_flat(eng, dst)
+                assert torch.equal(dst.float().cpu(), full)
+                assert eng.zero3.shard_buf.tensor.numel() * world <= eng.total
+            _lib.check_status(name)
+            res[name] = (full, norms, losses, lp_after.float().cpu(), eng.weight_norm()["norm"])
+        torch.save(res, os.path.join(out_dir, f"z{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_zero3_sharded_parameters_match_replicated_on_two_gpus():
+    """Stage 3 (sharded bf16 parameters, units pulled from peers on a side stream, per-piece P2P reduce) against the
+    replicated stage-1 engine: same losses, gradient norms, updated weights and weight norm."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_zero3_main, args=(2, _free_port(), d), nprocs=2, join=True)
+        res = [torch.load(os.path.join(d, f"z{r}.pt"), weights_only=False) for r in range(2)]
+    for r in res:
+        for other in ("z3", "z3c"):
+            assert all(abs(a - b) <= 2e-2 * abs(b) + 1e-4 for a, b in zip(r[other][1], r["z1"][1])), (r[other][1], r["z1"][1])
+            assert all(abs(a - b) <= 2e-2 * abs(b) + 2e-3 for a, b in zip(r[other][2], r["z1"][2]))
+            assert (r[other][0] - r["z1"][0]).abs().max() < 2e-2
+            assert (r[other][3] - r["z1"][3]).abs().max() < 0.05
+            assert abs(r[other][4] - r["z1"][4]) <= 1e-3 * r["z1"][4]
+    assert torch.equal(res[0]["z3"][0], res[1]["z3"][0])
