@@ -34,8 +34,26 @@ class DecoderConfig:
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    shared_expert_intermediate_size: int = 0     # > 0: a dense SwiGLU expert with a sigmoid gate beside the routed ones
+    # hybrid (Qwen3.5 / Qwen3-Next) features; the defaults describe plain Qwen3
+    layer_types: Optional[tuple] = None          # per layer "full_attention" | "linear_attention"
+    partial_rotary_factor: float = 1.0           # fraction of head_dim that is rotated
+    attn_output_gate: bool = False               # attention output multiplied by sigmoid(gate(x)) before o_proj
+    norm_one_plus: bool = False                  # RMSNorm weight stored as (w - 1)
+    linear_num_key_heads: int = 0
+    linear_num_value_heads: int = 0
+    linear_key_head_dim: int = 0
+    linear_value_head_dim: int = 0
+    linear_conv_kernel_dim: int = 4
     model_type: str = "qwen3"
     name: str = "qwen3"
+
+    def layer_type(self, i: int) -> str:
+        return "full_attention" if self.layer_types is None else self.layer_types[i]
+
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor)
 
     @property
     def q_size(self) -> int:
@@ -83,6 +101,7 @@ class DecoderConfig:
     def from_hf_dict(d: Dict[str, Any], name: str = "") -> "DecoderConfig":
         mt = d.get("model_type", "qwen3")
         heads = d["num_attention_heads"]
+        hybrid = mt in HYBRID_MODEL_TYPES
         return DecoderConfig(
             vocab_size=d["vocab_size"], hidden_size=d["hidden_size"],
             intermediate_size=d.get("intermediate_size", 0), num_layers=d["num_hidden_layers"],
@@ -92,7 +111,15 @@ class DecoderConfig:
             qk_norm=mt.startswith("qwen3"), max_position_embeddings=d.get("max_position_embeddings", 40960),
             num_experts=d.get("num_experts", 0) or 0, num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0,
-            norm_topk_prob=bool(d.get("norm_topk_prob", True)), model_type=mt, name=name or mt)
+            norm_topk_prob=bool(d.get("norm_topk_prob", True)),
+            shared_expert_intermediate_size=d.get("shared_expert_intermediate_size", 0) or 0,
+            layer_types=_hybrid_layer_types(d), partial_rotary_factor=float(d.get("partial_rotary_factor", 1.0)),
+            attn_output_gate=hybrid, norm_one_plus=hybrid,
+            linear_num_key_heads=d.get("linear_num_key_heads", 0) or 0,
+            linear_num_value_heads=d.get("linear_num_value_heads", 0) or 0,
+            linear_key_head_dim=d.get("linear_key_head_dim", 0) or 0,
+            linear_value_head_dim=d.get("linear_value_head_dim", 0) or 0,
+            linear_conv_kernel_dim=d.get("linear_conv_kernel_dim", 4) or 4, model_type=mt, name=name or mt)
 
     def to_hf_dict(self) -> Dict[str, Any]:
         d = {
@@ -108,7 +135,28 @@ class DecoderConfig:
         if self.is_moe:
             d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob)
+        if self.layer_types is not None:
+            d.update(model_type=self.model_type, architectures=["Qwen3_5MoeForCausalLM" if self.is_moe else "Qwen3NextForCausalLM"],
+                     layer_types=list(self.layer_types), partial_rotary_factor=self.partial_rotary_factor,
+                     linear_num_key_heads=self.linear_num_key_heads, linear_num_value_heads=self.linear_num_value_heads,
+                     linear_key_head_dim=self.linear_key_head_dim, linear_value_head_dim=self.linear_value_head_dim,
+                     linear_conv_kernel_dim=self.linear_conv_kernel_dim,
+                     shared_expert_intermediate_size=self.shared_expert_intermediate_size)
         return d
+
+
+HYBRID_MODEL_TYPES = ("qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text")
+
+
+def _hybrid_layer_types(d: Dict[str, Any]) -> Optional[tuple]:
+    """Hybrid checkpoints list the type of every layer, or give ``full_attention_interval`` (every n-th layer is
+    full attention, the others linear attention)."""
+    if d.get("model_type") not in HYBRID_MODEL_TYPES:
+        return None
+    if d.get("layer_types"):
+        return tuple(d["layer_types"])
+    n = int(d.get("full_attention_interval", 4))
+    return tuple("full_attention" if (i + 1) % n == 0 else "linear_attention" for i in range(d["num_hidden_layers"]))
 
 
 PRESETS: Dict[str, DecoderConfig] = {
@@ -131,6 +179,16 @@ PRESETS: Dict[str, DecoderConfig] = {
     "qwen3-30b-a3b": DecoderConfig(hidden_size=2048, intermediate_size=6144, num_layers=48, num_heads=32,
                                    num_kv_heads=4, tie_word_embeddings=False, num_experts=128, num_experts_per_tok=8,
                                    moe_intermediate_size=768, model_type="qwen3_moe", name="qwen3-30b-a3b"),
+    # hybrid family at test size: 3 of 4 layers are gated-delta-net linear attention, gated full attention with
+    # partial rotary, (1+w) norms, routed experts plus a sigmoid-gated shared expert
+    "qwen3.5-moe-tiny": DecoderConfig(vocab_size=32000, hidden_size=128, intermediate_size=256, num_layers=4,
+                                      num_heads=4, num_kv_heads=2, head_dim=64, num_experts=4, num_experts_per_tok=2,
+                                      moe_intermediate_size=64, shared_expert_intermediate_size=64,
+                                      layer_types=("linear_attention", "linear_attention", "linear_attention",
+                                                   "full_attention"),
+                                      partial_rotary_factor=0.25, attn_output_gate=True, norm_one_plus=True,
+                                      linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
+                                      linear_value_head_dim=32, model_type="qwen3_5_moe_text", name="qwen3.5-moe-tiny"),
     "qwen3-moe-tiny": DecoderConfig(vocab_size=32000, hidden_size=256, intermediate_size=688, num_layers=2,
                                     num_heads=4, num_kv_heads=2, head_dim=128, num_experts=8, num_experts_per_tok=2,
                                     moe_intermediate_size=128, model_type="qwen3_moe", name="qwen3-moe-tiny"),

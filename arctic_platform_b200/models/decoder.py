@@ -63,6 +63,28 @@ def gate_up_act(x: torch.Tensor, wgu: torch.Tensor) -> torch.Tensor:
     return _GateUpSwiGLUFn.apply(x, wgu)
 
 
+def _qknorm_partial_rope(qkv, wq, wk, rope, positions, cfg: DecoderConfig, w_offset: float):
+    """q/k RMSNorm (optionally with the (1+w) parameterisation) and rotate-half RoPE on the first ``rotary_dim``
+    dimensions of every head -- PyTorch ops; the fused kernel covers the full-rotation, plain-weight case."""
+    T = qkv.shape[0]
+    Hq, Hkv, D, rd = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.rotary_dim
+    q = qkv[:, :Hq * D].reshape(T, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].reshape(T, Hkv, D)
+    cos_t, sin_t = rope
+    pos = positions.long()
+    c, s = cos_t[pos][:, None, :rd // 2], sin_t[pos][:, None, :rd // 2]
+
+    def one(x, w):
+        xf = x.float()
+        if w is not None:
+            xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * (w.float() + w_offset)
+        a, b, rest = xf[..., :rd // 2], xf[..., rd // 2:rd], xf[..., rd:]
+        return torch.cat([a * c - b * s, b * c + a * s, rest], -1).to(x.dtype)
+
+    return one(q, wq), one(k, wk), v
+
+
 class DecoderBlock(nn.Module):
     def __init__(self, cfg: DecoderConfig, layer_idx: int, device, dtype):
         super().__init__()
@@ -71,10 +93,19 @@ class DecoderBlock(nn.Module):
         H, D = cfg.hidden_size, cfg.head_dim
         mk = lambda *s: nn.Parameter(torch.empty(*s, device=device, dtype=dtype))
         self.ln1 = mk(H)
-        self.wqkv = mk(cfg.qkv_size, H)
-        self.q_norm = mk(D) if cfg.qk_norm else None
-        self.k_norm = mk(D) if cfg.qk_norm else None
-        self.wo = mk(H, cfg.q_size)
+        self.kind = cfg.layer_type(layer_idx)
+        self.w_offset = 1.0 if cfg.norm_one_plus else 0.0
+        if self.kind == "linear_attention":
+            from .linear_attention import GatedDeltaNet
+            self.linear_attn = GatedDeltaNet(cfg, device, dtype)
+            self.wqkv = self.q_norm = self.k_norm = self.wo = self.wgate = None
+        else:
+            self.linear_attn = None
+            self.wqkv = mk(cfg.qkv_size, H)
+            self.wgate = mk(cfg.q_size, H) if cfg.attn_output_gate else None
+            self.q_norm = mk(D) if cfg.qk_norm else None
+            self.k_norm = mk(D) if cfg.qk_norm else None
+            self.wo = mk(H, cfg.q_size)
         self.ln2 = mk(H)
         if cfg.is_moe:
             from .moe import MoEFeedForward
@@ -89,17 +120,26 @@ class DecoderBlock(nn.Module):
         """``x`` is the previous sublayer output, ``stream`` the residual stream before adding it
         (None for the first block).  Returns the MLP output and the updated stream."""
         cfg = self.cfg
-        h, stream = norm.rmsnorm(x, self.ln1, cfg.rms_norm_eps, stream)
-        qkv = gemm.linear(h, self.wqkv)
-        q, k, v = norm.qknorm_rope(qkv, self.q_norm, self.k_norm, rope[0], rope[1], positions, cfg.num_heads,
-                                   cfg.num_kv_heads, cfg.head_dim, cfg.rms_norm_eps)
-        if getattr(self, "sp_group", None) is not None:
-            from ..parallel.ulysses import ulysses_attention
-            a = ulysses_attention(q, k, v, layout, self.sp_group)
+        h, stream = norm.rmsnorm(x, self.ln1, cfg.rms_norm_eps, stream, self.w_offset)
+        if self.linear_attn is not None:
+            o = self.linear_attn(h, layout)
         else:
-            a = segment_attention(q, k, v, layout)
-        o = gemm.linear(a.reshape(a.shape[0], -1), self.wo)
-        h2, stream = norm.rmsnorm(o, self.ln2, cfg.rms_norm_eps, stream)
+            qkv = gemm.linear(h, self.wqkv)
+            if cfg.rotary_dim != cfg.head_dim or self.w_offset:
+                q, k, v = _qknorm_partial_rope(qkv, self.q_norm, self.k_norm, rope, positions, cfg, self.w_offset)
+            else:
+                q, k, v = norm.qknorm_rope(qkv, self.q_norm, self.k_norm, rope[0], rope[1], positions, cfg.num_heads,
+                                           cfg.num_kv_heads, cfg.head_dim, cfg.rms_norm_eps)
+            if getattr(self, "sp_group", None) is not None:
+                from ..parallel.ulysses import ulysses_attention
+                a = ulysses_attention(q, k, v, layout, self.sp_group)
+            else:
+                a = segment_attention(q, k, v, layout)
+            a = a.reshape(a.shape[0], -1)
+            if self.wgate is not None:
+                a = (a.float() * torch.sigmoid(gemm.linear(h, self.wgate).float())).to(a.dtype)
+            o = gemm.linear(a, self.wo)
+        h2, stream = norm.rmsnorm(o, self.ln2, cfg.rms_norm_eps, stream, self.w_offset)
         if self.mlp is not None:
             d = self.mlp(h2)
         else:
@@ -127,8 +167,12 @@ class DecoderLM(nn.Module):
         """Deterministic normal(0, std) init keyed by parameter name, so the values do not depend on
         how the model is later sharded (norm weights are ones)."""
         for name, p in self.named_parameters():
+            if name.endswith("A_log") or name.endswith("dt_bias"):
+                p.copy_(torch.linspace(-1.0, 1.0, p.numel()).to(p.dtype))      # decays spread over the heads
+                continue
             if p.dim() == 1 and not name.endswith("router_bias"):
-                p.fill_(1.0)
+                is_plain = name.endswith("norm_w") or not self.cfg.norm_one_plus
+                p.fill_(1.0 if is_plain else 0.0)                              # (1+w) norms store w - 1
                 continue
             g = torch.Generator(device="cpu")
             g.manual_seed((hash_name(name) + seed) % (2 ** 31))
@@ -144,7 +188,7 @@ class DecoderLM(nn.Module):
         if dev.type == "cuda" and dev.index is None:
             dev = torch.device("cuda", torch.cuda.current_device())
         if self._rope is None or self._rope[0].device != dev:
-            self._rope = norm.rope_tables(self._rope_len, self.cfg.head_dim, self.cfg.rope_theta, dev)
+            self._rope = norm.rope_tables(self._rope_len, self.cfg.rotary_dim, self.cfg.rope_theta, dev)
         return self._rope
 
     @property
@@ -164,7 +208,7 @@ class DecoderLM(nn.Module):
                 x, stream = checkpoint(blk, x, stream, positions, layout, rope, use_reentrant=False)
             else:
                 x, stream = blk(x, stream, positions, layout, rope)
-        h, _ = norm.rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, stream)
+        h, _ = norm.rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, stream, 1.0 if self.cfg.norm_one_plus else 0.0)
         return h
 
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:

@@ -28,18 +28,33 @@ def split_gate_up(wgu: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return wgu[0::2], wgu[1::2]
 
 
+# Hugging Face names inside ``linear_attn.`` (split-projection layout) -> attribute of GatedDeltaNet
+LINEAR_ATTN_NAMES = ("in_proj_qkv.weight", "in_proj_z.weight", "in_proj_b.weight", "in_proj_a.weight", "conv1d.weight",
+                     "dt_bias", "A_log", "norm.weight", "out_proj.weight")
+_LINEAR_ATTN_ATTR = {"in_proj_qkv.weight": "in_qkv", "in_proj_z.weight": "in_z", "in_proj_b.weight": "in_b",
+                     "in_proj_a.weight": "in_a", "conv1d.weight": "conv_w", "dt_bias": "dt_bias", "A_log": "A_log",
+                     "norm.weight": "norm_w", "out_proj.weight": "out_proj"}
+
+
 def hf_param_names(cfg: DecoderConfig) -> List[str]:
     """Every Hugging Face tensor name of the architecture, in layer order."""
     names = ["model.embed_tokens.weight"]
     for i in range(cfg.num_layers):
         p = f"model.layers.{i}."
-        names += [p + "input_layernorm.weight", p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight",
-                  p + "self_attn.v_proj.weight"]
-        if cfg.qk_norm:
-            names += [p + "self_attn.q_norm.weight", p + "self_attn.k_norm.weight"]
-        names += [p + "self_attn.o_proj.weight", p + "post_attention_layernorm.weight"]
+        names.append(p + "input_layernorm.weight")
+        if cfg.layer_type(i) == "linear_attention":
+            names += [p + "linear_attn." + n for n in LINEAR_ATTN_NAMES]
+        else:
+            names += [p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight", p + "self_attn.v_proj.weight"]
+            if cfg.qk_norm:
+                names += [p + "self_attn.q_norm.weight", p + "self_attn.k_norm.weight"]
+            names.append(p + "self_attn.o_proj.weight")
+        names.append(p + "post_attention_layernorm.weight")
         if cfg.is_moe:
             names.append(p + "mlp.gate.weight")
+            if cfg.shared_expert_intermediate_size > 0:
+                names += [p + "mlp.shared_expert.gate_proj.weight", p + "mlp.shared_expert.up_proj.weight",
+                          p + "mlp.shared_expert.down_proj.weight", p + "mlp.shared_expert_gate.weight"]
             for e in range(cfg.num_experts):
                 names += [p + f"mlp.experts.{e}.gate_proj.weight", p + f"mlp.experts.{e}.up_proj.weight",
                           p + f"mlp.experts.{e}.down_proj.weight"]
@@ -60,17 +75,34 @@ def iter_hf_tensors(model) -> Iterator[Tuple[str, torch.Tensor]]:
     for i, blk in enumerate(model.blocks):
         p = f"model.layers.{i}."
         yield p + "input_layernorm.weight", blk.ln1.data
-        w = blk.wqkv.data
-        yield p + "self_attn.q_proj.weight", w[:qs]
-        yield p + "self_attn.k_proj.weight", w[qs:qs + ks]
-        yield p + "self_attn.v_proj.weight", w[qs + ks:]
-        if cfg.qk_norm:
-            yield p + "self_attn.q_norm.weight", blk.q_norm.data
-            yield p + "self_attn.k_norm.weight", blk.k_norm.data
-        yield p + "self_attn.o_proj.weight", blk.wo.data
+        if getattr(blk, "linear_attn", None) is not None:
+            for n in LINEAR_ATTN_NAMES:
+                t = getattr(blk.linear_attn, _LINEAR_ATTN_ATTR[n]).data
+                yield p + "linear_attn." + n, (t.unsqueeze(1) if n == "conv1d.weight" else t)
+        else:
+            w = blk.wqkv.data
+            if getattr(blk, "wgate", None) is not None:
+                # one projection on disk: per head [query rows | gate rows]
+                D, H = cfg.head_dim, w.shape[1]
+                both = torch.stack([w[:qs].view(cfg.num_heads, D, H), blk.wgate.data.view(cfg.num_heads, D, H)], 1)
+                yield p + "self_attn.q_proj.weight", both.reshape(2 * qs, H)
+            else:
+                yield p + "self_attn.q_proj.weight", w[:qs]
+            yield p + "self_attn.k_proj.weight", w[qs:qs + ks]
+            yield p + "self_attn.v_proj.weight", w[qs + ks:]
+            if cfg.qk_norm:
+                yield p + "self_attn.q_norm.weight", blk.q_norm.data
+                yield p + "self_attn.k_norm.weight", blk.k_norm.data
+            yield p + "self_attn.o_proj.weight", blk.wo.data
         yield p + "post_attention_layernorm.weight", blk.ln2.data
         if cfg.is_moe:
             yield p + "mlp.gate.weight", blk.mlp.router.data
+            if blk.mlp.shared_wgu is not None:
+                g, u = split_gate_up(blk.mlp.shared_wgu.data)
+                yield p + "mlp.shared_expert.gate_proj.weight", g
+                yield p + "mlp.shared_expert.up_proj.weight", u
+                yield p + "mlp.shared_expert.down_proj.weight", blk.mlp.shared_wdown.data
+                yield p + "mlp.shared_expert_gate.weight", blk.mlp.shared_gate.data
             for e in range(cfg.num_experts):
                 g, u = split_gate_up(blk.mlp.wgu.data[e])
                 yield p + f"mlp.experts.{e}.gate_proj.weight", g
@@ -114,6 +146,23 @@ def load_hf_tensor(model, name: str, tensor: torch.Tensor) -> None:
         return put(blk.ln1.data, tensor)
     if rest == "post_attention_layernorm.weight":
         return put(blk.ln2.data, tensor)
+    if parts[3] == "linear_attn":
+        sub = ".".join(parts[4:])
+        dst = getattr(blk.linear_attn, _LINEAR_ATTN_ATTR[sub]).data
+        return put(dst, tensor.squeeze(1) if sub == "conv1d.weight" else tensor)
+    if rest == "self_attn.q_proj.weight" and getattr(blk, "wgate", None) is not None:
+        D, H = cfg.head_dim, tensor.shape[1]
+        both = tensor.view(cfg.num_heads, 2, D, H)
+        put(blk.wqkv.data[:qs], both[:, 0].reshape(qs, H))
+        return put(blk.wgate.data, both[:, 1].reshape(qs, H))
+    if rest == "mlp.shared_expert.gate_proj.weight":
+        return put(blk.mlp.shared_wgu.data[0::2], tensor)
+    if rest == "mlp.shared_expert.up_proj.weight":
+        return put(blk.mlp.shared_wgu.data[1::2], tensor)
+    if rest == "mlp.shared_expert.down_proj.weight":
+        return put(blk.mlp.shared_wdown.data, tensor)
+    if rest == "mlp.shared_expert_gate.weight":
+        return put(blk.mlp.shared_gate.data, tensor)
     if rest == "self_attn.q_proj.weight":
         return put(blk.wqkv.data[:qs], tensor)
     if rest == "self_attn.k_proj.weight":

@@ -1,0 +1,172 @@
+"""Gated DeltaNet linear attention (the "linear_attention" layers of the Qwen3.5 / Qwen3-Next hybrids).
+
+Per head, with key/query dimension ``Dk``, value dimension ``Dv`` and state ``S`` of shape ``[Dk, Dv]``:
+
+    alpha_t = exp(g_t)                       (g_t <= 0: learned decay)
+    S'      = alpha_t * S_{t-1}
+    S_t     = S' + beta_t * k_t (v_t - S'^T k_t)^T          (delta rule: correct the value stored under k_t)
+    o_t     = S_t^T q_t / sqrt(Dk)
+
+with L2-normalised ``q_t, k_t``.  ``gated_delta_rule_recurrent`` is that recurrence token by token (the oracle);
+``gated_delta_rule_chunked`` evaluates it 64 tokens at a time: inside a chunk the corrections form a unit lower
+triangular system that is solved once (forward substitution), the carried state enters through two matmuls, and the
+state advances once per chunk -- the algorithm of the reference's ``torch_chunk_gated_delta_rule``
+(arctic_platform/model/implementations/qwen35/models/qwen3_5_moe/modeling_qwen3_5_moe.py:73-1086).
+
+``GatedDeltaNet`` is the layer: fused input projections, a causal depth-wise convolution (kernel 4) over q/k/v, the
+rule above, a gated RMSNorm (``norm(o) * silu(z)``) and the output projection.  It runs on the packed token axis and
+takes its sequence structure from the attention layout: every segment starts from the final (convolution, recurrent)
+state of its prefix segment, so a prompt shared by several rollouts is processed once (prompt reuse as in
+arctic_platform/rl/zorro_train/qwen_attention_patcher.py:589-752).  All math is PyTorch ops (fp32 state); there is
+no hand-written kernel for this family yet.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ..ops import gemm
+
+
+def _l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    return x * torch.rsqrt(x.pow(2).sum(-1, keepdim=True) + eps)
+
+
+def gated_delta_rule_recurrent(q, k, v, g, beta, state: Optional[torch.Tensor] = None, l2norm: bool = True
+                               ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``q, k [T, H, Dk]``, ``v [T, H, Dv]``, ``g, beta [T, H]`` -> ``(o [T, H, Dv], final state [H, Dk, Dv])``."""
+    T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    q, k, v, g, beta = (x.float() for x in (q, k, v, g, beta))
+    if l2norm:
+        q, k = _l2norm(q), _l2norm(k)
+    q = q * Dk ** -0.5
+    S = torch.zeros(H, Dk, Dv, dtype=torch.float32, device=q.device) if state is None else state.float().clone()
+    out = []
+    for t in range(T):
+        S = S * torch.exp(g[t])[:, None, None]
+        pred = torch.einsum("hkv,hk->hv", S, k[t])
+        S = S + torch.einsum("hk,hv->hkv", k[t] * beta[t][:, None], v[t] - pred)
+        out.append(torch.einsum("hkv,hk->hv", S, q[t]))
+    o = torch.stack(out) if out else v.new_zeros((0, H, Dv), dtype=torch.float32)
+    return o, S
+
+
+def gated_delta_rule_chunked(q, k, v, g, beta, state: Optional[torch.Tensor] = None, l2norm: bool = True,
+                             chunk: int = 64) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Same contract as the recurrent form, ``chunk`` tokens per step (differentiable)."""
+    T, H, Dk = q.shape
+    Dv = v.shape[-1]
+    if T == 0:
+        S0 = torch.zeros(H, Dk, Dv, dtype=torch.float32, device=q.device) if state is None else state.float()
+        return v.new_zeros((0, H, Dv), dtype=torch.float32), S0
+    q, k, v, g, beta = (x.float().transpose(0, 1) for x in (q, k, v, g, beta))          # [H, T, ...]
+    if l2norm:
+        q, k = _l2norm(q), _l2norm(k)
+    q = q * Dk ** -0.5
+    pad = (-T) % chunk
+    if pad:
+        q, k, v = (F.pad(x, (0, 0, 0, pad)) for x in (q, k, v))
+        g, beta = F.pad(g, (0, pad)), F.pad(beta, (0, pad))
+    N = (T + pad) // chunk
+    q, k, v = (x.reshape(H, N, chunk, -1) for x in (q, k, v))
+    g = g.reshape(H, N, chunk).cumsum(-1)                                                   # log decay since chunk start
+    beta = beta.reshape(H, N, chunk)
+    kb, vb = k * beta[..., None], v * beta[..., None]
+    # decay between positions j <= i of a chunk
+    diff = g[..., :, None] - g[..., None, :]
+    tril = torch.tril(torch.ones(chunk, chunk, dtype=torch.bool, device=q.device))
+    decay = torch.where(tril, torch.exp(torch.where(tril, diff, torch.zeros_like(diff))), torch.zeros_like(diff))
+    # corrections inside a chunk: (I + A) u = rhs with A strictly lower triangular -> u = (I + A)^{-1} rhs
+    A = (kb @ k.transpose(-1, -2)) * decay
+    A = A.masked_fill(~torch.tril(tril, -1), 0.0)
+    eye = torch.eye(chunk, device=q.device, dtype=torch.float32)
+    Tinv = torch.linalg.solve_triangular(eye + A, eye.expand_as(A).contiguous(), upper=False)
+    u_local = Tinv @ vb                                     # corrected values if the carried state were zero
+    w_state = Tinv @ (kb * torch.exp(g)[..., None])         # how the carried state enters the corrections
+    S = torch.zeros(H, Dk, Dv, dtype=torch.float32, device=q.device) if state is None else state.float()
+    outs = []
+    qk = (q @ k.transpose(-1, -2)) * decay                  # causal (diagonal included) intra-chunk scores
+    for n in range(N):
+        u = u_local[:, n] - w_state[:, n] @ S               # value corrections of this chunk given the carried state
+        o = (q[:, n] * torch.exp(g[:, n])[..., None]) @ S + qk[:, n] @ u
+        outs.append(o)
+        g_end = g[:, n, -1]
+        S = S * torch.exp(g_end)[:, None, None] + (k[:, n] * torch.exp(g_end[:, None] - g[:, n])[..., None]).transpose(-1, -2) @ u
+    o = torch.stack(outs, 1).reshape(H, N * chunk, Dv)[:, :T].transpose(0, 1)
+    if pad:
+        # padded steps have g = 0, beta = 0: they leave the state unchanged
+        pass
+    return o, S
+
+
+def causal_conv1d(x: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor] = None
+                  ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Depth-wise causal convolution along tokens.  ``x [T, C]``, ``w [C, K]``, ``state [K-1, C]`` = the last
+    ``K-1`` inputs of the preceding context (zeros at a sequence start).  Returns ``(y [T, C], new state)``."""
+    K = w.shape[1]
+    hist = x.new_zeros((K - 1, x.shape[1])) if state is None else state.to(x.dtype)
+    xx = torch.cat([hist, x], 0)                             # [T + K - 1, C]
+    y = F.conv1d(xx.t()[None].float(), w[:, None, :].float(), groups=w.shape[0])[0].t()
+    return y.to(x.dtype), xx[-(K - 1):]
+
+
+class GatedDeltaNet(nn.Module):
+    def __init__(self, cfg, device, dtype):
+        super().__init__()
+        self.cfg = cfg
+        H = cfg.hidden_size
+        self.Hk, self.Hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        self.Dk, self.Dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        self.key_dim, self.value_dim = self.Hk * self.Dk, self.Hv * self.Dv
+        self.conv_dim = 2 * self.key_dim + self.value_dim
+        mk = lambda *s: nn.Parameter(torch.empty(*s, device=device, dtype=dtype))
+        self.in_qkv = mk(self.conv_dim, H)
+        self.in_z = mk(self.value_dim, H)
+        self.in_b = mk(self.Hv, H)
+        self.in_a = mk(self.Hv, H)
+        self.conv_w = mk(self.conv_dim, cfg.linear_conv_kernel_dim)
+        self.dt_bias = mk(self.Hv)
+        self.A_log = mk(self.Hv)
+        self.norm_w = mk(self.Dv)
+        self.out_proj = mk(H, self.value_dim)
+        self.chunk = 64
+
+    def forward(self, x: torch.Tensor, layout) -> torch.Tensor:
+        """``x [T, H]`` on the packed axis -> ``[T, H]``."""
+        T = x.shape[0]
+        mixed = gemm.linear(x, self.in_qkv)
+        z = gemm.linear(x, self.in_z).view(T, self.Hv, self.Dv)
+        b = x.float() @ self.in_b.float().t()
+        a = x.float() @ self.in_a.float().t()
+        beta = torch.sigmoid(b)
+        g = -torch.exp(self.A_log.float()) * F.softplus(a + self.dt_bias.float())
+        out = x.new_zeros((T, self.Hv, self.Dv), dtype=torch.float32)
+        final: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}          # end row of a key range -> states after it
+        rep = self.Hv // self.Hk
+        for qs, ql, ps, pl, os_, ol in layout.segs.tolist():
+            if ol == 0:
+                continue
+            init = final.get(ps + pl) if pl > 0 else None
+            if pl > 0 and init is None:
+                raise ValueError("linear attention: a segment's prefix range must be an earlier segment's own range")
+            conv_state, S = init if init is not None else (None, None)
+            sl = slice(os_, os_ + ol)
+            y, conv_new = causal_conv1d(mixed[sl], self.conv_w, conv_state)
+            y = F.silu(y)
+            q = y[:, :self.key_dim].reshape(ol, self.Hk, self.Dk)
+            k = y[:, self.key_dim:2 * self.key_dim].reshape(ol, self.Hk, self.Dk)
+            v = y[:, 2 * self.key_dim:].reshape(ol, self.Hv, self.Dv)
+            if rep > 1:
+                q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+            o, S_new = gated_delta_rule_chunked(q, k, v, g[sl], beta[sl], S, chunk=self.chunk)
+            final[os_ + ol] = (conv_new, S_new)
+            # the segment's query rows are the last ``ql`` rows of its own range
+            out = out.index_put((torch.arange(qs, qs + ql, device=x.device),), o[ol - ql:])
+        # gated RMSNorm: norm(o) * w * silu(z)
+        o = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + self.cfg.rms_norm_eps) * self.norm_w.float()
+        o = (o * F.silu(z.float())).to(x.dtype)
+        return gemm.linear(o.reshape(T, self.value_dim), self.out_proj)

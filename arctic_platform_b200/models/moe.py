@@ -128,10 +128,26 @@ class MoEFeedForward(nn.Module):
         self.router = nn.Parameter(torch.empty(E, H, device=device, dtype=dtype))
         self.wgu = nn.Parameter(torch.empty(E, 2 * I, H, device=device, dtype=dtype))
         self.wdown = nn.Parameter(torch.empty(E, H, I, device=device, dtype=dtype))
+        S = cfg.shared_expert_intermediate_size
+        if S > 0:       # dense expert every token passes through, scaled by a per-token sigmoid gate
+            self.shared_wgu = nn.Parameter(torch.empty(2 * S, H, device=device, dtype=dtype))
+            self.shared_wdown = nn.Parameter(torch.empty(H, S, device=device, dtype=dtype))
+            self.shared_gate = nn.Parameter(torch.empty(1, H, device=device, dtype=dtype))
+        else:
+            self.shared_wgu = self.shared_wdown = self.shared_gate = None
         self.ep = None  # set by parallel.expert_parallel.attach() when experts are sharded over ranks
         self.last_tokens_per_expert: Optional[torch.Tensor] = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self._routed(x)
+        if self.shared_wgu is not None:
+            from .decoder import gate_up_act
+            shared = gemm.linear(gate_up_act(x, self.shared_wgu), self.shared_wdown)
+            gate = torch.sigmoid(x.float() @ self.shared_gate.float().t())
+            y = (y.float() + gate * shared.float()).to(x.dtype)
+        return y
+
+    def _routed(self, x: torch.Tensor) -> torch.Tensor:
         cfg = self.cfg
         T, H = x.shape
         logits = gemm.linear(x, self.router)
