@@ -502,28 +502,155 @@ __device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
   x ^= x >> 16;
   return x;
 }
+// Order-preserving map float -> uint32 (larger float = larger key) and back.
+__device__ __forceinline__ uint32_t float_key(float z) {
+  const uint32_t u = __float_as_uint(z);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+
+// top-k / top-p cut-off per row: thr[b] = smallest scaled logit that stays in the distribution (-inf: no filter).
+// Exact radix select on the 32-bit keys, 11 + 11 + 10 bits per pass; every pass builds a histogram of counts (top-k)
+// or of softmax mass (top-p) over the keys that match the prefix found so far, then walks it from the top.
+// One block per row; the row stays in L2 between passes.
+constexpr int kSelBins = 2048;
+__global__ void __launch_bounds__(1024)
+sample_threshold_kernel(const float* __restrict__ logits, long long ldl, const float* __restrict__ temperature, int V,
+                        const int* __restrict__ top_k, const float* __restrict__ top_p, float* __restrict__ thr) {
+  const int b = blockIdx.x;
+  const float T = temperature[b];
+  const int k_lim = top_k ? top_k[b] : 0;
+  const float p_lim = top_p ? top_p[b] : 1.f;
+  const bool use_k = k_lim > 0 && k_lim < V, use_p = p_lim < 1.f;
+  if (!(T > 0.f) || (!use_k && !use_p)) {
+    if (threadIdx.x == 0) thr[b] = -INFINITY;
+    return;
+  }
+  const float invT = 1.f / T;
+  const float* row = logits + b * ldl;
+  __shared__ float hist[kSelBins];
+  __shared__ float red[32];
+  __shared__ float sh_m, sh_s, sh_above;
+  __shared__ uint32_t sh_prefix;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // row maximum and softmax denominator (top-p needs the mass scale)
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) m = fmaxf(m, row[i] * invT);
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  if (warp == 0) {
+    m = red[lane];
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) sh_m = m;
+  }
+  __syncthreads();
+  m = sh_m;
+  float ssum = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) ssum += __expf(row[i] * invT - m);
+  for (int o = 16; o > 0; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = ssum;
+  __syncthreads();
+  if (warp == 0) {
+    ssum = red[lane];
+    for (int o = 16; o > 0; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+    if (lane == 0) sh_s = ssum;
+  }
+  __syncthreads();
+  float best_thr = -INFINITY;
+#pragma unroll 1
+  for (int mode = 0; mode < 2; ++mode) {  // 0: top-k (weights 1), 1: top-p (weights = softmax mass)
+    if ((mode == 0 && !use_k) || (mode == 1 && !use_p)) continue;
+    const float target = mode == 0 ? static_cast<float>(k_lim) : p_lim * sh_s;
+    if (threadIdx.x == 0) {
+      sh_prefix = 0u;
+      sh_above = 0.f;
+    }
+    int shift = 32;
+#pragma unroll 1
+    for (int pass = 0; pass < 3; ++pass) {
+      const int bits = pass < 2 ? 11 : 10;
+      shift -= bits;
+      const int nb = 1 << bits;
+      for (int i = threadIdx.x; i < nb; i += blockDim.x) hist[i] = 0.f;
+      __syncthreads();
+      const uint32_t prefix = sh_prefix;
+      const uint32_t hi_mask = pass == 0 ? 0u : ~((1u << (shift + bits)) - 1u);
+      for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float z = row[i] * invT;
+        const uint32_t key = float_key(z);
+        if ((key & hi_mask) != prefix) continue;
+        atomicAdd(&hist[(key >> shift) & (nb - 1)], mode == 0 ? 1.f : __expf(z - m));
+      }
+      __syncthreads();
+      if (warp == 0) {
+        // walk the bins from the top: lane l owns bins [nb - (l+1)*per, nb - l*per)
+        const int per = nb / 32;
+        float mine = 0.f;
+        for (int j = 0; j < per; ++j) mine += hist[nb - 1 - (lane * per + j)];
+        float incl = mine;
+        for (int o = 1; o < 32; o <<= 1) {
+          const float t = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += t;
+        }
+        const float above = sh_above;
+        const float before = above + incl - mine;              // weight above this lane's bins
+        const bool crosses = before < target && before + mine >= target;
+        const unsigned vote = __ballot_sync(0xffffffffu, crosses);
+        // no lane crosses only through rounding at the very end: take the last non-empty lane
+        const int owner = vote ? __ffs(vote) - 1 : 31;
+        if (lane == owner) {
+          float acc = before;
+          int chosen = nb - 1 - (lane * per + per - 1);
+          for (int j = 0; j < per; ++j) {
+            const int bin = nb - 1 - (lane * per + j);
+            if (acc + hist[bin] >= target) {
+              chosen = bin;
+              break;
+            }
+            acc += hist[bin];
+          }
+          sh_above = acc;
+          sh_prefix = prefix | (static_cast<uint32_t>(chosen) << shift);
+        }
+      }
+      __syncthreads();
+    }
+    best_thr = fmaxf(best_thr, key_float(sh_prefix));
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) thr[b] = best_thr;
+}
+
 // One block per row.  logits [B, V] fp32 (row stride ldl).  temperature[b] <= 0 -> greedy.
-// Gumbel-max sampling: argmax(z + g), z = logit / T.  Also returns log softmax(z)[token].
+// Gumbel-max sampling: argmax(z + g), z = logit / T, over the tokens with z >= thr[b] when a cut-off is given.
+// Also returns log softmax(z)[token] under the UNFILTERED distribution (what the trainer's old_log_probs expect).
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, long long ldl, const float* __restrict__ temperature, int V,
-              uint32_t seed, const int* __restrict__ step_dev, int* __restrict__ tokens,
-              float* __restrict__ logprobs) {
+              uint32_t seed, const int* __restrict__ step_dev, const float* __restrict__ thr,
+              int* __restrict__ tokens, float* __restrict__ logprobs) {
   const int b = blockIdx.x;
   const uint32_t step = step_dev ? static_cast<uint32_t>(*step_dev) : 0u;
   const float T = temperature[b];
   const bool greedy = !(T > 0.f);
   const float invT = greedy ? 1.f : 1.f / T;
   const float* row = logits + b * ldl;
+  const float cut = (thr && !greedy) ? thr[b] : -INFINITY;
   float best = -INFINITY, best_z = 0.f;
   int best_i = 0;
   float m = -INFINITY, s = 0.f;
   for (int i = threadIdx.x; i < V; i += blockDim.x) {
     const float z = row[i] * invT;
     float key = z;
-    if (!greedy) {
+    if (!greedy && z >= cut) {
       const uint32_t h = hash_u32(hash_u32(seed ^ (step * 0x9E3779B9u)) ^ hash_u32(static_cast<uint32_t>(b) * 0x85ebca6bU + i));
       const float u = (static_cast<float>(h >> 8) + 0.5f) * (1.f / 16777216.f);
       key = z - __logf(-__logf(u));
+    } else if (!greedy) {
+      key = -INFINITY;  // outside the top-k / top-p set
     }
     if (key > best) {
       best = key;
@@ -674,7 +801,19 @@ int apb_decode_merge(const float* const* o_ptrs, const float* const* ml_ptrs, co
 int apb_sample(const float* logits, long long ldl, const float* temperature, int B, int V, unsigned seed,
                const int* step_dev, int* tokens, float* logprobs, cudaStream_t s) {
   if (B <= 0) return 0;
-  sample_kernel<<<B, 1024, 0, s>>>(logits, ldl, temperature, V, seed, step_dev, tokens, logprobs);
+  sample_kernel<<<B, 1024, 0, s>>>(logits, ldl, temperature, V, seed, step_dev, nullptr, tokens, logprobs);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Sampling restricted to the top-k tokens and to the smallest set of tokens with probability mass >= top_p.
+// top_k [B] (<= 0: off), top_p [B] (>= 1: off), thr [B] fp32 scratch for the per-row cut-off.
+int apb_sample_filtered(const float* logits, long long ldl, const float* temperature, int B, int V, unsigned seed,
+                        const int* step_dev, const int* top_k, const float* top_p, float* thr, int* tokens,
+                        float* logprobs, cudaStream_t s) {
+  if (B <= 0) return 0;
+  if (!thr) return kBadArgument;
+  sample_threshold_kernel<<<B, 1024, 0, s>>>(logits, ldl, temperature, V, top_k, top_p, thr);
+  sample_kernel<<<B, 1024, 0, s>>>(logits, ldl, temperature, V, seed, step_dev, thr, tokens, logprobs);
   return static_cast<int>(cudaGetLastError());
 }
 }

@@ -161,6 +161,36 @@ gather_shards_kernel(PeerPtrs shards, PeerPtrs flags, int rank, int world, int e
   }
 }
 
+// ZeRO-3 unit gather: every parameter of a unit is stored as `world` equal pieces, piece r in rank r's shard buffer.
+// One launch rebuilds the whole unit in parameter-major layout by pulling the pieces from their owners (plain peer
+// loads).  The grid is capped so the copy shares the GPU with the GEMMs of the unit that is computing meanwhile.
+constexpr int kMaxGatherPieces = 24;
+struct GatherTable {
+  long long full_off[kMaxGatherPieces];   // element offset of the parameter inside the unit (destination)
+  long long piece_len[kMaxGatherPieces];  // elements per rank, multiple of 8
+  long long shard_off[kMaxGatherPieces];  // element offset of the piece inside the unit's part of a shard buffer
+  long long vec_start[kMaxGatherPieces + 1];  // running count of 16-byte vectors (all ranks) before each parameter
+  int n;
+};
+
+__global__ void __launch_bounds__(256)
+gather_unit_kernel(PeerPtrs shards, GatherTable t, int rank, int world, __nv_bfloat16* __restrict__ dst) {
+  const long long total = t.vec_start[t.n];
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    int pc = 0;
+    while (pc + 1 < t.n && i >= t.vec_start[pc + 1]) ++pc;
+    const long long j = i - t.vec_start[pc];
+    const long long n8 = t.piece_len[pc] >> 3;
+    const int rr = static_cast<int>(j / n8);
+    const int src = (rank + rr) % world;  // start with the local piece, then walk the peers
+    const long long off = (j - static_cast<long long>(rr) * n8) * 8;
+    const uint4 val =
+        *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(shards.p[src]) + t.shard_off[pc] + off);
+    *reinterpret_cast<uint4*>(dst + t.full_off[pc] + static_cast<long long>(src) * t.piece_len[pc] + off) = val;
+  }
+}
+
 __global__ void sumsq_f32_kernel(const float* __restrict__ x, long long n, double* __restrict__ out) {
   double acc = 0.0;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
@@ -233,6 +263,31 @@ int apb_gather_shards(void* const* shard_ptrs, void* const* flag_ptrs, int rank,
   gather_shards_kernel<<<grid_for(n / 8 * world), 256, 0, s>>>(to_peers(shard_ptrs, world), to_peers(flag_ptrs, world),
                                                                rank, world, epoch, n,
                                                                static_cast<__nv_bfloat16*>(dst), status_device_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+// shard_ptrs: per-rank pointers to the unit's part of the shard buffers.  full_off / piece_len / shard_off: host
+// arrays of n_pieces entries (elements).  max_ctas caps the grid (0 = 64).
+int apb_gather_unit(void* const* shard_ptrs, int rank, int world, const long long* full_off, const long long* piece_len,
+                    const long long* shard_off, int n_pieces, void* dst, int max_ctas, cudaStream_t s) {
+  if (world > kMaxRanks || n_pieces < 1 || n_pieces > kMaxGatherPieces) return kBadArgument;
+  GatherTable t;
+  t.n = n_pieces;
+  long long acc = 0;
+  for (int i = 0; i < n_pieces; ++i) {
+    if (piece_len[i] % 8 || full_off[i] % 8 || shard_off[i] % 8) return kBadArgument;
+    t.full_off[i] = full_off[i];
+    t.piece_len[i] = piece_len[i];
+    t.shard_off[i] = shard_off[i];
+    t.vec_start[i] = acc;
+    acc += piece_len[i] / 8 * world;
+  }
+  t.vec_start[n_pieces] = acc;
+  if (acc == 0) return 0;
+  const int cap = max_ctas > 0 ? max_ctas : 64;
+  const long long need = (acc + 255) / 256;
+  gather_unit_kernel<<<static_cast<int>(need < cap ? need : cap), 256, 0, s>>>(to_peers(shard_ptrs, world), t, rank, world,
+                                                                              static_cast<__nv_bfloat16*>(dst));
   return static_cast<int>(cudaGetLastError());
 }
 

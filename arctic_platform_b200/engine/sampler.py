@@ -125,6 +125,7 @@ def _fn(name: str):
         _FN["dec"] = _lib.declare("apb_paged_decode_partial", [vp, vp, vp, vp, i, vp, vp, vp, vp, vp, i, i, i, i, i, f, vp])
         _FN["merge"] = _lib.declare("apb_decode_merge", [vp, vp, vp, i, vp, vp, i, i, i, vp])
         _FN["sample"] = _lib.declare("apb_sample", [vp, ll, vp, i, i, u, vp, vp, vp, vp])
+        _FN["sample_f"] = _lib.declare("apb_sample_filtered", [vp, ll, vp, i, i, u, vp, vp, vp, vp, vp, vp, vp])
         _FN["prefix_tc"] = _lib.declare("apb_decode_prefix_tc",
                                         [vp, i, vp, vp, vp, i, vp, vp, vp, ll, vp, vp, i, i, i, i, i, f, vp])
         _FN["norm32"] = _lib.declare("apb_rmsnorm_fwd_f32in", [vp, vp, vp, vp, vp, i, i, f, f, vp])
@@ -193,6 +194,10 @@ class SamplerEngine:
         self.d_out_idx = torch.zeros((B, 1), device=dev, dtype=torch.int64)   # tokens emitted so far per slot
         self.d_step = torch.zeros(1, **i32)                                   # global decode step (RNG stream)
         self.d_stop = torch.full((8,), -1, **i32)
+        self.d_topk = torch.zeros(B, **i32)                       # per-slot top-k (0 = off)
+        self.d_topp = torch.ones(B, device=dev, dtype=torch.float32)
+        self.d_thr = torch.zeros(B, device=dev, dtype=torch.float32)
+        self._filter_on = False
         self.splits = 4
         self.n_groups = B            # groups in the prefix tables (a power-of-two bucket bounds the prefix grid)
         Hq, D = c.num_heads, c.head_dim
@@ -337,9 +342,16 @@ class SamplerEngine:
             h, _ = norm.rmsnorm(x, self.model.final_norm, c.rms_norm_eps, stream)
         logits = self.d_logits[:B]
         gemm.matmul_nt(h, self.model.output_weight, out=logits)
-        _lib.check(_fn("sample")(_lib.ptr(logits), logits.stride(0), _lib.ptr(self.d_temp), B, c.vocab_size,
-                                 ctypes.c_uint(self.seed & 0xFFFFFFFF), _lib.ptr(self.d_step), _lib.ptr(self.d_new_tok),
-                                 _lib.ptr(self.d_new_lp), _lib.stream_ptr()), "sample")
+        if self._filter_on:
+            _lib.check(_fn("sample_f")(_lib.ptr(logits), logits.stride(0), _lib.ptr(self.d_temp), B, c.vocab_size,
+                                       ctypes.c_uint(self.seed & 0xFFFFFFFF), _lib.ptr(self.d_step),
+                                       _lib.ptr(self.d_topk), _lib.ptr(self.d_topp), _lib.ptr(self.d_thr),
+                                       _lib.ptr(self.d_new_tok), _lib.ptr(self.d_new_lp), _lib.stream_ptr()),
+                       "sample_filtered")
+        else:
+            _lib.check(_fn("sample")(_lib.ptr(logits), logits.stride(0), _lib.ptr(self.d_temp), B, c.vocab_size,
+                                     ctypes.c_uint(self.seed & 0xFFFFFFFF), _lib.ptr(self.d_step),
+                                     _lib.ptr(self.d_new_tok), _lib.ptr(self.d_new_lp), _lib.stream_ptr()), "sample")
         new_tok, new_lp = self.d_new_tok[:B], self.d_new_lp[:B]
         idx = self.d_out_idx[:B].clamp(max=self.out_cap - 1)
         self.d_out_tokens[:B].scatter_(1, idx, torch.where(act, new_tok, self.d_out_tokens[:B].gather(1, idx).squeeze(1))[:, None])
@@ -415,7 +427,7 @@ class SamplerEngine:
             for _ in range(n):
                 self._decode_step(B)
             return
-        key = (B, self._group_bucket() if self.cascade else 0)
+        key = (B, self._group_bucket() if self.cascade else 0, self._filter_on)
         g = self._graphs.get(key)
         if g is None:
             # the first steps run eagerly (kernel attribute set-up, device binding, allocator warm-up)
@@ -441,8 +453,9 @@ class SamplerEngine:
         sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
         if self._asleep:
             raise RuntimeError("sampler is asleep; call wake() first")
-        if sp.top_k not in (-1, 0) or sp.top_p < 1.0:
-            raise NotImplementedError("top-k / top-p filtering is not implemented in the sampling kernel")
+        self._filter_on = bool((sp.top_k is not None and sp.top_k > 0) or sp.top_p < 1.0)
+        self.d_topk.fill_(int(sp.top_k) if sp.top_k and sp.top_k > 0 else 0)
+        self.d_topp.fill_(float(sp.top_p))
         prompts_np = [np.asarray(p, dtype=np.int64) for p in prompts]
         for p in prompts_np:
             if len(p) == 0:

@@ -22,6 +22,7 @@ arctic_platform/common/deepspeed_worker.py:208-324).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -87,6 +88,7 @@ class Zero3State:
         self.side = torch.cuda.Stream(device=dev) if engine.on_cuda else None
         self.ready: List[Optional[torch.cuda.Event]] = [None, None]
         self.gathers = 0
+        self.gather_ctas = int(os.environ.get("APB_ZERO3_GATHER_CTAS", "48"))   # SMs lent to a prefetch
         for ui in self.resident:
             self._gather(ui, self.resident[ui])
         self._install_hooks()
@@ -99,13 +101,16 @@ class Zero3State:
         base = e.unit_shard_off[ui]
         self.gathers += 1
         if self.fused:
-            fn = _fused_gather()
-            flags = e.flags.ptr_table()
+            rows = self.pieces[ui]
             s = _lib.stream_ptr()
-            for _name, fo, pl, so in self.pieces[ui]:
-                tbl = self.shard_buf.ptr_table((base + so) * 2)
-                _lib.check(fn(tbl, flags, e.rank, W, 0, pl, ctypes.c_void_p(buf.data_ptr() + fo * 2), s),
-                           "apb_gather_shards")
+            for lo in range(0, len(rows), 24):                     # one launch per (up to) 24 parameters
+                part = rows[lo:lo + 24]
+                n = len(part)
+                arr = ctypes.c_longlong * n
+                _lib.check(_fused_gather()(self.shard_buf.ptr_table(base * 2), e.rank, W,
+                                           arr(*[r[1] for r in part]), arr(*[r[2] for r in part]),
+                                           arr(*[r[3] for r in part]), n, ctypes.c_void_p(buf.data_ptr()),
+                                           self.gather_ctas, s), "apb_gather_unit")
             return
         for _name, fo, pl, so in self.pieces[ui]:
             mine = self.shard_buf.tensor[base + so:base + so + pl].contiguous()
@@ -224,6 +229,6 @@ def _fused_gather():
     global _GATHER
     if _GATHER is None:
         c = ctypes
-        _GATHER = _lib.declare("apb_gather_shards", [c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_longlong,
-                                                      c.c_void_p, c.c_void_p])
+        _GATHER = _lib.declare("apb_gather_unit", [c.c_void_p, c.c_int, c.c_int, c.c_void_p, c.c_void_p, c.c_void_p,
+                                                    c.c_int, c.c_void_p, c.c_int, c.c_void_p])
     return _GATHER

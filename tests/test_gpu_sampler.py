@@ -138,3 +138,56 @@ def test_paged_decode_mma_kernel_matches_reference_and_scalar_kernel(Hq, Hkv, nq
             assert (lse_mma[row] - ref_lse).abs().max() < 0.02
             if out_sc is not None:
                 assert (out_mma[row] - out_sc[row]).abs().max() < 0.03
+
+
+def test_top_k_top_p_filter_kernel_against_sorted_reference():
+    """Cut-offs of the radix-select kernel equal the sort-based definition, sampled tokens stay inside the allowed
+    set, and the reported log-prob is the unfiltered one."""
+    import ctypes
+    from arctic_platform_b200.engine.reference_sampler import filter_logits
+    from arctic_platform_b200.engine.sampler import _fn
+    from arctic_platform_b200.ops import _lib
+    dev = "cuda"
+    B, V = 12, 151936
+    g = torch.Generator(device=dev).manual_seed(3)
+    logits = (torch.randn(B, V, device=dev, generator=g) * 3.0).float()
+    temp = torch.tensor([1.0, 0.7, 1.3, 1.0, 1.0, 0.5, 1.0, 2.0, 1.0, 1.0, 0.0, 1.0], device=dev)
+    top_k = torch.tensor([50, 0, 1, 1000, 0, 20, 7, 0, 0, 3, 5, V + 5], device=dev, dtype=torch.int32)
+    top_p = torch.tensor([1.0, 0.9, 1.0, 0.5, 0.01, 0.95, 0.3, 0.999, 1.0, 0.2, 0.5, 1.0], device=dev)
+    thr = torch.zeros(B, device=dev)
+    tok = torch.zeros(B, device=dev, dtype=torch.int32)
+    lp = torch.zeros(B, device=dev)
+    step = torch.zeros(1, device=dev, dtype=torch.int32)
+    for it in range(3):
+        step.fill_(it)
+        _lib.check(_fn("sample_f")(_lib.ptr(logits), logits.stride(0), _lib.ptr(temp), B, V, ctypes.c_uint(99), _lib.ptr(step),
+                                   _lib.ptr(top_k), _lib.ptr(top_p), _lib.ptr(thr), _lib.ptr(tok), _lib.ptr(lp),
+                                   _lib.stream_ptr()), "sample_filtered")
+        _lib.check_status("sample_filtered")
+        for b in range(B):
+            T = float(temp[b])
+            if T <= 0:
+                assert int(tok[b]) == int(logits[b].argmax()) and thr[b] == float("-inf")
+                continue
+            z = logits[b] / T
+            allowed = torch.isfinite(filter_logits(z, int(top_k[b]) if int(top_k[b]) <= V else 0, float(top_p[b])))
+            got = z >= thr[b]
+            # the kernel's set equals the sorted definition up to ties / rounding at the boundary of the mass threshold
+            assert abs(int(got.sum()) - int(allowed.sum())) <= 1, (b, int(got.sum()), int(allowed.sum()))
+            assert bool(got[int(tok[b])])
+            ref_lp = torch.log_softmax(z, -1)[int(tok[b])]
+            assert abs(float(lp[b]) - float(ref_lp)) < 2e-3
+    # rows without any filter keep the whole vocabulary
+    assert thr[8] == float("-inf") and thr[11] == float("-inf")
+
+
+def test_engine_generates_with_top_k_and_top_p():
+    cfg, model, eng = _engine(True, True, max_batch=16)
+    prompt = list(range(5, 40))
+    greedy = eng.generate([prompt], {"n": 1, "temperature": 0.0, "max_tokens": 8})[0]["token_ids"]
+    k1 = eng.generate([prompt], {"n": 4, "temperature": 1.0, "max_tokens": 8, "top_k": 1, "seed": 3})
+    assert all(o["token_ids"] == greedy for o in k1)               # top-1 sampling is greedy decoding
+    tiny_p = eng.generate([prompt], {"n": 4, "temperature": 1.0, "max_tokens": 8, "top_p": 1e-6, "seed": 4})
+    assert all(o["token_ids"] == greedy for o in tiny_p)
+    free = eng.generate([prompt], {"n": 8, "temperature": 1.0, "max_tokens": 8, "top_k": 50, "top_p": 0.95, "seed": 5})
+    assert len({tuple(o["token_ids"]) for o in free}) > 1
