@@ -561,9 +561,28 @@ sample_threshold_kernel(const float* __restrict__ logits, long long ldl, const f
   }
   __syncthreads();
   float best_thr = -INFINITY;
+  uint32_t kcut = 0u;  // key of the k-th largest logit once top-k has run: top-p then works inside that set
 #pragma unroll 1
   for (int mode = 0; mode < 2; ++mode) {  // 0: top-k (weights 1), 1: top-p (weights = softmax mass)
     if ((mode == 0 && !use_k) || (mode == 1 && !use_p)) continue;
+    if (mode == 1 && kcut != 0u) {
+      // top-p applies to the distribution renormalised over the top-k set: its mass replaces the full sum
+      float part = 0.f;
+      for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float z = row[i] * invT;
+        if (float_key(z) >= kcut) part += __expf(z - m);
+      }
+      for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      __syncthreads();
+      if (lane == 0) red[warp] = part;
+      __syncthreads();
+      if (warp == 0) {
+        part = red[lane];
+        for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+        if (lane == 0) sh_s = part;
+      }
+      __syncthreads();
+    }
     const float target = mode == 0 ? static_cast<float>(k_lim) : p_lim * sh_s;
     if (threadIdx.x == 0) {
       sh_prefix = 0u;
@@ -582,7 +601,7 @@ sample_threshold_kernel(const float* __restrict__ logits, long long ldl, const f
       for (int i = threadIdx.x; i < V; i += blockDim.x) {
         const float z = row[i] * invT;
         const uint32_t key = float_key(z);
-        if ((key & hi_mask) != prefix) continue;
+        if ((key & hi_mask) != prefix || key < kcut) continue;
         atomicAdd(&hist[(key >> shift) & (nb - 1)], mode == 0 ? 1.f : __expf(z - m));
       }
       __syncthreads();
@@ -620,6 +639,7 @@ sample_threshold_kernel(const float* __restrict__ logits, long long ldl, const f
       __syncthreads();
     }
     best_thr = fmaxf(best_thr, key_float(sh_prefix));
+    if (mode == 0) kcut = sh_prefix;
     __syncthreads();
   }
   if (threadIdx.x == 0) thr[b] = best_thr;

@@ -136,7 +136,8 @@ class SamplerEngine:
     def __init__(self, cfg: DecoderConfig, device="cuda", model: Optional[DecoderLM] = None,
                  kv_cache_tokens: int = 1 << 20, max_batch: int = 256, max_seq_len: int = 8192,
                  cascade: bool = True, sync_interval: int = 16, use_cuda_graph: bool = True, seed: int = 0,
-                 eos_token_id: Optional[int] = None, prefix_on_tensor_cores: bool = True, split_k: bool = True):
+                 eos_token_id: Optional[int] = None, prefix_on_tensor_cores: bool = True, split_k: bool = True,
+                 quantization: Optional[str] = None):
         self.cfg = cfg
         self.device = torch.device(device)
         self.model = model if model is not None else DecoderLM(cfg, self.device, torch.bfloat16)
@@ -149,6 +150,13 @@ class SamplerEngine:
         self.eos = eos_token_id
         self.prefix_on_tensor_cores = prefix_on_tensor_cores
         self.split_k = split_k
+        if quantization not in (None, "", "fp8"):
+            raise ValueError(f"unsupported sampler quantization {quantization!r} (None or 'fp8')")
+        # "fp8": the dense projections are served from block-scaled e4m3 copies (128 x 128 weight blocks, per-token
+        # activation scales) that are rebuilt after every weight sync
+        self.fp8 = quantization == "fp8" and not cfg.is_moe
+        self._fp8_stale = True
+        self._fp8_w: List[dict] = []
         self.num_pages = max(64, kv_cache_tokens // PAGE)
         self.max_pages = (max_seq_len + PAGE - 1) // PAGE + 1
         self._alloc_cache()
@@ -219,6 +227,8 @@ class SamplerEngine:
     def _block(self, li: int, x, stream, positions, slots, attn_fn):
         c = self.cfg
         blk = self.model.blocks[li]
+        if self.fp8:
+            return self._block_fp8(li, x, stream, positions, slots, attn_fn)
         h, stream = norm.rmsnorm(x, blk.ln1, c.rms_norm_eps, stream)
         qkv = gemm.matmul_nt(h, blk.wqkv)
         q, k, v = norm.qknorm_rope(qkv, blk.q_norm, blk.k_norm, *self.model.rope(self.device), positions, c.num_heads,
@@ -235,6 +245,39 @@ class SamplerEngine:
             _, act = gemm.gate_up_swiglu(h2, blk.wgu, keep_gu=False)
             d = gemm.matmul_nt(act, blk.wdown)
         return d, stream
+
+    @torch.no_grad()
+    def weights_updated(self) -> None:
+        """Called after a weight sync / load: derived copies (fp8) are rebuilt before the next generation."""
+        self._fp8_stale = True
+
+    @torch.no_grad()
+    def _requantize_fp8(self) -> None:
+        from ..parallel.weight_sync import quantize_fp8_block128
+        self._fp8_w = []
+        self._graphs.clear()             # captured graphs hold pointers to the previous copies
+        for blk in self.model.blocks:
+            self._fp8_w.append({n: quantize_fp8_block128(getattr(blk, n).data) for n in ("wqkv", "wo", "wgu", "wdown")})
+        self._fp8_stale = False
+
+    @torch.no_grad()
+    def _block_fp8(self, li: int, x, stream, positions, slots, attn_fn):
+        from ..ops.fp8 import fp8_linear
+        c = self.cfg
+        blk = self.model.blocks[li]
+        w = self._fp8_w[li]
+        h, stream = norm.rmsnorm(x, blk.ln1, c.rms_norm_eps, stream)
+        qkv = fp8_linear(h, *w["wqkv"])
+        q, k, v = norm.qknorm_rope(qkv, blk.q_norm, blk.k_norm, *self.model.rope(self.device), positions, c.num_heads,
+                                   c.num_kv_heads, c.head_dim, c.rms_norm_eps)
+        _lib.check(_fn("kvw")(_lib.ptr(k), k.stride(0), _lib.ptr(v), v.stride(0), _lib.ptr(slots),
+                              _lib.ptr(self.kcache[li]), _lib.ptr(self.vcache[li]), k.shape[0], c.num_kv_heads,
+                              c.head_dim, _lib.stream_ptr()), "kv_cache_write")
+        a = attn_fn(li, q, k, v)
+        o = fp8_linear(a.reshape(a.shape[0], -1).contiguous(), *w["wo"])
+        h2, stream = norm.rmsnorm(o, blk.ln2, c.rms_norm_eps, stream)
+        act = norm.swiglu(fp8_linear(h2, *w["wgu"]))
+        return fp8_linear(act, *w["wdown"]), stream
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -334,7 +377,7 @@ class SamplerEngine:
         x = torch.nn.functional.embedding(self.d_tokens[:B].long(), self.model.embed)
         stream = None
         attn = lambda li, q, k, v: self._decode_attention(li, q, B)
-        if self.split_k and not c.is_moe:
+        if self.split_k and not c.is_moe and not self.fp8:
             h = self._decode_layers_splitk(x, positions, slots, B)
         else:
             for li in range(c.num_layers):
@@ -453,6 +496,8 @@ class SamplerEngine:
         sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
         if self._asleep:
             raise RuntimeError("sampler is asleep; call wake() first")
+        if self.fp8 and self._fp8_stale:
+            self._requantize_fp8()
         self._filter_on = bool((sp.top_k is not None and sp.top_k > 0) or sp.top_p < 1.0)
         self.d_topk.fill_(int(sp.top_k) if sp.top_k and sp.top_k > 0 else 0)
         self.d_topp.fill_(float(sp.top_p))
@@ -674,6 +719,7 @@ class SamplerEngine:
         for name, t in named_tensors:
             load_hf_tensor(self.model, name, t)
             n += 1
+        self.weights_updated()
         return n
 
     def weight_norm(self) -> Dict[str, float]:

@@ -72,7 +72,7 @@ class EngineWorker:
                 kv_cache_tokens=int(vc.get("kv_cache_tokens", 1 << 20)), max_batch=int(vc.get("max_num_seqs", 256)),
                 max_seq_len=int(vc.get("max_model_len", 8192)),
                 cascade=bool((job_config.get("arctic_inference_config") or {}).get("zorro_inference", {}).get("enable", True)),
-                seed=seed, eos_token_id=vc.get("eos_token_id"))
+                seed=seed, eos_token_id=vc.get("eos_token_id"), quantization=vc.get("quantization"))
             return True
         m = model if model is not None else self._load_model(job_config, dtype, seed)
         if self.job_type == "log_prob":
@@ -187,6 +187,8 @@ class EngineWorker:
             if flat is None or flat.numel() != self.engine.total:
                 flat = weight_sync.flatten_like(dst_model, self.engine)
             weight_sync.sync_flat(self.engine, flat)
+            if dst.sampler is not None and hasattr(dst.sampler, "weights_updated"):
+                dst.sampler.weights_updated()
             return n_names
         return weight_sync.sync_state_dict(((n, t.detach()) for n, t in self.engine.iter_hf_tensors()), dst_model)
 
