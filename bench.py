@@ -43,10 +43,10 @@ def parse_args():
     ap.add_argument("--samples", type=int, default=16)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--response-len", type=int, default=2048)
-    ap.add_argument("--rollouts-per-microbatch", type=int, default=4,
+    ap.add_argument("--rollouts-per-microbatch", type=int, default=8,
                     help="rollouts of one prompt per training micro-batch (prompt KV is recomputed per micro-batch)")
     ap.add_argument("--prompts-per-microbatch", type=int, default=1)
-    ap.add_argument("--ref-microbatch-merge", type=int, default=4,
+    ap.add_argument("--ref-microbatch-merge", type=int, default=2,
                     help="training micro-batches scored together in one reference (no-grad) forward")
     ap.add_argument("--zero-stage", type=int, default=3,
                     help="3: bf16 parameters sharded over ranks and gathered unit by unit; 2: replicated parameters")
@@ -317,6 +317,7 @@ def main():
                        "step": "sync_weights+rollout+ref_logprob+fwd_bwd+adamw", "lr": args.lr,
                        "train_microbatches": n_mb},
             "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches,
+            "peak_device_memory_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1),
             "rollout_tokens_per_step": B * R * world,
         }
         print(json.dumps(line), flush=True)
