@@ -493,6 +493,75 @@ __global__ void decode_merge_kernel(MergeSrc src, __nv_bfloat16* __restrict__ ou
   if (lse_out && lane == 0) lse_out[gw] = ll > 0.f ? (mm + log2f(ll)) * 0.6931471805599453f : -INFINITY;
 }
 
+// Decode-step epilogue of the split-K qkv projection: reads the fp32 sums [B, (Hq + 2 Hkv) * D] (and resets them to
+// zero for the next step), applies the per-head RMSNorm and rotate-half RoPE to q and k, writes q as bf16 and puts k
+// and v straight into their KV-cache slots -- one kernel instead of (bf16 store in the GEMM, norm+RoPE, cache write).
+// One warp per (token, head).
+template <int D>
+__global__ void __launch_bounds__(256)
+decode_qkv_post_kernel(float* __restrict__ acc, long long ld_acc, const __nv_bfloat16* __restrict__ wq,
+                       const __nv_bfloat16* __restrict__ wk, const float* __restrict__ cos_t,
+                       const float* __restrict__ sin_t, const int* __restrict__ pos, const int* __restrict__ slots,
+                       __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kcache,
+                       __nv_bfloat16* __restrict__ vcache, int B, int Hq, int Hkv, float eps) {
+  constexpr int E2 = D / 64;
+  const int lane = threadIdx.x & 31;
+  const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+  const int heads = Hq + 2 * Hkv;
+  if (gw >= static_cast<long long>(B) * heads) return;
+  const int t = static_cast<int>(gw / heads);
+  const int h = static_cast<int>(gw % heads);
+  float* src = acc + t * ld_acc + static_cast<long long>(h) * D;
+  float a[E2], b[E2];
+#pragma unroll
+  for (int j = 0; j < E2; ++j) {
+    a[j] = src[lane * E2 + j];
+    b[j] = src[D / 2 + lane * E2 + j];
+    src[lane * E2 + j] = 0.f;
+    src[D / 2 + lane * E2 + j] = 0.f;
+  }
+  const int slot = slots[t];
+  const bool is_q = h < Hq, is_k = !is_q && h < Hq + Hkv;
+  if (is_q || is_k) {
+    const __nv_bfloat16* w = is_q ? wq : wk;
+    if (w) {
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < E2; ++j) ss += a[j] * a[j] + b[j] * b[j];
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss / D + eps);
+#pragma unroll
+      for (int j = 0; j < E2; ++j) {
+        a[j] *= rstd * __bfloat162float(w[lane * E2 + j]);
+        b[j] *= rstd * __bfloat162float(w[D / 2 + lane * E2 + j]);
+      }
+    }
+    const int p = pos[t];
+#pragma unroll
+    for (int j = 0; j < E2; ++j) {
+      const int i = lane * E2 + j;
+      const float c = cos_t[static_cast<long long>(p) * (D / 2) + i], sn = sin_t[static_cast<long long>(p) * (D / 2) + i];
+      const float oa = a[j] * c - b[j] * sn, ob = b[j] * c + a[j] * sn;
+      a[j] = oa;
+      b[j] = ob;
+    }
+  }
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = q_out + (static_cast<long long>(t) * Hq + h) * D;
+  } else {
+    if (slot < 0) return;  // inactive sequence: nothing enters the cache
+    const int hh = is_k ? h - Hq : h - Hq - Hkv;
+    __nv_bfloat16* cache = is_k ? kcache : vcache;
+    dst = cache + ((static_cast<long long>(slot / kPage) * Hkv + hh) * kPage + slot % kPage) * D;
+  }
+#pragma unroll
+  for (int j = 0; j < E2; ++j) {
+    dst[lane * E2 + j] = __float2bfloat16(a[j]);
+    dst[D / 2 + lane * E2 + j] = __float2bfloat16(b[j]);
+  }
+}
+
 // ---------------------------------------------------------------------------- sampling
 __device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
   x ^= x >> 16;
@@ -753,6 +822,26 @@ int apb_kv_cache_write(const void* k, long long ldk, const void* v, long long ld
                                              static_cast<const __nv_bfloat16*>(v), ldv, slots,
                                              static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache),
                                              T, Hkv, D);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int apb_decode_qkv_post(float* acc, long long ld_acc, const void* wq, const void* wk, const float* cos_t,
+                        const float* sin_t, const int* pos, const int* slots, void* q_out, void* kcache, void* vcache,
+                        int B, int Hq, int Hkv, int D, float eps, cudaStream_t s) {
+  if (B <= 0) return 0;
+  const long long warps = static_cast<long long>(B) * (Hq + 2 * Hkv);
+  const int grid = static_cast<int>((warps * 32 + 255) / 256);
+#define APB_QKV_POST(DD)                                                                                       \
+  decode_qkv_post_kernel<DD><<<grid, 256, 0, s>>>(acc, ld_acc, static_cast<const __nv_bfloat16*>(wq),          \
+                                                  static_cast<const __nv_bfloat16*>(wk), cos_t, sin_t, pos, slots, \
+                                                  static_cast<__nv_bfloat16*>(q_out),                         \
+                                                  static_cast<__nv_bfloat16*>(kcache),                        \
+                                                  static_cast<__nv_bfloat16*>(vcache), B, Hq, Hkv, eps)
+  if (D == 128) APB_QKV_POST(128);
+  else if (D == 64) APB_QKV_POST(64);
+  else if (D == 256) APB_QKV_POST(256);
+  else return kBadArgument;
+#undef APB_QKV_POST
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -380,6 +380,26 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_qkv,
   }
 }
 
+// SwiGLU on fp32 split-K sums: acc [T, 2I] interleaved (gate, up) -> act [T, I] bf16; acc is reset to zero.
+// One thread handles four outputs (eight inputs, two 16-byte loads).
+__global__ void swiglu_f32in_kernel(float* __restrict__ acc, __nv_bfloat16* __restrict__ act, long long n_quads) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n_quads;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4* p = reinterpret_cast<float4*>(acc + i * 8);
+    const float4 x = p[0], y = p[1];
+    p[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    p[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float o0 = x.x / (1.f + __expf(-x.x)) * x.y;
+    const float o1 = x.z / (1.f + __expf(-x.z)) * x.w;
+    const float o2 = y.x / (1.f + __expf(-y.x)) * y.y;
+    const float o3 = y.z / (1.f + __expf(-y.z)) * y.w;
+    uint2 out;
+    *reinterpret_cast<__nv_bfloat162*>(&out.x) = __floats2bfloat162_rn(o0, o1);
+    *reinterpret_cast<__nv_bfloat162*>(&out.y) = __floats2bfloat162_rn(o2, o3);
+    *reinterpret_cast<uint2*>(act + i * 4) = out;
+  }
+}
+
 // --------------------------------------------------------------- SwiGLU
 // Interleaved layout: gu[t, 2j] = gate_j, gu[t, 2j+1] = up_j.
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
@@ -517,6 +537,14 @@ int apb_qknorm_rope_bwd(const void* qkv, long long ld_qkv, const void* wq, const
   return static_cast<int>(cudaGetLastError());
 }
 
+int apb_swiglu_f32in(float* acc, void* act, long long T, long long I, cudaStream_t s) {
+  if (I % 4) return kBadArgument;
+  const long long n = T * I / 4;
+  if (n <= 0) return 0;
+  const int grid = static_cast<int>(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);
+  swiglu_f32in_kernel<<<grid, 256, 0, s>>>(acc, static_cast<__nv_bfloat16*>(act), n);
+  return static_cast<int>(cudaGetLastError());
+}
 int apb_swiglu_fwd(const void* gu, void* act, long long T, long long I, cudaStream_t s) {
   if (I % 8) return kBadArgument;
   const long long n = T * I / 8;

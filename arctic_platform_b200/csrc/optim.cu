@@ -176,18 +176,32 @@ struct GatherTable {
 __global__ void __launch_bounds__(256)
 gather_unit_kernel(PeerPtrs shards, GatherTable t, int rank, int world, __nv_bfloat16* __restrict__ dst) {
   const long long total = t.vec_start[t.n];
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    int pc = 0;
-    while (pc + 1 < t.n && i >= t.vec_start[pc + 1]) ++pc;
-    const long long j = i - t.vec_start[pc];
-    const long long n8 = t.piece_len[pc] >> 3;
-    const int rr = static_cast<int>(j / n8);
-    const int src = (rank + rr) % world;  // start with the local piece, then walk the peers
-    const long long off = (j - static_cast<long long>(rr) * n8) * 8;
-    const uint4 val =
-        *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(shards.p[src]) + t.shard_off[pc] + off);
-    *reinterpret_cast<uint4*>(dst + t.full_off[pc] + static_cast<long long>(src) * t.piece_len[pc] + off) = val;
+  // A peer load over NVLink takes microseconds: every thread keeps kUnroll 16-byte loads in flight so that the
+  // capped grid still covers the bandwidth-delay product of the link.
+  constexpr int kUnroll = 8;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total; i0 += stride * kUnroll) {
+    uint4 val[kUnroll];
+    __nv_bfloat16* out[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long i = i0 + u * stride;
+      out[u] = nullptr;
+      if (i < total) {
+        int pc = 0;
+        while (pc + 1 < t.n && i >= t.vec_start[pc + 1]) ++pc;
+        const long long j = i - t.vec_start[pc];
+        const long long n8 = t.piece_len[pc] >> 3;
+        const int rr = static_cast<int>(j / n8);
+        const int src = (rank + rr) % world;  // start with the local piece, then walk the peers
+        const long long off = (j - static_cast<long long>(rr) * n8) * 8;
+        val[u] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(shards.p[src]) + t.shard_off[pc] + off);
+        out[u] = dst + t.full_off[pc] + static_cast<long long>(src) * t.piece_len[pc] + off;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u)
+      if (out[u]) *reinterpret_cast<uint4*>(out[u]) = val[u];
   }
 }
 

@@ -128,6 +128,8 @@ def _fn(name: str):
         _FN["sample_f"] = _lib.declare("apb_sample_filtered", [vp, ll, vp, i, i, u, vp, vp, vp, vp, vp, vp, vp])
         _FN["prefix_tc"] = _lib.declare("apb_decode_prefix_tc",
                                         [vp, i, vp, vp, vp, i, vp, vp, vp, ll, vp, vp, i, i, i, i, i, f, vp])
+        _FN["qkv_post"] = _lib.declare("apb_decode_qkv_post", [vp, ll, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, f, vp])
+        _FN["swiglu32"] = _lib.declare("apb_swiglu_f32in", [vp, vp, ll, ll, vp])
         _FN["norm32"] = _lib.declare("apb_rmsnorm_fwd_f32in", [vp, vp, vp, vp, vp, i, i, f, f, vp])
     return _FN[name]
 
@@ -216,6 +218,8 @@ class SamplerEngine:
         # fp32 split-K accumulators of the two skinny projections (kept zero between uses by the norm kernel)
         self.acc_o = torch.zeros((B, c.hidden_size), **f32)
         self.acc_d = torch.zeros((B, c.hidden_size), **f32)
+        self.acc_qkv = torch.zeros((B, c.qkv_size), **f32)
+        self.acc_gu = torch.zeros((B, 2 * c.intermediate_size), **f32) if not c.is_moe else None
         self.d_new_tok = torch.zeros(B, **i32)
         self.d_new_lp = torch.zeros(B, **f32)
 
@@ -441,6 +445,12 @@ class SamplerEngine:
         tiles = (H + 127) // 128
         so = max(1, min(148 // tiles, (c.q_size + 63) // 64))
         sd = max(1, min(148 // tiles, (c.intermediate_size + 63) // 64))
+        qkv_tiles = (c.qkv_size + 127) // 128
+        sq = max(1, min(148 // qkv_tiles, (H + 63) // 64)) if (B <= 128 and c.head_dim in (64, 128, 256)) else 1
+        if os.environ.get("APB_DECODE_QKV_SPLITS"):
+            sq = int(os.environ["APB_DECODE_QKV_SPLITS"])
+        acc_qkv = self.acc_qkv[:B]
+        sgu = int(os.environ.get("APB_DECODE_GU_SPLITS", "1"))      # >1: split-K gate/up with a separate SwiGLU pass
         stream = None
         for li in range(c.num_layers):
             blk = self.model.blocks[li]
@@ -448,18 +458,37 @@ class SamplerEngine:
                 h, stream = norm.rmsnorm(x, blk.ln1, c.rms_norm_eps, None)
             else:
                 h, stream = self._norm_f32(acc_d, blk.ln1, stream)
-            qkv = gemm.matmul_nt(h, blk.wqkv)
-            q, k, v = norm.qknorm_rope(qkv, blk.q_norm, blk.k_norm, *self.model.rope(self.device), positions,
-                                       c.num_heads, c.num_kv_heads, c.head_dim, c.rms_norm_eps)
-            _lib.check(_fn("kvw")(_lib.ptr(k), k.stride(0), _lib.ptr(v), v.stride(0), _lib.ptr(slots),
-                                  _lib.ptr(self.kcache[li]), _lib.ptr(self.vcache[li]), B, c.num_kv_heads, c.head_dim,
-                                  _lib.stream_ptr()), "kv_cache_write")
+            if sq > 1:
+                # split-K qkv into fp32 sums, then one kernel: q/k norm + RoPE, q to bf16, k and v into the cache
+                gemm.gemm_raw(h, blk.wqkv, acc_qkv, M=B, N=c.qkv_size, K=H, epi=gemm.EPI_F32_ATOMIC, splits=sq, bn=128)
+                q = torch.empty((B, c.num_heads, c.head_dim), device=self.device, dtype=torch.bfloat16)
+                cos_t, sin_t = self.model.rope(self.device)
+                _lib.check(_fn("qkv_post")(_lib.ptr(acc_qkv), acc_qkv.stride(0), _lib.ptr(blk.q_norm), _lib.ptr(blk.k_norm),
+                                           _lib.ptr(cos_t), _lib.ptr(sin_t), _lib.ptr(positions), _lib.ptr(slots),
+                                           _lib.ptr(q), _lib.ptr(self.kcache[li]), _lib.ptr(self.vcache[li]), B,
+                                           c.num_heads, c.num_kv_heads, c.head_dim, c.rms_norm_eps, _lib.stream_ptr()),
+                           "decode_qkv_post")
+            else:
+                qkv = gemm.matmul_nt(h, blk.wqkv)
+                q, k, v = norm.qknorm_rope(qkv, blk.q_norm, blk.k_norm, *self.model.rope(self.device), positions,
+                                           c.num_heads, c.num_kv_heads, c.head_dim, c.rms_norm_eps)
+                _lib.check(_fn("kvw")(_lib.ptr(k), k.stride(0), _lib.ptr(v), v.stride(0), _lib.ptr(slots),
+                                      _lib.ptr(self.kcache[li]), _lib.ptr(self.vcache[li]), B, c.num_kv_heads,
+                                      c.head_dim, _lib.stream_ptr()), "kv_cache_write")
             a = self._decode_attention(li, q, B).reshape(B, -1)
             gemm.gemm_raw(a, blk.wo, acc_o, M=B, N=H, K=c.q_size, epi=gemm.EPI_F32_ATOMIC, splits=so, bn=128)
             h2, stream = self._norm_f32(acc_o, blk.ln2, stream)
             act = torch.empty((B, c.intermediate_size), device=self.device, dtype=torch.bfloat16)
-            gemm.gemm_raw(h2, blk.wgu, None, M=B, N=2 * c.intermediate_size, K=H, epi=gemm.EPI_SWIGLU, out2=act,
-                          bn=self._gate_up_bn(B))
+            if sgu > 1:
+                # 256-wide tiles halve the activation re-reads; two K splits restore one CTA per SM
+                acc_gu = self.acc_gu[:B]
+                gemm.gemm_raw(h2, blk.wgu, acc_gu, M=B, N=2 * c.intermediate_size, K=H, epi=gemm.EPI_F32_ATOMIC,
+                              splits=sgu, bn=256)
+                _lib.check(_fn("swiglu32")(_lib.ptr(acc_gu), _lib.ptr(act), B, c.intermediate_size, _lib.stream_ptr()),
+                           "swiglu_f32in")
+            else:
+                gemm.gemm_raw(h2, blk.wgu, None, M=B, N=2 * c.intermediate_size, K=H, epi=gemm.EPI_SWIGLU, out2=act,
+                              bn=self._gate_up_bn(B))
             gemm.gemm_raw(act, blk.wdown, acc_d, M=B, N=H, K=c.intermediate_size, epi=gemm.EPI_F32_ATOMIC, splits=sd,
                           bn=128)
         h, _ = self._norm_f32(acc_d, self.model.final_norm, stream)

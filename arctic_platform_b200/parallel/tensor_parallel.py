@@ -45,14 +45,20 @@ class TPContext:
         self.flags = EpochFlags(device, group if self.world > 1 else False)
         self.max_rows, self.max_cols = max_rows, max_cols
         g = group if self.world > 1 else False
-        self.act = SymmetricBuffer(max_rows * max_cols, torch.bfloat16, device, g)
+        # two activation buffers used alternately: a rank overwrites buffer b again only two calls later, after it
+        # has passed the next call's barrier -- which every peer reaches only once its reads of b have finished --
+        # so ONE barrier per call orders both "shards are written" and "shards may be overwritten"
+        self.act = [SymmetricBuffer(max_rows * max_cols, torch.bfloat16, device, g) for _ in range(2)]
         self.acc = [SymmetricBuffer(max_rows * max_cols, torch.float32, device, g) for _ in range(2)]
         self._flip = 0
+        self._act_flip = 0
 
-    def act_view(self, rows: int, cols: int) -> torch.Tensor:
-        if rows * cols > self.act.numel:
+    def next_act(self, rows: int, cols: int):
+        buf = self.act[self._act_flip]
+        self._act_flip ^= 1
+        if rows * cols > buf.numel:
             raise ValueError("activation exceeds the tensor-parallel scratch")
-        return self.act.tensor[: rows * cols].view(rows, cols)
+        return buf, buf.tensor[: rows * cols].view(rows, cols)
 
 
 def ag_gemm(ctx: TPContext, x_local: torch.Tensor, w_local: torch.Tensor, bn: int = 0) -> torch.Tensor:
@@ -61,17 +67,15 @@ def ag_gemm(ctx: TPContext, x_local: torch.Tensor, w_local: torch.Tensor, bn: in
     N = w_local.shape[0]
     if ctx.world == 1:
         return gemm.matmul_nt(x_local, w_local)
-    buf = ctx.act_view(rows, K)
+    symm, buf = ctx.next_act(rows, K)
     buf.copy_(x_local)
     f = _fns()
     s = _lib.stream_ptr()
     flags = ctx.flags.ptr_table()
     _lib.check(f["wait"](flags, ctx.rank, ctx.world, ctx.flags.next(), s), "apb_epoch_wait")
     out = torch.empty((ctx.world * rows, N), device=x_local.device, dtype=torch.bfloat16)
-    _lib.check(f["ag"](ctx.act.ptr_table(), ctx.world, rows, _lib.ptr(w_local), _lib.ptr(out), N, K, K, w_local.stride(0),
+    _lib.check(f["ag"](symm.ptr_table(), ctx.world, rows, _lib.ptr(w_local), _lib.ptr(out), N, K, K, w_local.stride(0),
                        out.stride(0), bn, s), "apb_gemm_ag")
-    # peers may overwrite their shard only after everyone has read it
-    _lib.check(f["wait"](flags, ctx.rank, ctx.world, ctx.flags.next(), s), "apb_epoch_wait")
     return out
 
 
