@@ -674,9 +674,17 @@ class SamplerEngine:
             temp = torch.full((n,), float(sp.temperature), device=self.device, dtype=torch.float32)
             tok0 = torch.empty(n, device=self.device, dtype=torch.int32)
             lp0 = torch.empty(n, device=self.device, dtype=torch.float32)
-            _lib.check(_fn("sample")(_lib.ptr(logits), logits.stride(0), _lib.ptr(temp), n, c.vocab_size,
-                                     ctypes.c_uint((self.seed * 2654435761 + 12345) & 0xFFFFFFFF), _lib.ptr(self.d_step),
-                                     _lib.ptr(tok0), _lib.ptr(lp0), _lib.stream_ptr()), "sample")
+            seed0 = ctypes.c_uint((self.seed * 2654435761 + 12345) & 0xFFFFFFFF)
+            if self._filter_on:       # the first token obeys the same top-k / top-p cut-off as the decode steps
+                topk0 = torch.full((n,), int(sp.top_k) if sp.top_k and sp.top_k > 0 else 0, device=self.device, dtype=torch.int32)
+                topp0 = torch.full((n,), float(sp.top_p), device=self.device, dtype=torch.float32)
+                thr0 = torch.empty(n, device=self.device, dtype=torch.float32)
+                _lib.check(_fn("sample_f")(_lib.ptr(logits), logits.stride(0), _lib.ptr(temp), n, c.vocab_size, seed0,
+                                           _lib.ptr(self.d_step), _lib.ptr(topk0), _lib.ptr(topp0), _lib.ptr(thr0),
+                                           _lib.ptr(tok0), _lib.ptr(lp0), _lib.stream_ptr()), "sample_filtered")
+            else:
+                _lib.check(_fn("sample")(_lib.ptr(logits), logits.stride(0), _lib.ptr(temp), n, c.vocab_size, seed0,
+                                         _lib.ptr(self.d_step), _lib.ptr(tok0), _lib.ptr(lp0), _lib.stream_ptr()), "sample")
             self.d_step += 1
             st = torch.tensor(slots, device=self.device, dtype=torch.long)
             P_t = torch.tensor([live[s].prompt_len for s in slots], device=self.device, dtype=torch.int32)
