@@ -205,6 +205,49 @@ gather_unit_kernel(PeerPtrs shards, GatherTable t, int rank, int world, __nv_bfl
   }
 }
 
+// ZeRO-3 reduce-scatter of one unit: for every parameter, this rank's piece of the fp32 gradient is summed over all
+// ranks' gradient buffers (P2P loads), scaled and written to the shard-layout buffer; the sum of squares feeds the
+// global gradient norm.  Table fields: full_off = element offset of THIS rank's piece inside the unit's gradients,
+// shard_off = destination offset, vec_start counts float4 groups.  One flag barrier per launch.
+__global__ void __launch_bounds__(256)
+zero3_reduce_unit_kernel(PeerPtrs grads, GatherTable t, PeerPtrs flags, int rank, int world, int epoch, float scale,
+                         float* __restrict__ reduced, double* __restrict__ sumsq, int* status) {
+  if (!epoch_barrier(flags, rank, world, epoch, status)) return;
+  const long long total = t.vec_start[t.n];
+  double acc = 0.0;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    int pc = 0;
+    while (pc + 1 < t.n && i >= t.vec_start[pc + 1]) ++pc;
+    const long long off = (i - t.vec_start[pc]) * 4;
+    float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < world; ++r) {
+      const int src = (rank + r) % world;
+      const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[src]) + t.full_off[pc] + off);
+      s4.x += v.x;
+      s4.y += v.y;
+      s4.z += v.z;
+      s4.w += v.w;
+    }
+    s4.x *= scale;
+    s4.y *= scale;
+    s4.z *= scale;
+    s4.w *= scale;
+    *reinterpret_cast<float4*>(reduced + t.shard_off[pc] + off) = s4;
+    acc += static_cast<double>(s4.x) * s4.x + static_cast<double>(s4.y) * s4.y + static_cast<double>(s4.z) * s4.z +
+           static_cast<double>(s4.w) * s4.w;
+  }
+  __shared__ double red[8];
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double tt = 0.0;
+    for (int w = 0; w < blockDim.x / 32; ++w) tt += red[w];
+    atomicAdd(sumsq, tt);
+  }
+}
+
 __global__ void sumsq_f32_kernel(const float* __restrict__ x, long long n, double* __restrict__ out) {
   double acc = 0.0;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
@@ -302,6 +345,30 @@ int apb_gather_unit(void* const* shard_ptrs, int rank, int world, const long lon
   const long long need = (acc + 255) / 256;
   gather_unit_kernel<<<static_cast<int>(need < cap ? need : cap), 256, 0, s>>>(to_peers(shard_ptrs, world), t, rank, world,
                                                                               static_cast<__nv_bfloat16*>(dst));
+  return static_cast<int>(cudaGetLastError());
+}
+
+// grad_ptrs: per-rank pointers to the unit's part of the fp32 gradient buffers.  src_off[i]: element offset of this
+// rank's piece of parameter i inside the unit; piece_len[i] (multiple of 4); dst_off[i]: offset inside `reduced`.
+int apb_zero3_reduce_unit(void* const* grad_ptrs, void* const* flag_ptrs, int rank, int world, int epoch,
+                          const long long* src_off, const long long* piece_len, const long long* dst_off, int n_pieces,
+                          float scale, float* reduced, double* sumsq, cudaStream_t s) {
+  if (world > kMaxRanks || n_pieces < 1 || n_pieces > kMaxGatherPieces) return kBadArgument;
+  GatherTable t;
+  t.n = n_pieces;
+  long long acc = 0;
+  for (int i = 0; i < n_pieces; ++i) {
+    if (piece_len[i] % 4 || src_off[i] % 4 || dst_off[i] % 4) return kBadArgument;
+    t.full_off[i] = src_off[i];
+    t.piece_len[i] = piece_len[i];
+    t.shard_off[i] = dst_off[i];
+    t.vec_start[i] = acc;
+    acc += piece_len[i] / 4;
+  }
+  t.vec_start[n_pieces] = acc;
+  zero3_reduce_unit_kernel<<<grid_for(acc > 0 ? acc : 1), 256, 0, s>>>(to_peers(grad_ptrs, world), t,
+                                                                       to_peers(flag_ptrs, world), rank, world, epoch,
+                                                                       scale, reduced, sumsq, status_device_ptr());
   return static_cast<int>(cudaGetLastError());
 }
 

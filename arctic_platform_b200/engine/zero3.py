@@ -200,14 +200,18 @@ class Zero3State:
     def reduce_pieces_fused(self, fn_r, flags_tbl, s) -> None:
         e = self.e
         W, r = e.world, e.rank
+        fn = _fused_reduce()
         for ui, u in enumerate(e.units):
             base = e.unit_shard_off[ui]
-            for _name, fo, pl, so in self.pieces[ui]:
-                gp = e.grad_buf.ptr_table((u.offset + fo) * 4)
-                mc = e.grad_buf.mc_ptr((u.offset + fo) * 4)
-                out = e.reduced.data_ptr() + (base + so) * 4
-                _lib.check(fn_r(gp, mc, flags_tbl, r, W, e.flags.next(), r * pl, pl, 1.0 / W, ctypes.c_void_p(out),
-                                _lib.ptr(e.sumsq), s), "apb_zero_reduce")
+            rows = self.pieces[ui]
+            gp = e.grad_buf.ptr_table(u.offset * 4)
+            for lo in range(0, len(rows), 24):                     # one launch (one flag barrier) per 24 parameters
+                part = rows[lo:lo + 24]
+                n = len(part)
+                arr = ctypes.c_longlong * n
+                _lib.check(fn(gp, flags_tbl, r, W, e.flags.next(), arr(*[p[1] + r * p[2] for p in part]),
+                              arr(*[p[2] for p in part]), arr(*[base + p[3] for p in part]), n, 1.0 / W,
+                              _lib.ptr(e.reduced), _lib.ptr(e.sumsq), s), "apb_zero3_reduce_unit")
 
     def reduced_pieces_collective(self) -> List[torch.Tensor]:
         """Per unit: this rank's shard of the averaged gradient (shard layout)."""
@@ -223,6 +227,17 @@ class Zero3State:
 
 
 _GATHER = None
+_REDUCE = None
+
+
+def _fused_reduce():
+    global _REDUCE
+    if _REDUCE is None:
+        c = ctypes
+        _REDUCE = _lib.declare("apb_zero3_reduce_unit", [c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_void_p,
+                                                          c.c_void_p, c.c_void_p, c.c_int, c.c_float, c.c_void_p,
+                                                          c.c_void_p, c.c_void_p])
+    return _REDUCE
 
 
 def _fused_gather():
