@@ -88,7 +88,7 @@ class Zero3State:
         self.side = torch.cuda.Stream(device=dev) if engine.on_cuda else None
         self.ready: List[Optional[torch.cuda.Event]] = [None, None]
         self.gathers = 0
-        self.gather_ctas = int(os.environ.get("APB_ZERO3_GATHER_CTAS", "48"))   # SMs lent to a prefetch
+        self.gather_ctas = int(os.environ.get("APB_ZERO3_GATHER_CTAS", "128"))   # SMs lent to a prefetch
         for ui in self.resident:
             self._gather(ui, self.resident[ui])
         self._install_hooks()
