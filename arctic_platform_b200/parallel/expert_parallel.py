@@ -80,9 +80,12 @@ def plan_routing(idx: torch.Tensor, num_experts: int, world: int, rank: int, gro
     pos = torch.arange(P, device=idx.device) - first[sorted_e]
     dst_row = (start[sorted_e] + pos).to(torch.int32)
     dst_rank = torch.div(sorted_e, El, rounding_mode="floor").to(torch.int32)
-    recv_counts = blk[rank].cpu()
-    send = counts.view(world, El).sum(1).tolist()
-    recv = allc[:, rank * El:(rank + 1) * El].sum(1).tolist()
+    # ONE device->host copy per layer call: the count matrix; every host-side number derives from it
+    allc_h = allc.cpu()
+    mine_h = allc_h[:, rank * El:(rank + 1) * El]
+    recv_counts = mine_h.sum(0)
+    send = allc_h[rank].view(world, El).sum(1).tolist()
+    recv = mine_h.sum(1).tolist()
     routing = Routing(order, torch.div(order, k, rounding_mode="floor").to(torch.int32), dst_rank, dst_row,
                       recv_counts, int(recv_counts.sum()), send, recv, P)
     routing._allc = allc
