@@ -195,6 +195,8 @@ def segment_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, layout:
                       scale: Optional[float] = None) -> torch.Tensor:
     """q [T,Hq,D], k/v [T,Hkv,D] on the packed token axis -> o [T,Hq,D]."""
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if not q.is_cuda:
+    if not q.is_cuda or q.shape[-1] != 128:
+        # the tcgen05 kernels are written for head_dim 128 (the Qwen3 family); other head sizes (64: test presets,
+        # 256: Qwen3.5 hybrids) run the dense PyTorch expression, on either device
         return attention_ref(q, k, v, layout, scale)
     return _SegmentAttentionFn.apply(q, k, v, layout, scale)
