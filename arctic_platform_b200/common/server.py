@@ -258,23 +258,18 @@ class ArcticRLServerCore:
         src = self._job(source_job_id, ("training",))
         t0 = time.perf_counter()
         total = 0
+        from .utils.weight_sync import sync_pair
+        strategies = set()
         for tid in target_job_ids:
             dst = self._job(tid, ("sampling", "log_prob"))
             for i, dw in enumerate(dst.workers):
                 sw = src.workers[i % len(src.workers)]
-                total += self._sync_pair(sw, dw)
-        return {"status": "ok", "num_tensors": total, "seconds": time.perf_counter() - t0}
-
-    def _sync_pair(self, sw, dw) -> int:
-        s_obj = getattr(sw, "obj", None)
-        d_obj = getattr(dw, "obj", None)
-        if s_obj is not None and d_obj is not None:
-            return s_obj.sync_weights_to(d_obj)
-        # different processes: stream named tensors through the actor interface
-        names = sw.call("get_parameter_names")
-        for name in names:
-            dw.call("load_named_weight", name, sw.call("get_named_weight", name))
-        return len(names)
+                r = sync_pair(sw, dw, cuda_ipc=cuda_ipc, low_memory=low_memory,
+                              via_file=bool(src.config.get("weight_sync_via_file")))
+                total += r["num_tensors"]
+                strategies.add(r["strategy"])
+        return {"status": "ok", "num_tensors": total, "seconds": time.perf_counter() - t0,
+                "strategies": sorted(strategies)}
 
     def weight_norm(self, training_job_id: Optional[int] = None, sampling_job_id: Optional[int] = None) -> Dict[str, Any]:
         out: Dict[str, Any] = {}

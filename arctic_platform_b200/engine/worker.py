@@ -170,9 +170,57 @@ class EngineWorker:
         raise KeyError(name)
 
     def load_named_weight(self, name: str, tensor: torch.Tensor) -> None:
+        self.load_weights([(name, tensor)])
+
+    def _target_model(self):
+        return self.sampler.model if self.sampler is not None else self.engine.model
+
+    def load_weights(self, named_tensors) -> int:
+        """Copies ``(hf_name, tensor)`` pairs into this worker's model (sampler or forward-only engine)."""
         from ..models.hf_io import load_hf_tensor
-        model = self.sampler.model if self.sampler is not None else self.engine.model
-        load_hf_tensor(model, name, tensor)
+        n = 0
+        model = self._target_model()
+        for name, t in named_tensors:
+            load_hf_tensor(model, name, t)
+            n += 1
+        if self.sampler is not None and hasattr(self.sampler, "weights_updated"):
+            self.sampler.weights_updated()
+        return n
+
+    def get_weights(self) -> List:
+        """Every weight under its Hugging Face name as CPU tensors: one call, one pass over the parameters (one
+        gather of the shards under ZeRO-3) -- the bulk strategy of a cross-process sync."""
+        return [(n, t.detach().to("cpu", copy=True)) for n, t in self.engine.iter_hf_tensors()]
+
+    def weight_buckets(self, bucket_bytes: int = 256 << 20) -> List[List[str]]:
+        """Names grouped so that each group is at most ``bucket_bytes`` (one tensor may exceed it alone)."""
+        from ..models.hf_io import hf_param_names
+        sizes = {n: t.numel() * t.element_size() for n, t in self.engine.iter_hf_tensors()}
+        out, cur, tot = [], [], 0
+        for n in hf_param_names(self.model_cfg):
+            if cur and tot + sizes[n] > bucket_bytes:
+                out.append(cur)
+                cur, tot = [], 0
+            cur.append(n)
+            tot += sizes[n]
+        if cur:
+            out.append(cur)
+        return out
+
+    def get_weight_bucket(self, names: List[str]) -> List:
+        want = set(names)
+        return [(n, t.detach().to("cpu", copy=True)) for n, t in self.engine.iter_hf_tensors() if n in want]
+
+    def save_weights_to_path(self, path: str) -> Dict[str, Any]:
+        """Writes the weights as one safetensors file (a tmpfs path makes this the shared-memory hand-over)."""
+        from ..models.hf_io import write_safetensors
+        tensors = {n: t.detach().to("cpu") for n, t in self.engine.iter_hf_tensors()}
+        write_safetensors(path, tensors, {"format": "pt"})
+        return {"path": path, "num_tensors": len(tensors), "bytes": sum(t.numel() * t.element_size() for t in tensors.values())}
+
+    def load_weights_from_path(self, path: str) -> int:
+        from ..models.hf_io import read_safetensors
+        return self.load_weights(read_safetensors(path))
 
     def sync_weights_to(self, dst: "EngineWorker") -> int:
         """Pushes this (training) worker's parameters into ``dst`` (a sampling or log-prob worker of the
@@ -195,6 +243,9 @@ class EngineWorker:
     def sleep_inference(self, level: int = 1) -> None:
         if self.sampler is not None:
             self.sampler.sleep(level)
+
+    def has_sampler(self) -> bool:
+        return self.sampler is not None
 
     def wake_inference(self, tags=None) -> None:
         if self.sampler is not None:

@@ -1,0 +1,66 @@
+"""Trainer -> sampler weight hand-over: in-process copy, bulk RPC, bucketed (low memory) RPC and the safetensors file
+path all leave the sampler with the trainer's weights (checked with the fp64 weight norm and a bit-exact compare)."""
+import pytest
+import torch
+
+from arctic_platform_b200.common.utils import weight_sync as ws
+from arctic_platform_b200.engine.worker import EngineWorker
+
+
+class RemoteLike:
+    """Actor that only offers ``call`` (like a worker in another process)."""
+
+    def __init__(self, worker):
+        self._w = worker
+
+    def call(self, method, *a, **kw):
+        return getattr(self._w, method)(*a, **kw)
+
+
+def _worker(job_type, seed):
+    w = EngineWorker(device="cpu")
+    w.initialize({"model_name": "qwen3-tiny", "job_type": job_type, "seed": seed,
+                  "ds_config": {"optimizer": {"params": {"lr": 1e-3}}}, "vllm_config": {"max_model_len": 64}})
+    return w
+
+
+@pytest.fixture(scope="module")
+def trainer():
+    return _worker("training", 1)
+
+
+def _flat(worker):
+    m = worker.sampler.model if worker.sampler is not None else worker.engine.model
+    return torch.cat([p.data.reshape(-1).float() for p in m.parameters()])
+
+
+@pytest.mark.parametrize("strategy", ["bulk", "low_mem", "cpu_file", "in_process"])
+def test_strategies_transfer_identical_weights(trainer, strategy, tmp_path):
+    sampler = _worker("sampling", 2)
+    assert abs(sampler.weight_norm()["norm"] - trainer.weight_norm()["norm"]) > 1e-3
+    src, dst = RemoteLike(trainer), RemoteLike(sampler)
+    if strategy == "bulk":
+        n = ws.sync_weights_bulk(src, dst, staged=True)
+    elif strategy == "low_mem":
+        buckets = trainer.weight_buckets(64 << 10)
+        assert len(buckets) > 3 and sum(len(b) for b in buckets) == len(trainer.get_parameter_names())
+        n = ws.sync_weights_low_mem(src, dst, bucket_bytes=64 << 10)
+    elif strategy == "cpu_file":
+        n = ws.sync_weights_cpu_file(src, dst, directory=str(tmp_path))
+        assert list(tmp_path.iterdir()) == []                         # the hand-over file is removed
+    else:
+        from arctic_platform_b200.common.server import InProcessActor
+        r = ws.sync_pair(InProcessActor(trainer), InProcessActor(sampler))
+        assert r["strategy"] == "in_process"
+        n = r["num_tensors"]
+    assert n == len(trainer.get_parameter_names())
+    assert torch.equal(_flat(sampler), _flat(trainer))
+    assert sampler.weight_norm()["norm"] == pytest.approx(trainer.weight_norm()["norm"], rel=1e-9)
+
+
+def test_sync_pair_picks_by_flags(trainer):
+    sampler = _worker("sampling", 3)
+    src, dst = RemoteLike(trainer), RemoteLike(sampler)
+    assert ws.sync_pair(src, dst)["strategy"] == "bulk"
+    assert ws.sync_pair(src, dst, low_memory=True)["strategy"] == "low_mem"
+    assert ws.sync_pair(src, dst, via_file=True)["strategy"] == "cpu_file"
