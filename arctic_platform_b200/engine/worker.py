@@ -230,6 +230,11 @@ class EngineWorker:
         from ..parallel import weight_sync
         dst_model = dst.sampler.model if dst.sampler is not None else dst.engine.model
         n_names = len(hf_param_names(self.model_cfg))
+        dst_engine = dst.engine if dst.sampler is None else None
+        if dst_engine is not None and getattr(dst_engine, "zero3", None) is not None:
+            # the target keeps its parameters as shards too: hand it a full copy and let it cut its own shard
+            dst_engine.load_full_flat(self.engine.full_flat_params())
+            return n_names
         if self.engine.on_cuda and next(dst_model.parameters()).device == self.device:
             flat = getattr(dst_model, "_flat_params", None)
             if flat is None or flat.numel() != self.engine.total:
