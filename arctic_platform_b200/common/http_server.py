@@ -135,6 +135,11 @@ def create_app(core: Optional[ArcticRLServerCore] = None) -> FastAPI:
     async def log_probs(job_id: int, request: LogProbsRequest):
         return await run(app.state.core.log_probs, job_id, request.prompts, request.completions, request.top_k)
 
+    @app.post("/heartbeat")
+    async def heartbeat(job_id: int):
+        await run(app.state.core.heartbeat, job_id)
+        return {"status": "ok"}
+
     @app.get("/status")
     async def status():
         return app.state.core.status()

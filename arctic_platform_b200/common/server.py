@@ -145,8 +145,10 @@ class ArcticRLServerCore:
 
     def heartbeat(self, job_id: int) -> None:
         with self._lock:
-            if job_id in self.jobs:
-                self.jobs[job_id].last_heartbeat = time.time()
+            j = self.jobs.get(int(job_id))
+            if j is None:
+                raise JobError(404, f"unknown job {job_id}")
+            j.last_heartbeat = time.time()
 
     def find_job(self, job_type: str) -> Optional[Job]:
         with self._lock:
