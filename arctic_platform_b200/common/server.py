@@ -141,6 +141,7 @@ class ArcticRLServerCore:
         if self.heartbeat_timeout and time.time() - j.last_heartbeat > self.heartbeat_timeout:
             j.status = "FAILED"
             raise JobError(409, f"job {job_id} missed its heartbeat deadline")
+        j.last_heartbeat = time.time()      # any call on the job is a sign of life from its client
         return j
 
     def heartbeat(self, job_id: int) -> None:
