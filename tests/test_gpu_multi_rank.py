@@ -225,3 +225,54 @@ def test_zero3_sharded_parameters_match_replicated_on_two_gpus():
             assert (r[other][3] - r["z1"][3]).abs().max() < 0.05
             assert abs(r[other][4] - r["z1"][4]) <= 1e-3 * r["z1"][4]
     assert torch.equal(res[0]["z3"][0], res[1]["z3"][0])
+
+
+def _ulysses_main(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import copy
+        from arctic_platform_b200.models.config import PRESETS
+        from arctic_platform_b200.models.decoder import DecoderLM, token_logprobs
+        from arctic_platform_b200.ops import _lib
+        from arctic_platform_b200.parallel.ulysses import apply_sequence_parallelism, sp_token_logprobs
+        from arctic_platform_b200.rl.zorro_train.layout import build_packed_batch
+        from tests.test_zorro_equivalence_cpu import make_grpo_batch
+        cfg = PRESETS["qwen3-tiny-d128"]
+        ref = DecoderLM(cfg, "cuda", torch.bfloat16).init_weights(seed=4)
+        spm = DecoderLM(cfg, "cuda", torch.bfloat16).init_weights(seed=4)
+        apply_sequence_parallelism(spm, dist.group.WORLD)
+        ids, mask, R = make_grpo_batch(n_prompts=3, n_samples=3, p_rng=(60, 200), r_rng=(10, 90), seed=6)
+        pb = build_packed_batch(ids, mask, R).to("cuda")
+        lp_ref, _ = token_logprobs(ref, pb)
+        lp_ref.sum().backward()
+        lp, _, owned = sp_token_logprobs(spm, copy.copy(pb), dist.group.WORLD)
+        lp.sum().backward()
+        _lib.check_status("ulysses")
+        err_lp = float((lp - lp_ref[owned]).abs().max())
+        cos = []
+        for p, q in zip(spm.parameters(), ref.parameters()):
+            g = p.grad.float().clone() if p.grad is not None else torch.zeros_like(p, dtype=torch.float32)
+            dist.all_reduce(g)
+            cos.append(float(torch.nn.functional.cosine_similarity(g.flatten(), q.grad.float().flatten(), dim=0)))
+        n = torch.tensor([int(owned.sum())], device="cuda")
+        dist.all_reduce(n)
+        torch.save({"lp": err_lp, "cos": min(cos), "n": int(n), "N": int(pb.labels.numel())}, os.path.join(out_dir, f"u{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_ulysses_sequence_parallel_on_two_gpus():
+    """Head <-> sequence all-to-all around the tcgen05 segment attention: log-probs and (summed) gradients of the
+    sequence-parallel model equal the single-GPU model's."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_ulysses_main, args=(2, _free_port(), d), nprocs=2, join=True)
+        res = [torch.load(os.path.join(d, f"u{r}.pt"), weights_only=False) for r in range(2)]
+    for r in res:
+        assert r["n"] == r["N"] and r["lp"] < 0.08 and r["cos"] > 0.97, r
