@@ -125,12 +125,25 @@ class Unit:
     params: List[Tuple[str, torch.nn.Parameter]]
     offset: int = 0      # element offset of the unit in the flat buffers
     length: int = 0      # padded element count (multiple of 8 * world)
+    local_only: bool = False   # expert-parallel parameters: every rank holds DIFFERENT values, nothing is reduced
+
+    def shard_len(self, world: int) -> int:
+        return self.length if self.local_only else self.length // world
 
 
 def model_units(model: DecoderLM) -> List[Unit]:
+    """Embedding (+ untied lm-head), one unit per block, the final norm.  Parameters tagged ``expert_parallel`` (the
+    expert weights of a layer whose experts are sharded over ranks) form their own ``local_only`` unit: their
+    gradients are complete on the owning rank (dispatch brought every rank's tokens), so they are only rescaled, and
+    the optimizer state of such a unit lives wholly on its rank."""
     units = [Unit("embed", [("embed", model.embed)] + ([("lm_head", model.lm_head)] if model.lm_head is not None else []))]
     for i, blk in enumerate(model.blocks):
-        units.append(Unit(f"block{i}", [(f"blocks.{i}.{n}", p) for n, p in blk.named_parameters()]))
+        named = [(f"blocks.{i}.{n}", p) for n, p in blk.named_parameters()]
+        dense = [(n, p) for n, p in named if not getattr(p, "expert_parallel", False)]
+        local = [(n, p) for n, p in named if getattr(p, "expert_parallel", False)]
+        units.append(Unit(f"block{i}", dense))
+        if local:
+            units.append(Unit(f"block{i}.experts", local, local_only=True))
     units.append(Unit("final", [("final_norm", model.final_norm)]))
     return units
 
@@ -201,17 +214,17 @@ class TrainEngine:
                 p.grad_f32 = gflat[o:o + n].view(shape)
         self.flags = EpochFlags(self.device, self.group if use_symm else False) if self.on_cuda else None
         # optimizer shards: for every unit this rank owns [offset + rank*len/W, +len/W)
-        self.shard_total = self.total // W
         self.unit_shard_off: List[int] = []
         acc = 0
         for u in self.units:
             self.unit_shard_off.append(acc)
-            acc += u.length // W
+            acc += u.shard_len(W)
+        self.shard_total = acc
         opt_dev = "cpu" if (self.cfg.offload_optimizer and not self.on_cuda) else self.device
         self.master = torch.empty(self.shard_total, dtype=torch.float32, device=opt_dev)
         for u, so in zip(self.units, self.unit_shard_off):
-            n = u.length // W
-            s = u.offset + self.rank * n
+            n = u.shard_len(W)
+            s = u.offset + (0 if u.local_only else self.rank * n)
             self.master[so:so + n].copy_(flat[s:s + n].float())
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
@@ -236,12 +249,25 @@ class TrainEngine:
                 o, n, shape = self.param_slices[name]
                 p.grad_f32 = gflat[o:o + n].view(shape)
         opt_dev = "cpu" if (self.cfg.offload_optimizer and not self.on_cuda) else self.device
-        self.master = self.zero3.shard_buf.tensor.float().to(opt_dev)
+        self.master = self._zero3_state_from_params().to(opt_dev)
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
         self.reduced = torch.empty(self.shard_total, dtype=torch.float32, device=self.device)
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
         self._offloaded = {}
+
+    def _zero3_state_from_params(self) -> torch.Tensor:
+        """fp32 copy of this rank's parameters in the optimizer-state layout: bf16 shards of the sharded units, the
+        whole of every expert-parallel unit."""
+        z = self.zero3
+        parts = []
+        for ui, u in enumerate(self.units):
+            if u.local_only:
+                parts.append(z.resident[ui].float())
+            else:
+                o = z.bf16_off[ui]
+                parts.append(z.shard_buf.tensor[o:o + z.unit_shard_len[ui]].float())
+        return torch.cat(parts)
 
     # ------------------------------------------------------------------ training loop pieces
     def zero_grad(self) -> None:
@@ -301,6 +327,9 @@ class TrainEngine:
         if self.zero3 is not None:
             return self._step_fused_zero3(lr, bias1, bias2, fn_r, fn_a, fn_w, flags_tbl, s)
         for u, so in zip(self.units, self.unit_shard_off):
+            if u.local_only and W > 1:
+                self._local_unit_reduce(u, so, fn_r, flags_tbl, s)
+                continue
             n = u.length // W
             shard_off = r * n
             gp = self.grad_buf.ptr_table(u.offset * 4)
@@ -312,6 +341,10 @@ class TrainEngine:
             dist.all_reduce(self.sumsq, group=self.group)
         self._grad_norm_tensor = self.sumsq.sqrt().float().clone()
         for u, so in zip(self.units, self.unit_shard_off):
+            if u.local_only and W > 1:
+                self._local_unit_adamw(u, so, self.param_buf.tensor.data_ptr() + u.offset * 2, fn_a, flags_tbl, lr, bias1,
+                                       bias2, s)
+                continue
             n = u.length // W
             shard_off = r * n
             pp = self.param_buf.ptr_table(u.offset * 2)
@@ -326,6 +359,23 @@ class TrainEngine:
         if W > 1:
             _lib.check(fn_w(flags_tbl, r, W, self.flags.next(), s), "apb_epoch_wait")
 
+    def _local_unit_reduce(self, u: Unit, so: int, fn_r, flags_tbl, s) -> None:
+        """Expert-parallel unit: the local gradient is the whole gradient; scale it like the data-parallel mean."""
+        own = (ctypes.c_void_p * 1)(self.grad_buf.tensor.data_ptr() + u.offset * 4)
+        _lib.check(fn_r(own, ctypes.c_void_p(0), flags_tbl, 0, 1, 0, 0, u.length, 1.0 / self.world,
+                        ctypes.c_void_p(self.reduced.data_ptr() + so * 4), _lib.ptr(self.sumsq), s), "apb_zero_reduce")
+
+    def _local_unit_adamw(self, u: Unit, so: int, param_ptr: int, fn_a, flags_tbl, lr, bias1, bias2, s) -> None:
+        cfg = self.cfg
+        own = (ctypes.c_void_p * 1)(param_ptr)
+        _lib.check(fn_a(own, ctypes.c_void_p(0), flags_tbl, 0, 1, 0, 0, u.length,
+                        ctypes.c_void_p(self.reduced.data_ptr() + so * 4),
+                        ctypes.c_void_p(self.master.data_ptr() + so * 4),
+                        ctypes.c_void_p(self.exp_avg.data_ptr() + so * 4),
+                        ctypes.c_void_p(self.exp_avg_sq.data_ptr() + so * 4), _lib.ptr(self.sumsq),
+                        lr, cfg.betas[0], cfg.betas[1], cfg.eps, cfg.weight_decay, bias1, bias2,
+                        cfg.max_grad_norm, s), "apb_zero_adamw")
+
     def _step_fused_zero3(self, lr, bias1, bias2, fn_r, fn_a, fn_w, flags_tbl, s) -> None:
         """Stage 3: every parameter piece is reduced from all ranks into the owner's shard layout, then ONE AdamW
         launch per unit updates master, moments and this rank's bf16 shard (no all-gather: peers pull what they need
@@ -333,12 +383,18 @@ class TrainEngine:
         cfg = self.cfg
         z = self.zero3
         z.reduce_pieces_fused(fn_r, flags_tbl, s)
+        for ui, (u, so) in enumerate(zip(self.units, self.unit_shard_off)):
+            if u.local_only:
+                self._local_unit_reduce(u, so, fn_r, flags_tbl, s)
         dist.all_reduce(self.sumsq, group=self.group)
         self._grad_norm_tensor = self.sumsq.sqrt().float().clone()
         own = (ctypes.c_void_p * 1)()
         for ui, so in enumerate(self.unit_shard_off):
+            if self.units[ui].local_only:
+                self._local_unit_adamw(self.units[ui], so, z.resident[ui].data_ptr(), fn_a, flags_tbl, lr, bias1, bias2, s)
+                continue
             n = z.unit_shard_len[ui]
-            own[0] = z.shard_buf.tensor.data_ptr() + so * 2
+            own[0] = z.shard_buf.tensor.data_ptr() + z.bf16_off[ui] * 2
             _lib.check(fn_a(own, ctypes.c_void_p(0), flags_tbl, 0, 1, 0, 0, n, ctypes.c_void_p(self.reduced.data_ptr() + so * 4),
                             ctypes.c_void_p(self.master.data_ptr() + so * 4),
                             ctypes.c_void_p(self.exp_avg.data_ptr() + so * 4),
@@ -359,7 +415,7 @@ class TrainEngine:
         self._grad_norm_tensor = norm.reshape(())
         clip = torch.clamp(cfg.max_grad_norm / (norm + 1e-6), max=1.0) if cfg.max_grad_norm > 0 else None
         for ui, (so, g) in enumerate(zip(self.unit_shard_off, shards)):
-            n = z.unit_shard_len[ui]
+            n = self.units[ui].length if self.units[ui].local_only else z.unit_shard_len[ui]
             g = g.to(self.master.device)
             if clip is not None:
                 g = g * clip.to(g.device)
@@ -368,7 +424,10 @@ class TrainEngine:
             v.mul_(cfg.betas[1]).addcmul_(g, g, value=1 - cfg.betas[1])
             w.mul_(1 - lr * cfg.weight_decay)
             w.addcdiv_(m / bias1, (v / bias2).sqrt_().add_(cfg.eps), value=-lr)
-            z.shard_buf.tensor[so:so + n].copy_(w.to(self.param_dtype))
+            if self.units[ui].local_only:
+                z.resident[ui][:n].copy_(w.to(self.param_dtype))
+            else:
+                z.shard_buf.tensor[z.bf16_off[ui]:z.bf16_off[ui] + n].copy_(w.to(self.param_dtype))
         if self.on_cuda:
             torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
@@ -382,8 +441,11 @@ class TrainEngine:
         gflat = self.grad_buf.tensor
         shards = []
         for u in self.units:
-            n = u.length // W
+            n = u.shard_len(W)
             g = gflat[u.offset:u.offset + u.length]
+            if u.local_only:
+                shards.append(g / W)          # complete on this rank: only the data-parallel mean's 1/W
+                continue
             if W > 1:
                 if self.on_cuda:
                     out = torch.empty(n, dtype=torch.float32, device=self.device)
@@ -404,7 +466,7 @@ class TrainEngine:
         clip = torch.clamp(cfg.max_grad_norm / (norm + 1e-6), max=1.0) if cfg.max_grad_norm > 0 else None
         flat = self.param_buf.tensor
         for u, so, g in zip(self.units, self.unit_shard_off, shards):
-            n = u.length // W
+            n = u.shard_len(W)
             g = g.to(self.master.device)
             if clip is not None:
                 g = g * clip.to(g.device)
@@ -417,7 +479,9 @@ class TrainEngine:
             w.addcdiv_(m / bias1, (v / bias2).sqrt_().add_(cfg.eps), value=-lr)
             new = w.to(self.param_dtype).to(self.device)
             dst = flat[u.offset:u.offset + u.length]
-            if W > 1:
+            if u.local_only:
+                dst.copy_(new)
+            elif W > 1:
                 dist.all_gather_into_tensor(dst, new.contiguous(), group=self.group) if self.on_cuda else \
                     _gloo_all_gather(dst, new, W, self.group)
             else:
@@ -464,12 +528,15 @@ class TrainEngine:
         z = self.zero3
         r = self.rank
         for ui, u in enumerate(self.units):
-            base = self.unit_shard_off[ui]
+            if u.local_only:
+                z.resident[ui].copy_(full[u.offset:u.offset + u.length])
+                continue
+            base = z.bf16_off[ui]
             for _name, fo, pl, so in z.pieces[ui]:
                 src = full[u.offset + fo + r * pl:u.offset + fo + (r + 1) * pl]
                 z.shard_buf.tensor[base + so:base + so + pl].copy_(src)
         if not self.forward_only:
-            self.master.copy_(z.shard_buf.tensor.float())
+            self.master.copy_(self._zero3_state_from_params())
         if self.on_cuda:
             torch.cuda.synchronize(self.device)
         if dist.is_initialized():
@@ -483,7 +550,12 @@ class TrainEngine:
         sq = torch.zeros((), dtype=torch.float64, device=self.device)
         n = sum(p.numel() for p in self.model.parameters())
         if self.zero3 is not None:                       # sum of squares of the shards, added over ranks
-            sq += self.zero3.shard_buf.tensor.double().pow(2).sum()
+            z = self.zero3
+            used = sum(z.unit_shard_len)
+            sq += z.shard_buf.tensor[:used].double().pow(2).sum()
+            for ui, u in enumerate(self.units):          # expert-parallel units: every rank owns different values
+                if u.local_only:
+                    sq += z.resident[ui].double().pow(2).sum()
             dist.all_reduce(sq, group=self.group)
         else:
             for p in self.model.parameters():

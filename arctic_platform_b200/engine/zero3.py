@@ -43,6 +43,10 @@ class Zero3State:
         self.unit_shard_len: List[int] = []
         for u in engine.units:
             rows, off = [], 0
+            if u.local_only:             # expert-parallel unit: already different on every rank, kept whole
+                self.pieces.append([])
+                self.unit_shard_len.append(0)
+                continue
             for name, p in u.params:
                 n = p.numel()
                 if n % (8 * W):
@@ -52,22 +56,27 @@ class Zero3State:
                 off += n // W
             self.pieces.append(rows)
             self.unit_shard_len.append(off)
+        # two offset systems: ``unit_shard_off`` for the fp32 state (master, moments, reduced gradients), which also
+        # holds the whole of every expert-parallel unit, and ``bf16_off`` for the bf16 shard buffer peers read
         engine.unit_shard_off = []
-        acc = 0
-        for n in self.unit_shard_len:
-            engine.unit_shard_off.append(acc)
-            acc += n
-        engine.shard_total = acc
+        self.bf16_off: List[int] = []
+        acc32 = acc16 = 0
+        for u, n in zip(engine.units, self.unit_shard_len):
+            engine.unit_shard_off.append(acc32)
+            self.bf16_off.append(acc16)
+            acc32 += u.length if u.local_only else n
+            acc16 += n
+        engine.shard_total = acc32
         # ---- shard buffer (peers read it) filled from the model's current parameters
-        self.shard_buf = SymmetricBuffer(acc, dt, dev, engine.group if self.fused else False)
+        self.shard_buf = SymmetricBuffer(max(acc16, 8), dt, dev, engine.group if self.fused else False)
         with torch.no_grad():
             for ui, u in enumerate(engine.units):
-                base = engine.unit_shard_off[ui]
+                base = self.bf16_off[ui]
                 pmap = dict(u.params)
                 for name, _fo, pl, so in self.pieces[ui]:
                     self.shard_buf.tensor[base + so:base + so + pl].copy_(pmap[name].data.reshape(-1)[r * pl:(r + 1) * pl])
         # ---- gather slots: blocks alternate between two, everything else stays resident
-        self.is_block = [u.name.startswith("block") for u in engine.units]
+        self.is_block = [u.name.startswith("block") and not u.local_only for u in engine.units]
         max_block = max([u.length for u, b in zip(engine.units, self.is_block) if b] or [8])
         self.slots = [torch.empty(max_block, dtype=dt, device=dev) for _ in range(2)]
         self.slot_content = [-1, -1]
@@ -80,11 +89,14 @@ class Zero3State:
                 buf = self.slots[k % 2]
                 k += 1
             else:
-                buf = torch.empty(u.length, dtype=dt, device=dev)
+                buf = torch.zeros(u.length, dtype=dt, device=dev)
                 self.resident[ui] = buf
             for name, p in u.params:
                 o, n, shape = engine.param_slices[name]
-                p.data = buf[o - u.offset:o - u.offset + n].view(shape)
+                view = buf[o - u.offset:o - u.offset + n].view(shape)
+                if u.local_only:
+                    view.copy_(p.data)           # nothing to gather later: the rank's own values live here
+                p.data = view
         self.side = torch.cuda.Stream(device=dev) if engine.on_cuda else None
         self.ready: List[Optional[torch.cuda.Event]] = [None, None]
         self.gathers = 0
@@ -98,7 +110,11 @@ class Zero3State:
         """All pieces of unit ``ui`` from every rank into ``buf`` (full parameter-major layout of the unit)."""
         e = self.e
         W = e.world
-        base = e.unit_shard_off[ui]
+        if e.units[ui].local_only:
+            if buf.data_ptr() != self.resident[ui].data_ptr():
+                buf.copy_(self.resident[ui])
+            return
+        base = self.bf16_off[ui]
         self.gathers += 1
         if self.fused:
             rows = self.pieces[ui]
@@ -202,6 +218,8 @@ class Zero3State:
         W, r = e.world, e.rank
         fn = _fused_reduce()
         for ui, u in enumerate(e.units):
+            if u.local_only:
+                continue
             base = e.unit_shard_off[ui]
             rows = self.pieces[ui]
             gp = e.grad_buf.ptr_table(u.offset * 4)
@@ -218,10 +236,14 @@ class Zero3State:
         e = self.e
         W, r = e.world, e.rank
         g = e.grad_buf.tensor
-        dist.all_reduce(g, group=e.group)
         out = []
         for ui, u in enumerate(e.units):
-            parts = [g[u.offset + fo + r * pl:u.offset + fo + (r + 1) * pl] for _n, fo, pl, _so in self.pieces[ui]]
+            gu = g[u.offset:u.offset + u.length]
+            if u.local_only:
+                out.append(gu / W)               # complete on this rank
+                continue
+            dist.all_reduce(gu, group=e.group)
+            parts = [gu[fo + r * pl:fo + (r + 1) * pl] for _n, fo, pl, _so in self.pieces[ui]]
             out.append(torch.cat(parts) / W)
         return out
 
