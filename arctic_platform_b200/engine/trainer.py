@@ -558,8 +558,15 @@ class TrainEngine:
                     sq += z.resident[ui].double().pow(2).sum()
             dist.all_reduce(sq, group=self.group)
         else:
+            ep_sq = torch.zeros((), dtype=torch.float64, device=self.device)
             for p in self.model.parameters():
-                sq += p.data.double().pow(2).sum()
+                if getattr(p, "expert_parallel", False):
+                    ep_sq += p.data.double().pow(2).sum()
+                else:
+                    sq += p.data.double().pow(2).sum()
+            if self.world > 1 and any(u.local_only for u in self.units):
+                dist.all_reduce(ep_sq, group=self.group)        # every rank owns different experts
+            sq += ep_sq
         return {"norm": float(sq.sqrt().item()), "sq_sum": float(sq.item()), "num_params": n}
 
     # ------------------------------------------------------------------ sleep / wake

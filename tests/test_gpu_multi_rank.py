@@ -276,3 +276,55 @@ def test_ulysses_sequence_parallel_on_two_gpus():
         res = [torch.load(os.path.join(d, f"u{r}.pt"), weights_only=False) for r in range(2)]
     for r in res:
         assert r["n"] == r["N"] and r["lp"] < 0.08 and r["cos"] > 0.97, r
+
+
+def _ep_train_main(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from arctic_platform_b200.engine.trainer import EngineConfig, TrainEngine
+        from arctic_platform_b200.models.config import PRESETS
+        from arctic_platform_b200.models.decoder import DecoderLM, token_logprobs
+        from arctic_platform_b200.ops import _lib
+        from arctic_platform_b200.parallel.expert_parallel import attach_expert_parallel
+        from arctic_platform_b200.rl.zorro_train.layout import build_packed_batch
+        from tests.test_zorro_equivalence_cpu import make_grpo_batch
+        cfg = PRESETS["qwen3-moe-tiny"]
+        ids, mask, R = make_grpo_batch(n_prompts=4, n_samples=2, p_rng=(40, 160), r_rng=(10, 60), seed=12)
+        ids = ids % cfg.vocab_size
+        B = ids.shape[0]
+        sl = slice(rank * B // world, (rank + 1) * B // world)
+        pb = build_packed_batch(ids[sl], mask[sl], R).to("cuda")
+        a = torch.randn(pb.labels.shape[0], generator=torch.Generator().manual_seed(7 + rank)).cuda()
+        res = {}
+        for name, impl, stage in (("fused", "fused", 1), ("collective", "collective", 1), ("fused_z3", "fused", 3)):
+            model = DecoderLM(cfg, "cuda", torch.bfloat16).init_weights(seed=8, std=0.05)
+            attach_expert_parallel(model, world, impl=impl, max_recv_rows=8192, max_pairs=8192)
+            eng = TrainEngine(model, EngineConfig(lr=1e-3, max_grad_norm=1.0, impl=impl, zero_stage=stage))
+            norms = []
+            for _ in range(2):
+                lp, _ = token_logprobs(eng.model, pb)
+                eng.backward(-(lp * a).mean())
+                norms.append(float(eng.step()["grad_norm"]))
+            _lib.check_status(name)
+            res[name] = (eng.full_flat_params().float().cpu(), norms, eng.weight_norm()["norm"])
+        torch.save(res, os.path.join(out_dir, f"p{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_expert_parallel_training_fused_matches_collective_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_ep_train_main, args=(2, _free_port(), d), nprocs=2, join=True)
+        res = [torch.load(os.path.join(d, f"p{r}.pt"), weights_only=False) for r in range(2)]
+    for r in res:
+        for other in ("fused", "fused_z3"):
+            assert all(abs(x - y) <= 3e-2 * abs(y) + 1e-4 for x, y in zip(r[other][1], r["collective"][1])), (other, r[other][1], r["collective"][1])
+            assert (r[other][0] - r["collective"][0]).abs().mean() < 2e-4
+            assert abs(r[other][2] - r["collective"][2]) <= 2e-3 * r["collective"][2]
