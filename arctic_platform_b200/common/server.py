@@ -35,6 +35,23 @@ class JobError(RuntimeError):
         self.status = status
 
 
+def route_prompts(prompts, n_replicas: int, routing_key=None, strict: bool = False) -> List[int]:
+    """Replica index per prompt.  ``routing_key`` (one key, or one per prompt) pins equal keys to one replica by a
+    stable hash -- conversations or prompt families that share a prefix stay together; ``strict`` is plain
+    round-robin; the default gives every replica one contiguous slice (equal load, neighbours together)."""
+    import zlib
+    P = len(prompts)
+    if routing_key is not None:
+        keys = list(routing_key) if isinstance(routing_key, (list, tuple)) else [routing_key] * P
+        if len(keys) != P:
+            raise JobError(400, f"routing_key has {len(keys)} entries for {P} prompts")
+        return [zlib.crc32(repr(k).encode()) % n_replicas for k in keys]
+    if strict:
+        return [i % n_replicas for i in range(P)]
+    per = (P + n_replicas - 1) // n_replicas
+    return [i // per for i in range(P)]
+
+
 class InProcessActor:
     """Actor facade over an object living in this process."""
 
@@ -222,16 +239,24 @@ class ArcticRLServerCore:
         n = len(job.workers)
         if n == 1:
             return {"job_id": job.job_id, "results": job.workers[0].call("generate", prompts, sampling_params)}
-        # replica data parallelism: contiguous slices keep the rollouts of one prompt on one replica
-        per = (len(prompts) + n - 1) // n
-        results: List[dict] = []
-        for i, w in enumerate(job.workers):
-            part = prompts[i * per:(i + 1) * per]
-            if part:
-                out = w.call("generate", part, sampling_params)
-                for o in out:
-                    o["prompt_index"] += i * per
-                results.extend(out)
+        # replica data parallelism: every prompt goes to ONE replica with all its samples (so the replica shares the
+        # prompt's KV among them); replicas run concurrently and the results come back in prompt order
+        assign = route_prompts(prompts, n, routing_key, strict)
+        groups: Dict[int, List[int]] = {}
+        for i, r in enumerate(assign):
+            groups.setdefault(r, []).append(i)
+
+        def run(item):
+            r, idxs = item
+            out = job.workers[r].call("generate", [prompts[i] for i in idxs], sampling_params)
+            for o in out:
+                o["prompt_index"] = idxs[o["prompt_index"]]
+            return out
+
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=len(groups)) as pool:
+            parts = list(pool.map(run, sorted(groups.items())))
+        results = sorted((o for part in parts for o in part), key=lambda o: o["prompt_index"])   # stable: sample order kept
         return {"job_id": job.job_id, "results": results}
 
     def log_probs(self, job_id: int, prompts, completions, top_k: int = 1) -> Dict[str, Any]:

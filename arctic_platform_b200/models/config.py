@@ -189,6 +189,27 @@ PRESETS: Dict[str, DecoderConfig] = {
                                       partial_rotary_factor=0.25, attn_output_gate=True, norm_one_plus=True,
                                       linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
                                       linear_value_head_dim=32, model_type="qwen3_5_moe_text", name="qwen3.5-moe-tiny"),
+    # hybrid checkpoints at their published sizes (linear attention on 3 of every 4 layers)
+    "qwen3-next-80b-a3b": DecoderConfig(vocab_size=151936, hidden_size=2048, intermediate_size=5120, num_layers=48,
+                                        num_heads=16, num_kv_heads=2, head_dim=256, tie_word_embeddings=False,
+                                        num_experts=512, num_experts_per_tok=10, moe_intermediate_size=512,
+                                        shared_expert_intermediate_size=512, rope_theta=1e7,
+                                        layer_types=tuple("full_attention" if (i + 1) % 4 == 0 else "linear_attention"
+                                                          for i in range(48)),
+                                        partial_rotary_factor=0.25, attn_output_gate=True, norm_one_plus=True,
+                                        linear_num_key_heads=16, linear_num_value_heads=32, linear_key_head_dim=128,
+                                        linear_value_head_dim=128, max_position_embeddings=262144,
+                                        model_type="qwen3_next", name="qwen3-next-80b-a3b"),
+    "qwen3.5-moe-35b-a3b": DecoderConfig(vocab_size=248320, hidden_size=2048, intermediate_size=5120, num_layers=40,
+                                         num_heads=16, num_kv_heads=2, head_dim=256, tie_word_embeddings=False,
+                                         num_experts=256, num_experts_per_tok=8, moe_intermediate_size=512,
+                                         shared_expert_intermediate_size=512, rope_theta=1e7,
+                                         layer_types=tuple("full_attention" if (i + 1) % 4 == 0 else "linear_attention"
+                                                           for i in range(40)),
+                                         partial_rotary_factor=0.25, attn_output_gate=True, norm_one_plus=True,
+                                         linear_num_key_heads=16, linear_num_value_heads=32, linear_key_head_dim=128,
+                                         linear_value_head_dim=128, max_position_embeddings=262144,
+                                         model_type="qwen3_5_moe_text", name="qwen3.5-moe-35b-a3b"),
     "qwen3-moe-tiny": DecoderConfig(vocab_size=32000, hidden_size=256, intermediate_size=688, num_layers=2,
                                     num_heads=4, num_kv_heads=2, head_dim=128, num_experts=8, num_experts_per_tok=2,
                                     moe_intermediate_size=128, model_type="qwen3_moe", name="qwen3-moe-tiny"),

@@ -124,3 +124,41 @@ def test_placement_arithmetic():
     assert gpu_fraction("training", True) == 0.34 and gpu_fraction("sampling", False) == 1.0
     opts = pg_scheduling_options(plan, 9, "log_prob", True)
     assert opts["num_gpus"] == 0.33
+
+
+def test_generate_routing_over_replicas():
+    from arctic_platform_b200.common.server import route_prompts
+
+    class Sampler:
+        seen = []
+
+        def __init__(self, rank):
+            self.rank = rank
+
+        def call(self, method, *args, **kwargs):
+            if method == "generate":
+                prompts, sp = args
+                Sampler.seen.append((self.rank, [p[0] for p in prompts]))
+                n = (sp or {}).get("n", 1)
+                return [{"token_ids": [p[0] * 10 + s], "prompt_index": i, "rank": self.rank}
+                        for i, p in enumerate(prompts) for s in range(n)]
+            return True
+
+        def kill(self):
+            pass
+
+    core = ArcticRLServerCore(worker_factory=lambda cfg, r, n: Sampler(r))
+    job = core.initialize({"model_name": "m", "job_type": "sampling", "num_devices": 3})
+    prompts = [[i] for i in range(7)]
+    out = core.generate(job["job_id"], prompts, {"n": 2})["results"]
+    assert [o["prompt_index"] for o in out] == [i for i in range(7) for _ in range(2)]
+    assert [o["token_ids"][0] for o in out] == [i * 10 + s for i in range(7) for s in range(2)]
+    assert [o["rank"] for o in out][::2] == [0, 0, 0, 1, 1, 1, 2]                     # contiguous slices
+    assert route_prompts(prompts, 3, strict=True) == [0, 1, 2, 0, 1, 2, 0]
+    keyed = route_prompts(prompts, 3, routing_key=["a", "b", "a", "c", "b", "a", "c"])
+    assert keyed[0] == keyed[2] == keyed[5] and keyed[1] == keyed[4] and keyed[3] == keyed[6]
+    assert route_prompts(prompts, 3, routing_key="same") == [route_prompts(prompts, 3, routing_key="same")[0]] * 7
+    out2 = core.generate(job["job_id"], prompts, {"n": 1}, routing_key=["a", "b", "a", "c", "b", "a", "c"])["results"]
+    assert [o["prompt_index"] for o in out2] == list(range(7)) and out2[0]["rank"] == out2[2]["rank"] == out2[5]["rank"]
+    with pytest.raises(JobError):
+        core.generate(job["job_id"], prompts, None, routing_key=[1, 2])
