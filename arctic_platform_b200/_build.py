@@ -102,7 +102,7 @@ def build_runtime(force: bool = False) -> Path:
             and RT_LIB.stat().st_mtime >= _newest_mtime(srcs + _headers())):
         return RT_LIB
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
-    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", str(CSRC),
+    cmd = [cxx, "-O3", "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", str(CSRC),
            "-o", str(RT_LIB), *map(str, srcs)]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:

@@ -23,6 +23,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, Iterable, List, Optional, Tuple
 
@@ -220,14 +221,14 @@ class TrainEngine:
             self.unit_shard_off.append(acc)
             acc += u.shard_len(W)
         self.shard_total = acc
-        opt_dev = "cpu" if (self.cfg.offload_optimizer and not self.on_cuda) else self.device
-        self.master = torch.empty(self.shard_total, dtype=torch.float32, device=opt_dev)
+        self.master = self._new_opt_state(self.shard_total)
         for u, so in zip(self.units, self.unit_shard_off):
             n = u.shard_len(W)
             s = u.offset + (0 if u.local_only else self.rank * n)
             self.master[so:so + n].copy_(flat[s:s + n].float())
-        self.exp_avg = torch.zeros_like(self.master)
-        self.exp_avg_sq = torch.zeros_like(self.master)
+        self.exp_avg = self._new_opt_state(self.shard_total).zero_()
+        self.exp_avg_sq = self._new_opt_state(self.shard_total).zero_()
+        self._build_host_staging()
         # W == 1: the reduced gradient is the gradient buffer itself (in place)
         self.reduced = gflat if W == 1 else torch.empty(self.shard_total, dtype=torch.float32, device=self.device)
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
@@ -248,13 +249,71 @@ class TrainEngine:
             for name, p in u.params:
                 o, n, shape = self.param_slices[name]
                 p.grad_f32 = gflat[o:o + n].view(shape)
-        opt_dev = "cpu" if (self.cfg.offload_optimizer and not self.on_cuda) else self.device
-        self.master = self._zero3_state_from_params().to(opt_dev)
-        self.exp_avg = torch.zeros_like(self.master)
-        self.exp_avg_sq = torch.zeros_like(self.master)
+        init = self._zero3_state_from_params()
+        self.master = self._new_opt_state(init.numel())
+        self.master.copy_(init)
+        del init
+        self.exp_avg = self._new_opt_state(self.shard_total).zero_()
+        self.exp_avg_sq = self._new_opt_state(self.shard_total).zero_()
+        self._build_host_staging()
         self.reduced = torch.empty(self.shard_total, dtype=torch.float32, device=self.device)
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
         self._offloaded = {}
+
+    # ------------------------------------------------------------------ optimizer state on the host
+    @property
+    def opt_on_host(self) -> bool:
+        """``zero_optimization.offload_optimizer.device: cpu``: fp32 master weights and both moments live in pinned
+        host memory and the update runs there (the reference passes the same key through to DeepSpeed's CPU Adam,
+        arctic_platform/integrations/verl/config/remote_backend/arctic.yaml:91)."""
+        return bool(self.cfg.offload_optimizer)
+
+    def _new_opt_state(self, n: int) -> torch.Tensor:
+        if self.opt_on_host:
+            return torch.empty(n, dtype=torch.float32, device="cpu", pin_memory=self.on_cuda)
+        return torch.empty(n, dtype=torch.float32, device=self.device)
+
+    def _build_host_staging(self) -> None:
+        """Pinned staging for the offloaded update: the reduced fp32 gradient shard on its way down and the new
+        low-precision parameters on their way up."""
+        self._host_grad = self._host_out = None
+        if self.opt_on_host:
+            pin = self.on_cuda
+            self._host_grad = torch.empty(self.shard_total, dtype=torch.float32, pin_memory=pin)
+            self._host_out = torch.empty(self.shard_total, dtype=torch.bfloat16, pin_memory=pin)
+
+    def _host_stage_grads(self, shards) -> list:
+        """Queues the device-to-host copies of every unit's reduced gradient at once, so that unit ``i + 1`` crosses
+        PCIe / C2C while the host updates unit ``i``.  Returns one event per unit (``None`` on a CPU engine)."""
+        events = []
+        for so, g in zip(self.unit_shard_off, shards):
+            self._host_grad[so:so + g.numel()].copy_(g, non_blocking=True)
+            if self.on_cuda:
+                ev = torch.cuda.Event()
+                ev.record()
+                events.append(ev)
+            else:
+                events.append(None)
+        return events
+
+    def _host_adamw(self, so: int, n: int, event, gscale: float, lr: float, bias1: float, bias2: float) -> torch.Tensor:
+        """Native single-pass AdamW over ``[so, so + n)`` of the host state; returns the new parameters in the
+        parameter dtype on the engine's device."""
+        if event is not None:
+            event.synchronize()
+        cfg = self.cfg
+        rt = _lib.rt_lib()
+        out = self._host_out[so:so + n]
+        use_out = self.param_dtype == torch.bfloat16
+        rc = rt.apb_rt_cpu_adamw(self.master[so:].data_ptr(), self.exp_avg[so:].data_ptr(),
+                                 self.exp_avg_sq[so:].data_ptr(), self._host_grad[so:].data_ptr(),
+                                 out.data_ptr() if use_out else None, n, lr, cfg.betas[0], cfg.betas[1], cfg.eps,
+                                 cfg.weight_decay, bias1, bias2, gscale, int(os.environ.get("APB_CPU_ADAM_THREADS", 0)))
+        if rc != 0:
+            raise RuntimeError(f"host AdamW rejected its arguments (unit at {so}, {n} elements)")
+        if use_out:
+            return out.to(self.device, non_blocking=True)
+        return self.master[so:so + n].to(self.param_dtype).to(self.device)
 
     def _zero3_state_from_params(self) -> torch.Tensor:
         """fp32 copy of this rank's parameters in the optimizer-state layout: bf16 shards of the sharded units, the
@@ -302,7 +361,7 @@ class TrainEngine:
         bias1 = 1.0 - cfg.betas[0] ** t
         bias2 = 1.0 - cfg.betas[1] ** t
         self.sumsq.zero_()
-        if self.impl == "fused":
+        if self.impl == "fused" and not self.opt_on_host:
             self._step_fused(lr, bias1, bias2)
         else:
             self._step_collective(lr, bias1, bias2)
@@ -414,24 +473,35 @@ class TrainEngine:
         norm = sq.sqrt().float()
         self._grad_norm_tensor = norm.reshape(())
         clip = torch.clamp(cfg.max_grad_norm / (norm + 1e-6), max=1.0) if cfg.max_grad_norm > 0 else None
+        events = self._host_stage_grads(shards) if self.opt_on_host else None
+        gscale = (float(clip.item()) if clip is not None else 1.0) if self.opt_on_host else None
         for ui, (so, g) in enumerate(zip(self.unit_shard_off, shards)):
             n = self.units[ui].length if self.units[ui].local_only else z.unit_shard_len[ui]
-            g = g.to(self.master.device)
-            if clip is not None:
-                g = g * clip.to(g.device)
-            m, v, w = self.exp_avg[so:so + n], self.exp_avg_sq[so:so + n], self.master[so:so + n]
-            m.mul_(cfg.betas[0]).add_(g, alpha=1 - cfg.betas[0])
-            v.mul_(cfg.betas[1]).addcmul_(g, g, value=1 - cfg.betas[1])
-            w.mul_(1 - lr * cfg.weight_decay)
-            w.addcdiv_(m / bias1, (v / bias2).sqrt_().add_(cfg.eps), value=-lr)
-            if self.units[ui].local_only:
-                z.resident[ui][:n].copy_(w.to(self.param_dtype))
+            if self.opt_on_host:
+                new = self._host_adamw(so, n, events[ui], gscale, lr, bias1, bias2)
             else:
-                z.shard_buf.tensor[z.bf16_off[ui]:z.bf16_off[ui] + n].copy_(w.to(self.param_dtype))
+                new = self._torch_adamw(so, n, g, clip, lr, bias1, bias2)
+            if self.units[ui].local_only:
+                z.resident[ui][:n].copy_(new)
+            else:
+                z.shard_buf.tensor[z.bf16_off[ui]:z.bf16_off[ui] + n].copy_(new)
         if self.on_cuda:
             torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
         z.invalidate()
+
+    def _torch_adamw(self, so: int, n: int, g: torch.Tensor, clip, lr: float, bias1: float, bias2: float) -> torch.Tensor:
+        """AdamW over ``[so, so + n)`` of the optimizer state with plain tensor ops (the collective baseline)."""
+        cfg = self.cfg
+        g = g.to(self.master.device)
+        if clip is not None:
+            g = g * clip.to(g.device)
+        m, v, w = self.exp_avg[so:so + n], self.exp_avg_sq[so:so + n], self.master[so:so + n]
+        m.mul_(cfg.betas[0]).add_(g, alpha=1 - cfg.betas[0])
+        v.mul_(cfg.betas[1]).addcmul_(g, g, value=1 - cfg.betas[1])
+        w.mul_(1 - lr * cfg.weight_decay)
+        w.addcdiv_(m / bias1, (v / bias2).sqrt_().add_(cfg.eps), value=-lr)
+        return w.to(self.param_dtype).to(self.device)
 
     def _step_collective(self, lr, bias1, bias2) -> None:
         if self.zero3 is not None:
@@ -465,19 +535,14 @@ class TrainEngine:
         self._grad_norm_tensor = norm.reshape(())
         clip = torch.clamp(cfg.max_grad_norm / (norm + 1e-6), max=1.0) if cfg.max_grad_norm > 0 else None
         flat = self.param_buf.tensor
-        for u, so, g in zip(self.units, self.unit_shard_off, shards):
+        events = self._host_stage_grads(shards) if self.opt_on_host else None
+        gscale = (float(clip.item()) if clip is not None else 1.0) if self.opt_on_host else None
+        for ui, (u, so, g) in enumerate(zip(self.units, self.unit_shard_off, shards)):
             n = u.shard_len(W)
-            g = g.to(self.master.device)
-            if clip is not None:
-                g = g * clip.to(g.device)
-            m = self.exp_avg[so:so + n]
-            v = self.exp_avg_sq[so:so + n]
-            w = self.master[so:so + n]
-            m.mul_(cfg.betas[0]).add_(g, alpha=1 - cfg.betas[0])
-            v.mul_(cfg.betas[1]).addcmul_(g, g, value=1 - cfg.betas[1])
-            w.mul_(1 - lr * cfg.weight_decay)
-            w.addcdiv_(m / bias1, (v / bias2).sqrt_().add_(cfg.eps), value=-lr)
-            new = w.to(self.param_dtype).to(self.device)
+            if self.opt_on_host:
+                new = self._host_adamw(so, n, events[ui], gscale, lr, bias1, bias2)
+            else:
+                new = self._torch_adamw(so, n, g, clip, lr, bias1, bias2)
             dst = flat[u.offset:u.offset + u.length]
             if u.local_only:
                 dst.copy_(new)

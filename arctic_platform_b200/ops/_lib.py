@@ -188,4 +188,8 @@ def _declare_rt(lib) -> None:
          ctypes.c_int32)
     _sig(lib, "apb_rt_balance_groups", [f64p, i32p, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, i32p],
          ctypes.c_int32)
+    f = ctypes.c_float
+    _sig(lib, "apb_rt_cpu_adamw", [c_vp, c_vp, c_vp, c_vp, c_vp, ctypes.c_int64, f, f, f, f, f, f, f, f, ctypes.c_int32],
+         ctypes.c_int32)
+    _sig(lib, "apb_rt_cpu_sumsq", [c_vp, ctypes.c_int64], ctypes.c_double)
     _sig(lib, "apb_rt_version", [], ctypes.c_int32)

@@ -7,13 +7,13 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _setup(impl):
+def _setup(impl, **kw):
     from arctic_platform_b200.engine.trainer import EngineConfig, TrainEngine
     from arctic_platform_b200.models.config import PRESETS
     from arctic_platform_b200.models.decoder import DecoderLM
     cfg = PRESETS["qwen3-tiny-d128"]
     model = DecoderLM(cfg, "cuda", torch.bfloat16).init_weights(seed=11)
-    ecfg = EngineConfig(lr=1e-3, weight_decay=0.01, max_grad_norm=0.5, impl=impl)
+    ecfg = EngineConfig(lr=1e-3, weight_decay=0.01, max_grad_norm=0.5, impl=impl, **kw)
     return cfg, TrainEngine(model, ecfg)
 
 
@@ -43,6 +43,35 @@ def test_fused_step_matches_torch_ops():
     # the two runs use the same kernels for forward/backward, so gradients agree up to atomics ordering
     assert (mf - mc).abs().max() < 5e-3, (mf - mc).abs().max()
     assert (pf - pc).abs().max() < 2e-2
+
+
+def test_host_offloaded_optimizer_matches_fused_step(stage=2):
+    """Optimizer state in pinned host memory, updated by the native host AdamW: same parameters as the fused device
+    step, and no fp32 optimizer state left on the device."""
+    from arctic_platform_b200.models.decoder import token_logprobs
+    from arctic_platform_b200.ops import _lib
+    from arctic_platform_b200.rl.zorro_train.layout import build_packed_batch
+    from tests.test_zorro_equivalence_cpu import make_grpo_batch
+    ids, mask, R = make_grpo_batch(n_prompts=2, n_samples=4, p_rng=(40, 200), r_rng=(10, 80))
+    pb = build_packed_batch(ids, mask, R).to("cuda")
+    adv = torch.randn(pb.labels.shape[0], device="cuda")
+    results = {}
+    for off in (False, True):
+        _cfg, eng = _setup("fused", zero_stage=stage, offload_optimizer=off)
+        if off:
+            assert eng.master.device.type == "cpu" and eng.master.is_pinned() and eng.exp_avg_sq.is_pinned()
+        norms = []
+        for _ in range(3):
+            lp, _ = token_logprobs(eng.model, pb, 1.0)
+            eng.backward(-(lp * adv).mean())
+            norms.append(float(eng.step()["grad_norm"]))
+        _lib.check_status(f"offload={off}")
+        results[off] = (eng.full_flat_params().float().clone(), eng.master.cpu().clone(), norms)
+    pf, mf, nf = results[False]
+    ph, mh, nh = results[True]
+    assert all(abs(a - b) <= 2e-2 * abs(b) + 1e-4 for a, b in zip(nh, nf)), (nh, nf)
+    assert (mf - mh).abs().max() < 5e-3, (mf - mh).abs().max()
+    assert (pf - ph).abs().max() < 2e-2
 
 
 def test_gradient_accumulation_and_lr_schedule():
