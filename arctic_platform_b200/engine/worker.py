@@ -87,11 +87,12 @@ class EngineWorker:
 
     def _load_model(self, job_config, dtype, seed) -> DecoderLM:
         from pathlib import Path
-        from ..models.hf_io import load_hf_checkpoint
+        from ..models.conversion_cache import load_through_cache
         m = DecoderLM(self.model_cfg, self.device, dtype)
         path = Path(str(job_config["model_name"]))
         if path.is_dir() and any(path.glob("*.safetensors")):
-            load_hf_checkpoint(m, path)
+            # converted once per node when a cache directory is configured, else straight from the shards
+            load_through_cache(m, path, cache_dir=job_config.get("weight_conversion_cache_dir"))
         else:
             m.init_weights(seed=seed)     # no checkpoint on disk: deterministic random initialisation
         return m

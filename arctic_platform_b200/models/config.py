@@ -40,6 +40,8 @@ class DecoderConfig:
     partial_rotary_factor: float = 1.0           # fraction of head_dim that is rotated
     attn_output_gate: bool = False               # attention output multiplied by sigmoid(gate(x)) before o_proj
     norm_one_plus: bool = False                  # RMSNorm weight stored as (w - 1)
+    vlm_layout: bool = False                     # checkpoint is a composite: language model + vision tower
+    composite_extra: Optional[Dict[str, Any]] = None   # the composite config's top level (vision_config, token ids)
     linear_num_key_heads: int = 0
     linear_num_value_heads: int = 0
     linear_key_head_dim: int = 0
@@ -99,6 +101,9 @@ class DecoderConfig:
 
     @staticmethod
     def from_hf_dict(d: Dict[str, Any], name: str = "") -> "DecoderConfig":
+        from .vlm import text_config_of
+        top = d
+        d, composite = text_config_of(d)
         mt = d.get("model_type", "qwen3")
         heads = d["num_attention_heads"]
         hybrid = mt in HYBRID_MODEL_TYPES
@@ -119,7 +124,9 @@ class DecoderConfig:
             linear_num_value_heads=d.get("linear_num_value_heads", 0) or 0,
             linear_key_head_dim=d.get("linear_key_head_dim", 0) or 0,
             linear_value_head_dim=d.get("linear_value_head_dim", 0) or 0,
-            linear_conv_kernel_dim=d.get("linear_conv_kernel_dim", 4) or 4, model_type=mt, name=name or mt)
+            linear_conv_kernel_dim=d.get("linear_conv_kernel_dim", 4) or 4, model_type=mt, name=name or mt,
+            vlm_layout=composite,
+            composite_extra={k: v for k, v in top.items() if k != "text_config"} if composite else None)
 
     def to_hf_dict(self) -> Dict[str, Any]:
         d = {
@@ -142,6 +149,11 @@ class DecoderConfig:
                      linear_key_head_dim=self.linear_key_head_dim, linear_value_head_dim=self.linear_value_head_dim,
                      linear_conv_kernel_dim=self.linear_conv_kernel_dim,
                      shared_expert_intermediate_size=self.shared_expert_intermediate_size)
+        if self.vlm_layout:
+            from .vlm import composite_config
+            d["model_type"] = self.model_type
+            d.pop("architectures", None)
+            return composite_config(d, self.composite_extra)
         return d
 
 

@@ -144,13 +144,13 @@ def _load_moe(ctx: LoaderContext, device, seed: int) -> DecoderLM:
 
 def _instantiate(ctx: LoaderContext, device, seed: int) -> DecoderLM:
     from pathlib import Path
-    from .hf_io import load_hf_checkpoint
+    from .conversion_cache import load_through_cache
     dev = torch.device(device)
     dtype = _torch_dtype(ctx.spec.dtype) if dev.type == "cuda" else torch.float32
     model = DecoderLM(ctx.hf_config, dev, dtype)
     p = Path(ctx.spec.model_path_or_name)
     if p.is_dir() and any(p.glob("*.safetensors")):
-        load_hf_checkpoint(model, p)
+        load_through_cache(model, p, cache_dir=ctx.spec.loader_options.get("weight_conversion_cache_dir"))
     else:
         model.init_weights(seed=seed)
     return model

@@ -241,6 +241,16 @@ def write_safetensors(path, tensors: Dict[str, torch.Tensor], metadata: Optional
                 f.write(t.view(torch.uint8).reshape(-1).numpy().tobytes())
 
 
+def _composite_stream(model, source):
+    """A composite (vision + language) checkpoint: language-model tensors under their composite names, then every
+    tensor that was carried through from the loaded checkpoint."""
+    from .vlm import composite_name
+    for name, t in source:
+        yield composite_name(name), t
+    for name, t in (getattr(model, "passthrough", None) or ()):
+        yield name, t
+
+
 def save_hf_checkpoint(model, out_dir, max_shard_bytes: int = 4 << 30, tensors=None) -> List[str]:
     """Writes ``config.json``, sharded ``model-XXXXX-of-YYYYY.safetensors`` and the index file.
     ``tensors`` overrides the source of ``(name, tensor)`` pairs (e.g. gathered ZeRO shards)."""
@@ -249,7 +259,10 @@ def save_hf_checkpoint(model, out_dir, max_shard_bytes: int = 4 << 30, tensors=N
     (out / "config.json").write_text(json.dumps(model.cfg.to_hf_dict(), indent=2))
     shards: List[Dict[str, torch.Tensor]] = [{}]
     size = 0
-    for name, t in (tensors if tensors is not None else iter_hf_tensors(model)):
+    source = tensors if tensors is not None else iter_hf_tensors(model)
+    if model.cfg.vlm_layout:
+        source = _composite_stream(model, source)
+    for name, t in source:
         n = t.numel() * t.element_size()
         if size + n > max_shard_bytes and shards[-1]:
             shards.append({})
@@ -274,10 +287,17 @@ def load_hf_checkpoint(model, ckpt_dir, strict: bool = True) -> int:
     files = sorted(d.glob("*.safetensors"))
     if not files:
         raise FileNotFoundError(f"no .safetensors files in {d}")
+    from .vlm import PassthroughTensors, text_name
     expected = set(hf_param_names(model.cfg))
     seen = set()
     for f in files:
-        for name, t in read_safetensors(f):
+        for raw, t in read_safetensors(f):
+            name = text_name(raw)
+            if name is None:                  # vision tower / extra heads of a composite checkpoint: kept, not trained
+                if getattr(model, "passthrough", None) is None:
+                    model.passthrough = PassthroughTensors()
+                model.passthrough.add(raw, t)
+                continue
             if name not in expected:
                 if strict and not (name == "lm_head.weight" and model.lm_head is None):
                     raise KeyError(f"{f.name}: unexpected tensor {name!r}")
