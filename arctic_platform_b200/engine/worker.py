@@ -65,7 +65,10 @@ class EngineWorker:
             from .sampler import SamplerEngine
             vc = dict(job_config.get("vllm_config") or {})
             m = model if model is not None else self._load_model(job_config, dtype, seed)
-            if self.device.type != "cuda":
+            if self.model_cfg.layer_types is not None:
+                # hybrid family: recurrent state + sparse K/V layers, served by the stateful tensor-op engine
+                from .hybrid_sampler import HybridSampler as SamplerEngine      # noqa: F811
+            elif self.device.type != "cuda":
                 from .reference_sampler import ReferenceSampler as SamplerEngine   # noqa: F811  (CPU: recompute sampler)
             self.sampler = SamplerEngine(
                 self.model_cfg, self.device, model=m,

@@ -106,6 +106,7 @@ class DecoderBlock(nn.Module):
             self.q_norm = mk(D) if cfg.qk_norm else None
             self.k_norm = mk(D) if cfg.qk_norm else None
             self.wo = mk(H, cfg.q_size)
+        self.kv_capture = None           # a sampler's prefill sets a list; forward appends this layer's (k, v)
         self.ln2 = mk(H)
         if cfg.is_moe:
             from .moe import MoEFeedForward
@@ -130,6 +131,8 @@ class DecoderBlock(nn.Module):
             else:
                 q, k, v = norm.qknorm_rope(qkv, self.q_norm, self.k_norm, rope[0], rope[1], positions, cfg.num_heads,
                                            cfg.num_kv_heads, cfg.head_dim, cfg.rms_norm_eps)
+            if self.kv_capture is not None:
+                self.kv_capture.append((k, v))
             if getattr(self, "sp_group", None) is not None:
                 from ..parallel.ulysses import ulysses_attention
                 a = ulysses_attention(q, k, v, layout, self.sp_group)

@@ -134,6 +134,9 @@ class GatedDeltaNet(nn.Module):
         self.norm_w = mk(self.Dv)
         self.out_proj = mk(H, self.value_dim)
         self.chunk = 64
+        # a sampler's prefill sets this to a dict; forward then leaves ``end row -> (conv state, S)`` of every
+        # segment in it, the starting point of token-by-token decoding
+        self.capture: Optional[Dict[int, Tuple[torch.Tensor, torch.Tensor]]] = None
 
     def forward(self, x: torch.Tensor, layout) -> torch.Tensor:
         """``x [T, H]`` on the packed axis -> ``[T, H]``."""
@@ -166,7 +169,40 @@ class GatedDeltaNet(nn.Module):
             final[os_ + ol] = (conv_new, S_new)
             # the segment's query rows are the last ``ql`` rows of its own range
             out = out.index_put((torch.arange(qs, qs + ql, device=x.device),), o[ol - ql:])
-        # gated RMSNorm: norm(o) * w * silu(z)
+        if self.capture is not None:
+            self.capture.update(final)
+        return self._gated_out(out, z, x.dtype)
+
+    def _gated_out(self, out: torch.Tensor, z: torch.Tensor, dtype) -> torch.Tensor:
+        """Gated RMSNorm ``norm(o) * w * silu(z)`` and the output projection; ``out, z [T, Hv, Dv]``."""
+        T = out.shape[0]
         o = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + self.cfg.rms_norm_eps) * self.norm_w.float()
-        o = (o * F.silu(z.float())).to(x.dtype)
+        o = (o * F.silu(z.float())).to(dtype)
         return gemm.linear(o.reshape(T, self.value_dim), self.out_proj)
+
+    @torch.no_grad()
+    def step(self, x: torch.Tensor, conv_state: torch.Tensor, S: torch.Tensor
+             ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """One token for each of ``B`` independent sequences: ``x [B, H]``, ``conv_state [B, K-1, C]``,
+        ``S [B, Hv, Dk, Dv]`` (fp32) -> ``(y [B, H], new conv_state, new S)``.  The same arithmetic as one step
+        of :func:`gated_delta_rule_recurrent` behind the causal convolution."""
+        B = x.shape[0]
+        mixed = gemm.linear(x, self.in_qkv)
+        z = gemm.linear(x, self.in_z).view(B, self.Hv, self.Dv)
+        beta = torch.sigmoid(x.float() @ self.in_b.float().t())
+        g = -torch.exp(self.A_log.float()) * F.softplus(x.float() @ self.in_a.float().t() + self.dt_bias.float())
+        window = torch.cat([conv_state.to(mixed.dtype), mixed[:, None, :]], 1)              # [B, K, C]
+        y = (window.float() * self.conv_w.float().t()[None]).sum(1).to(mixed.dtype)
+        y = F.silu(y)
+        q = y[:, :self.key_dim].reshape(B, self.Hk, self.Dk)
+        k = y[:, self.key_dim:2 * self.key_dim].reshape(B, self.Hk, self.Dk)
+        v = y[:, 2 * self.key_dim:].reshape(B, self.Hv, self.Dv).float()
+        rep = self.Hv // self.Hk
+        if rep > 1:
+            q, k = q.repeat_interleave(rep, 1), k.repeat_interleave(rep, 1)
+        q, k = _l2norm(q.float()) * self.Dk ** -0.5, _l2norm(k.float())
+        S = S * torch.exp(g)[:, :, None, None]
+        pred = torch.einsum("bhkv,bhk->bhv", S, k)
+        S = S + torch.einsum("bhk,bhv->bhkv", k * beta[:, :, None], v - pred)
+        o = torch.einsum("bhkv,bhk->bhv", S, q)
+        return self._gated_out(o, z, x.dtype), window[:, 1:], S

@@ -88,3 +88,31 @@ def test_hybrid_family_runs_on_gpu():
     for n in ("blocks.0.linear_attn.in_qkv", "blocks.0.linear_attn.out_proj", "blocks.3.wqkv", "blocks.3.wgate"):
         a = dict(gpu.named_parameters())[n].grad.float().cpu().flatten()
         assert torch.nn.functional.cosine_similarity(a, gr[n].grad.flatten(), dim=0) > 0.95, n
+
+
+def test_hybrid_sampler_on_gpu_agrees_with_teacher_forced_scoring():
+    """The stateful hybrid sampler in bf16 on the GPU: the log-probs it reports while decoding token by token match
+    a packed teacher-forced pass of the training model over prompt + sampled tokens."""
+    import numpy as np
+    from arctic_platform_b200.engine.hybrid_sampler import HybridSampler
+    from arctic_platform_b200.ops import _lib
+    from arctic_platform_b200.ops.attention import AttnLayout
+    cfg, _ref, gpu = _models("qwen3.5-moe-tiny")
+    eng = HybridSampler(cfg, "cuda", model=gpu, max_seq_len=256)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 23)]
+    res = eng.generate(prompts, {"n": 3, "temperature": 1.0, "max_tokens": 16, "seed": 1})
+    _lib.check_status("hybrid sampler")
+    assert len(res) == 6 and eng.prefill_tokens == 32
+    diffs = []
+    for r in res:
+        seq = prompts[r["prompt_index"]] + r["token_ids"]
+        ids = torch.tensor(seq, device="cuda")
+        with torch.no_grad():
+            h = gpu.forward_hidden(ids, torch.arange(len(seq), device="cuda"), AttnLayout.from_cu_seqlens(np.array([0, len(seq)])))
+            lp = torch.log_softmax(gpu.logits(h).float(), -1)
+        P = r["prompt_len"]
+        want = lp[P - 1:len(seq) - 1].gather(1, ids[P:, None])[:, 0].cpu()
+        diffs.append((want - torch.tensor(r["logprobs"])).abs())
+    d = torch.cat(diffs)
+    assert d.mean() < 0.03 and d.max() < 0.3, (d.mean(), d.max())
