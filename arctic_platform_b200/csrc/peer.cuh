@@ -24,7 +24,19 @@ __device__ __forceinline__ bool epoch_barrier(const PeerPtrs& flags, int rank, i
     flag_store_release(static_cast<int*>(flags.p[threadIdx.x]) + rank, epoch);
   }
   if (threadIdx.x < world) {
-    if (!flag_wait_ge(static_cast<const int*>(flags.p[rank]) + threadIdx.x, epoch, status, kTimeoutFlag)) ok_s = 0;
+    const int* slot = static_cast<const int*>(flags.p[rank]) + threadIdx.x;
+    if (!flag_wait_ge(slot, epoch, status, kTimeoutFlag)) {
+      ok_s = 0;
+      // first reporter fills the record behind the code: expected epoch, the peer that never announced it, and
+      // the epoch that peer's slot holds now (a stale epoch shows a peer that is a step behind, 0 one that never
+      // started)
+      if (status && atomicCAS(status + 1, 0, epoch) == 0) {
+        int seen;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(slot) : "memory");
+        status[2] = threadIdx.x;
+        status[3] = seen;
+      }
+    }
   }
   __syncthreads();
   return ok_s != 0;

@@ -90,6 +90,14 @@ int apb_status_read() {
   return v;
 }
 
+// The whole record: {code, expected epoch, peer, epoch seen} -- the last three are filled by a timed-out wait on a
+// peer's flag and are zero otherwise.
+int apb_status_read4(int* out4) {
+  int* p = apb::status_device_ptr();
+  if (!p || !out4) return -1;
+  return cudaMemcpy(out4, p, 4 * sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -2;
+}
+
 int apb_status_clear() {
   int* p = apb::status_device_ptr();
   if (!p) return -1;

@@ -11,6 +11,7 @@ from __future__ import annotations
 import ctypes
 import threading
 from pathlib import Path
+from typing import Tuple
 
 import torch
 
@@ -27,6 +28,19 @@ class NativeLibraryError(RuntimeError):
 
 class KernelError(RuntimeError):
     """A kernel launch returned a non-zero code or the status word is set."""
+
+
+class CollectiveTimeout(KernelError):
+    """A bounded device-side wait ran out: a pipeline stage that never filled (codes 101-104) or a peer that never
+    announced the expected epoch (105; ``peer``, ``expected_epoch`` and ``seen_epoch`` are then set)."""
+
+    def __init__(self, message: str, code: int, expected_epoch: int = 0, peer: int = -1, seen_epoch: int = 0):
+        super().__init__(message)
+        self.code, self.expected_epoch, self.peer, self.seen_epoch = code, expected_epoch, peer, seen_epoch
+
+
+TIMEOUT_CODES = {101: "a TMA stage never filled", 102: "a stage never drained", 103: "an accumulator never arrived",
+                 104: "TMEM was never released", 105: "a flag never reached the expected epoch"}
 
 
 def _load(path: Path, builder):
@@ -115,12 +129,28 @@ def status_clear() -> None:
     cuda_lib().apb_status_clear()
 
 
+def status_record() -> Tuple[int, int, int, int]:
+    """``(code, expected epoch, peer, epoch seen)`` of the current device."""
+    fn = cuda_lib().apb_status_read4
+    fn.argtypes, fn.restype = [ctypes.c_void_p], ctypes.c_int
+    buf = (ctypes.c_int * 4)()
+    if fn(ctypes.cast(buf, ctypes.c_void_p)) != 0:
+        return (int(status_read()), 0, 0, 0)
+    return tuple(int(x) for x in buf)            # type: ignore[return-value]
+
+
 def check_status(what: str = "kernel") -> None:
-    """Synchronises and raises if any kernel recorded an error (e.g. a bounded wait ran out)."""
+    """Synchronises and raises if any kernel recorded an error: :class:`CollectiveTimeout` when a bounded wait ran
+    out, :class:`KernelError` for everything else (bad arguments, routing entries outside the group)."""
     torch.cuda.synchronize()
     st = status_read()
     if st != 0:
+        code, expected, peer, seen = status_record()
         status_clear()
+        if st in TIMEOUT_CODES:
+            detail = f" (peer {peer} holds epoch {seen}, expected {expected})" if st == 105 and expected else ""
+            raise CollectiveTimeout(f"{what}: device status word = {st}: {TIMEOUT_CODES[st]}{detail}", st, expected,
+                                    peer if expected else -1, seen)
         raise KernelError(f"{what}: device status word = {st}")
 
 

@@ -21,8 +21,11 @@ def test_flag_wait_times_out_with_status_and_context_survives():
     _lib.status_clear()
     t0 = time.perf_counter()
     _lib.check(wait(table, 0, 2, 5, _lib.stream_ptr()), "apb_epoch_wait")
-    with pytest.raises(_lib.KernelError, match="105"):
+    with pytest.raises(_lib.CollectiveTimeout, match="105") as err:
         _lib.check_status("waiting for a rank that never arrives")
+    # the record names the missing peer and the epochs: slot 1 still holds 0, epoch 5 was expected
+    assert (err.value.code, err.value.peer, err.value.expected_epoch, err.value.seen_epoch) == (105, 1, 5, 0)
+    assert isinstance(err.value, _lib.KernelError)
     elapsed = time.perf_counter() - t0
     assert 0.5 < elapsed < 10.0                      # the limit is one second, not forever
     assert int(flags[0]) == 5 and int(flags[1]) == 0
