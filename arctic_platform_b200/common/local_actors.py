@@ -115,8 +115,11 @@ def spawned_worker_factory(master_port: int = 29500):
     """``worker_factory`` for ``ArcticRLServerCore``: one spawned process per rank, rank r on GPU r."""
     def factory(job_config: Dict[str, Any], rank: int, world: int):
         import torch
-        env = {"RANK": str(rank), "LOCAL_RANK": "0", "WORLD_SIZE": str(world), "MASTER_ADDR": "127.0.0.1",
-               "MASTER_PORT": str(master_port + (1 if job_config.get("job_type") == "log_prob" else 0))}
-        gpu = rank if torch.cuda.is_available() else None
-        return SpawnedActor(_make_engine_worker, env=env, gpu=gpu)
+        # every rank sees all GPUs and takes the one named by LOCAL_RANK (as under torchrun): peer mappings of
+        # the symmetric buffers need the peers' devices visible.  Each job type rendezvouses on its own port;
+        # sampler replicas form no group at all.
+        offset = {"training": 0, "log_prob": 1, "sampling": 2}.get(job_config.get("job_type", "training"), 0)
+        env = {"RANK": str(rank), "LOCAL_RANK": str(rank if torch.cuda.is_available() else 0), "WORLD_SIZE": str(world),
+               "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(master_port + offset)}
+        return SpawnedActor(_make_engine_worker, env=env)
     return factory

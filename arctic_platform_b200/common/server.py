@@ -19,7 +19,7 @@ import itertools
 import threading
 import time
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, List, Optional
+from typing import Any, Callable, Dict, List, Optional, Sequence
 
 import torch
 
@@ -80,6 +80,29 @@ class Job:
     info: Dict[str, Any] = field(default_factory=dict)
 
 
+def call_all(workers: Sequence[Any], method: str, per_worker_args: Optional[Sequence[tuple]] = None, *shared_args) -> List[Any]:
+    """Calls ``method`` on every worker AT THE SAME TIME and returns the results in worker order.  The ranks of a
+    job run collectives inside these calls (process-group set-up, ZeRO-3 gathers, the optimizer's reduce-scatter),
+    so a rank-by-rank loop would block on the first rank for ever; it would also serialise the ranks' compute.
+    The first failure is raised after every call has returned."""
+    args = [tuple(a) for a in per_worker_args] if per_worker_args is not None else [tuple(shared_args)] * len(workers)
+    if len(workers) == 1:
+        return [workers[0].call(method, *args[0])]
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=len(workers)) as pool:
+        futs = [pool.submit(w.call, method, *a) for w, a in zip(workers, args)]
+        results, first = [], None
+        for f in futs:
+            try:
+                results.append(f.result())
+            except BaseException as exc:  # noqa: BLE001 - re-raised below
+                results.append(None)
+                first = first or exc
+    if first is not None:
+        raise first
+    return results
+
+
 def default_worker_factory(job_config: Dict[str, Any], rank: int, world: int):
     from ..engine.worker import EngineWorker
     return InProcessActor(EngineWorker())
@@ -113,10 +136,8 @@ class ArcticRLServerCore:
             for rank in range(n):
                 w = self.worker_factory(job_config, rank, n)
                 workers.append(w)
-            for w in workers:
-                ok = w.call("initialize", job_config)
-                if ok is False:
-                    raise RuntimeError("worker.initialize returned False")
+            if any(ok is False for ok in call_all(workers, "initialize", None, job_config)):
+                raise RuntimeError("worker.initialize returned False")
         except Exception as exc:
             for w in workers:          # all-or-nothing: no half-initialised job survives
                 try:
@@ -181,7 +202,7 @@ class ArcticRLServerCore:
         meta = dict(payload.get("meta") or {})
         processing = payload.get("processing")
         shards, order = split_batch_for_ranks(batch, meta, len(job.workers))
-        results = [w.call(method, shard, meta, processing) for w, shard in zip(job.workers, shards)]
+        results = call_all(job.workers, method, [(shard, meta, processing) for shard in shards])
         return results, order
 
     def forward_backward(self, job_id: int, payload: Dict[str, Any]) -> Dict[str, Any]:
@@ -201,13 +222,12 @@ class ArcticRLServerCore:
 
     def step(self, job_id: int, learning_rate: Optional[float] = None) -> Dict[str, Any]:
         job = self._job(job_id, ("training",))
-        outs = [w.call("step", learning_rate) for w in job.workers]
+        outs = call_all(job.workers, "step", None, learning_rate)
         return {"job_id": job.job_id, "metrics": outs[0]["metrics"], "batch": {}}
 
     def empty_training_cache(self, job_id: int) -> Dict[str, Any]:
         job = self._job(job_id, ("training", "log_prob"))
-        for w in job.workers:
-            w.call("empty_cache")
+        call_all(job.workers, "empty_cache")
         return {"job_id": job.job_id, "status": "ok"}
 
     # ------------------------------------------------------------------ checkpoints
@@ -219,7 +239,7 @@ class ArcticRLServerCore:
         if not root:
             raise JobError(400, "no checkpoint path configured")
         save_dir, tag = resolve_checkpoint_save_paths(root, step)
-        outs = [w.call("save_checkpoint", save_dir, tag, export_hf) for w in job.workers]
+        outs = call_all(job.workers, "save_checkpoint", None, save_dir, tag, export_hf)
         if save_total_limit:
             prune_checkpoint_dirs(save_dir, save_total_limit)
         return {"job_id": job.job_id, "path": save_dir, "tag": tag, "files": outs[0].get("files", [])}
@@ -230,7 +250,7 @@ class ArcticRLServerCore:
         if not root:
             raise JobError(400, "no checkpoint path configured")
         tag = f"checkpoint-{step}" if step is not None else None
-        steps = [w.call("load_checkpoint", root, tag) for w in job.workers]
+        steps = call_all(job.workers, "load_checkpoint", None, root, tag)
         return {"job_id": job.job_id, "global_steps": int(steps[0] or 0)}
 
     # ------------------------------------------------------------------ rollout
@@ -288,8 +308,19 @@ class ArcticRLServerCore:
         total = 0
         from .utils.weight_sync import sync_pair
         strategies = set()
+        stage = int(((src.config.get("ds_config") or {}).get("zero_optimization") or {}).get("stage", 1))
+        sharded = stage >= 3 and len(src.workers) > 1
         for tid in target_job_ids:
             dst = self._job(tid, ("sampling", "log_prob"))
+            if sharded and not all(getattr(w, "obj", None) is not None for w in list(src.workers) + list(dst.workers)):
+                # parameters exist only as shards spread over the source ranks: every rank takes part in the
+                # gather, rank 0 hands the full tensors over, every target loads them
+                from .utils.weight_sync import load_staged
+                weights = call_all(src.workers, "get_weights", None, 0)[0]
+                for dw in dst.workers:
+                    total += load_staged(dw, weights)
+                strategies.add("gather_bulk")
+                continue
             for i, dw in enumerate(dst.workers):
                 sw = src.workers[i % len(src.workers)]
                 r = sync_pair(sw, dw, cuda_ipc=cuda_ipc, low_memory=low_memory,
@@ -302,7 +333,7 @@ class ArcticRLServerCore:
     def weight_norm(self, training_job_id: Optional[int] = None, sampling_job_id: Optional[int] = None) -> Dict[str, Any]:
         out: Dict[str, Any] = {}
         if training_job_id is not None:
-            r = self._job(training_job_id).workers[0].call("weight_norm")
+            r = call_all(self._job(training_job_id).workers, "weight_norm")[0]      # sharded engines: a collective
             out["training_norm"], out["training_num_params"] = r["norm"], r["num_params"]
         if sampling_job_id is not None:
             r = self._job(sampling_job_id).workers[0].call("weight_norm")
@@ -312,20 +343,17 @@ class ArcticRLServerCore:
     # ------------------------------------------------------------------ sleep / wake
     def sleep_inference(self, job_id: int, level: int = 1) -> Dict[str, Any]:
         job = self._job(job_id, ("sampling",))
-        for w in job.workers:
-            w.call("sleep_inference", level)
+        call_all(job.workers, "sleep_inference", None, level)
         return {"job_id": job.job_id, "status": "sleeping"}
 
     def wake_inference(self, job_id: int, tags=None) -> Dict[str, Any]:
         job = self._job(job_id, ("sampling",))
-        for w in job.workers:
-            w.call("wake_inference", tags)
+        call_all(job.workers, "wake_inference", None, tags)
         return {"job_id": job.job_id, "status": "awake"}
 
     def reset_prefix_cache(self, job_id: int) -> Dict[str, Any]:
         job = self._job(job_id, ("sampling",))
-        for w in job.workers:
-            w.call("reset_prefix_cache")
+        call_all(job.workers, "reset_prefix_cache")
         return {"job_id": job.job_id, "status": "ok"}
 
     def sleep_training(self, job_id: int, mode: str = "all") -> Dict[str, Any]:
@@ -333,14 +361,12 @@ class ArcticRLServerCore:
         method = {"all": "offload_to_cpu", "non_lp": "offload_non_lp_states", "lp_params": "offload_lp_params"}.get(mode)
         if method is None:
             raise JobError(400, f"unknown sleep mode {mode!r}")
-        for w in job.workers:
-            w.call(method)
+        call_all(job.workers, method)
         return {"job_id": job.job_id, "status": "sleeping", "mode": mode}
 
     def wake_training(self, job_id: int) -> Dict[str, Any]:
         job = self._job(job_id, ("training", "log_prob"))
-        for w in job.workers:
-            w.call("backload_to_gpu")
+        call_all(job.workers, "backload_to_gpu")
         return {"job_id": job.job_id, "status": "awake"}
 
     def operation(self, operation_type: str, sub_job_id: int, payload: Optional[dict] = None) -> Dict[str, Any]:

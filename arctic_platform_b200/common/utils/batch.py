@@ -99,6 +99,41 @@ def shard_token_stats(shards: Sequence[Dict[str, Any]]) -> List[int]:
     return [int(s["attention_mask"].sum()) if "attention_mask" in s else 0 for s in shards]
 
 
+def rank_token_stats(batch: Dict[str, Any], meta: Optional[Dict[str, Any]] = None) -> Dict[str, int]:
+    """Valid-token summary of the shard one data-parallel rank received -- what to compare across ranks when one
+    of them is the straggler (arctic_platform/common/utils/batch.py:25-52 in the reference)."""
+    stats: Dict[str, int] = {}
+    am = batch.get("attention_mask")
+    if torch.is_tensor(am) and am.ndim == 2:
+        lens = am.sum(dim=1).to(torch.int64)
+        stats.update(valid_tokens=int(lens.sum()), batch_size=int(am.shape[0]), seq_len_min=int(lens.min()),
+                     seq_len_max=int(lens.max()))
+    cu = batch.get("cu_seqlens")
+    if torch.is_tensor(cu) and cu.numel() > 0:
+        stats["cu_seqlens_packed"] = int(cu[-1])
+    ids = batch.get("input_ids")
+    if torch.is_tensor(ids) and (ids.ndim == 1 or (ids.ndim == 2 and ids.shape[0] == 1)):
+        stats["packed_tokens"] = int(ids.numel())
+    for key in ("loss_mask", "response_mask"):
+        m = batch.get(key)
+        if torch.is_tensor(m):
+            stats[f"{key}_tokens"] = int(m.sum())
+    bnt = (meta or {}).get("batch_num_tokens")
+    if bnt is not None:
+        stats["meta_batch_num_tokens"] = int(bnt)
+    return stats
+
+
+def log_dp_shard_tokens(rank: int, tag: str, batch: Dict[str, Any], meta: Optional[Dict[str, Any]] = None) -> None:
+    """Prints :func:`rank_token_stats` when ``ARL_LOG_DP_SHARD_TOKENS`` is set (silent otherwise)."""
+    import os
+    if not os.environ.get("ARL_LOG_DP_SHARD_TOKENS"):
+        return
+    stats = rank_token_stats(batch, meta)
+    if stats:
+        print(f"[{rank}] [DP-shard] {tag}: " + " ".join(f"{k}={v}" for k, v in sorted(stats.items())), flush=True)
+
+
 def split_batch_for_ranks(batch, meta: Dict[str, Any], n: int) -> Tuple[List[Any], Optional[torch.Tensor]]:
     """Returns ``(shards, order)``; ``order`` is the permutation applied to the samples (or None).
     ``meta`` is updated in place with ``dp_size`` and the global normalisers."""

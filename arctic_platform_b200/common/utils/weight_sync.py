@@ -32,6 +32,11 @@ def _staged(dst, fn):
     return n
 
 
+def load_staged(dst, weights) -> int:
+    """Loads already gathered ``(name, tensor)`` pairs into one target with the staged wake-up."""
+    return _staged(dst, lambda: dst.call("load_weights", weights))
+
+
 def sync_weights_in_process(src, dst) -> int:
     return src.obj.sync_weights_to(dst.obj)
 

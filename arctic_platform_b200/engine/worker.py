@@ -14,6 +14,7 @@ from typing import Any, Dict, Iterable, List, Optional
 
 import torch
 
+from ..common.utils.batch import log_dp_shard_tokens
 from ..common.utils.metrics import combine_metric_microbatches
 from ..models.config import DecoderConfig, resolve_config
 from ..models.decoder import DecoderLM
@@ -41,7 +42,15 @@ def split_microbatches(batch: Dict[str, torch.Tensor], n: int) -> List[Dict[str,
 
 class EngineWorker:
     def __init__(self, device=None):
-        self.device = torch.device(device if device is not None else ("cuda" if torch.cuda.is_available() else "cpu"))
+        import os
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        if device is None:
+            # one process per GPU: the launcher (torchrun, the job server's spawned actors) names it in LOCAL_RANK
+            device = f"cuda:{int(os.environ.get('LOCAL_RANK', '0'))}" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
         self.job_type: Optional[str] = None
         self.engine: Optional[TrainEngine] = None
         self.sampler = None
@@ -61,6 +70,8 @@ class EngineWorker:
             enable_full_determinism(seed)
         self.model_cfg = model.cfg if model is not None else resolve_config(job_config["model_name"])
         dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        if self.job_type != "sampling":
+            self._ensure_process_group(job_config)
         if self.job_type == "sampling":
             from .sampler import SamplerEngine
             vc = dict(job_config.get("vllm_config") or {})
@@ -88,6 +99,35 @@ class EngineWorker:
             self.engine = TrainEngine(m, ecfg)
         return True
 
+    def rank_info(self) -> Dict[str, Any]:
+        import torch.distributed as dist
+        return {"rank": self.rank, "world": self.world, "device": str(self.device),
+                "process_group": dist.is_initialized(),
+                "zero3": bool(self.engine is not None and getattr(self.engine, "zero3", None) is not None)}
+
+    def _ensure_process_group(self, job_config) -> None:
+        """Joins the job's data-parallel group when the launcher described one (``WORLD_SIZE`` > 1 with a
+        rendezvous address) and none exists yet: NCCL on a GPU, gloo on CPU.  Sampler replicas are independent and
+        never call this.  The reference does the same through ``deepspeed.init_distributed``
+        (arctic_platform/common/deepspeed_worker.py:155)."""
+        import datetime
+        import os
+        import torch.distributed as dist
+        if dist.is_initialized():
+            self.rank, self.world = dist.get_rank(), dist.get_world_size()
+            return
+        if self.world <= 1 or "MASTER_ADDR" not in os.environ or "MASTER_PORT" not in os.environ:
+            self.world = 1
+            return
+        from ..utils.debug import drop_stale_nccl_topo_file
+        drop_stale_nccl_topo_file()
+        timeout = datetime.timedelta(seconds=float(job_config.get("process_group_timeout_s", 600)))
+        if self.device.type == "cuda":
+            dist.init_process_group("nccl", rank=self.rank, world_size=self.world, timeout=timeout, device_id=self.device)
+        else:
+            dist.init_process_group("gloo", rank=self.rank, world_size=self.world, timeout=timeout)
+        self._owns_process_group = True
+
     def _load_model(self, job_config, dtype, seed) -> DecoderLM:
         from pathlib import Path
         from ..models.conversion_cache import load_through_cache
@@ -105,6 +145,10 @@ class EngineWorker:
         self.sampler = None
         if self.device.type == "cuda":
             torch.cuda.empty_cache()
+        import torch.distributed as dist
+        if getattr(self, "_owns_process_group", False) and dist.is_initialized():
+            dist.destroy_process_group()
+            self._owns_process_group = False
 
     # ------------------------------------------------------------------ forward / backward / step
     def _forward_maybe_backward(self, batch, meta, processing, backward: bool) -> Dict[str, Any]:
@@ -117,7 +161,9 @@ class EngineWorker:
             n_mb = int((meta or {}).get("num_micro_batches", 1) or 1)
             mbs = split_microbatches(batch, n_mb)
         per_mb, outs = [], []
-        for mb in mbs:
+        for i, mb in enumerate(mbs):
+            if isinstance(mb, dict):
+                log_dp_shard_tokens(self.rank, f"{'fwd_bwd' if backward else 'fwd'} micro-batch {i}", mb, meta)
             r = run_pipeline(self.engine, mb, meta, processing, self.device, backward=backward, return_tensors=True)
             per_mb.append(r["metrics"])
             outs.append(r)
@@ -127,6 +173,9 @@ class EngineWorker:
             keys = outs[0].get("batch", {}).keys()
             result["batch"] = {k: torch.cat([o["batch"][k] for o in outs], 0) for k in keys}
         metrics["_profile_ms"] = {"fwd_bwd" if backward else "fwd": (time.perf_counter() - t0) * 1e3}
+        if backward:
+            from ..utils.debug import maybe_log_moe_imbalance
+            maybe_log_moe_imbalance(self.rank)
         return result
 
     def forward_backward(self, batch, meta=None, processing=None) -> Dict[str, Any]:
@@ -191,9 +240,14 @@ class EngineWorker:
             self.sampler.weights_updated()
         return n
 
-    def get_weights(self) -> List:
+    def get_weights(self, only_rank: Optional[int] = None) -> Optional[List]:
         """Every weight under its Hugging Face name as CPU tensors: one call, one pass over the parameters (one
-        gather of the shards under ZeRO-3) -- the bulk strategy of a cross-process sync."""
+        gather of the shards under ZeRO-3) -- the bulk strategy of a cross-process sync.  With ``only_rank`` every
+        rank still takes part in the gather but only that rank copies the tensors out; the others return None."""
+        if only_rank is not None and self.rank != only_rank:
+            for _ in self.engine.iter_hf_tensors():
+                pass
+            return None
         return [(n, t.detach().to("cpu", copy=True)) for n, t in self.engine.iter_hf_tensors()]
 
     def weight_buckets(self, bucket_bytes: int = 256 << 20) -> List[List[str]]:

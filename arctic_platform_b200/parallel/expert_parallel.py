@@ -89,6 +89,8 @@ def plan_routing(idx: torch.Tensor, num_experts: int, world: int, rank: int, gro
     routing = Routing(order, torch.div(order, k, rounding_mode="floor").to(torch.int32), dst_rank, dst_row,
                       recv_counts, int(recv_counts.sum()), send, recv, P)
     routing._allc = allc
+    from ..utils.debug import maybe_record_recv_tokens
+    maybe_record_recv_tokens(routing.recv_rows)
     return routing
 
 

@@ -7,6 +7,7 @@ import cProfile
 import fcntl
 import gc
 import io
+import logging
 import os
 import pstats
 import random
@@ -203,3 +204,53 @@ def enable_full_determinism(seed: int, warn_only: bool = True) -> None:
     torch.use_deterministic_algorithms(True, warn_only=warn_only)
     torch.backends.cudnn.deterministic = True
     torch.backends.cudnn.benchmark = False
+
+
+# ----------------------------------------------------------------------------- opt-in diagnostics
+_moe_imbalance = {"max_chunk": 0, "total": 0, "n_dispatch": 0}
+
+
+def moe_imbalance_enabled() -> bool:
+    """``DSS_MOE_IMBALANCE`` (the reference's name, arctic_platform/model/implementations/qwen35/gpu/debug.py:14) or
+    ``APB_MOE_IMBALANCE``.  Read at call time, so a test can switch it."""
+    return bool(os.environ.get("DSS_MOE_IMBALANCE") or os.environ.get("APB_MOE_IMBALANCE"))
+
+
+def maybe_record_recv_tokens(num_recv_tokens: int) -> None:
+    """One expert-parallel dispatch received ``num_recv_tokens`` rows on this rank.  The largest value sizes the
+    fp32 combine buffer; its spread across ranks is the routing imbalance."""
+    if not moe_imbalance_enabled():
+        return
+    _moe_imbalance["max_chunk"] = max(_moe_imbalance["max_chunk"], int(num_recv_tokens))
+    _moe_imbalance["total"] += int(num_recv_tokens)
+    _moe_imbalance["n_dispatch"] += 1
+
+
+def maybe_log_moe_imbalance(rank: int) -> Optional[Dict[str, float]]:
+    """Logs and resets this rank's dispatch counters after a forward/backward request (grep ``MOE_IMBALANCE`` and
+    compare max / min across ranks).  Returns what it logged, ``None`` when the switch is off."""
+    if not moe_imbalance_enabled():
+        return None
+    stats: Dict[str, float] = dict(_moe_imbalance)
+    _moe_imbalance.update(max_chunk=0, total=0, n_dispatch=0)
+    if torch.cuda.is_available():
+        stats["peak_alloc_GiB"] = torch.cuda.max_memory_allocated() / 2 ** 30
+        stats["peak_reserved_GiB"] = torch.cuda.max_memory_reserved() / 2 ** 30
+    logging.getLogger(__name__).info(
+        "MOE_IMBALANCE rank=%d max_chunk_recv=%d total_recv=%d n_dispatch=%d peak_alloc_GiB=%.2f peak_reserved_GiB=%.2f",
+        rank, stats["max_chunk"], stats["total"], stats["n_dispatch"], stats.get("peak_alloc_GiB", 0.0),
+        stats.get("peak_reserved_GiB", 0.0))
+    return stats
+
+
+def drop_stale_nccl_topo_file() -> Optional[str]:
+    """A network plugin passes its generated topology to NCCL through ``NCCL_TOPO_FILE=/proc/self/fd/<n>``.  That
+    handle means something only in the process that created it; a child that inherits it would load an unrelated
+    file and the rendezvous would hang.  Called before the process group is created; an administrator's static
+    path is left alone.  Returns the dropped value (arctic_platform/common/deepspeed_worker.py:139-153)."""
+    topo = os.environ.get("NCCL_TOPO_FILE", "")
+    if topo.startswith("/proc/self/fd/"):
+        logging.getLogger(__name__).warning("dropping inherited stale NCCL_TOPO_FILE=%s", topo)
+        os.environ.pop("NCCL_TOPO_FILE", None)
+        return topo
+    return None

@@ -83,3 +83,40 @@ def test_registry_lookup_and_dotted_fallback():
         registry.resolve_fn("nope", registry.LOSS_FNS)
     with pytest.raises(KeyError):
         registry.resolve_fn("math.nope", registry.LOSS_FNS)
+
+
+def test_env_gated_diagnostics(monkeypatch, capsys):
+    import torch
+    from arctic_platform_b200.common.utils.batch import log_dp_shard_tokens, rank_token_stats
+    from arctic_platform_b200.utils import debug
+    mask = torch.tensor([[1, 1, 1, 0], [1, 1, 0, 0]])
+    batch = {"input_ids": torch.zeros(2, 4, dtype=torch.long), "attention_mask": mask, "response_mask": mask[:, 2:]}
+    stats = rank_token_stats(batch, {"batch_num_tokens": 9})
+    assert stats == {"valid_tokens": 5, "batch_size": 2, "seq_len_min": 2, "seq_len_max": 3, "response_mask_tokens": 1,
+                     "meta_batch_num_tokens": 9}
+    assert rank_token_stats({"input_ids": torch.zeros(7, dtype=torch.long), "cu_seqlens": torch.tensor([0, 3, 7])}) == \
+        {"cu_seqlens_packed": 7, "packed_tokens": 7}
+    monkeypatch.delenv("ARL_LOG_DP_SHARD_TOKENS", raising=False)
+    log_dp_shard_tokens(3, "fwd", batch)
+    assert capsys.readouterr().out == ""
+    monkeypatch.setenv("ARL_LOG_DP_SHARD_TOKENS", "1")
+    log_dp_shard_tokens(3, "fwd", batch)
+    assert "[3] [DP-shard] fwd: batch_size=2" in capsys.readouterr().out
+    # MoE dispatch counters: silent unless switched on, reset by the log call
+    monkeypatch.delenv("DSS_MOE_IMBALANCE", raising=False)
+    monkeypatch.delenv("APB_MOE_IMBALANCE", raising=False)
+    debug.maybe_record_recv_tokens(100)
+    assert debug.maybe_log_moe_imbalance(0) is None
+    monkeypatch.setenv("DSS_MOE_IMBALANCE", "1")
+    for n in (10, 40, 25):
+        debug.maybe_record_recv_tokens(n)
+    got = debug.maybe_log_moe_imbalance(0)
+    assert (got["max_chunk"], got["total"], got["n_dispatch"]) == (40, 75, 3)
+    assert debug.maybe_log_moe_imbalance(0)["n_dispatch"] == 0
+    # a topology handle inherited from a parent process is dropped, an administrator's path is kept
+    monkeypatch.setenv("NCCL_TOPO_FILE", "/proc/self/fd/17")
+    assert debug.drop_stale_nccl_topo_file() == "/proc/self/fd/17"
+    import os
+    assert "NCCL_TOPO_FILE" not in os.environ
+    monkeypatch.setenv("NCCL_TOPO_FILE", "/etc/nccl/topo.xml")
+    assert debug.drop_stale_nccl_topo_file() is None and os.environ["NCCL_TOPO_FILE"] == "/etc/nccl/topo.xml"

@@ -1,0 +1,109 @@
+"""Two data-parallel ranks as spawned worker processes behind the job server (gloo): the server dispatches to all
+ranks at once (the ranks meet in collectives inside initialize / forward / step), the ranks form their process
+group from the launcher's environment, and the result equals one process training on the whole batch.  Stage 3
+adds gathers inside the forward pass and a weight hand-over that needs every source rank."""
+import socket
+
+import pytest
+import torch
+
+from arctic_platform_b200.common.local_actors import spawned_worker_factory
+from arctic_platform_b200.common.server import ArcticRLServerCore, call_all
+from tests.test_zorro_equivalence_cpu import make_grpo_batch
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _job(stage):
+    return {"model_name": "qwen3-tiny", "job_type": "training", "seed": 11,
+            "ds_config": {"zero_optimization": {"stage": stage}, "gradient_clipping": 1.0,
+                          "optimizer": {"type": "AdamW", "params": {"lr": 1e-3, "weight_decay": 0.01}}}}
+
+
+def _payload():
+    ids, mask, R = make_grpo_batch(n_prompts=4, n_samples=2, seed=3)
+    B = ids.shape[0]
+    g = torch.Generator().manual_seed(1)
+    batch = {"input_ids": ids, "attention_mask": mask, "response_mask": mask[:, -R:],
+             "old_log_probs": torch.randn(B, R, generator=g) * 0.01 - 2.0,
+             "advantages": torch.randn(B, 1, generator=g).expand(B, R).contiguous()}
+    meta = {"response_length": R, "zorro_train_enable": True, "batch_num_tokens": float(mask[:, -R:].sum()),
+            "global_batch_size": float(B)}
+    return {"batch": batch, "meta": meta, "processing": {"loss_fn": "verl_grpo"}}
+
+
+def _train(core, job_id, steps=2):
+    out = []
+    for _ in range(steps):
+        r = core.forward_backward(job_id, _payload())
+        s = core.step(job_id)
+        out.append((r["avg_loss"], s["metrics"]["grad_norm"]))
+    return out
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("stage", [1, 3])
+def test_two_spawned_ranks_match_one_process(stage):
+    single = ArcticRLServerCore()
+    j1 = single.initialize(_job(stage))["job_id"]
+    want = _train(single, j1)
+    want_norm = single.weight_norm(training_job_id=j1)["training_norm"]
+
+    core = ArcticRLServerCore(worker_factory=spawned_worker_factory(_free_port()), training_gpus=2)
+    try:
+        info = core.initialize(_job(stage))
+        assert info["num_devices"] == 2
+        job = core.jobs[info["job_id"]]
+        ranks = call_all(job.workers, "rank_info")
+        assert [r["rank"] for r in ranks] == [0, 1] and all(r["world"] == 2 and r["process_group"] for r in ranks)
+        assert all(r["zero3"] == (stage == 3) for r in ranks)
+        got = _train(core, info["job_id"])
+        for (la, na), (lb, nb) in zip(got, want):
+            assert la == pytest.approx(lb, rel=1e-4, abs=1e-6) and na == pytest.approx(nb, rel=1e-4)
+        norms = [r["norm"] for r in call_all(job.workers, "weight_norm")]      # stage 3: a collective
+        assert core.weight_norm(training_job_id=info["job_id"])["training_norm"] == pytest.approx(norms[0], rel=1e-7)
+        assert norms[0] == pytest.approx(norms[1], rel=1e-7) and norms[0] == pytest.approx(want_norm, rel=1e-5)
+        # hand the trained weights to a sampler job (its own process, no process group)
+        sj = core.initialize({"model_name": "qwen3-tiny", "job_type": "sampling", "num_devices": 1, "seed": 5,
+                              "vllm_config": {"max_model_len": 64}})
+        before = core.weight_norm(sampling_job_id=sj["job_id"])["sampling_norm"]
+        res = core.weight_sync(info["job_id"], [sj["job_id"]])
+        assert res["strategies"] == (["gather_bulk"] if stage == 3 else ["bulk"])
+        after = core.weight_norm(sampling_job_id=sj["job_id"])["sampling_norm"]
+        assert after == pytest.approx(norms[0], rel=1e-6) and after != pytest.approx(before, rel=1e-6)
+        out = core.generate(sj["job_id"], [[3, 4, 5]], {"n": 2, "max_tokens": 3, "temperature": 1.0})
+        assert len(out["results"]) == 2
+    finally:
+        core.destroy()
+        single.destroy()
+
+
+def test_call_all_runs_workers_concurrently_and_reports_the_first_failure():
+    import threading
+    import time
+    barrier = threading.Barrier(3, timeout=5)
+
+    class W:
+        def __init__(self, i):
+            self.i = i
+
+        def call(self, method, *args):
+            if method == "meet":
+                barrier.wait()                       # passes only if all three calls are in flight together
+                return (self.i,) + args
+            if method == "boom" and self.i == 1:
+                raise ValueError("rank 1 failed")
+            time.sleep(0.05)
+            return self.i
+
+    ws = [W(i) for i in range(3)]
+    assert call_all(ws, "meet", None, "x") == [(0, "x"), (1, "x"), (2, "x")]
+    barrier.reset()
+    assert call_all(ws, "meet", [(10,), (11,), (12,)]) == [(0, 10), (1, 11), (2, 12)]
+    with pytest.raises(ValueError, match="rank 1"):
+        call_all(ws, "boom")
+    assert call_all(ws[:1], "other") == [0]
