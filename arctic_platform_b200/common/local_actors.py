@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import multiprocessing as mp
 import os
+import threading
 import traceback
 from typing import Any, Callable, Dict, Optional
 
@@ -55,6 +56,7 @@ class SpawnedActor:
         env = dict(env or {})
         if gpu is not None:
             env["CUDA_VISIBLE_DEVICES"] = str(gpu)
+        self._lock = threading.Lock()         # one request on the pipe at a time (several jobs may share a process)
         self._proc = ctx.Process(target=_serve, args=(child, factory, env), daemon=True)
         self._proc.start()
         child.close()
@@ -74,11 +76,12 @@ class SpawnedActor:
     def call(self, method: str, *args, timeout: Optional[float] = None, **kwargs):
         if not self._proc.is_alive():
             raise ActorDied(f"actor pid {self._proc.pid} is not running (code {self._proc.exitcode})")
-        try:
-            self._conn.send((method, args, kwargs))
-        except (BrokenPipeError, OSError) as exc:
-            raise ActorDied(f"actor pid {self._proc.pid} is gone") from exc
-        kind, payload = self._recv(timeout)
+        with self._lock:
+            try:
+                self._conn.send((method, args, kwargs))
+            except (BrokenPipeError, OSError) as exc:
+                raise ActorDied(f"actor pid {self._proc.pid} is gone") from exc
+            kind, payload = self._recv(timeout)
         if kind == "error":
             raise ActorError(payload)
         return payload
@@ -123,3 +126,105 @@ def spawned_worker_factory(master_port: int = 29500):
                "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(master_port + offset)}
         return SpawnedActor(_make_engine_worker, env=env)
     return factory
+
+
+# ----------------------------------------------------------------------------- one process per GPU, many jobs
+class _RankHost:
+    """Lives inside a rank's process and owns the engine workers of every job placed on that rank, so that a
+    training engine and a sampling engine of the same GPU are in ONE process: the weight hand-over between them is
+    the in-process kernel (no copy through the host), and sleep / wake trade the same device memory."""
+
+    def __init__(self) -> None:
+        self.workers: Dict[str, Any] = {}
+
+    def create(self, key: str) -> bool:
+        from ..engine.worker import EngineWorker
+        self.workers[key] = EngineWorker()
+        return True
+
+    def invoke(self, key: str, method: str, *args, **kwargs):
+        return getattr(self.workers[key], method)(*args, **kwargs)
+
+    def drop(self, key: str) -> bool:
+        w = self.workers.pop(key, None)
+        if w is not None:
+            w.destroy()
+        return w is not None
+
+    def sync(self, src_key: str, dst_key: str) -> int:
+        return self.workers[src_key].sync_weights_to(self.workers[dst_key])
+
+    def keys(self):
+        return sorted(self.workers)
+
+
+class RankWorkerHandle:
+    """What the job server holds for one (rank process, job) pair: the actor interface of a single worker."""
+
+    def __init__(self, actor: SpawnedActor, key: str, rank: int, owns_process: bool = False):
+        self.actor, self.key, self.rank, self.owns_process = actor, key, rank, owns_process
+
+    def call(self, method: str, *args, timeout: Optional[float] = None, **kwargs):
+        return self.actor.call("invoke", self.key, method, *args, timeout=timeout, **kwargs)
+
+    def heartbeat(self, timeout: float = 5.0) -> bool:
+        return self.actor.heartbeat(timeout)
+
+    def kill(self) -> None:
+        """Ends this job's worker; the rank's process stays for the other jobs (the pool ends processes)."""
+        try:
+            self.actor.call("drop", self.key, timeout=60.0)
+        except (ActorDied, ActorError):
+            pass
+        if self.owns_process:
+            self.actor.kill()
+
+
+class RankProcessPool:
+    """``world`` long-lived rank processes (rank r on GPU r, all GPUs visible, one rendezvous), created on first
+    use.  ``factory`` is a ``worker_factory`` for ``ArcticRLServerCore``: jobs whose ranks form a process group
+    (training, log-prob) must span the whole pool; sampler jobs may use any prefix of it."""
+
+    def __init__(self, world: int, master_port: int = 29500, colocate: bool = True):
+        self.world, self.master_port, self.colocate = int(world), int(master_port), bool(colocate)
+        self.actors: Dict[int, SpawnedActor] = {}
+        self._ids = 0
+        self._lock = threading.Lock()
+
+    def _actor(self, rank: int) -> SpawnedActor:
+        with self._lock:
+            a = self.actors.get(rank)
+            if a is None:
+                import torch
+                env = {"RANK": str(rank), "LOCAL_RANK": str(rank if torch.cuda.is_available() else 0),
+                       "WORLD_SIZE": str(self.world), "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(self.master_port)}
+                a = self.actors[rank] = SpawnedActor(_RankHost, env=env)
+            return a
+
+    def factory(self, job_config: Dict[str, Any], rank: int, world: int) -> RankWorkerHandle:
+        job_type = job_config.get("job_type", "training")
+        if job_type == "sampling" and not self.colocate:
+            # split placement: sampler replica r gets a process of its own on the GPU after the trainer's GPUs
+            import torch
+            env = {"RANK": "0", "WORLD_SIZE": "1",
+                   "LOCAL_RANK": str(self.world + rank if torch.cuda.is_available() else 0)}
+            actor = SpawnedActor(_RankHost, env=env)
+            actor.call("create", "sampling", timeout=600.0)
+            return RankWorkerHandle(actor, "sampling", rank, owns_process=True)
+        if rank >= self.world:
+            raise ValueError(f"{job_type} job wants rank {rank} but the pool has {self.world} rank processes")
+        if job_type != "sampling" and world != self.world:
+            raise ValueError(f"a {job_type} job forms a process group over the whole pool: it needs {self.world} "
+                             f"ranks, not {world}")
+        with self._lock:
+            self._ids += 1
+            key = f"{job_type}-{self._ids}"
+        actor = self._actor(rank)
+        actor.call("create", key, timeout=600.0)
+        return RankWorkerHandle(actor, key, rank)
+
+    def shutdown(self) -> None:
+        with self._lock:
+            actors, self.actors = list(self.actors.values()), {}
+        for a in actors:
+            a.kill()

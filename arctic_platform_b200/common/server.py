@@ -103,17 +103,35 @@ def call_all(workers: Sequence[Any], method: str, per_worker_args: Optional[Sequ
     return results
 
 
+def _free_port() -> int:
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def default_worker_factory(job_config: Dict[str, Any], rank: int, world: int):
     from ..engine.worker import EngineWorker
     return InProcessActor(EngineWorker())
 
 
 class ArcticRLServerCore:
-    def __init__(self, worker_factory: Callable = default_worker_factory, training_gpus: int = 0,
+    def __init__(self, worker_factory: Optional[Callable] = None, training_gpus: int = 0,
                  sampling_gpus: int = 0, log_prob_gpus: int = 0, colocate: bool = False,
-                 heartbeat_timeout: float = 0.0):
-        self.worker_factory = worker_factory
+                 heartbeat_timeout: float = 0.0, master_port: Optional[int] = None):
         self.gpus = {"training": training_gpus, "sampling": sampling_gpus, "log_prob": log_prob_gpus}
+        self.pool = None
+        if worker_factory is None:
+            ranks = max(int(training_gpus or 0), int(log_prob_gpus or 0))
+            if ranks > 1:
+                # more than one rank per job: one long-lived process per GPU hosting that GPU's engines of every
+                # job (the ranks need a process group; colocated engines need to share a process)
+                from .local_actors import RankProcessPool
+                self.pool = RankProcessPool(ranks, master_port or _free_port(), colocate=colocate)
+                worker_factory = self.pool.factory
+            else:
+                worker_factory = default_worker_factory
+        self.worker_factory = worker_factory
         self.colocate = colocate
         self.jobs: Dict[int, Job] = {}
         self._ids = itertools.count(1)
@@ -165,6 +183,8 @@ class ArcticRLServerCore:
             for w in j.workers:
                 w.kill()
             j.status = "DESTROYED"
+        if job_id is None and self.pool is not None:
+            self.pool.shutdown()                  # everything was destroyed: the rank processes go too
         return {"destroyed": [j.job_id for j in jobs]}
 
     def _job(self, job_id: int, kinds=None) -> Job:
@@ -312,6 +332,18 @@ class ArcticRLServerCore:
         sharded = stage >= 3 and len(src.workers) > 1
         for tid in target_job_ids:
             dst = self._job(tid, ("sampling", "log_prob"))
+            from .utils.weight_sync import same_rank_process
+            paired = len(dst.workers) == len(src.workers) and all(
+                same_rank_process(sw, dw) for sw, dw in zip(src.workers, dst.workers))
+            if len(src.workers) > 1 and paired and cuda_ipc is not False:
+                # trainer rank r and sampler replica r share a process: every rank runs the in-process kernel at
+                # the same time (under stage 3 it gathers the peers' shards, a collective)
+                from concurrent.futures import ThreadPoolExecutor
+                with ThreadPoolExecutor(max_workers=len(src.workers)) as pool:
+                    outs = list(pool.map(lambda p: sync_pair(p[0], p[1], cuda_ipc=cuda_ipc), zip(src.workers, dst.workers)))
+                total += sum(o["num_tensors"] for o in outs)
+                strategies.update(o["strategy"] for o in outs)
+                continue
             if sharded and not all(getattr(w, "obj", None) is not None for w in list(src.workers) + list(dst.workers)):
                 # parameters exist only as shards spread over the source ranks: every rank takes part in the
                 # gather, rank 0 hands the full tensors over, every target loads them

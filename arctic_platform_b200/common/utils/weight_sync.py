@@ -69,12 +69,20 @@ def sync_weights_cpu_file(src, dst, directory: Optional[str] = None, staged: boo
     return _staged(dst, run) if staged else run()
 
 
+def same_rank_process(src, dst) -> bool:
+    a, b = getattr(src, "actor", None), getattr(dst, "actor", None)
+    return a is not None and a is b
+
+
 def sync_pair(src, dst, cuda_ipc: Optional[bool] = None, low_memory: Optional[bool] = None,
               via_file: bool = False, bucket_bytes: int = 256 << 20) -> Dict[str, Any]:
     """Picks the strategy for one (source worker, target worker) pair and reports which one ran."""
     same_process = getattr(src, "obj", None) is not None and getattr(dst, "obj", None) is not None
     if same_process and cuda_ipc is not False:
         return {"strategy": "in_process", "num_tensors": sync_weights_in_process(src, dst)}
+    if same_rank_process(src, dst) and cuda_ipc is not False:
+        # both engines live in the same spawned rank process: the in-process kernel runs there
+        return {"strategy": "in_process", "num_tensors": src.actor.call("sync", src.key, dst.key)}
     if via_file:
         return {"strategy": "cpu_file", "num_tensors": sync_weights_cpu_file(src, dst)}
     if low_memory:

@@ -40,6 +40,10 @@ def split_microbatches(batch: Dict[str, torch.Tensor], n: int) -> List[Dict[str,
     return outs
 
 
+# the process group a worker of this process created from the launcher's environment, and how many workers use it
+_PG = {"created_here": False, "users": 0}
+
+
 class EngineWorker:
     def __init__(self, device=None):
         import os
@@ -115,6 +119,9 @@ class EngineWorker:
         import torch.distributed as dist
         if dist.is_initialized():
             self.rank, self.world = dist.get_rank(), dist.get_world_size()
+            if _PG["created_here"]:
+                _PG["users"] += 1
+                self._owns_process_group = True
             return
         if self.world <= 1 or "MASTER_ADDR" not in os.environ or "MASTER_PORT" not in os.environ:
             self.world = 1
@@ -126,6 +133,7 @@ class EngineWorker:
             dist.init_process_group("nccl", rank=self.rank, world_size=self.world, timeout=timeout, device_id=self.device)
         else:
             dist.init_process_group("gloo", rank=self.rank, world_size=self.world, timeout=timeout)
+        _PG["created_here"], _PG["users"] = True, 1
         self._owns_process_group = True
 
     def _load_model(self, job_config, dtype, seed) -> DecoderLM:
@@ -146,9 +154,12 @@ class EngineWorker:
         if self.device.type == "cuda":
             torch.cuda.empty_cache()
         import torch.distributed as dist
-        if getattr(self, "_owns_process_group", False) and dist.is_initialized():
-            dist.destroy_process_group()
+        if getattr(self, "_owns_process_group", False):
             self._owns_process_group = False
+            _PG["users"] -= 1
+            if _PG["users"] <= 0 and dist.is_initialized():      # the last engine of this process that used it
+                dist.destroy_process_group()
+                _PG["created_here"] = False
 
     # ------------------------------------------------------------------ forward / backward / step
     def _forward_maybe_backward(self, batch, meta, processing, backward: bool) -> Dict[str, Any]:

@@ -107,3 +107,39 @@ def test_call_all_runs_workers_concurrently_and_reports_the_first_failure():
     with pytest.raises(ValueError, match="rank 1"):
         call_all(ws, "boom")
     assert call_all(ws[:1], "other") == [0]
+
+
+@pytest.mark.timeout(600)
+def test_rank_process_pool_hosts_trainer_and_sampler_of_a_rank_together():
+    """The server's default for more than one rank per job: one process per rank hosting that rank's engines of
+    every job.  Stage-3 trainer + log-prob engine + sampler replicas share the processes; the weight hand-over runs
+    inside each rank process on all ranks at once."""
+    core = ArcticRLServerCore(training_gpus=2, sampling_gpus=2, log_prob_gpus=2, colocate=True)
+    assert core.pool is not None and core.pool.world == 2
+    try:
+        tj = core.initialize(_job(3))["job_id"]
+        lj = core.initialize({**_job(3), "job_type": "log_prob"})["job_id"]
+        sj = core.initialize({"model_name": "qwen3-tiny", "job_type": "sampling", "seed": 5,
+                              "vllm_config": {"max_model_len": 64}})["job_id"]
+        assert len(core.pool.actors) == 2                       # three jobs, still two processes
+        assert sorted(k.split("-")[0] for k in core.pool.actors[0].call("keys")) == ["log_prob", "sampling", "training"]
+        got = _train(core, tj, steps=1)
+        assert got[0][1] > 0
+        res = core.weight_sync(tj, [sj, lj])
+        assert res["strategies"] == ["in_process"]
+        tn = core.weight_norm(training_job_id=tj)["training_norm"]
+        assert core.weight_norm(sampling_job_id=sj)["sampling_norm"] == pytest.approx(tn, rel=1e-6)
+        # the log-prob engine scores with the synced weights: same log-probs as the trainer's own forward
+        p = _payload()
+        a = core.forward(tj, {"batch": p["batch"], "meta": p["meta"]})["batch"]["log_probs"]
+        b = core.forward(lj, {"batch": p["batch"], "meta": p["meta"]})["batch"]["log_probs"]
+        assert torch.allclose(a, b, atol=1e-5)
+        out = core.generate(sj, [[3, 4, 5], [6, 7]], {"n": 2, "max_tokens": 3, "temperature": 1.0})
+        assert len(out["results"]) == 4
+        # destroying one job leaves the processes (and the other jobs) alive
+        core.destroy(lj)
+        assert len(core.pool.actors[0].call("keys")) == 2
+        assert _train(core, tj, steps=1)[0][1] > 0
+    finally:
+        core.destroy()
+    assert core.pool.actors == {}
