@@ -100,6 +100,10 @@ class EngineWorker:
             ecfg = EngineConfig.from_ds_config(job_config.get("ds_config"), job_config.get("training_config"))
             wc = job_config.get("ds_worker_config") or {}
             ecfg.gradient_checkpointing = bool(wc.get("gradient_checkpointing", False))
+            from ..models.factory import _tiled_mlp_setting
+            shards = _tiled_mlp_setting(wc.get("tiled_mlp"))
+            for blk in m.blocks:
+                blk.tiled_mlp_shards = shards
             self.engine = TrainEngine(m, ecfg)
         return True
 

@@ -107,6 +107,7 @@ class DecoderBlock(nn.Module):
             self.k_norm = mk(D) if cfg.qk_norm else None
             self.wo = mk(H, cfg.q_size)
         self.kv_capture = None           # a sampler's prefill sets a list; forward appends this layer's (k, v)
+        self.tiled_mlp_shards = 0        # > 1 or "auto": the dense MLP runs over row tiles (activation memory)
         self.ln2 = mk(H)
         if cfg.is_moe:
             from .moe import MoEFeedForward
@@ -145,9 +146,15 @@ class DecoderBlock(nn.Module):
         h2, stream = norm.rmsnorm(o, self.ln2, cfg.rms_norm_eps, stream, self.w_offset)
         if self.mlp is not None:
             d = self.mlp(h2)
+        elif self.tiled_mlp_shards:
+            from .tiled_mlp import tiled_mlp
+            d = tiled_mlp(h2, self._dense_mlp, self.tiled_mlp_shards, (self.wgu, self.wdown))
         else:
-            d = gemm.linear(gate_up_act(h2, self.wgu), self.wdown)
+            d = self._dense_mlp(h2)
         return d, stream
+
+    def _dense_mlp(self, h: torch.Tensor) -> torch.Tensor:
+        return gemm.linear(gate_up_act(h, self.wgu), self.wdown)
 
 
 class DecoderLM(nn.Module):

@@ -18,7 +18,18 @@ import torch
 from .config import DecoderConfig, resolve_config
 from .decoder import DecoderLM
 
-PATCH_ORDER = ("liger", "zorro_train", "gradient_checkpointing")
+PATCH_ORDER = ("liger", "zorro_train", "tiled_mlp", "gradient_checkpointing")
+
+
+def _tiled_mlp_setting(v) -> Any:
+    """``tiled_mlp`` of the worker config: ``True`` / ``"auto"`` / an int / ``{"enable": ..., "shards": ...}``."""
+    if isinstance(v, dict):
+        if not v.get("enable", True):
+            return 0
+        v = v.get("shards", "auto")
+    if v is True:
+        return "auto"
+    return v or 0
 
 
 @dataclass
@@ -50,6 +61,7 @@ class Patches:
     liger: bool = True
     zorro_train: Optional[ZorroTrainPatch] = None
     gradient_checkpointing: bool = False
+    tiled_mlp: Any = 0                     # row tiles of the dense MLP: an int, "auto" (ceil(tokens / hidden)) or 0
 
 
 @dataclass
@@ -71,7 +83,8 @@ class ModelSpec:
         patches = Patches(liger=bool(wc.get("liger", True)),
                           zorro_train=ZorroTrainPatch(**{k: v for k, v in z.items() if k != "enable"})
                           if isinstance(z, dict) and z.get("enable", True) else None,
-                          gradient_checkpointing=bool(wc.get("gradient_checkpointing", True)))
+                          gradient_checkpointing=bool(wc.get("gradient_checkpointing", True)),
+                          tiled_mlp=_tiled_mlp_setting(wc.get("tiled_mlp")))
         par = ParallelismConfig(expert_parallel=int(wc.get("expert_parallel", 1)),
                                 sequence_parallel=int(wc.get("sequence_parallel", 1)))
         return ModelSpec(model_name, dtype=wc.get("dtype", "bfloat16"), attn_implementation=wc.get("attn_implementation"),
@@ -166,6 +179,10 @@ def apply_patches(model: DecoderLM, patches: Patches) -> List[str]:
             done.append(name)
         elif name == "zorro_train" and patches.zorro_train is not None:
             model.zorro = patches.zorro_train
+            done.append(name)
+        elif name == "tiled_mlp" and patches.tiled_mlp:
+            for blk in model.blocks:
+                blk.tiled_mlp_shards = patches.tiled_mlp
             done.append(name)
         elif name == "gradient_checkpointing" and patches.gradient_checkpointing:
             model.gradient_checkpointing = True
