@@ -137,6 +137,6 @@ def test_tiled_mlp_on_gpu_matches_untiled():
         res[shards] = (lp.detach().float(), {n: p.grad.float() for n, p in gpu.named_parameters() if p.grad is not None})
     assert (res[0][0] - res[3][0]).abs().max() < 1e-3
     assert set(res[0][1]) == set(res[3][1])
-    for n in ("blocks.0.wgu", "blocks.0.wdown", "blocks.1.wqkv", "embed"):
+    for n in ("blocks.0.wgu", "blocks.0.wdown", "blocks.1.wqkv", "blocks.1.wo"):
         a, b = res[0][1][n].flatten(), res[3][1][n].flatten()
         assert torch.nn.functional.cosine_similarity(a, b, dim=0) > 0.999, n
