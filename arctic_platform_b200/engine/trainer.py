@@ -56,6 +56,7 @@ class EngineConfig:
     scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
     impl: str = "fused"             # fused | collective
     offload_optimizer: bool = False
+    adam_w_mode: bool = True           # False: classic Adam, weight decay added to the gradient (L2) instead of decoupled
     gradient_checkpointing: bool = False
 
     @staticmethod
@@ -69,7 +70,7 @@ class EngineConfig:
             o = training_config.get("optimizer", {}) or {}
             betas = o.get("betas") or [o.get("beta1", 0.9), o.get("beta2", 0.999)]
             opt = {"lr": o.get("lr", 1e-5), "betas": list(betas), "eps": o.get("eps", 1e-8),
-                   "weight_decay": o.get("weight_decay", 0.0)}
+                   "weight_decay": o.get("weight_decay", 0.0), "adam_w_mode": o.get("adam_w_mode", True)}
             if "gradient_accumulation_steps" in training_config:
                 ds["gradient_accumulation_steps"] = training_config["gradient_accumulation_steps"]
             for src, key in ((o, "gradient_clipping"), (training_config, "gradient_clipping"), (o, "max_grad_norm")):
@@ -95,6 +96,7 @@ class EngineConfig:
         cfg.betas = (float(b[0]), float(b[1]))
         cfg.eps = float(opt.get("eps", 1e-8))
         cfg.weight_decay = float(opt.get("weight_decay", 0.0))
+        cfg.adam_w_mode = bool(opt.get("adam_w_mode", True))
         cfg.max_grad_norm = float(ds.get("gradient_clipping", 0.0) or 0.0)
         cfg.gradient_accumulation_steps = int(ds.get("gradient_accumulation_steps", 1))
         zero = ds.get("zero_optimization", {}) or {}
@@ -361,7 +363,7 @@ class TrainEngine:
         bias1 = 1.0 - cfg.betas[0] ** t
         bias2 = 1.0 - cfg.betas[1] ** t
         self.sumsq.zero_()
-        if self.impl == "fused" and not self.opt_on_host:
+        if self.impl == "fused" and not self.opt_on_host and self.cfg.adam_w_mode:
             self._step_fused(lr, bias1, bias2)
         else:
             self._step_collective(lr, bias1, bias2)
@@ -477,7 +479,7 @@ class TrainEngine:
         gscale = (float(clip.item()) if clip is not None else 1.0) if self.opt_on_host else None
         for ui, (so, g) in enumerate(zip(self.unit_shard_off, shards)):
             n = self.units[ui].length if self.units[ui].local_only else z.unit_shard_len[ui]
-            if self.opt_on_host:
+            if self.opt_on_host and cfg.adam_w_mode:
                 new = self._host_adamw(so, n, events[ui], gscale, lr, bias1, bias2)
             else:
                 new = self._torch_adamw(so, n, g, clip, lr, bias1, bias2)
@@ -497,9 +499,12 @@ class TrainEngine:
         if clip is not None:
             g = g * clip.to(g.device)
         m, v, w = self.exp_avg[so:so + n], self.exp_avg_sq[so:so + n], self.master[so:so + n]
+        if not cfg.adam_w_mode and cfg.weight_decay:
+            g = g + cfg.weight_decay * w                     # L2 regularisation: the decay goes through the moments
         m.mul_(cfg.betas[0]).add_(g, alpha=1 - cfg.betas[0])
         v.mul_(cfg.betas[1]).addcmul_(g, g, value=1 - cfg.betas[1])
-        w.mul_(1 - lr * cfg.weight_decay)
+        if cfg.adam_w_mode:
+            w.mul_(1 - lr * cfg.weight_decay)
         w.addcdiv_(m / bias1, (v / bias2).sqrt_().add_(cfg.eps), value=-lr)
         return w.to(self.param_dtype).to(self.device)
 
@@ -539,7 +544,7 @@ class TrainEngine:
         gscale = (float(clip.item()) if clip is not None else 1.0) if self.opt_on_host else None
         for ui, (u, so, g) in enumerate(zip(self.units, self.unit_shard_off, shards)):
             n = u.shard_len(W)
-            if self.opt_on_host:
+            if self.opt_on_host and cfg.adam_w_mode:
                 new = self._host_adamw(so, n, events[ui], gscale, lr, bias1, bias2)
             else:
                 new = self._torch_adamw(so, n, g, clip, lr, bias1, bias2)
