@@ -228,6 +228,45 @@ class EngineWorker:
         from ..models.hf_io import hf_param_names
         return hf_param_names(self.model_cfg)
 
+    def max_param_bytes(self) -> int:
+        """Size of the largest single weight under its Hugging Face name: what a receiver has to be able to stage
+        when weights arrive one tensor at a time."""
+        return max(t.numel() * t.element_size() for _n, t in self.engine.iter_hf_tensors())
+
+    def export_hf_checkpoint(self, path: str) -> List[str]:
+        """Hugging Face safetensors + ``config.json`` under ``path`` without the optimizer files.  Under ZeRO-3
+        every rank takes part in the gather; rank 0 writes (arctic_platform/common/deepspeed_worker.py:602-636)."""
+        import torch.distributed as dist
+        from ..models.hf_io import save_hf_checkpoint
+        files: List[str] = []
+        sharded = getattr(self.engine, "zero3", None) is not None
+        tensors = None
+        if sharded:
+            tensors = [(n, t.detach().to("cpu").clone() if self.rank == 0 else None) for n, t in self.engine.iter_hf_tensors()]
+        if self.rank == 0:
+            files = save_hf_checkpoint(self.engine.model, path, tensors=tensors)
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier()
+        return files
+
+    def gather_and_save_state_dict(self, path: str) -> Dict[str, Any]:
+        """All ranks gather, rank 0 writes one safetensors file (the hand-over file of the ``cpu_file`` strategy)."""
+        import torch.distributed as dist
+        from ..models.hf_io import write_safetensors
+        tensors = {n: (t.detach().to("cpu").clone() if self.rank == 0 else None) for n, t in self.engine.iter_hf_tensors()}
+        out = {"path": path, "num_tensors": len(tensors), "bytes": 0}
+        if self.rank == 0:
+            write_safetensors(path, tensors, {"format": "pt"})
+            out["bytes"] = sum(t.numel() * t.element_size() for t in tensors.values())
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier()
+        return out
+
+    def release_ipc_handles(self) -> int:
+        """Nothing to release: engines of one GPU share a process and hand weights over with a kernel, so no
+        inter-process memory handles are ever exported (the reference frees its CUDA-IPC handles here)."""
+        return 0
+
     def weight_norm(self) -> Dict[str, float]:
         return self.sampler.weight_norm() if self.sampler is not None else self.engine.weight_norm()
 

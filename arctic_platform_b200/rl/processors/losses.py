@@ -21,7 +21,8 @@ from typing import Any, Dict, Tuple
 import torch
 
 from ...common.registry import register_loss_fn
-from .functional import agg_loss, kl_penalty, masked_sum, ppo_clip_token_loss
+from .functional import (agg_loss, kl_penalty, m2po_mask, masked_sum, ppo_actor_loss_fn, ppo_clip_token_loss,
+                         resolve_proximal_logp, sapo_loss_fn)
 
 
 def _global_info(meta: dict) -> dict:
@@ -113,51 +114,86 @@ def verl_grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, d
 
 @register_loss_fn("grpo")
 def grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, device) -> Tuple[torch.Tensor, dict]:
-    """Decoupled PPO: the clip is taken against a proximal policy (``prox_log_probs``, defaulting to the
-    behaviour policy) and the behaviour mismatch enters as a capped importance weight."""
+    """Decoupled PPO for synchronous and asynchronous RL.
+
+    The clip is taken against a proximal policy and the behaviour mismatch enters as a capped importance weight.
+    Optional pieces, all off by default (config keys in brackets):
+
+    * proximal log-probs sent by the client (``prox_log_probs`` / ``prox_logp`` in the batch) or interpolated from
+      per-token ``versions`` and ``current_version`` without an extra forward pass [``prox_logp_method``:
+      ``recompute`` | ``loglinear`` | ``metrics``];
+    * M2PO second-moment masking of the most off-policy tokens [``m2_threshold``];
+    * SAPO soft gate instead of the hard clip [``use_sapo_loss``, ``sapo_tau_pos``, ``sapo_tau_neg``];
+    * token- or sequence-level importance ratios [``importance_sampling_level``];
+    * dual clip [``c_clip``], behaviour-importance cap [``behav_imp_weight_cap``], per-token correction weights
+      (``rollout_is_weights`` in the batch), entropy bonus [``entropy_coeff``], KL penalty to a reference policy
+      [``use_kl_loss`` or a non-zero ``kl_ctl``, ``kl_loss_coef``, ``kl_loss_type``], four aggregation modes
+      [``loss_agg_mode``]."""
     cfg = {**(meta.get("actor_config") or {}), **(config or {})}
     eps = float(cfg.get("eps_clip", cfg.get("clip_ratio", 0.2)))
-    eps_hi = float(cfg.get("eps_clip_higher", eps) or eps)
+    eps_hi = cfg.get("eps_clip_higher")
+    eps_hi = float(eps_hi) if eps_hi else None
     c_clip = cfg.get("c_clip")
     cap = cfg.get("behav_imp_weight_cap")
     agg_mode = cfg.get("loss_agg_mode", "token-mean")
+    level = cfg.get("importance_sampling_level", "token")
     packed, take, mask, seq_ids = _token_views(model_outputs, batch, device)
     info = _global_info(meta)
-    info.update(seq_ids=seq_ids, num_seqs=packed.batch_size)
+    seq_kw = {"seq_ids": seq_ids, "num_seqs": packed.batch_size}
     lp = model_outputs["logprobs"].float()
     old = take("old_log_probs")
+    if old is None:
+        old = lp.detach()                                  # strictly on-policy client: behaviour == current
     adv = take("advantages")
-    prox = take("prox_log_probs", old)
-    ratio = torch.exp(torch.clamp(lp - prox, -20, 20))
-    clipped_ratio = torch.clamp(ratio, 1 - eps, 1 + eps_hi)
-    l1, l2 = -adv * ratio, -adv * clipped_ratio
-    tok = torch.maximum(l1, l2)
-    clip_mask = l2 > l1
-    if c_clip is not None:
-        l3 = -adv * float(c_clip)
-        tok = torch.where(adv < 0, torch.minimum(l3, tok), tok)
-    behav_w = torch.exp(torch.clamp(prox - old, -20, 20))
-    if cap is not None:
-        keep = behav_w <= float(cap)
-        mask = mask & keep
-    tok = tok * behav_w.detach()
-    loss = agg_loss(tok, mask, agg_mode, **info)
+    prox_sent = take("prox_log_probs")
+    if prox_sent is None:
+        prox_sent = take("prox_logp")
+    versions = batch.get("versions")
+    if versions is not None:
+        versions = packed.gather_from_grid(versions.to(device))
+    prox = resolve_proximal_logp(prox_sent, cfg.get("prox_logp_method", "recompute"), old, lp.detach(), versions,
+                                 cfg.get("current_version"))
+    if cfg.get("m2_threshold") is not None:
+        mask = m2po_mask(old, prox, mask, float(cfg["m2_threshold"]))
+    if cfg.get("use_sapo_loss"):
+        if cfg.get("use_decoupled_loss"):
+            raise ValueError("SAPO is not compatible with use_decoupled_loss=True.")
+        loss, stat = sapo_loss_fn(lp, old, adv, float(cfg.get("sapo_tau_pos", 1.0)), float(cfg.get("sapo_tau_neg", 1.05)),
+                                  mask, level, **seq_kw)
+    else:
+        loss, stat = ppo_actor_loss_fn(lp, prox, old, adv, eps, mask, eps_clip_higher=eps_hi,
+                                       c_clip=float(c_clip) if c_clip is not None else None,
+                                       behav_imp_weight_cap=float(cap) if cap is not None else None,
+                                       importance_sampling_level=level, loss_agg_mode=agg_mode,
+                                       rollout_is_weights=take("rollout_is_weights"), **seq_kw, **info)
     ent_coef = float(cfg.get("entropy_coeff", 0.0) or 0.0)
     entropy = model_outputs.get("entropy")
     if entropy is not None and ent_coef:
-        loss = loss - ent_coef * agg_loss(entropy.float(), mask, agg_mode, **info)
-    kl_coef = float(cfg.get("kl_ctl", cfg.get("kl_loss_coef", 0.0)) or 0.0)
+        loss = loss - ent_coef * agg_loss(entropy.float().detach() if cfg.get("detach_entropy") else entropy.float(),
+                                          mask, agg_mode, **seq_kw, **info)
+    kl_coef = float(cfg.get("kl_ctl", 0.0) or 0.0) or (float(cfg.get("kl_loss_coef", 0.001)) if cfg.get("use_kl_loss") else 0.0)
     ref = take("ref_log_prob")
-    if kl_coef and ref is not None:
-        loss = loss + kl_coef * agg_loss(kl_penalty(lp, ref, cfg.get("kl_loss_type", "k3")), mask, agg_mode, **info)
+    if ref is None:
+        ref = take("ref_log_probs")
+    if kl_coef:
+        if ref is None:
+            raise ValueError("a KL penalty is configured but the batch has no ref_log_prob")
+        loss = loss + kl_coef * agg_loss(kl_penalty(lp, ref, cfg.get("kl_loss_type", "k3")), mask, agg_mode, **seq_kw, **info)
     mf = mask.float()
-    vals = torch.stack([mf.sum(), (tok * mf).sum(), (clip_mask.float() * mf).sum(),
-                        ((lp - old) * mf).sum(), (behav_w * mf).sum()]).detach().cpu().tolist()
+    behav = stat.get("behave_imp_weight")
+    vals = torch.stack([mf.sum(), (stat["loss"] * mf).sum(), (stat["clip_mask"].float() * mf).sum(),
+                        (stat["approx_kl"] * mf).sum(), (stat["importance_weight"] * mf).sum(),
+                        (behav * mf).sum() if behav is not None else mf.sum(),
+                        (stat["dual_clip_mask"].float() * mf).sum(),
+                        ((entropy.float().detach() if entropy is not None else -lp.detach()) * mf).sum()]).detach().cpu().tolist()
     n = vals[0]
     metrics = {"loss.sum": vals[1], "loss.tokens": n, "actor/pg_loss.sum": vals[1], "actor/pg_loss.tokens": n,
                "actor/pg_clipfrac.sum": vals[2], "actor/pg_clipfrac.tokens": n,
-               "actor/approx_kl.sum": -vals[3], "actor/approx_kl.tokens": n,
-               "actor/behav_imp_weight.sum": vals[4], "actor/behav_imp_weight.tokens": n}
+               "actor/approx_kl.sum": vals[3], "actor/approx_kl.tokens": n,
+               "actor/importance_weight.sum": vals[4], "actor/importance_weight.tokens": n,
+               "actor/behav_imp_weight.sum": vals[5], "actor/behav_imp_weight.tokens": n,
+               "actor/pg_clipfrac_lower.sum": vals[6], "actor/pg_clipfrac_lower.tokens": n,
+               "actor/entropy.sum": vals[7], "actor/entropy.tokens": n}
     return loss, metrics
 
 

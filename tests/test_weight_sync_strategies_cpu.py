@@ -64,3 +64,22 @@ def test_sync_pair_picks_by_flags(trainer):
     assert ws.sync_pair(src, dst)["strategy"] == "bulk"
     assert ws.sync_pair(src, dst, low_memory=True)["strategy"] == "low_mem"
     assert ws.sync_pair(src, dst, via_file=True)["strategy"] == "cpu_file"
+
+
+def test_worker_export_helpers(tmp_path):
+    from arctic_platform_b200.engine.worker import EngineWorker
+    from arctic_platform_b200.models.hf_io import read_safetensors
+    w = EngineWorker("cpu")
+    w.initialize({"model_name": "qwen3-tiny", "job_type": "training", "ds_config": {"zero_optimization": {"stage": 1}}})
+    sizes = {n: t.numel() * t.element_size() for n, t in w.engine.iter_hf_tensors()}
+    assert w.max_param_bytes() == max(sizes.values())
+    files = w.export_hf_checkpoint(str(tmp_path / "hf"))
+    assert files and (tmp_path / "hf" / "config.json").exists()
+    got = {}
+    for f in files:
+        got.update(dict(read_safetensors(tmp_path / "hf" / f)))
+    assert set(got) == set(w.get_parameter_names())
+    out = w.gather_and_save_state_dict(str(tmp_path / "w.safetensors"))
+    assert out["num_tensors"] == len(sizes) and out["bytes"] == sum(sizes.values())
+    assert set(dict(read_safetensors(tmp_path / "w.safetensors"))) == set(sizes)
+    assert w.release_ipc_handles() == 0
