@@ -49,7 +49,8 @@ def save_checkpoint(engine, save_dir: str, tag: Optional[str] = None, export_hf:
         if module is None:
             module = OrderedDict((n, t.detach().to("cpu").clone()) for n, t in engine.iter_hf_tensors())
         state = {
-            "module": module, "buffer_names": [], "optimizer": None,
+            "module": module, "buffer_names": [n for n, _b in engine.model.named_buffers()], "optimizer": None,
+            "buffers": OrderedDict((n, b.detach().to("cpu").clone()) for n, b in engine.model.named_buffers()),
             "param_shapes": [OrderedDict((n, t.shape) for n, t in module.items())],
             "frozen_param_shapes": None, "frozen_param_fragments": None, "shared_params": {},
             "lr_scheduler": {"type": engine.cfg.scheduler.type, "warmup_steps": engine.cfg.scheduler.warmup_steps,
@@ -138,6 +139,10 @@ def load_checkpoint(engine, load_dir: str, tag: Optional[str] = None) -> int:
     else:
         for name, t in state["module"].items():
             load_hf_tensor(engine.model, name, t)
+    bufs = dict(engine.model.named_buffers())
+    for name, t in (state.get("buffers") or {}).items():       # e.g. the routers' load-balancing bias
+        if name in bufs:
+            bufs[name].copy_(t.to(bufs[name].device))
     engine.global_steps = int(state.get("global_steps", 0))
     engine.micro_steps = int(state.get("micro_steps", 0))
     if not engine.forward_only:

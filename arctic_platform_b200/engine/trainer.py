@@ -56,6 +56,7 @@ class EngineConfig:
     scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
     impl: str = "fused"             # fused | collective
     offload_optimizer: bool = False
+    moe_bias_update_rate: float = 1e-3  # step of the routers' load-balancing bias (models that have one)
     adam_w_mode: bool = True           # False: classic Adam, weight decay added to the gradient (L2) instead of decoupled
     gradient_checkpointing: bool = False
 
@@ -370,6 +371,12 @@ class TrainEngine:
         self.global_steps += 1
         self.zero_grad()
         self.last_lr = lr
+        if getattr(self.model.cfg, "moe_expert_bias", False):
+            # aux-loss-free load balancing: one nudge of every router's selection bias per optimizer step, from the
+            # expert loads of all data-parallel ranks
+            for mod in self.model.modules():
+                if getattr(mod, "expert_bias", None) is not None:
+                    mod.update_expert_bias(self.cfg.moe_bias_update_rate, group=self.group if self.world > 1 else False)
         return {"last_lr": lr, "grad_norm": self._grad_norm_tensor}
 
     def grad_norm_value(self) -> float:

@@ -99,7 +99,10 @@ class EngineWorker:
         else:
             ecfg = EngineConfig.from_ds_config(job_config.get("ds_config"), job_config.get("training_config"))
             wc = job_config.get("ds_worker_config") or {}
-            ecfg.gradient_checkpointing = bool(wc.get("gradient_checkpointing", False))
+            gc_cfg = wc.get("gradient_checkpointing", False)
+            ecfg.gradient_checkpointing = bool(gc_cfg.get("enable", True)) if isinstance(gc_cfg, dict) else bool(gc_cfg)
+            if isinstance(gc_cfg, dict) and gc_cfg.get("mode", "full") == "selective":
+                m.checkpoint_targets = tuple(gc_cfg.get("targets") or ("mlp", "routed_experts", "linear_attn"))
             from ..models.factory import _tiled_mlp_setting
             shards = _tiled_mlp_setting(wc.get("tiled_mlp"))
             for blk in m.blocks:

@@ -34,6 +34,11 @@ class DecoderConfig:
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    moe_score_func: str = "softmax"              # router scores: softmax over experts, or independent sigmoids
+    moe_route_scale: float = 1.0                 # factor on the kept routing weights
+    moe_expert_bias: bool = False                # selection bias per expert, nudged toward equal load (no aux loss)
+    moe_n_group: int = 1                         # group-limited routing: experts in n groups,
+    moe_topk_group: int = 1                      # ... only the best topk_group groups are eligible per token
     shared_expert_intermediate_size: int = 0     # > 0: a dense SwiGLU expert with a sigmoid gate beside the routed ones
     # hybrid (Qwen3.5 / Qwen3-Next) features; the defaults describe plain Qwen3
     layer_types: Optional[tuple] = None          # per layer "full_attention" | "linear_attention"
@@ -117,6 +122,10 @@ class DecoderConfig:
             num_experts=d.get("num_experts", 0) or 0, num_experts_per_tok=d.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=d.get("moe_intermediate_size", 0) or 0,
             norm_topk_prob=bool(d.get("norm_topk_prob", True)),
+            moe_score_func=d.get("scoring_func", d.get("score_func", "softmax")) or "softmax",
+            moe_route_scale=float(d.get("routed_scaling_factor", d.get("route_scale", 1.0)) or 1.0),
+            moe_expert_bias=bool(d.get("moe_expert_bias", d.get("load_balance_coeff") is not None)),
+            moe_n_group=int(d.get("n_group", 1) or 1), moe_topk_group=int(d.get("topk_group", 1) or 1),
             shared_expert_intermediate_size=d.get("shared_expert_intermediate_size", 0) or 0,
             layer_types=_hybrid_layer_types(d), partial_rotary_factor=float(d.get("partial_rotary_factor", 1.0)),
             attn_output_gate=hybrid, norm_one_plus=hybrid,

@@ -108,6 +108,7 @@ class DecoderBlock(nn.Module):
             self.wo = mk(H, cfg.q_size)
         self.kv_capture = None           # a sampler's prefill sets a list; forward appends this layer's (k, v)
         self.tiled_mlp_shards = 0        # > 1 or "auto": the dense MLP runs over row tiles (activation memory)
+        self.ac_targets: Tuple[str, ...] = ()   # parts of this block under selective activation checkpointing
         self.ln2 = mk(H)
         if cfg.is_moe:
             from .moe import MoEFeedForward
@@ -124,7 +125,7 @@ class DecoderBlock(nn.Module):
         cfg = self.cfg
         h, stream = norm.rmsnorm(x, self.ln1, cfg.rms_norm_eps, stream, self.w_offset)
         if self.linear_attn is not None:
-            o = self.linear_attn(h, layout)
+            o = self._part("linear_attn", self.linear_attn, h, layout)
         else:
             qkv = gemm.linear(h, self.wqkv)
             if cfg.rotary_dim != cfg.head_dim or self.w_offset:
@@ -145,16 +146,27 @@ class DecoderBlock(nn.Module):
             o = gemm.linear(a, self.wo)
         h2, stream = norm.rmsnorm(o, self.ln2, cfg.rms_norm_eps, stream, self.w_offset)
         if self.mlp is not None:
-            d = self.mlp(h2)
+            d = self._part("routed_experts" if "routed_experts" in self.ac_targets else "mlp", self.mlp, h2)
         elif self.tiled_mlp_shards:
             from .tiled_mlp import tiled_mlp
             d = tiled_mlp(h2, self._dense_mlp, self.tiled_mlp_shards, (self.wgu, self.wdown))
         else:
-            d = self._dense_mlp(h2)
+            d = self._part("mlp", self._dense_mlp, h2)
         return d, stream
 
     def _dense_mlp(self, h: torch.Tensor) -> torch.Tensor:
         return gemm.linear(gate_up_act(h, self.wgu), self.wdown)
+
+    def _part(self, target: str, fn, *args):
+        """Runs one part of the block, under activation checkpointing when selective checkpointing names it."""
+        if target not in self.ac_targets or not torch.is_grad_enabled():
+            return fn(*args)
+        from torch.utils.checkpoint import checkpoint
+        if self.mlp is not None and fn is self.mlp:
+            from .moe import router_replay_scope
+            ctx = lambda: (router_replay_scope(self, "capture"), router_replay_scope(self, "replay"))
+            return checkpoint(fn, *args, use_reentrant=False, context_fn=ctx)
+        return checkpoint(fn, *args, use_reentrant=False)
 
 
 class DecoderLM(nn.Module):
@@ -170,6 +182,9 @@ class DecoderLM(nn.Module):
         self._rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
         self._rope_len = max_positions or min(cfg.max_position_embeddings, 40960)
         self.gradient_checkpointing = False
+        # selective checkpointing: only these parts of every block are recomputed ("mlp", "routed_experts",
+        # "linear_attn", "attn_proj"); empty = whole blocks
+        self.checkpoint_targets: Tuple[str, ...] = ()
 
     # ------------------------------------------------------------------ init
     @torch.no_grad()
@@ -212,10 +227,18 @@ class DecoderLM(nn.Module):
         rope = self.rope(x.device)
         positions = positions.to(torch.int32) if x.is_cuda else positions
         stream = None
+        targets = tuple(self.checkpoint_targets) if self.gradient_checkpointing else ()
         for blk in self.blocks:
-            if self.gradient_checkpointing and torch.is_grad_enabled():
+            blk.ac_targets = targets
+            if self.gradient_checkpointing and torch.is_grad_enabled() and not self.checkpoint_targets:
                 from torch.utils.checkpoint import checkpoint
-                x, stream = checkpoint(blk, x, stream, positions, layout, rope, use_reentrant=False)
+                if blk.mlp is not None:
+                    # the recompute replays the routing of the original pass (same expert counts, same shapes)
+                    from .moe import router_replay_scope
+                    ctx = lambda b=blk: (router_replay_scope(b, "capture"), router_replay_scope(b, "replay"))
+                    x, stream = checkpoint(blk, x, stream, positions, layout, rope, use_reentrant=False, context_fn=ctx)
+                else:
+                    x, stream = checkpoint(blk, x, stream, positions, layout, rope, use_reentrant=False)
             else:
                 x, stream = blk(x, stream, positions, layout, rope)
         h, _ = norm.rmsnorm(x, self.final_norm, self.cfg.rms_norm_eps, stream, 1.0 if self.cfg.norm_one_plus else 0.0)

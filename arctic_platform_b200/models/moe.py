@@ -22,12 +22,48 @@ from ..ops import gemm
 from .config import DecoderConfig
 
 
-def route_topk(logits: torch.Tensor, k: int, renorm: bool) -> Tuple[torch.Tensor, torch.Tensor]:
-    """fp32 softmax + top-k.  Returns ``(weights [T,k] fp32, experts [T,k] int64)``."""
-    probs = torch.softmax(logits.float(), dim=-1)
-    w, idx = torch.topk(probs, k, dim=-1)
+def route_topk(logits: torch.Tensor, k: int, renorm: bool, score_func: str = "softmax", route_scale: float = 1.0,
+               expert_bias: Optional[torch.Tensor] = None, routed_experts: Optional[torch.Tensor] = None,
+               n_group: int = 1, topk_group: int = 1) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Token-choice routing in fp32.  Returns ``(weights [T, k] fp32, experts [T, k] int64)``.
+
+    * ``score_func``: softmax over the experts or independent sigmoids;
+    * ``expert_bias [E]`` shifts the scores for the SELECTION only, the weights are the unbiased scores
+      (aux-loss-free load balancing);
+    * ``n_group`` / ``topk_group``: group-limited routing -- a token may only pick experts from its ``topk_group``
+      best groups (a group's quality is the sum of its two best biased scores);
+    * ``routed_experts [T, k]`` replays a decision taken elsewhere (an earlier pass over the same tokens, an
+      inference engine): the weights are gathered from the current scores, nothing is re-selected.
+    (arctic_platform/model/implementations/qwen35/models/layers/moe.py:196-269, NemotronHRouter in the same file)."""
+    x = logits.float()
+    if score_func == "softmax":
+        scores = torch.softmax(x, dim=-1)
+    elif score_func == "sigmoid":
+        scores = torch.sigmoid(x)
+    else:
+        raise NotImplementedError(f"Unknown score function {score_func}")
+    # The decision is taken without autograd and the weights are ALWAYS a gather from the scores: a fresh decision
+    # and a replayed one then build the same graph (same saved tensors), which activation checkpointing checks.
+    if routed_experts is not None:
+        if routed_experts.shape[-1] != k:
+            raise ValueError(f"routed_experts has {routed_experts.shape[-1]} experts per token, the router keeps {k}")
+        idx = routed_experts.to(torch.int64)
+    else:
+        with torch.no_grad():
+            pick = scores if expert_bias is None else scores + expert_bias.float()
+            if n_group > 1:
+                T, E = pick.shape
+                grouped = pick.view(T, n_group, E // n_group)
+                quality = grouped.topk(min(2, E // n_group), dim=-1).values.sum(-1)        # [T, n_group]
+                best = quality.topk(topk_group, dim=-1).indices
+                allowed = torch.zeros_like(quality, dtype=torch.bool).scatter_(1, best, True)
+                pick = grouped.masked_fill(~allowed[:, :, None], float("-inf")).view(T, E)
+            idx = torch.topk(pick, k, dim=-1).indices
+    w = scores.gather(-1, idx)
     if renorm:
-        w = w / w.sum(-1, keepdim=True)
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    if route_scale != 1.0:
+        w = w * route_scale
     return w, idx
 
 
@@ -137,6 +173,17 @@ class MoEFeedForward(nn.Module):
             self.shared_wgu = self.shared_wdown = self.shared_gate = None
         self.ep = None  # set by parallel.expert_parallel.attach() when experts are sharded over ranks
         self.last_tokens_per_expert: Optional[torch.Tensor] = None
+        # aux-loss-free load balancing: a selection bias per expert and the load seen since the last update
+        if cfg.moe_expert_bias:
+            self.register_buffer("expert_bias", torch.zeros(E, device=device, dtype=torch.float32), persistent=True)
+            self.register_buffer("tokens_per_expert", torch.zeros(E, device=device, dtype=torch.float32), persistent=False)
+        else:
+            self.expert_bias = self.tokens_per_expert = None
+        # routing replay: "capture" stores every pass's decision, "replay" consumes them in the same order (the
+        # recompute of an activation-checkpointed block); ``routed_experts`` forces one decision from outside
+        self.replay_mode: Optional[str] = None
+        self._captured: list = []
+        self.routed_experts: Optional[torch.Tensor] = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = self._routed(x)
@@ -151,7 +198,15 @@ class MoEFeedForward(nn.Module):
         cfg = self.cfg
         T, H = x.shape
         logits = gemm.linear(x, self.router)
-        w, idx = route_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
+        forced = self.routed_experts
+        if forced is None and self.replay_mode == "replay" and self._captured:
+            forced = self._captured.pop(0)
+        w, idx = route_topk(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob, cfg.moe_score_func, cfg.moe_route_scale,
+                            self.expert_bias, forced, cfg.moe_n_group, cfg.moe_topk_group)
+        if self.replay_mode == "capture":
+            self._captured.append(idx.detach())
+        if self.tokens_per_expert is not None and self.training and self.replay_mode != "replay":
+            self.tokens_per_expert += torch.bincount(idx.reshape(-1), minlength=cfg.num_experts).to(self.tokens_per_expert.dtype)
         if self.ep is not None:
             return self.ep.forward(self, x, w, idx)
         k = cfg.num_experts_per_tok
@@ -166,3 +221,42 @@ class MoEFeedForward(nn.Module):
         out = torch.zeros((T, H), device=x.device, dtype=torch.float32 if x.is_cuda else x.dtype)
         out.index_add_(0, src_tok, (ys * wflat[:, None]).to(out.dtype))
         return out.to(x.dtype)
+
+
+    @torch.no_grad()
+    def update_expert_bias(self, coeff: float = 1e-3, group=None) -> Optional[torch.Tensor]:
+        """Moves every expert's selection bias by ``coeff`` toward the mean load (up for starved experts, down for
+        crowded ones) from the token counts accumulated since the last call -- summed over ``group`` when the data
+        is sharded -- and clears the counts.  Call once per optimizer step."""
+        if self.expert_bias is None:
+            return None
+        load = self.tokens_per_expert.clone()
+        if group is not False and torch.distributed.is_initialized() and torch.distributed.get_world_size(group) > 1:
+            torch.distributed.all_reduce(load, group=group)
+        self.expert_bias += coeff * torch.sign(load.mean() - load)
+        self.expert_bias -= self.expert_bias.mean()
+        self.tokens_per_expert.zero_()
+        return load
+
+
+class router_replay_scope:
+    """Context for one pass over a block: ``capture`` on the original forward, ``replay`` on the recompute, so that
+    both passes route identically and every tensor inside the checkpointed region keeps its shape even when the
+    router's scores differ in the last bits (arctic_platform/model/implementations/qwen35/gpu/
+    router_replay_recompute.py:1-124 patches the checkpoint machinery for the same effect)."""
+
+    def __init__(self, block: nn.Module, mode: str):
+        self.moes = [m for m in block.modules() if isinstance(m, MoEFeedForward)]
+        self.mode = mode
+
+    def __enter__(self):
+        for m in self.moes:
+            m.replay_mode = self.mode
+        return self
+
+    def __exit__(self, *exc):
+        for m in self.moes:
+            m.replay_mode = None
+            if self.mode == "replay":
+                m._captured.clear()
+        return False
