@@ -116,3 +116,49 @@ def responses_in_orig_sample_order(values: torch.Tensor, pb: PackedBatch) -> Lis
     """Splits per-token values into one tensor per sample (original order; empty for samples without a response)."""
     counts = torch.bincount(torch.div(pb.out_index, pb.response_length, rounding_mode="floor"), minlength=pb.batch_size)
     return list(torch.split(values, counts.tolist()))
+
+
+def get_group_token_layout(pb: PackedBatch) -> List[dict]:
+    """Token layout of the deduplicated axis, group by group: ``{"group_idx", "sample_indices", "prompt_start",
+    "prompt_tokens", "response_starts", "response_tokens"}``.  A group is one prompt segment followed by the
+    response segments that attend to it; ``sample_indices`` are the original batch rows of those responses in the
+    order they are laid out (arctic_platform/rl/zorro_train/zorro_train.py:2413-2436)."""
+    segs = [tuple(int(v) for v in s[:4]) for s in pb.layout.segs.tolist()]
+    members: dict = {}
+    for b, g in enumerate(np.asarray(pb.group_of).tolist()):
+        members.setdefault(int(g), []).append(b)
+    out: List[dict] = []
+    by_prompt_start: dict = {}
+    for q_start, q_len, p_start, p_len in segs:
+        if p_len == 0:                                   # a segment without a shared prefix opens a group
+            by_prompt_start[q_start] = len(out)
+            out.append({"group_idx": len(out), "sample_indices": [], "prompt_start": q_start, "prompt_tokens": q_len,
+                        "response_starts": [], "response_tokens": []})
+        else:
+            g = out[by_prompt_start[p_start]]
+            g["response_starts"].append(q_start)
+            g["response_tokens"].append(q_len)
+    for g in out:
+        samples = members.get(g["group_idx"], [])
+        # rows whose response is empty have no segment; the others appear in ascending batch order
+        present = [b for b in samples if pb.sample_tokens[b] > g["prompt_tokens"]] if g["response_tokens"] else []
+        g["sample_indices"] = present if len(present) == len(g["response_tokens"]) else samples[:len(g["response_tokens"])]
+    return out
+
+
+def split_deduplicated_hidden_by_group(dedup_hidden: torch.Tensor, pb: PackedBatch) -> List[dict]:
+    """Per-group views of a ``[T_dedup, ...]`` tensor: ``{"group_idx", "sample_indices", "prompt_hidden",
+    "response_hiddens"}`` -- what a recurrent (linear-attention) layer needs to run each prompt once and every
+    response from the prompt's final state (arctic_platform/rl/zorro_train/zorro_train.py:2438-2464)."""
+    if dedup_hidden.shape[0] != pb.total_tokens:
+        raise ValueError(f"expected {pb.total_tokens} rows on the deduplicated axis, got {dedup_hidden.shape[0]}")
+    groups, used = [], 0
+    for g in get_group_token_layout(pb):
+        ps, pl = g["prompt_start"], g["prompt_tokens"]
+        resp = [dedup_hidden[s:s + n] for s, n in zip(g["response_starts"], g["response_tokens"])]
+        groups.append({"group_idx": g["group_idx"], "sample_indices": g["sample_indices"],
+                       "prompt_hidden": dedup_hidden[ps:ps + pl], "response_hiddens": resp})
+        used += pl + sum(g["response_tokens"])
+    if used != pb.total_tokens:
+        raise AssertionError(f"group split covered {used} tokens, expected {pb.total_tokens}")
+    return groups

@@ -196,3 +196,36 @@ def rearrange_micro_batches_with_dedup(batch: Dict[str, torch.Tensor], response_
                     for k, v in batch.items()})
         idx_lists.append(rows)
     return mbs, idx_lists
+
+
+def reorg_global_batch_verl(super_batch, response_length: int, world_size: int, max_token_len: Optional[int] = None,
+                            max_group_length_threshold: Optional[int] = None):
+    """The balancer for a verl-style super-batch object (``.batch``: tensors keyed by name, ``.non_tensor_batch``:
+    numpy arrays with the same leading dimension): rows are permuted so that contiguous ``B / world_size`` blocks
+    hold whole prompt groups of balanced cost.  The object is reordered in place when it offers ``reorder(indices)``,
+    else its two dicts are re-indexed; it is returned either way, untouched when there is nothing to balance
+    (arctic_platform/rl/zorro_train/seqlen_balancing.py:489-600)."""
+    batch = super_batch.batch
+    ids = batch["input_ids"]
+    B = ids.shape[0]
+    if B <= world_size:
+        return super_batch
+    view = {k: batch[k] for k in ("input_ids", "attention_mask", "response_mask", "responses") if k in batch.keys()}
+    meta = {"response_length": response_length, "max_rollouts": max_group_length_threshold}
+    _, order = reorg_global_batch(view, meta, world_size)
+    if torch.equal(order, torch.arange(B)):
+        return super_batch
+    if hasattr(super_batch, "reorder"):
+        super_batch.reorder(order)
+        return super_batch
+    for k in list(batch.keys()):
+        v = batch[k]
+        if torch.is_tensor(v) and v.dim() > 0 and v.shape[0] == B:
+            batch[k] = v[order]
+    non_tensor = getattr(super_batch, "non_tensor_batch", None) or {}
+    idx = order.numpy()
+    for k in list(non_tensor.keys()):
+        v = non_tensor[k]
+        if hasattr(v, "__len__") and len(v) == B:
+            non_tensor[k] = v[idx] if isinstance(v, np.ndarray) else [v[i] for i in idx]
+    return super_batch

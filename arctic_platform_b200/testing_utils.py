@@ -145,9 +145,19 @@ def reserve_free_port(host: str = "127.0.0.1") -> int:
         return s.getsockname()[1]
 
 
+def gpu_partitioning_active() -> bool:
+    """True when the test session gave every parallel test worker its own disjoint slice of the GPUs
+    (``ARL_GPU_PARTITIONED=1``); the host-wide serial lock is then unnecessary."""
+    return os.environ.get("ARL_GPU_PARTITIONED") == "1"
+
+
 @contextlib.contextmanager
 def gpu_serial_lock(name: str = "apb-gpu-serial") -> Iterator[None]:
-    """Cross-process exclusive lock (flock) for tests that must not share the GPU with one another."""
+    """Cross-process exclusive lock (flock) for tests that must not share the GPU with one another; a no-op when
+    the workers' GPUs are partitioned."""
+    if gpu_partitioning_active():
+        yield
+        return
     path = Path(tempfile.gettempdir()) / f"{name}.lock"
     with open(path, "w") as fh:
         fcntl.flock(fh, fcntl.LOCK_EX)
@@ -173,3 +183,65 @@ class TestCasePlus(unittest.TestCase):
         for d in self._tmp:
             d.cleanup()
         super().tearDown()
+
+
+def make_tied_lm_head_model(hidden_size: int, vocab_size: int, device: str = "cpu", dtype=torch.float32, seed: int = 0):
+    """The smallest object the log-prob primitives accept as a model: ``.output_weight [vocab, hidden]`` (also
+    reachable as ``.lm_head.weight`` and, tied, ``.embed``) and ``.config.vocab_size``."""
+    from types import SimpleNamespace
+    g = torch.Generator().manual_seed(seed)
+    w = torch.nn.Parameter((torch.randn(vocab_size, hidden_size, generator=g) * hidden_size ** -0.5).to(device, dtype))
+    return SimpleNamespace(output_weight=w, embed=w, lm_head=SimpleNamespace(weight=w),
+                           config=SimpleNamespace(vocab_size=vocab_size, hidden_size=hidden_size))
+
+
+class RunOutput:
+    def __init__(self, returncode: int, stdout, stderr):
+        self.returncode, self.stdout, self.stderr = returncode, stdout, stderr
+
+
+async def _stream_subprocess(cmd, env, stdin, timeout, quiet, echo) -> RunOutput:
+    import asyncio
+    if echo:
+        print("\nRunning:", " ".join(cmd))
+    proc = await asyncio.create_subprocess_exec(cmd[0], *cmd[1:], stdin=stdin, stdout=asyncio.subprocess.PIPE,
+                                                stderr=asyncio.subprocess.PIPE, env=env)
+    out, err = [], []
+
+    async def pump(stream, sink, label, target):
+        while True:
+            line = await stream.readline()
+            if not line:
+                return
+            text = line.decode("utf-8", "replace").rstrip()
+            sink.append(text)
+            if not quiet:
+                print(label, text, file=target)
+
+    pumps = asyncio.gather(pump(proc.stdout, out, "stdout:", sys.stdout), pump(proc.stderr, err, "stderr:", sys.stderr))
+    try:
+        await asyncio.wait_for(asyncio.gather(pumps, proc.wait()), timeout=timeout)
+    except asyncio.TimeoutError:
+        proc.kill()                      # the exact child started above
+        await proc.wait()
+        raise RuntimeError(f"'{' '.join(cmd)}' did not finish within {timeout}s") from None
+    return RunOutput(proc.returncode, out, err)
+
+
+def execute_subprocess_async(cmd, env=None, stdin=None, timeout: float = 180, quiet: bool = False, echo: bool = True
+                             ) -> RunOutput:
+    """Runs ``cmd`` (a list), streaming its output line by line while capturing it.  Raises when the command fails,
+    runs past ``timeout`` or prints nothing at all (a test that delegates its checks to the child must have seen
+    the child say something)."""
+    import asyncio
+    loop = asyncio.new_event_loop()          # never the ambient loop: an earlier async test may have closed it
+    try:
+        result = loop.run_until_complete(_stream_subprocess(list(cmd), env, stdin, timeout, quiet, echo))
+    finally:
+        loop.close()
+    if result.returncode != 0:
+        raise RuntimeError(f"'{' '.join(cmd)}' failed with returncode {result.returncode}\n\n"
+                           "stderr of the child:\n" + "\n".join(result.stderr))
+    if not result.stdout and not result.stderr:
+        raise RuntimeError(f"'{' '.join(cmd)}' produced no output.")
+    return result

@@ -97,3 +97,68 @@ def test_stats_tracker_scopes_and_reduce_types():
         tr.stat("missing", x=torch.zeros(1))
     with pytest.raises(ValueError):
         tr.denominator(bad=torch.ones(2))
+
+
+def test_group_token_layout_and_split_by_group():
+    import torch
+    from arctic_platform_b200.rl.zorro_train.layout import build_packed_batch
+    from arctic_platform_b200.rl.zorro_train.reconstruct import get_group_token_layout, split_deduplicated_hidden_by_group
+    from tests.test_zorro_equivalence_cpu import make_grpo_batch
+    ids, mask, R = make_grpo_batch(n_prompts=3, n_samples=3, seed=9)
+    pb = build_packed_batch(ids, mask, R, dedup=True)
+    layout = get_group_token_layout(pb)
+    assert len(layout) == pb.num_groups == 3
+    assert sum(g["prompt_tokens"] + sum(g["response_tokens"]) for g in layout) == pb.total_tokens
+    assert sorted(b for g in layout for b in g["sample_indices"]) == list(range(ids.shape[0]))
+    P = ids.shape[1] - R
+    parts = split_deduplicated_hidden_by_group(pb.input_ids, pb)
+    for g in parts:
+        first = g["sample_indices"][0]
+        assert g["prompt_hidden"].tolist() == ids[first, :P][mask[first, :P].bool()].tolist()
+        for b, resp in zip(g["sample_indices"], g["response_hiddens"]):
+            assert resp.tolist() == ids[b, P:][mask[b, P:].bool()].tolist()      # the right sample's own tokens
+    hid = torch.randn(pb.total_tokens, 4)
+    parts = split_deduplicated_hidden_by_group(hid, pb)
+    assert parts[0]["prompt_hidden"].data_ptr() == hid[layout[0]["prompt_start"]:].data_ptr()      # views, not copies
+    import pytest
+    with pytest.raises(ValueError):
+        split_deduplicated_hidden_by_group(hid[:-1], pb)
+
+
+def test_reorg_global_batch_for_a_verl_style_super_batch():
+    import numpy as np
+    import torch
+    from arctic_platform_b200.rl.zorro_train.seqlen_balancing import reorg_global_batch_verl
+    from tests.test_zorro_equivalence_cpu import make_grpo_batch
+    ids, mask, R = make_grpo_batch(n_prompts=4, n_samples=2, seed=12, p_rng=(4, 40), r_rng=(2, 30))
+    B = ids.shape[0]
+    perm = torch.randperm(B, generator=torch.Generator().manual_seed(0))       # groups scattered over the batch
+
+    class Super:
+        def __init__(self):
+            self.batch = {"input_ids": ids[perm].clone(), "attention_mask": mask[perm].clone(),
+                          "tag": torch.arange(B)}
+            self.non_tensor_batch = {"uid": np.arange(B), "names": [f"s{i}" for i in range(B)]}
+    sb = Super()
+    out = reorg_global_batch_verl(sb, R, world_size=2)
+    assert out is sb
+    order = sb.batch["tag"]
+    assert sorted(order.tolist()) == list(range(B))
+    assert torch.equal(sb.batch["input_ids"], ids[perm][order]) and sb.non_tensor_batch["uid"].tolist() == order.tolist()
+    assert sb.non_tensor_batch["names"] == [f"s{i}" for i in order.tolist()]
+    # every prompt group now sits inside one rank's half
+    P = ids.shape[1] - R
+    for half in (sb.batch["input_ids"][:B // 2], sb.batch["input_ids"][B // 2:]):
+        prompts = {tuple(r[:P].tolist()) for r in half}
+        assert len(prompts) == 2
+    tiny = Super()
+    tiny.batch = {k: v[:2] for k, v in tiny.batch.items()}
+    before = tiny.batch["tag"].clone()
+    assert reorg_global_batch_verl(tiny, R, world_size=2) is tiny and torch.equal(tiny.batch["tag"], before)
+
+    class Reorderable(Super):
+        def reorder(self, indices):
+            self.seen = indices
+    r = Reorderable()
+    reorg_global_batch_verl(r, R, world_size=2)
+    assert sorted(r.seen.tolist()) == list(range(B))

@@ -120,3 +120,29 @@ def test_env_gated_diagnostics(monkeypatch, capsys):
     assert "NCCL_TOPO_FILE" not in os.environ
     monkeypatch.setenv("NCCL_TOPO_FILE", "/etc/nccl/topo.xml")
     assert debug.drop_stale_nccl_topo_file() is None and os.environ["NCCL_TOPO_FILE"] == "/etc/nccl/topo.xml"
+
+
+def test_subprocess_runner_and_small_helpers(monkeypatch):
+    import sys
+    import pytest
+    import torch
+    from arctic_platform_b200 import testing_utils as tu
+    r = tu.execute_subprocess_async([sys.executable, "-c", "import sys; print('hello'); print('warn', file=sys.stderr)"],
+                                    quiet=True, echo=False)
+    assert r.returncode == 0 and r.stdout == ["hello"] and r.stderr == ["warn"]
+    with pytest.raises(RuntimeError, match="returncode 3"):
+        tu.execute_subprocess_async([sys.executable, "-c", "import sys; print('x'); sys.exit(3)"], quiet=True, echo=False)
+    with pytest.raises(RuntimeError, match="no output"):
+        tu.execute_subprocess_async([sys.executable, "-c", "pass"], quiet=True, echo=False)
+    with pytest.raises(RuntimeError, match="did not finish"):
+        tu.execute_subprocess_async([sys.executable, "-c", "import time; time.sleep(30)"], timeout=1, quiet=True, echo=False)
+    m = tu.make_tied_lm_head_model(16, 50)
+    assert m.output_weight.shape == (50, 16) and m.lm_head.weight is m.embed and m.config.vocab_size == 50
+    monkeypatch.setenv("ARL_GPU_PARTITIONED", "1")
+    assert tu.gpu_partitioning_active()
+    with tu.gpu_serial_lock():
+        pass
+    monkeypatch.delenv("ARL_GPU_PARTITIONED")
+    assert not tu.gpu_partitioning_active()
+    with tu.gpu_serial_lock("apb-test-lock"):
+        pass
