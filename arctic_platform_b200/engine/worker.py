@@ -79,6 +79,11 @@ class EngineWorker:
         if self.job_type == "sampling":
             from .sampler import SamplerEngine
             vc = dict(job_config.get("vllm_config") or {})
+            if int(vc.get("tensor_parallel_size", 1) or 1) > 1:
+                import logging
+                logging.getLogger(__name__).warning(
+                    "tensor_parallel_size=%s: this sampler runs one full replica per GPU; the value is ignored",
+                    vc["tensor_parallel_size"])
             m = model if model is not None else self._load_model(job_config, dtype, seed)
             if self.model_cfg.layer_types is not None:
                 # hybrid family: recurrent state + sparse K/V layers, served by the stateful tensor-op engine
