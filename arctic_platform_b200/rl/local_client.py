@@ -40,12 +40,17 @@ class ArcticRLLocalClient:
     def __init__(self, config: ArcticRLClientConfig, server: Optional[ArcticRLServerCore] = None):
         self.config = config
         self.server = server or ArcticRLServerCore(colocate=config.colocate)
-        self.spmd_world = dist.get_world_size() if dist.is_initialized() else 1
         self.job_ids: Dict[str, Optional[int]] = {"training": config.training_job_id,
                                                   "sampling": config.sampling_job_id,
                                                   "log_prob": config.log_prob_job_id}
         if config.training_job_id is None:
             self._initialize_jobs()
+
+    @property
+    def spmd_world(self) -> int:
+        """Ranks of the SPMD job this client is one rank of.  Read when needed: the process group may be created by
+        the caller before the client exists, or by the first engine during job initialisation."""
+        return dist.get_world_size() if dist.is_initialized() else 1
 
     def _initialize_jobs(self) -> None:
         counts = {"training": self.config.training_gpus, "sampling": self.config.sampling_gpus,
