@@ -183,6 +183,7 @@ class EngineWorker:
         else:
             n_mb = int((meta or {}).get("num_micro_batches", 1) or 1)
             mbs = split_microbatches(batch, n_mb)
+        meta = self._with_sft_global_tokens(mbs, meta, processing)
         per_mb, outs = [], []
         for i, mb in enumerate(mbs):
             if isinstance(mb, dict):
@@ -200,6 +201,25 @@ class EngineWorker:
             from ..utils.debug import maybe_log_moe_imbalance
             maybe_log_moe_imbalance(self.rank)
         return result
+
+    def _with_sft_global_tokens(self, mbs, meta, processing):
+        """Cross-entropy losses normalised by the GLOBAL token count need that count before the first micro-batch
+        runs: loss tokens of all this rank's micro-batches, summed over the data-parallel ranks (one all-reduce of
+        an int64), plus ``dp_size``.  A client that sends ``batch_num_tokens`` itself is left alone
+        (arctic_platform/common/deepspeed_worker.py:404-441 does the same before its SFT pipeline)."""
+        from ..sft.processor import SFT_GLOBAL_TOKEN_LOSS_FNS, count_loss_tokens
+        if (processing or {}).get("loss_fn") not in SFT_GLOBAL_TOKEN_LOSS_FNS or "batch_num_tokens" in (meta or {}):
+            return meta
+        import torch.distributed as dist
+        meta = dict(meta or {})
+        n = torch.tensor([sum(count_loss_tokens(mb) for mb in mbs if isinstance(mb, dict))], dtype=torch.int64)
+        group = getattr(self.engine, "group", None)
+        if dist.is_initialized() and self.engine.world > 1:
+            n = n.to(self.device if dist.get_backend(group) == "nccl" else "cpu")
+            dist.all_reduce(n, group=group)
+            meta.setdefault("dp_size", self.engine.world)
+        meta["batch_num_tokens"] = float(n.item())
+        return meta
 
     def forward_backward(self, batch, meta=None, processing=None) -> Dict[str, Any]:
         return self._forward_maybe_backward(batch, meta, processing, backward=True)

@@ -62,6 +62,13 @@ def pack_for_model(batch: dict, meta: dict, sft: bool) -> PackedBatch:
     if mask is None:
         mask = torch.ones_like(ids)
     if sft:
+        cu = batch.get("cu_seqlens")
+        pos = batch.get("position_ids")
+        prepacked = ids.dim() == 2 and ids.shape[0] == 1 and (
+            cu is not None or (torch.is_tensor(pos) and pos.numel() == ids.numel() and bool((pos.reshape(-1)[1:] == 0).any())))
+        if prepacked:
+            from ..zorro_train.layout import build_prepacked
+            return build_prepacked(ids, pos, cu)              # the client packed several documents into one row
         return build_plain_packed(ids, mask)
     return build_packed_batch(ids, mask, response_length_of(batch, meta),
                               dedup=bool(meta.get("zorro_train_enable", True)))

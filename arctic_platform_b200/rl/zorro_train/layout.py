@@ -210,3 +210,49 @@ def build_plain_packed(input_ids: torch.Tensor, attention_mask: torch.Tensor) ->
         pred_index=torch.from_numpy(cat(pred)), labels=torch.from_numpy(cat(labels)),
         out_index=torch.from_numpy(cat(out_idx)), batch_size=B, response_length=S, num_groups=B,
         group_of=np.arange(B, dtype=np.int32), total_tokens=T, full_tokens=T, sample_tokens=lens)
+
+
+def build_prepacked(input_ids: torch.Tensor, position_ids: Optional[torch.Tensor] = None,
+                    cu_seqlens: Optional[torch.Tensor] = None) -> PackedBatch:
+    """A batch the client packed itself: ONE row ``[1, T]`` holding several documents back to back.  Document
+    boundaries come from ``cu_seqlens`` or from the places where ``position_ids`` restart at 0; attention stays
+    inside a document and the last token of a document predicts nothing (it would predict the next document's
+    first token).  Per-token results map back to the ``[1, T]`` grid at the column of the predicted token."""
+    ids = input_ids.detach().to("cpu", torch.int64).reshape(-1).numpy()
+    T = int(ids.shape[0])
+    if cu_seqlens is not None:
+        cu = cu_seqlens.detach().to("cpu", torch.int64).reshape(-1).numpy()
+    elif position_ids is not None:
+        pos_in = position_ids.detach().to("cpu", torch.int64).reshape(-1).numpy()
+        starts = np.flatnonzero(pos_in == 0)
+        if starts.size == 0 or starts[0] != 0:
+            starts = np.concatenate([[0], starts])
+        cu = np.concatenate([starts, [T]])
+    else:
+        cu = np.asarray([0, T], dtype=np.int64)
+    if cu[0] != 0 or cu[-1] > T or np.any(np.diff(cu) < 0):
+        raise ValueError(f"document boundaries {cu.tolist()} do not partition {T} tokens")
+    pos = np.empty(T, dtype=np.int32)
+    pred, labels, out_idx, segs = [], [], [], []
+    lens = np.diff(cu)
+    for s0, n in zip(cu[:-1].tolist(), lens.tolist()):
+        if n == 0:
+            continue
+        pos[s0:s0 + n] = np.arange(n, dtype=np.int32)
+        segs.append([s0, n, 0, 0, s0, n])
+        if n > 1:
+            pred.append(np.arange(s0, s0 + n - 1))
+            labels.append(ids[s0 + 1:s0 + n])
+            out_idx.append(np.arange(s0 + 1, s0 + n))
+    used = int(cu[-1])
+    if used < T:                                   # trailing padding: its own never-scored segment
+        pos[used:] = np.arange(T - used, dtype=np.int32)
+        segs.append([used, T - used, 0, 0, used, T - used])
+    cat = lambda xs: np.concatenate(xs).astype(np.int64) if xs else np.zeros(0, dtype=np.int64)
+    D = len(lens)
+    return PackedBatch(
+        input_ids=torch.from_numpy(ids.copy()), positions=torch.from_numpy(pos),
+        layout=AttnLayout(np.asarray(segs, dtype=np.int32).reshape(-1, 6), T),
+        pred_index=torch.from_numpy(cat(pred)), labels=torch.from_numpy(cat(labels)),
+        out_index=torch.from_numpy(cat(out_idx)), batch_size=1, response_length=T, num_groups=max(D, 1),
+        group_of=np.zeros(1, dtype=np.int32), total_tokens=T, full_tokens=T, sample_tokens=np.asarray([T], dtype=np.int64))

@@ -22,12 +22,35 @@ def batch_is_packed(batch: Dict[str, Any]) -> bool:
     return bool(torch.is_tensor(pos) and pos.dim() == 2 and pos.shape[0] == 1 and (pos[0, 1:] == 0).any())
 
 
-def inject_sft_global_token_meta(batch: Dict[str, Any], meta: Dict[str, Any], group=None) -> None:
-    """``meta['batch_num_tokens']`` = loss tokens over ALL ranks (one all-reduce of an int64)."""
+def count_loss_tokens(batch: Dict[str, Any]) -> int:
+    """Tokens of this shard that the loss is taken over: selected by ``loss_mask`` / ``labels != -100``, inside the
+    attention mask, and PREDICTED by an earlier token of the same sequence -- the first valid token of a row (of a
+    document, for a row the client packed) has no predictor whichever side the padding is on."""
+    ids = batch["input_ids"] if "input_ids" in batch else batch.get("labels")
     lm = batch.get("loss_mask")
     if lm is None and batch.get("labels") is not None:
         lm = batch["labels"] != -100
-    n = torch.tensor([int(lm[:, 1:].sum()) if lm is not None else 0], dtype=torch.int64)
+    valid = batch.get("attention_mask")
+    valid = valid.bool() if valid is not None else torch.ones_like(ids, dtype=torch.bool)
+    sel = valid if lm is None else (lm.bool() & valid)
+    first = valid & (valid.int().cumsum(1) == 1)
+    if ids.dim() == 2 and ids.shape[0] == 1:
+        cu, pos = batch.get("cu_seqlens"), batch.get("position_ids")
+        if cu is not None:
+            T = ids.shape[1]
+            starts = cu.reshape(-1)[:-1].long()
+            first = torch.zeros_like(valid)
+            first[0, starts[starts < T]] = True
+            sel = sel.clone()
+            sel[0, int(cu.reshape(-1)[-1]):] = False                 # trailing padding behind the last document
+        elif torch.is_tensor(pos) and pos.numel() == ids.numel():
+            first = first | (pos.reshape(1, -1) == 0)
+    return int((sel & ~first).sum())
+
+
+def inject_sft_global_token_meta(batch: Dict[str, Any], meta: Dict[str, Any], group=None) -> None:
+    """``meta['batch_num_tokens']`` = loss tokens over ALL ranks (one all-reduce of an int64)."""
+    n = torch.tensor([count_loss_tokens(batch)], dtype=torch.int64)
     if dist.is_initialized() and dist.get_world_size(group) > 1:
         n = n.to("cuda" if dist.get_backend(group) == "nccl" else "cpu")
         dist.all_reduce(n, group=group)
