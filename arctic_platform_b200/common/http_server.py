@@ -37,6 +37,11 @@ def create_app(core: Optional[ArcticRLServerCore] = None) -> FastAPI:
                 return await asyncio.get_running_loop().run_in_executor(None, lambda: fn(*args, **kwargs))
             except JobError as exc:
                 raise HTTPException(exc.status, str(exc)) from exc
+            except ValueError as exc:                  # the request itself is wrong (lengths, shapes, unknown names)
+                raise HTTPException(400, f"{type(exc).__name__}: {exc}") from exc
+            except Exception as exc:  # noqa: BLE001 - a failing engine must not take the server down
+                asleep = isinstance(exc, RuntimeError) and "asleep" in str(exc)
+                raise HTTPException(409 if asleep else 500, f"{type(exc).__name__}: {exc}") from exc
 
     def octet(obj) -> Response:
         return Response(content=wire.dumps(obj), media_type=OCTET)
