@@ -5,6 +5,7 @@ from __future__ import annotations
 
 from typing import Any, List, Optional
 
+from ..utils.record_replay import record_replay_generation
 from .config import ArcticRLClientConfig, CortexConfig
 from .transport import JobHandles, Request, Transport, initialize_or_cleanup
 
@@ -105,6 +106,7 @@ class SyncArcticRLClient:
     def load_checkpoint(self, path=None, *, step=None) -> dict:
         return self.transport.call(_load_request(self.jobs, path, step))
 
+    @record_replay_generation
     def generate(self, prompts: list, sampling_params: Optional[dict] = None, routing_key=None, strict=False) -> list:
         return self.transport.call(_generate_request(self.jobs, prompts, sampling_params, routing_key, strict))["results"]
 
@@ -176,6 +178,7 @@ class ArcticRLClient:
     async def load_checkpoint(self, path=None, *, step=None):
         return await self.transport.acall(_load_request(self.jobs, path, step))
 
+    @record_replay_generation
     async def generate(self, prompts, sampling_params=None, routing_key=None, strict=False):
         return (await self.transport.acall(_generate_request(self.jobs, prompts, sampling_params, routing_key, strict)))["results"]
 

@@ -16,6 +16,7 @@ import torch
 
 from ..common.utils.batch import log_dp_shard_tokens
 from ..common.utils.metrics import combine_metric_microbatches
+from ..utils import sft_profile
 from ..models.config import DecoderConfig, resolve_config
 from ..models.decoder import DecoderLM
 from ..rl.processors.pipeline import run_pipeline
@@ -196,7 +197,8 @@ class EngineWorker:
         if not backward:
             keys = outs[0].get("batch", {}).keys()
             result["batch"] = {k: torch.cat([o["batch"][k] for o in outs], 0) for k in keys}
-        metrics["_profile_ms"] = {"fwd_bwd" if backward else "fwd": (time.perf_counter() - t0) * 1e3}
+        metrics["_profile_ms"] = {"fwd_bwd" if backward else "fwd_total": (time.perf_counter() - t0) * 1e3}
+        sft_profile.merge_into(metrics)          # per-phase buckets when ARL_SFT_PROFILE=1
         if backward:
             from ..utils.debug import maybe_log_moe_imbalance
             maybe_log_moe_imbalance(self.rank)
@@ -231,8 +233,10 @@ class EngineWorker:
     def step(self, learning_rate: Optional[float] = None) -> Dict[str, Any]:
         if learning_rate is not None:
             self.engine.cfg.lr = float(learning_rate)
-        out = self.engine.step()
-        return {"metrics": {"last_lr": out["last_lr"], "grad_norm": float(out["grad_norm"])}, "batch": {}}
+        with sft_profile.timed("step"):
+            out = self.engine.step()
+            gn = float(out["grad_norm"])
+        return sft_profile.merge_into({"metrics": {"last_lr": out["last_lr"], "grad_norm": gn}, "batch": {}})
 
     def compute_log_probs(self, input_ids: torch.Tensor) -> torch.Tensor:
         """``log softmax(logits)[next token]`` for every position of unpadded ``input_ids [B, S]``:

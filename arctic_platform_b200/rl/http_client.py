@@ -16,6 +16,7 @@ from typing import Any, Dict, List, Optional
 
 import requests
 
+from ..utils.record_replay import record_replay_generation
 from .. import wire
 from .config import ArcticRLClientConfig
 from .local_client import job_config_from, run_sync
@@ -165,6 +166,7 @@ class ArcticRLHttpClient:
     async def empty_training_cache(self):
         return self._json("/empty-training-cache", {"job_id": self._need("training")})
 
+    @record_replay_generation
     async def generate(self, prompts: List[Any], sampling_params: Optional[dict] = None) -> List[dict]:
         return self._octet("/generate", self._need("sampling"), {"prompts": prompts, "sampling_params": sampling_params})["results"]
 

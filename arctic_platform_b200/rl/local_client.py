@@ -18,6 +18,7 @@ from typing import Any, Dict, List, Optional
 import torch
 import torch.distributed as dist
 
+from ..utils.record_replay import record_replay_generation
 from ..common.server import ArcticRLServerCore
 from .config import ArcticRLClientConfig
 
@@ -114,6 +115,7 @@ class ArcticRLLocalClient:
         return self.server.empty_training_cache(self._need("training"))
 
     # ------------------------------------------------------------------ rollout
+    @record_replay_generation
     async def generate(self, prompts: List[List[int]], sampling_params: Optional[dict] = None) -> List[dict]:
         return self.server.generate(self._need("sampling"), prompts, sampling_params)["results"]
 

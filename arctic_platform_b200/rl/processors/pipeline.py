@@ -16,6 +16,7 @@ from typing import Any, Dict, List, Optional
 
 import torch
 
+from ...utils import sft_profile
 from ...common.registry import LOSS_FNS, POST_PROCESSORS, register_post_processor, resolve_fn
 from ...models.decoder import token_logprobs
 from ..zorro_train.layout import PackedBatch, build_packed_batch, build_plain_packed
@@ -84,14 +85,16 @@ def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = 
     loss_name = processing.get("loss_fn")
     sft = loss_name in _losses.SFT_LOSS_FNS or bool(meta.get("plain_packing"))
     t0 = time.perf_counter()
-    packed = pack_for_model(batch, meta, sft).to(device)
+    with sft_profile.timed("h2d"):
+        packed = pack_for_model(batch, meta, sft).to(device)
     actor = meta.get("actor_config", {}) or {}
     want_entropy = bool(actor.get("entropy_coeff", 0.0)) or bool(meta.get("compute_entropy", not backward))
     temperature = float(meta.get("temperature", 1.0) or 1.0)
     model.train(backward)
     ctx = torch.enable_grad() if backward else torch.no_grad()
     with ctx:
-        lp, ent = token_logprobs(model, packed, 1.0 / temperature, with_entropy=want_entropy)
+        with sft_profile.timed("fwd"):
+            lp, ent = token_logprobs(model, packed, 1.0 / temperature, with_entropy=want_entropy)
         outputs: Dict[str, Any] = {"logprobs": lp, "entropy": ent, "packed": packed}
         for name in processing.get("post") or []:
             outputs = resolve_fn(name, POST_PROCESSORS)(outputs, batch, meta, processing, device)
@@ -99,11 +102,13 @@ def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = 
         metrics: Dict[str, Any] = {}
         if loss_name:
             loss_fn = resolve_fn(loss_name, LOSS_FNS)
-            loss, metrics = loss_fn(outputs, batch, meta, processing.get("loss_kwargs") or {}, device)
+            with sft_profile.timed("loss"):
+                loss, metrics = loss_fn(outputs, batch, meta, processing.get("loss_kwargs") or {}, device)
         if backward:
             if loss is None:
                 raise ValueError("backward needs a loss_fn")
-            engine.backward(loss)
+            with sft_profile.timed("bwd"):
+                engine.backward(loss)
     result: Dict[str, Any] = {"metrics": metrics, "avg_loss": float(loss.detach()) if loss is not None else 0.0}
     metrics.setdefault("perf/packed_tokens", float(packed.total_tokens))
     metrics.setdefault("perf/dedup_redundancy", float(packed.redundancy))
