@@ -9,6 +9,8 @@ meet inside ``TrainEngine.step`` (fused NVLink kernels) -- the server only fans 
 """
 from __future__ import annotations
 
+import contextlib
+import os
 import time
 from typing import Any, Dict, Iterable, List, Optional
 
@@ -47,7 +49,6 @@ _PG = {"created_here": False, "users": 0}
 
 class EngineWorker:
     def __init__(self, device=None):
-        import os
         self.rank = int(os.environ.get("RANK", "0"))
         self.world = int(os.environ.get("WORLD_SIZE", "1"))
         if device is None:
@@ -61,6 +62,8 @@ class EngineWorker:
         self.sampler = None
         self.model_cfg: Optional[DecoderConfig] = None
         self.job_config: Dict[str, Any] = {}
+        self.activation_offload = None
+        self._nvtx = os.environ.get("APB_NVTX", "0") == "1"
 
     # ------------------------------------------------------------------ lifecycle
     def initialize(self, job_config: Dict[str, Any], model: Optional[DecoderLM] = None) -> bool:
@@ -114,6 +117,15 @@ class EngineWorker:
             for blk in m.blocks:
                 blk.tiled_mlp_shards = shards
             self.engine = TrainEngine(m, ecfg)
+            ao = wc.get("activation_offload")
+            if ao:
+                # saved activations go to pinned host memory on a side stream and come back ahead of their use
+                from ..utils.activation_offload import ActivationOffload
+                opts = ao if isinstance(ao, dict) else {}
+                if opts.get("enable", True):
+                    self.activation_offload = ActivationOffload(
+                        min_bytes=int(opts.get("min_bytes", 1 << 20)), keep_last=int(opts.get("keep_last", 2)),
+                        prefetch=int(opts.get("prefetch", 2)))
         return True
 
     def rank_info(self) -> Dict[str, Any]:
@@ -186,12 +198,25 @@ class EngineWorker:
             mbs = split_microbatches(batch, n_mb)
         meta = self._with_sft_global_tokens(mbs, meta, processing)
         per_mb, outs = [], []
-        for i, mb in enumerate(mbs):
-            if isinstance(mb, dict):
-                log_dp_shard_tokens(self.rank, f"{'fwd_bwd' if backward else 'fwd'} micro-batch {i}", mb, meta)
-            r = run_pipeline(self.engine, mb, meta, processing, self.device, backward=backward, return_tensors=True)
-            per_mb.append(r["metrics"])
-            outs.append(r)
+        from ..utils.debug import ProfilerContext, nvtx_range, see_memory_usage
+        tag = "fwd_bwd" if backward else "fwd"
+        self._calls = getattr(self, "_calls", 0) + 1
+        prof_type = os.environ.get("APB_PROFILER", "none") if self._calls == int(os.environ.get("APB_PROFILER_CALL", "2")) else "none"
+        see_memory_usage(f"{tag} start")
+        with ProfilerContext(prof_type, os.environ.get("APB_PROFILER_DIR", "/tmp/apb-prof"), f"{tag}-rank{self.rank}") as prof:
+            for i, mb in enumerate(mbs):
+                if isinstance(mb, dict):
+                    log_dp_shard_tokens(self.rank, f"{tag} micro-batch {i}", mb, meta)
+                offload = self.activation_offload if backward else None
+                with nvtx_range(f"{tag}/mb{i}", enabled=self._nvtx), (offload or contextlib.nullcontext()):
+                    r = run_pipeline(self.engine, mb, meta, processing, self.device, backward=backward, return_tensors=True)
+                if offload is not None:
+                    offload.release()
+                per_mb.append(r["metrics"])
+                outs.append(r)
+        if prof.report and self.rank == 0:
+            print(f"[profile] {tag}: {prof.report}", flush=True)
+        see_memory_usage(f"{tag} end")
         metrics = combine_metric_microbatches(per_mb)
         result: Dict[str, Any] = {"metrics": metrics, "avg_loss": sum(o["avg_loss"] for o in outs)}
         if not backward:

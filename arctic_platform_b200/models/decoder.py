@@ -259,12 +259,16 @@ def hash_name(name: str) -> int:
     return h
 
 
-def token_logprobs(model: DecoderLM, packed, inv_temperature=1.0, with_entropy: bool = True):
+def token_logprobs(model: DecoderLM, packed, inv_temperature=1.0, with_entropy: bool = True, action_masks=None):
     """Log-probabilities (and entropies) of ``packed.labels`` under ``model``; ``packed`` is a
     :class:`~arctic_platform_b200.rl.zorro_train.layout.PackedBatch` already on the model's device.
-    Returns fp32 tensors of shape ``[N]`` in original sample order."""
+    Returns fp32 tensors of shape ``[N]`` in original sample order.  ``action_masks`` (one row per prediction)
+    restricts the distribution of the constrained rows to their legal tokens."""
     from ..ops.logprob import lm_head_logprobs
 
     hidden = model.forward_hidden(packed.input_ids, packed.positions, packed.layout)
     pred = hidden.index_select(0, packed.pred_index)
+    if action_masks is not None:
+        from ..utils.action_masks import masked_logprobs
+        return masked_logprobs(pred, model.output_weight, packed.labels, action_masks, inv_temperature, with_entropy)
     return lm_head_logprobs(pred, model.output_weight, packed.labels, inv_temperature, with_entropy)

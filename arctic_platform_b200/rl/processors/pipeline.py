@@ -75,6 +75,22 @@ def pack_for_model(batch: dict, meta: dict, sft: bool) -> PackedBatch:
                               dedup=bool(meta.get("zorro_train_enable", True)))
 
 
+def action_masks_of(batch: Dict[str, Any], packed):
+    """Token-set constraints of the batch, one row per prediction of ``packed``.  The batch carries them densely on
+    the response grid: ``action_mask_tokens [B, R, K]`` (padded with -1) and ``action_mask_allow [B, R]`` (1 = the
+    listed tokens are the legal set, 0 = they are illegal, -1 = unconstrained position)."""
+    toks = batch.get("action_mask_tokens")
+    if toks is None:
+        return None
+    from ...utils.action_masks import ActionMasks
+    allow = batch.get("action_mask_allow")
+    B, R, K = toks.shape
+    if allow is None:
+        allow = torch.where((toks >= 0).any(-1), 1, -1)
+    rows = packed.out_index.to("cpu")
+    return ActionMasks.from_grid(toks.reshape(B * R, K).to("cpu")[rows], allow.reshape(B * R).to("cpu")[rows])
+
+
 def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = None,
                  processing: Optional[dict] = None, device=None, backward: bool = True,
                  return_tensors: bool = True) -> Dict[str, Any]:
@@ -94,7 +110,8 @@ def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = 
     ctx = torch.enable_grad() if backward else torch.no_grad()
     with ctx:
         with sft_profile.timed("fwd"):
-            lp, ent = token_logprobs(model, packed, 1.0 / temperature, with_entropy=want_entropy)
+            lp, ent = token_logprobs(model, packed, 1.0 / temperature, with_entropy=want_entropy,
+                                     action_masks=action_masks_of(batch, packed))
         outputs: Dict[str, Any] = {"logprobs": lp, "entropy": ent, "packed": packed}
         for name in processing.get("post") or []:
             outputs = resolve_fn(name, POST_PROCESSORS)(outputs, batch, meta, processing, device)

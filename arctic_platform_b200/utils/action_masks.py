@@ -57,6 +57,22 @@ class ActionMasks:
         return ActionMasks(row_ptr, torch.tensor(toks, dtype=torch.int64), allow)
 
     @staticmethod
+    def from_grid(tokens: torch.Tensor, allow: torch.Tensor) -> "ActionMasks":
+        """From the dense form a batch carries over the wire: ``tokens [N, K]`` int64 padded with ``-1`` and
+        ``allow [N]`` with 1 = the listed tokens are the legal set, 0 = they are illegal, negative = no constraint
+        on that row."""
+        tokens = tokens.to("cpu", torch.int64)
+        allow = allow.to("cpu", torch.int64)
+        keep = (tokens >= 0) & (allow >= 0)[:, None]
+        counts = keep.sum(1)
+        if bool(((allow == 1) & (counts == 0)).any()):
+            raise ValueError("an empty allow list leaves no legal token")
+        row_ptr = torch.zeros(tokens.shape[0] + 1, dtype=torch.int64)
+        row_ptr[1:] = counts.cumsum(0)
+        srt = torch.where(keep, tokens, torch.full_like(tokens, torch.iinfo(torch.int64).max)).sort(1).values
+        return ActionMasks(row_ptr, srt[srt != torch.iinfo(torch.int64).max], allow == 1)
+
+    @staticmethod
     def pack(parts: Sequence["ActionMasks"]) -> "ActionMasks":
         """Concatenates the masks of several samples in the order their prediction rows are packed."""
         ptrs, off = [torch.zeros(1, dtype=torch.int64)], 0

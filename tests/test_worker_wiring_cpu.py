@@ -1,0 +1,89 @@
+"""Options that reach the engines through the worker: token-set constraints carried by the batch, activation
+offload, the one-shot profiler and memory reports."""
+import os
+
+import pytest
+import torch
+
+from arctic_platform_b200.engine.worker import EngineWorker
+from tests.test_zorro_equivalence_cpu import make_grpo_batch
+
+
+def _worker(job_type="log_prob", **wc):
+    w = EngineWorker("cpu")
+    w.initialize({"model_name": "qwen3-tiny", "job_type": job_type, "seed": 6, "ds_worker_config": wc,
+                  "ds_config": {"zero_optimization": {"stage": 1}}})
+    return w
+
+
+def test_action_masks_in_the_batch_constrain_the_scored_distribution():
+    w = _worker()
+    ids, mask, R = make_grpo_batch(n_prompts=2, n_samples=2, seed=3)
+    B = ids.shape[0]
+    rmask = mask[:, -R:].contiguous()
+    batch = {"input_ids": ids, "attention_mask": mask, "response_mask": rmask}
+    meta = {"zorro_train_enable": True, "compute_entropy": True}
+    free = w.forward_no_grad(batch, meta)["batch"]
+    # response position 0 of every rollout: only {label, 3, 4} are legal; position 1 of rollout 0: token 5 is illegal
+    K = 3
+    toks = torch.full((B, R, K), -1, dtype=torch.int64)
+    allow = torch.full((B, R), -1, dtype=torch.int64)
+    P = ids.shape[1] - R
+    for b in range(B):
+        toks[b, 0] = torch.tensor([int(ids[b, P]), 3, 4])
+        allow[b, 0] = 1
+    toks[0, 1, 0] = 5
+    allow[0, 1] = 0
+    con = w.forward_no_grad({**batch, "action_mask_tokens": toks, "action_mask_allow": allow}, meta)["batch"]
+    lp_f, lp_c = free["log_probs"], con["log_probs"]
+    assert (lp_c[:, 0] > lp_f[:, 0]).all()                         # mass of a three-token set: the label gains
+    assert (con["entropy"][:, 0] < free["entropy"][:, 0]).all() and (con["entropy"][:, 0] <= torch.log(torch.tensor(3.0)) + 1e-5).all()
+    assert lp_c[0, 1] >= lp_f[0, 1] - 1e-6                         # removing another token can only help the label
+    untouched = rmask.bool().clone()
+    untouched[:, 0] = False
+    untouched[0, 1] = False
+    assert torch.allclose(lp_c[untouched], lp_f[untouched], atol=1e-6)
+    # a label outside its own allow list is impossible
+    toks2 = toks.clone()
+    toks2[1, 0] = torch.tensor([3, 4, -1])
+    bad = w.forward_no_grad({**batch, "action_mask_tokens": toks2, "action_mask_allow": allow}, meta)["batch"]["log_probs"]
+    assert torch.isinf(bad[1, 0]) and bad[1, 0] < 0
+    # the allow flags can be left out: every position with tokens listed is an allow list
+    same = w.forward_no_grad({**batch, "action_mask_tokens": torch.where(allow[..., None] == 0, -1, toks)}, meta)["batch"]["log_probs"]
+    assert torch.allclose(same[:, 0], lp_c[:, 0], atol=1e-6)
+
+
+def test_activation_offload_option_changes_nothing_but_where_tensors_wait():
+    ids, mask, R = make_grpo_batch(n_prompts=2, n_samples=2, seed=4)
+    B = ids.shape[0]
+    batch = {"input_ids": ids, "attention_mask": mask, "response_mask": mask[:, -R:].contiguous(),
+             "advantages": torch.ones(B, R), "old_log_probs": torch.full((B, R), -3.0)}
+    grads = {}
+    for name, wc in (("plain", {}), ("offload", {"activation_offload": {"min_bytes": 1, "keep_last": 0}})):
+        w = _worker("training", **wc)
+        assert (w.activation_offload is not None) == (name == "offload")
+        w.forward_backward(batch, {"zorro_train_enable": True}, {"loss_fn": "verl_grpo"})
+        grads[name] = w.engine.grad_buf.tensor.clone()
+        if name == "offload":
+            st = w.activation_offload.stats.as_dict()
+            assert st["skipped_tensors"] > 0 and st["offloaded_tensors"] == 0      # host tensors stay put; device tensors move (GPU test)
+    assert torch.equal(grads["plain"], grads["offload"])
+    assert _worker("training", activation_offload={"enable": False}).activation_offload is None
+
+
+def test_one_shot_profiler_and_memory_report(monkeypatch, capsys, tmp_path):
+    monkeypatch.setenv("APB_PROFILER", "c")
+    monkeypatch.setenv("APB_PROFILER_CALL", "1")
+    w = _worker()
+    ids, mask, R = make_grpo_batch(n_prompts=1, n_samples=2, seed=5)
+    batch = {"input_ids": ids, "attention_mask": mask, "response_mask": mask[:, -R:].contiguous()}
+    w.forward_no_grad(batch, {})
+    out = capsys.readouterr().out
+    assert "[profile] fwd:" in out and "cumulative" in out
+    w.forward_no_grad(batch, {})
+    assert "[profile]" not in capsys.readouterr().out               # only the chosen call is profiled
+    from arctic_platform_b200.utils import debug
+    monkeypatch.setattr(debug, "DISABLE_DEBUG", False)
+    w.forward_no_grad(batch, {})
+    out = capsys.readouterr().out
+    assert "[mem][rank 0] fwd start" in out and "[mem][rank 0] fwd end" in out
