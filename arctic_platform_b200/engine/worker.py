@@ -191,12 +191,16 @@ class EngineWorker:
         if self.engine is None:
             raise RuntimeError("worker has no training/log-prob engine")
         t0 = time.perf_counter()
+        row_order = None
         if isinstance(batch, (list, tuple)):
             mbs = list(batch)                               # client-side gradient-accumulation split
+        elif (meta or {}).get("max_tokens_per_mb"):
+            mbs, row_order = self._split_by_token_budget(batch, meta, processing)
         else:
             n_mb = int((meta or {}).get("num_micro_batches", 1) or 1)
             mbs = split_microbatches(batch, n_mb)
         meta = self._with_sft_global_tokens(mbs, meta, processing)
+        meta = self._with_rl_global_counts(mbs, meta, processing)
         per_mb, outs = [], []
         from ..utils.debug import ProfilerContext, nvtx_range, see_memory_usage
         tag = "fwd_bwd" if backward else "fwd"
@@ -222,12 +226,58 @@ class EngineWorker:
         if not backward:
             keys = outs[0].get("batch", {}).keys()
             result["batch"] = {k: torch.cat([o["batch"][k] for o in outs], 0) for k in keys}
+            if row_order is not None:                      # micro-batches were formed by size: back to the caller's order
+                inv = torch.empty_like(row_order)
+                inv[row_order] = torch.arange(row_order.numel())
+                result["batch"] = {k: v[inv] for k, v in result["batch"].items()}
         metrics["_profile_ms"] = {"fwd_bwd" if backward else "fwd_total": (time.perf_counter() - t0) * 1e3}
         sft_profile.merge_into(metrics)          # per-phase buckets when ARL_SFT_PROFILE=1
         if backward:
             from ..utils.debug import maybe_log_moe_imbalance
             maybe_log_moe_imbalance(self.rank)
         return result
+
+    def _split_by_token_budget(self, batch, meta, processing):
+        """Micro-batches of at most ``meta['max_tokens_per_mb']`` tokens (first-fit decreasing).  With prompt
+        de-duplication whole prompt groups stay together and the shared prompt counts once; every data-parallel rank
+        ends up with the same number of micro-batches.  Returns the micro-batches and the row permutation they
+        follow (arctic_platform/rl/processors/pipeline.py:502-606 in the reference)."""
+        from ..rl.processors.losses import SFT_LOSS_FNS
+        from ..rl.processors.microbatch import MicroBatchSpec, split_padded_tensor_dict_into_mb_list
+        from ..rl.processors.pipeline import response_length_of
+        from ..rl.zorro_train.seqlen_balancing import rearrange_micro_batches_with_dedup
+        budget = int(meta["max_tokens_per_mb"])
+        group = getattr(self.engine, "group", None)
+        if "attention_mask" not in batch:
+            batch = {**batch, "attention_mask": torch.ones_like(batch["input_ids"])}
+        sft = (processing or {}).get("loss_fn") in SFT_LOSS_FNS or bool(meta.get("plain_packing"))
+        if not sft and meta.get("zorro_train_enable", True):
+            mbs, rows = rearrange_micro_batches_with_dedup(batch, response_length_of(batch, meta), budget,
+                                                            meta.get("max_rollouts"), dp_group=group)
+        else:
+            mbs, rows = split_padded_tensor_dict_into_mb_list(batch, MicroBatchSpec(budget), group)
+        return mbs, torch.tensor([i for r in rows for i in r], dtype=torch.long)
+
+    def _with_rl_global_counts(self, mbs, meta, processing):
+        """Several micro-batches and no normalisers from the client: the policy losses then need the token and
+        sequence counts of the WHOLE batch (all micro-batches, all ranks), or every micro-batch would be averaged on
+        its own and the accumulated gradient would scale with the number of micro-batches."""
+        from ..rl.processors.losses import SFT_LOSS_FNS
+        loss_fn = (processing or {}).get("loss_fn")
+        if (len(mbs) <= 1 or not loss_fn or loss_fn in SFT_LOSS_FNS or "batch_num_tokens" in (meta or {})
+                or not all(isinstance(mb, dict) and "response_mask" in mb for mb in mbs)):
+            return meta
+        import torch.distributed as dist
+        meta = dict(meta or {})
+        t = torch.tensor([float(sum(int(mb["response_mask"].sum()) for mb in mbs)),
+                          float(sum(mb["input_ids"].shape[0] for mb in mbs))], dtype=torch.float64)
+        group = getattr(self.engine, "group", None)
+        if dist.is_initialized() and self.engine.world > 1:
+            t = t.to(self.device if dist.get_backend(group) == "nccl" else "cpu")
+            dist.all_reduce(t, group=group)
+            meta.setdefault("dp_size", self.engine.world)
+        meta["batch_num_tokens"], meta["global_batch_size"] = float(t[0]), float(t[1])
+        return meta
 
     def _with_sft_global_tokens(self, mbs, meta, processing):
         """Cross-entropy losses normalised by the GLOBAL token count need that count before the first micro-batch

@@ -87,3 +87,30 @@ def test_one_shot_profiler_and_memory_report(monkeypatch, capsys, tmp_path):
     w.forward_no_grad(batch, {})
     out = capsys.readouterr().out
     assert "[mem][rank 0] fwd start" in out and "[mem][rank 0] fwd end" in out
+
+
+def test_token_budget_micro_batches_keep_results_and_order():
+    ids, mask, R = make_grpo_batch(n_prompts=4, n_samples=3, seed=9, p_rng=(4, 40), r_rng=(2, 24))
+    B = ids.shape[0]
+    g = torch.Generator().manual_seed(1)
+    batch = {"input_ids": ids, "attention_mask": mask, "response_mask": mask[:, -R:].contiguous(),
+             "advantages": torch.randn(B, 1, generator=g).expand(B, R).contiguous(),
+             "old_log_probs": -2.0 + 0.01 * torch.randn(B, R, generator=g)}
+    lp = _worker()
+    whole = lp.forward_no_grad(batch, {"zorro_train_enable": True})["batch"]["log_probs"]
+    budget = int(mask.sum(1).max()) * 3
+    split = lp.forward_no_grad(batch, {"zorro_train_enable": True, "max_tokens_per_mb": budget})["batch"]["log_probs"]
+    assert torch.allclose(split, whole, atol=1e-5)                          # same rows, same order
+    plain = lp.forward_no_grad(batch, {"zorro_train_enable": False, "max_tokens_per_mb": budget})["batch"]["log_probs"]
+    assert torch.allclose(plain, whole, atol=1e-5)
+    with pytest.raises(ValueError):
+        lp.forward_no_grad(batch, {"zorro_train_enable": False, "max_tokens_per_mb": 3})
+    # training: the gradient of the whole batch, however it is cut up
+    grads = {}
+    for name, meta in (("whole", {}), ("budget", {"max_tokens_per_mb": budget}), ("four", {"num_micro_batches": 4})):
+        w = _worker("training")
+        out = w.forward_backward(batch, {"zorro_train_enable": True, **meta}, {"loss_fn": "verl_grpo"})
+        grads[name] = w.engine.grad_buf.tensor.clone()
+        assert out["metrics"]["loss.tokens"] == float(mask[:, -R:].sum())
+    assert torch.allclose(grads["budget"], grads["whole"], atol=1e-6, rtol=1e-4)
+    assert torch.allclose(grads["four"], grads["whole"], atol=1e-6, rtol=1e-4)
