@@ -221,8 +221,23 @@ class ArcticRLServerCore:
         batch = payload.get("batch")
         meta = dict(payload.get("meta") or {})
         processing = payload.get("processing")
-        shards, order = split_batch_for_ranks(batch, meta, len(job.workers))
+        n = len(job.workers)
+        sp = int(((job.config.get("ds_worker_config") or {}).get("sequence_parallel", 1)) or 1)
+        if sp > 1:
+            # ranks [k*sp, (k+1)*sp) form one sequence-parallel group: they all get data shard k and split its tokens
+            if n % sp:
+                raise JobError(400, f"sequence_parallel={sp} does not divide the job's {n} ranks")
+            shards, order = split_batch_for_ranks(batch, meta, n // sp)
+            shards = [shards[r // sp] for r in range(n)]
+        else:
+            shards, order = split_batch_for_ranks(batch, meta, n)
         results = call_all(job.workers, method, [(shard, meta, processing) for shard in shards])
+        if sp > 1:
+            # tensors come back complete from every rank of a group: keep the group leader's copy; metrics are sums
+            # over the rows each rank scored, so they all count
+            for r, res in enumerate(results):
+                if r % sp and isinstance(res, dict) and "batch" in res:
+                    res["batch"] = None
         return results, order
 
     def forward_backward(self, job_id: int, payload: Dict[str, Any]) -> Dict[str, Any]:
@@ -235,7 +250,7 @@ class ArcticRLServerCore:
         job = self._job(job_id, ("training", "log_prob"))
         results, order = self._fan_out(job, "forward_no_grad", payload)
         metrics, avg_loss = finalize_fwd_bwd_metrics(results)
-        merged = merge_dict_shards([r.get("batch") or {} for r in results])
+        merged = merge_dict_shards([r["batch"] for r in results if r.get("batch")])
         if order is not None:
             merged = restore_batch_order(merged, order)
         return {"job_id": job.job_id, "batch": merged, "metrics": metrics, "avg_loss": avg_loss}

@@ -63,6 +63,7 @@ class EngineWorker:
         self.model_cfg: Optional[DecoderConfig] = None
         self.job_config: Dict[str, Any] = {}
         self.activation_offload = None
+        self.sp = 1
         self._nvtx = os.environ.get("APB_NVTX", "0") == "1"
 
     # ------------------------------------------------------------------ lifecycle
@@ -105,6 +106,7 @@ class EngineWorker:
         if self.job_type == "log_prob":
             ecfg = EngineConfig.from_ds_config(job_config.get("log_prob_config") or job_config.get("ds_config"))
             self.engine = TrainEngine(m, ecfg, forward_only=True)
+            self._setup_sequence_parallel(m, int((job_config.get("ds_worker_config") or {}).get("sequence_parallel", 1) or 1))
         else:
             ecfg = EngineConfig.from_ds_config(job_config.get("ds_config"), job_config.get("training_config"))
             wc = job_config.get("ds_worker_config") or {}
@@ -117,6 +119,7 @@ class EngineWorker:
             for blk in m.blocks:
                 blk.tiled_mlp_shards = shards
             self.engine = TrainEngine(m, ecfg)
+            self._setup_sequence_parallel(m, int(wc.get("sequence_parallel", 1) or 1))
             ao = wc.get("activation_offload")
             if ao:
                 # saved activations go to pinned host memory on a side stream and come back ahead of their use
@@ -237,6 +240,27 @@ class EngineWorker:
             maybe_log_moe_imbalance(self.rank)
         return result
 
+    def _setup_sequence_parallel(self, model, sp: int) -> None:
+        """Ulysses groups of ``sp`` consecutive ranks.  Every rank of a group receives the same batch and works on
+        its slice of the packed token axis; ZeRO and the gradient mean still span all ranks."""
+        self.sp = 1
+        if sp <= 1:
+            return
+        import torch.distributed as dist
+        if not dist.is_initialized() or self.world % sp:
+            raise ValueError(f"sequence_parallel={sp} needs a process group whose size ({self.world}) it divides")
+        if model.cfg.layer_types is not None:
+            raise NotImplementedError("sequence parallelism covers softmax-attention layers; the hybrid family's "
+                                      "recurrent layers have no sequence-parallel form here")
+        from ..parallel.ulysses import apply_sequence_parallelism
+        mine = None
+        for g0 in range(0, self.world, sp):                    # every rank creates every group, in the same order
+            grp = dist.new_group(list(range(g0, g0 + sp)))
+            if g0 <= self.rank < g0 + sp:
+                mine = grp
+        apply_sequence_parallelism(model, mine)
+        self.sp = sp
+
     def _split_by_token_budget(self, batch, meta, processing):
         """Micro-batches of at most ``meta['max_tokens_per_mb']`` tokens (first-fit decreasing).  With prompt
         de-duplication whole prompt groups stay together and the shared prompt counts once; every data-parallel rank
@@ -275,7 +299,8 @@ class EngineWorker:
         if dist.is_initialized() and self.engine.world > 1:
             t = t.to(self.device if dist.get_backend(group) == "nccl" else "cpu")
             dist.all_reduce(t, group=group)
-            meta.setdefault("dp_size", self.engine.world)
+            t = t / self.sp                                    # the ranks of a sequence-parallel group hold the same rows
+            meta.setdefault("dp_size", self.engine.world // self.sp)
         meta["batch_num_tokens"], meta["global_batch_size"] = float(t[0]), float(t[1])
         return meta
 
@@ -294,7 +319,8 @@ class EngineWorker:
         if dist.is_initialized() and self.engine.world > 1:
             n = n.to(self.device if dist.get_backend(group) == "nccl" else "cpu")
             dist.all_reduce(n, group=group)
-            meta.setdefault("dp_size", self.engine.world)
+            n = n // self.sp
+            meta.setdefault("dp_size", self.engine.world // self.sp)
         meta["batch_num_tokens"] = float(n.item())
         return meta
 

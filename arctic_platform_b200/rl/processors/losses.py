@@ -46,6 +46,8 @@ def _token_views(model_outputs: dict, batch: dict, device):
         mask = torch.ones_like(model_outputs["logprobs"], dtype=torch.bool)
     else:
         mask = packed.gather_from_grid(mask_grid.to(device)).bool()
+    if model_outputs.get("owned") is not None:          # sequence parallelism: this rank's share of the rows
+        mask = mask & model_outputs["owned"].to(mask.device)
     seq_ids = torch.div(packed.out_index.to(device), R, rounding_mode="floor")
     return packed, take, mask, seq_ids
 
@@ -205,6 +207,8 @@ def _sft_core(model_outputs: dict, batch: dict, meta: dict, device):
         lm = (batch["labels"] != -100)
     mask = (packed.gather_from_grid(lm.to(device)).bool() if lm is not None
             else torch.ones_like(lp, dtype=torch.bool))
+    if model_outputs.get("owned") is not None:
+        mask = mask & model_outputs["owned"].to(mask.device)
     ce_sum = -masked_sum(lp, mask)
     ntok = mask.sum()
     return ce_sum, ntok

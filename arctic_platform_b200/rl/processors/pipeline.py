@@ -91,6 +91,20 @@ def action_masks_of(batch: Dict[str, Any], packed):
     return ActionMasks.from_grid(toks.reshape(B * R, K).to("cpu")[rows], allow.reshape(B * R).to("cpu")[rows])
 
 
+def _sp_logprobs(model, packed, sp_group, inv_temperature, want_entropy: bool, batch):
+    """Ulysses sequence parallelism: this rank runs its row shard of the packed axis and scores the prediction rows
+    that fall into it.  Returns full-length ``[N]`` tensors (zero where another rank scores) and the ownership mask."""
+    from ...parallel.ulysses import sp_token_logprobs
+    if batch.get("action_mask_tokens") is not None:
+        raise NotImplementedError("action masks are not supported together with sequence parallelism")
+    lp_loc, ent_loc, owned = sp_token_logprobs(model, packed, sp_group, inv_temperature, want_entropy)
+    idx = owned.nonzero()[:, 0]
+    N = packed.labels.numel()
+    lp = torch.zeros(N, dtype=lp_loc.dtype, device=lp_loc.device).index_put((idx,), lp_loc)
+    ent = torch.zeros(N, dtype=lp_loc.dtype, device=lp_loc.device).index_put((idx,), ent_loc) if ent_loc is not None else None
+    return lp, ent, owned
+
+
 def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = None,
                  processing: Optional[dict] = None, device=None, backward: bool = True,
                  return_tensors: bool = True) -> Dict[str, Any]:
@@ -109,10 +123,21 @@ def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = 
     model.train(backward)
     ctx = torch.enable_grad() if backward else torch.no_grad()
     with ctx:
+        sp_group = getattr(model, "sp_group", None)
+        owned = None
         with sft_profile.timed("fwd"):
-            lp, ent = token_logprobs(model, packed, 1.0 / temperature, with_entropy=want_entropy,
-                                     action_masks=action_masks_of(batch, packed))
+            if sp_group is None:
+                lp, ent = token_logprobs(model, packed, 1.0 / temperature, with_entropy=want_entropy,
+                                         action_masks=action_masks_of(batch, packed))
+            else:
+                lp, ent, owned = _sp_logprobs(model, packed, sp_group, 1.0 / temperature, want_entropy, batch)
+                # every rank of the sequence-parallel group holds the same batch and scores its own rows; the loss
+                # factor dp_size counts data-parallel GROUPS, the gradient mean runs over all ranks
+                import torch.distributed as dist
+                meta["dp_size"] = int(meta.get("dp_size", 1) or 1) * dist.get_world_size(sp_group)
         outputs: Dict[str, Any] = {"logprobs": lp, "entropy": ent, "packed": packed}
+        if owned is not None:
+            outputs["owned"] = owned
         for name in processing.get("post") or []:
             outputs = resolve_fn(name, POST_PROCESSORS)(outputs, batch, meta, processing, device)
         loss = None
@@ -131,8 +156,15 @@ def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = 
     metrics.setdefault("perf/dedup_redundancy", float(packed.redundancy))
     metrics["perf/pipeline_ms"] = (time.perf_counter() - t0) * 1e3
     if return_tensors:
-        out_batch = {"log_probs": packed.scatter_to_grid(lp.detach().float()).cpu()}
-        if ent is not None:
-            out_batch["entropy"] = packed.scatter_to_grid(ent.detach().float()).cpu()
+        lp_out = lp.detach().float()
+        ent_out = ent.detach().float() if ent is not None else None
+        if owned is not None:                     # rows scored by the other ranks of the group are zero here: sum them in
+            import torch.distributed as dist
+            both = torch.stack([lp_out, ent_out if ent_out is not None else torch.zeros_like(lp_out)])
+            dist.all_reduce(both, group=sp_group)
+            lp_out, ent_out = both[0], (both[1] if ent_out is not None else None)
+        out_batch = {"log_probs": packed.scatter_to_grid(lp_out).cpu()}
+        if ent_out is not None:
+            out_batch["entropy"] = packed.scatter_to_grid(ent_out).cpu()
         result["batch"] = out_batch
     return result

@@ -143,3 +143,32 @@ def test_rank_process_pool_hosts_trainer_and_sampler_of_a_rank_together():
     finally:
         core.destroy()
     assert core.pool.actors == {}
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("stage", [1, 3])
+def test_sequence_parallel_group_of_two_equals_one_process(stage):
+    """Two ranks as ONE Ulysses group behind the server: both receive the whole batch, each runs half of the packed
+    token axis; scores, loss, gradient norm and updated weights equal the single-process run."""
+    single = ArcticRLServerCore()
+    j1 = single.initialize(_job(stage))["job_id"]
+    p = _payload()
+    want_lp = single.forward(j1, {"batch": p["batch"], "meta": p["meta"]})["batch"]["log_probs"]
+    want = _train(single, j1, steps=2)
+    want_norm = single.weight_norm(training_job_id=j1)["training_norm"]
+    core = ArcticRLServerCore(worker_factory=spawned_worker_factory(_free_port()), training_gpus=2)
+    try:
+        job = {**_job(stage), "ds_worker_config": {"sequence_parallel": 2}}
+        jid = core.initialize(job)["job_id"]
+        got_lp = core.forward(jid, {"batch": p["batch"], "meta": p["meta"]})["batch"]["log_probs"]
+        assert got_lp.shape == want_lp.shape and torch.allclose(got_lp, want_lp, atol=1e-5)
+        got = _train(core, jid, steps=2)
+        for (la, na), (lb, nb) in zip(got, want):
+            assert la == pytest.approx(lb, rel=1e-4, abs=1e-6) and na == pytest.approx(nb, rel=1e-4)
+        assert core.weight_norm(training_job_id=jid)["training_norm"] == pytest.approx(want_norm, rel=1e-5)
+        with pytest.raises(Exception):
+            core.initialize({**_job(1), "job_type": "log_prob", "num_devices": 2,
+                             "ds_worker_config": {"sequence_parallel": 3}})
+    finally:
+        core.destroy()
+        single.destroy()
