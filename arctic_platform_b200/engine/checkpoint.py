@@ -41,8 +41,10 @@ def save_checkpoint(engine, save_dir: str, tag: Optional[str] = None, export_hf:
     d.mkdir(parents=True, exist_ok=True)
     files = []
     module = None
-    if getattr(engine, "zero3", None) is not None:
-        # stage 3: materialising the weights is a collective gather -- every rank takes part, rank 0 keeps the result
+    collective_export = getattr(engine, "zero3", None) is not None or any(u.local_only for u in engine.units)
+    if collective_export:
+        # stage 3 / expert parallelism: materialising the weights is a collective gather -- every rank takes part,
+        # rank 0 keeps the result
         gathered = ((n, t.detach().to("cpu").clone() if engine.rank == 0 else None) for n, t in engine.iter_hf_tensors())
         module = OrderedDict(gathered)
     if engine.rank == 0:
@@ -95,7 +97,7 @@ def save_checkpoint(engine, save_dir: str, tag: Optional[str] = None, export_hf:
         (root / "latest").write_text(tag)
         if export_hf:
             from ..models.hf_io import save_hf_checkpoint
-            tensors = module.items() if getattr(engine, "zero3", None) is not None else None   # gathered above
+            tensors = module.items() if collective_export else None   # gathered above
             files += [str(root / "hf" / x) for x in save_hf_checkpoint(engine.model, root / "hf", tensors=tensors)]
     _barrier(engine)
     return {"path": str(d), "tag": tag, "files": files}

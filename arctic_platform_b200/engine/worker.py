@@ -103,6 +103,14 @@ class EngineWorker:
                 seed=seed, eos_token_id=vc.get("eos_token_id"), quantization=vc.get("quantization"))
             return True
         m = model if model is not None else self._load_model(job_config, dtype, seed)
+        ep = int((job_config.get("ds_worker_config") or {}).get("expert_parallel", 1) or 1)
+        if ep > 1 and m.cfg.is_moe:
+            # experts sharded over the ranks of the job; tokens travel to their experts and back (peer memory on
+            # GPUs, all_to_all on CPU); expert parameters become rank-local units of the engine
+            from ..parallel.expert_parallel import attach_expert_parallel
+            if ep != self.world:
+                raise ValueError(f"expert_parallel={ep} must equal the number of ranks of the job ({self.world})")
+            attach_expert_parallel(m, ep, impl="fused" if self.device.type == "cuda" else "collective")
         if self.job_type == "log_prob":
             ecfg = EngineConfig.from_ds_config(job_config.get("log_prob_config") or job_config.get("ds_config"))
             self.engine = TrainEngine(m, ecfg, forward_only=True)
@@ -480,6 +488,13 @@ class EngineWorker:
             # the target keeps its parameters as shards too: hand it a full copy and let it cut its own shard
             dst_engine.load_full_flat(self.engine.full_flat_params())
             return n_names
+        if any(u.local_only for u in self.engine.units):
+            # expert parallelism: no rank holds all experts, so there is no flat buffer to copy -- every rank gathers
+            # the expert shards layer by layer and fills its target under the Hugging Face names
+            n = weight_sync.sync_state_dict(((n, t.detach()) for n, t in self.engine.iter_hf_tensors()), dst_model)
+            if dst.sampler is not None and hasattr(dst.sampler, "weights_updated"):
+                dst.sampler.weights_updated()
+            return n
         if self.engine.on_cuda and next(dst_model.parameters()).device == self.device:
             flat = getattr(dst_model, "_flat_params", None)
             if flat is None or flat.numel() != self.engine.total:

@@ -66,6 +66,33 @@ def hf_param_names(cfg: DecoderConfig) -> List[str]:
     return names
 
 
+def _all_experts(moe) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``(wgu [E, 2I, H], wdown [E, H, I])`` of one MoE layer.  Under expert parallelism every rank holds ``E / ep``
+    experts: the shards are all-gathered over the expert-parallel group (a collective -- every rank of the group
+    iterates), layer by layer, and dropped after the layer's tensors were yielded
+    (arctic_platform/model/implementations/qwen35/deepspeed_integration.py:262-268 does the same for its sync)."""
+    ep = getattr(moe, "ep", None)
+    if ep is None or ep.world <= 1:
+        return moe.wgu.data, moe.wdown.data
+    import torch.distributed as dist
+    out = []
+    for local in (moe.wgu.data, moe.wdown.data):
+        parts = [torch.empty_like(local) for _ in range(ep.world)]
+        dist.all_gather(parts, local.contiguous(), group=ep.group)
+        out.append(torch.cat(parts, 0))
+    return out[0], out[1]
+
+
+def _local_expert(moe, e: int) -> Optional[int]:
+    """Index of global expert ``e`` inside this rank's shard, or ``None`` when another rank owns it."""
+    ep = getattr(moe, "ep", None)
+    if ep is None or ep.world <= 1:
+        return e
+    n_local = moe.wgu.shape[0]
+    lo = ep.rank * n_local
+    return e - lo if lo <= e < lo + n_local else None
+
+
 def iter_hf_tensors(model) -> Iterator[Tuple[str, torch.Tensor]]:
     """Yields ``(hf_name, tensor)`` views/slices of the fused parameters (no copies except the
     de-interleave of gate/up)."""
@@ -103,11 +130,13 @@ def iter_hf_tensors(model) -> Iterator[Tuple[str, torch.Tensor]]:
                 yield p + "mlp.shared_expert.up_proj.weight", u
                 yield p + "mlp.shared_expert.down_proj.weight", blk.mlp.shared_wdown.data
                 yield p + "mlp.shared_expert_gate.weight", blk.mlp.shared_gate.data
+            wgu_all, wdown_all = _all_experts(blk.mlp)
             for e in range(cfg.num_experts):
-                g, u = split_gate_up(blk.mlp.wgu.data[e])
+                g, u = split_gate_up(wgu_all[e])
                 yield p + f"mlp.experts.{e}.gate_proj.weight", g
                 yield p + f"mlp.experts.{e}.up_proj.weight", u
-                yield p + f"mlp.experts.{e}.down_proj.weight", blk.mlp.wdown.data[e]
+                yield p + f"mlp.experts.{e}.down_proj.weight", wdown_all[e]
+            del wgu_all, wdown_all
         else:
             g, u = split_gate_up(blk.wgu.data)
             yield p + "mlp.gate_proj.weight", g
@@ -184,8 +213,10 @@ def load_hf_tensor(model, name: str, tensor: torch.Tensor) -> None:
     if rest == "mlp.gate.weight":
         return put(blk.mlp.router.data, tensor)
     if parts[3] == "mlp" and parts[4] == "experts":
-        e = int(parts[5])
+        e = _local_expert(blk.mlp, int(parts[5]))
         which = parts[6]
+        if e is None:
+            return None                          # expert parallelism: that expert lives on another rank
         if which == "gate_proj":
             return put(blk.mlp.wgu.data[e][0::2], tensor)
         if which == "up_proj":

@@ -172,3 +172,38 @@ def test_sequence_parallel_group_of_two_equals_one_process(stage):
     finally:
         core.destroy()
         single.destroy()
+
+
+@pytest.mark.timeout(600)
+def test_expert_parallel_job_behind_the_server(tmp_path):
+    """``ds_worker_config.expert_parallel = 2``: each rank keeps half of every layer's experts; training equals the
+    single-process run, and checkpoint export and the weight hand-over gather the expert shards."""
+    def moe_job(**extra):
+        return {"model_name": "qwen3-moe-tiny", "job_type": "training", "seed": 11, **extra,
+                "ds_config": {"zero_optimization": {"stage": 1}, "gradient_clipping": 1.0,
+                              "optimizer": {"type": "AdamW", "params": {"lr": 1e-3}}}}
+    single = ArcticRLServerCore()
+    j1 = single.initialize(moe_job())["job_id"]
+    want = _train(single, j1, steps=2)
+    want_norm = single.weight_norm(training_job_id=j1)["training_norm"]
+    core = ArcticRLServerCore(training_gpus=2, sampling_gpus=2, colocate=True)       # rank process pool
+    try:
+        jid = core.initialize(moe_job(ds_worker_config={"expert_parallel": 2}, checkpoint_path=str(tmp_path)))["job_id"]
+        got = _train(core, jid, steps=2)
+        for (la, na), (lb, nb) in zip(got, want):
+            assert la == pytest.approx(lb, rel=2e-3, abs=1e-5) and na == pytest.approx(nb, rel=2e-3)
+        assert core.weight_norm(training_job_id=jid)["training_norm"] == pytest.approx(want_norm, rel=1e-4)
+        saved = core.save(jid, step=2, export_hf=True)
+        hf = [f for f in saved["files"] if f.endswith(".safetensors")]
+        assert hf
+        from arctic_platform_b200.models.hf_io import read_safetensors
+        names = {n for f in hf for n, _t in read_safetensors(f)}
+        assert {f"model.layers.0.mlp.experts.{e}.down_proj.weight" for e in range(4)} <= names      # all experts, once
+        sj = core.initialize({"model_name": "qwen3-moe-tiny", "job_type": "sampling", "seed": 5,
+                              "vllm_config": {"max_model_len": 64}})["job_id"]
+        res = core.weight_sync(jid, [sj])
+        assert res["strategies"] == ["in_process"]
+        assert core.weight_norm(sampling_job_id=sj)["sampling_norm"] == pytest.approx(want_norm, rel=1e-4)
+    finally:
+        core.destroy()
+        single.destroy()
