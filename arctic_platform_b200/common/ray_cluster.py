@@ -79,8 +79,26 @@ def init_ray_cluster(auto_attach: bool = True) -> Dict[str, object]:
     return {"ray": True, "attached": False, "address": head, "temp_dir": temp_dir, "peers": peers}
 
 
+def own_cluster_pids(temp_dir: str) -> List[int]:
+    """Processes of the Ray cluster started with ``--temp-dir=temp_dir``: every Ray daemon carries that path on its
+    command line, and the directory name is unique to this process, so nothing of another cluster matches."""
+    import psutil
+    key = os.path.basename(os.path.normpath(temp_dir))
+    me = os.getpid()
+    pids = []
+    for proc in psutil.process_iter(["pid", "cmdline"]):
+        try:
+            cmd = " ".join(proc.info.get("cmdline") or [])
+        except (psutil.NoSuchProcess, psutil.AccessDenied):
+            continue
+        if key and key in cmd and proc.info["pid"] != me:
+            pids.append(int(proc.info["pid"]))
+    return pids
+
+
 def shutdown_own_cluster() -> None:
-    """Stops the Ray cluster this process started (identified by its temp dir), nothing else."""
+    """Stops the Ray cluster this process started -- identified by its private temp dir -- and nothing else: a
+    machine-wide ``ray stop`` would take other users' clusters down with it."""
     temp_dir = _started.get("temp_dir")
     if not temp_dir:
         return
@@ -90,6 +108,22 @@ def shutdown_own_cluster() -> None:
             ray.shutdown()
     except Exception:
         pass
-    subprocess.run(["ray", "stop", "--force"], check=False, capture_output=True,
-                   env={**os.environ, "RAY_TMPDIR": temp_dir})
+    try:
+        import psutil
+        procs = []
+        for pid in own_cluster_pids(temp_dir):
+            try:
+                p = psutil.Process(pid)
+                p.terminate()
+                procs.append(p)
+            except psutil.Error:
+                pass
+        _gone, alive = psutil.wait_procs(procs, timeout=5)
+        for p in alive:
+            try:
+                p.kill()
+            except psutil.Error:
+                pass
+    except ImportError:
+        pass
     _started["temp_dir"] = None
