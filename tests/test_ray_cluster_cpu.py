@@ -64,7 +64,8 @@ def test_starts_a_private_head_and_fans_out(monkeypatch, recorded, tmp_path):
     monkeypatch.setitem(sys.modules, "ray", ray)
     hostfile = tmp_path / "hostfile"
     hostfile.write_text("# nodes\nnode-a slots=8\n10.0.0.1 slots=8\n\nnode-b slots=8\n")
-    monkeypatch.setattr(rc, "read_hostfile", lambda path="/job/hostfile", _r=rc.read_hostfile: _r(str(hostfile)))
+    real_read = rc.read_hostfile
+    monkeypatch.setattr(rc, "read_hostfile", lambda path=str(hostfile): real_read(path))
     monkeypatch.setattr(rc.shutil, "which", lambda name: "/usr/bin/pdsh" if name == "pdsh" else None)
     monkeypatch.setenv("ARL_RAY_TEMP_DIR", str(tmp_path / "ray-tmp"))
     monkeypatch.setenv("RAY_PORT", "6400")
