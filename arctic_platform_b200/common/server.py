@@ -395,6 +395,16 @@ class ArcticRLServerCore:
 
     def wake_inference(self, job_id: int, tags=None) -> Dict[str, Any]:
         job = self._job(job_id, ("sampling",))
+        if self.colocate:
+            # the sampler is about to take its weights / KV memory back: return what the training engines of the same
+            # GPUs only hold as allocator cache first (arctic_platform/common/ray_server.py:266-288)
+            with self._lock:
+                trainers = [j for j in self.jobs.values() if j.job_type in ("training", "log_prob") and j.status == "RUNNING"]
+            for tj in trainers:
+                try:
+                    call_all(tj.workers, "empty_cache")
+                except Exception:
+                    pass
         call_all(job.workers, "wake_inference", None, tags)
         return {"job_id": job.job_id, "status": "awake"}
 
