@@ -79,7 +79,7 @@ def test_activation_offload_round_trip_and_pool_reuse():
         g = [w.grad.clone() for w in ws]
         for w in ws:
             w.grad = None
-        return float(loss), g
+        return float(loss.detach()), g
 
     import contextlib
     ref_loss, ref_g = run(contextlib.nullcontext())
