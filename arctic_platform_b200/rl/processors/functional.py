@@ -38,7 +38,7 @@ def _per_sequence(values, mask, seq_ids, num_seqs):
 def agg_loss(loss_mat: torch.Tensor, loss_mask: torch.Tensor, loss_agg_mode: str = "token-mean", dp_size: int = 1,
              batch_num_tokens: Optional[float] = None, global_batch_size: Optional[float] = None,
              loss_scale_factor: Optional[float] = None, seq_ids: Optional[torch.Tensor] = None,
-             num_seqs: Optional[int] = None) -> torch.Tensor:
+             num_seqs: Optional[int] = None, count_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Scalar loss that is invariant to how the global batch was split over ranks and micro-batches:
     every mode divides by a GLOBAL denominator and multiplies by ``dp_size`` (gradients are averaged over
     ranks afterwards)."""
@@ -53,6 +53,12 @@ def agg_loss(loss_mat: torch.Tensor, loss_mask: torch.Tensor, loss_agg_mode: str
     if loss_mat.dim() == 1 and seq_ids is None:
         raise ValueError("sequence-level aggregation of packed tokens needs seq_ids")
     sums, cnts = _per_sequence(loss_mat, loss_mask, seq_ids, num_seqs)
+    if count_mask is not None:
+        # this rank holds only part of every sequence's tokens (sequence parallelism): the per-sequence token counts
+        # come from the complete mask, so that the ranks' partial sums add up to the sequence's mean
+        _s, cnts = _per_sequence(torch.zeros_like(loss_mat), count_mask, seq_ids, num_seqs)
+        if global_batch_size is None:
+            raise ValueError("global_batch_size is required when a rank holds partial sequences")
     present = (cnts > 0).to(sums.dtype)
     per_seq = sums / (cnts + 1e-8) if loss_agg_mode == "seq-mean-token-mean" else sums
     if global_batch_size is None:

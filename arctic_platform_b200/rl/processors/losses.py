@@ -25,9 +25,17 @@ from .functional import (agg_loss, kl_penalty, m2po_mask, masked_sum, ppo_actor_
                          resolve_proximal_logp, sapo_loss_fn)
 
 
-def _global_info(meta: dict) -> dict:
-    return {"dp_size": int(meta.get("dp_size", 1) or 1), "batch_num_tokens": meta.get("batch_num_tokens"),
+def _global_info(meta: dict, model_outputs: dict = None) -> dict:
+    info = {"dp_size": int(meta.get("dp_size", 1) or 1), "batch_num_tokens": meta.get("batch_num_tokens"),
             "global_batch_size": meta.get("global_batch_size")}
+    if model_outputs is not None and model_outputs.get("_full_mask") is not None:
+        info["count_mask"] = model_outputs["_full_mask"]
+    # the "-norm" aggregation divides by the response horizon of the padded grid, not by the packed token count
+    horizon = meta.get("loss_scale_factor")
+    if horizon is None and model_outputs is not None and model_outputs.get("packed") is not None:
+        horizon = model_outputs["packed"].response_length
+    info["loss_scale_factor"] = horizon
+    return info
 
 
 def _token_views(model_outputs: dict, batch: dict, device):
@@ -47,6 +55,7 @@ def _token_views(model_outputs: dict, batch: dict, device):
     else:
         mask = packed.gather_from_grid(mask_grid.to(device)).bool()
     if model_outputs.get("owned") is not None:          # sequence parallelism: this rank's share of the rows
+        model_outputs["_full_mask"] = mask
         mask = mask & model_outputs["owned"].to(mask.device)
     seq_ids = torch.div(packed.out_index.to(device), R, rounding_mode="floor")
     return packed, take, mask, seq_ids
@@ -58,7 +67,7 @@ def verl_grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, d
     agg_mode = actor.get("loss_agg_mode", "token-mean")
     entropy_coeff = float(actor.get("entropy_coeff", 0.0) or 0.0)
     packed, take, mask, seq_ids = _token_views(model_outputs, batch, device)
-    info = _global_info(meta)
+    info = _global_info(meta, model_outputs)
     info.update(seq_ids=seq_ids, num_seqs=packed.batch_size)
     lp = model_outputs["logprobs"].float()
     old = take("old_log_probs")
@@ -140,8 +149,11 @@ def grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, device
     agg_mode = cfg.get("loss_agg_mode", "token-mean")
     level = cfg.get("importance_sampling_level", "token")
     packed, take, mask, seq_ids = _token_views(model_outputs, batch, device)
-    info = _global_info(meta)
+    info = _global_info(meta, model_outputs)
     seq_kw = {"seq_ids": seq_ids, "num_seqs": packed.batch_size}
+    if model_outputs.get("owned") is not None and (level == "sequence" or cfg.get("use_sapo_loss") or cfg.get("m2_threshold") is not None):
+        raise NotImplementedError("sequence-level importance, SAPO and M2PO masking need whole sequences on a rank; "
+                                  "they are not available together with sequence parallelism")
     lp = model_outputs["logprobs"].float()
     old = take("old_log_probs")
     if old is None:

@@ -278,3 +278,45 @@ def test_grpo_loss_options_through_the_registry():
     onp, _ = LOSS_FNS["grpo"](out, {k: v for k, v in batch.items() if k != "old_log_probs"}, {}, {}, "cpu")
     adv_tok = pb.gather_from_grid(batch["advantages"])
     assert onp.item() == pytest.approx(-adv_tok.mean().item(), rel=1e-5)       # ratio == 1 everywhere
+
+
+@pytest.mark.parametrize("mode", ["token-mean", "seq-mean-token-sum", "seq-mean-token-mean", "seq-mean-token-sum-norm"])
+def test_ownership_split_of_sequences_adds_up_to_the_whole(mode):
+    """Sequence parallelism: two ranks hold complementary parts of every sequence's tokens.  With the global
+    normalisers the mean of the ranks' losses (factor dp_size = 2 ranks) equals the loss of the whole batch."""
+    pb, lp, batch = _rl_inputs()
+    meta = {"batch_num_tokens": float(batch["response_mask"].sum()), "global_batch_size": 3.0}
+    cfg = {"loss_agg_mode": mode, "kl_loss_coef": 0.01, "use_kl_loss": True}
+    whole, _ = LOSS_FNS["verl_grpo"]({"logprobs": lp, "entropy": None, "packed": pb}, batch,
+                                     {**meta, "dp_size": 1, "actor_config": cfg}, {}, "cpu")
+    n = lp.numel()
+    owned0 = torch.arange(n) % 2 == 0
+    parts = []
+    for owned in (owned0, ~owned0):
+        l, m = LOSS_FNS["verl_grpo"]({"logprobs": lp * owned, "entropy": None, "packed": pb, "owned": owned}, batch,
+                                     {**meta, "dp_size": 2, "actor_config": cfg}, {}, "cpu")
+        parts.append(l)
+        assert m["loss.tokens"] == int(owned.sum())
+    assert ((parts[0] + parts[1]) / 2).item() == pytest.approx(whole.item(), rel=1e-5, abs=1e-7)
+    g, _ = LOSS_FNS["grpo"]({"logprobs": lp * owned0, "entropy": None, "packed": pb, "owned": owned0}, batch,
+                            {**meta, "dp_size": 2}, {"loss_agg_mode": mode}, "cpu")
+    assert torch.isfinite(g)
+    with pytest.raises(NotImplementedError):
+        LOSS_FNS["grpo"]({"logprobs": lp, "entropy": None, "packed": pb, "owned": owned0}, batch, {**meta, "dp_size": 2},
+                         {"importance_sampling_level": "sequence"}, "cpu")
+
+
+@pytest.mark.parametrize("mode", ["token-mean", "seq-mean-token-sum", "seq-mean-token-mean", "seq-mean-token-sum-norm"])
+def test_registered_loss_equals_the_padded_grid_formula_in_every_aggregation_mode(mode):
+    pb, lp, batch = _rl_inputs()
+    R = batch["response_mask"].shape[1]
+    loss, _ = LOSS_FNS["verl_grpo"]({"logprobs": lp, "entropy": None, "packed": pb}, batch,
+                                    {"actor_config": {"loss_agg_mode": mode}}, {}, "cpu")
+    grid_lp = pb.scatter_to_grid(lp.detach())
+    tok, _, _, _ = F.ppo_clip_token_loss(grid_lp, batch["old_log_probs"], batch["advantages"])
+    want = F.agg_loss(tok, batch["response_mask"], mode)               # [B, R] layout: the horizon is R
+    assert loss.item() == pytest.approx(want.item(), rel=1e-5)
+    if mode.endswith("norm"):
+        plain, _ = LOSS_FNS["verl_grpo"]({"logprobs": lp, "entropy": None, "packed": pb}, batch,
+                                         {"actor_config": {"loss_agg_mode": "seq-mean-token-sum"}}, {}, "cpu")
+        assert loss.item() == pytest.approx(plain.item() / R, rel=1e-5)
