@@ -1,4 +1,5 @@
 """The stand-alone actor harness: deduplicated and plain packing optimise the same objective."""
+import pytest
 import torch
 
 from arctic_platform_b200.rl.zorro_train.actor import DeduplicatedActor, packed_ppo_policy_loss
@@ -54,3 +55,23 @@ def test_dedup_actor_equals_plain_actor_and_microbatching_is_exact():
     assert mc["actor/num_micro_batches"] > 1 and abs(mc["actor/loss"] - ma["actor/loss"]) < 1e-5
     for x, p in zip(ga, a.model.parameters()):
         assert torch.allclose(x, p.grad, atol=2e-5)
+
+
+def test_harness_batch_convention_equivalence_and_timing():
+    import torch
+    from arctic_platform_b200.rl.zorro_train import harness
+    b = harness.create_dummy_batch(num_prompts=3, rollouts=4, prompt_len=(6, 20), response_len=(2, 9), vocab_size=500, seed=1)
+    ids, mask, R = b["input_ids"], b["attention_mask"], b["response_length"]
+    P = ids.shape[1] - R
+    assert ids.shape == (12, 29) and R == 9
+    for row in mask:                                  # prompts left-padded, responses right-padded
+        p, r = row[:P], row[P:]
+        assert p.sum() >= 6 and torch.equal(p, p.sort().values) and torch.equal(r, r.sort(descending=True).values)
+    assert len({tuple(x[:P].tolist()) for x in ids}) == 3
+    report = harness.main(["--model", "qwen3-tiny", "--prompts", "2", "--rollouts", "3", "--prompt-len", "16",
+                           "--response-len", "8", "--iters", "1", "--device", "cpu"])
+    assert report["max_logprob_diff"] < 1e-4 and report["min_cosine"] > 0.9999 and report["max_rel"] < 1e-3
+    assert report["tokens_dedup"] < report["tokens_plain"] and report["plain_ms"] > 0 and report["dedup_ms"] > 0
+    same = harness.compare_gradients({"w": torch.ones(3)}, {"w": torch.ones(3)})
+    assert same["max_abs"] == 0 and same["min_cosine"] == pytest.approx(1.0)
+    assert harness.timed(lambda: None, warmup=0, iters=2) >= 0
