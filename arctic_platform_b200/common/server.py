@@ -316,8 +316,21 @@ class ArcticRLServerCore:
 
     def log_probs(self, job_id: int, prompts, completions, top_k: int = 1) -> Dict[str, Any]:
         job = self._job(job_id, ("sampling", "log_prob", "training"))
+        if len(prompts) != len(completions):
+            raise JobError(400, f"{len(prompts)} prompts but {len(completions)} completions")
         if job.job_type == "sampling":
-            raise JobError(400, "log-probs are served by a log_prob or training job in this build")
+            # scored with the sampler's own weights (the reference's ``log_prob_engine = vllm``): the requests are
+            # spread over the replicas, each scores its share in one packed pass
+            n = len(job.workers)
+            share = [list(range(r, len(prompts), n)) for r in range(n)]
+            active = [(w, idx) for w, idx in zip(job.workers, share) if idx]
+            outs = call_all([w for w, _ in active], "score_completions",
+                            [([prompts[i] for i in idx], [completions[i] for i in idx]) for _, idx in active])
+            rows = [None] * len(prompts)
+            for (_, idx), res in zip(active, outs):
+                for i, r in zip(idx, res):
+                    rows[i] = r
+            return {"job_id": job.job_id, "log_probs": rows}
         rows = []
         P = max(len(p) for p in prompts)
         R = max(len(c) for c in completions)

@@ -355,6 +355,35 @@ class EngineWorker:
                          backward=False)
         return r["batch"]["log_probs"][:, 1:]
 
+    @torch.no_grad()
+    def score_completions(self, prompts, completions) -> List[List[float]]:
+        """Log-probability of every completion token given its prompt, under this worker's CURRENT weights -- the
+        sampler's when the worker hosts one (what the rollouts were drawn from), else the engine's.  One packed
+        pass; identical prompts are computed once."""
+        from ..models.decoder import token_logprobs
+        from ..rl.zorro_train.layout import build_packed_batch
+        model = self._target_model()
+        if self.sampler is not None and getattr(self.sampler, "_asleep", False):
+            raise RuntimeError("sampler is asleep; call wake() first")
+        P = max(len(p) for p in prompts)
+        R = max(len(c) for c in completions)
+        ids = torch.zeros((len(prompts), P + R), dtype=torch.int64)
+        mask = torch.zeros_like(ids)
+        for i, (p, c) in enumerate(zip(prompts, completions)):
+            if len(p) == 0:
+                raise ValueError("empty prompt")
+            ids[i, P - len(p):P] = torch.tensor(p)
+            mask[i, P - len(p):P] = 1
+            ids[i, P:P + len(c)] = torch.tensor(c)
+            mask[i, P:P + len(c)] = 1
+        pk = build_packed_batch(ids, mask, R, dedup=True).to(self.device)
+        was_training = model.training
+        model.eval()
+        lp, _ = token_logprobs(model, pk, 1.0, with_entropy=False)
+        model.train(was_training)
+        grid = pk.scatter_to_grid(lp.float()).cpu()
+        return [grid[i, :len(c)].tolist() for i, c in enumerate(completions)]
+
     # ------------------------------------------------------------------ rollout
     def generate(self, prompts, sampling_params=None) -> List[dict]:
         if self.sampler is None:

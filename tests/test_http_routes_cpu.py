@@ -79,7 +79,15 @@ def test_all_routes(api):
     lp = api.post("/log-probs", params={"job_id": jobs["log_prob"]},
                   json={"prompts": [[4, 5, 6], [7, 8]], "completions": [[9, 10], [11]]}).json()["log_probs"]
     assert [len(r) for r in lp] == [2, 1] and all(v < 0 for r in lp for v in r)
-    assert api.post("/log-probs", params={"job_id": jobs["sampling"]}, json={"prompts": [[1]], "completions": [[2]]}).status_code == 400
+    # a sampling job scores with the sampler's own weights; after the hand-over above they are the trainer's, the
+    # reference engine still holds the initial policy
+    sl = api.post("/log-probs", params={"job_id": jobs["sampling"]},
+                  json={"prompts": [[4, 5, 6], [7, 8], [4, 5, 6]], "completions": [[9, 10], [11], [12]]})
+    assert sl.status_code == 200 and [len(r) for r in sl.json()["log_probs"]] == [2, 1, 1]
+    tl = api.post("/log-probs", params={"job_id": jobs["training"]},
+                  json={"prompts": [[4, 5, 6], [7, 8], [4, 5, 6]], "completions": [[9, 10], [11], [12]]}).json()["log_probs"]
+    assert sl.json()["log_probs"][0] == pytest.approx(tl[0], abs=1e-5) and sl.json()["log_probs"][2] == pytest.approx(tl[2], abs=1e-5)
+    assert api.post("/log-probs", params={"job_id": jobs["sampling"]}, json={"prompts": [[1]], "completions": [[2], [3]]}).status_code == 400
     code, fw = _octet(api, "/forward", {"batch": {"input_ids": torch.tensor([[4, 5, 6, 9, 10]]),
                                                   "attention_mask": torch.ones(1, 5, dtype=torch.long),
                                                   "response_mask": torch.ones(1, 2, dtype=torch.long)},
