@@ -1,0 +1,167 @@
+"""Stand-alone service client against the in-memory service: retry policy, job life cycle, chunked uploads and
+results, streaming, request failures, configuration validation."""
+import pytest
+import torch
+
+from cortex_client.dss_client import NeutrinoClient, NeutrinoError, SubJobConfig
+from cortex_client.dss_client import neutrino_client as nc
+from tests.fake_service import FakeResponse, FakeServiceSession
+
+
+def _client(session=None, **kw):
+    sleeps = []
+    c = NeutrinoClient("https://svc.example/api", session=session or FakeServiceSession(), sleep=sleeps.append,
+                       poll_interval=0.01, **kw)
+    return c, sleeps
+
+
+def _job(c):
+    return c.create_job([SubJobConfig.training_job("qwen3-tiny"), SubJobConfig.sampling_job("qwen3-tiny")])["job_id"]
+
+
+def test_retries_transient_codes_with_growing_jittered_delays():
+    c, sleeps = _client()
+    c.session.fail_next = [503, 429, 500]
+    assert c.get_capacity() == {"free_gpus": 8}
+    assert len(sleeps) == 3 and all(0.25 <= sleeps[0] <= 0.75 for _ in [0]) and 0.5 <= sleeps[1] <= 1.5 and 1.0 <= sleeps[2] <= 3.0
+    # a client error is final at once and carries status and body
+    c.session.fail_next = [403]
+    with pytest.raises(NeutrinoError) as e:
+        c.get_capacity()
+    assert e.value.status == 403 and e.value.detail == {"error": "injected"} and len(sleeps) == 3
+    # gives up after max_retries + 1 attempts
+    c2, sleeps2 = _client(max_retries=2)
+    c2.session.fail_next = [502] * 5
+    with pytest.raises(NeutrinoError, match="failed after 3 attempts"):
+        c2.get_capacity()
+    assert len(sleeps2) == 2
+
+
+def test_connection_errors_count_as_transient():
+    class Flaky(FakeServiceSession):
+        def __init__(self):
+            super().__init__()
+            self.breaks = 2
+
+        def request(self, *a, **k):
+            if self.breaks:
+                self.breaks -= 1
+                raise ConnectionError("reset by peer")
+            return super().request(*a, **k)
+    c, sleeps = _client(Flaky())
+    assert c.get_capacity()["free_gpus"] == 8 and len(sleeps) == 2
+
+
+def test_headers_from_a_programmatic_access_token():
+    s = FakeServiceSession()
+    c = NeutrinoClient.from_pat("acct.example.com", "DB", "SCH", "secret", session=s, sleep=lambda x: None)
+    c.get_capacity()
+    _m, _p, _params, headers = s.calls[-1]
+    assert headers["Authorization"] == "Bearer secret"
+    assert headers["X-Snowflake-Authorization-Token-Type"] == "PROGRAMMATIC_ACCESS_TOKEN"
+    assert c.base == "https://acct.example.com/api/v2/databases/DB/schemas/SCH/cortex-training"
+
+
+def test_job_life_cycle_and_waiting():
+    c, sleeps = _client(FakeServiceSession(ready_after=3))
+    jid = _job(c)
+    body = c.session.jobs[jid]["body"]
+    assert [s["sub_job_type"] for s in body["sub_jobs"]] == ["training", "sampling"] and body["colocate"] is True
+    assert body["sub_jobs"][0]["ds_config"]["zero_optimization"]["stage"] == 3
+    assert c.list_jobs("PENDING")[0]["job_id"] == jid and c.list_jobs("RUNNING") == []
+    job = c.wait_for_job(jid)
+    assert job["status"] == "RUNNING" and sleeps == [1.0, 1.5]                     # polled three times
+    c.cancel_job(jid)
+    with pytest.raises(NeutrinoError, match="CANCELLED"):
+        c.wait_for_job(jid)
+    with pytest.raises(NeutrinoError) as e:
+        c.get_job("nope")
+    assert e.value.status == 404
+    with pytest.raises(ValueError):
+        c.create_job([])
+    # a job that never starts
+    c3, _ = _client(FakeServiceSession(ready_after=10 ** 9))
+    with pytest.raises(NeutrinoError, match="not RUNNING"):
+        c3.wait_for_job(_job(c3), timeout=-1.0)
+    assert NeutrinoClient._normalize_job_status("JobStatus.running") == "RUNNING"
+    assert NeutrinoClient._normalize_job_status(None) == "UNKNOWN"
+
+
+def test_config_validation():
+    with pytest.raises(ValueError):
+        SubJobConfig.training_job("m", num_gpus=0).to_wire()
+    with pytest.raises(ValueError):
+        SubJobConfig.training_job("m", zero_stage=4).to_wire()
+    with pytest.raises(ValueError):
+        SubJobConfig.training_job("m", learning_rate=0.0).to_wire()
+    with pytest.raises(ValueError):
+        SubJobConfig.sampling_job("m", num_gpus=6, tensor_parallel_size=4).to_wire()
+    w = SubJobConfig.sampling_job("m", num_gpus=8, tensor_parallel_size=4, extra={"seed": 3}).to_wire()
+    assert w["sub_job_type"] == "sampling" and w["vllm_config"]["tensor_parallel_size"] == 4 and w["seed"] == 3
+
+
+def test_large_uploads_are_chunked_and_lost_groups_are_resent(monkeypatch):
+    monkeypatch.setattr(nc, "MAX_CHUNK_BYTES", 16384)
+    c, _ = _client()
+    jid = _job(c)
+    batch = {"input_ids": torch.arange(6000).view(4, 1500)}                       # 48 kB frame: several chunks
+    out = c.forward_backward(jid, batch, sub_job_id="s0")
+    posts = [x for x in c.session.calls if x[0] == "POST" and x[1].endswith("/forward_backward")]
+    assert len(posts) >= 3 and out["metrics"]["n"] == 4 and out["sub_job_id"] == "s0"
+    assert all(p[3]["Content-Type"] == "application/octet-stream" and p[2] == {"sub_job_id": "s0"} for p in posts)
+    # the server forgets the group in the middle: the whole group goes again under a new id
+    c.session.restart_chunk_groups = 1
+    n0 = len(c.session.calls)
+    assert c.forward(jid, batch)["batch"]["log_probs"].shape == (4, 3)
+    resent = [x for x in c.session.calls[n0:] if x[0] == "POST"]
+    assert len(resent) >= len(posts) + 1
+    # ... but not for ever
+    c.session.restart_chunk_groups = 10
+    with pytest.raises(NeutrinoError):
+        c.forward(jid, batch)
+
+
+def test_results_arrive_in_chunks_and_errors_surface():
+    c, _ = _client(FakeServiceSession(chunk_results_over=16384))
+    jid = _job(c)
+    out = c.forward(jid, {"input_ids": torch.zeros(3000, 4, dtype=torch.long)})    # 36 kB of log-probs back
+    assert out["batch"]["log_probs"].shape == (3000, 3)
+    with pytest.raises(NeutrinoError, match="engine exploded"):
+        c._operation(jid, "fail", {})
+    with pytest.raises(NeutrinoError) as e:
+        c.step("missing-job")
+    assert e.value.status == 404
+    with pytest.raises(NeutrinoError):
+        c.wait_request("r-unknown")
+
+
+def test_request_timeout_and_empty_polls():
+    class Silent(FakeServiceSession):
+        def _route(self, method, path, params, body, data):
+            if path.startswith("/requests/"):
+                return FakeResponse(200, {"events": []})
+            return super()._route(method, path, params, body, data)
+    c, sleeps = _client(Silent(), request_timeout=0.05)
+    jid = _job(c)
+    with pytest.raises(NeutrinoError, match="timed out"):
+        c.step(jid)
+    assert sleeps and all(s == 0.01 for s in sleeps)
+
+
+def test_generate_checks_lengths_and_streams():
+    c, _ = _client()
+    jid = _job(c)
+    res = c.generate(jid, [[1, 2, 3], [4]], {"n": 2, "max_tokens": 8}, max_seq_len=16)
+    assert len(res["results"]) == 4
+    with pytest.raises(ValueError, match="prompt 1"):
+        c.generate(jid, [[1], list(range(12))], {"max_tokens": 8}, max_seq_len=16)
+    evs = list(c.generate_stream(jid, [[1, 2]], {"max_tokens": 2}))
+    assert [e["type"] for e in evs] == ["result"]
+    assert c.step(jid, learning_rate=3e-6)["metrics"]["last_lr"] == 3e-6
+    for call, op in ((c.weight_sync, "weight_sync"), (c.reset_prefix_cache, "reset_prefix_cache"),
+                     (c.router_replay_discard, "router_replay_discard")):
+        assert call(jid)["op"] == op
+    assert c.save(jid, path="/ck", step=4, export_hf=True)["body"] == {"path": "/ck", "step": 4, "export_hf": True}
+    assert c.load(jid, step=4)["op"] == "load"
+    assert c.bootstrap_router_replay(jid, {"layer0": torch.zeros(2, 2, dtype=torch.long)})["op"] == "bootstrap_router_replay"
+    assert c.fwd == c.forward_backward and c.fwd_no_grad == c.forward
