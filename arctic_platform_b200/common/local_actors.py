@@ -66,11 +66,11 @@ class SpawnedActor:
             raise ActorError(f"actor failed to start: {payload}")
 
     def _recv(self, timeout: Optional[float]):
-        if not self._conn.poll(timeout):
-            raise ActorDied(f"no answer from actor pid {self._proc.pid} within {timeout}s")
         try:
+            if not self._conn.poll(timeout):
+                raise ActorDied(f"no answer from actor pid {self._proc.pid} within {timeout}s")
             return self._conn.recv()
-        except (EOFError, ConnectionResetError) as exc:
+        except (EOFError, ConnectionResetError, OSError, ValueError) as exc:    # pipe closed: process gone or stopped
             raise ActorDied(f"actor pid {self._proc.pid} exited (code {self._proc.exitcode})") from exc
 
     def call(self, method: str, *args, timeout: Optional[float] = None, **kwargs):
@@ -92,14 +92,17 @@ class SpawnedActor:
         except (ActorDied, ActorError):
             return False
 
-    def kill(self) -> None:
+    def terminate(self) -> None:
+        self.kill(grace_s=0.0)
+
+    def kill(self, grace_s: float = 2.0) -> None:
         try:
-            if self._proc.is_alive():
+            if self._proc.is_alive() and grace_s > 0:
                 try:
                     self._conn.send(None)
                 except Exception:
                     pass
-                self._proc.join(2.0)
+                self._proc.join(grace_s)
             if self._proc.is_alive():
                 self._proc.terminate()
                 self._proc.join(5.0)
@@ -169,6 +172,11 @@ class RankWorkerHandle:
 
     def heartbeat(self, timeout: float = 5.0) -> bool:
         return self.actor.heartbeat(timeout)
+
+    def terminate(self) -> None:
+        """Stops the rank's process outright (the job is lost: a peer failed while this rank may be waiting for it
+        in a collective, where a polite request would never be read)."""
+        self.actor.kill()
 
     def kill(self) -> None:
         """Ends this job's worker; the rank's process stays for the other jobs (the pool ends processes)."""

@@ -80,24 +80,59 @@ class Job:
     info: Dict[str, Any] = field(default_factory=dict)
 
 
-def call_all(workers: Sequence[Any], method: str, per_worker_args: Optional[Sequence[tuple]] = None, *shared_args) -> List[Any]:
+class RanksLost(RuntimeError):
+    """A rank of a job died, or failed while its peers were left waiting for it in a collective; the peers were
+    stopped.  The job cannot continue (recovery = restart from the last checkpoint)."""
+
+
+def _hard_stop(worker) -> None:
+    try:
+        if hasattr(worker, "terminate"):
+            worker.terminate()
+        else:
+            worker.kill()
+    except Exception:
+        pass
+
+
+def call_all(workers: Sequence[Any], method: str, per_worker_args: Optional[Sequence[tuple]] = None, *shared_args,
+             peer_grace_s: float = 30.0) -> List[Any]:
     """Calls ``method`` on every worker AT THE SAME TIME and returns the results in worker order.  The ranks of a
     job run collectives inside these calls (process-group set-up, ZeRO-3 gathers, the optimizer's reduce-scatter),
     so a rank-by-rank loop would block on the first rank for ever; it would also serialise the ranks' compute.
-    The first failure is raised after every call has returned."""
+
+    When one rank fails, its peers may be stuck in a collective that the failed rank will never join.  They get
+    ``peer_grace_s`` seconds to return on their own (none when the rank died outright); those still busy are then
+    stopped and :class:`RanksLost` is raised.  If everybody returned, the first failure is raised as it is."""
     args = [tuple(a) for a in per_worker_args] if per_worker_args is not None else [tuple(shared_args)] * len(workers)
     if len(workers) == 1:
         return [workers[0].call(method, *args[0])]
-    from concurrent.futures import ThreadPoolExecutor
-    with ThreadPoolExecutor(max_workers=len(workers)) as pool:
+    from concurrent.futures import FIRST_EXCEPTION, ThreadPoolExecutor, wait
+    from .local_actors import ActorDied
+    pool = ThreadPoolExecutor(max_workers=len(workers))
+    try:
         futs = [pool.submit(w.call, method, *a) for w, a in zip(workers, args)]
+        done, pending = wait(futs, return_when=FIRST_EXCEPTION)
+        stopped = []
+        if pending:
+            died = any(isinstance(f.exception(), ActorDied) for f in done if f.exception() is not None)
+            _d, pending = wait(pending, timeout=0.0 if died else peer_grace_s)
+            for w, f in zip(workers, futs):
+                if f in pending:
+                    _hard_stop(w)
+                    stopped.append(w)
+            wait(pending, timeout=30.0)
         results, first = [], None
-        for f in futs:
-            try:
-                results.append(f.result())
-            except BaseException as exc:  # noqa: BLE001 - re-raised below
-                results.append(None)
-                first = first or exc
+        for w, f in zip(workers, futs):
+            exc = f.exception() if f.done() else TimeoutError("worker did not return after it was stopped")
+            results.append(None if exc is not None else f.result())
+            if exc is not None and first is None and w not in stopped:      # a stopped peer's error is a consequence
+                first = exc
+    finally:
+        pool.shutdown(wait=False)
+    if stopped:
+        raise RanksLost(f"{method}: a rank failed ({type(first).__name__}: {str(first)[:300]}); "
+                        f"{len(stopped)} waiting peer(s) were stopped") from first
     if first is not None:
         raise first
     return results
@@ -217,6 +252,30 @@ class ArcticRLServerCore:
         return None
 
     # ------------------------------------------------------------------ training / scoring
+    def _fail_job(self, job: Job, why: str) -> None:
+        """Host-side failure handling: the job is marked FAILED and every worker of it is stopped."""
+        job.status = "FAILED"
+        job.info["failure"] = why
+        for w in job.workers:
+            _hard_stop(w)
+
+    def _call_job(self, job: Job, method: str, per_worker_args=None, *shared):
+        from .local_actors import ActorDied
+        try:
+            return call_all(job.workers, method, per_worker_args, *shared)
+        except (ActorDied, RanksLost) as exc:
+            self._fail_job(job, str(exc))
+            raise JobError(500, f"job {job.job_id} FAILED: {exc}") from exc
+
+    def check_workers(self, job_id: int, timeout: float = 5.0) -> Dict[str, Any]:
+        """Liveness probe of every worker of a job (for a watchdog or an operator): a job with a worker that does
+        not answer is marked FAILED and torn down."""
+        job = self._job(job_id)
+        alive = [bool(w.heartbeat(timeout)) if hasattr(w, "heartbeat") else True for w in job.workers]
+        if not all(alive):
+            self._fail_job(job, f"workers {[i for i, a in enumerate(alive) if not a]} do not answer")
+        return {"job_id": job.job_id, "alive": alive, "status": job.status}
+
     def _fan_out(self, job: Job, method: str, payload: Dict[str, Any]) -> List[Dict[str, Any]]:
         batch = payload.get("batch")
         meta = dict(payload.get("meta") or {})
@@ -231,7 +290,7 @@ class ArcticRLServerCore:
             shards = [shards[r // sp] for r in range(n)]
         else:
             shards, order = split_batch_for_ranks(batch, meta, n)
-        results = call_all(job.workers, method, [(shard, meta, processing) for shard in shards])
+        results = self._call_job(job, method, [(shard, meta, processing) for shard in shards])
         if sp > 1:
             # tensors come back complete from every rank of a group: keep the group leader's copy; metrics are sums
             # over the rows each rank scored, so they all count
@@ -257,7 +316,7 @@ class ArcticRLServerCore:
 
     def step(self, job_id: int, learning_rate: Optional[float] = None) -> Dict[str, Any]:
         job = self._job(job_id, ("training",))
-        outs = call_all(job.workers, "step", None, learning_rate)
+        outs = self._call_job(job, "step", None, learning_rate)
         return {"job_id": job.job_id, "metrics": outs[0]["metrics"], "batch": {}}
 
     def empty_training_cache(self, job_id: int) -> Dict[str, Any]:
@@ -274,7 +333,7 @@ class ArcticRLServerCore:
         if not root:
             raise JobError(400, "no checkpoint path configured")
         save_dir, tag = resolve_checkpoint_save_paths(root, step)
-        outs = call_all(job.workers, "save_checkpoint", None, save_dir, tag, export_hf)
+        outs = self._call_job(job, "save_checkpoint", None, save_dir, tag, export_hf)
         if save_total_limit:
             prune_checkpoint_dirs(save_dir, save_total_limit)
         return {"job_id": job.job_id, "path": save_dir, "tag": tag, "files": outs[0].get("files", [])}
@@ -285,7 +344,7 @@ class ArcticRLServerCore:
         if not root:
             raise JobError(400, "no checkpoint path configured")
         tag = f"checkpoint-{step}" if step is not None else None
-        steps = call_all(job.workers, "load_checkpoint", None, root, tag)
+        steps = self._call_job(job, "load_checkpoint", None, root, tag)
         return {"job_id": job.job_id, "global_steps": int(steps[0] or 0)}
 
     # ------------------------------------------------------------------ rollout

@@ -207,3 +207,54 @@ def test_expert_parallel_job_behind_the_server(tmp_path):
     finally:
         core.destroy()
         single.destroy()
+
+
+@pytest.mark.timeout(300)
+def test_a_rank_that_dies_between_steps_fails_the_job_and_frees_its_peer():
+    """Host-side fault: one rank's process is ended between two calls (nothing in flight).  The next call must not
+    leave the surviving rank waiting in a collective: the server stops it, marks the job FAILED and says why."""
+    import time
+    from arctic_platform_b200.common.server import JobError
+    core = ArcticRLServerCore(worker_factory=spawned_worker_factory(_free_port()), training_gpus=2)
+    try:
+        jid = core.initialize(_job(3))["job_id"]
+        _train(core, jid, steps=1)
+        job = core.jobs[jid]
+        assert core.check_workers(jid)["alive"] == [True, True]
+        victim = job.workers[1]
+        victim._proc.terminate()                        # the exact child this test started
+        victim._proc.join(10)
+        t0 = time.time()
+        with pytest.raises(JobError, match="FAILED"):
+            core.forward_backward(jid, _payload())      # rank 0 would wait for rank 1 in the first gather
+        assert time.time() - t0 < 60
+        assert job.status == "FAILED" and "failure" in job.info
+        assert not job.workers[0]._proc.is_alive() and not job.workers[1]._proc.is_alive()
+        with pytest.raises(JobError, match="FAILED"):
+            core.step(jid)                              # a failed job answers with its state, it does not hang
+        # the server itself is fine: a fresh job runs
+        core.destroy(jid)
+        j2 = core.initialize(_job(1))["job_id"]
+        assert _train(core, j2, steps=1)[0][1] > 0
+    finally:
+        core.destroy()
+
+
+@pytest.mark.timeout(300)
+def test_a_rank_that_raises_does_not_leave_its_peer_waiting(monkeypatch):
+    """One rank gets a shard it rejects (host-side error before any collective); the other enters the forward pass
+    and would wait for it in the first ZeRO-3 gather.  After the grace period the waiting rank is stopped."""
+    from arctic_platform_b200.common import server as srv
+    from arctic_platform_b200.common.server import JobError, RanksLost, call_all
+    core = ArcticRLServerCore(worker_factory=spawned_worker_factory(_free_port()), training_gpus=2)
+    try:
+        jid = core.initialize(_job(3))["job_id"]
+        job = core.jobs[jid]
+        p = _payload()
+        good = (p["batch"], p["meta"], p["processing"])
+        bad = ({"input_ids": "not a tensor"}, p["meta"], p["processing"])
+        with pytest.raises(RanksLost, match="waiting peer"):
+            call_all(job.workers, "forward_backward", [good, bad], peer_grace_s=3.0)
+        assert not job.workers[0]._proc.is_alive()
+    finally:
+        core.destroy()
