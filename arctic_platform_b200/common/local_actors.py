@@ -86,6 +86,10 @@ class SpawnedActor:
             raise ActorError(payload)
         return payload
 
+    def alive(self) -> bool:
+        """Whether the process exists -- never blocks, also while a long call is in flight."""
+        return self._proc.is_alive()
+
     def heartbeat(self, timeout: float = 5.0) -> bool:
         try:
             return bool(self.call("__heartbeat__", timeout=timeout))
@@ -172,6 +176,9 @@ class RankWorkerHandle:
 
     def heartbeat(self, timeout: float = 5.0) -> bool:
         return self.actor.heartbeat(timeout)
+
+    def alive(self) -> bool:
+        return self.actor.alive()
 
     def terminate(self) -> None:
         """Stops the rank's process outright (the job is lost: a peer failed while this rank may be waiting for it

@@ -172,6 +172,7 @@ class ArcticRLServerCore:
         self._ids = itertools.count(1)
         self._lock = threading.RLock()
         self.heartbeat_timeout = heartbeat_timeout
+        self._watchdog = None
 
     # ------------------------------------------------------------------ lifecycle
     def initialize(self, job_config: Dict[str, Any]) -> Dict[str, Any]:
@@ -267,11 +268,39 @@ class ArcticRLServerCore:
             self._fail_job(job, str(exc))
             raise JobError(500, f"job {job.job_id} FAILED: {exc}") from exc
 
+    def start_worker_watchdog(self, period_s: float = 10.0) -> None:
+        """Background liveness check of every running job's workers; a job that lost a worker is marked FAILED and
+        torn down without waiting for the client's next call."""
+        if self._watchdog is not None:
+            return
+        stop = threading.Event()
+
+        def loop():
+            while not stop.wait(period_s):
+                with self._lock:
+                    ids = [j.job_id for j in self.jobs.values() if j.status == "RUNNING"]
+                for jid in ids:
+                    try:
+                        self.check_workers(jid)
+                    except JobError:
+                        pass
+        t = threading.Thread(target=loop, name="apb-worker-watchdog", daemon=True)
+        t.start()
+        self._watchdog = (t, stop)
+
+    def stop_worker_watchdog(self) -> None:
+        if self._watchdog is not None:
+            self._watchdog[1].set()
+            self._watchdog[0].join(timeout=5.0)
+            self._watchdog = None
+
     def check_workers(self, job_id: int, timeout: float = 5.0) -> Dict[str, Any]:
         """Liveness probe of every worker of a job (for a watchdog or an operator): a job with a worker that does
         not answer is marked FAILED and torn down."""
         job = self._job(job_id)
-        alive = [bool(w.heartbeat(timeout)) if hasattr(w, "heartbeat") else True for w in job.workers]
+        # process liveness where the worker offers it (never blocks behind a long call), else a round trip
+        alive = [bool(w.alive()) if hasattr(w, "alive") else (bool(w.heartbeat(timeout)) if hasattr(w, "heartbeat") else True)
+                 for w in job.workers]
         if not all(alive):
             self._fail_job(job, f"workers {[i for i, a in enumerate(alive) if not a]} do not answer")
         return {"job_id": job.job_id, "alive": alive, "status": job.status}

@@ -162,3 +162,36 @@ def test_generate_routing_over_replicas():
     assert [o["prompt_index"] for o in out2] == list(range(7)) and out2[0]["rank"] == out2[2]["rank"] == out2[5]["rank"]
     with pytest.raises(JobError):
         core.generate(job["job_id"], prompts, None, routing_key=[1, 2])
+
+
+class _Initable(_Echo):
+    def initialize(self, job_config):
+        return True
+
+    def destroy(self):
+        return None
+
+
+def test_watchdog_marks_a_job_failed_when_a_worker_process_is_gone():
+    import time
+    from arctic_platform_b200.common.local_actors import SpawnedActor
+    core = ArcticRLServerCore(worker_factory=lambda cfg, r, n: SpawnedActor(_Initable))
+    try:
+        jid = core.initialize({"model_name": "x", "job_type": "training", "num_devices": 2})["job_id"]
+        job = core.jobs[jid]
+        assert core.check_workers(jid) == {"job_id": jid, "alive": [True, True], "status": "RUNNING"}
+        core.start_worker_watchdog(period_s=0.1)
+        core.start_worker_watchdog(period_s=0.1)                 # idempotent
+        time.sleep(0.3)
+        assert job.status == "RUNNING"
+        job.workers[0]._proc.terminate()                         # the exact child created above
+        job.workers[0]._proc.join(10)
+        for _ in range(100):
+            if job.status == "FAILED":
+                break
+            time.sleep(0.05)
+        assert job.status == "FAILED" and "do not answer" in job.info["failure"]
+        assert not job.workers[1]._proc.is_alive()               # the peer was stopped with it
+    finally:
+        core.stop_worker_watchdog()
+        core.destroy()
