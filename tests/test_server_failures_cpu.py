@@ -191,6 +191,7 @@ def test_watchdog_marks_a_job_failed_when_a_worker_process_is_gone():
                 break
             time.sleep(0.05)
         assert job.status == "FAILED" and "do not answer" in job.info["failure"]
+        job.workers[1]._proc.join(15)                            # teardown follows the state change
         assert not job.workers[1]._proc.is_alive()               # the peer was stopped with it
     finally:
         core.stop_worker_watchdog()
