@@ -145,6 +145,13 @@ def create_app(core: Optional[ArcticRLServerCore] = None) -> FastAPI:
         await run(app.state.core.heartbeat, job_id)
         return {"status": "ok"}
 
+    @app.get("/job/{job_id}/workers")
+    async def job_workers(job_id: int):
+        try:
+            return app.state.core.check_workers(job_id)
+        except JobError as exc:
+            raise HTTPException(exc.status, str(exc)) from exc
+
     @app.get("/status")
     async def status():
         return app.state.core.status()
@@ -170,6 +177,8 @@ def build_arg_parser() -> argparse.ArgumentParser:
     ap.add_argument("--colocate", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--no-ray-auto-attach", action="store_true")
+    ap.add_argument("--worker-watchdog-seconds", type=float, default=10.0,
+                    help="period of the background liveness check of the rank processes (0 = off)")
     return ap
 
 
@@ -178,6 +187,8 @@ def main(argv=None) -> None:
     args = build_arg_parser().parse_args(argv)
     core = ArcticRLServerCore(training_gpus=args.training_gpus, sampling_gpus=args.sampling_gpus,
                               log_prob_gpus=args.log_prob_gpus, colocate=args.colocate)
+    if args.worker_watchdog_seconds > 0:
+        core.start_worker_watchdog(args.worker_watchdog_seconds)
     uvicorn.run(create_app(core), host=args.host, port=args.port, log_level="info" if args.verbose else "warning")
 
 

@@ -35,6 +35,8 @@ def test_all_routes(api):
     assert api.get(f"/job/{jobs['training']}").json()["job_type"] == "training"
     assert api.post("/heartbeat", params={"job_id": jobs["sampling"]}).json() == {"status": "ok"}
     assert api.post("/heartbeat", params={"job_id": 999}).status_code == 404
+    assert api.get(f"/job/{jobs['training']}/workers").json() == {"job_id": jobs["training"], "alive": [True], "status": "RUNNING"}
+    assert api.get("/job/999/workers").status_code == 404
 
     # rollout, then sleep: a sleeping sampler refuses to generate until it is woken
     code, out = _octet(api, "/generate", {"prompts": [[4, 5, 6], [7, 8]], "sampling_params": {"n": 2, "max_tokens": 3}},
