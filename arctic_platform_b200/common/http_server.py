@@ -145,6 +145,10 @@ def create_app(core: Optional[ArcticRLServerCore] = None) -> FastAPI:
         await run(app.state.core.heartbeat, job_id)
         return {"status": "ok"}
 
+    @app.post("/recover")
+    async def recover(job_id: int, request: LoadCheckpointRequest = Body(default=LoadCheckpointRequest())):
+        return await run(app.state.core.recover, job_id, request.path, request.step)
+
     @app.get("/job/{job_id}/workers")
     async def job_workers(job_id: int):
         try:

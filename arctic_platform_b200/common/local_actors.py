@@ -209,6 +209,8 @@ class RankProcessPool:
     def _actor(self, rank: int) -> SpawnedActor:
         with self._lock:
             a = self.actors.get(rank)
+            if a is not None and not a.alive():       # the rank's process was lost (or stopped with a failed job)
+                a = None
             if a is None:
                 import torch
                 env = {"RANK": str(rank), "LOCAL_RANK": str(rank if torch.cuda.is_available() else 0),

@@ -268,6 +268,29 @@ class ArcticRLServerCore:
             self._fail_job(job, str(exc))
             raise JobError(500, f"job {job.job_id} FAILED: {exc}") from exc
 
+    def recover(self, job_id: int, path: Optional[str] = None, step: Optional[int] = None) -> Dict[str, Any]:
+        """Checkpoint + restart, the platform's recovery path: tears the (failed) job down, starts a new job from the
+        same configuration on fresh worker processes and loads the newest checkpoint of the OLD job (or ``path``).
+        Returns the new job's info with ``recovered_from`` and the restored ``global_steps`` (0 = no checkpoint)."""
+        with self._lock:
+            old = self.jobs.get(int(job_id))
+        if old is None:
+            raise JobError(404, f"unknown job {job_id}")
+        cfg, ckpt = dict(old.config), path or old.info.get("checkpoint_path")
+        for w in old.workers:
+            _hard_stop(w)
+        with self._lock:
+            self.jobs.pop(old.job_id, None)
+        old.status = "DESTROYED"
+        info = dict(self.initialize(cfg))
+        steps = 0
+        if ckpt and old.job_type == "training":
+            import os
+            if os.path.isdir(ckpt):
+                steps = self.load_checkpoint(info["job_id"], ckpt, step)["global_steps"]
+        info.update(recovered_from=old.job_id, global_steps=steps)
+        return info
+
     def start_worker_watchdog(self, period_s: float = 10.0) -> None:
         """Background liveness check of every running job's workers; a job that lost a worker is marked FAILED and
         torn down without waiting for the client's next call."""

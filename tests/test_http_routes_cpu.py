@@ -20,7 +20,7 @@ def _octet(c, path, obj, **params):
     return r.status_code, (wire.loads(r.content) if r.status_code == 200 else r.json())
 
 
-def test_all_routes(api):
+def test_all_routes(api, tmp_path):
     assert api.get("/health").json() == {"status": "ok"}
     jobs = {}
     for jt in ("sampling", "log_prob", "training"):
@@ -103,6 +103,14 @@ def test_all_routes(api):
     assert api.post("/sleep-training", params={"job_id": jobs["training"], "mode": "deep"}).status_code == 400
     assert api.post("/sleep-log-prob", params={"job_id": jobs["log_prob"]}).json()["status"] == "sleeping"
     assert api.post("/wake-log-prob", params={"job_id": jobs["log_prob"]}).json()["status"] == "awake"
+
+    # checkpoint + restart through the API: a new job id, the step counter comes back
+    ck = api.post("/save", params={"job_id": jobs["training"]}, json={"path": str(tmp_path), "step": 1}).json()
+    assert ck["tag"] == "checkpoint-1"
+    rec = api.post("/recover", params={"job_id": jobs["training"]}, json={"path": str(tmp_path)}).json()
+    assert rec["recovered_from"] == jobs["training"] and rec["global_steps"] == 1 and rec["job_id"] != jobs["training"]
+    assert api.post("/recover", params={"job_id": jobs["training"]}).status_code == 404
+    jobs["training"] = rec["job_id"]
 
     # teardown: one job, an unknown job, then everything
     assert api.post("/destroy", params={"job_id": jobs["log_prob"]}).json() == {"destroyed": [jobs["log_prob"]]}

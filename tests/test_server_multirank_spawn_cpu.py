@@ -258,3 +258,37 @@ def test_a_rank_that_raises_does_not_leave_its_peer_waiting(monkeypatch):
         assert not job.workers[0]._proc.is_alive()
     finally:
         core.destroy()
+
+
+@pytest.mark.timeout(600)
+def test_recovery_is_checkpoint_plus_restart(tmp_path):
+    """Train, checkpoint, lose a rank (host-side: its process is ended between calls), recover: a new job on fresh
+    rank processes continues from the checkpoint exactly as the uninterrupted run does."""
+    from arctic_platform_b200.common.server import JobError
+    steady = ArcticRLServerCore()
+    js = steady.initialize(_job(3))["job_id"]
+    want = _train(steady, js, steps=3)
+    core = ArcticRLServerCore(training_gpus=2)                                  # rank process pool
+    try:
+        job_cfg = {**_job(3), "checkpoint_path": str(tmp_path)}
+        jid = core.initialize(job_cfg)["job_id"]
+        got = _train(core, jid, steps=2)
+        saved = core.save(jid, step=2)
+        assert saved["tag"] == "checkpoint-2"
+        lost = core.pool.actors[1]
+        lost._proc.terminate()                                                  # the exact child of this pool
+        lost._proc.join(10)
+        with pytest.raises(JobError, match="FAILED"):
+            core.forward_backward(jid, _payload())
+        assert core.get_job_status(jid)["status"] == "FAILED"
+        info = core.recover(jid)
+        assert info["recovered_from"] == jid and info["global_steps"] == 2 and info["job_id"] != jid
+        assert all(a.alive() for a in core.pool.actors.values()) and len(core.pool.actors) == 2
+        got += _train(core, info["job_id"], steps=1)
+        for (la, na), (lb, nb) in zip(got, want):
+            assert la == pytest.approx(lb, rel=1e-4, abs=1e-6) and na == pytest.approx(nb, rel=1e-4)
+        with pytest.raises(JobError):
+            core.recover(12345)
+    finally:
+        core.destroy()
+        steady.destroy()
