@@ -160,6 +160,12 @@ class ArcticRLHttpClient:
     async def load_checkpoint(self, path=None, step=None):
         return self._json("/load-checkpoint", {"job_id": self._need("training")}, {"path": path, "step": step})
 
+    async def recover_training(self, path=None, step=None):
+        """Checkpoint + restart of the training job after a failure; this client follows the job to its new id."""
+        out = self._json("/recover", {"job_id": self._need("training")}, {"path": path, "step": step})
+        self.job_ids["training"] = out["job_id"]
+        return out
+
     async def save_weights(self, path: str):
         return self._json("/save", {"job_id": self._need("training")}, {"path": path, "export_hf": True})
 

@@ -107,6 +107,12 @@ class ArcticRLLocalClient:
     async def load_checkpoint(self, path: Optional[str] = None, step: Optional[int] = None) -> Dict[str, Any]:
         return self.server.load_checkpoint(self._need("training"), path, step)
 
+    async def recover_training(self, path: Optional[str] = None, step: Optional[int] = None) -> Dict[str, Any]:
+        """Checkpoint + restart of the training job after a failure; this client follows the job to its new id."""
+        out = self.server.recover(self._need("training"), path, step)
+        self.job_ids["training"] = out["job_id"]
+        return out
+
     async def save_weights(self, path: str) -> Dict[str, Any]:
         """Hugging Face safetensors export of the current training weights."""
         return self.server.save(self._need("training"), path, None, True, None)

@@ -59,6 +59,10 @@ def test_http_training_loop_and_errors(server, tmp_path):
     loaded = c.call("load_checkpoint", None, 3)
     assert loaded["global_steps"] == 1
     assert c.call("sleep_log_prob")["status"] == "sleeping" and c.call("wake_log_prob")["status"] == "awake"
+    before = c.job_ids["training"]
+    rec = c.call("recover_training")                     # checkpoint + restart: same weights and step counter, new id
+    assert rec["recovered_from"] == before and rec["global_steps"] == 1 and c.job_ids["training"] == rec["job_id"] != before
+    assert c.call("weight_norm")["training_norm"] == pytest.approx(norms["training_norm"], rel=1e-6)
     with pytest.raises(RuntimeError, match="no sampling job"):
         c.call("generate", [[1, 2, 3]])
     # reconnect: a second client attaches to the same jobs without re-initialising
