@@ -385,10 +385,41 @@ class EngineWorker:
         return [grid[i, :len(c)].tolist() for i, c in enumerate(completions)]
 
     # ------------------------------------------------------------------ rollout
+    def _tokenizer_for(self):
+        """The checkpoint's tokenizer when ``model_name`` is a directory that ships one (local files only); ``None``
+        for presets and weight-only directories.  Loaded on first use."""
+        if not hasattr(self, "_tokenizer"):
+            self._tokenizer = None
+            from pathlib import Path
+            path = Path(str(self.job_config.get("tokenizer") or self.job_config.get("model_name", "")))
+            if path.is_dir() and any((path / f).exists() for f in ("tokenizer.json", "tokenizer_config.json", "tokenizer.model")):
+                try:
+                    from transformers import AutoTokenizer
+                    self._tokenizer = AutoTokenizer.from_pretrained(str(path), local_files_only=True)
+                except Exception as exc:  # noqa: BLE001 - generation by token ids still works
+                    import logging
+                    logging.getLogger(__name__).warning("could not load the tokenizer under %s: %s", path, exc)
+        return self._tokenizer
+
     def generate(self, prompts, sampling_params=None) -> List[dict]:
+        """Token ids in, token ids out.  With a tokenizer beside the checkpoint, text prompts are accepted too and
+        every result carries its decoded ``text`` (the reference's samplers return text the same way)."""
         if self.sampler is None:
             raise RuntimeError("worker has no sampling engine")
-        return self.sampler.generate(prompts, sampling_params)
+        tok = self._tokenizer_for() if prompts and (any(isinstance(p, str) for p in prompts)
+                                                      or (sampling_params or {}).get("detokenize", True)) else None
+        if any(isinstance(p, str) for p in prompts):
+            if tok is None:
+                raise ValueError("text prompts need a tokenizer beside the checkpoint (or job_config['tokenizer'])")
+            prompts = [tok.encode(p, add_special_tokens=False) if isinstance(p, str) else p for p in prompts]
+        sp = {k: v for k, v in (sampling_params or {}).items() if k != "detokenize"} if isinstance(sampling_params, dict) \
+            else sampling_params
+        outs = self.sampler.generate(prompts, sp)
+        if tok is not None:
+            for o in outs:
+                o["text"] = tok.decode(o["token_ids"], skip_special_tokens=bool((sp or {}).get("skip_special_tokens", True))
+                                       if isinstance(sp, dict) else True)
+        return outs
 
     # ------------------------------------------------------------------ weights
     def iter_weights(self):

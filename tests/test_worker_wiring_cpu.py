@@ -114,3 +114,31 @@ def test_token_budget_micro_batches_keep_results_and_order():
         assert out["metrics"]["loss.tokens"] == float(mask[:, -R:].sum())
     assert torch.allclose(grads["budget"], grads["whole"], atol=1e-6, rtol=1e-4)
     assert torch.allclose(grads["four"], grads["whole"], atol=1e-6, rtol=1e-4)
+
+
+def test_sampler_worker_uses_the_tokenizer_that_ships_with_a_checkpoint(tmp_path):
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+    from arctic_platform_b200.models.config import PRESETS
+    from arctic_platform_b200.models.decoder import DecoderLM
+    from arctic_platform_b200.models.hf_io import save_hf_checkpoint
+    ck = tmp_path / "ck"
+    save_hf_checkpoint(DecoderLM(PRESETS["qwen3-tiny"], "cpu", torch.float32).init_weights(seed=1), ck)
+    w = EngineWorker("cpu")
+    w.initialize({"model_name": str(ck), "job_type": "sampling", "vllm_config": {"max_model_len": 64}})
+    out = w.generate([[5, 6, 7]], {"n": 1, "max_tokens": 3, "temperature": 0.0})
+    assert out[0]["text"] is None                                   # weights only: ids in, ids out
+    with pytest.raises(ValueError, match="tokenizer"):
+        w.generate(["hello"], {"max_tokens": 2})
+    vocab = {**{f"w{i}": i for i in range(1, PRESETS["qwen3-tiny"].vocab_size)}, "[UNK]": 0}
+    tk = Tokenizer(models.WordLevel(vocab, unk_token="[UNK]"))
+    tk.pre_tokenizer = pre_tokenizers.Whitespace()
+    PreTrainedTokenizerFast(tokenizer_object=tk, unk_token="[UNK]").save_pretrained(str(ck))
+    w2 = EngineWorker("cpu")
+    w2.initialize({"model_name": str(ck), "job_type": "sampling", "vllm_config": {"max_model_len": 64}})
+    ids = w2.generate([[5, 6, 7]], {"n": 1, "max_tokens": 3, "temperature": 0.0})
+    txt = w2.generate(["w5 w6 w7"], {"n": 1, "max_tokens": 3, "temperature": 0.0})
+    assert txt[0]["token_ids"] == ids[0]["token_ids"] == out[0]["token_ids"]
+    assert txt[0]["text"] == " ".join(f"w{t}" for t in txt[0]["token_ids"]) and txt[0]["prompt_len"] == 3
+    quiet = w2.generate([[5, 6, 7]], {"n": 1, "max_tokens": 3, "temperature": 0.0, "detokenize": False})
+    assert quiet[0]["text"] is None
