@@ -180,6 +180,7 @@ class EngineWorker:
         if path.is_dir() and any(path.glob("*.safetensors")):
             # converted once per node when a cache directory is configured, else straight from the shards
             load_through_cache(m, path, cache_dir=job_config.get("weight_conversion_cache_dir"))
+            m.source_dir = str(path)                 # exports take the tokenizer files from here
         else:
             m.init_weights(seed=seed)     # no checkpoint on disk: deterministic random initialisation
         return m

@@ -164,6 +164,7 @@ def _instantiate(ctx: LoaderContext, device, seed: int) -> DecoderLM:
     p = Path(ctx.spec.model_path_or_name)
     if p.is_dir() and any(p.glob("*.safetensors")):
         load_through_cache(model, p, cache_dir=ctx.spec.loader_options.get("weight_conversion_cache_dir"))
+        model.source_dir = str(p)
     else:
         model.init_weights(seed=seed)
     return model

@@ -309,7 +309,28 @@ def save_hf_checkpoint(model, out_dir, max_shard_bytes: int = 4 << 30, tensors=N
             weight_map[k] = fn
     if len(shards) > 1:
         (out / "model.safetensors.index.json").write_text(json.dumps({"metadata": {}, "weight_map": weight_map}))
+    copy_tokenizer_files(getattr(model, "source_dir", None), out)
     return files
+
+
+TOKENIZER_FILES = ("tokenizer.json", "tokenizer_config.json", "tokenizer.model", "special_tokens_map.json", "vocab.json",
+                   "merges.txt", "added_tokens.json", "generation_config.json", "chat_template.jinja", "chat_template.json")
+
+
+def copy_tokenizer_files(source_dir, out_dir) -> List[str]:
+    """An exported checkpoint is loadable on its own: the tokenizer, generation config and chat template of the
+    checkpoint the model was loaded from travel with the new weights."""
+    import shutil
+    if not source_dir:
+        return []
+    src, dst, done = Path(source_dir), Path(out_dir), []
+    if not src.is_dir() or src.resolve() == dst.resolve():
+        return []
+    for name in TOKENIZER_FILES:
+        if (src / name).is_file():
+            shutil.copy2(src / name, dst / name)
+            done.append(name)
+    return done
 
 
 def load_hf_checkpoint(model, ckpt_dir, strict: bool = True) -> int:

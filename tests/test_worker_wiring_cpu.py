@@ -142,3 +142,10 @@ def test_sampler_worker_uses_the_tokenizer_that_ships_with_a_checkpoint(tmp_path
     assert txt[0]["text"] == " ".join(f"w{t}" for t in txt[0]["token_ids"]) and txt[0]["prompt_len"] == 3
     quiet = w2.generate([[5, 6, 7]], {"n": 1, "max_tokens": 3, "temperature": 0.0, "detokenize": False})
     assert quiet[0]["text"] is None
+    # a training worker loaded from that directory exports checkpoints that carry the tokenizer along
+    t = EngineWorker("cpu")
+    t.initialize({"model_name": str(ck), "job_type": "training", "ds_config": {"zero_optimization": {"stage": 1}}})
+    t.export_hf_checkpoint(str(tmp_path / "export"))
+    assert (tmp_path / "export" / "tokenizer.json").exists() and (tmp_path / "export" / "config.json").exists()
+    from transformers import AutoTokenizer
+    assert AutoTokenizer.from_pretrained(str(tmp_path / "export"), local_files_only=True).encode("w5 w6", add_special_tokens=False) == [5, 6]
