@@ -415,11 +415,29 @@ class EngineWorker:
             prompts = [tok.encode(p, add_special_tokens=False) if isinstance(p, str) else p for p in prompts]
         sp = {k: v for k, v in (sampling_params or {}).items() if k != "detokenize"} if isinstance(sampling_params, dict) \
             else sampling_params
+        text_stops: List[str] = []
+        if isinstance(sp, dict) and sp.get("stop"):
+            # stop STRINGS: one-token strings end the sequence in the sampler itself; longer ones cut the decoded text
+            if tok is None:
+                raise ValueError("stop strings need a tokenizer beside the checkpoint; use stop_token_ids")
+            stops = [sp["stop"]] if isinstance(sp["stop"], str) else list(sp["stop"])
+            ids = list(sp.get("stop_token_ids") or [])
+            for st in stops:
+                enc = tok.encode(st, add_special_tokens=False)
+                if len(enc) == 1:
+                    ids.append(int(enc[0]))
+                else:
+                    text_stops.append(st)
+            sp = {**{k: v for k, v in sp.items() if k != "stop"}, "stop_token_ids": ids}
         outs = self.sampler.generate(prompts, sp)
         if tok is not None:
+            skip = bool(sp.get("skip_special_tokens", True)) if isinstance(sp, dict) else True
             for o in outs:
-                o["text"] = tok.decode(o["token_ids"], skip_special_tokens=bool((sp or {}).get("skip_special_tokens", True))
-                                       if isinstance(sp, dict) else True)
+                o["text"] = tok.decode(o["token_ids"], skip_special_tokens=skip)
+                cuts = [o["text"].find(st) for st in text_stops if st in o["text"]]
+                if cuts:
+                    o["text"] = o["text"][:min(cuts)]
+                    o["finish_reason"] = "stop"
         return outs
 
     # ------------------------------------------------------------------ weights

@@ -142,6 +142,17 @@ def test_sampler_worker_uses_the_tokenizer_that_ships_with_a_checkpoint(tmp_path
     assert txt[0]["text"] == " ".join(f"w{t}" for t in txt[0]["token_ids"]) and txt[0]["prompt_len"] == 3
     quiet = w2.generate([[5, 6, 7]], {"n": 1, "max_tokens": 3, "temperature": 0.0, "detokenize": False})
     assert quiet[0]["text"] is None
+    # stop strings: a one-token string ends the sequence in the sampler, a longer one cuts the decoded text
+    full = ids[0]["token_ids"]
+    stop_tok = full[1]
+    cut = w2.generate([[5, 6, 7]], {"n": 1, "max_tokens": 3, "temperature": 0.0, "stop": f"w{stop_tok}"})
+    assert cut[0]["token_ids"] == full[:full.index(stop_tok) + 1] and cut[0]["finish_reason"] == "stop"
+    two = " ".join(f"w{t}" for t in full[1:3])
+    cut2 = w2.generate([[5, 6, 7]], {"n": 1, "max_tokens": 3, "temperature": 0.0, "stop": [two]})
+    whole = " ".join(f"w{t}" for t in full)
+    assert cut2[0]["token_ids"] == full and cut2[0]["text"] == whole[:whole.find(two)] and cut2[0]["finish_reason"] == "stop"
+    with pytest.raises(ValueError, match="stop strings"):
+        w.generate([[5, 6, 7]], {"max_tokens": 2, "stop": "x"})
     # a training worker loaded from that directory exports checkpoints that carry the tokenizer along
     t = EngineWorker("cpu")
     t.initialize({"model_name": str(ck), "job_type": "training", "ds_config": {"zero_optimization": {"stage": 1}}})
