@@ -7,7 +7,8 @@ policy update is taken per batch.
         --training-gpus 8 --sampling-gpus 8 --batch-prompts 64 --n 16 --max-tokens 4096
 
 A tokenizer directory (``--tokenizer``) is needed for real checkpoints; without one a byte-level codec is used,
-which is enough for the tiny presets and the tests."""
+which is enough for the tiny presets and the tests.  The reference drives the same loop through SkyRL's trainer
+(recipes/rl/skyrl/*/arctic_rl/entrypoint.py and the ``run_qwen3_*_grpo_arl.sh`` launchers beside them)."""
 from __future__ import annotations
 
 import argparse
