@@ -39,6 +39,9 @@ PAGE = 16
 MAX_NQ = 16
 
 
+_WARNED_KEYS: set = set()
+
+
 @dataclass
 class SamplingParams:
     n: int = 1
@@ -60,6 +63,16 @@ class SamplingParams:
                 setattr(sp, k, d[k])
         if d.get("stop_token_ids"):
             sp.stop_token_ids = tuple(int(x) for x in d["stop_token_ids"])
+        # keys of other samplers that would change the distribution if honoured: say so once instead of silently
+        # sampling from a different policy than the caller believes
+        for k in ("repetition_penalty", "presence_penalty", "frequency_penalty", "min_p", "min_tokens", "logit_bias",
+                  "bad_words", "best_of", "use_beam_search"):
+            v = d.get(k)
+            neutral = {"repetition_penalty": 1.0, "best_of": sp.n}.get(k, 0)
+            if v not in (None, False, neutral, [], {}) and k not in _WARNED_KEYS:
+                _WARNED_KEYS.add(k)
+                import logging
+                logging.getLogger(__name__).warning("sampling parameter %s=%r is not supported and is ignored", k, v)
         return sp
 
 
