@@ -96,14 +96,15 @@ def _hard_stop(worker) -> None:
 
 
 def call_all(workers: Sequence[Any], method: str, per_worker_args: Optional[Sequence[tuple]] = None, *shared_args,
-             peer_grace_s: float = 30.0) -> List[Any]:
+             peer_grace_s: Optional[float] = 30.0) -> List[Any]:
     """Calls ``method`` on every worker AT THE SAME TIME and returns the results in worker order.  The ranks of a
     job run collectives inside these calls (process-group set-up, ZeRO-3 gathers, the optimizer's reduce-scatter),
     so a rank-by-rank loop would block on the first rank for ever; it would also serialise the ranks' compute.
 
     When one rank fails, its peers may be stuck in a collective that the failed rank will never join.  They get
     ``peer_grace_s`` seconds to return on their own (none when the rank died outright); those still busy are then
-    stopped and :class:`RanksLost` is raised.  If everybody returned, the first failure is raised as it is."""
+    stopped and :class:`RanksLost` is raised.  If everybody returned, the first failure is raised as it is.
+    ``peer_grace_s=None`` is for workers that never wait for one another (sampler replicas): nobody is stopped."""
     args = [tuple(a) for a in per_worker_args] if per_worker_args is not None else [tuple(shared_args)] * len(workers)
     if len(workers) == 1:
         return [workers[0].call(method, *args[0])]
@@ -116,7 +117,10 @@ def call_all(workers: Sequence[Any], method: str, per_worker_args: Optional[Sequ
         stopped = []
         if pending:
             died = any(isinstance(f.exception(), ActorDied) for f in done if f.exception() is not None)
-            _d, pending = wait(pending, timeout=0.0 if died else peer_grace_s)
+            if peer_grace_s is None:
+                _d, pending = wait(pending)
+            else:
+                _d, pending = wait(pending, timeout=0.0 if died else peer_grace_s)
             for w, f in zip(workers, futs):
                 if f in pending:
                     _hard_stop(w)
@@ -514,7 +518,7 @@ class ArcticRLServerCore:
     # ------------------------------------------------------------------ sleep / wake
     def sleep_inference(self, job_id: int, level: int = 1) -> Dict[str, Any]:
         job = self._job(job_id, ("sampling",))
-        call_all(job.workers, "sleep_inference", None, level)
+        call_all(job.workers, "sleep_inference", None, level, peer_grace_s=None)
         return {"job_id": job.job_id, "status": "sleeping"}
 
     def wake_inference(self, job_id: int, tags=None) -> Dict[str, Any]:
@@ -529,12 +533,12 @@ class ArcticRLServerCore:
                     call_all(tj.workers, "empty_cache")
                 except Exception:
                     pass
-        call_all(job.workers, "wake_inference", None, tags)
+        call_all(job.workers, "wake_inference", None, tags, peer_grace_s=None)
         return {"job_id": job.job_id, "status": "awake"}
 
     def reset_prefix_cache(self, job_id: int) -> Dict[str, Any]:
         job = self._job(job_id, ("sampling",))
-        call_all(job.workers, "reset_prefix_cache")
+        call_all(job.workers, "reset_prefix_cache", peer_grace_s=None)
         return {"job_id": job.job_id, "status": "ok"}
 
     def sleep_training(self, job_id: int, mode: str = "all") -> Dict[str, Any]:
