@@ -440,7 +440,8 @@ class ArcticRLServerCore:
             share = [list(range(r, len(prompts), n)) for r in range(n)]
             active = [(w, idx) for w, idx in zip(job.workers, share) if idx]
             outs = call_all([w for w, _ in active], "score_completions",
-                            [([prompts[i] for i in idx], [completions[i] for i in idx]) for _, idx in active])
+                            [([prompts[i] for i in idx], [completions[i] for i in idx]) for _, idx in active],
+                            peer_grace_s=None)
             rows = [None] * len(prompts)
             for (_, idx), res in zip(active, outs):
                 for i, r in zip(idx, res):
