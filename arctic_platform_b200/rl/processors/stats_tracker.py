@@ -93,9 +93,13 @@ class DistributedStatsTracker:
                 if rt is None:
                     mins = [float(v[m].min()) for v, m in items if m.any()]
                     maxs = [float(v[m].max()) for v, m in items if m.any()]
-                    if mins:
-                        out[skey + "/min"] = float(allreduce(torch.tensor(min(mins), dtype=torch.float64), dist.ReduceOp.MIN))
-                        out[skey + "/max"] = float(allreduce(torch.tensor(max(maxs), dtype=torch.float64), dist.ReduceOp.MAX))
+                    # a rank whose masks are all empty still takes part in the reductions (with the neutral element):
+                    # collectives that only some ranks enter would never complete
+                    if mins or do_reduce:
+                        lo = float(allreduce(torch.tensor(min(mins, default=float("inf")), dtype=torch.float64), dist.ReduceOp.MIN))
+                        hi = float(allreduce(torch.tensor(max(maxs, default=float("-inf")), dtype=torch.float64), dist.ReduceOp.MAX))
+                        if lo != float("inf"):
+                            out[skey + "/min"], out[skey + "/max"] = lo, hi
             elif rt == ReduceType.SUM:
                 out[skey] = float(allreduce(torch.tensor(s, dtype=torch.float64), dist.ReduceOp.SUM))
             elif rt == ReduceType.MIN:
