@@ -43,6 +43,20 @@ def split_microbatches(batch: Dict[str, torch.Tensor], n: int) -> List[Dict[str,
     return outs
 
 
+def _loss_free_row(batch: Dict[str, Any]) -> Dict[str, Any]:
+    """One row of ``batch`` that contributes nothing to the loss (masks and labels cleared), marked ``_dummy`` so that
+    its outputs are dropped: a filler pass that keeps a rank in step with its peers' collectives."""
+    B = batch["input_ids"].shape[0]
+    row = {k: (v[:1].clone() if torch.is_tensor(v) and v.dim() > 0 and v.shape[0] == B else v) for k, v in batch.items()}
+    for k in ("response_mask", "loss_mask"):
+        if k in row:
+            row[k] = torch.zeros_like(row[k])
+    if "labels" in row:
+        row["labels"] = torch.full_like(row["labels"], -100)
+    row["_dummy"] = True
+    return row
+
+
 # the process group a worker of this process created from the launcher's environment, and how many workers use it
 _PG = {"created_here": False, "users": 0}
 
@@ -229,7 +243,8 @@ class EngineWorker:
                 if offload is not None:
                     offload.release()
                 per_mb.append(r["metrics"])
-                outs.append(r)
+                if not (isinstance(mb, dict) and mb.get("_dummy")):
+                    outs.append(r)                           # a filler pass has no rows of the caller's batch
         if prof.report and self.rank == 0:
             print(f"[profile] {tag}: {prof.report}", flush=True)
         see_memory_usage(f"{tag} end")
@@ -289,6 +304,15 @@ class EngineWorker:
                                                             meta.get("max_rollouts"), dp_group=group)
         else:
             mbs, rows = split_padded_tensor_dict_into_mb_list(batch, MicroBatchSpec(budget), group)
+        # every rank must run the same number of passes (the ZeRO-3 gathers and the gradient reduction are
+        # collectives): a rank whose rows fit into fewer micro-batches pads with loss-free copies of its first row
+        import torch.distributed as dist
+        if dist.is_initialized() and self.engine.world > 1:
+            n = torch.tensor([len(mbs)], dtype=torch.int64)
+            n = n.to(self.device if dist.get_backend(group) == "nccl" else "cpu")
+            dist.all_reduce(n, op=dist.ReduceOp.MAX, group=group)
+            while len(mbs) < int(n):
+                mbs.append(_loss_free_row(batch))
         return mbs, torch.tensor([i for r in rows for i in r], dtype=torch.long)
 
     def _with_rl_global_counts(self, mbs, meta, processing):

@@ -292,3 +292,41 @@ def test_recovery_is_checkpoint_plus_restart(tmp_path):
     finally:
         core.destroy()
         steady.destroy()
+
+
+@pytest.mark.timeout(600)
+def test_token_budget_micro_batches_stay_in_step_across_ranks():
+    """Two ZeRO-3 ranks whose shards need different numbers of token-budget micro-batches: the rank with fewer pads
+    with loss-free passes, so the per-pass gathers line up; results equal one process on the whole batch."""
+    ids, mask, R = make_grpo_batch(n_prompts=4, n_samples=2, seed=21, p_rng=(4, 8), r_rng=(2, 6))
+    # rank 0's half: long sequences; rank 1's half: short ones -> different micro-batch counts under one budget
+    ids2, mask2, _ = make_grpo_batch(n_prompts=4, n_samples=2, seed=22, p_rng=(30, 40), r_rng=(2, 6))
+    P = ids2.shape[1] - R
+    big_ids = torch.zeros(8, P + R, dtype=torch.int64)
+    big_mask = torch.zeros_like(big_ids)
+    big_ids[:, P - (ids.shape[1] - R):] = ids
+    big_mask[:, P - (mask.shape[1] - R):] = mask
+    all_ids, all_mask = torch.cat([ids2[:4], big_ids[:4]]), torch.cat([mask2[:4], big_mask[:4]])
+    B = all_ids.shape[0]
+    g = torch.Generator().manual_seed(2)
+    batch = {"input_ids": all_ids, "attention_mask": all_mask, "response_mask": all_mask[:, -R:].contiguous(),
+             "old_log_probs": torch.randn(B, R, generator=g) * 0.01 - 2.0,
+             "advantages": torch.randn(B, 1, generator=g).expand(B, R).contiguous()}
+    budget = int(all_mask.sum(1).max()) + 4
+    meta = {"response_length": R, "zorro_train_enable": False, "max_tokens_per_mb": budget}
+    single = ArcticRLServerCore()
+    j1 = single.initialize(_job(3))["job_id"]
+    want_lp = single.forward(j1, {"batch": batch, "meta": dict(meta)})["batch"]["log_probs"]
+    want = single.forward_backward(j1, {"batch": batch, "meta": dict(meta), "processing": {"loss_fn": "verl_grpo"}})
+    want_norm = single.step(j1)["metrics"]["grad_norm"]
+    core = ArcticRLServerCore(worker_factory=spawned_worker_factory(_free_port()), training_gpus=2)
+    try:
+        jid = core.initialize(_job(3))["job_id"]
+        got_lp = core.forward(jid, {"batch": batch, "meta": dict(meta)})["batch"]["log_probs"]
+        assert torch.allclose(got_lp, want_lp, atol=1e-5)
+        got = core.forward_backward(jid, {"batch": batch, "meta": dict(meta), "processing": {"loss_fn": "verl_grpo"}})
+        assert got["avg_loss"] == pytest.approx(want["avg_loss"], rel=1e-4, abs=1e-6)
+        assert core.step(jid)["metrics"]["grad_norm"] == pytest.approx(want_norm, rel=1e-4)
+    finally:
+        core.destroy()
+        single.destroy()
