@@ -180,6 +180,10 @@ class RankWorkerHandle:
     def alive(self) -> bool:
         return self.actor.alive()
 
+    def sync_to(self, dst: "RankWorkerHandle") -> int:
+        """Weight hand-over to another job's engine in the SAME rank process (the in-process kernel runs there)."""
+        return self.actor.call("sync", self.key, dst.key)
+
     def terminate(self) -> None:
         """Stops the rank's process outright (the job is lost: a peer failed while this rank may be waiting for it
         in a collective, where a polite request would never be read)."""

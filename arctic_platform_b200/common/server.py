@@ -165,8 +165,17 @@ class ArcticRLServerCore:
             if ranks > 1:
                 # more than one rank per job: one long-lived process per GPU hosting that GPU's engines of every
                 # job (the ranks need a process group; colocated engines need to share a process)
-                from .local_actors import RankProcessPool
-                self.pool = RankProcessPool(ranks, master_port or _free_port(), colocate=colocate)
+                from .ray_cluster import ray_available
+                ray_up = False
+                if ray_available():
+                    import ray
+                    ray_up = ray.is_initialized()
+                if ray_up:                        # a Ray cluster is attached: one actor per GPU, placed by Ray
+                    from .ray_actors import RayRankPool
+                    self.pool = RayRankPool(ranks, master_port or _free_port(), colocate=colocate)
+                else:
+                    from .local_actors import RankProcessPool
+                    self.pool = RankProcessPool(ranks, master_port or _free_port(), colocate=colocate)
                 worker_factory = self.pool.factory
             else:
                 worker_factory = default_worker_factory

@@ -82,7 +82,7 @@ def sync_pair(src, dst, cuda_ipc: Optional[bool] = None, low_memory: Optional[bo
         return {"strategy": "in_process", "num_tensors": sync_weights_in_process(src, dst)}
     if same_rank_process(src, dst) and cuda_ipc is not False:
         # both engines live in the same spawned rank process: the in-process kernel runs there
-        return {"strategy": "in_process", "num_tensors": src.actor.call("sync", src.key, dst.key)}
+        return {"strategy": "in_process", "num_tensors": src.sync_to(dst)}
     if via_file:
         return {"strategy": "cpu_file", "num_tensors": sync_weights_cpu_file(src, dst)}
     if low_memory:
