@@ -189,6 +189,10 @@ def build_arg_parser() -> argparse.ArgumentParser:
 def main(argv=None) -> None:
     import uvicorn
     args = build_arg_parser().parse_args(argv)
+    from .ray_cluster import init_ray_cluster
+    cluster = init_ray_cluster(auto_attach=not args.no_ray_auto_attach)     # {"ray": False} without Ray: local ranks
+    if args.verbose:
+        print(f"[server] cluster: {cluster}", flush=True)
     core = ArcticRLServerCore(training_gpus=args.training_gpus, sampling_gpus=args.sampling_gpus,
                               log_prob_gpus=args.log_prob_gpus, colocate=args.colocate)
     if args.worker_watchdog_seconds > 0:
