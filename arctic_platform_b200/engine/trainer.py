@@ -104,6 +104,11 @@ class EngineConfig:
         cfg.zero_stage = int(zero.get("stage", 1))
         cfg.offload_optimizer = (zero.get("offload_optimizer") or {}).get("device", "none") == "cpu"
         cfg.impl = ds.get("b200_impl", "fused")
+        if (ds.get("fp16") or {}).get("enabled"):
+            import logging
+            logging.getLogger(__name__).warning(
+                "fp16.enabled is set: this engine computes in bf16 with fp32 master weights and gradients (no loss "
+                "scaling is needed); the fp16 block is ignored")
         return cfg
 
 
