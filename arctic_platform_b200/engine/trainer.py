@@ -104,6 +104,11 @@ class EngineConfig:
         cfg.zero_stage = int(zero.get("stage", 1))
         cfg.offload_optimizer = (zero.get("offload_optimizer") or {}).get("device", "none") == "cpu"
         cfg.impl = ds.get("b200_impl", "fused")
+        if (zero.get("offload_param") or {}).get("device", "none") not in ("none", None):
+            import logging
+            logging.getLogger(__name__).warning(
+                "zero_optimization.offload_param is set: parameter shards stay in device memory (peers read them over "
+                "NVLink); use offload_optimizer to move the fp32 state to the host")
         if (ds.get("fp16") or {}).get("enabled"):
             import logging
             logging.getLogger(__name__).warning(
