@@ -1,0 +1,70 @@
+"""Import-compatibility alias: ``arctic_platform.<x>`` resolves to ``arctic_platform_b200.<x>``.
+
+Code written against the reference platform (``from arctic_platform.rl import ArcticRLClientConfig,
+create_arctic_rl_client``; ``from arctic_platform import wire``; ``arctic_platform.integrations.verl...``) runs on this
+build without edits.  The alias is a meta-path finder, so every sub-module is the SAME module object under both names
+(no second copy, registries and singletons stay single)."""
+from __future__ import annotations
+
+import importlib
+import importlib.abc
+import importlib.util
+import sys
+
+_TARGET = "arctic_platform_b200"
+_ALIAS = __name__
+
+# where the reference keeps a module under a different path than this build
+_MOVED = {
+    "common.deepspeed_worker": "engine.worker",
+    "common.utils.debug": "utils.debug",
+    "common.utils.sft_profile": "utils.sft_profile",
+    "common.utils.record_replay": "utils.record_replay",
+    "rl.zorro_train.zorro_train": "rl.zorro_train.layout",
+    "model.loader": "models.factory",
+    "model.patch": "models.factory",
+}
+
+
+class _AliasLoader(importlib.abc.Loader):
+    def __init__(self, real_name: str):
+        self.real_name = real_name
+
+    def create_module(self, spec):
+        mod = importlib.import_module(self.real_name)
+        self._real_spec = mod.__spec__
+        return mod
+
+    def exec_module(self, module):
+        # already executed under its real name; the import machinery has just stamped the alias spec on it -- put the
+        # real one back, the module's own relative imports go by it
+        module.__spec__ = self._real_spec
+
+
+class _AliasFinder(importlib.abc.MetaPathFinder):
+    def find_spec(self, fullname, path=None, target=None):
+        if not fullname.startswith(_ALIAS + "."):
+            return None
+        rest = fullname[len(_ALIAS) + 1:]
+        real = _TARGET + "." + _MOVED.get(rest, rest)
+        try:
+            if importlib.util.find_spec(real) is None:
+                return None
+        except (ImportError, ValueError):
+            return None
+        mod = importlib.import_module(real)
+        return importlib.util.spec_from_loader(fullname, _AliasLoader(real), is_package=hasattr(mod, "__path__"))
+
+
+if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):
+    sys.meta_path.insert(0, _AliasFinder())
+
+_pkg = importlib.import_module(_TARGET)
+__version__ = getattr(_pkg, "__version__", "0.1.0")
+
+
+def __getattr__(name):                      # ``from arctic_platform import wire`` / ``arctic_platform.rl``
+    try:
+        return importlib.import_module(f"{_ALIAS}.{name}")
+    except ImportError:
+        return getattr(_pkg, name)
