@@ -60,14 +60,15 @@ def reference_arm(args) -> None:
     """The reference needs deepspeed, ray, arctic_inference and deep_ep (pyproject.toml:111-131 of the reference);
     none is installed here or in the offline wheelhouse, and its build backend (hatchling) is missing too."""
     why = "reference not installable offline: build backend hatchling and hard deps deepspeed/ray/arctic_inference/deep_ep are absent from the image and /opt/wheelhouse"
-    try:
-        sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
-        import arctic_platform  # noqa: F401
-        import deepspeed  # noqa: F401
-        import ray  # noqa: F401
-        why = "reference imports, but no reference runner is wired because its engines (DeepSpeed/vLLM/ArcticInference) are unavailable"
-    except Exception:
-        pass
+    # only an installed copy of the reference counts (this repository's own ``arctic_platform`` is an import alias of
+    # the product and must never stand in for it)
+    if (ROOT / "baseline" / "_ref" / "arctic_platform" / "__init__.py").is_file():
+        try:
+            import deepspeed  # noqa: F401
+            import ray  # noqa: F401
+            why = "reference is installed, but no reference runner is wired because its engines (DeepSpeed/vLLM/ArcticInference) are unavailable"
+        except Exception:
+            pass
     print(json.dumps({"impl": "reference", "unavailable": why}))
 
 
