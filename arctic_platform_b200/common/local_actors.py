@@ -23,8 +23,21 @@ class ActorDied(RuntimeError):
     pass
 
 
+def _exit_with_parent(parent_pid: int, period_s: float = 2.0) -> None:
+    """A worker must not outlive the server that owns it (it may sit in a collective for ever and hold a GPU): when
+    the parent is gone the process ends itself."""
+    def watch():
+        import time
+        while True:
+            time.sleep(period_s)
+            if os.getppid() != parent_pid:
+                os._exit(1)
+    threading.Thread(target=watch, name="apb-parent-watch", daemon=True).start()
+
+
 def _serve(conn, factory: Callable[[], Any], env: Dict[str, str]) -> None:
     os.environ.update(env)
+    _exit_with_parent(os.getppid())
     try:
         obj = factory()
         conn.send(("ready", None))

@@ -196,3 +196,37 @@ def test_watchdog_marks_a_job_failed_when_a_worker_process_is_gone():
     finally:
         core.stop_worker_watchdog()
         core.destroy()
+
+
+def test_worker_process_ends_when_its_owner_is_gone(tmp_path):
+    """A process that owns a spawned worker is ended hard (no clean-up runs); the worker notices and exits."""
+    import subprocess
+    import sys
+    import time
+    import psutil
+    script = tmp_path / "owner.py"
+    script.write_text(
+        "import sys, time\n"
+        f"sys.path.insert(0, {str(__import__('pathlib').Path(__file__).resolve().parents[1])!r})\n"
+        "from arctic_platform_b200.common.local_actors import SpawnedActor\n"
+        "class W:\n"
+        "    def pid(self):\n"
+        "        import os; return os.getpid()\n"
+        "if __name__ == '__main__':\n"
+        "    a = SpawnedActor(W)\n"
+        "    print(a.call('pid'), flush=True)\n"
+        "    time.sleep(600)\n")
+    owner = subprocess.Popen([sys.executable, str(script)], stdout=subprocess.PIPE, text=True)
+    try:
+        child_pid = int(owner.stdout.readline())
+        assert psutil.pid_exists(child_pid)
+        owner.kill()                                   # the exact process started above; SIGKILL: no atexit, no cleanup
+        owner.wait(10)
+        for _ in range(100):
+            if not psutil.pid_exists(child_pid) or psutil.Process(child_pid).status() == psutil.STATUS_ZOMBIE:
+                break
+            time.sleep(0.1)
+        assert not psutil.pid_exists(child_pid) or psutil.Process(child_pid).status() == psutil.STATUS_ZOMBIE
+    finally:
+        if owner.poll() is None:
+            owner.kill()
