@@ -273,9 +273,6 @@ class EngineWorker:
         import torch.distributed as dist
         if not dist.is_initialized() or self.world % sp:
             raise ValueError(f"sequence_parallel={sp} needs a process group whose size ({self.world}) it divides")
-        if model.cfg.layer_types is not None:
-            raise NotImplementedError("sequence parallelism covers softmax-attention layers; the hybrid family's "
-                                      "recurrent layers have no sequence-parallel form here")
         from ..parallel.ulysses import apply_sequence_parallelism
         mine = None
         for g0 in range(0, self.world, sp):                    # every rank creates every group, in the same order

@@ -139,7 +139,20 @@ class GatedDeltaNet(nn.Module):
         self.capture: Optional[Dict[int, Tuple[torch.Tensor, torch.Tensor]]] = None
 
     def forward(self, x: torch.Tensor, layout) -> torch.Tensor:
-        """``x [T, H]`` on the packed axis -> ``[T, H]``."""
+        """``x [T, H]`` on the packed axis -> ``[T, H]``.  Under sequence parallelism ``x`` is this rank's row shard
+        and ``layout`` the (padded) global layout: the rows are gathered, the layer runs on the whole axis and the
+        rank keeps its slice."""
+        sp_group = getattr(self, "sp_group", None)
+        if sp_group is not None:
+            import torch.distributed as dist
+            from ..parallel.ulysses import gather_rows_with_grad
+            rows = x.shape[0]
+            full = self._forward_full(gather_rows_with_grad(x, sp_group), layout)
+            r = dist.get_rank(sp_group)
+            return full[r * rows:(r + 1) * rows]
+        return self._forward_full(x, layout)
+
+    def _forward_full(self, x: torch.Tensor, layout) -> torch.Tensor:
         T = x.shape[0]
         mixed = gemm.linear(x, self.in_qkv)
         z = gemm.linear(x, self.in_z).view(T, self.Hv, self.Dv)

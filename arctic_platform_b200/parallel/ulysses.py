@@ -113,11 +113,42 @@ def gather_rows(t_local: torch.Tensor, group, total: Optional[int] = None) -> to
     return out if total is None else out[:total]
 
 
+class _GatherRowsFn(torch.autograd.Function):
+    """All-gather of row shards with a gradient: the backward sums, over the ranks, the gradient every rank holds for
+    the full tensor and hands each rank the rows of its own shard (a reduce-scatter; an all-reduce + slice where the
+    backend has no reduce-scatter)."""
+
+    @staticmethod
+    def forward(ctx, t_local, group):
+        ctx.group, ctx.rows = group, t_local.shape[0]
+        return gather_rows(t_local, group)
+
+    @staticmethod
+    def backward(ctx, grad_full):
+        g = grad_full.contiguous()
+        r = dist.get_rank(ctx.group)
+        if dist.get_backend(ctx.group) == "nccl":
+            out = torch.empty((ctx.rows,) + tuple(g.shape[1:]), dtype=g.dtype, device=g.device)
+            dist.reduce_scatter_tensor(out.view(-1), g.view(-1), group=ctx.group)
+            return out, None
+        g = g.clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g[r * ctx.rows:(r + 1) * ctx.rows].contiguous(), None
+
+
+def gather_rows_with_grad(t_local: torch.Tensor, group) -> torch.Tensor:
+    return _GatherRowsFn.apply(t_local, group)
+
+
 def apply_sequence_parallelism(model, group) -> None:
     """Routes every block's attention through the Ulysses exchange.  The caller feeds each rank its row shard
     of ``input_ids`` / ``positions`` (``shard_rows``) and the global layout padded to ``sp * ceil(T/sp)`` rows."""
     for blk in model.blocks:
         blk.sp_group = group
+        if getattr(blk, "linear_attn", None) is not None:
+            # recurrent layers carry state along the whole sequence: every rank runs them on the gathered rows and
+            # keeps its own slice (correct, not sequence-scaled; attention and MLP / experts stay sharded)
+            blk.linear_attn.sp_group = group
     model.sp_group = group
 
 

@@ -330,3 +330,31 @@ def test_token_budget_micro_batches_stay_in_step_across_ranks():
     finally:
         core.destroy()
         single.destroy()
+
+
+@pytest.mark.timeout(600)
+def test_sequence_parallel_hybrid_model_equals_one_process():
+    """The hybrid family under sequence parallelism: softmax-attention layers exchange heads for sequence, the
+    recurrent layers run on the gathered rows and keep their slice; two ranks equal one process."""
+    def job(**extra):
+        return {"model_name": "qwen3.5-moe-tiny", "job_type": "training", "seed": 11, **extra,
+                "ds_config": {"zero_optimization": {"stage": 1}, "gradient_clipping": 1.0,
+                              "optimizer": {"type": "AdamW", "params": {"lr": 1e-3}}}}
+    p = _payload()
+    p["batch"]["input_ids"] = p["batch"]["input_ids"] % 1000
+    single = ArcticRLServerCore()
+    j1 = single.initialize(job())["job_id"]
+    want_lp = single.forward(j1, {"batch": p["batch"], "meta": p["meta"]})["batch"]["log_probs"]
+    want = single.forward_backward(j1, p)
+    want_norm = single.step(j1)["metrics"]["grad_norm"]
+    core = ArcticRLServerCore(worker_factory=spawned_worker_factory(_free_port()), training_gpus=2)
+    try:
+        jid = core.initialize(job(ds_worker_config={"sequence_parallel": 2}))["job_id"]
+        got_lp = core.forward(jid, {"batch": p["batch"], "meta": p["meta"]})["batch"]["log_probs"]
+        assert torch.allclose(got_lp, want_lp, atol=2e-5)
+        got = core.forward_backward(jid, p)
+        assert got["avg_loss"] == pytest.approx(want["avg_loss"], rel=1e-4, abs=1e-6)
+        assert core.step(jid)["metrics"]["grad_norm"] == pytest.approx(want_norm, rel=2e-4)
+    finally:
+        core.destroy()
+        single.destroy()
