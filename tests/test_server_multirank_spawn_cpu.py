@@ -146,7 +146,7 @@ def test_rank_process_pool_hosts_trainer_and_sampler_of_a_rank_together():
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("stage", [1, 3])
+@pytest.mark.parametrize("stage", [3])
 def test_sequence_parallel_group_of_two_equals_one_process(stage):
     """Two ranks as ONE Ulysses group behind the server: both receive the whole batch, each runs half of the packed
     token axis; scores, loss, gradient norm and updated weights equal the single-process run."""
@@ -341,7 +341,8 @@ def test_sequence_parallel_hybrid_model_equals_one_process():
                 "ds_config": {"zero_optimization": {"stage": 1}, "gradient_clipping": 1.0,
                               "optimizer": {"type": "AdamW", "params": {"lr": 1e-3}}}}
     p = _payload()
-    p["batch"]["input_ids"] = p["batch"]["input_ids"] % 1000
+    p["batch"] = {k: v[:4].contiguous() for k, v in p["batch"].items()}          # two prompt groups are enough here
+    p["meta"] = {**p["meta"], "batch_num_tokens": float(p["batch"]["response_mask"].sum()), "global_batch_size": 4.0}
     single = ArcticRLServerCore()
     j1 = single.initialize(job())["job_id"]
     want_lp = single.forward(j1, {"batch": p["batch"], "meta": p["meta"]})["batch"]["log_probs"]
