@@ -26,7 +26,7 @@ import torch.nn.functional as F
 from ..models.decoder import _qknorm_partial_rope, gate_up_act
 from ..ops import gemm, norm
 from ..ops.attention import AttnLayout
-from .reference_sampler import ReferenceSampler, filter_logits
+from .reference_sampler import EXTRA_KEYS, LogitsProcessor, ReferenceSampler, filter_logits
 from .sampler import SamplingParams
 
 
@@ -149,10 +149,13 @@ class HybridSampler(ReferenceSampler):
         return m.logits(hf).float()
 
     # ------------------------------------------------------------------ sampling
-    def _pick(self, logits: torch.Tensor, sp: SamplingParams) -> Tuple[torch.Tensor, torch.Tensor]:
+    def _pick(self, logits: torch.Tensor, sp: SamplingParams, shaper: Optional[LogitsProcessor] = None
+              ) -> Tuple[torch.Tensor, torch.Tensor]:
         """Token and its log-probability under the unfiltered (temperature-scaled) policy, per row."""
         if sp.temperature and sp.temperature > 0:
             scaled = logits / sp.temperature
+            if shaper is not None:
+                scaled = shaper.after_temperature(scaled)
             probs = torch.softmax(filter_logits(scaled, sp.top_k, sp.top_p), -1).cpu()
             tok = torch.multinomial(probs, 1, generator=self.gen)[:, 0].to(logits.device)
             lp = torch.log_softmax(scaled, -1).gather(1, tok[:, None])[:, 0]
@@ -163,7 +166,9 @@ class HybridSampler(ReferenceSampler):
 
     @torch.no_grad()
     def generate(self, prompts: Sequence[Sequence[int]], sampling_params=None) -> List[dict]:
-        sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
+        sp = sampling_params if isinstance(sampling_params, SamplingParams) else \
+            SamplingParams.from_dict(sampling_params, supported=EXTRA_KEYS)
+        self._raw_params = sampling_params if isinstance(sampling_params, dict) else None
         if self._asleep:
             raise RuntimeError("sampler is asleep; call wake() first")
         if sp.seed is not None:
@@ -205,8 +210,11 @@ class HybridSampler(ReferenceSampler):
         lps: List[List[float]] = [[] for _ in range(B)]
         reason = ["length"] * B
         alive = [sp.max_tokens > 0] * B
+        shaper = LogitsProcessor(getattr(self, "_raw_params", None), sorted(stops))
         for _t in range(sp.max_tokens):
-            tok, lp = self._pick(logits, sp)
+            if shaper.active:
+                logits = torch.stack([shaper.before_temperature(logits[b], prompts[seq_prompt[b]], out[b]) for b in range(B)])
+            tok, lp = self._pick(logits, sp, shaper)
             tok_l, lp_l = tok.tolist(), lp.tolist()
             for b in range(B):
                 if not alive[b]:

@@ -31,6 +31,55 @@ def filter_logits(logits: torch.Tensor, top_k: int, top_p: float) -> torch.Tenso
     return logits
 
 
+EXTRA_KEYS = ("repetition_penalty", "presence_penalty", "frequency_penalty", "min_p", "min_tokens", "logit_bias")
+
+
+class LogitsProcessor:
+    """Distribution shaping that the tensor-op samplers implement beyond temperature / top-k / top-p, in the order
+    vLLM applies it: ``logit_bias``, repetition penalty (prompt and output tokens: positive logits divided, negative
+    multiplied), presence / frequency penalties (output tokens), then -- after temperature -- ``min_p`` (tokens below
+    ``min_p`` times the top probability are dropped); ``min_tokens`` keeps the stop tokens impossible until that many
+    tokens were produced."""
+
+    def __init__(self, params: Optional[dict], stop_ids: Sequence[int] = ()):
+        p = dict(params or {})
+        self.repetition = float(p.get("repetition_penalty") or 1.0)
+        self.presence = float(p.get("presence_penalty") or 0.0)
+        self.frequency = float(p.get("frequency_penalty") or 0.0)
+        self.min_p = float(p.get("min_p") or 0.0)
+        self.min_tokens = int(p.get("min_tokens") or 0)
+        self.bias = {int(k): float(v) for k, v in (p.get("logit_bias") or {}).items()}
+        self.stop_ids = [int(t) for t in stop_ids]
+        self.active = (self.repetition != 1.0 or self.presence or self.frequency or self.min_p or self.min_tokens
+                       or bool(self.bias))
+
+    def before_temperature(self, logits: torch.Tensor, prompt: Sequence[int], output: Sequence[int]) -> torch.Tensor:
+        """``logits [V]`` of one sequence -> adjusted copy."""
+        if not self.active:
+            return logits
+        logits = logits.clone()
+        for t, b in self.bias.items():
+            if 0 <= t < logits.shape[-1]:
+                logits[t] += b
+        if self.repetition != 1.0:
+            seen = torch.tensor(sorted(set(prompt) | set(output)), dtype=torch.long, device=logits.device)
+            if seen.numel():
+                v = logits[seen]
+                logits[seen] = torch.where(v > 0, v / self.repetition, v * self.repetition)
+        if (self.presence or self.frequency) and len(output):
+            toks, counts = torch.tensor(output, dtype=torch.long, device=logits.device).unique(return_counts=True)
+            logits[toks] -= self.presence + self.frequency * counts.to(logits.dtype)
+        if len(output) < self.min_tokens and self.stop_ids:
+            logits[torch.tensor(self.stop_ids, dtype=torch.long, device=logits.device)] = float("-inf")
+        return logits
+
+    def after_temperature(self, scaled: torch.Tensor) -> torch.Tensor:
+        if not self.min_p:
+            return scaled
+        probs = torch.softmax(scaled, -1)
+        return scaled.masked_fill(probs < self.min_p * probs.max(-1, keepdim=True).values, float("-inf"))
+
+
 class ReferenceSampler:
     def __init__(self, cfg: DecoderConfig, device="cpu", model: Optional[DecoderLM] = None, max_seq_len: int = 8192,
                  seed: int = 0, eos_token_id: Optional[int] = None, **_ignored):
@@ -44,7 +93,8 @@ class ReferenceSampler:
 
     @torch.no_grad()
     def generate(self, prompts: Sequence[Sequence[int]], sampling_params=None) -> List[dict]:
-        sp = sampling_params if isinstance(sampling_params, SamplingParams) else SamplingParams.from_dict(sampling_params)
+        sp = sampling_params if isinstance(sampling_params, SamplingParams) else \
+            SamplingParams.from_dict(sampling_params, supported=EXTRA_KEYS)
         if self._asleep:
             raise RuntimeError("sampler is asleep; call wake() first")
         if sp.seed is not None:
@@ -52,6 +102,7 @@ class ReferenceSampler:
         stops = set(int(t) for t in sp.stop_token_ids)
         if self.eos is not None and not sp.ignore_eos:
             stops.add(int(self.eos))
+        shaper = LogitsProcessor(sampling_params if isinstance(sampling_params, dict) else None, sorted(stops))
         results: List[dict] = []
         for pi, prompt in enumerate(prompts):
             if len(prompt) == 0:
@@ -65,9 +116,9 @@ class ReferenceSampler:
                     ids = torch.tensor(seq, dtype=torch.int64, device=self.device)
                     layout = AttnLayout.from_cu_seqlens(np.array([0, len(seq)]))
                     h = self.model.forward_hidden(ids, torch.arange(len(seq), device=self.device), layout)[-1:]
-                    logits = self.model.logits(h)[0].float()
+                    logits = shaper.before_temperature(self.model.logits(h)[0].float(), prompt, out)
                     if sp.temperature and sp.temperature > 0:
-                        scaled = logits / sp.temperature
+                        scaled = shaper.after_temperature(logits / sp.temperature)
                         dist_logits = filter_logits(scaled, sp.top_k, sp.top_p)
                         probs = torch.softmax(dist_logits, -1).cpu()
                         tok = int(torch.multinomial(probs, 1, generator=self.gen))

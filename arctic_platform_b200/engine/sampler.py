@@ -55,7 +55,8 @@ class SamplingParams:
     seed: Optional[int] = None
 
     @staticmethod
-    def from_dict(d: Optional[dict]) -> "SamplingParams":
+    def from_dict(d: Optional[dict], supported: Tuple[str, ...] = ()) -> "SamplingParams":
+        """``supported`` names extra keys the calling engine implements itself (they are then not reported)."""
         d = dict(d or {})
         sp = SamplingParams()
         for k in ("n", "temperature", "max_tokens", "top_p", "top_k", "ignore_eos", "logprobs", "seed"):
@@ -69,7 +70,7 @@ class SamplingParams:
                   "bad_words", "best_of", "use_beam_search"):
             v = d.get(k)
             neutral = {"repetition_penalty": 1.0, "best_of": sp.n}.get(k, 0)
-            if v not in (None, False, neutral, [], {}) and k not in _WARNED_KEYS:
+            if k not in supported and v not in (None, False, neutral, [], {}) and k not in _WARNED_KEYS:
                 _WARNED_KEYS.add(k)
                 import logging
                 logging.getLogger(__name__).warning("sampling parameter %s=%r is not supported and is ignored", k, v)

@@ -92,3 +92,45 @@ def test_worker_serves_the_hybrid_family_with_the_stateful_engine():
     before = w.weight_norm()["norm"]
     t.sync_weights_to(w)
     assert w.weight_norm()["norm"] == pytest.approx(t.weight_norm()["norm"], rel=1e-6) != before
+
+
+def test_logits_processor_arithmetic():
+    from arctic_platform_b200.engine.reference_sampler import LogitsProcessor
+    logits = torch.tensor([2.0, -1.0, 0.5, 3.0, -2.0])
+    lp = LogitsProcessor({"repetition_penalty": 2.0, "presence_penalty": 0.5, "frequency_penalty": 0.25,
+                          "logit_bias": {"4": 1.0, "99": 5.0}, "min_tokens": 3}, stop_ids=[3])
+    got = lp.before_temperature(logits, prompt=[0], output=[1, 1])
+    # token 0 (prompt): 2 / 2; token 1 (output twice): -1 * 2 - 0.5 - 2 * 0.25; token 4: bias; token 3: held back
+    assert got.tolist() == [1.0, -3.0, 0.5, float("-inf"), -1.0]
+    assert torch.equal(logits, torch.tensor([2.0, -1.0, 0.5, 3.0, -2.0]))          # the input is not modified
+    assert lp.before_temperature(logits, [0], [1, 1, 2])[3] == 3.0                 # min_tokens reached
+    assert not LogitsProcessor({"repetition_penalty": 1.0, "min_p": 0.0}).active
+    mp_ = LogitsProcessor({"min_p": 0.5})
+    kept = mp_.after_temperature(torch.tensor([[0.0, -0.1, -5.0]]))
+    assert kept[0, :2].tolist() == pytest.approx([0.0, -0.1]) and kept[0, 2] == float("-inf")
+
+
+def test_penalties_and_min_tokens_agree_between_the_two_samplers():
+    import warnings
+    cfg, hyb, ref = _pair("qwen3.5-moe-tiny")
+    prompts = _prompts(cfg, [6, 10])
+    plain = ref.generate(prompts, {"n": 1, "temperature": 0.0, "max_tokens": 12})
+    stop = plain[0]["token_ids"][1]
+    sp = {"n": 1, "temperature": 0.0, "max_tokens": 12, "repetition_penalty": 1.3, "frequency_penalty": 0.4,
+          "presence_penalty": 0.2, "min_tokens": 6, "stop_token_ids": [stop]}
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")                     # keys that these engines implement are not reported
+        a, b = hyb.generate(prompts, sp), ref.generate(prompts, sp)
+    assert [r["token_ids"] for r in a] == [r["token_ids"] for r in b]
+    for r in a:
+        assert stop not in r["token_ids"][:6]
+        assert len(r["token_ids"]) >= 6
+    # a strong repetition penalty leaves no token repeated in a short greedy continuation
+    strong = hyb.generate(prompts, {"n": 1, "temperature": 0.0, "max_tokens": 10, "repetition_penalty": 50.0,
+                                    "presence_penalty": 50.0})
+    for r in strong:
+        assert len(set(r["token_ids"])) == len(r["token_ids"])
+    # min_p = 1 keeps only the most likely token: sampling becomes greedy
+    greedy = hyb.generate(prompts, {"n": 1, "temperature": 0.0, "max_tokens": 8})
+    mp1 = hyb.generate(prompts, {"n": 2, "temperature": 1.0, "min_p": 1.0, "max_tokens": 8, "seed": 1})
+    assert [r["token_ids"] for r in mp1] == [greedy[0]["token_ids"]] * 2 + [greedy[1]["token_ids"]] * 2
