@@ -40,6 +40,8 @@ class DecoderConfig:
     moe_n_group: int = 1                         # group-limited routing: experts in n groups,
     moe_topk_group: int = 1                      # ... only the best topk_group groups are eligible per token
     shared_expert_intermediate_size: int = 0     # > 0: a dense SwiGLU expert with a sigmoid gate beside the routed ones
+    moe_activation: str = "swiglu"               # "relu2": non-gated experts down(relu(up x)^2) (models/latent_moe.py)
+    moe_latent_dim: int = 0                      # > 0 (relu2 layer): routed rows are projected to this width for the experts
     # hybrid (Qwen3.5 / Qwen3-Next) features; the defaults describe plain Qwen3
     layer_types: Optional[tuple] = None          # per layer "full_attention" | "linear_attention"
     partial_rotary_factor: float = 1.0           # fraction of head_dim that is rotated
@@ -81,7 +83,11 @@ class DecoderConfig:
     def num_parameters(self, include_embeddings: bool = True) -> int:
         H, L = self.hidden_size, self.num_layers
         attn = self.qkv_size * H + H * self.q_size + (2 * self.head_dim if self.qk_norm else 0)
-        if self.is_moe:
+        if self.is_moe and self.moe_activation == "relu2":
+            W = self.moe_latent_dim or H
+            mlp = (self.num_experts * 2 * W * self.moe_intermediate_size + self.num_experts * H
+                   + (2 * W * H if self.moe_latent_dim else 0) + 2 * H * self.shared_expert_intermediate_size)
+        elif self.is_moe:
             mlp = self.num_experts * 3 * H * self.moe_intermediate_size + self.num_experts * H
         else:
             mlp = 3 * H * self.intermediate_size
@@ -97,6 +103,10 @@ class DecoderConfig:
         attn_w = self.qkv_size * H + H * self.q_size
         mlp_w = (self.num_experts_per_tok * 3 * H * self.moe_intermediate_size if self.is_moe
                  else 3 * H * self.intermediate_size)
+        if self.is_moe and self.moe_activation == "relu2":
+            W, k = self.moe_latent_dim or H, self.num_experts_per_tok
+            mlp_w = (k * 2 * W * self.moe_intermediate_size + (k * 2 * W * H if self.moe_latent_dim else 0)
+                     + 2 * H * self.shared_expert_intermediate_size)
         dense = 2.0 * (L * (attn_w + mlp_w) + self.vocab_size * H)
         attn = 2.0 * 2.0 * L * self.num_heads * self.head_dim * seq_len / 2.0
         return (dense + attn) * (3.0 if backward else 1.0)
@@ -126,7 +136,10 @@ class DecoderConfig:
             moe_route_scale=float(d.get("routed_scaling_factor", d.get("route_scale", 1.0)) or 1.0),
             moe_expert_bias=bool(d.get("moe_expert_bias", d.get("load_balance_coeff") is not None)),
             moe_n_group=int(d.get("n_group", 1) or 1), moe_topk_group=int(d.get("topk_group", 1) or 1),
-            shared_expert_intermediate_size=d.get("shared_expert_intermediate_size", 0) or 0,
+            shared_expert_intermediate_size=d.get("shared_expert_intermediate_size",
+                                                  d.get("moe_shared_expert_intermediate_size", 0)) or 0,
+            moe_activation="relu2" if (d.get("moe_activation") or d.get("mlp_hidden_act")) == "relu2" else "swiglu",
+            moe_latent_dim=int(d.get("moe_latent_size", d.get("moe_latent_dim", 0)) or 0),
             layer_types=_hybrid_layer_types(d), partial_rotary_factor=float(d.get("partial_rotary_factor", 1.0)),
             attn_output_gate=hybrid, norm_one_plus=hybrid,
             linear_num_key_heads=d.get("linear_num_key_heads", 0) or 0,
@@ -151,6 +164,18 @@ class DecoderConfig:
         if self.is_moe:
             d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob)
+            # router variants and the expert layout travel only when they differ from the Qwen3-MoE defaults
+            if self.moe_score_func != "softmax":
+                d["scoring_func"] = self.moe_score_func
+            if self.moe_route_scale != 1.0:
+                d["routed_scaling_factor"] = self.moe_route_scale
+            if self.moe_n_group > 1:
+                d.update(n_group=self.moe_n_group, topk_group=self.moe_topk_group)
+            if self.moe_expert_bias:
+                d["moe_expert_bias"] = True
+            if self.moe_activation != "swiglu":
+                d.update(moe_activation=self.moe_activation, moe_latent_size=self.moe_latent_dim,
+                         shared_expert_intermediate_size=self.shared_expert_intermediate_size)
         if self.layer_types is not None:
             d.update(model_type=self.model_type, architectures=["Qwen3_5MoeForCausalLM" if self.is_moe else "Qwen3NextForCausalLM"],
                      layer_types=list(self.layer_types), partial_rotary_factor=self.partial_rotary_factor,
@@ -234,6 +259,13 @@ PRESETS: Dict[str, DecoderConfig] = {
     "qwen3-moe-tiny": DecoderConfig(vocab_size=32000, hidden_size=256, intermediate_size=688, num_layers=2,
                                     num_heads=4, num_kv_heads=2, head_dim=128, num_experts=8, num_experts_per_tok=2,
                                     moe_intermediate_size=128, model_type="qwen3_moe", name="qwen3-moe-tiny"),
+    # latent relu^2 experts behind a group-limited sigmoid router (the Nemotron-H style feed-forward)
+    "latent-moe-tiny": DecoderConfig(vocab_size=32000, hidden_size=128, intermediate_size=256, num_layers=2,
+                                     num_heads=4, num_kv_heads=2, head_dim=32, num_experts=8, num_experts_per_tok=2,
+                                     moe_intermediate_size=64, shared_expert_intermediate_size=96,
+                                     moe_activation="relu2", moe_latent_dim=64, moe_score_func="sigmoid",
+                                     moe_n_group=4, moe_topk_group=2, moe_route_scale=2.5, moe_expert_bias=True,
+                                     model_type="qwen3_moe", name="latent-moe-tiny"),
 }
 
 

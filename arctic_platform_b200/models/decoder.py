@@ -111,7 +111,10 @@ class DecoderBlock(nn.Module):
         self.ac_targets: Tuple[str, ...] = ()   # parts of this block under selective activation checkpointing
         self.ln2 = mk(H)
         if cfg.is_moe:
-            from .moe import MoEFeedForward
+            if cfg.moe_activation == "relu2":
+                from .latent_moe import LatentMoEFeedForward as MoEFeedForward
+            else:
+                from .moe import MoEFeedForward
             self.mlp = MoEFeedForward(cfg, device, dtype)
             self.wgu = self.wdown = None
         else:

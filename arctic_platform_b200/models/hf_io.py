@@ -50,7 +50,15 @@ def hf_param_names(cfg: DecoderConfig) -> List[str]:
                 names += [p + "self_attn.q_norm.weight", p + "self_attn.k_norm.weight"]
             names.append(p + "self_attn.o_proj.weight")
         names.append(p + "post_attention_layernorm.weight")
-        if cfg.is_moe:
+        if cfg.is_moe and cfg.moe_activation == "relu2":
+            names += [p + "mlp.gate.weight", p + "mlp.gate.e_score_correction_bias"]
+            if cfg.moe_latent_dim:
+                names += [p + "mlp.fc1_latent_proj.weight", p + "mlp.fc2_latent_proj.weight"]
+            if cfg.shared_expert_intermediate_size > 0:
+                names += [p + "mlp.shared_experts.up_proj.weight", p + "mlp.shared_experts.down_proj.weight"]
+            for e in range(cfg.num_experts):
+                names += [p + f"mlp.experts.{e}.up_proj.weight", p + f"mlp.experts.{e}.down_proj.weight"]
+        elif cfg.is_moe:
             names.append(p + "mlp.gate.weight")
             if cfg.shared_expert_intermediate_size > 0:
                 names += [p + "mlp.shared_expert.gate_proj.weight", p + "mlp.shared_expert.up_proj.weight",
@@ -122,7 +130,20 @@ def iter_hf_tensors(model) -> Iterator[Tuple[str, torch.Tensor]]:
                 yield p + "self_attn.k_norm.weight", blk.k_norm.data
             yield p + "self_attn.o_proj.weight", blk.wo.data
         yield p + "post_attention_layernorm.weight", blk.ln2.data
-        if cfg.is_moe:
+        if cfg.is_moe and getattr(blk.mlp, "latent", False):
+            m = blk.mlp
+            yield p + "mlp.gate.weight", m.router.data
+            yield p + "mlp.gate.e_score_correction_bias", m.e_score_correction_bias
+            if m.fc1 is not None:
+                yield p + "mlp.fc1_latent_proj.weight", m.fc1.data
+                yield p + "mlp.fc2_latent_proj.weight", m.fc2.data
+            if m.shared_wup is not None:
+                yield p + "mlp.shared_experts.up_proj.weight", m.shared_wup.data
+                yield p + "mlp.shared_experts.down_proj.weight", m.shared_wdown.data
+            for e in range(cfg.num_experts):
+                yield p + f"mlp.experts.{e}.up_proj.weight", m.wup.data[e]
+                yield p + f"mlp.experts.{e}.down_proj.weight", m.wdown.data[e]
+        elif cfg.is_moe:
             yield p + "mlp.gate.weight", blk.mlp.router.data
             if blk.mlp.shared_wgu is not None:
                 g, u = split_gate_up(blk.mlp.shared_wgu.data)
@@ -184,6 +205,16 @@ def load_hf_tensor(model, name: str, tensor: torch.Tensor) -> None:
         both = tensor.view(cfg.num_heads, 2, D, H)
         put(blk.wqkv.data[:qs], both[:, 0].reshape(qs, H))
         return put(blk.wgate.data, both[:, 1].reshape(qs, H))
+    if getattr(blk.mlp, "latent", False) and parts[3] == "mlp":
+        m, sub = blk.mlp, ".".join(parts[4:])
+        plain = {"gate.weight": m.router, "gate.e_score_correction_bias": m.e_score_correction_bias,
+                 "fc1_latent_proj.weight": m.fc1, "fc2_latent_proj.weight": m.fc2,
+                 "shared_experts.up_proj.weight": m.shared_wup, "shared_experts.down_proj.weight": m.shared_wdown}
+        if sub in plain and plain[sub] is not None:
+            return put(plain[sub].data, tensor)
+        if parts[4] == "experts" and parts[6] in ("up_proj", "down_proj"):
+            return put((m.wup if parts[6] == "up_proj" else m.wdown).data[int(parts[5])], tensor)
+        raise KeyError(f"unexpected tensor name {name!r}")
     if rest == "mlp.shared_expert.gate_proj.weight":
         return put(blk.mlp.shared_wgu.data[0::2], tensor)
     if rest == "mlp.shared_expert.up_proj.weight":

@@ -269,6 +269,9 @@ def attach_expert_parallel(model, ep_size: int, group=None, impl: str = "fused",
         moe = blk.mlp
         if moe is None:
             continue
+        if getattr(moe, "latent", False):
+            raise NotImplementedError("expert parallelism is built for the SwiGLU expert layout; "
+                                      "the latent relu^2 layer runs data-parallel")
         E = moe.wgu.shape[0]
         if E % world:
             raise ValueError(f"{E} experts do not divide over {world} ranks")
