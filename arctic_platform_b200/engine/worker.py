@@ -134,8 +134,8 @@ class EngineWorker:
             wc = job_config.get("ds_worker_config") or {}
             gc_cfg = wc.get("gradient_checkpointing", False)
             ecfg.gradient_checkpointing = bool(gc_cfg.get("enable", True)) if isinstance(gc_cfg, dict) else bool(gc_cfg)
-            if isinstance(gc_cfg, dict) and gc_cfg.get("mode", "full") == "selective":
-                m.checkpoint_targets = tuple(gc_cfg.get("targets") or ("mlp", "routed_experts", "linear_attn"))
+            if isinstance(gc_cfg, dict) and ecfg.gradient_checkpointing:
+                m.set_activation_checkpointing(gc_cfg.get("mode", "full"), gc_cfg.get("targets"), int(gc_cfg.get("freq", 1) or 1))
             from ..models.factory import _tiled_mlp_setting
             shards = _tiled_mlp_setting(wc.get("tiled_mlp"))
             for blk in m.blocks:

@@ -85,6 +85,9 @@ def _qknorm_partial_rope(qkv, wq, wk, rope, positions, cfg: DecoderConfig, w_off
     return one(q, wq), one(k, wk), v
 
 
+SELECTIVE_AC_TARGETS = ("norm", "attn_proj", "mlp", "routed_experts", "linear_attn")
+
+
 class DecoderBlock(nn.Module):
     def __init__(self, cfg: DecoderConfig, layer_idx: int, device, dtype):
         super().__init__()
@@ -125,17 +128,11 @@ class DecoderBlock(nn.Module):
     def forward(self, x, stream, positions, layout: AttnLayout, rope):
         """``x`` is the previous sublayer output, ``stream`` the residual stream before adding it
         (None for the first block).  Returns the MLP output and the updated stream."""
-        cfg = self.cfg
-        h, stream = norm.rmsnorm(x, self.ln1, cfg.rms_norm_eps, stream, self.w_offset)
+        h, stream = self._part("norm", self._norm, x, stream, self.ln1)
         if self.linear_attn is not None:
             o = self._part("linear_attn", self.linear_attn, h, layout)
         else:
-            qkv = gemm.linear(h, self.wqkv)
-            if cfg.rotary_dim != cfg.head_dim or self.w_offset:
-                q, k, v = _qknorm_partial_rope(qkv, self.q_norm, self.k_norm, rope, positions, cfg, self.w_offset)
-            else:
-                q, k, v = norm.qknorm_rope(qkv, self.q_norm, self.k_norm, rope[0], rope[1], positions, cfg.num_heads,
-                                           cfg.num_kv_heads, cfg.head_dim, cfg.rms_norm_eps)
+            q, k, v = self._part("attn_proj", self._attn_in, h, positions, rope)
             if self.kv_capture is not None:
                 self.kv_capture.append((k, v))
             if getattr(self, "sp_group", None) is not None:
@@ -143,11 +140,8 @@ class DecoderBlock(nn.Module):
                 a = ulysses_attention(q, k, v, layout, self.sp_group)
             else:
                 a = segment_attention(q, k, v, layout)
-            a = a.reshape(a.shape[0], -1)
-            if self.wgate is not None:
-                a = (a.float() * torch.sigmoid(gemm.linear(h, self.wgate).float())).to(a.dtype)
-            o = gemm.linear(a, self.wo)
-        h2, stream = norm.rmsnorm(o, self.ln2, cfg.rms_norm_eps, stream, self.w_offset)
+            o = self._part("attn_proj", self._attn_out, a.reshape(a.shape[0], -1), h)
+        h2, stream = self._part("norm", self._norm, o, stream, self.ln2)
         if self.mlp is not None:
             d = self._part("routed_experts" if "routed_experts" in self.ac_targets else "mlp", self.mlp, h2)
         elif self.tiled_mlp_shards:
@@ -159,6 +153,37 @@ class DecoderBlock(nn.Module):
 
     def _dense_mlp(self, h: torch.Tensor) -> torch.Tensor:
         return gemm.linear(gate_up_act(h, self.wgu), self.wdown)
+
+    def _norm(self, x, stream, weight):
+        return norm.rmsnorm(x, weight, self.cfg.rms_norm_eps, stream, self.w_offset)
+
+    def _attn_in(self, h, positions, rope):
+        """q/k/v projection, per-head norm and rotation."""
+        cfg = self.cfg
+        qkv = gemm.linear(h, self.wqkv)
+        if cfg.rotary_dim != cfg.head_dim or self.w_offset:
+            return _qknorm_partial_rope(qkv, self.q_norm, self.k_norm, rope, positions, cfg, self.w_offset)
+        return norm.qknorm_rope(qkv, self.q_norm, self.k_norm, rope[0], rope[1], positions, cfg.num_heads,
+                                cfg.num_kv_heads, cfg.head_dim, cfg.rms_norm_eps)
+
+    def _attn_out(self, a, h):
+        """Output gate (where the family has one) and output projection."""
+        if self.wgate is not None:
+            a = (a.float() * torch.sigmoid(gemm.linear(h, self.wgate).float())).to(a.dtype)
+        return gemm.linear(a, self.wo)
+
+    def supported_ac_targets(self) -> frozenset:
+        """Selective-checkpointing targets that name a part of THIS block (same rule as the reference's
+        ``get_supported_targets``, arctic_platform/model/implementations/qwen35/models/layers/checkpointing.py:97-115)."""
+        out = {"norm"}
+        if self.linear_attn is not None:
+            out.add("linear_attn")
+        else:
+            out.add("attn_proj")
+        out.add("routed_experts" if self.mlp is not None else "mlp")
+        if self.mlp is not None:
+            out.add("mlp")                                   # the whole MoE layer, router and shared expert included
+        return frozenset(out)
 
     def _part(self, target: str, fn, *args):
         """Runs one part of the block, under activation checkpointing when selective checkpointing names it."""
@@ -185,9 +210,34 @@ class DecoderLM(nn.Module):
         self._rope: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
         self._rope_len = max_positions or min(cfg.max_position_embeddings, 40960)
         self.gradient_checkpointing = False
-        # selective checkpointing: only these parts of every block are recomputed ("mlp", "routed_experts",
-        # "linear_attn", "attn_proj"); empty = whole blocks
+        # selective checkpointing: only these parts of every block are recomputed (SELECTIVE_AC_TARGETS); empty =
+        # whole blocks.  ``checkpoint_freq`` = n: every n-th block (0, n, 2n, ...) is checkpointed, the rest keep
+        # their activations
         self.checkpoint_targets: Tuple[str, ...] = ()
+        self.checkpoint_freq = 1
+
+    def set_activation_checkpointing(self, mode: str = "full", targets=None, freq: int = 1) -> None:
+        """``mode`` ``full`` (whole blocks) or ``selective`` (``targets``, default ``["norm"]`` as in the reference's
+        ``ActivationCheckpointConfig``, arctic_platform/model/implementations/qwen35/config.py:33-40).  Unknown
+        target names, and names that no layer of this model has, are errors."""
+        if mode not in ("full", "selective"):
+            raise ValueError(f"activation checkpointing mode {mode!r}: expected 'full' or 'selective'")
+        if int(freq) < 1:
+            raise ValueError(f"activation checkpointing freq must be >= 1, got {freq}")
+        chosen: Tuple[str, ...] = ()
+        if mode == "selective":
+            chosen = tuple(sorted(set(targets if targets is not None else ("norm",))))
+            unknown = set(chosen) - set(SELECTIVE_AC_TARGETS)
+            if unknown:
+                raise ValueError(f"Unsupported selective activation checkpoint targets: {sorted(unknown)}")
+            have = set().union(*(blk.supported_ac_targets() for blk in self.blocks))
+            missing = set(chosen) - have
+            if missing:
+                raise ValueError(f"Selective activation checkpoint targets {sorted(missing)} are not supported by the "
+                                 f"selected model layers. Supported targets across the model: {sorted(have)}")
+        self.gradient_checkpointing = True
+        self.checkpoint_targets = chosen
+        self.checkpoint_freq = int(freq)
 
     # ------------------------------------------------------------------ init
     @torch.no_grad()
@@ -231,9 +281,11 @@ class DecoderLM(nn.Module):
         positions = positions.to(torch.int32) if x.is_cuda else positions
         stream = None
         targets = tuple(self.checkpoint_targets) if self.gradient_checkpointing else ()
-        for blk in self.blocks:
-            blk.ac_targets = targets
-            if self.gradient_checkpointing and torch.is_grad_enabled() and not self.checkpoint_targets:
+        freq = max(1, int(getattr(self, "checkpoint_freq", 1)))
+        for li, blk in enumerate(self.blocks):
+            on = self.gradient_checkpointing and li % freq == 0
+            blk.ac_targets = targets if on else ()
+            if on and torch.is_grad_enabled() and not self.checkpoint_targets:
                 from torch.utils.checkpoint import checkpoint
                 if blk.mlp is not None:
                     # the recompute replays the routing of the original pass (same expert counts, same shapes)

@@ -103,7 +103,9 @@ def test_routing_replay_keeps_recompute_consistent(monkeypatch):
 
 
 @pytest.mark.parametrize("preset,targets", [("qwen3-tiny", ("mlp",)), ("qwen3-moe-tiny", ("routed_experts",)),
-                                            ("qwen3.5-moe-tiny", ("linear_attn", "mlp"))])
+                                            ("qwen3.5-moe-tiny", ("linear_attn", "mlp")),
+                                            ("qwen3-tiny", ("norm", "attn_proj")),
+                                            ("qwen3.5-moe-tiny", ("norm", "attn_proj", "routed_experts"))])
 def test_selective_checkpointing_matches_plain(preset, targets):
     ids, mask, R = make_grpo_batch(n_prompts=2, n_samples=2, seed=5)
     cfg = PRESETS[preset]
@@ -127,6 +129,45 @@ def test_selective_checkpointing_matches_plain(preset, targets):
     assert torch.equal(got_lp, want_lp) and seen and "DecoderBlock" not in seen
     for n in want:
         assert torch.allclose(got[n], want[n], atol=1e-6, rtol=1e-5), n
+
+
+def test_checkpoint_frequency_and_target_validation():
+    cfg = PRESETS["qwen3.5-moe-tiny"]
+    model = DecoderLM(cfg, "cpu", torch.float32).init_weights(seed=2)
+    ids, mask, R = make_grpo_batch(n_prompts=2, n_samples=2, seed=5)
+    pb = build_packed_batch(ids % cfg.vocab_size, mask, R, dedup=True)
+    want_lp, want = _grads(model, pb)
+    import torch.utils.checkpoint as ck
+    real, seen = ck.checkpoint, []
+
+    def spy(fn, *a, **kw):
+        seen.append(getattr(fn, "__name__", type(fn).__name__))
+        return real(fn, *a, **kw)
+    for mode, targets, freq, per_block in (("full", None, 2, 1), ("selective", None, 3, 2), ("selective", ["norm"], 1, 2)):
+        model.set_activation_checkpointing(mode, targets, freq)
+        assert model.checkpoint_targets == (() if mode == "full" else ("norm",))
+        seen.clear()
+        ck.checkpoint = spy
+        try:
+            got_lp, got = _grads(model, pb)
+        finally:
+            ck.checkpoint = real
+        blocks = len(range(0, cfg.num_layers, freq))
+        assert len(seen) == blocks * per_block, (mode, freq, seen)        # every freq-th block, 2 norms per block
+        assert torch.equal(got_lp, want_lp)
+        for n in want:
+            assert torch.allclose(got[n], want[n], atol=1e-6, rtol=1e-5), n
+    with pytest.raises(ValueError, match="Unsupported selective activation checkpoint targets: \\['mla_up'\\]"):
+        model.set_activation_checkpointing("selective", ["norm", "mla_up"])
+    with pytest.raises(ValueError, match="mode"):
+        model.set_activation_checkpointing("partial")
+    with pytest.raises(ValueError, match="freq"):
+        model.set_activation_checkpointing("full", None, 0)
+    dense = DecoderLM(PRESETS["qwen3-tiny"], "cpu", torch.float32)
+    assert dense.blocks[0].supported_ac_targets() == {"norm", "attn_proj", "mlp"}
+    assert model.blocks[0].supported_ac_targets() == {"norm", "linear_attn", "routed_experts", "mlp"}
+    with pytest.raises(ValueError, match="not supported by the selected model layers"):
+        dense.set_activation_checkpointing("selective", ["linear_attn"])
 
 
 def test_worker_config_selects_selective_mode():
