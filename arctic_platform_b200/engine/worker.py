@@ -133,6 +133,18 @@ class EngineWorker:
             ecfg = EngineConfig.from_ds_config(job_config.get("ds_config"), job_config.get("training_config"))
             wc = job_config.get("ds_worker_config") or {}
             gc_cfg = wc.get("gradient_checkpointing", False)
+            # the reference's spelling: training_config.ac_config = {mode, freq, targets, offload_config: {enabled,
+            # keep_last_n, tensor_size_threshold}} (arctic_platform/model/implementations/qwen35/config.py:33-52)
+            ac = (job_config.get("training_config") or {}).get("ac_config")
+            if isinstance(ac, dict):
+                gc_cfg = {k: ac[k] for k in ("mode", "freq", "targets") if k in ac}
+                off = ac.get("offload_config") or {}
+                if off.get("enabled"):
+                    if ac.get("mode", "full") != "full":
+                        raise ValueError("Activation-checkpoint CPU offload (ac_config.offload_config.enabled=True) requires "
+                                         f"ac_config.mode='full', but the active mode is '{ac.get('mode')}'")
+                    wc = {**wc, "activation_offload": {"keep_last": int(off.get("keep_last_n", 1)),
+                                                       "min_bytes": int(off.get("tensor_size_threshold") or (1 << 20))}}
             ecfg.gradient_checkpointing = bool(gc_cfg.get("enable", True)) if isinstance(gc_cfg, dict) else bool(gc_cfg)
             if isinstance(gc_cfg, dict) and ecfg.gradient_checkpointing:
                 m.set_activation_checkpointing(gc_cfg.get("mode", "full"), gc_cfg.get("targets"), int(gc_cfg.get("freq", 1) or 1))

@@ -178,6 +178,23 @@ def test_worker_config_selects_selective_mode():
     assert w.engine.model.gradient_checkpointing and w.engine.model.checkpoint_targets == ("routed_experts",)
 
 
+def test_worker_reads_the_nested_ac_config_of_the_training_config():
+    from arctic_platform_b200.engine.worker import EngineWorker
+    base = {"model_name": "qwen3-tiny", "job_type": "training", "ds_config": {"zero_optimization": {"stage": 1}}}
+    w = EngineWorker("cpu")
+    w.initialize({**base, "training_config": {"ac_config": {"mode": "full", "freq": 2, "offload_config": {
+        "enabled": True, "keep_last_n": 1, "tensor_size_threshold": 4096}}}})
+    m = w.engine.model
+    assert m.gradient_checkpointing and m.checkpoint_targets == () and m.checkpoint_freq == 2
+    assert w.activation_offload is not None and w.activation_offload.min_bytes == 4096
+    w2 = EngineWorker("cpu")
+    w2.initialize({**base, "training_config": {"ac_config": {"mode": "selective"}}})
+    assert w2.engine.model.checkpoint_targets == ("norm",) and w2.activation_offload is None
+    with pytest.raises(ValueError, match="requires ac_config.mode='full'"):
+        EngineWorker("cpu").initialize({**base, "training_config": {"ac_config": {
+            "mode": "selective", "offload_config": {"enabled": True}}}})
+
+
 def test_engine_updates_and_checkpoints_the_load_balancing_bias(tmp_path):
     from arctic_platform_b200.engine.checkpoint import load_checkpoint, save_checkpoint
     from arctic_platform_b200.engine.trainer import EngineConfig, TrainEngine
