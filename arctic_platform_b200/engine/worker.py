@@ -93,6 +93,25 @@ class EngineWorker:
             enable_full_determinism(seed)
         self.model_cfg = model.cfg if model is not None else resolve_config(job_config["model_name"])
         dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        # strict schema, as the reference's loader: a misspelt option is an error, not a silent default
+        from ..models.loader_options import LoaderOptions
+        raw_lo = (job_config.get("ds_worker_config") or {}).get("loader_options") or {}
+        self.loader_options = lo = LoaderOptions.from_dict(raw_lo)
+        if "optimization_dtype" in raw_lo:
+            if self.device.type == "cuda" and lo.optimization_dtype != "bfloat16":
+                raise ValueError("loader_options.optimization_dtype='float32': the GPU kernels compute in bf16 with fp32 "
+                                 "master weights and fp32 accumulation")
+            if self.device.type != "cuda":
+                dtype = getattr(torch, lo.optimization_dtype)
+        if lo.debug is not None and model is None:
+            if lo.debug.num_layers is not None:
+                import dataclasses
+                n = int(lo.debug.num_layers)
+                lt = self.model_cfg.layer_types
+                self.model_cfg = dataclasses.replace(self.model_cfg, num_layers=n,
+                                                     layer_types=None if lt is None else tuple(lt[:n]))
+            if lo.debug.deterministic_algorithms:
+                torch.use_deterministic_algorithms(True, warn_only=True)
         if self.job_type != "sampling":
             self._ensure_process_group(job_config)
         if self.job_type == "sampling":
@@ -135,16 +154,17 @@ class EngineWorker:
             gc_cfg = wc.get("gradient_checkpointing", False)
             # the reference's spelling: training_config.ac_config = {mode, freq, targets, offload_config: {enabled,
             # keep_last_n, tensor_size_threshold}} (arctic_platform/model/implementations/qwen35/config.py:33-52)
-            ac = (job_config.get("training_config") or {}).get("ac_config")
-            if isinstance(ac, dict):
-                gc_cfg = {k: ac[k] for k in ("mode", "freq", "targets") if k in ac}
-                off = ac.get("offload_config") or {}
-                if off.get("enabled"):
-                    if ac.get("mode", "full") != "full":
-                        raise ValueError("Activation-checkpoint CPU offload (ac_config.offload_config.enabled=True) requires "
-                                         f"ac_config.mode='full', but the active mode is '{ac.get('mode')}'")
-                    wc = {**wc, "activation_offload": {"keep_last": int(off.get("keep_last_n", 1)),
-                                                       "min_bytes": int(off.get("tensor_size_threshold") or (1 << 20))}}
+            # It travels in ds_worker_config.loader_options (validated above) or in training_config.
+            ac = lo.ac_config
+            if ac is None and isinstance((job_config.get("training_config") or {}).get("ac_config"), dict):
+                from ..models.loader_options import ActivationCheckpointOptions, _strict
+                ac = _strict(ActivationCheckpointOptions, job_config["training_config"]["ac_config"], "training_config.ac_config")
+            if ac is not None:
+                gc_cfg, ao_cfg = ac.to_worker_dicts()
+                if ao_cfg is not None:
+                    wc = {**wc, "activation_offload": ao_cfg}
+            if lo.tiled_mlp_token_chunk_size is not None and not wc.get("tiled_mlp"):
+                wc = {**wc, "tiled_mlp": f"chunk:{int(lo.tiled_mlp_token_chunk_size)}"}
             ecfg.gradient_checkpointing = bool(gc_cfg.get("enable", True)) if isinstance(gc_cfg, dict) else bool(gc_cfg)
             if isinstance(gc_cfg, dict) and ecfg.gradient_checkpointing:
                 m.set_activation_checkpointing(gc_cfg.get("mode", "full"), gc_cfg.get("targets"), int(gc_cfg.get("freq", 1) or 1))
@@ -203,9 +223,12 @@ class EngineWorker:
         from ..models.conversion_cache import load_through_cache
         m = DecoderLM(self.model_cfg, self.device, dtype)
         path = Path(str(job_config["model_name"]))
-        if path.is_dir() and any(path.glob("*.safetensors")):
+        lo = getattr(self, "loader_options", None)
+        random_init = bool(lo is not None and lo.debug is not None and lo.debug.random_init)
+        if path.is_dir() and any(path.glob("*.safetensors")) and not random_init:
             # converted once per node when a cache directory is configured, else straight from the shards
-            load_through_cache(m, path, cache_dir=job_config.get("weight_conversion_cache_dir"))
+            load_through_cache(m, path, cache_dir=job_config.get("weight_conversion_cache_dir")
+                               or (lo.weight_conversion_cache_dir if lo is not None else None))
             m.source_dir = str(path)                 # exports take the tokenizer files from here
         else:
             m.init_weights(seed=seed)     # no checkpoint on disk: deterministic random initialisation

@@ -45,6 +45,8 @@ def resolve_shards(shards: Union[int, str, None], tokens: int, hidden: int) -> i
         return 1
     if shards == "auto" or shards is True:
         return max(1, math.ceil(tokens / max(1, hidden)))
+    if isinstance(shards, str) and shards.startswith("chunk:"):        # tiles of a fixed number of tokens
+        return max(1, math.ceil(tokens / max(1, int(shards[6:]))))
     return max(1, min(int(shards), tokens))
 
 
