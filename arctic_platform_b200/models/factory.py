@@ -110,13 +110,25 @@ class LoadedModel:
 
 
 _LOADERS: Dict[str, Tuple[Callable, Optional[Callable], bool]] = {}
+_LOADER_OPTIONS: Dict[str, Any] = {}
 
 
-def register_loader(name: str, matches: Optional[Callable[[LoaderContext], bool]] = None, default: bool = False):
+def register_loader(name: str, matches: Optional[Callable[[LoaderContext], bool]] = None, default: bool = False,
+                    options: Any = None):
+    """``options``: a class with ``from_dict(dict)`` that validates ``ModelSpec.loader_options`` for this loader
+    (arctic_platform/model/loader.py:83-107 registers a pydantic model for the same purpose)."""
     def deco(fn):
         _LOADERS[name] = (fn, matches, default)
+        _LOADER_OPTIONS[name] = options
         return fn
     return deco
+
+
+def get_loader_options_model(name: str):
+    """The options schema registered for a loader, or ``None``."""
+    if name not in _LOADERS:
+        raise KeyError(f"unknown loader {name!r} (known: {sorted(_LOADERS)})")
+    return _LOADER_OPTIONS.get(name)
 
 
 def resolve_loader_name(ctx: LoaderContext) -> str:
@@ -139,14 +151,19 @@ def _torch_dtype(name: str) -> torch.dtype:
     return {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}[name]
 
 
-@register_loader("dense", default=True)
+def _options_schema():
+    from .loader_options import LoaderOptions
+    return LoaderOptions
+
+
+@register_loader("dense", default=True, options=_options_schema())
 def _load_dense(ctx: LoaderContext, device, seed: int) -> DecoderLM:
     if ctx.spec.parallelism.expert_parallel > 1:
         raise ValueError("the dense loader does not take expert_parallel > 1")
     return _instantiate(ctx, device, seed)
 
 
-@register_loader("moe", matches=lambda c: c.hf_config.is_moe)
+@register_loader("moe", matches=lambda c: c.hf_config.is_moe, options=_options_schema())
 def _load_moe(ctx: LoaderContext, device, seed: int) -> DecoderLM:
     model = _instantiate(ctx, device, seed)
     if ctx.spec.parallelism.expert_parallel > 1:
@@ -160,9 +177,15 @@ def _instantiate(ctx: LoaderContext, device, seed: int) -> DecoderLM:
     from .conversion_cache import load_through_cache
     dev = torch.device(device)
     dtype = _torch_dtype(ctx.spec.dtype) if dev.type == "cuda" else torch.float32
-    model = DecoderLM(ctx.hf_config, dev, dtype)
+    cfg = ctx.hf_config
+    debug = ctx.spec.loader_options.get("debug") or {}
+    if debug.get("num_layers") is not None:                    # test-only: a shallower model of the same family
+        import dataclasses
+        n, lt = int(debug["num_layers"]), cfg.layer_types
+        cfg = dataclasses.replace(cfg, num_layers=n, layer_types=None if lt is None else tuple(lt[:n]))
+    model = DecoderLM(cfg, dev, dtype)
     p = Path(ctx.spec.model_path_or_name)
-    if p.is_dir() and any(p.glob("*.safetensors")):
+    if p.is_dir() and any(p.glob("*.safetensors")) and not debug.get("random_init"):
         load_through_cache(model, p, cache_dir=ctx.spec.loader_options.get("weight_conversion_cache_dir"))
         model.source_dir = str(p)
     else:
@@ -194,6 +217,22 @@ def apply_patches(model: DecoderLM, patches: Patches) -> List[str]:
 
 def build_model(spec: ModelSpec, parallel_groups: Optional[dict] = None, device="cpu", seed: int = 42) -> LoadedModel:
     ctx = LoaderContext(spec)
-    fn, _, _ = _LOADERS[resolve_loader_name(ctx)]
+    name = resolve_loader_name(ctx)
+    fn, _, _ = _LOADERS[name]
+    schema = _LOADER_OPTIONS.get(name)
+    opts = schema.from_dict(spec.loader_options) if schema is not None else None     # raises on unknown / bad options
     model = fn(ctx, device, seed)
-    return LoadedModel(model, apply_patches(model, spec.patches))
+    applied = apply_patches(model, spec.patches)
+    ac = getattr(opts, "ac_config", None)
+    if ac is not None:
+        model.set_activation_checkpointing(ac.mode, ac.targets, ac.freq)
+        if "gradient_checkpointing" not in applied:
+            applied.append("gradient_checkpointing")
+            model._applied_patches = applied
+    chunk = getattr(opts, "tiled_mlp_token_chunk_size", None)
+    if chunk is not None and "tiled_mlp" not in applied:
+        for blk in model.blocks:
+            blk.tiled_mlp_shards = f"chunk:{int(chunk)}"
+        applied.append("tiled_mlp")
+        model._applied_patches = applied
+    return LoadedModel(model, applied)

@@ -70,3 +70,22 @@ def test_worker_applies_the_options(tmp_path):
     assert len(m2.blocks) == 1 and m2.embed.dtype == torch.bfloat16 and not torch.equal(m2.embed.data.float(), src.embed.data)
     with pytest.raises(ValueError, match="unknown option"):
         EngineWorker("cpu").initialize({**base, "ds_worker_config": {"loader_options": {"atn": "sdpa"}}})
+
+
+def test_model_builder_validates_and_applies_the_options():
+    from arctic_platform_b200.models.factory import ModelSpec, build_model, get_loader_options_model
+    assert get_loader_options_model("dense") is LoaderOptions and get_loader_options_model("moe") is LoaderOptions
+    with pytest.raises(KeyError):
+        get_loader_options_model("nope")
+    spec = ModelSpec("qwen3.5-moe-tiny", loader_options={"debug": {"num_layers": 2, "random_init": True},
+                                                         "ac_config": {"mode": "selective", "targets": ["linear_attn"]},
+                                                         "tiled_mlp_token_chunk_size": 64})
+    loaded = build_model(spec)
+    m = loaded.model
+    assert len(m.blocks) == 2 and m.cfg.layer_types == ("linear_attention", "linear_attention")
+    assert m.checkpoint_targets == ("linear_attn",) and m.gradient_checkpointing
+    assert "gradient_checkpointing" in loaded.applied_patches and "tiled_mlp" in loaded.applied_patches
+    with pytest.raises(ValueError, match="unknown option"):
+        build_model(ModelSpec("qwen3-tiny", loader_options={"sequence_len": 8}))
+    with pytest.raises(ValueError, match="not supported by the selected model layers"):
+        build_model(ModelSpec("qwen3-tiny", loader_options={"ac_config": {"mode": "selective", "targets": ["linear_attn"]}}))
