@@ -141,8 +141,10 @@ class HybridSampler(ReferenceSampler):
                 if blk.wgate is not None:
                     a = (a.float() * torch.sigmoid(gemm.linear(h, blk.wgate).float())).to(a.dtype)
                 o = gemm.linear(a, blk.wo)
+            o = blk.tp_reduce(o)
             h2, stream = norm.rmsnorm(o, blk.ln2, cfg.rms_norm_eps, stream, w_off)
             x = blk.mlp(h2) if blk.mlp is not None else gemm.linear(gate_up_act(h2, blk.wgu), blk.wdown)
+            x = blk.tp_reduce(x)
         hf, _ = norm.rmsnorm(x, m.final_norm, cfg.rms_norm_eps, stream, w_off)
         st.lens += 1
         self.decode_steps += 1

@@ -110,6 +110,8 @@ class DecoderBlock(nn.Module):
             self.k_norm = mk(D) if cfg.qk_norm else None
             self.wo = mk(H, cfg.q_size)
         self.kv_capture = None           # a sampler's prefill sets a list; forward appends this layer's (k, v)
+        self.tp_group = None             # inference tensor parallelism: this block holds a head / column shard and
+        #                                  sums the two row-parallel outputs over the group (parallel/tp_sampler.py)
         self.tiled_mlp_shards = 0        # > 1 or "auto": the dense MLP runs over row tiles (activation memory)
         self.ac_targets: Tuple[str, ...] = ()   # parts of this block under selective activation checkpointing
         self.ln2 = mk(H)
@@ -141,6 +143,7 @@ class DecoderBlock(nn.Module):
             else:
                 a = segment_attention(q, k, v, layout)
             o = self._part("attn_proj", self._attn_out, a.reshape(a.shape[0], -1), h)
+        o = self.tp_reduce(o)
         h2, stream = self._part("norm", self._norm, o, stream, self.ln2)
         if self.mlp is not None:
             d = self._part("routed_experts" if "routed_experts" in self.ac_targets else "mlp", self.mlp, h2)
@@ -149,7 +152,17 @@ class DecoderBlock(nn.Module):
             d = tiled_mlp(h2, self._dense_mlp, self.tiled_mlp_shards, (self.wgu, self.wdown))
         else:
             d = self._part("mlp", self._dense_mlp, h2)
-        return d, stream
+        return self.tp_reduce(d), stream
+
+    def tp_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """Sum of the row-parallel partial outputs over the tensor-parallel group (identity without one)."""
+        if self.tp_group is None:
+            return t
+        if torch.is_grad_enabled() and t.requires_grad:
+            raise RuntimeError("tensor-parallel blocks are inference-only")
+        import torch.distributed as dist
+        dist.all_reduce(t, group=self.tp_group)
+        return t
 
     def _dense_mlp(self, h: torch.Tensor) -> torch.Tensor:
         return gemm.linear(gate_up_act(h, self.wgu), self.wdown)
