@@ -193,6 +193,9 @@ class ArcticRLServerCore:
         if job_type not in ("training", "sampling", "log_prob"):
             raise JobError(400, f"unknown job_type {job_type!r}")
         n = int(job_config.get("num_devices") or self.gpus.get(job_type) or 1)
+        tp = int((job_config.get("vllm_config") or {}).get("tensor_parallel_size", 1) or 1) if job_type == "sampling" else 1
+        if tp > 1 and n % tp:
+            raise JobError(400, f"tensor_parallel_size={tp} does not divide the sampling job's {n} devices")
         with self._lock:
             for j in self.jobs.values():
                 if j.job_type == job_type and j.status == "RUNNING" and not job_config.get("allow_multiple"):
@@ -415,9 +418,17 @@ class ArcticRLServerCore:
     # ------------------------------------------------------------------ rollout
     def generate(self, job_id: int, prompts, sampling_params=None, routing_key=None, strict: bool = False):
         job = self._job(job_id, ("sampling",))
-        n = len(job.workers)
+        replicas = self._replicas(job)
+        n = len(replicas)
+
+        def on_replica(r, method, *args):
+            # the ranks of a tensor-parallel replica run the call together and return the same thing
+            if len(replicas[r]) == 1:
+                return replicas[r][0].call(method, *args)
+            return call_all(replicas[r], method, None, *args)[0]
+
         if n == 1:
-            return {"job_id": job.job_id, "results": job.workers[0].call("generate", prompts, sampling_params)}
+            return {"job_id": job.job_id, "results": on_replica(0, "generate", prompts, sampling_params)}
         # replica data parallelism: every prompt goes to ONE replica with all its samples (so the replica shares the
         # prompt's KV among them); replicas run concurrently and the results come back in prompt order
         assign = route_prompts(prompts, n, routing_key, strict)
@@ -427,7 +438,7 @@ class ArcticRLServerCore:
 
         def run(item):
             r, idxs = item
-            out = job.workers[r].call("generate", [prompts[i] for i in idxs], sampling_params)
+            out = on_replica(r, "generate", [prompts[i] for i in idxs], sampling_params)
             for o in out:
                 o["prompt_index"] = idxs[o["prompt_index"]]
             return out
@@ -438,6 +449,15 @@ class ArcticRLServerCore:
         results = sorted((o for part in parts for o in part), key=lambda o: o["prompt_index"])   # stable: sample order kept
         return {"job_id": job.job_id, "results": results}
 
+    @staticmethod
+    def _replicas(job: Job) -> List[List[Any]]:
+        """Workers of a sampling job grouped into replicas: ``tensor_parallel_size`` consecutive ranks each."""
+        tp = int((job.config.get("vllm_config") or {}).get("tensor_parallel_size", 1) or 1)
+        ws = list(job.workers)
+        if tp <= 1 or len(ws) < tp:
+            return [[w] for w in ws]
+        return [ws[i:i + tp] for i in range(0, len(ws), tp)]
+
     def log_probs(self, job_id: int, prompts, completions, top_k: int = 1) -> Dict[str, Any]:
         job = self._job(job_id, ("sampling", "log_prob", "training"))
         if len(prompts) != len(completions):
@@ -445,14 +465,20 @@ class ArcticRLServerCore:
         if job.job_type == "sampling":
             # scored with the sampler's own weights (the reference's ``log_prob_engine = vllm``): the requests are
             # spread over the replicas, each scores its share in one packed pass
-            n = len(job.workers)
+            replicas = self._replicas(job)
+            n = len(replicas)
             share = [list(range(r, len(prompts), n)) for r in range(n)]
-            active = [(w, idx) for w, idx in zip(job.workers, share) if idx]
-            outs = call_all([w for w, _ in active], "score_completions",
-                            [([prompts[i] for i in idx], [completions[i] for i in idx]) for _, idx in active],
+            active = [(ws, idx) for ws, idx in zip(replicas, share) if idx]
+            flat = [(w, idx) for ws, idx in active for w in ws]          # all ranks of a replica score the same share
+            outs = call_all([w for w, _ in flat], "score_completions",
+                            [([prompts[i] for i in idx], [completions[i] for i in idx]) for _, idx in flat],
                             peer_grace_s=None)
+            firsts, k = [], 0
+            for ws, _idx in active:
+                firsts.append(outs[k])
+                k += len(ws)
             rows = [None] * len(prompts)
-            for (_, idx), res in zip(active, outs):
+            for (_, idx), res in zip(active, firsts):
                 for i, r in zip(idx, res):
                     rows[i] = r
             return {"job_id": job.job_id, "log_probs": rows}
@@ -521,7 +547,7 @@ class ArcticRLServerCore:
             r = call_all(self._job(training_job_id).workers, "weight_norm")[0]      # sharded engines: a collective
             out["training_norm"], out["training_num_params"] = r["norm"], r["num_params"]
         if sampling_job_id is not None:
-            r = self._job(sampling_job_id).workers[0].call("weight_norm")
+            r = call_all(self._replicas(self._job(sampling_job_id))[0], "weight_norm")[0]   # a replica's ranks together
             out["sampling_norm"], out["sampling_num_params"] = r["norm"], r["num_params"]
         return out
 

@@ -78,6 +78,7 @@ class EngineWorker:
         self.job_config: Dict[str, Any] = {}
         self.activation_offload = None
         self.sp = 1
+        self.tp = 1                      # ranks per sampling replica (tensor parallelism)
         self._nvtx = os.environ.get("APB_NVTX", "0") == "1"
 
     # ------------------------------------------------------------------ lifecycle
@@ -112,16 +113,15 @@ class EngineWorker:
                                                      layer_types=None if lt is None else tuple(lt[:n]))
             if lo.debug.deterministic_algorithms:
                 torch.use_deterministic_algorithms(True, warn_only=True)
-        if self.job_type != "sampling":
+        tp = int((job_config.get("vllm_config") or {}).get("tensor_parallel_size", 1) or 1) \
+            if self.job_type == "sampling" else 1
+        if self.job_type != "sampling" or tp > 1:
             self._ensure_process_group(job_config)
+        if self.job_type == "sampling" and tp > 1:
+            return self._initialize_tp_sampler(job_config, model, tp, dtype, seed)
         if self.job_type == "sampling":
             from .sampler import SamplerEngine
             vc = dict(job_config.get("vllm_config") or {})
-            if int(vc.get("tensor_parallel_size", 1) or 1) > 1:
-                import logging
-                logging.getLogger(__name__).warning(
-                    "tensor_parallel_size=%s: this sampler runs one full replica per GPU; the value is ignored",
-                    vc["tensor_parallel_size"])
             m = model if model is not None else self._load_model(job_config, dtype, seed)
             if self.model_cfg.layer_types is not None:
                 # hybrid family: recurrent state + sparse K/V layers, served by the stateful tensor-op engine
@@ -185,6 +185,28 @@ class EngineWorker:
                         prefetch=int(opts.get("prefetch", 2)))
         return True
 
+    def _initialize_tp_sampler(self, job_config, model, tp: int, dtype, seed) -> bool:
+        """A sampling replica over ``tp`` consecutive ranks of the job: every rank keeps a head / column shard of the
+        decoder (``parallel/tp_sampler.py``) and all ranks of a replica are called together."""
+        import torch.distributed as dist
+        from ..parallel.tp_sampler import TensorParallelSampler
+        if not dist.is_initialized() or self.world % tp:
+            raise ValueError(f"tensor_parallel_size={tp} needs a process group whose size ({self.world}) it divides")
+        first = self.rank - self.rank % tp
+        # only the members create their group: the ranks of other replicas (or of no replica) need not take part
+        group = dist.new_group(list(range(first, first + tp)), use_local_synchronization=True)
+        vc = dict(job_config.get("vllm_config") or {})
+        full = model if model is not None else self._load_model(job_config, dtype, seed)
+        self.sampler = TensorParallelSampler(
+            self.model_cfg, self.device, model=full, tp_group=group, dtype=dtype,
+            max_batch=int(vc.get("max_num_seqs", 256)), max_seq_len=int(vc.get("max_model_len", 8192)), seed=seed,
+            eos_token_id=vc.get("eos_token_id"))
+        self.tp = tp
+        del full                                                 # only the shard stays resident
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+        return True
+
     def rank_info(self) -> Dict[str, Any]:
         import torch.distributed as dist
         return {"rank": self.rank, "world": self.world, "device": str(self.device),
@@ -194,7 +216,7 @@ class EngineWorker:
     def _ensure_process_group(self, job_config) -> None:
         """Joins the job's data-parallel group when the launcher described one (``WORLD_SIZE`` > 1 with a
         rendezvous address) and none exists yet: NCCL on a GPU, gloo on CPU.  Sampler replicas are independent and
-        never call this.  The reference does the same through ``deepspeed.init_distributed``
+        call this only when they are tensor-parallel.  The reference does the same through ``deepspeed.init_distributed``
         (arctic_platform/common/deepspeed_worker.py:155)."""
         import datetime
         import os
@@ -561,6 +583,8 @@ class EngineWorker:
     def load_weights(self, named_tensors) -> int:
         """Copies ``(hf_name, tensor)`` pairs into this worker's model (sampler or forward-only engine)."""
         from ..models.hf_io import load_hf_tensor
+        if self.sampler is not None and hasattr(self.sampler, "tp"):
+            return self.sampler.load_weights(named_tensors)      # full tensors in, this rank's slices kept
         n = 0
         model = self._target_model()
         for name, t in named_tensors:
@@ -616,6 +640,9 @@ class EngineWorker:
         their Hugging Face names.  Returns the number of tensors covered."""
         from ..models.hf_io import hf_param_names
         from ..parallel import weight_sync
+        if dst.sampler is not None and hasattr(dst.sampler, "tp"):
+            # tensor-parallel replica: a different layout per rank, so the tensors travel under their names
+            return dst.sampler.load_weights((n, t.detach()) for n, t in self.engine.iter_hf_tensors())
         dst_model = dst.sampler.model if dst.sampler is not None else dst.engine.model
         n_names = len(hf_param_names(self.model_cfg))
         dst_engine = dst.engine if dst.sampler is None else None

@@ -82,3 +82,48 @@ def test_two_rank_replica_equals_one_rank(preset):
         assert [x["token_ids"] for x in r["tp_other"]] == [x["token_ids"] for x in r["one_other"]]
     assert [x["token_ids"] for x in res[0]["sampled"]] == [x["token_ids"] for x in res[1]["sampled"]]
     assert res[0]["sampled"][0]["logprobs"] == res[1]["sampled"][0]["logprobs"]
+
+
+@pytest.mark.timeout(600)
+def test_tensor_parallel_replica_behind_the_server():
+    """Two rank processes host a two-rank trainer and ONE two-rank sampling replica: the server calls both ranks of
+    the replica together, the trainer's weights reach the shards, and the rollouts are those of a one-rank sampler
+    with the same weights."""
+    from arctic_platform_b200.common.server import ArcticRLServerCore, JobError
+    from arctic_platform_b200.engine.worker import EngineWorker
+    from tests.test_server_multirank_spawn_cpu import _job, _train
+    core = ArcticRLServerCore(training_gpus=2, sampling_gpus=2, colocate=True)
+    try:
+        tj = core.initialize(_job(1))["job_id"]
+        with pytest.raises(JobError, match="does not divide"):
+            core.initialize({"model_name": "qwen3-tiny", "job_type": "sampling", "num_devices": 3,
+                             "vllm_config": {"tensor_parallel_size": 2}})
+        sj = core.initialize({"model_name": "qwen3-tiny", "job_type": "sampling", "seed": 5,
+                              "vllm_config": {"max_model_len": 64, "tensor_parallel_size": 2}})["job_id"]
+        assert len(core._replicas(core._job(sj))) == 1
+        _train(core, tj, steps=1)
+        core.weight_sync(tj, [sj])
+        tn = core.weight_norm(training_job_id=tj)
+        sn = core.weight_norm(sampling_job_id=sj)
+        assert sn["sampling_norm"] == pytest.approx(tn["training_norm"], rel=1e-6)
+        assert sn["sampling_num_params"] == tn["training_num_params"]
+        prompts = [[3, 4, 5, 9], [6, 7]]
+        greedy = {"n": 1, "max_tokens": 5, "temperature": 0.0}
+        out = core.generate(sj, prompts, greedy)["results"]
+        scores = core.log_probs(sj, prompts, [r["token_ids"] for r in out])["log_probs"]
+        for r, s in zip(out, scores):
+            assert s == pytest.approx(r["logprobs"], abs=2e-4)          # scoring == what sampling reported
+        # a plain one-rank sampler given the trainer's weights draws the same tokens
+        weights = call_all_first(core, tj)
+        solo = EngineWorker("cpu")
+        solo.initialize({"model_name": "qwen3-tiny", "job_type": "sampling", "seed": 5, "vllm_config": {"max_model_len": 64}})
+        solo.load_weights(weights)
+        want = solo.generate(prompts, greedy)
+        assert [r["token_ids"] for r in out] == [r["token_ids"] for r in want]
+    finally:
+        core.destroy()
+
+
+def call_all_first(core, job_id):
+    from arctic_platform_b200.common.server import call_all
+    return call_all(core._job(job_id).workers, "get_weights", None, 0)[0]
