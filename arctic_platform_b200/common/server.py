@@ -17,6 +17,7 @@ from __future__ import annotations
 
 import itertools
 import threading
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, List, Optional, Sequence
@@ -194,7 +195,10 @@ class ArcticRLServerCore:
             raise JobError(400, f"unknown job_type {job_type!r}")
         n = int(job_config.get("num_devices") or self.gpus.get(job_type) or 1)
         tp = int((job_config.get("vllm_config") or {}).get("tensor_parallel_size", 1) or 1) if job_type == "sampling" else 1
-        if tp > 1 and n % tp:
+        # (an SPMD launch -- one client and one in-process worker per rank -- forms its replicas over the launcher's
+        # world: the worker checks the division there)
+        spmd = n == 1 and int(os.environ.get("WORLD_SIZE", "1") or 1) > 1
+        if tp > 1 and n % tp and not spmd:
             raise JobError(400, f"tensor_parallel_size={tp} does not divide the sampling job's {n} devices")
         with self._lock:
             for j in self.jobs.values():

@@ -68,3 +68,34 @@ def test_two_spmd_ranks_equal_one_process():
     # each rank reports the token mean of its own shard; the global figure lies between them
     lo, hi = sorted(r["loss"] for r in res)
     assert lo - 1e-6 <= ref["avg_loss"] <= hi + 1e-6
+
+
+def _tp_rank(rank, world, port, out_dir):
+    os.environ.update(RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    from arctic_platform_b200.rl import create_arctic_rl_client
+    cfg = _cfg().model_copy(update={"sampling_gpus": 1, "colocate": True,
+                                    "vllm_config": {"max_model_len": 64, "tensor_parallel_size": 2}})
+    client = create_arctic_rl_client(cfg)
+    client.call("fwd_bwd", _payload(slice(rank * 4, (rank + 1) * 4)), {"loss_fn": "verl_grpo"})
+    client.call("step")
+    client.call("sync_weights")
+    norms = client.call("weight_norm")
+    # every rank of the replica passes the same prompts, as one program on two ranks does
+    out = client.call("generate", [[3, 4, 5, 9], [6, 7]], {"n": 1, "max_tokens": 5, "temperature": 0.0})
+    torch.save({"norms": norms, "tokens": [r["token_ids"] for r in out]}, os.path.join(out_dir, f"t{rank}.pt"))
+    client.call("shutdown")
+
+
+@pytest.mark.timeout(300)
+def test_spmd_ranks_form_one_tensor_parallel_sampling_replica():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_tp_rank, args=(2, port, d), nprocs=2, join=True)
+        res = [torch.load(os.path.join(d, f"t{r}.pt")) for r in range(2)]
+    assert res[0]["tokens"] == res[1]["tokens"] and all(len(t) == 5 for t in res[0]["tokens"])
+    for r in res:
+        assert r["norms"]["sampling_norm"] == pytest.approx(r["norms"]["training_norm"], rel=1e-6)
+        assert r["norms"]["sampling_num_params"] == r["norms"]["training_num_params"]
