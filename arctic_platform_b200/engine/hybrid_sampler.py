@@ -201,7 +201,22 @@ class HybridSampler(ReferenceSampler):
             owner += [d] * sp.n
             seq_prompt += [pi] * sp.n
         uniq = [list(k) for k in distinct]
+        # rollout routing replay: every MoE layer logs the experts it chose, pass by pass
+        want_routing = bool(getattr(self, "always_return_routing", False)
+                            or (getattr(self, "_raw_params", None) and self._raw_params.get("return_routed_experts")))
+        moes = [blk.mlp for blk in self.model.blocks if blk.mlp is not None] if want_routing else []
+        for mm in moes:
+            mm.routing_log = []
+        try:
+            self._run_wave(prompts, sp, stops, results, uniq, owner, seq_prompt, moes)
+        finally:
+            for mm in moes:
+                mm.routing_log = None
+
+    def _run_wave(self, prompts, sp, stops, results, uniq, owner, seq_prompt, moes) -> None:
         logits_p, linear, kv, cu = self._prefill(uniq)
+        pre_routing = torch.stack([mm.routing_log.pop() for mm in moes], 1) if moes else None       # [T, L, k]
+        step_routing: List[torch.Tensor] = []
         B = len(owner)
         t_max = max(len(u) for u in uniq) + sp.max_tokens
         st = self._spread(linear, kv, cu, owner, t_max)
@@ -228,10 +243,18 @@ class HybridSampler(ReferenceSampler):
             if not any(alive) or _t == sp.max_tokens - 1:
                 break
             logits = self._step(tok, st)                 # finished rows keep stepping; their outputs are ignored
+            if moes:
+                step_routing.append(torch.stack([mm.routing_log.pop() for mm in moes], 1))           # [B, L, k]
         for b in range(B):
             pi = seq_prompt[b]
-            results[pi * sp.n + (b % sp.n)] = {"token_ids": out[b], "logprobs": lps[b], "finish_reason": reason[b],
-                                               "prompt_len": len(prompts[pi]), "prompt_index": pi, "text": None}
+            res = {"token_ids": out[b], "logprobs": lps[b], "finish_reason": reason[b],
+                   "prompt_len": len(prompts[pi]), "prompt_index": pi, "text": None}
+            if moes:
+                # one row per token that was FED to the model: the prompt and all drawn tokens but the last
+                p = owner[b]
+                rows = [pre_routing[int(cu[p]):int(cu[p + 1])]] + [s[b:b + 1] for s in step_routing[:max(0, len(out[b]) - 1)]]
+                res["routed_experts"] = torch.cat(rows).to(torch.int32).cpu()
+            results[pi * sp.n + (b % sp.n)] = res
 
     def kv_bytes(self) -> int:
         return self.last_state_bytes

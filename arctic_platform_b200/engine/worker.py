@@ -126,6 +126,9 @@ class EngineWorker:
             if self.model_cfg.layer_types is not None:
                 # hybrid family: recurrent state + sparse K/V layers, served by the stateful tensor-op engine
                 from .hybrid_sampler import HybridSampler as SamplerEngine      # noqa: F811
+            elif vc.get("enable_return_routed_experts") and self.model_cfg.is_moe:
+                # rollout routing replay: the tensor-op engine records the experts chosen for every fed token
+                from .hybrid_sampler import HybridSampler as SamplerEngine      # noqa: F811
             elif self.device.type != "cuda":
                 from .reference_sampler import ReferenceSampler as SamplerEngine   # noqa: F811  (CPU: recompute sampler)
             self.sampler = SamplerEngine(
@@ -134,6 +137,8 @@ class EngineWorker:
                 max_seq_len=int(vc.get("max_model_len", 8192)),
                 cascade=bool((job_config.get("arctic_inference_config") or {}).get("zorro_inference", {}).get("enable", True)),
                 seed=seed, eos_token_id=vc.get("eos_token_id"), quantization=vc.get("quantization"))
+            if vc.get("enable_return_routed_experts"):
+                self.sampler.always_return_routing = True
             return True
         m = model if model is not None else self._load_model(job_config, dtype, seed)
         ep = int((job_config.get("ds_worker_config") or {}).get("expert_parallel", 1) or 1)

@@ -287,8 +287,24 @@ class DecoderLM(nn.Module):
         return self.embed if self.lm_head is None else self.lm_head
 
     # --------------------------------------------------------------- forward
-    def forward_hidden(self, input_ids: torch.Tensor, positions: torch.Tensor, layout: AttnLayout) -> torch.Tensor:
-        """Final-norm hidden states ``[T, H]`` for packed ``input_ids [T]``."""
+    def forward_hidden(self, input_ids: torch.Tensor, positions: torch.Tensor, layout: AttnLayout,
+                       routed_experts: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Final-norm hidden states ``[T, H]`` for packed ``input_ids [T]``.  ``routed_experts [T, L_moe, k]`` replays
+        the expert choice recorded for every token and MoE layer elsewhere (the sampler that drew the rollout);
+        entries of -1 leave the choice to the router (arctic_platform/model/implementations/qwen35/models/qwen3_5_moe/
+        modeling_qwen3_5_moe.py:758-798 slices the same tensor per layer)."""
+        if routed_experts is not None:
+            moes = [blk.mlp for blk in self.blocks if blk.mlp is not None]
+            if routed_experts.shape[0] != input_ids.shape[0] or routed_experts.shape[1] != len(moes):
+                raise ValueError(f"routed_experts {tuple(routed_experts.shape)}: expected [{input_ids.shape[0]}, "
+                                 f"{len(moes)}, k]")
+            for i, m in enumerate(moes):
+                m.routed_experts = routed_experts[:, i].to(input_ids.device)
+            try:
+                return self.forward_hidden(input_ids, positions, layout)
+            finally:
+                for m in moes:
+                    m.routed_experts = None
         x = torch.nn.functional.embedding(input_ids, self.embed)
         rope = self.rope(x.device)
         positions = positions.to(torch.int32) if x.is_cuda else positions
@@ -327,14 +343,17 @@ def hash_name(name: str) -> int:
     return h
 
 
-def token_logprobs(model: DecoderLM, packed, inv_temperature=1.0, with_entropy: bool = True, action_masks=None):
+def token_logprobs(model: DecoderLM, packed, inv_temperature=1.0, with_entropy: bool = True, action_masks=None,
+                   routed_experts=None):
     """Log-probabilities (and entropies) of ``packed.labels`` under ``model``; ``packed`` is a
     :class:`~arctic_platform_b200.rl.zorro_train.layout.PackedBatch` already on the model's device.
     Returns fp32 tensors of shape ``[N]`` in original sample order.  ``action_masks`` (one row per prediction)
     restricts the distribution of the constrained rows to their legal tokens."""
     from ..ops.logprob import lm_head_logprobs
 
-    hidden = model.forward_hidden(packed.input_ids, packed.positions, packed.layout)
+    if routed_experts is not None:          # [B, S, L_moe, k] aligned with the input grid -> packed token order
+        routed_experts = packed.gather_inputs(routed_experts)
+    hidden = model.forward_hidden(packed.input_ids, packed.positions, packed.layout, routed_experts)
     pred = hidden.index_select(0, packed.pred_index)
     if action_masks is not None:
         from ..utils.action_masks import masked_logprobs

@@ -79,6 +79,7 @@ class LatentMoEFeedForward(MoEFeedForward):
         self.replay_mode: Optional[str] = None
         self._captured: list = []
         self.routed_experts: Optional[torch.Tensor] = None
+        self.routing_log: Optional[list] = None
         # names the SwiGLU layer's users look for
         self.shared_wgu = self.shared_gate = None
         self.wgu = None
@@ -104,6 +105,8 @@ class LatentMoEFeedForward(MoEFeedForward):
                             cfg.moe_n_group, cfg.moe_topk_group)
         if self.replay_mode == "capture":
             self._captured.append(idx.detach())
+        if self.routing_log is not None:
+            self.routing_log.append(idx.detach())
         if self.tokens_per_expert is not None and self.training and self.replay_mode != "replay":
             self.tokens_per_expert += torch.bincount(idx.reshape(-1), minlength=cfg.num_experts).to(self.tokens_per_expert.dtype)
         flat_e = idx.reshape(-1)

@@ -48,6 +48,11 @@ def route_topk(logits: torch.Tensor, k: int, renorm: bool, score_func: str = "so
         if routed_experts.shape[-1] != k:
             raise ValueError(f"routed_experts has {routed_experts.shape[-1]} experts per token, the router keeps {k}")
         idx = routed_experts.to(torch.int64)
+        if bool((idx < 0).any()):
+            # tokens without a recorded decision (marked -1) route themselves
+            with torch.no_grad():       # a decision only: the graph must not depend on whether a replay was partial
+                _w, own = route_topk(logits, k, renorm, score_func, route_scale, expert_bias, None, n_group, topk_group)
+            idx = torch.where(idx < 0, own, idx)
     else:
         with torch.no_grad():
             pick = scores if expert_bias is None else scores + expert_bias.float()
@@ -184,6 +189,7 @@ class MoEFeedForward(nn.Module):
         self.replay_mode: Optional[str] = None
         self._captured: list = []
         self.routed_experts: Optional[torch.Tensor] = None
+        self.routing_log: Optional[list] = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         y = self._routed(x)
@@ -205,6 +211,8 @@ class MoEFeedForward(nn.Module):
                             self.expert_bias, forced, cfg.moe_n_group, cfg.moe_topk_group)
         if self.replay_mode == "capture":
             self._captured.append(idx.detach())
+        if self.routing_log is not None:                         # a sampler records what it routed, pass by pass
+            self.routing_log.append(idx.detach())
         if self.tokens_per_expert is not None and self.training and self.replay_mode != "replay":
             self.tokens_per_expert += torch.bincount(idx.reshape(-1), minlength=cfg.num_experts).to(self.tokens_per_expert.dtype)
         if self.ep is not None:

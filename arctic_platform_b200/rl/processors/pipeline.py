@@ -127,8 +127,11 @@ def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = 
         owned = None
         with sft_profile.timed("fwd"):
             if sp_group is None:
+                # rollout routing replay: the experts the sampler chose, per input token and MoE layer
+                routed = batch.get("routed_experts") if packed.src_index is not None else None
                 lp, ent = token_logprobs(model, packed, 1.0 / temperature, with_entropy=want_entropy,
-                                         action_masks=action_masks_of(batch, packed))
+                                         action_masks=action_masks_of(batch, packed),
+                                         routed_experts=None if routed is None else routed.to(device))
             else:
                 lp, ent, owned = _sp_logprobs(model, packed, sp_group, 1.0 / temperature, want_entropy, batch)
                 # every rank of the sequence-parallel group holds the same batch and scores its own rows; the loss

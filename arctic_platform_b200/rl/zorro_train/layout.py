@@ -53,6 +53,15 @@ class PackedBatch:
     total_tokens: int            # T
     full_tokens: int             # tokens a non-deduplicated packing would have
     sample_tokens: np.ndarray    # [B] valid prompt+response tokens per sample
+    src_index: Optional[torch.Tensor] = None   # [T] int64: flat index into the [B, S] input grid each packed token came from
+
+    def gather_inputs(self, grid: torch.Tensor) -> torch.Tensor:
+        """Per-input-token values ``[B, S, ...]`` -> ``[T, ...]`` in packed order (a de-duplicated prompt takes the
+        values of its group's first sample)."""
+        if self.src_index is None:
+            raise ValueError("this packed batch does not record where its tokens came from")
+        flat = grid.reshape((grid.shape[0] * grid.shape[1],) + tuple(grid.shape[2:]))
+        return flat[self.src_index.to(grid.device)]
 
     def to(self, device) -> "PackedBatch":
         self.input_ids = self.input_ids.to(device, non_blocking=True)
@@ -130,6 +139,7 @@ def build_packed_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, re
 
     packed_ids = np.empty(T, dtype=np.int64)
     positions = np.empty(T, dtype=np.int32)
+    src = np.empty(T, dtype=np.int64)
     segs: List[List[int]] = []
     for g in range(G):
         b0 = rep[g]
@@ -137,6 +147,7 @@ def build_packed_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, re
         s0 = int(g_start[g])
         if pl:
             packed_ids[s0:s0 + pl] = ids[b0, :P][p_mask[b0]]
+            src[s0:s0 + pl] = b0 * S + np.nonzero(p_mask[b0])[0]
             positions[s0:s0 + pl] = np.arange(pl, dtype=np.int32)
             segs.append([s0, pl, 0, 0, s0, pl])
     for b in range(B):
@@ -147,6 +158,7 @@ def build_packed_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, re
         pl = int(g_plen[g])
         s0 = int(resp_start[b])
         packed_ids[s0:s0 + rl] = ids[b, P:][r_mask[b]]
+        src[s0:s0 + rl] = b * S + P + np.nonzero(r_mask[b])[0]
         positions[s0:s0 + rl] = np.arange(pl, pl + rl, dtype=np.int32)
         segs.append([s0, rl, int(g_start[g]), pl, s0, rl])
 
@@ -175,7 +187,7 @@ def build_packed_batch(input_ids: torch.Tensor, attention_mask: torch.Tensor, re
         input_ids=torch.from_numpy(packed_ids), positions=torch.from_numpy(positions), layout=layout,
         pred_index=torch.from_numpy(pred), labels=torch.from_numpy(labels), out_index=torch.from_numpy(out_idx),
         batch_size=B, response_length=R, num_groups=G, group_of=group_of, total_tokens=T,
-        full_tokens=int((p_len + r_len).sum()), sample_tokens=(p_len + r_len))
+        full_tokens=int((p_len + r_len).sum()), sample_tokens=(p_len + r_len), src_index=torch.from_numpy(src))
 
 
 def build_plain_packed(input_ids: torch.Tensor, attention_mask: torch.Tensor) -> PackedBatch:

@@ -28,6 +28,13 @@ def _settings():
     return (Path(d) if d else None), mode, start
 
 
+def _jsonable(obj):
+    """Tensors / arrays inside a result (recorded expert choices) are taped as nested lists."""
+    if hasattr(obj, "tolist"):
+        return obj.tolist()
+    raise TypeError(f"{type(obj).__name__} is not JSON serialisable")
+
+
 def record_replay_generation(fn: Callable) -> Callable:
     counter = {"i": 0}
 
@@ -50,7 +57,7 @@ def record_replay_generation(fn: Callable) -> Callable:
     def _after(d, i, result):
         if d is not None:
             d.mkdir(parents=True, exist_ok=True)
-            _path(d, i).write_text(json.dumps({"call": i, "result": result}))
+            _path(d, i).write_text(json.dumps({"call": i, "result": result}, default=_jsonable))
         return result
 
     if asyncio.iscoroutinefunction(fn):
