@@ -25,16 +25,21 @@ class TokenOutput:
     log_probs: Optional[List[float]] = None
     stop_reason: Optional[str] = None
     extra: Dict[str, Any] = field(default_factory=dict)
+    routed_experts: Any = None           # [fed tokens, L_moe, k] with ``enable_rollout_routing_replay``
 
 
 class ArcticLLMServer:
     """One generation endpoint.  ``generate`` takes prompt token ids and returns generated token ids -- no
     tokenizer round trip (the reference's adapter decodes ids to text before calling its engine)."""
 
-    def __init__(self, wrapper: ArcticRLClientWrapper, mode: RolloutMode = RolloutMode.HYBRID):
+    def __init__(self, wrapper: ArcticRLClientWrapper, mode: RolloutMode = RolloutMode.HYBRID,
+                 enable_rollout_routing_replay: bool = False):
         self.wrapper = wrapper
         self.mode = RolloutMode(mode)
         self._awake = True
+        # ask the sampler for the experts it chose, so that training can replay them
+        # (arctic_platform/integrations/verl/rollout.py:303-305)
+        self.enable_rollout_routing_replay = bool(enable_rollout_routing_replay)
 
     async def generate(self, prompt_ids: Sequence[int], sampling_params: Optional[dict] = None,
                        request_id: Optional[str] = None, **_) -> TokenOutput:
@@ -42,12 +47,15 @@ class ArcticLLMServer:
         if "max_new_tokens" in sp:
             sp["max_tokens"] = sp.pop("max_new_tokens")
         sp.pop("logprobs", None) if sp.get("logprobs") in (None, False, 0) else None
+        if self.enable_rollout_routing_replay:
+            sp["return_routed_experts"] = True
         loop = asyncio.get_running_loop()
         outs = await loop.run_in_executor(None, lambda: self.wrapper.generate([list(prompt_ids)], sp, routing_key=request_id))
         o = outs[0]
         first = o["outputs"][0] if "outputs" in o else o
         return TokenOutput(list(first.get("token_ids", [])), first.get("logprobs"), first.get("finish_reason"),
-                           {"request_id": request_id})
+                           {"request_id": request_id},
+                           first.get("routed_experts") if self.enable_rollout_routing_replay else None)
 
     async def generate_batch(self, prompts: Sequence[Sequence[int]], sampling_params: Optional[dict] = None) -> List[TokenOutput]:
         return list(await asyncio.gather(*[self.generate(p, sampling_params, str(i)) for i, p in enumerate(prompts)]))
@@ -73,9 +81,10 @@ class ArcticReplica:
     wrapper: ArcticRLClientWrapper
     mode: RolloutMode = RolloutMode.HYBRID
     server: Optional[ArcticLLMServer] = None
+    enable_rollout_routing_replay: bool = False
 
     async def init(self) -> "ArcticReplica":
-        self.server = ArcticLLMServer(self.wrapper, self.mode)
+        self.server = ArcticLLMServer(self.wrapper, self.mode, self.enable_rollout_routing_replay)
         return self
 
     @property

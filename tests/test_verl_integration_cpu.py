@@ -119,6 +119,10 @@ def test_rollout_server_and_registry():
     srv: ArcticLLMServer = rep.server_handle
     out = asyncio.run(srv.generate([1, 2, 3], {"max_new_tokens": 5}, request_id="r1"))
     assert out.token_ids == [7, 8, 9] and out.stop_reason == "length" and fake.calls[-1][1][1]["max_tokens"] == 5
+    assert out.routed_experts is None and "return_routed_experts" not in fake.calls[-1][1][1]
+    replay = asyncio.run(ArcticReplica(1, w, RolloutMode.HYBRID, enable_rollout_routing_replay=True).init()).server_handle
+    asyncio.run(replay.generate([1, 2, 3], {"max_new_tokens": 5}))
+    assert fake.calls[-1][1][1]["return_routed_experts"] is True      # the sampler is asked for its expert choices
     asyncio.run(srv.sleep())
     asyncio.run(srv.sleep())                                        # idempotent
     asyncio.run(srv.wake_up())
