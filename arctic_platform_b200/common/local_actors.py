@@ -112,6 +112,15 @@ class SpawnedActor:
     def terminate(self) -> None:
         self.kill(grace_s=0.0)
 
+    def request_destroy(self) -> None:
+        """Posts the shutdown message and returns: the process ends by itself once its current call comes back (a
+        bounded device wait or the process group's timeout ends a call stuck behind a failed peer).  Used instead of
+        ``terminate`` while the ranks' buffers are bound to an NVSwitch multicast object."""
+        try:
+            self._conn.send(None)
+        except Exception:
+            pass
+
     def kill(self, grace_s: float = 2.0) -> None:
         try:
             if self._proc.is_alive() and grace_s > 0:
@@ -196,6 +205,9 @@ class RankWorkerHandle:
     def sync_to(self, dst: "RankWorkerHandle") -> int:
         """Weight hand-over to another job's engine in the SAME rank process (the in-process kernel runs there)."""
         return self.actor.call("sync", self.key, dst.key)
+
+    def request_destroy(self) -> None:
+        self.actor.request_destroy()
 
     def terminate(self) -> None:
         """Stops the rank's process outright (the job is lost: a peer failed while this rank may be waiting for it

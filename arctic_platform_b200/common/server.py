@@ -87,8 +87,19 @@ class RanksLost(RuntimeError):
 
 
 def _hard_stop(worker) -> None:
+    """Stops a rank that is stuck behind a failed peer.  Normally the rank's process is terminated.  When the job
+    runs its kernels on NVSwitch multicast (``APB_MULTIMEM=1``) the rank's buffers are bound to a multicast object
+    shared with the surviving ranks, and ending a process in that state can fault the other GPUs: the rank is then
+    only ASKED to shut down (``destroy``), and what ends its wait is the bounded device wait (1 s, status word) and
+    the process group's timeout."""
+    from ..parallel.symm import multimem_enabled
     try:
-        if hasattr(worker, "terminate"):
+        if multimem_enabled():
+            if hasattr(worker, "request_destroy"):
+                worker.request_destroy()
+            else:
+                worker.kill()               # in-process and spawned actors: kill() asks the worker to destroy itself
+        elif hasattr(worker, "terminate"):
             worker.terminate()
         else:
             worker.kill()
@@ -399,25 +410,41 @@ class ArcticRLServerCore:
     # ------------------------------------------------------------------ checkpoints
     def save(self, job_id: int, path: Optional[str] = None, step: Optional[int] = None, export_hf: bool = False,
              save_total_limit: Optional[int] = None) -> Dict[str, Any]:
+        """``<root>/checkpoint-<step>/`` is a complete engine checkpoint directory (``latest``, ``global_step<N>/``,
+        optional ``hf/``); ``<root>/latest`` holds the integer step; old ``checkpoint-*`` children are pruned under
+        ``root`` (arctic_platform/common/ray_server.py:765-789 in the reference)."""
         from .utils.checkpoint import prune_checkpoint_dirs, resolve_checkpoint_save_paths
         job = self._job(job_id, ("training",))
         root = path or job.info.get("checkpoint_path")
         if not root:
             raise JobError(400, "no checkpoint path configured")
-        save_dir, tag = resolve_checkpoint_save_paths(root, step)
-        outs = self._call_job(job, "save_checkpoint", None, save_dir, tag, export_hf)
-        if save_total_limit:
-            prune_checkpoint_dirs(save_dir, save_total_limit)
-        return {"job_id": job.job_id, "path": save_dir, "tag": tag, "files": outs[0].get("files", [])}
+        save_dir, prune_root = resolve_checkpoint_save_paths(root, step)
+        os.makedirs(save_dir, exist_ok=True)
+        outs = self._call_job(job, "save_checkpoint", None, save_dir, None, export_hf)
+        if step is not None:
+            with open(os.path.join(prune_root, "latest"), "w", encoding="utf-8") as f:
+                f.write(str(int(step)))
+        if save_total_limit and int(save_total_limit) > 0:
+            prune_checkpoint_dirs(prune_root, int(save_total_limit))
+        first = outs[0] if outs and isinstance(outs[0], dict) else {}
+        return {"job_id": job.job_id, "path": save_dir, "hf_path": first.get("hf_path"),
+                "global_step": first.get("global_step"), "tag": first.get("tag"), "files": first.get("files", [])}
 
     def load_checkpoint(self, job_id: int, path: Optional[str] = None, step: Optional[int] = None) -> Dict[str, Any]:
+        from .utils.checkpoint import resolve_checkpoint_load_path
         job = self._job(job_id, ("training",))
         root = path or job.info.get("checkpoint_path")
         if not root:
             raise JobError(400, "no checkpoint path configured")
-        tag = f"checkpoint-{step}" if step is not None else None
-        steps = self._call_job(job, "load_checkpoint", None, root, tag)
-        return {"job_id": job.job_id, "global_steps": int(steps[0] or 0)}
+        ckpt = resolve_checkpoint_load_path(root, step, explicit_path=path is not None)
+        # an explicit path or step that holds no checkpoint is an error, never a silent restart from step 0
+        strict = path is not None or step is not None
+        try:
+            steps = self._call_job(job, "load_checkpoint", None, ckpt, None, strict)
+        except FileNotFoundError as exc:
+            raise JobError(404, str(exc)) from exc
+        n = int(steps[0] or 0)
+        return {"job_id": job.job_id, "path": ckpt, "global_step": n, "global_steps": n}
 
     # ------------------------------------------------------------------ rollout
     def generate(self, job_id: int, prompts, sampling_params=None, routing_key=None, strict: bool = False):

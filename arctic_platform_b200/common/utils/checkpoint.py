@@ -10,10 +10,29 @@ from typing import Optional, Tuple
 _TAG = re.compile(r"^checkpoint-(\d+)$")
 
 
-def resolve_checkpoint_save_paths(root: str, step: Optional[int]) -> Tuple[str, Optional[str]]:
-    """``(save_dir, tag)``: with a step the engine writes under ``root`` with tag ``checkpoint-<step>``;
-    without one it uses its own default tag (``global_step<N>``)."""
-    return (str(root), f"checkpoint-{int(step)}") if step is not None else (str(root), None)
+def resolve_checkpoint_save_paths(root: str, step: Optional[int]) -> Tuple[str, str]:
+    """``(save_dir, prune_root)``.  With a step the checkpoint is a self-contained directory
+    ``<root>/checkpoint-<step>`` (its own ``latest``, ``global_step<N>/`` and ``hf/`` inside); without one the
+    engine writes straight into ``root``.  ``prune_root`` -- the parent of the ``checkpoint-*`` children -- is
+    always ``root``."""
+    root = str(root)
+    return (str(Path(root) / f"checkpoint-{int(step)}"), root) if step is not None else (root, root)
+
+
+def resolve_checkpoint_load_path(root: str, step: Optional[int], explicit_path: bool) -> str:
+    """Directory handed to the engines' ``load_checkpoint``: ``<root>/checkpoint-<step>`` for a step; for the job's
+    configured root (no explicit path) the child named by the integer in ``<root>/latest``; otherwise ``root``."""
+    root = str(root)
+    if step is not None:
+        return str(Path(root) / f"checkpoint-{int(step)}")
+    if not explicit_path:
+        latest = Path(root) / "latest"
+        if latest.is_file():
+            try:
+                return str(Path(root) / f"checkpoint-{int(latest.read_text().strip())}")
+            except ValueError:
+                pass                      # an engine-level ``latest`` (a tag): root itself is the checkpoint directory
+    return root
 
 
 def prune_checkpoint_dirs(parent: str, keep: int) -> list:

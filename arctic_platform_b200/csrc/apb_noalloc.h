@@ -20,7 +20,9 @@
 //   * The function itself calls no cudaMalloc, cudaFree or any other allocating routine; inputs and
 //     outputs are still supplied by the caller.
 //   * The first call on a device looks up the device address of the scratch array (and configures
-//     the kernel's shared-memory limit).  Make that first call outside any stream capture.
+//     the kernel's shared-memory limit).  Make that first call outside any stream capture.  The
+//     looked-up address is cached per device without a lock; host threads that race on the first
+//     call each store the same address, so no serialisation is needed for that.
 //   * All calls share the one scratch array, which keeps the contents of the previous call.  The
 //     kernel overwrites every record it later reads, so nothing has to be cleared, but two calls
 //     that overlap on the GPU (different streams, or concurrent host threads) race on the scratch:

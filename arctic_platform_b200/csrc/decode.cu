@@ -18,6 +18,7 @@ __global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ k, long 
                                       const __nv_bfloat16* __restrict__ v, long long ldv,
                                       const int* __restrict__ slots, __nv_bfloat16* __restrict__ kcache,
                                       __nv_bfloat16* __restrict__ vcache, int T, int Hkv, int D) {
+  pdl_entry();
   const int vec_per_row = Hkv * D / 8;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
        i < static_cast<long long>(T) * vec_per_row; i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -50,6 +51,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const int* __restrict__
                     const int* __restrict__ kv_len, const __nv_bfloat16* __restrict__ kcache,
                     const __nv_bfloat16* __restrict__ vcache, float* __restrict__ out_o, float* __restrict__ out_ml,
                     int Hq, int Hkv, int splits, float scale_log2) {
+  pdl_entry();
   static_assert(D == 128, "head_dim 128");
   const int g = blockIdx.x / Hkv;
   const int kvh = blockIdx.x % Hkv;
@@ -271,6 +273,7 @@ paged_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const int* __restri
                         const int* __restrict__ kv_len, const __nv_bfloat16* __restrict__ kcache,
                         const __nv_bfloat16* __restrict__ vcache, float* __restrict__ out_o, float* __restrict__ out_ml,
                         int Hq, int Hkv, int splits, float scale_log2) {
+  pdl_entry();
   constexpr int D = 128;
   extern __shared__ __align__(128) uint8_t dec_smem[];
   const int g = blockIdx.x / Hkv;
@@ -465,6 +468,7 @@ struct MergeSrc {
 };
 __global__ void decode_merge_kernel(MergeSrc src, __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out,
                                     int rows, int Hq, int D) {
+  pdl_entry();
   const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (gw >= static_cast<long long>(rows) * Hq) return;
@@ -504,6 +508,7 @@ decode_qkv_post_kernel(float* __restrict__ acc, long long ld_acc, const __nv_bfl
                        const float* __restrict__ sin_t, const int* __restrict__ pos, const int* __restrict__ slots,
                        __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ kcache,
                        __nv_bfloat16* __restrict__ vcache, int B, int Hq, int Hkv, float eps) {
+  pdl_entry();
   constexpr int E2 = D / 64;
   const int lane = threadIdx.x & 31;
   const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
@@ -562,6 +567,78 @@ decode_qkv_post_kernel(float* __restrict__ acc, long long ld_acc, const __nv_bfl
   }
 }
 
+// ---------------------------------------------------------------------------- step bookkeeping
+// Start of a decode step, one block per slot: the cache slot of the token being fed (page table look-up; -1 for
+// an inactive slot) and the token's embedding row copied into the activation buffer.
+__global__ void __launch_bounds__(128)
+decode_begin_kernel(const int* __restrict__ tokens, const int* __restrict__ pos, const int* __restrict__ active,
+                    const int* __restrict__ page_table, int max_pages, const __nv_bfloat16* __restrict__ embed,
+                    long long ld_embed, int H, int vocab, int* __restrict__ slots, __nv_bfloat16* __restrict__ x) {
+  pdl_entry();
+  const int b = blockIdx.x;
+  const int ps = pos[b];
+  if (threadIdx.x == 0) {
+    int slot = -1;
+    if (active[b] > 0 && ps >= 0 && ps / kPage < max_pages)
+      slot = page_table[static_cast<long long>(b) * max_pages + ps / kPage] * kPage + ps % kPage;
+    slots[b] = slot;
+  }
+  int tok = tokens[b];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+  const uint4* src = reinterpret_cast<const uint4*>(embed + static_cast<long long>(tok) * ld_embed);
+  uint4* dst = reinterpret_cast<uint4*>(x + static_cast<long long>(b) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+struct DecodeAdvanceArgs {
+  const int* new_tok;
+  const float* new_lp;
+  int* active;
+  int* finished;
+  int* tokens;
+  int* pos;
+  int* len;
+  int* priv_len;
+  const int* max_len;
+  const int* stop;       // 8 stop token ids, -1 = unused
+  long long* out_idx;    // [B] tokens emitted so far
+  int* out_tokens;       // [B, out_cap]
+  float* out_lps;        // [B, out_cap]
+  int out_cap;
+  int* step;             // global decode step (random stream)
+  int B;
+};
+
+// End of a decode step: store the sampled token and its log-prob, decide which sequences end (stop token or length
+// limit), and advance positions / lengths of those that go on.  One thread per slot.
+__global__ void __launch_bounds__(256) decode_advance_kernel(const DecodeAdvanceArgs a) {
+  pdl_entry();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b == 0) *a.step += 1;
+  if (b >= a.B) return;
+  const bool act = a.active[b] > 0;
+  if (!act) return;
+  const int tok = a.new_tok[b];
+  long long idx = a.out_idx[b];
+  if (idx > a.out_cap - 1) idx = a.out_cap - 1;
+  a.out_tokens[static_cast<long long>(b) * a.out_cap + idx] = tok;
+  a.out_lps[static_cast<long long>(b) * a.out_cap + idx] = a.new_lp[b];
+  a.out_idx[b] += 1;
+  const int newlen = a.len[b] + 1;
+  bool stop = false;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) stop |= (a.stop[i] == tok);
+  if (stop || newlen >= a.max_len[b]) {
+    a.finished[b] = 1;
+    a.active[b] = 0;
+    return;
+  }
+  a.tokens[b] = tok;
+  a.pos[b] += 1;
+  a.len[b] = newlen;
+  a.priv_len[b] += 1;
+}
+
 // ---------------------------------------------------------------------------- sampling
 __device__ __forceinline__ uint32_t hash_u32(uint32_t x) {
   x ^= x >> 16;
@@ -588,6 +665,7 @@ constexpr int kSelBins = 2048;
 __global__ void __launch_bounds__(1024)
 sample_threshold_kernel(const float* __restrict__ logits, long long ldl, const float* __restrict__ temperature, int V,
                         const int* __restrict__ top_k, const float* __restrict__ top_p, float* __restrict__ thr) {
+  pdl_entry();
   const int b = blockIdx.x;
   const float T = temperature[b];
   const int k_lim = top_k ? top_k[b] : 0;
@@ -721,6 +799,7 @@ __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, long long ldl, const float* __restrict__ temperature, int V,
               uint32_t seed, const int* __restrict__ step_dev, const float* __restrict__ thr,
               int* __restrict__ tokens, float* __restrict__ logprobs) {
+  pdl_entry();
   const int b = blockIdx.x;
   const uint32_t step = step_dev ? static_cast<uint32_t>(*step_dev) : 0u;
   const float T = temperature[b];
@@ -731,24 +810,47 @@ sample_kernel(const float* __restrict__ logits, long long ldl, const float* __re
   float best = -INFINITY, best_z = 0.f;
   int best_i = 0;
   float m = -INFINITY, s = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float z = row[i] * invT;
+  // one hash per element: the per-(seed, step, row) part is mixed once, the column enters by a Weyl step
+  const uint32_t base = hash_u32(seed ^ (step * 0x9E3779B9u)) ^ hash_u32(static_cast<uint32_t>(b) * 0x85ebca6bU + 1u);
+  auto consider = [&](float raw, int i) {
+    const float z = raw * invT;
+    // running softmax statistics with ONE exponential per element (the rescaling branch is taken only when a new
+    // maximum appears, which becomes rare after the first few elements of a thread)
+    if (z > m) {
+      s = s * __expf(m - z) + 1.f;
+      m = z;
+    } else if (z > -INFINITY) {
+      s += __expf(z - m);
+    }
     float key = z;
-    if (!greedy && z >= cut) {
-      const uint32_t h = hash_u32(hash_u32(seed ^ (step * 0x9E3779B9u)) ^ hash_u32(static_cast<uint32_t>(b) * 0x85ebca6bU + i));
-      const float u = (static_cast<float>(h >> 8) + 0.5f) * (1.f / 16777216.f);
-      key = z - __logf(-__logf(u));
-    } else if (!greedy) {
-      key = -INFINITY;  // outside the top-k / top-p set
+    if (!greedy) {
+      if (z >= cut) {
+        const uint32_t h = hash_u32(base + static_cast<uint32_t>(i) * 0x9E3779B9u);
+        const float u = (static_cast<float>(h >> 8) + 0.5f) * (1.f / 16777216.f);
+        key = z - __logf(-__logf(u));
+      } else {
+        key = -INFINITY;  // outside the top-k / top-p set
+      }
     }
     if (key > best) {
       best = key;
       best_i = i;
       best_z = z;
     }
-    const float mn = fmaxf(m, z);
-    s = s * __expf(m - mn) + __expf(z - mn);
-    m = mn;
+  };
+  if ((ldl & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    const int n4 = V >> 2;
+    for (int i4 = threadIdx.x; i4 < n4; i4 += blockDim.x) {
+      const float4 v = row4[i4];
+      consider(v.x, 4 * i4);
+      consider(v.y, 4 * i4 + 1);
+      consider(v.z, 4 * i4 + 2);
+      consider(v.w, 4 * i4 + 3);
+    }
+    for (int i = 4 * n4 + threadIdx.x; i < V; i += blockDim.x) consider(row[i], i);
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) consider(row[i], i);
   }
   __shared__ float sb[32], sz[32], sm[32], ss[32];
   __shared__ int si[32];
@@ -818,11 +920,10 @@ int apb_kv_cache_write(const void* k, long long ldk, const void* v, long long ld
   if ((D % 8) || (ldk % 8) || (ldv % 8)) return kBadArgument;
   const long long n = static_cast<long long>(T) * Hkv * D / 8;
   const int grid = static_cast<int>((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
-  kv_cache_write_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(k), ldk,
-                                             static_cast<const __nv_bfloat16*>(v), ldv, slots,
-                                             static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache),
-                                             T, Hkv, D);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(kv_cache_write_kernel, dim3(grid), dim3(256), 0, s,
+                                        static_cast<const __nv_bfloat16*>(k), ldk, static_cast<const __nv_bfloat16*>(v),
+                                        ldv, slots, static_cast<__nv_bfloat16*>(kcache),
+                                        static_cast<__nv_bfloat16*>(vcache), T, Hkv, D));
 }
 
 int apb_decode_qkv_post(float* acc, long long ld_acc, const void* wq, const void* wk, const float* cos_t,
@@ -832,17 +933,16 @@ int apb_decode_qkv_post(float* acc, long long ld_acc, const void* wq, const void
   const long long warps = static_cast<long long>(B) * (Hq + 2 * Hkv);
   const int grid = static_cast<int>((warps * 32 + 255) / 256);
 #define APB_QKV_POST(DD)                                                                                       \
-  decode_qkv_post_kernel<DD><<<grid, 256, 0, s>>>(acc, ld_acc, static_cast<const __nv_bfloat16*>(wq),          \
-                                                  static_cast<const __nv_bfloat16*>(wk), cos_t, sin_t, pos, slots, \
-                                                  static_cast<__nv_bfloat16*>(q_out),                         \
-                                                  static_cast<__nv_bfloat16*>(kcache),                        \
-                                                  static_cast<__nv_bfloat16*>(vcache), B, Hq, Hkv, eps)
+  return static_cast<int>(launch_kernel(decode_qkv_post_kernel<DD>, dim3(grid), dim3(256), 0, s, acc, ld_acc,  \
+                                        static_cast<const __nv_bfloat16*>(wq),                                \
+                                        static_cast<const __nv_bfloat16*>(wk), cos_t, sin_t, pos, slots,      \
+                                        static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(kcache), \
+                                        static_cast<__nv_bfloat16*>(vcache), B, Hq, Hkv, eps))
   if (D == 128) APB_QKV_POST(128);
-  else if (D == 64) APB_QKV_POST(64);
-  else if (D == 256) APB_QKV_POST(256);
-  else return kBadArgument;
+  if (D == 64) APB_QKV_POST(64);
+  if (D == 256) APB_QKV_POST(256);
 #undef APB_QKV_POST
-  return static_cast<int>(cudaGetLastError());
+  return kBadArgument;
 }
 
 // Selects the scalar (CUDA-core) paged decode kernel instead of the MMA one: numerics cross-check and A/B timing.
@@ -868,11 +968,11 @@ int apb_paged_decode_partial(const void* q, const int* q_start, const int* q_cou
       if (e != cudaSuccess) return static_cast<int>(e);
       configured[dev & 63] = true;
     }
-    paged_decode_mma_kernel<<<grid, kDecThreads, kMmaSmem, s>>>(
-        static_cast<const __nv_bfloat16*>(q), q_start, q_count, pages, max_pages, kv_len,
-        static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache), out_o, out_ml, Hq, Hkv,
-        splits, sl2);
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(launch_kernel(paged_decode_mma_kernel, grid, dim3(kDecThreads), kMmaSmem, s,
+                                          static_cast<const __nv_bfloat16*>(q), q_start, q_count, pages, max_pages,
+                                          kv_len, static_cast<const __nv_bfloat16*>(kcache),
+                                          static_cast<const __nv_bfloat16*>(vcache), out_o, out_ml, Hq, Hkv, splits,
+                                          sl2));
   }
 #define APB_DEC(RR)                                                                                           \
   paged_decode_kernel<RR, 128><<<grid, kDecThreads, 0, s>>>(                                                  \
@@ -902,16 +1002,42 @@ int apb_decode_merge(const float* const* o_ptrs, const float* const* ml_ptrs, co
   }
   const long long warps = static_cast<long long>(rows) * Hq;
   const int grid = static_cast<int>((warps * 32 + 255) / 256);
-  decode_merge_kernel<<<grid, 256, 0, s>>>(src, static_cast<__nv_bfloat16*>(out), lse, rows, Hq, D);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(decode_merge_kernel, dim3(grid), dim3(256), 0, s, src,
+                                        static_cast<__nv_bfloat16*>(out), lse, rows, Hq, D));
+}
+
+// Step bookkeeping of the rollout engine (see decode_begin_kernel / decode_advance_kernel).  All arrays are
+// device buffers of the engine; x [B, H] bf16 receives the embedding rows, slots [B] the cache slots.
+int apb_decode_begin(const int* tokens, const int* pos, const int* active, const int* page_table, int max_pages,
+                     const void* embed, long long ld_embed, int H, int vocab, int* slots, void* x, int B,
+                     cudaStream_t s) {
+  if (B <= 0) return 0;
+  if ((H % 8) || (ld_embed % 8) || !tokens || !pos || !active || !page_table || !embed || !slots || !x)
+    return kBadArgument;
+  return static_cast<int>(launch_kernel(decode_begin_kernel, dim3(B), dim3(128), 0, s, tokens, pos, active, page_table,
+                                        max_pages, static_cast<const __nv_bfloat16*>(embed), ld_embed, H, vocab, slots,
+                                        static_cast<__nv_bfloat16*>(x)));
+}
+
+int apb_decode_advance(const int* new_tok, const float* new_lp, int* active, int* finished, int* tokens, int* pos,
+                       int* len, int* priv_len, const int* max_len, const int* stop, long long* out_idx,
+                       int* out_tokens, float* out_lps, int out_cap, int* step, int B, cudaStream_t s) {
+  if (B <= 0) return 0;
+  if (!new_tok || !new_lp || !active || !finished || !tokens || !pos || !len || !priv_len || !max_len || !stop ||
+      !out_idx || !out_tokens || !out_lps || !step || out_cap < 1)
+    return kBadArgument;
+  DecodeAdvanceArgs a{new_tok, new_lp, active, finished, tokens, pos, len, priv_len, max_len, stop, out_idx,
+                      out_tokens, out_lps, out_cap, step, B};
+  return static_cast<int>(launch_kernel(decode_advance_kernel, dim3((B + 255) / 256), dim3(256), 0, s, a));
 }
 
 // step_dev: device int holding the decode step (read by the kernel, so a captured graph sees new values).
 int apb_sample(const float* logits, long long ldl, const float* temperature, int B, int V, unsigned seed,
                const int* step_dev, int* tokens, float* logprobs, cudaStream_t s) {
   if (B <= 0) return 0;
-  sample_kernel<<<B, 1024, 0, s>>>(logits, ldl, temperature, V, seed, step_dev, nullptr, tokens, logprobs);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(sample_kernel, dim3(B), dim3(1024), 0, s, logits, ldl, temperature, V,
+                                        static_cast<uint32_t>(seed), step_dev, static_cast<const float*>(nullptr),
+                                        tokens, logprobs));
 }
 
 // Sampling restricted to the top-k tokens and to the smallest set of tokens with probability mass >= top_p.
@@ -921,8 +1047,11 @@ int apb_sample_filtered(const float* logits, long long ldl, const float* tempera
                         float* logprobs, cudaStream_t s) {
   if (B <= 0) return 0;
   if (!thr) return kBadArgument;
-  sample_threshold_kernel<<<B, 1024, 0, s>>>(logits, ldl, temperature, V, top_k, top_p, thr);
-  sample_kernel<<<B, 1024, 0, s>>>(logits, ldl, temperature, V, seed, step_dev, thr, tokens, logprobs);
-  return static_cast<int>(cudaGetLastError());
+  cudaError_t e = launch_kernel(sample_threshold_kernel, dim3(B), dim3(1024), 0, s, logits, ldl, temperature, V, top_k,
+                                top_p, thr);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(launch_kernel(sample_kernel, dim3(B), dim3(1024), 0, s, logits, ldl, temperature, V,
+                                        static_cast<uint32_t>(seed), step_dev, static_cast<const float*>(thr), tokens,
+                                        logprobs));
 }
 }

@@ -64,7 +64,10 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const int b1 = min(n_blocks_all, b0 + per);
   const int n_blocks = max(0, b1 - b0);
   const int last_page = (len + 15) / 16 - 1;
-  if (nq <= 0) return;  // uniform across the CTA, nothing allocated yet
+  if (nq <= 0) {        // uniform across the CTA, nothing allocated yet
+    pdl_entry();        // a chained kernel never ends before its predecessor has: later kernels rely on that order
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kDpSlots; ++s) {
@@ -85,6 +88,9 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // chained launch: barriers and TMEM are set up; q and the newest KV rows come from the previous kernels
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0 && n_blocks > 0) {
@@ -294,7 +300,6 @@ int apb_decode_prefix_tc(const void* q, int Bq, const int* q_start, const int* q
     configured[dev & 63] = true;
   }
   const dim3 grid(G * Hkv, splits);
-  decode_prefix_kernel<<<grid, kDpThreads, kDpSmem, s>>>(tq, tk, tv, p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(decode_prefix_kernel, grid, dim3(kDpThreads), kDpSmem, s, tq, tk, tv, p));
 }
 }

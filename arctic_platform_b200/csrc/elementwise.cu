@@ -50,6 +50,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int T, int H, float eps,
                    float w_offset, float* __restrict__ x_f32) {
+  pdl_entry();
   __shared__ float scratch[32];
   const int nvec = H / 8;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
@@ -383,6 +384,7 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_qkv,
 // SwiGLU on fp32 split-K sums: acc [T, 2I] interleaved (gate, up) -> act [T, I] bf16; acc is reset to zero.
 // One thread handles four outputs (eight inputs, two 16-byte loads).
 __global__ void swiglu_f32in_kernel(float* __restrict__ acc, __nv_bfloat16* __restrict__ act, long long n_quads) {
+  pdl_entry();
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n_quads;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float4* p = reinterpret_cast<float4*>(acc + i * 8);
@@ -454,11 +456,11 @@ int apb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void
   if (T <= 0) return 0;
   if (H % 8 || H > kNormThreads * 8 * kNormMaxVec) return kBadArgument;
   const int grid = T < 148 * 8 ? T : 148 * 8;
-  rmsnorm_fwd_kernel<<<grid, kNormThreads, 0, s>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
-      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(res_out),
-      rstd, T, H, eps, w_offset, nullptr);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(rmsnorm_fwd_kernel, dim3(grid), dim3(kNormThreads), 0, s,
+                                        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
+                                        static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
+                                        static_cast<__nv_bfloat16*>(res_out), rstd, T, H, eps, w_offset,
+                                        static_cast<float*>(nullptr)));
 }
 
 // Same as apb_rmsnorm_fwd with the input taken from an fp32 buffer (split-K GEMM sums) that is reset to
@@ -468,10 +470,11 @@ int apb_rmsnorm_fwd_f32in(float* x_f32, const void* res, const void* w, void* y,
   if (T <= 0) return 0;
   if (H % 8 || H > kNormThreads * 8 * kNormMaxVec || !res_out) return kBadArgument;
   const int grid = T < 148 * 8 ? T : 148 * 8;
-  rmsnorm_fwd_kernel<<<grid, kNormThreads, 0, s>>>(
-      nullptr, static_cast<const __nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(w),
-      static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(res_out), nullptr, T, H, eps, w_offset, x_f32);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(rmsnorm_fwd_kernel, dim3(grid), dim3(kNormThreads), 0, s,
+                                        static_cast<const __nv_bfloat16*>(nullptr),
+                                        static_cast<const __nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(w),
+                                        static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(res_out),
+                                        static_cast<float*>(nullptr), T, H, eps, w_offset, x_f32));
 }
 
 // dw (fp32 [H]) is accumulated into; the caller zeroes it.
@@ -542,8 +545,8 @@ int apb_swiglu_f32in(float* acc, void* act, long long T, long long I, cudaStream
   const long long n = T * I / 4;
   if (n <= 0) return 0;
   const int grid = static_cast<int>(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);
-  swiglu_f32in_kernel<<<grid, 256, 0, s>>>(acc, static_cast<__nv_bfloat16*>(act), n);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(swiglu_f32in_kernel, dim3(grid), dim3(256), 0, s, acc,
+                                        static_cast<__nv_bfloat16*>(act), n));
 }
 int apb_swiglu_fwd(const void* gu, void* act, long long T, long long I, cudaStream_t s) {
   if (I % 8) return kBadArgument;

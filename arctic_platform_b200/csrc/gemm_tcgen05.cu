@@ -14,58 +14,12 @@
 // nn.Linear of the reference (arctic_platform/model/patches/liger.py:25-36
 // keeps them on cuBLAS).
 #include "common.cuh"
+#include "gemm_common.cuh"
 #include "host_utils.cuh"
 #include "peer.cuh"
+#include <stdlib.h>
 
 namespace apb {
-
-enum GemmEpilogue : int {
-  kEpiBf16 = 0,        // C(bf16) = alpha * acc (+ bias[n])
-  kEpiF32 = 1,         // C(f32)  = alpha * acc
-  kEpiF32Atomic = 2,   // C(f32) += alpha * acc  (red.add; split-K or shared accumulation)
-  kEpiF32Accum = 3,    // C(f32) += alpha * acc  (plain read-modify-write, one writer)
-  kEpiSwiGLU = 4,      // columns interleaved (gate, up): C2(bf16)[m, n/2] = silu(g) * u; C(bf16) = acc if C != null
-  kEpiLogprobPartial = 5,  // per row and 128-column tile: (max, sum exp, sum exp*z, label z) of z = acc*alpha*row_scale
-  kEpiDlogits = 6,         // C(bf16) = d loss / d acc for log-prob / entropy heads (see lm-head section below)
-  kEpiF32AtomicPeer = 7,   // GEMM -> reduce-scatter: red.add of the partial row into the fp32 buffer of the rank
-                           // that owns the row (owner = row / rows_per_rank), over its NVLink peer mapping
-  kEpiBf16ScatterPeer = 8, // GEMM -> all-to-all: bf16 row stored to (peer, row) = row_map[m] (MoE combine)
-};
-
-struct PeerTensorMaps {
-  CUtensorMap m[8];
-};
-
-struct GemmParams {
-  int M, N, K;
-  int a_mn, b_mn;
-  int epi;
-  int splits;
-  void* C;
-  long long ldc;
-  void* C2;
-  long long ldc2;
-  const __nv_bfloat16* bias;
-  float alpha;
-  // Optional tile table for grouped problems: {m0, m_end, b_row_offset, n_tile}.
-  const int4* tile_map;
-  int num_map_tiles;
-  int* status;
-  // log-prob epilogues
-  const float* row_scale;  // [M] per-row multiplier of the logits (inverse temperature) or null
-  const int* labels;       // [M]
-  float* partial;          // [M][tiles_n][4]
-  const float* row_lse;    // [M] log-sum-exp of the scaled logits
-  const float* row_ent;    // [M] entropy
-  const float* row_glp;    // [M] upstream gradient of the log-prob
-  const float* row_gent;   // [M] upstream gradient of the entropy, or null
-  // peer-aware modes
-  void* c_peers[8];        // per-rank output base pointers (symmetric buffers)
-  int rows_per_rank;       // kEpiF32AtomicPeer: rows owned by each rank
-  const int2* row_map;     // kEpiBf16ScatterPeer: (rank, destination row) per output row, rank < 0 = drop
-  int a_peer_rows;         // > 0: A is row-sharded over ranks, this many rows each, read through per-rank maps
-  int world;
-};
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
@@ -82,8 +36,6 @@ struct GemmCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
   static constexpr int kTmemCols = 2 * BN;
 };
-
-__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 
 template <int BN, int ST = 0>
 __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtensorMap& tma_b,
@@ -129,6 +81,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  pdl_launch_dependents();   // the next kernel of a chained launch may start its own set-up now
 
   // Tile decode shared by all roles.  Consecutive tile ids walk 8 m-tiles of
   // one n-band before moving on, so CTAs running at the same time share B in L2.
@@ -165,17 +118,39 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // Chained launch: the B tiles (weights) of the first ring-full of k-blocks are requested BEFORE waiting for
+      // the previous kernel, so the weight stream is already in flight when its output (A) becomes readable.
+      int prefetched = 0;
+      if (p.chained && blockIdx.x < total_tiles && !(a_peer_maps != nullptr && p.a_peer_rows > 0)) {
+        int m0, m_end, b_row, n0, kb0, kb1;
+        decode(blockIdx.x, m0, m_end, b_row, n0, kb0, kb1);
+        prefetched = min(Cfg::kStages, kb1 - kb0);
+        for (int i = 0; i < prefetched; ++i) {
+          uint8_t* sb = smem + i * Cfg::kStageBytes + Cfg::kABytes;
+          mbar_expect_tx(&full_bar[i], Cfg::kStageBytes);
+          if (!p.b_mn) {
+            tma_load_2d(sb, &tma_b, &full_bar[i], (kb0 + i) * kBK, b_row);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (64 * kBK * 2), &tma_b, &full_bar[i], b_row + c * 64, (kb0 + i) * kBK);
+          }
+        }
+      }
+      pdl_wait();
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int m0, m_end, b_row, n0, kb0, kb1;
         decode(t, m0, m_end, b_row, n0, kb0, kb1);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kTimeoutEmpty)) {
+          const bool b_done = prefetched > 0;      // this stage's barrier is armed and its B tile requested already
+          if (b_done) --prefetched;
+          if (!b_done && !mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kTimeoutEmpty)) {
             ok = false;
             break;
           }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kABytes;
-          mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          if (!b_done) mbar_expect_tx(&full_bar[stage], Cfg::kStageBytes);
           if (a_peer_maps != nullptr && p.a_peer_rows > 0) {
             // all-gather fused into the operand fetch: each slab of the A tile comes from the rank that owns
             // those rows, by a plain (non-multicast) TMA load from its peer mapping
@@ -193,7 +168,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
             for (int c = 0; c < kBM / 64; ++c)
               tma_load_2d(sa + c * (64 * kBK * 2), &tma_a, &full_bar[stage], m0 + c * 64, kb * kBK);
           }
-          if (!p.b_mn) {
+          if (b_done) {
+            // requested before the wait
+          } else if (!p.b_mn) {
             tma_load_2d(sb, &tma_b, &full_bar[stage], kb * kBK, b_row);
           } else {
 #pragma unroll
@@ -216,6 +193,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      pdl_wait();
       const uint32_t idesc = umma_idesc_bf16(kBM, BN, p.a_mn, p.b_mn);
       int stage = 0;
       uint32_t phase = 0;
@@ -262,6 +240,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
     const int quarter = warp & 3;  // TMEM lanes this warp may read
     int it = 0;
     bool ok = true;
+    pdl_wait();                    // the output buffer may still be read (or cleared) by the previous kernel
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
       int m0, m_end, b_row, n0, kb0, kb1;
       decode(t, m0, m_end, b_row, n0, kb0, kb1);
@@ -369,98 +348,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
         if (!row_ok) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        if (p.epi == kEpiBf16 || (p.epi == kEpiSwiGLU && p.C != nullptr)) {
-          if (p.bias) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
-          }
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (col0 + q * 8 < p.N) {
-              uint4 o;
-              o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-              o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-              o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-              o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-              *reinterpret_cast<uint4*>(dst + q * 8) = o;
-            }
-          }
-        }
-        if (p.epi == kEpiSwiGLU) {
-          __nv_bfloat16* dst =
-              static_cast<__nv_bfloat16*>(p.C2) + static_cast<long long>(row) * p.ldc2 + (col0 >> 1);
-#pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            if (col0 + q * 16 < p.N) {
-              float a[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) a[j] = silu_f(v[q * 16 + 2 * j]) * v[q * 16 + 2 * j + 1];
-              uint4 o;
-              o.x = pack_bf16x2(a[0], a[1]);
-              o.y = pack_bf16x2(a[2], a[3]);
-              o.z = pack_bf16x2(a[4], a[5]);
-              o.w = pack_bf16x2(a[6], a[7]);
-              *reinterpret_cast<uint4*>(dst + q * 8) = o;
-            }
-          }
-        } else if (p.epi == kEpiF32 || p.epi == kEpiF32Accum) {
-          float* dst = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            if (col0 + q * 4 < p.N) {
-              float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-              if (p.epi == kEpiF32Accum) {
-                const float4 old = *reinterpret_cast<const float4*>(dst + q * 4);
-                o.x += old.x;
-                o.y += old.y;
-                o.z += old.z;
-                o.w += old.w;
-              }
-              *reinterpret_cast<float4*>(dst + q * 4) = o;
-            }
-          }
-        } else if (p.epi == kEpiF32AtomicPeer) {
-          const int owner = min(row / p.rows_per_rank, p.world - 1);
-          float* dst = static_cast<float*>(p.c_peers[owner]) +
-                       static_cast<long long>(row - owner * p.rows_per_rank) * p.ldc + col0;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            if (col0 + q * 4 < p.N)
-              atomicAdd(reinterpret_cast<float4*>(dst + q * 4),
-                        make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
-          }
-        } else if (p.epi == kEpiBf16ScatterPeer) {
-          const int2 to = p.row_map[row];
-          if (to.x >= p.world || to.y < 0) {
-            atomicCAS(p.status, 0, kBadRouting);
-          } else if (to.x >= 0) {
-            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c_peers[to.x]) + static_cast<long long>(to.y) * p.ldc + col0;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (col0 + q * 8 < p.N) {
-                uint4 o;
-                o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
-                o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
-                o.z = pack_bf16x2(v[q * 8 + 4], v[q * 8 + 5]);
-                o.w = pack_bf16x2(v[q * 8 + 6], v[q * 8 + 7]);
-                *reinterpret_cast<uint4*>(dst + q * 8) = o;
-              }
-            }
-          }
-        } else if (p.epi == kEpiF32Atomic) {
-          float* dst = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            if (col0 + q * 4 < p.N)
-              atomicAdd(reinterpret_cast<float4*>(dst + q * 4),
-                        make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
-          }
-        }
+        gemm_store_chunk(p, row, col0, r);
       }
       tc_fence_before();
       __syncwarp();
@@ -507,15 +395,6 @@ gemm_bf16_ag_kernel(const __grid_constant__ PeerTensorMaps a_maps, const __grid_
 // ---------------------------------------------------------------------------
 namespace apb {
 
-static int sm_count() {
-  static int n[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return 148;
-  if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
-  return n[dev] > 0 ? n[dev] : 148;
-}
-
 template <int BN>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_ctas,
                        cudaStream_t stream) {
@@ -536,8 +415,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   int grid = static_cast<int>(total < sm_count() ? total : sm_count());
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
-  gemm_bf16_kernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(gemm_bf16_kernel<BN>, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream,
+                                        ta, tb, p));
 }
 
 template <int BN>
@@ -559,10 +438,25 @@ static int launch_gemm_x2(const CUtensorMap& ta, const CUtensorMap& tb, const Ge
   const int cap = 2 * sm_count();
   const int grid = static_cast<int>(total < cap ? total : cap);
   if (grid <= 0) return 0;
-  gemm_bf16_x2_kernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(launch_kernel(gemm_bf16_x2_kernel<BN>, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes,
+                                        stream, ta, tb, p));
 }
 
+}  // namespace apb
+
+extern "C" int apb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                  long long ldb, long long ldc, int a_mn, int b_mn, int epi, float alpha,
+                                  const void* bias, void* C2, long long ldc2, cudaStream_t stream);
+
+namespace apb {
+static bool pair_kernel_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("APB_GEMM_PAIR");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
 }  // namespace apb
 
 extern "C" {
@@ -595,6 +489,13 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   if (splits < 1) splits = 1;
   if (splits > k_blocks) splits = k_blocks;
   if (splits > 1 && epi != kEpiF32Atomic) return kBadArgument;
+  // Large plain problems go to the CTA-pair kernel (256 x 256 tiles, half of B per SM): at least one full wave
+  // of pairs, automatic tile choice, no grid cap.  APB_GEMM_PAIR=0 keeps everything on the one-CTA kernel.
+  if (bn == 0 && splits == 1 && !tile_map && max_ctas <= 0 && pair_kernel_enabled() &&
+      (epi == kEpiBf16 || epi == kEpiF32 || epi == kEpiF32Accum || epi == kEpiSwiGLU) &&
+      !(epi == kEpiBf16 && !C) &&
+      static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) >= sm_count() / 2)
+    return apb_gemm_bf16_pair(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, alpha, bias, C2, ldc2, stream);
   if (bn == 0) {
     const long long tm = (M + kBM - 1) / kBM;
     const long long t256 = tm * ((N + 255) / 256) * splits;
@@ -645,6 +546,7 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   p.labels = nullptr;
   p.partial = nullptr;
   p.row_lse = p.row_ent = p.row_glp = p.row_gent = nullptr;
+  p.chained = chained_launch_on() ? 1 : 0;
   if (x2) return bn == 64 ? launch_gemm_x2<64>(ta, tb, p, stream) : launch_gemm_x2<128>(ta, tb, p, stream);
   if (bn == 64) return launch_gemm<64>(ta, tb, p, max_ctas, stream);
   return bn == 256 ? launch_gemm<256>(ta, tb, p, max_ctas, stream) : launch_gemm<128>(ta, tb, p, max_ctas, stream);
@@ -730,6 +632,7 @@ int apb_lmhead_logprob_fwd(const void* hidden, const void* weight, const int* la
                            long long ldw, float scale, cudaStream_t stream) {
   using namespace apb;
   if (M <= 0) return 0;
+  if (!hidden || !weight || !labels || !partial || !lp || !ent || !lse) return kBadArgument;
   GemmParams p{};
   p.epi = kEpiLogprobPartial;
   p.alpha = scale;
@@ -787,10 +690,12 @@ extern "C" int apb_lmhead_logprob_fwd_noalloc(const void* hidden, const void* we
                                                cudaStream_t stream) {
   using namespace apb;
   if (M <= 0) return 0;
-  if (V <= 0 || H <= 0) return kBadArgument;
+  if (V <= 0 || H <= 0 || !hidden || !weight || !labels || !lp || !ent || !lse) return kBadArgument;
   const long long tiles = (static_cast<long long>(V) + 127) / 128;
   if (static_cast<long long>(M) * tiles > APB_NOALLOC_MAX_TILE_RECORDS) return APB_NOALLOC_TOO_LARGE;
   // One-time set-up per device (with that device current): resolve the device address of the scratch.
+  // The cache below is filled without a lock: two host threads that make the first call together both
+  // look the address up and store the same value, which is harmless.
   static float4* scratch_ptr[64] = {nullptr};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return APB_NOALLOC_SETUP_FAILED;

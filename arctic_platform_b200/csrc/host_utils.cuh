@@ -13,6 +13,31 @@ namespace apb {
 // status.cu; kernels receive its device address as a parameter.
 int* status_device_ptr();
 
+// Multiprocessor count of the current device (cached per device; 148 on a B200).
+int sm_count();
+
+// Chained-launch mode (see apb_set_chained_launch in status.cu): while it is on, kernels go out with the
+// programmatic-serialization attribute, so that each may start (set-up, weight prefetch) before the previous
+// one has finished; every such kernel calls pdl_wait() before it touches data of its predecessor.
+bool chained_launch_on();
+
+// Launch helper used instead of <<<>>> by the kernels that take part in chained launches.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained_launch_on() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,

@@ -285,8 +285,12 @@ static int grid_for(long long work_items) {
 int apb_zero_reduce(void* const* grad_ptrs, const float* mc_grads, void* const* flag_ptrs, int rank, int world,
                     int epoch, long long shard_off, long long n, float scale, float* reduced, double* sumsq,
                     cudaStream_t s) {
-  if (world > kMaxRanks || (n % 4) || (shard_off % 4)) return kBadArgument;
+  if (world < 1 || world > kMaxRanks || (n % 4) || (shard_off % 4)) return kBadArgument;
   if (n == 0 && world <= 1) return 0;
+  // an engine whose state was moved to the host hands out null (empty-tensor) addresses: refuse them here
+  if (!grad_ptrs || !reduced || !sumsq || (world > 1 && !flag_ptrs)) return kBadArgument;
+  for (int i = 0; i < world; ++i)
+    if (!grad_ptrs[i] || (world > 1 && !flag_ptrs[i])) return kBadArgument;
   zero_reduce_kernel<<<grid_for(n / 4), 256, 0, s>>>(to_peers(grad_ptrs, world), mc_grads, to_peers(flag_ptrs, world),
                                                      rank, world, epoch, shard_off, n, scale, reduced, sumsq,
                                                      status_device_ptr());
@@ -298,8 +302,11 @@ int apb_zero_adamw(void* const* param_ptrs, void* mc_params, void* const* flag_p
                    long long shard_off, long long n, const float* grad, float* master, float* m, float* v,
                    const double* total_sumsq, float lr, float beta1, float beta2, float eps, float weight_decay,
                    float bias1, float bias2, float max_grad_norm, cudaStream_t s) {
-  if (world > kMaxRanks || (n % 8) || (shard_off % 8)) return kBadArgument;
+  if (world < 1 || world > kMaxRanks || (n % 8) || (shard_off % 8)) return kBadArgument;
   if (n == 0 && world <= 1) return 0;
+  if (!param_ptrs || !grad || !master || !m || !v || !total_sumsq || (world > 1 && !flag_ptrs)) return kBadArgument;
+  for (int i = 0; i < world; ++i)
+    if (!param_ptrs[i] || (world > 1 && !flag_ptrs[i])) return kBadArgument;
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, bias1, bias2, max_grad_norm};
   zero_adamw_kernel<<<grid_for(n / 8), 256, 0, s>>>(to_peers(param_ptrs, world), mc_params,
                                                     to_peers(flag_ptrs, world), rank, world, epoch, shard_off, n, grad,

@@ -1,6 +1,7 @@
 // Kernel status word, tensor-map encoding through the driver entry point and
 // small exported utilities (status read/clear, L2 flush helper).
 #include "host_utils.cuh"
+#include <stdlib.h>
 
 namespace apb {
 
@@ -18,6 +19,18 @@ int* status_device_ptr() {
     ptrs[dev] = static_cast<int*>(p);
   }
   return ptrs[dev];
+}
+
+static int g_chained_launch = 0;
+bool chained_launch_on() { return g_chained_launch != 0; }
+
+int sm_count() {
+  static int n[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+  return n[dev] > 0 ? n[dev] : 148;
 }
 
 EncodeTiledFn encode_tiled_fn() {
@@ -125,5 +138,20 @@ int apb_bind_device(int dev) {
   return 0;
 }
 
-int apb_version() { return 1; }
+// Switches chained launches on or off for this process and returns the previous setting.  While on, the kernels
+// of this library that support it are launched with the programmatic-serialization attribute and the GEMM
+// prefetches its B operand before waiting for the previous kernel: only valid while B (the weights) is not
+// written by any kernel of the chain, i.e. during a decode step.  APB_PDL=0 in the environment keeps it off.
+int apb_set_chained_launch(int on) {
+  static int allowed = -1;
+  if (allowed < 0) {
+    const char* e = getenv("APB_PDL");
+    allowed = (e && e[0] == '0') ? 0 : 1;
+  }
+  const int prev = apb::g_chained_launch;
+  apb::g_chained_launch = (on && allowed) ? 1 : 0;
+  return prev;
+}
+
+int apb_version() { return 2; }
 }

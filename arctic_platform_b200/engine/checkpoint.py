@@ -14,7 +14,9 @@ The model-states file keeps the DeepSpeed keys (``module``, ``param_shapes``, ``
 stored under Hugging Face parameter names; the optimizer file keeps ``optimizer_state_dict`` with
 ``zero_stage``, ``partition_count``, ``base_optimizer_state`` (``exp_avg`` / ``exp_avg_sq`` / ``step``) and
 ``single_partition_of_fp32_groups``.  The flat partition follows THIS engine's unit layout (recorded under
-``b200_layout``), which is what makes a resume bit-exact; the HF export is the interchange format.
+``b200_layout`` and checked on load), which is what makes a resume bit-exact.  DeepSpeed itself could not resume
+from these optimizer files -- its flat groups follow the order of ``module.parameters()`` -- so between this
+engine and any other the interchange format is the ``hf/`` safetensors export, not the optimizer partition.
 """
 from __future__ import annotations
 
@@ -34,7 +36,14 @@ def _barrier(engine) -> None:
         dist.barrier(group=engine.group)
 
 
+def _layout_of(engine) -> Dict[str, Any]:
+    return {"total": engine.total, "units": [(u.name, u.offset, u.length) for u in engine.units],
+            "param_slices": {k: (o, n, tuple(s)) for k, (o, n, s) in engine.param_slices.items()}}
+
+
 def save_checkpoint(engine, save_dir: str, tag: Optional[str] = None, export_hf: bool = False) -> Dict[str, Any]:
+    if hasattr(engine, "require_awake"):
+        engine.require_awake("save_checkpoint")      # a sleeping engine's optimizer tensors are empty placeholders
     tag = tag or f"global_step{engine.global_steps}"
     root = Path(save_dir)
     d = root / tag
@@ -66,8 +75,7 @@ def save_checkpoint(engine, save_dir: str, tag: Optional[str] = None, export_hf:
                           "gradient_accumulation_steps": engine.cfg.gradient_accumulation_steps,
                           "gradient_clipping": engine.cfg.max_grad_norm},
             "ds_version": DS_VERSION,
-            "b200_layout": {"total": engine.total, "units": [(u.name, u.offset, u.length) for u in engine.units],
-                            "param_slices": {k: (o, n, tuple(s)) for k, (o, n, s) in engine.param_slices.items()}},
+            "b200_layout": _layout_of(engine),
         }
         f = d / "mp_rank_00_model_states.pt"
         torch.save(state, f)
@@ -100,19 +108,41 @@ def save_checkpoint(engine, save_dir: str, tag: Optional[str] = None, export_hf:
             tensors = module.items() if collective_export else None   # gathered above
             files += [str(root / "hf" / x) for x in save_hf_checkpoint(engine.model, root / "hf", tensors=tensors)]
     _barrier(engine)
-    return {"path": str(d), "tag": tag, "files": files}
+    return {"path": str(d), "tag": tag, "files": files, "global_step": engine.global_steps,
+            "hf_path": str(root / "hf") if export_hf else None}
 
 
-def load_checkpoint(engine, load_dir: str, tag: Optional[str] = None) -> int:
-    """Restores module weights, optimizer partition and step counters; returns ``global_steps`` (0 when the
-    directory has no checkpoint)."""
+def _locate(load_dir: str, tag: Optional[str]) -> Optional[Path]:
+    """The directory that holds ``mp_rank_00_model_states.pt``: ``load_dir/<tag>``, the tag named by
+    ``load_dir/latest``, or ``load_dir`` itself when it is a tag directory."""
     root = Path(load_dir)
-    if tag is None:
-        latest = root / "latest"
-        if not latest.exists():
-            return 0
-        tag = latest.read_text().strip()
-    d = root / tag
+    if tag is not None:
+        return root / tag
+    if (root / "mp_rank_00_model_states.pt").is_file():
+        return root
+    latest = root / "latest"
+    if latest.is_file():
+        name = latest.read_text().strip()
+        for cand in (root / name, root / f"global_step{name}", root / f"checkpoint-{name}"):
+            if (cand / "mp_rank_00_model_states.pt").is_file():
+                return cand
+            if (cand / "latest").is_file():                      # a job root: descend into its newest checkpoint
+                return _locate(str(cand), None)
+        return root / name
+    return None
+
+
+def load_checkpoint(engine, load_dir: str, tag: Optional[str] = None, strict: bool = False) -> int:
+    """Restores module weights, optimizer partition, learning-rate schedule and step counters; returns
+    ``global_steps``.  A directory without any checkpoint returns 0 (a fresh start) unless ``strict`` is set or a
+    tag was named, in which case it raises ``FileNotFoundError``."""
+    if hasattr(engine, "require_awake"):
+        engine.require_awake("load_checkpoint")
+    d = _locate(load_dir, tag)
+    if d is None:
+        if strict:
+            raise FileNotFoundError(f"no checkpoint under {load_dir} (no 'latest' file and no model-states file)")
+        return 0
     ms = d / "mp_rank_00_model_states.pt"
     if not ms.exists():
         raise FileNotFoundError(f"{ms} not found")
@@ -120,6 +150,13 @@ def load_checkpoint(engine, load_dir: str, tag: Optional[str] = None) -> int:
     if state.get("dp_world_size", 1) != engine.world and not engine.forward_only:
         raise ValueError(f"checkpoint was written with {state.get('dp_world_size')} data-parallel ranks, this job has "
                          f"{engine.world}; use the hf/ export to change the world size")
+    saved_layout = state.get("b200_layout")
+    if saved_layout is not None and not engine.forward_only:
+        mine = _layout_of(engine)
+        if int(saved_layout.get("total", -1)) != mine["total"] or \
+                [tuple(u) for u in saved_layout.get("units", [])] != [tuple(u) for u in mine["units"]]:
+            raise ValueError("the checkpoint's optimizer partition was written for a different parameter layout "
+                             f"({saved_layout.get('total')} vs {mine['total']} flat elements); load the hf/ export instead")
     from ..models.hf_io import load_hf_tensor
     if getattr(engine, "zero3", None) is not None:
         # stage 3: load into a temporary full buffer, then cut this rank's shard out of it
@@ -151,8 +188,20 @@ def load_checkpoint(engine, load_dir: str, tag: Optional[str] = None) -> int:
         f = d / f"bf16_zero_pp_rank_{engine.rank}_mp_rank_00_optim_states.pt"
         osd = torch.load(f, map_location="cpu", weights_only=False)["optimizer_state_dict"]
         base = osd["base_optimizer_state"]["state"][0]
-        engine.master.copy_(osd["single_partition_of_fp32_groups"][0])
+        part = osd["single_partition_of_fp32_groups"][0]
+        if part.numel() != engine.master.numel():
+            raise ValueError(f"optimizer partition of {part.numel()} elements does not fit this rank's "
+                             f"{engine.master.numel()} (different world size or ZeRO stage)")
+        engine.master.copy_(part)
         engine.exp_avg.copy_(base["exp_avg"])
         engine.exp_avg_sq.copy_(base["exp_avg_sq"])
+        groups = osd["base_optimizer_state"].get("param_groups") or []
+        if groups and "lr" in groups[0]:
+            engine.cfg.lr = float(groups[0]["lr"])
+        sched = state.get("lr_scheduler") or {}
+        if sched.get("type"):
+            from .trainer import SchedulerConfig
+            engine.cfg.scheduler = SchedulerConfig(str(sched["type"]), int(sched.get("warmup_steps", 0)),
+                                                   int(sched.get("total_steps", 0)), float(sched.get("min_lr_ratio", 0.0)))
     _barrier(engine)
     return engine.global_steps

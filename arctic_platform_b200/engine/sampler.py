@@ -34,6 +34,7 @@ from ..models.config import DecoderConfig
 from ..models.decoder import DecoderLM
 from ..ops import _lib, gemm, norm
 from ..ops.attention import AttnLayout, attention_fwd_cuda
+from ..utils.transfer_stats import to_device, to_host
 
 PAGE = 16
 MAX_NQ = 16
@@ -145,6 +146,9 @@ def _fn(name: str):
         _FN["qkv_post"] = _lib.declare("apb_decode_qkv_post", [vp, ll, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, f, vp])
         _FN["swiglu32"] = _lib.declare("apb_swiglu_f32in", [vp, vp, ll, ll, vp])
         _FN["norm32"] = _lib.declare("apb_rmsnorm_fwd_f32in", [vp, vp, vp, vp, vp, i, i, f, f, vp])
+        _FN["begin"] = _lib.declare("apb_decode_begin", [vp, vp, vp, vp, i, vp, ll, i, i, vp, vp, i, vp])
+        _FN["advance"] = _lib.declare("apb_decode_advance", [vp] * 13 + [i, vp, i, vp])
+        _FN["chain"] = _lib.declare("apb_set_chained_launch", [i])
     return _FN[name]
 
 
@@ -236,6 +240,8 @@ class SamplerEngine:
         self.acc_gu = torch.zeros((B, 2 * c.intermediate_size), **f32) if not c.is_moe else None
         self.d_new_tok = torch.zeros(B, **i32)
         self.d_new_lp = torch.zeros(B, **f32)
+        self.d_slots = torch.full((B,), -1, **i32)                              # cache slot of the token being fed
+        self.d_x = torch.empty((B, c.hidden_size), device=dev, dtype=torch.bfloat16)   # its embedding row
 
     def kv_bytes(self) -> int:
         return 2 * self.kcache.numel() * 2
@@ -305,12 +311,12 @@ class SamplerEngine:
         lens = np.array([len(p) for p in prompts], dtype=np.int64)
         cu = np.concatenate([[0], np.cumsum(lens)])
         T = int(cu[-1])
-        ids = torch.from_numpy(np.concatenate(prompts).astype(np.int64)).to(self.device)
+        ids = to_device(torch.from_numpy(np.concatenate(prompts).astype(np.int64)), self.device)
         pos_np = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
         slots_np = np.concatenate([pl[np.arange(n) // PAGE] * PAGE + np.arange(n) % PAGE
                                    for n, pl in zip(lens, page_lists)]).astype(np.int32)
-        positions = torch.from_numpy(pos_np).to(self.device)
-        slots = torch.from_numpy(slots_np).to(self.device)
+        positions = to_device(torch.from_numpy(pos_np), self.device)
+        slots = to_device(torch.from_numpy(slots_np), self.device)
         layout = AttnLayout.from_cu_seqlens(cu)
         scale = 1.0 / math.sqrt(self.cfg.head_dim)
 
@@ -323,7 +329,7 @@ class SamplerEngine:
         stream = None
         for li in range(self.cfg.num_layers):
             x, stream = self._block(li, x, stream, positions, slots, attn)
-        last = torch.from_numpy((cu[1:] - 1).astype(np.int64)).to(self.device)
+        last = to_device(torch.from_numpy((cu[1:] - 1).astype(np.int64)), self.device)
         xl = x.index_select(0, last)
         sl = stream.index_select(0, last)
         h, _ = norm.rmsnorm(xl, self.model.final_norm, self.cfg.rms_norm_eps, sl)
@@ -387,48 +393,47 @@ class SamplerEngine:
         """One token for slots [0, B).  Reads and updates device state only, so the whole step can be
         captured in a CUDA graph and replayed."""
         c = self.cfg
-        act = self.d_active[:B] > 0
-        positions = self.d_pos[:B]
-        pidx = torch.div(positions, PAGE, rounding_mode="floor").long()
-        page = self.d_page_table[:B].gather(1, pidx[:, None]).squeeze(1)
-        slots = torch.where(act, page * PAGE + positions % PAGE, torch.full_like(page, -1)).int()
-        x = torch.nn.functional.embedding(self.d_tokens[:B].long(), self.model.embed)
-        stream = None
-        attn = lambda li, q, k, v: self._decode_attention(li, q, B)
-        if self.split_k and not c.is_moe and not self.fp8:
-            h = self._decode_layers_splitk(x, positions, slots, B)
-        else:
-            for li in range(c.num_layers):
-                x, stream = self._block(li, x, stream, positions, slots, attn)
-            h, _ = norm.rmsnorm(x, self.model.final_norm, c.rms_norm_eps, stream)
-        logits = self.d_logits[:B]
-        gemm.matmul_nt(h, self.model.output_weight, out=logits)
-        if self._filter_on:
-            _lib.check(_fn("sample_f")(_lib.ptr(logits), logits.stride(0), _lib.ptr(self.d_temp), B, c.vocab_size,
-                                       ctypes.c_uint(self.seed & 0xFFFFFFFF), _lib.ptr(self.d_step),
-                                       _lib.ptr(self.d_topk), _lib.ptr(self.d_topp), _lib.ptr(self.d_thr),
-                                       _lib.ptr(self.d_new_tok), _lib.ptr(self.d_new_lp), _lib.stream_ptr()),
-                       "sample_filtered")
-        else:
-            _lib.check(_fn("sample")(_lib.ptr(logits), logits.stride(0), _lib.ptr(self.d_temp), B, c.vocab_size,
-                                     ctypes.c_uint(self.seed & 0xFFFFFFFF), _lib.ptr(self.d_step),
-                                     _lib.ptr(self.d_new_tok), _lib.ptr(self.d_new_lp), _lib.stream_ptr()), "sample")
-        new_tok, new_lp = self.d_new_tok[:B], self.d_new_lp[:B]
-        idx = self.d_out_idx[:B].clamp(max=self.out_cap - 1)
-        self.d_out_tokens[:B].scatter_(1, idx, torch.where(act, new_tok, self.d_out_tokens[:B].gather(1, idx).squeeze(1))[:, None])
-        self.d_out_lps[:B].scatter_(1, idx, torch.where(act, new_lp, self.d_out_lps[:B].gather(1, idx).squeeze(1))[:, None])
-        self.d_out_idx[:B] += act.long()[:, None]
-        newlen = self.d_len[:B] + act.int()
-        stop = (new_tok[:, None] == self.d_stop[None, :]).any(1)
-        done = act & (stop | (newlen >= self.d_max_len[:B]))
-        self.d_finished[:B] |= done.int()
-        still = act & ~done
-        self.d_active[:B] = still.int()
-        self.d_tokens[:B] = torch.where(still, new_tok, self.d_tokens[:B])
-        self.d_pos[:B] += still.int()
-        self.d_len[:B] = torch.where(still, newlen, self.d_len[:B])
-        self.d_priv_len[:B] += still.int()
-        self.d_step += 1
+        # chained launches: every kernel of the step may start (set-up, weight prefetch) while its predecessor is
+        # still running; valid here because no kernel of a decode step writes the weights
+        prev_chain = _fn("chain")(1)
+        try:
+            positions = self.d_pos[:B]
+            slots = self.d_slots[:B]
+            x = self.d_x[:B]
+            # one kernel: cache slot of the fed token (page-table look-up) + its embedding row
+            _lib.check(_fn("begin")(_lib.ptr(self.d_tokens), _lib.ptr(self.d_pos), _lib.ptr(self.d_active),
+                                    _lib.ptr(self.d_page_table), self.max_pages, _lib.ptr(self.model.embed),
+                                    self.model.embed.stride(0), c.hidden_size, c.vocab_size, _lib.ptr(slots), _lib.ptr(x), B,
+                                    _lib.stream_ptr()), "decode_begin")
+            stream = None
+            attn = lambda li, q, k, v: self._decode_attention(li, q, B)
+            if self.split_k and not c.is_moe and not self.fp8:
+                h = self._decode_layers_splitk(x, positions, slots, B)
+            else:
+                for li in range(c.num_layers):
+                    x, stream = self._block(li, x, stream, positions, slots, attn)
+                h, _ = norm.rmsnorm(x, self.model.final_norm, c.rms_norm_eps, stream)
+            logits = self.d_logits[:B]
+            gemm.matmul_nt(h, self.model.output_weight, out=logits)
+            if self._filter_on:
+                _lib.check(_fn("sample_f")(_lib.ptr(logits), logits.stride(0), _lib.ptr(self.d_temp), B, c.vocab_size,
+                                           ctypes.c_uint(self.seed & 0xFFFFFFFF), _lib.ptr(self.d_step),
+                                           _lib.ptr(self.d_topk), _lib.ptr(self.d_topp), _lib.ptr(self.d_thr),
+                                           _lib.ptr(self.d_new_tok), _lib.ptr(self.d_new_lp), _lib.stream_ptr()),
+                           "sample_filtered")
+            else:
+                _lib.check(_fn("sample")(_lib.ptr(logits), logits.stride(0), _lib.ptr(self.d_temp), B, c.vocab_size,
+                                         ctypes.c_uint(self.seed & 0xFFFFFFFF), _lib.ptr(self.d_step),
+                                         _lib.ptr(self.d_new_tok), _lib.ptr(self.d_new_lp), _lib.stream_ptr()), "sample")
+            # one kernel: store token + log-prob, stop / length decisions, advance positions and lengths, step counter
+            _lib.check(_fn("advance")(_lib.ptr(self.d_new_tok), _lib.ptr(self.d_new_lp), _lib.ptr(self.d_active),
+                                      _lib.ptr(self.d_finished), _lib.ptr(self.d_tokens), _lib.ptr(self.d_pos),
+                                      _lib.ptr(self.d_len), _lib.ptr(self.d_priv_len), _lib.ptr(self.d_max_len),
+                                      _lib.ptr(self.d_stop), _lib.ptr(self.d_out_idx), _lib.ptr(self.d_out_tokens),
+                                      _lib.ptr(self.d_out_lps), self.out_cap, _lib.ptr(self.d_step), B,
+                                      _lib.stream_ptr()), "decode_advance")
+        finally:
+            _fn("chain")(prev_chain)
 
     def _norm_f32(self, acc: torch.Tensor, w: torch.Tensor, res: torch.Tensor):
         """RMSNorm whose input is an fp32 split-K accumulator (reset to zero as it is read)."""
@@ -614,12 +619,12 @@ class SamplerEngine:
                 self._set_groups(group_members, live)
                 self._run_steps(bucket, self.sync_interval)
             # ---- harvest
-            fin = self.d_finished[:max(B, 1)].cpu().numpy() if B else np.zeros(0, dtype=np.int32)
+            fin = to_host(self.d_finished[:max(B, 1)]).numpy() if B else np.zeros(0, dtype=np.int32)
             done_slots = [s for s in list(live) if fin[s]]
             if done_slots:
-                nout = self.d_out_idx[:B, 0].cpu().numpy()
-                toks = self.d_out_tokens[:B].cpu().numpy()
-                lps = self.d_out_lps[:B].cpu().numpy()
+                nout = to_host(self.d_out_idx[:B, 0]).numpy()
+                toks = to_host(self.d_out_tokens[:B]).numpy()
+                lps = to_host(self.d_out_lps[:B]).numpy()
                 for s in done_slots:
                     sq = live.pop(s)
                     k = int(nout[s])
@@ -725,10 +730,10 @@ class SamplerEngine:
                 pv[i, :len(sq.private_pages)] = sq.private_pages
                 sh[i] = len(sq.shared_pages) * PAGE
                 plen[i] = sq.prompt_len - sh[i] + 1
-            self.d_page_table[st] = torch.from_numpy(pt).to(self.device)
-            self.d_priv_table[st] = torch.from_numpy(pv).to(self.device)
-            self.d_priv_len[st] = torch.from_numpy(plen).to(self.device)
-            self.d_shared_tokens[st] = torch.from_numpy(sh).to(self.device)
+            self.d_page_table[st] = to_device(torch.from_numpy(pt), self.device)
+            self.d_priv_table[st] = to_device(torch.from_numpy(pv), self.device)
+            self.d_priv_len[st] = to_device(torch.from_numpy(plen), self.device)
+            self.d_shared_tokens[st] = to_device(torch.from_numpy(sh), self.device)
 
     def _set_groups(self, group_members: Dict[int, List[int]], live: Dict[int, _Seq]) -> None:
         """Prefix-forest tables for cascade decode: runs of consecutive slots (at most 16) that share

@@ -59,6 +59,10 @@ class EngineConfig:
     moe_bias_update_rate: float = 1e-3  # step of the routers' load-balancing bias (models that have one)
     adam_w_mode: bool = True           # False: classic Adam, weight decay added to the gradient (L2) instead of decoupled
     gradient_checkpointing: bool = False
+    # stage 3: how many gathered (full) parameter elements may stay live between uses.  -1 = automatic (all decoder
+    # blocks stay gathered from one optimizer step to the next when they take at most a tenth of the device memory,
+    # otherwise two alternating slots); DeepSpeed's ``zero_optimization.stage3_max_live_parameters`` sets it.
+    zero3_max_live_parameters: int = -1
 
     @staticmethod
     def from_ds_config(ds_config: Optional[dict], training_config: Optional[dict] = None) -> "EngineConfig":
@@ -103,6 +107,8 @@ class EngineConfig:
         zero = ds.get("zero_optimization", {}) or {}
         cfg.zero_stage = int(zero.get("stage", 1))
         cfg.offload_optimizer = (zero.get("offload_optimizer") or {}).get("device", "none") == "cpu"
+        if zero.get("stage3_max_live_parameters") is not None:
+            cfg.zero3_max_live_parameters = int(float(zero["stage3_max_live_parameters"]))
         cfg.impl = ds.get("b200_impl", "fused")
         if (zero.get("offload_param") or {}).get("device", "none") not in ("none", None):
             import logging
@@ -183,6 +189,8 @@ class TrainEngine:
         self.micro_steps = 0
         self.last_grad_norm = 0.0
         model.gradient_checkpointing = cfg.gradient_checkpointing
+        # sleep state: names of the states whose device copies were released by offload_states() (empty = awake)
+        self._offloaded: Dict[str, Optional[torch.Tensor]] = {}
         # stage 3: bf16 parameters exist only as per-rank shards and are gathered unit by unit (engine/zero3.py)
         self.zero3 = None
         self._zero3_wanted = cfg.zero_stage >= 3 and self.world > 1
@@ -245,7 +253,6 @@ class TrainEngine:
         # W == 1: the reduced gradient is the gradient buffer itself (in place)
         self.reduced = gflat if W == 1 else torch.empty(self.shard_total, dtype=torch.float32, device=self.device)
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
-        self._offloaded: Dict[str, torch.Tensor] = {}
 
     def _build_zero3(self) -> None:
         from .zero3 import Zero3State
@@ -271,7 +278,6 @@ class TrainEngine:
         self._build_host_staging()
         self.reduced = torch.empty(self.shard_total, dtype=torch.float32, device=self.device)
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
-        self._offloaded = {}
 
     # ------------------------------------------------------------------ optimizer state on the host
     @property
@@ -350,7 +356,21 @@ class TrainEngine:
     def gradient_accumulation_steps(self) -> int:
         return self.cfg.gradient_accumulation_steps
 
+    @property
+    def asleep(self) -> bool:
+        """True between ``offload_states`` and ``reload_states`` (the reference tracks the same thing as
+        ``_on_gpu``, arctic_platform/common/deepspeed_worker.py:1028,1060)."""
+        return bool(self._offloaded)
+
+    def require_awake(self, what: str) -> None:
+        """The optimizer state of a sleeping engine lives on the host and its device tensors are empty; anything that
+        would read or write them is refused here instead of reaching a kernel with null addresses."""
+        if self._offloaded:
+            raise RuntimeError(f"training engine is asleep ({', '.join(sorted(self._offloaded))} offloaded); "
+                               f"call wake before {what}")
+
     def backward(self, loss: torch.Tensor) -> None:
+        self.require_awake("backward")
         loss.backward()
         self.collect_autograd_grads()
         self.micro_steps += 1
@@ -368,6 +388,7 @@ class TrainEngine:
 
     # ------------------------------------------------------------------ optimizer step
     def step(self) -> Dict[str, float]:
+        self.require_awake("step")
         cfg = self.cfg
         lr = lr_at(cfg, self.global_steps)
         t = self.global_steps + 1
@@ -658,34 +679,42 @@ class TrainEngine:
 
     # ------------------------------------------------------------------ sleep / wake
     def offload_states(self, include: Iterable[str] = ("optimizer", "grads", "params")) -> None:
-        """Moves the selected state to pinned host memory and frees the device copies.  ``params`` can
-        only be offloaded when they are not in symmetric memory (their addresses are registered with peers)."""
-        if not self.on_cuda:
+        """Moves the selected state to pinned host memory and frees the device copies.  Idempotent: a state that is
+        already on the host is left alone (a second call with a wider ``include`` only adds what is still on the
+        device).  ``params`` can only be offloaded when they are not in symmetric memory (their addresses are
+        registered with peers), so they stay."""
+        if self.forward_only:
             return
+        moved = []
         for key in include:
-            if key == "optimizer" and not self.forward_only:
+            if key == "optimizer" and not self.opt_on_host:
                 for nm in ("master", "exp_avg", "exp_avg_sq"):
+                    if nm in self._offloaded:
+                        continue                      # already asleep: the device tensor is an empty placeholder
                     t = getattr(self, nm)
-                    if t.is_cuda:
-                        host = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
-                        host.copy_(t, non_blocking=True)
-                        self._offloaded[nm] = host
-            elif key == "grads" and not self.forward_only and self.world == 1:
-                self._offloaded["grads"] = None
-        torch.cuda.synchronize(self.device)
-        for nm in list(self._offloaded):
-            if nm in ("master", "exp_avg", "exp_avg_sq"):
-                setattr(self, nm, torch.empty(0, device=self.device))
-        torch.cuda.empty_cache()
+                    host = torch.empty(t.shape, dtype=t.dtype, pin_memory=self.on_cuda)
+                    host.copy_(t, non_blocking=True)
+                    self._offloaded[nm] = host
+                    moved.append(nm)
+            elif key == "grads" and self.world == 1 and "grads" not in self._offloaded:
+                self._offloaded["grads"] = None       # marker only: the gradient buffer stays (zero between steps)
+        if self.on_cuda:
+            torch.cuda.synchronize(self.device)
+        for nm in moved:
+            setattr(self, nm, torch.empty(0, device=self.device))
+        if moved and self.on_cuda:
+            torch.cuda.empty_cache()
 
     def reload_states(self) -> None:
-        if not self.on_cuda:
+        """Brings back whatever ``offload_states`` moved; a no-op on an engine that is awake."""
+        if not self._offloaded:
             return
         for nm, host in list(self._offloaded.items()):
             if host is not None:
-                setattr(self, nm, host.to(self.device, non_blocking=True))
+                setattr(self, nm, host.to(self.device, non_blocking=True) if self.on_cuda else host.clone())
+        if self.on_cuda:
+            torch.cuda.synchronize(self.device)
         self._offloaded.clear()
-        torch.cuda.synchronize(self.device)
 
 
 def _gloo_all_gather(dst: torch.Tensor, shard: torch.Tensor, world: int, group) -> None:

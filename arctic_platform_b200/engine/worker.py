@@ -386,7 +386,10 @@ class EngineWorker:
         import torch.distributed as dist
         meta = dict(meta or {})
         t = torch.tensor([float(sum(int(mb["response_mask"].sum()) for mb in mbs)),
-                          float(sum(mb["input_ids"].shape[0] for mb in mbs))], dtype=torch.float64)
+                          # loss-free filler micro-batches (appended so that all ranks run the same number of
+                          # passes) are not sequences of the batch: the seq-mean modes divide by real rows only
+                          float(sum(mb["input_ids"].shape[0] for mb in mbs if not mb.get("_dummy")))],
+                         dtype=torch.float64)
         group = getattr(self.engine, "group", None)
         if dist.is_initialized() and self.engine.world > 1:
             t = t.to(self.device if dist.get_backend(group) == "nccl" else "cpu")
@@ -714,6 +717,6 @@ class EngineWorker:
         from .checkpoint import save_checkpoint
         return save_checkpoint(self.engine, path, tag, export_hf=export_hf)
 
-    def load_checkpoint(self, path: str, tag: Optional[str] = None) -> int:
+    def load_checkpoint(self, path: str, tag: Optional[str] = None, strict: bool = False) -> int:
         from .checkpoint import load_checkpoint
-        return load_checkpoint(self.engine, path, tag)
+        return load_checkpoint(self.engine, path, tag, strict=strict)

@@ -6,11 +6,14 @@ peers can read it.  The fp32 master weights and Adam moments have the same per-r
 kernel updates master, moments and the bf16 shard in one pass without any all-gather.
 
 Materialisation.  A unit (one decoder block) is rebuilt just in time by ``gather_shards_kernel``: every rank PULLS the
-peers' pieces over NVLink with plain loads into one of two alternating gather slots; a side stream prefetches the next
-unit (forward: i+1, backward: i-1) while the current one computes, and module pre-hooks (forward and backward) wait
-for the slot.  Parameters of unit ``i`` are permanent views into slot ``i % 2``, so tensors autograd saved in the
-forward point at the right bytes again once the backward hook has re-gathered the unit.  The embedding / lm-head
-and the final norm stay gathered (they are touched at both ends of every pass).
+peers' pieces over NVLink with plain loads into a gather slot; a side stream prefetches the next unit (forward: i+1,
+backward: i-1) while the current one computes, and module pre-hooks (forward and backward) wait for the slot.
+Parameters of unit ``i`` are permanent views into slot ``i % n_slots``, so tensors autograd saved in the forward point
+at the right bytes again once the backward hook has re-gathered the unit.  ``n_slots`` is 2 (every use re-gathers)
+unless the gathered blocks may stay live (``stage3_max_live_parameters``; automatic when they take at most a tenth
+of the device memory): then every block has a slot of its own and is gathered ONCE per optimizer step instead of
+once per micro-batch pass -- with 16 micro-batches per step that removes 31 of 32 gathers per block.  The embedding /
+lm-head and the final norm stay gathered (they are touched at both ends of every pass).
 
 Gradients stay full-size in fp32 (accumulated locally over micro-batches); at the step every piece is reduced from
 all ranks by ``zero_reduce_kernel`` straight into the owner's shard layout (reduce-scatter by P2P loads).
@@ -77,16 +80,18 @@ class Zero3State:
                     self.shard_buf.tensor[base + so:base + so + pl].copy_(pmap[name].data.reshape(-1)[r * pl:(r + 1) * pl])
         # ---- gather slots: blocks alternate between two, everything else stays resident
         self.is_block = [u.name.startswith("block") and not u.local_only for u in engine.units]
-        max_block = max([u.length for u, b in zip(engine.units, self.is_block) if b] or [8])
-        self.slots = [torch.empty(max_block, dtype=dt, device=dev) for _ in range(2)]
-        self.slot_content = [-1, -1]
+        block_lens = [u.length for u, b in zip(engine.units, self.is_block) if b]
+        max_block = max(block_lens or [8])
+        self.n_slots = self._choose_slot_count(block_lens, max_block, dt)
+        self.slots = [torch.empty(max_block, dtype=dt, device=dev) for _ in range(self.n_slots)]
+        self.slot_content = [-1] * self.n_slots
         self.resident: Dict[int, torch.Tensor] = {}
         self.block_rank: Dict[int, int] = {}
         k = 0
         for ui, u in enumerate(engine.units):
             if self.is_block[ui]:
                 self.block_rank[ui] = k
-                buf = self.slots[k % 2]
+                buf = self.slots[k % self.n_slots]
                 k += 1
             else:
                 buf = torch.zeros(u.length, dtype=dt, device=dev)
@@ -98,12 +103,28 @@ class Zero3State:
                     view.copy_(p.data)           # nothing to gather later: the rank's own values live here
                 p.data = view
         self.side = torch.cuda.Stream(device=dev) if engine.on_cuda else None
-        self.ready: List[Optional[torch.cuda.Event]] = [None, None]
+        self.ready: List[Optional[torch.cuda.Event]] = [None] * self.n_slots
         self.gathers = 0
         self.gather_ctas = int(os.environ.get("APB_ZERO3_GATHER_CTAS", "128"))   # SMs lent to a prefetch
         for ui in self.resident:
             self._gather(ui, self.resident[ui])
         self._install_hooks()
+
+    def _choose_slot_count(self, block_lens: List[int], max_block: int, dt: torch.dtype) -> int:
+        """Two alternating slots, or one per block when the gathered blocks may stay live between uses."""
+        n = len(block_lens)
+        if n <= 2:
+            return 2
+        limit = int(getattr(self.e.cfg, "zero3_max_live_parameters", -1))
+        if os.environ.get("APB_ZERO3_LIVE_PARAMETERS"):
+            limit = int(float(os.environ["APB_ZERO3_LIVE_PARAMETERS"]))
+        need = n * max_block
+        if limit >= 0:
+            return n if need <= limit else 2
+        if not self.e.on_cuda:
+            return 2
+        total = torch.cuda.get_device_properties(self.e.device).total_memory
+        return n if need * torch.empty(0, dtype=dt).element_size() * 10 <= total else 2
 
     # ------------------------------------------------------------------ gather
     def _gather(self, ui: int, buf: torch.Tensor) -> None:
@@ -148,7 +169,7 @@ class Zero3State:
         """Unit ``ui`` is in its slot when this returns (on the current stream)."""
         if not self.is_block[ui]:
             return
-        k = self.block_rank[ui] % 2
+        k = self.block_rank[ui] % self.n_slots
         if self.slot_content[k] == ui:
             if self.ready[k] is not None:
                 torch.cuda.current_stream(self.e.device).wait_event(self.ready[k])
@@ -165,7 +186,7 @@ class Zero3State:
         main stream (the unit two positions away), so the side stream first waits for the main stream."""
         if ui < 0 or ui >= len(self.e.units) or not self.is_block[ui]:
             return
-        k = self.block_rank[ui] % 2
+        k = self.block_rank[ui] % self.n_slots
         if self.slot_content[k] == ui:
             return
         if self.side is None or not self.fused:
@@ -181,8 +202,8 @@ class Zero3State:
 
     def invalidate(self) -> None:
         """After an optimizer step the shards changed: slots are stale, resident units are gathered again."""
-        self.slot_content = [-1, -1]
-        self.ready = [None, None]
+        self.slot_content = [-1] * self.n_slots
+        self.ready = [None] * self.n_slots
         for ui, buf in self.resident.items():
             self._gather(ui, buf)
 

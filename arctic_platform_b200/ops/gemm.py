@@ -82,7 +82,7 @@ def matmul_nt(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] 
 
 
 def matmul_nn(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None,
-              out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+              out_dtype: torch.dtype = torch.bfloat16, bn: int = 0) -> torch.Tensor:
     """``a[M,K] @ b[K,N]`` with b row-major (the data gradient dX = dY @ W)."""
     if not a.is_cuda:
         r = a.float() @ b.float()
@@ -96,12 +96,12 @@ def matmul_nn(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] =
     if out is None:
         out = torch.empty((M, N), device=a.device, dtype=out_dtype)
     epi = EPI_BF16 if out.dtype == torch.bfloat16 else EPI_F32
-    gemm_raw(a, b, out, M=M, N=N, K=K, b_mn=True, epi=epi)
+    gemm_raw(a, b, out, M=M, N=N, K=K, b_mn=True, epi=epi, bn=bn)
     return out
 
 
 def matmul_tn(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] = None,
-              out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False) -> torch.Tensor:
+              out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, bn: int = 0) -> torch.Tensor:
     """``a[K,M]^T @ b[K,N]`` (the weight gradient dW = dY^T @ X), optionally accumulated into fp32 ``out``."""
     if not a.is_cuda:
         r = a.float().t() @ b.float()
@@ -127,7 +127,7 @@ def matmul_tn(a: torch.Tensor, b: torch.Tensor, *, out: Optional[torch.Tensor] =
         epi = EPI_BF16
     else:
         epi = EPI_F32_ACCUM if accumulate else EPI_F32
-    gemm_raw(a, b, out, M=M, N=N, K=K, a_mn=True, b_mn=True, epi=epi)
+    gemm_raw(a, b, out, M=M, N=N, K=K, a_mn=True, b_mn=True, epi=epi, bn=bn)
     return out
 
 

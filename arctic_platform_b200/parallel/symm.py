@@ -33,6 +33,16 @@ def multimem_enabled() -> bool:
     return os.environ.get("APB_MULTIMEM", "0") == "1"
 
 
+def _keep_rendezvous_off_multicast() -> None:
+    """Unless ``APB_MULTIMEM=1`` asks for ``multimem`` kernels, tell torch's symmetric-memory rendezvous not to bind
+    the allocation to an NVSwitch multicast object at all (``TORCH_SYMM_MEM_DISABLE_MULTICAST``).  A binding that no
+    kernel uses still ties every rank's memory into one multicast group, and a rank that ends while bound can raise
+    NVLink faults on its peers' GPUs; with the binding off, stopping a rank leaves the others on plain peer
+    mappings only."""
+    if not multimem_enabled():
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
+
 class SymmetricBuffer:
     def __init__(self, numel: int, dtype: torch.dtype, device, group=None, zero: bool = True):
         self.group = group
@@ -44,6 +54,7 @@ class SymmetricBuffer:
         self._handle = None
         dev = torch.device(device)
         if self.world > 1 and dev.type == "cuda":
+            _keep_rendezvous_off_multicast()
             import torch.distributed._symmetric_memory as symm_mem
 
             self.tensor = symm_mem.empty(numel, dtype=dtype, device=dev)

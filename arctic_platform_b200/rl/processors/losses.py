@@ -21,6 +21,7 @@ from typing import Any, Dict, Tuple
 import torch
 
 from ...common.registry import register_loss_fn
+from ...utils.transfer_stats import to_device, to_host
 from .functional import (agg_loss, kl_penalty, m2po_mask, masked_sum, ppo_actor_loss_fn, ppo_clip_token_loss,
                          resolve_proximal_logp, sapo_loss_fn)
 
@@ -47,13 +48,13 @@ def _token_views(model_outputs: dict, batch: dict, device):
         t = batch.get(name)
         if t is None:
             return default
-        return packed.gather_from_grid(t.to(device)).float()
+        return packed.gather_from_grid(to_device(t, device)).float()
 
     mask_grid = batch.get("response_mask")
     if mask_grid is None:
         mask = torch.ones_like(model_outputs["logprobs"], dtype=torch.bool)
     else:
-        mask = packed.gather_from_grid(mask_grid.to(device)).bool()
+        mask = packed.gather_from_grid(to_device(mask_grid, device)).bool()
     if model_outputs.get("owned") is not None:          # sequence parallelism: this rank's share of the rows
         model_outputs["_full_mask"] = mask
         mask = mask & model_outputs["owned"].to(mask.device)
@@ -78,7 +79,7 @@ def verl_grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, d
     tok_loss, neg_kl, clipped, lower = ppo_clip_token_loss(lp, old, adv, 0.2, 0.2, 3.0)
     is_w = meta.get("rollout_is_weights")
     if is_w is not None:
-        tok_loss = tok_loss * packed.gather_from_grid(is_w.to(device)).float()
+        tok_loss = tok_loss * packed.gather_from_grid(to_device(is_w, device)).float()
     loss = agg_loss(tok_loss, mask, agg_mode, **info)
     mf = mask.float()
     sums = torch.stack([mf.sum(), (clipped.float() * mf).sum(), (-neg_kl * mf).sum(), (lower.float() * mf).sum(),
@@ -99,7 +100,7 @@ def verl_grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, d
         loss = loss + kl_coef * agg_loss(kld, mask, agg_mode, **info)
         extra.append((kld * mf).sum().detach())
     vals = torch.cat([sums, torch.stack(extra)]) if extra else sums
-    vals = vals.cpu().tolist()                      # the one device->host sync of the loss
+    vals = to_host(vals).tolist()                   # the one device->host sync of the loss
     ntok, clip_s, kl_s, lower_s, pg_s = vals[:5]
     metrics: Dict[str, Any] = {}
     for name, v in (("actor/pg_clipfrac", clip_s), ("actor/ppo_kl", kl_s), ("actor/pg_clipfrac_lower", lower_s),
@@ -164,7 +165,7 @@ def grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, device
         prox_sent = take("prox_logp")
     versions = batch.get("versions")
     if versions is not None:
-        versions = packed.gather_from_grid(versions.to(device))
+        versions = packed.gather_from_grid(to_device(versions, device))
     prox = resolve_proximal_logp(prox_sent, cfg.get("prox_logp_method", "recompute"), old, lp.detach(), versions,
                                  cfg.get("current_version"))
     if cfg.get("m2_threshold") is not None:
@@ -199,7 +200,8 @@ def grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, device
                         (stat["approx_kl"] * mf).sum(), (stat["importance_weight"] * mf).sum(),
                         (behav * mf).sum() if behav is not None else mf.sum(),
                         (stat["dual_clip_mask"].float() * mf).sum(),
-                        ((entropy.float().detach() if entropy is not None else -lp.detach()) * mf).sum()]).detach().cpu().tolist()
+                        ((entropy.float().detach() if entropy is not None else -lp.detach()) * mf).sum()]).detach()
+    vals = to_host(vals).tolist()
     n = vals[0]
     metrics = {"loss.sum": vals[1], "loss.tokens": n, "actor/pg_loss.sum": vals[1], "actor/pg_loss.tokens": n,
                "actor/pg_clipfrac.sum": vals[2], "actor/pg_clipfrac.tokens": n,
@@ -217,7 +219,7 @@ def _sft_core(model_outputs: dict, batch: dict, meta: dict, device):
     lm = batch.get("loss_mask")
     if lm is None and batch.get("labels") is not None:
         lm = (batch["labels"] != -100)
-    mask = (packed.gather_from_grid(lm.to(device)).bool() if lm is not None
+    mask = (packed.gather_from_grid(to_device(lm, device)).bool() if lm is not None
             else torch.ones_like(lp, dtype=torch.bool))
     if model_outputs.get("owned") is not None:
         mask = mask & model_outputs["owned"].to(mask.device)
@@ -235,7 +237,7 @@ def sft_ce_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, devi
     t_global = meta.get("batch_num_tokens")
     denom = float(t_global) if t_global else ntok.clamp_min(1).float()
     loss = ce_sum / denom * dp
-    s, n = torch.stack([ce_sum.detach(), ntok.float()]).cpu().tolist()
+    s, n = to_host(torch.stack([ce_sum.detach(), ntok.float()])).tolist()
     return loss, {"loss.sum": s, "loss.tokens": n}
 
 
@@ -244,7 +246,7 @@ def sft_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, device)
     """Mean next-token cross entropy of the shard (the Hugging Face ``outputs.loss`` convention)."""
     ce_sum, ntok = _sft_core(model_outputs, batch, meta, device)
     loss = ce_sum / ntok.clamp_min(1).float()
-    s, n = torch.stack([ce_sum.detach(), ntok.float()]).cpu().tolist()
+    s, n = to_host(torch.stack([ce_sum.detach(), ntok.float()])).tolist()
     return loss, {"loss.sum": s, "loss.tokens": n}
 
 

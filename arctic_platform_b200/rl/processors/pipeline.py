@@ -17,6 +17,7 @@ from typing import Any, Dict, List, Optional
 import torch
 
 from ...utils import sft_profile
+from ...utils.transfer_stats import to_device, to_host
 from ...common.registry import LOSS_FNS, POST_PROCESSORS, register_post_processor, resolve_fn
 from ...models.decoder import token_logprobs
 from ..zorro_train.layout import PackedBatch, build_packed_batch, build_plain_packed
@@ -131,7 +132,7 @@ def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = 
                 routed = batch.get("routed_experts") if packed.src_index is not None else None
                 lp, ent = token_logprobs(model, packed, 1.0 / temperature, with_entropy=want_entropy,
                                          action_masks=action_masks_of(batch, packed),
-                                         routed_experts=None if routed is None else routed.to(device))
+                                         routed_experts=None if routed is None else to_device(routed, device))
             else:
                 lp, ent, owned = _sp_logprobs(model, packed, sp_group, 1.0 / temperature, want_entropy, batch)
                 # every rank of the sequence-parallel group holds the same batch and scores its own rows; the loss
@@ -154,7 +155,8 @@ def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = 
                 raise ValueError("backward needs a loss_fn")
             with sft_profile.timed("bwd"):
                 engine.backward(loss)
-    result: Dict[str, Any] = {"metrics": metrics, "avg_loss": float(loss.detach()) if loss is not None else 0.0}
+    result: Dict[str, Any] = {"metrics": metrics,
+                              "avg_loss": float(to_host(loss.detach())) if loss is not None else 0.0}
     metrics.setdefault("perf/packed_tokens", float(packed.total_tokens))
     metrics.setdefault("perf/dedup_redundancy", float(packed.redundancy))
     metrics["perf/pipeline_ms"] = (time.perf_counter() - t0) * 1e3
@@ -166,8 +168,8 @@ def run_pipeline(engine, batch: Dict[str, torch.Tensor], meta: Optional[dict] = 
             both = torch.stack([lp_out, ent_out if ent_out is not None else torch.zeros_like(lp_out)])
             dist.all_reduce(both, group=sp_group)
             lp_out, ent_out = both[0], (both[1] if ent_out is not None else None)
-        out_batch = {"log_probs": packed.scatter_to_grid(lp_out).cpu()}
+        out_batch = {"log_probs": to_host(packed.scatter_to_grid(lp_out))}
         if ent_out is not None:
-            out_batch["entropy"] = packed.scatter_to_grid(ent_out).cpu()
+            out_batch["entropy"] = to_host(packed.scatter_to_grid(ent_out))
         result["batch"] = out_batch
     return result

@@ -64,11 +64,12 @@ class PackedBatch:
         return flat[self.src_index.to(grid.device)]
 
     def to(self, device) -> "PackedBatch":
-        self.input_ids = self.input_ids.to(device, non_blocking=True)
-        self.positions = self.positions.to(device, non_blocking=True)
-        self.pred_index = self.pred_index.to(device, non_blocking=True)
-        self.labels = self.labels.to(device, non_blocking=True)
-        self.out_index = self.out_index.to(device, non_blocking=True)
+        from ...utils.transfer_stats import to_device
+        self.input_ids = to_device(self.input_ids, device)
+        self.positions = to_device(self.positions, device)
+        self.pred_index = to_device(self.pred_index, device)
+        self.labels = to_device(self.labels, device)
+        self.out_index = to_device(self.out_index, device)
         return self
 
     def scatter_to_grid(self, values: torch.Tensor, fill: float = 0.0) -> torch.Tensor:

@@ -7,11 +7,14 @@ configuration, 64 prompts x 16 samples on 8 GPUs, is 8 prompts per GPU).  The he
 whole-job tokens/s = global (prompt + response) tokens of a step / step time, as the reference's verl
 integration reports (arctic_platform/integrations/verl/README.md:100-109).
 
-Two timed regions of ``--steps`` steps each, both bracketed by barrier + synchronize, timed with CUDA
-events, max over ranks:
-  * ``value``: the engines driven directly;
-  * ``e2e``:   the same step through the public client API (``create_arctic_rl_client``), where every
-               step copies its inputs from pinned host memory to the device and reads its results back.
+ONE timed region of ``--steps`` steps, driven through the public client API (``create_arctic_rl_client``),
+bracketed by barrier + synchronize, timed with CUDA events, max over ranks.  Every step builds its batch in
+pinned host memory, copies it to the device inside the engines and reads its results (tokens, log-prob grids,
+loss) back:
+  * ``e2e``:   CUDA-event time of the whole region (host batch building, copies and read-backs included);
+  * ``value``: the device time of the engine phases inside the SAME steps (sync_weights, rollout, reference
+               log-probs, forward/backward, optimizer), each bracketed by CUDA events, host batch building excluded.
+Bytes copied per step are counted where the copies are issued (``utils/transfer_stats.py``).
 
     python bench.py [--gpus N --steps K --warmup W]          # N > 1 under torch.distributed.run
     python bench.py --impl reference                          # the reference's own stack, if installable
@@ -50,8 +53,9 @@ def parse_args():
                     help="training micro-batches scored together in one reference (no-grad) forward")
     ap.add_argument("--zero-stage", type=int, default=3,
                     help="3: bf16 parameters sharded over ranks and gathered unit by unit; 2: replicated parameters")
-    ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--phases", action="store_true", help="print per-phase wall times of the direct step to stderr")
+    ap.add_argument("--baseline-json", default=None,
+                    help="file with a same-box anchor {'grpo_step_tokens_per_s_per_gpu': x, 'what': ...}; default "
+                         "benchmarks/anchors_1gpu.json when present (vs_baseline = value / (x * gpus))")
     ap.add_argument("--lr", type=float, default=1e-6)
     return ap.parse_args()
 
@@ -132,9 +136,6 @@ def main():
     if args.gpus != world and rank == 0 and world > 1:
         print(f"[bench] --gpus {args.gpus} but WORLD_SIZE {world}; using {world}", file=sys.stderr)
 
-    from arctic_platform_b200.engine.sampler import SamplingParams
-    from arctic_platform_b200.engine.trainer import EngineConfig, TrainEngine
-    from arctic_platform_b200.engine.worker import EngineWorker
     from arctic_platform_b200.models.config import resolve_config
     from arctic_platform_b200.ops import _lib
     from arctic_platform_b200.rl import ArcticRLClientConfig, create_arctic_rl_client
@@ -152,10 +153,6 @@ def main():
         vllm_config={"kv_cache_tokens": kv_tokens, "max_num_seqs": max(8, B), "max_model_len": P + R + 16},
         arctic_inference_config={"zorro_inference": {"enable": True}})
     client = create_arctic_rl_client(client_cfg)
-    server = client.get_server_state()
-    train_w = server.find_job("training").workers[0].obj
-    samp_w = server.find_job("sampling").workers[0].obj
-    ref_w = server.find_job("log_prob").workers[0].obj
 
     gen = torch.Generator().manual_seed(99 + rank)
     sp = {"n": NS, "temperature": 1.0, "max_tokens": R, "ignore_eos": True}
@@ -170,13 +167,16 @@ def main():
     def make_prompts():
         return [torch.randint(1, cfg.vocab_size, (P,), generator=gen).tolist() for _ in range(NP)]
 
+    ids_host = torch.zeros((B, P + R), dtype=torch.int64).pin_memory()
+    old_host = torch.zeros((B, R), dtype=torch.float32).pin_memory()
+
     def build_batches(prompts, results):
         """Padded RL batch on pinned host memory, split so that each micro-batch holds every prompt with a
         slice of its rollouts (the prompt is deduplicated inside a micro-batch)."""
-        ids = torch.zeros((B, P + R), dtype=torch.int64).pin_memory()
-        old = torch.zeros((B, R), dtype=torch.float32).pin_memory()
+        ids, old = ids_host.zero_(), old_host.zero_()
+        prompt_t = [torch.tensor(p) for p in prompts]
         for i, r in enumerate(results):
-            ids[i, :P] = torch.tensor(prompts[r["prompt_index"]])
+            ids[i, :P] = prompt_t[r["prompt_index"]]
             ids[i, P:P + len(r["token_ids"])] = torch.tensor(r["token_ids"])
             old[i, :len(r["logprobs"])] = torch.tensor(r["logprobs"])
         mask = torch.ones_like(ids)
@@ -211,113 +211,111 @@ def main():
             m["ref_log_prob"] = logp[r0:r0 + n]
             r0 += n
 
-    def in_bytes(mbs, prompts):
-        return sum(t.numel() * t.element_size() for mb in mbs for t in mb.values()) + sum(len(p) for p in prompts) * 8
+    from arctic_platform_b200.utils import transfer_stats
 
-    counters = {"h2d": 0, "d2h": 0}
+    PHASES = ("sync_weights", "rollout", "ref_logprob", "fwd_bwd", "optimizer")
+    marks = []          # per step: list of (phase, start event, end event)
 
-    phase_ms = {}
-
-    def mark(name, t0):
-        if args.phases:
-            torch.cuda.synchronize(dev)
-            phase_ms[name] = phase_ms.get(name, 0.0) + (time.perf_counter() - t0) * 1e3
-        return time.perf_counter()
-
-    def step_direct():
-        """Engines driven directly (no client / server layer)."""
-        t = time.perf_counter()
-        prompts = make_prompts()
-        train_w.sync_weights_to(samp_w)
-        samp_w.sampler.wake(["kv_cache"])
-        t = mark("sync_weights", t)
-        results = samp_w.generate(prompts, sp)
-        t = mark("rollout", t)
-        samp_w.sampler.sleep(1)
-        mbs = build_batches(prompts, results)
-        t = mark("build_batch", t)
-        for grp in ref_groups(mbs):
-            ref = ref_w.forward_no_grad(grp["batch"], dict(meta), None)
-            scatter_ref(grp, ref["batch"]["log_probs"])
-        t = mark("ref_logprob", t)
-        out = train_w.forward_backward(mbs, dict(meta), {"loss_fn": "verl_grpo"})
-        t = mark("fwd_bwd", t)
-        st = train_w.step()
-        t = mark("optimizer", t)
-        return out["avg_loss"], st["metrics"]["grad_norm"]
+    def phase(name, fn, *a, **kw):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn(*a, **kw)
+        e1.record()
+        marks[-1].append((name, e0, e1))
+        return out
 
     def step_client():
-        """The same step through the public client API; inputs start in pinned host memory."""
+        """One GRPO step through the public client API; inputs start in pinned host memory, results come back to
+        the host (generated tokens and log-probs, reference log-prob grids, loss and gradient norm)."""
+        marks.append([])
         prompts = make_prompts()
-        client.call("sync_weights")
-        results = client.call("generate", prompts, sp)
+        phase("sync_weights", client.call, "sync_weights")
+        results = phase("rollout", client.call, "generate", prompts, sp)
         client.call("sleep_inference", 1)
         mbs = build_batches(prompts, results)
-        counters["h2d"] = 2 * in_bytes(mbs, prompts)          # every micro-batch goes to the device twice (ref + train)
-        d2h = sum(len(r["token_ids"]) * 8 for r in results)
-        for grp in ref_groups(mbs):
-            ref = client.call("fwd_no_grad", {"batch": grp["batch"], "meta": dict(meta)}, reference_model=True)
-            scatter_ref(grp, ref["batch"]["log_probs"])
-            d2h += ref["batch"]["log_probs"].numel() * 4
-        out = client.call("fwd_bwd", {"batch": mbs, "meta": dict(meta)}, {"loss_fn": "verl_grpo"})
-        st = client.call("step")
-        counters["d2h"] = d2h + 8 * (len(out["metrics"]) + 2)
-        return out["avg_loss"], st["metrics"]["grad_norm"]
+
+        def ref_pass():
+            for grp in ref_groups(mbs):
+                ref = client.call("fwd_no_grad", {"batch": grp["batch"], "meta": dict(meta)}, reference_model=True)
+                scatter_ref(grp, ref["batch"]["log_probs"])
+
+        phase("ref_logprob", ref_pass)
+        out = phase("fwd_bwd", client.call, "fwd_bwd", {"batch": mbs, "meta": dict(meta)}, {"loss_fn": "verl_grpo"})
+        st = phase("optimizer", client.call, "step")
+        return out["avg_loss"], float(st["metrics"]["grad_norm"])
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    def timed(fn, k):
-        barrier()
-        st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0 = _lib.launch_count()
-        st.record()
-        for _ in range(k):
-            fn()
-        en.record()
-        barrier()
-        ms = st.elapsed_time(en)
-        if world > 1:
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms / k, _lib.launch_count() - l0
+    def reduce_max(vals):
+        if world == 1:
+            return [float(v) for v in vals]
+        t = torch.tensor(list(vals), device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
 
     for _ in range(args.warmup):
-        step_direct()
+        step_client()
+    marks.clear()
     sampler = ClockSampler(local_rank)
     sampler.start()
-    phase_ms.clear()
-    ms_direct, launches = timed(step_direct, args.steps)
-    if args.phases and rank == 0:
-        print("[bench] phases ms/step: " + json.dumps({k: round(v / args.steps, 1) for k, v in phase_ms.items()}),
-              file=sys.stderr, flush=True)
-    e2e = None
-    if not args.no_e2e:
-        step_client()                                        # client path warm-up (separate caches / graphs)
-        ms_client, _ = timed(step_client, args.steps)
-        tokens = B * (P + R) * world
-        e2e = {"value": tokens / (ms_client / 1e3), "unit": "tokens/s", "ms_per_step": ms_client,
-               "h2d_bytes_per_step": counters["h2d"], "d2h_bytes_per_step": counters["d2h"]}
+    barrier()
+    transfer_stats.reset()
+    l0 = _lib.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        loss, gnorm = step_client()
+    ev1.record()
+    barrier()
+    launches = _lib.launch_count() - l0
+    xfer = transfer_stats.snapshot()
     sampler.stop_flag.set()
     sampler.join(timeout=3)
     _lib.check_status("bench")
+    if not (loss == loss and gnorm == gnorm):
+        raise SystemExit(f"bench: non-finite loss {loss} / grad norm {gnorm}")
+    phase_ms = {n: 0.0 for n in PHASES}
+    for step_marks in marks:
+        for name, e0, e1 in step_marks:
+            phase_ms[name] += e0.elapsed_time(e1)
+    K = args.steps
+    red = reduce_max([ev0.elapsed_time(ev1) / K, sum(phase_ms.values()) / K] + [phase_ms[n] / K for n in PHASES])
+    ms_e2e, ms_dev, per_phase = red[0], red[1], red[2:]
     if rank == 0:
         tokens = B * (P + R) * world
+        value = tokens / (ms_dev / 1e3)
+        anchor, vs = None, None
+        bj = Path(args.baseline_json) if args.baseline_json else ROOT / "benchmarks" / "anchors_1gpu.json"
+        if bj.is_file():
+            try:
+                anchor = json.loads(bj.read_text())
+                per_gpu = float(anchor["grpo_step_tokens_per_s_per_gpu"])
+                vs = value / (per_gpu * world)
+            except Exception:
+                anchor = None
+        stage_label = f"zero{args.zero_stage}-fused" if world > 1 else "single-rank fused clip+AdamW (no sharding)"
         line = {
-            "metric": "grpo_step_tokens_per_s", "value": tokens / (ms_direct / 1e3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_direct,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "metric": "grpo_step_tokens_per_s", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": vs, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
             "config": {"model": args.model, "global_batch": B * world, "prompts": NP * world, "samples_per_prompt": NS,
                        "seq_len": P + R, "prompt_len": P, "response_len": R,
-                       "parallelism": f"dp{world}-zero{args.zero_stage}-fused + sampler tp1 x{world} replicas, colocated",
+                       "parallelism": f"dp{world} {stage_label} + sampler tp1 x{world} replicas, colocated",
                        "l2_policy": "inputs larger than L2 (new random prompts and rollouts every step)",
                        "step": "sync_weights+rollout+ref_logprob+fwd_bwd+adamw", "lr": args.lr,
-                       "train_microbatches": n_mb},
-            "clocks": sampler.summary(), "e2e": e2e, "gpu_launches": launches,
+                       "train_microbatches": n_mb,
+                       "timed_region": "one region through the client API; value = sum of CUDA-event phase times "
+                                       "inside it, e2e = the whole region",
+                       "vs_baseline_is": (anchor or {}).get("what") if vs is not None else None},
+            "clocks": sampler.summary(),
+            "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": xfer["h2d"] // K, "d2h_bytes_per_step": xfer["d2h"] // K},
+            "phases_ms": {n: round(v, 1) for n, v in zip(PHASES, per_phase)},
+            "gpu_launches": launches,
             "peak_device_memory_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1),
             "rollout_tokens_per_step": B * R * world,
         }

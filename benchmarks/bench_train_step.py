@@ -4,7 +4,11 @@
                                           [--rollouts 4] [--iters 3]
 
 CUDA-event timing after warm-up; every iteration uses fresh random tokens (inputs far larger than L2 stream through).
-Meant to be run under ``ncu --metrics gpu__time_duration.sum`` for the per-kernel launch list of a training step."""
+For the per-kernel launch list of a training step, run a small case (``--layers 4 --iters 1``) plainly first and,
+where the profiler is open on the box, again under
+``ncu --metrics gpu__time_duration.sum --clock-control none -c 4000 --csv --log-file train_launches.csv``
+(always with ``--clock-control none``: without it the profiler locks the GPU clocks, a setting that outlives the
+process on a shared GPU)."""
 import argparse
 import dataclasses
 import json

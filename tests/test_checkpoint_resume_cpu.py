@@ -70,3 +70,57 @@ def test_latest_tag_and_missing_checkpoint(tmp_path):
     c = _engine(3, False)
     assert load_checkpoint(c, str(tmp_path), "global_step1") == 1
     assert not torch.equal(c.full_flat_params(), b.full_flat_params())
+
+
+def test_sleep_is_idempotent_and_a_sleeping_engine_refuses_state_changes(tmp_path):
+    """Sleep / wake state machine: sleeping twice keeps the real optimizer state, stepping or touching checkpoints
+    while asleep raises (nothing reaches a kernel with empty tensors), waking twice is a no-op, and the engine
+    continues exactly as one that never slept."""
+    batches = [make_grpo_batch(n_prompts=2, n_samples=2, seed=s) for s in range(4)]
+    a, b = _engine(1, False), _engine(1, False)
+    _run(a, batches, 2)
+    _run(b, batches, 2)
+    master = a.master.clone()
+    assert not a.asleep
+    a.offload_states(("optimizer",))                     # "non_lp" ...
+    assert a.asleep and a.master.numel() == 0
+    a.offload_states(("optimizer", "grads", "params"))   # ... then "all": must not replace the host copy by an empty one
+    assert torch.equal(a._offloaded["master"], master)
+    ids, mask, R = batches[0]
+    lp, _ = token_logprobs(a.model, build_packed_batch(ids, mask, R, dedup=True))
+    with pytest.raises(RuntimeError, match="asleep"):
+        a.backward(-lp.mean())
+    with pytest.raises(RuntimeError, match="asleep"):
+        a.step()
+    with pytest.raises(RuntimeError, match="asleep"):
+        save_checkpoint(a, str(tmp_path), "t")
+    with pytest.raises(RuntimeError, match="asleep"):
+        load_checkpoint(a, str(tmp_path), "t")
+    assert not list(tmp_path.iterdir())                  # the refused save wrote nothing
+    a.reload_states()
+    a.reload_states()                                    # waking an engine that is awake changes nothing
+    assert not a.asleep and torch.equal(a.master, master)
+    for p in a.model.parameters():
+        p.grad = None
+    a.zero_grad()
+    assert _run(a, batches, 2) == _run(b, batches, 2)
+    assert torch.equal(a.master, b.master) and torch.equal(a.exp_avg_sq, b.exp_avg_sq)
+
+
+def test_load_rejects_a_layout_mismatch_and_accepts_a_tag_directory(tmp_path):
+    a = _engine(1, False)
+    _run(a, [make_grpo_batch(n_prompts=2, n_samples=2, seed=0)], 1)
+    saved = save_checkpoint(a, str(tmp_path))            # <dir>/latest -> global_step1
+    b = _engine(2, False)
+    assert load_checkpoint(b, saved["path"]) == 1        # the tag directory itself (holds the model-states file)
+    assert torch.equal(a.master, b.master)
+    with pytest.raises(FileNotFoundError):
+        load_checkpoint(b, str(tmp_path / "void"), strict=True)
+    # a checkpoint written for another parameter layout must not be poured into this engine's flat buffers
+    import torch as _t
+    f = tmp_path / "global_step1" / "mp_rank_00_model_states.pt"
+    st = _t.load(f, weights_only=False)
+    st["b200_layout"]["total"] += 8
+    _t.save(st, f)
+    with pytest.raises(ValueError, match="layout"):
+        load_checkpoint(b, str(tmp_path))

@@ -132,3 +132,62 @@ def test_two_ctas_per_sm_variant_matches_reference(bn, epi):
         _lib.check_status("x2 gemm swiglu")
         want = torch.nn.functional.silu(ref[:, 0::2]) * ref[:, 1::2]
         assert (act.float() - want).abs().max() < 0.05
+
+
+def _pair(a, b, out, M, N, K, a_mn=False, b_mn=False, epi=0, alpha=1.0, bias=None, out2=None):
+    """Direct call of the CTA-pair kernel (any size; the automatic dispatch only sends large problems there)."""
+    import ctypes as c
+    from arctic_platform_b200.ops import _lib
+    vp, i, ll, f = c.c_void_p, c.c_int, c.c_longlong, c.c_float
+    fn = _lib.declare("apb_gemm_bf16_pair", [vp, vp, vp, i, i, i, ll, ll, ll, i, i, i, f, vp, vp, ll, vp])
+    _lib.check(fn(_lib.ptr(a), _lib.ptr(b), _lib.ptr(out), M, N, K, a.stride(0), b.stride(0),
+                  out.stride(0) if out is not None else 0, int(a_mn), int(b_mn), epi, alpha, _lib.ptr(bias),
+                  _lib.ptr(out2), out2.stride(0) if out2 is not None else 0, _lib.stream_ptr()), "apb_gemm_bf16_pair")
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (300, 264, 72), (1000, 2568, 1096),
+                                   (4096, 2560, 2560), (77, 8, 8)])
+def test_cta_pair_kernel_all_operand_layouts(M, N, K):
+    """256 x 256 tiles on two SMs (tcgen05 cta_group::2): NT / NN / TN products, bf16 and fp32 outputs, accumulation,
+    row / column / depth tails, against fp32 matmul."""
+    from arctic_platform_b200.ops import _lib
+    a, b = _rand((M, K)), _rand((N, K))
+    ref = a.float() @ b.float().t()
+    out = torch.empty((M, N), device="cuda", dtype=torch.bfloat16)
+    _pair(a, b, out, M, N, K)
+    _lib.check_status("pair nt")
+    _close(out, ref, K)
+    bias = _rand((N,))
+    _pair(a, b, out, M, N, K, bias=bias, alpha=0.5)
+    _lib.check_status("pair nt bias")
+    _close(out, 0.5 * ref + bias.float(), K)
+    bt = b.t().contiguous()                                   # [K, N]: the data-gradient form
+    out32 = torch.empty((M, N), device="cuda", dtype=torch.float32)
+    _pair(a, bt, out32, M, N, K, b_mn=True, epi=1)
+    _lib.check_status("pair nn")
+    _close(out32, ref, K)
+    at = a.t().contiguous()                                   # [K, M]: the weight-gradient form, accumulated
+    acc = torch.full((M, N), 2.0, device="cuda", dtype=torch.float32)
+    _pair(at, bt, acc, M, N, K, a_mn=True, b_mn=True, epi=3)
+    _lib.check_status("pair tn acc")
+    _close(acc, ref + 2.0, K)
+
+
+def test_cta_pair_kernel_swiglu_and_many_tiles_per_pair():
+    """More tiles than resident pairs (the persistent loop and both accumulator buffers are exercised) and the
+    SwiGLU epilogue; also the automatic dispatch of a large product equals the one-CTA kernel's result."""
+    from arctic_platform_b200.ops import _lib, gemm
+    M, K, I = 2304, 512, 9728
+    x, w = _rand((M, K)), _rand((2 * I, K), 0.1)
+    gu = torch.empty((M, 2 * I), device="cuda", dtype=torch.bfloat16)
+    act = torch.empty((M, I), device="cuda", dtype=torch.bfloat16)
+    _pair(x, w, gu, M, 2 * I, K, epi=4, out2=act)
+    _lib.check_status("pair swiglu")
+    ref_gu = x.float() @ w.float().t()
+    _close(gu, ref_gu, K)
+    _close(act, torch.nn.functional.silu(ref_gu[:, 0::2]) * ref_gu[:, 1::2], K)
+    auto = gemm.matmul_nt(x, w)                               # dispatch picks the pair kernel for this size
+    one = gemm.matmul_nt(x, w, bn=256)                        # forced one-CTA kernel
+    _lib.check_status("pair vs one")
+    assert torch.equal(auto, gu)
+    assert (auto.float() - one.float()).abs().max().item() <= 2e-2 * ref_gu.abs().max().item()

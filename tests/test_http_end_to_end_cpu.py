@@ -55,9 +55,21 @@ def test_http_training_loop_and_errors(server, tmp_path):
     norms = c.call("weight_norm")
     assert norms["training_norm"] > 0
     saved = c.call("save_checkpoint", None, 3, True)
-    assert saved["tag"] == "checkpoint-3"
+    # the reference's contract: a self-contained <root>/checkpoint-3/ (own latest, global_step<N>/, hf/), the
+    # integer step in <root>/latest, and path / hf_path / global_step in the reply
+    import os
+    ck = saved["path"]
+    assert os.path.basename(ck) == "checkpoint-3" and saved["global_step"] == 1
+    assert saved["hf_path"] == os.path.join(ck, "hf") and os.path.isdir(saved["hf_path"])
+    assert open(os.path.join(ck, "latest")).read().strip() == "global_step1"
+    assert os.path.isfile(os.path.join(ck, "global_step1", "mp_rank_00_model_states.pt"))
+    assert open(os.path.join(os.path.dirname(ck), "latest")).read().strip() == "3"
     loaded = c.call("load_checkpoint", None, 3)
-    assert loaded["global_steps"] == 1
+    assert loaded["global_steps"] == 1 and loaded["global_step"] == 1 and loaded["path"] == ck
+    assert c.call("load_checkpoint")["global_step"] == 1             # the job root: follows <root>/latest
+    assert c.call("load_checkpoint", ck)["global_step"] == 1         # the reference form: path=<root>/checkpoint-N
+    with pytest.raises(RuntimeError):                                 # a step that was never saved is an error, not step 0
+        c.call("load_checkpoint", None, 99)
     assert c.call("sleep_log_prob")["status"] == "sleeping" and c.call("wake_log_prob")["status"] == "awake"
     before = c.job_ids["training"]
     rec = c.call("recover_training")                     # checkpoint + restart: same weights and step counter, new id

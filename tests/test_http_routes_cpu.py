@@ -106,7 +106,10 @@ def test_all_routes(api, tmp_path):
 
     # checkpoint + restart through the API: a new job id, the step counter comes back
     ck = api.post("/save", params={"job_id": jobs["training"]}, json={"path": str(tmp_path), "step": 1}).json()
-    assert ck["tag"] == "checkpoint-1"
+    assert ck["path"].endswith("checkpoint-1") and ck["global_step"] == 1 and ck["hf_path"] is None
+    assert (tmp_path / "latest").read_text().strip() == "1"
+    assert api.post("/load-checkpoint", params={"job_id": jobs["training"]},
+                    json={"path": str(tmp_path), "step": 7}).status_code == 404      # never saved: an error, not step 0
     rec = api.post("/recover", params={"job_id": jobs["training"]}, json={"path": str(tmp_path)}).json()
     assert rec["recovered_from"] == jobs["training"] and rec["global_steps"] == 1 and rec["job_id"] != jobs["training"]
     assert api.post("/recover", params={"job_id": jobs["training"]}).status_code == 404

@@ -59,8 +59,15 @@ def test_position_ids_reconstruction():
 
 
 def test_checkpoint_paths_and_pruning(tmp_path):
-    assert resolve_checkpoint_save_paths("/x/y", 12) == ("/x/y", "checkpoint-12")
-    assert resolve_checkpoint_save_paths("/x/y", None) == ("/x/y", None)
+    # (save_dir, prune_root): a step makes a self-contained child directory, pruning always happens under the root
+    assert resolve_checkpoint_save_paths("/x/y", 12) == ("/x/y/checkpoint-12", "/x/y")
+    assert resolve_checkpoint_save_paths("/x/y", None) == ("/x/y", "/x/y")
+    from arctic_platform_b200.common.utils.checkpoint import resolve_checkpoint_load_path
+    (tmp_path / "latest").write_text("20")
+    assert resolve_checkpoint_load_path(str(tmp_path), 5, False) == str(tmp_path / "checkpoint-5")
+    assert resolve_checkpoint_load_path(str(tmp_path), None, False) == str(tmp_path / "checkpoint-20")
+    assert resolve_checkpoint_load_path(str(tmp_path), None, True) == str(tmp_path)      # an explicit path is taken as is
+    (tmp_path / "latest").unlink()
     for s in (1, 5, 10, 20):
         (tmp_path / f"checkpoint-{s}").mkdir()
     (tmp_path / "hf").mkdir()

@@ -274,7 +274,7 @@ def test_recovery_is_checkpoint_plus_restart(tmp_path):
         jid = core.initialize(job_cfg)["job_id"]
         got = _train(core, jid, steps=2)
         saved = core.save(jid, step=2)
-        assert saved["tag"] == "checkpoint-2"
+        assert saved["path"].endswith("checkpoint-2") and saved["global_step"] == 2
         lost = core.pool.actors[1]
         lost._proc.terminate()                                                  # the exact child of this pool
         lost._proc.join(10)
@@ -295,9 +295,11 @@ def test_recovery_is_checkpoint_plus_restart(tmp_path):
 
 
 @pytest.mark.timeout(600)
-def test_token_budget_micro_batches_stay_in_step_across_ranks():
+@pytest.mark.parametrize("agg_mode", ["token-mean", "seq-mean-token-mean"])
+def test_token_budget_micro_batches_stay_in_step_across_ranks(agg_mode):
     """Two ZeRO-3 ranks whose shards need different numbers of token-budget micro-batches: the rank with fewer pads
-    with loss-free passes, so the per-pass gathers line up; results equal one process on the whole batch."""
+    with loss-free passes, so the per-pass gathers line up; results equal one process on the whole batch.  The
+    sequence-mean aggregation divides by the number of REAL rows: the filler passes must not count as sequences."""
     ids, mask, R = make_grpo_batch(n_prompts=4, n_samples=2, seed=21, p_rng=(4, 8), r_rng=(2, 6))
     # rank 0's half: long sequences; rank 1's half: short ones -> different micro-batch counts under one budget
     ids2, mask2, _ = make_grpo_batch(n_prompts=4, n_samples=2, seed=22, p_rng=(30, 40), r_rng=(2, 6))
@@ -313,7 +315,8 @@ def test_token_budget_micro_batches_stay_in_step_across_ranks():
              "old_log_probs": torch.randn(B, R, generator=g) * 0.01 - 2.0,
              "advantages": torch.randn(B, 1, generator=g).expand(B, R).contiguous()}
     budget = int(all_mask.sum(1).max()) + 4
-    meta = {"response_length": R, "zorro_train_enable": False, "max_tokens_per_mb": budget}
+    meta = {"response_length": R, "zorro_train_enable": False, "max_tokens_per_mb": budget,
+            "actor_config": {"loss_agg_mode": agg_mode}}
     single = ArcticRLServerCore()
     j1 = single.initialize(_job(3))["job_id"]
     want_lp = single.forward(j1, {"batch": batch, "meta": dict(meta)})["batch"]["log_probs"]
