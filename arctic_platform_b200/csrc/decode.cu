@@ -466,19 +466,25 @@ struct MergeSrc {
   int splits[4];
   int n;
 };
-__global__ void decode_merge_kernel(MergeSrc src, __nv_bfloat16* __restrict__ out, float* __restrict__ lse_out,
-                                    int rows, int Hq, int D) {
+__global__ void decode_merge_kernel(MergeSrc src, const int* __restrict__ row_mask, __nv_bfloat16* __restrict__ out,
+                                    float* __restrict__ lse_out, int rows, int Hq, int D) {
   pdl_entry();
   const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (gw >= static_cast<long long>(rows) * Hq) return;
+  // bit s of row_mask[row]: source s holds partials of this row (a sequence without a node at some level of the
+  // forest has stale data there); null = every source is valid for every row
+  const int valid = row_mask ? row_mask[gw / Hq] : 0xF;
   float mm = -INFINITY;
-  for (int s = 0; s < src.n; ++s)
+  for (int s = 0; s < src.n; ++s) {
+    if (!((valid >> s) & 1)) continue;
     for (int k = 0; k < src.splits[s]; ++k) mm = fmaxf(mm, src.ml[s][(gw * src.splits[s] + k) * 2]);
+  }
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   float ll = 0.f;
   for (int s = 0; s < src.n; ++s)
     for (int k = 0; k < src.splits[s]; ++k) {
+      if (!((valid >> s) & 1)) break;
       const long long b = gw * src.splits[s] + k;
       const float m = src.ml[s][b * 2];
       const float sc = (m == -INFINITY) ? 0.f : exp2f(m - mm);
@@ -989,8 +995,9 @@ int apb_paged_decode_partial(const void* q, const int* q_start, const int* q_cou
 }
 
 // Merges up to 4 partial sets into out [rows, Hq, D] bf16 (+ optional natural-log LSE [rows, Hq]).
-int apb_decode_merge(const float* const* o_ptrs, const float* const* ml_ptrs, const int* splits, int n_src, void* out,
-                     float* lse, int rows, int Hq, int D, cudaStream_t s) {
+// row_mask [rows] (or null): bit s set = source s is valid for the row.
+int apb_decode_merge(const float* const* o_ptrs, const float* const* ml_ptrs, const int* splits, int n_src,
+                     const int* row_mask, void* out, float* lse, int rows, int Hq, int D, cudaStream_t s) {
   if (rows <= 0) return 0;
   if (n_src < 1 || n_src > 4 || D != 128) return kBadArgument;
   MergeSrc src;
@@ -1002,7 +1009,7 @@ int apb_decode_merge(const float* const* o_ptrs, const float* const* ml_ptrs, co
   }
   const long long warps = static_cast<long long>(rows) * Hq;
   const int grid = static_cast<int>((warps * 32 + 255) / 256);
-  return static_cast<int>(launch_kernel(decode_merge_kernel, dim3(grid), dim3(256), 0, s, src,
+  return static_cast<int>(launch_kernel(decode_merge_kernel, dim3(grid), dim3(256), 0, s, src, row_mask,
                                         static_cast<__nv_bfloat16*>(out), lse, rows, Hq, D));
 }
 

@@ -1,12 +1,14 @@
 // Forest-cascade decode, shared-prefix pass on tcgen05 tensor cores.
 //
-// All decode queries that share one node of the prefix forest (the rollouts of one prompt) attend to the
-// node's KV pages TOGETHER: the query rows of up to 128/R sequences x R query heads of one KV head form one
+// All decode queries that share one node of the prefix forest (the rollouts of one prompt, or all rollouts of
+// all prompts under a common header) attend to the node's KV pages TOGETHER: the query rows of up to 128/R sequences x R query heads of one KV head form one
 // 128-row UMMA tile, the node's K/V pages are streamed once by TMA (one 16-token page per copy, straight out
 // of the paged cache), S = Q K^T and P V run on the tensor core with S/P in tensor memory, and the result is
 // left as an un-normalised partial (max, sum, numerator) per query row and KV split, in the same format as
 // the per-sequence pass, so one LSE merge joins the two levels.  KV of a shared prompt is therefore read once
-// per step for all of its rollouts instead of once per rollout.  The reference obtains this behaviour from
+// per step for all of its rollouts instead of once per rollout.  A forest with several shared levels (header ->
+// prompt -> rollout) is one launch: every node names its level, partials of level l go to buffer l, and the merge
+// joins the levels a sequence takes part in with its private pass.  The reference obtains this behaviour from
 // ArcticInference's forest cascade attention (`use_fca`, arctic_platform/common/utils/server_models.py:123-132).
 //
 // CTA = 192 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax (one row each).
@@ -21,8 +23,9 @@ struct DecPrefixParams {
   const int* pages;     // [G, max_pages]
   int max_pages;
   const int* kv_len;    // [G] tokens in the node
-  float* out_o;         // [Bq, Hq, splits, D] fp32 un-normalised numerators
-  float* out_ml;        // [Bq, Hq, splits, 2] (max in base-2 scaled units, sum)
+  const int* level;     // [G] tree level of the node (selects the output buffer) or null (all level 0)
+  float* out_o[3];      // per level: [Bq, Hq, splits, D] fp32 un-normalised numerators
+  float* out_ml[3];     // per level: [Bq, Hq, splits, 2] (max in base-2 scaled units, sum)
   int Hq, Hkv, splits;
   float scale_log2;
   int* status;
@@ -232,12 +235,16 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       const int seq = qs + row / R;
       const int head = kvh * R + row % R;
       const long long base = (static_cast<long long>(seq) * p.Hq + head) * p.splits + split;
-      float4* dst = reinterpret_cast<float4*>(p.out_o + base * D);
+      int lvl = p.level ? p.level[g] : 0;
+      lvl = lvl < 0 ? 0 : (lvl > 2 ? 2 : lvl);
+      float* out_o = lvl == 0 ? p.out_o[0] : (lvl == 1 ? p.out_o[1] : p.out_o[2]);
+      float* out_ml = lvl == 0 ? p.out_ml[0] : (lvl == 1 ? p.out_ml[1] : p.out_ml[2]);
+      float4* dst = reinterpret_cast<float4*>(out_o + base * D);
 #pragma unroll
       for (int q = 0; q < D / 4; ++q)
         dst[q] = make_float4(o_acc[q * 4], o_acc[q * 4 + 1], o_acc[q * 4 + 2], o_acc[q * 4 + 3]);
-      p.out_ml[base * 2] = m_run;
-      p.out_ml[base * 2 + 1] = l_run;
+      out_ml[base * 2] = m_run;
+      out_ml[base * 2 + 1] = l_run;
     }
   }
 
@@ -253,18 +260,22 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
 
 extern "C" {
 
-// Shared-prefix pass of cascade decode on the tensor cores.  Same group tables and output format as
-// apb_paged_decode_partial.  q [Bq, Hq, D] bf16 contiguous; caches [num_pages, Hkv, 16, D] bf16.
-// Requires D == 128 and R * max(q_count) <= 128.
+// Shared-prefix pass of cascade decode on the tensor cores.  Same node tables and output format as
+// apb_paged_decode_partial, plus `level` [G] (or null): the partials of a node go to out_o[level] / out_ml[level]
+// (up to 3 shared levels; unused entries may be null).  q [Bq, Hq, D] bf16 contiguous; caches
+// [num_pages, Hkv, 16, D] bf16.  Requires D == 128 and R * max(q_count) <= 128.
 int apb_decode_prefix_tc(const void* q, int Bq, const int* q_start, const int* q_count, const int* pages,
-                         int max_pages, const int* kv_len, const void* kcache, const void* vcache, long long num_pages,
-                         float* out_o, float* out_ml, int G, int Hq, int Hkv, int D, int splits, float scale,
-                         cudaStream_t s) {
+                         int max_pages, const int* kv_len, const int* level, const void* kcache, const void* vcache,
+                         long long num_pages, float* const* out_o, float* const* out_ml, int n_levels, int G, int Hq,
+                         int Hkv, int D, int splits, float scale, cudaStream_t s) {
   using namespace apb;
   if (G <= 0) return 0;
-  if (D != 128 || Hq % Hkv || splits < 1) return kBadArgument;
+  if (D != 128 || Hq % Hkv || splits < 1 || n_levels < 1 || n_levels > 3 || !out_o || !out_ml) return kBadArgument;
   const int R = Hq / Hkv;
   if (R > 128 || 128 % R) return kBadArgument;
+  for (int l = 0; l < n_levels; ++l)
+    if (!out_o[l] || !out_ml[l]) return kBadArgument;
+  if (n_levels > 1 && !level) return kBadArgument;
   CUtensorMap tq, tk, tv;
   {
     const uint64_t dims[4] = {128, static_cast<uint64_t>(R), static_cast<uint64_t>(Hkv), static_cast<uint64_t>(Bq)};
@@ -284,8 +295,12 @@ int apb_decode_prefix_tc(const void* q, int Bq, const int* q_start, const int* q
   p.pages = pages;
   p.max_pages = max_pages;
   p.kv_len = kv_len;
-  p.out_o = out_o;
-  p.out_ml = out_ml;
+  p.level = level;
+  for (int l = 0; l < 3; ++l) {
+    // levels beyond n_levels alias the last valid buffer: a level id out of range can never reach a null pointer
+    p.out_o[l] = out_o[l < n_levels ? l : n_levels - 1];
+    p.out_ml[l] = out_ml[l < n_levels ? l : n_levels - 1];
+  }
   p.Hq = Hq;
   p.Hkv = Hkv;
   p.splits = splits;

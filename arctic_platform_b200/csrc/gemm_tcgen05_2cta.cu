@@ -113,7 +113,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
 
   const int tiles_m = (p.M + 255) / 256;
   const int tiles_n = (p.N + 255) / 256;
-  const int total_tiles = tiles_m * tiles_n;
+  const int mn_tiles = tiles_m * tiles_n;
+  const int total_tiles = mn_tiles * p.splits;   // work units: output tiles x K splits (split-K adds into C)
   const int k_blocks = (p.K + kPairBK - 1) / kPairBK;
 
   if (threadIdx.x == 0) {
@@ -142,7 +143,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const uint32_t tmem_base = *tmem_holder;
 
   // Tile order: 8 m-tiles of one n-band at a time, so pairs running together share B in L2.
-  auto decode = [&](int t, int& m0, int& n0) {
+  auto decode = [&](int unit, int& m0, int& n0, int& kb0, int& kb1) {
+    const int split = unit / mn_tiles;
+    const int t = unit - split * mn_tiles;
+    kb0 = static_cast<int>((static_cast<long long>(k_blocks) * split) / p.splits);
+    kb1 = static_cast<int>((static_cast<long long>(k_blocks) * (split + 1)) / p.splits);
     constexpr int G = 8;
     const int per_group = G * tiles_n;
     const int g = t / per_group;
@@ -160,11 +165,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       uint32_t phase = 0;
       bool ok = true;
       for (int t = pair; t < total_tiles && ok; t += num_pairs) {
-        int m0, n0;
-        decode(t, m0, n0);
+        int m0, n0, kb0, kb1;
+        decode(t, m0, n0, kb0, kb1);
         const int my_m = m0 + static_cast<int>(cta) * 128;
         const int my_n = n0 + static_cast<int>(cta) * 128;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kTimeoutEmpty)) {
             ok = false;
             break;
@@ -209,6 +214,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       int it = 0;
       bool ok = true;
       for (int t = pair; t < total_tiles && ok; t += num_pairs, ++it) {
+        int m0, n0, kb0, kb1;
+        decode(t, m0, n0, kb0, kb1);
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&tempty_bar[buf], acc_phase ^ 1, p.status, kTimeoutTmemEmpty)) {
@@ -217,7 +224,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buf * 256;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.status, kTimeoutFull)) {
             ok = false;
             break;
@@ -231,7 +238,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                                        : umma_smem_desc(sa + k * 32, 0, 1024);
             const uint64_t db = p.b_mn ? umma_smem_desc(sb + k * 2048, 64 * kPairBK * 2, 1024)
                                        : umma_smem_desc(sb + k * 32, 0, 1024);
-            umma_bf16_ss_pair(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16_ss_pair(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           // the stage is free in both CTAs once these MMAs have read it
           const uint32_t eb = smem_u32(&empty_bar[stage]);
@@ -255,8 +262,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     int it = 0;
     bool ok = true;
     for (int t = pair; t < total_tiles && ok; t += num_pairs, ++it) {
-      int m0, n0;
-      decode(t, m0, n0);
+      int m0, n0, kb0, kb1;
+      decode(t, m0, n0, kb0, kb1);
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&tfull_bar[buf], acc_phase, p.status, kTimeoutTmemFull)) {
@@ -299,7 +306,7 @@ extern "C" {
 
 // D[M,N] = alpha * op(A) * op(B)^T with the CTA-pair kernel.  Same operand conventions as apb_gemm_bf16
 // (a_mn / b_mn, leading dimensions multiples of 8, 16-byte aligned bases).  Epilogues: bf16 (+bias), f32,
-// f32 accumulate, SwiGLU.  No split-K, no tile table.  Returns kBadArgument for anything else so that the caller
+// f32 accumulate (split along K by the kernel's own choice when that fills the last wave), SwiGLU.  No tile table.  Returns kBadArgument for anything else so that the caller
 // can fall back to the one-CTA kernel.
 int apb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                        long long ldc, int a_mn, int b_mn, int epi, float alpha, const void* bias, void* C2,
@@ -340,6 +347,32 @@ int apb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int 
   p.epi = epi;
   p.splits = 1;
   p.C = C;
+  // Accumulating products (weight gradients: few output tiles, very long K) whose tile count leaves much of the
+  // last wave of pairs idle are cut along K; the parts add into C with red.add, which is what "+=" asks for.
+  if (epi == kEpiF32Accum) {
+    const int k_blocks = (K + kPairBK - 1) / kPairBK;
+    const long long tiles = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
+    const int pairs_hint = sm_count() / 2;
+    auto wave_eff = [&](int s) {
+      const long long units = tiles * s;
+      const long long waves = (units + pairs_hint - 1) / pairs_hint;
+      return static_cast<double>(units) / static_cast<double>(waves * pairs_hint);
+    };
+    int best = 1;
+    double best_eff = wave_eff(1);
+    for (int s = 2; s <= 4; ++s) {
+      if (k_blocks / s < 32) break;
+      const double e = wave_eff(s);
+      if (e > best_eff + 0.04) {
+        best = s;
+        best_eff = e;
+      }
+    }
+    if (best > 1) {
+      p.splits = best;
+      p.epi = kEpiF32Atomic;
+    }
+  }
   p.ldc = ldc;
   p.C2 = C2;
   p.ldc2 = ldc2;
@@ -376,7 +409,7 @@ int apb_gemm_bf16_pair(const void* A, const void* B, void* C, int M, int N, int 
     }
     resident_pairs[dev & 63] = n < sm_count() / 2 ? n : sm_count() / 2;
   }
-  const long long total = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
+  const long long total = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) * p.splits;
   const int max_pairs = resident_pairs[dev & 63];
   const int pairs = static_cast<int>(total < max_pairs ? total : max_pairs);
   cfg.gridDim = dim3(2 * pairs);

@@ -12,9 +12,11 @@ engine for the same contract -- ``generate(prompts, sampling_params)`` returning
   skinny problems), fused q/k-norm+RoPE, paged split-KV attention, SwiGLU epilogue, lm-head and a
   Gumbel-max sampling kernel; sequence lengths, positions and page tables live in device buffers
   that the graph reads, so the host only looks at finished flags every ``sync_interval`` steps;
-* with ``cascade=True`` decode attention is two passes merged by log-sum-exp: one pass per prompt
-  group over the shared prompt pages (KV read once for all rollouts of the group), one pass per
-  sequence over its private pages.
+* with ``cascade=True`` decode attention is a forest cascade (``ops/forest_attention.py``): prompts that
+  start with the same tokens share a HEADER node (found at admission from the token ids, page aligned,
+  prefilled and stored once), the rollouts of one prompt share the PROMPT node, and every sequence owns
+  its private pages; each node is attended once per step by all sequences below it and the levels are
+  merged by log-sum-exp.
 
 Pages for a sequence's maximum length are reserved at admission, which keeps the decode loop free
 of host-side allocation.
@@ -36,8 +38,10 @@ from ..ops import _lib, gemm, norm
 from ..ops.attention import AttnLayout, attention_fwd_cuda
 from ..utils.transfer_stats import to_device, to_host
 
+from ..ops.forest_attention import ForestNode, forest_decode_attention, plan_forest
+
 PAGE = 16
-MAX_NQ = 16
+MIN_HEADER_PAGES = 4      # a common prefix shorter than this many pages is not worth a node of its own
 
 
 _WARNED_KEYS: set = set()
@@ -121,9 +125,11 @@ class _Seq:
     sample: int                  # rollout index within the prompt
     prompt_len: int
     max_new: int
-    shared_pages: np.ndarray     # full prompt pages shared with the group
+    shared_pages: np.ndarray     # full prompt pages (beyond the header) shared with the prompt's rollouts
     private_pages: np.ndarray    # prompt tail + response pages owned by this sequence
     group: int
+    header_pages: np.ndarray = field(default_factory=lambda: np.zeros(0, dtype=np.int32))   # shared with other prompts
+    root: int = -1               # id of the header node, -1 = none
     out: List[int] = field(default_factory=list)
     lps: List[float] = field(default_factory=list)
     finish: Optional[str] = None
@@ -138,11 +144,9 @@ def _fn(name: str):
         vp, i, ll, f, u = c.c_void_p, c.c_int, c.c_longlong, c.c_float, c.c_uint
         _FN["kvw"] = _lib.declare("apb_kv_cache_write", [vp, ll, vp, ll, vp, vp, vp, i, i, i, vp])
         _FN["dec"] = _lib.declare("apb_paged_decode_partial", [vp, vp, vp, vp, i, vp, vp, vp, vp, vp, i, i, i, i, i, f, vp])
-        _FN["merge"] = _lib.declare("apb_decode_merge", [vp, vp, vp, i, vp, vp, i, i, i, vp])
+        _FN["merge"] = _lib.declare("apb_decode_merge", [vp, vp, vp, i, vp, vp, vp, i, i, i, vp])
         _FN["sample"] = _lib.declare("apb_sample", [vp, ll, vp, i, i, u, vp, vp, vp, vp])
         _FN["sample_f"] = _lib.declare("apb_sample_filtered", [vp, ll, vp, i, i, u, vp, vp, vp, vp, vp, vp, vp])
-        _FN["prefix_tc"] = _lib.declare("apb_decode_prefix_tc",
-                                        [vp, i, vp, vp, vp, i, vp, vp, vp, ll, vp, vp, i, i, i, i, i, f, vp])
         _FN["qkv_post"] = _lib.declare("apb_decode_qkv_post", [vp, ll, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, f, vp])
         _FN["swiglu32"] = _lib.declare("apb_swiglu_f32in", [vp, vp, ll, ll, vp])
         _FN["norm32"] = _lib.declare("apb_rmsnorm_fwd_f32in", [vp, vp, vp, vp, vp, i, i, f, f, vp])
@@ -211,11 +215,17 @@ class SamplerEngine:
         self.d_shared_tokens = torch.zeros(B, **i32)
         self.d_q_start = torch.arange(B, **i32)
         self.d_q_one = torch.ones(B, **i32)
-        # prefix groups (cascade): rows of one group are consecutive slots
-        self.d_g_start = torch.zeros(B, **i32)
-        self.d_g_count = torch.zeros(B, **i32)
-        self.d_g_pages = torch.zeros((B, self.max_pages), **i32)
-        self.d_g_len = torch.zeros(B, **i32)
+        # prefix forest (cascade): one table row per run of consecutive slots under a shared node; a sequence sits
+        # under at most two shared nodes (header, prompt), so 2 * B rows always suffice
+        self.n_node_rows = 2 * B
+        self.d_g_start = torch.zeros(self.n_node_rows, **i32)
+        self.d_g_count = torch.zeros(self.n_node_rows, **i32)
+        self.d_g_pages = torch.zeros((self.n_node_rows, self.max_pages), **i32)
+        self.d_g_len = torch.zeros(self.n_node_rows, **i32)
+        self.d_g_level = torch.zeros(self.n_node_rows, **i32)
+        self.d_row_mask = torch.full((B,), 1, **i32)
+        self.n_levels = 1            # shared levels in use: 1 = prompt nodes only, 2 = header + prompt nodes
+        self.forest_stats = {"shared_tokens": 0, "covered_tokens": 0}
         self.out_cap = 0
         self.d_out_tokens = None
         self.d_out_lps = None
@@ -227,11 +237,12 @@ class SamplerEngine:
         self.d_thr = torch.zeros(B, device=dev, dtype=torch.float32)
         self._filter_on = False
         self.splits = 4
-        self.n_groups = B            # groups in the prefix tables (a power-of-two bucket bounds the prefix grid)
+        self.n_groups = B            # rows in use in the node tables (a power-of-two bucket bounds the prefix grid)
         Hq, D = c.num_heads, c.head_dim
         f32 = dict(device=dev, dtype=torch.float32)
-        self.part_o = [torch.empty((B, Hq, self.splits, D), **f32) for _ in range(2)]
-        self.part_ml = [torch.empty((B, Hq, self.splits, 2), **f32) for _ in range(2)]
+        # partial results per source: header level, prompt level, private pass
+        self.part_o = [torch.empty((B, Hq, self.splits, D), **f32) for _ in range(3)]
+        self.part_ml = [torch.empty((B, Hq, self.splits, 2), **f32) for _ in range(3)]
         self.d_logits = torch.empty((B, c.vocab_size), **f32)
         # fp32 split-K accumulators of the two skinny projections (kept zero between uses by the norm kernel)
         self.acc_o = torch.zeros((B, c.hidden_size), **f32)
@@ -303,90 +314,56 @@ class SamplerEngine:
         act = norm.swiglu(fp8_linear(h2, *w["wgu"]))
         return fp8_linear(act, *w["wdown"]), stream
 
-    # ------------------------------------------------------------------ prefill
-    @torch.no_grad()
-    def _prefill(self, prompts: List[np.ndarray], page_lists: List[np.ndarray]) -> torch.Tensor:
-        """Runs the packed prompts through the model, fills their KV pages and returns the final-norm
-        hidden state of each prompt's last token ``[len(prompts), H]``."""
-        lens = np.array([len(p) for p in prompts], dtype=np.int64)
-        cu = np.concatenate([[0], np.cumsum(lens)])
-        T = int(cu[-1])
-        ids = to_device(torch.from_numpy(np.concatenate(prompts).astype(np.int64)), self.device)
-        pos_np = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
-        slots_np = np.concatenate([pl[np.arange(n) // PAGE] * PAGE + np.arange(n) % PAGE
-                                   for n, pl in zip(lens, page_lists)]).astype(np.int32)
-        positions = to_device(torch.from_numpy(pos_np), self.device)
-        slots = to_device(torch.from_numpy(slots_np), self.device)
-        layout = AttnLayout.from_cu_seqlens(cu)
-        scale = 1.0 / math.sqrt(self.cfg.head_dim)
-
-        def attn(li, q, k, v):
-            o, _ = attention_fwd_cuda(q, k, v.contiguous() if v.stride(1) != v.shape[2] else v, layout, scale,
-                                      need_lse=False)
-            return o
-
-        x = torch.nn.functional.embedding(ids, self.model.embed)
-        stream = None
-        for li in range(self.cfg.num_layers):
-            x, stream = self._block(li, x, stream, positions, slots, attn)
-        last = to_device(torch.from_numpy((cu[1:] - 1).astype(np.int64)), self.device)
-        xl = x.index_select(0, last)
-        sl = stream.index_select(0, last)
-        h, _ = norm.rmsnorm(xl, self.model.final_norm, self.cfg.rms_norm_eps, sl)
-        return h
-
     # ------------------------------------------------------------------ decode step
     @torch.no_grad()
     def _decode_attention(self, li: int, q: torch.Tensor, B: int) -> torch.Tensor:
         c = self.cfg
         scale = 1.0 / math.sqrt(c.head_dim)
-        s = _lib.stream_ptr()
-        dec, merge = _fn("dec"), _fn("merge")
         kc, vc = self.kcache[li], self.vcache[li]
-        out = torch.empty((B, c.num_heads, c.head_dim), device=self.device, dtype=torch.bfloat16)
         # per-sequence pass: one CTA per (sequence, kv head) already fills the GPU at rollout batch sizes, so the
         # KV range is split only when there are fewer CTAs than two waves of SMs
         seq_splits = max(1, min(self.splits, 296 // max(1, B * c.num_kv_heads)))
         if os.environ.get("APB_DECODE_SEQ_SPLITS"):               # tuning knob for A/B timing
             seq_splits = max(1, min(self.splits, int(os.environ["APB_DECODE_SEQ_SPLITS"])))
-        if self.cascade:
-            R = c.num_heads // c.num_kv_heads
-            G = min(B, self._group_bucket())          # groups are packed at the front of the tables
-            if self.prefix_on_tensor_cores and c.head_dim == 128 and R * MAX_NQ <= 128 and 128 % R == 0:
-                _lib.check(_fn("prefix_tc")(_lib.ptr(q), B, _lib.ptr(self.d_g_start), _lib.ptr(self.d_g_count),
-                                            _lib.ptr(self.d_g_pages), self.max_pages, _lib.ptr(self.d_g_len),
-                                            _lib.ptr(kc), _lib.ptr(vc), self.num_pages, _lib.ptr(self.part_o[0]),
-                                            _lib.ptr(self.part_ml[0]), G, c.num_heads, c.num_kv_heads, c.head_dim,
-                                            self.splits, scale, s), "decode_prefix_tc")
-            else:
-                _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_g_start), _lib.ptr(self.d_g_count),
-                               _lib.ptr(self.d_g_pages), self.max_pages, _lib.ptr(self.d_g_len), _lib.ptr(kc),
-                               _lib.ptr(vc), _lib.ptr(self.part_o[0]), _lib.ptr(self.part_ml[0]), G, c.num_heads,
-                               c.num_kv_heads, c.head_dim, self.splits, scale, s), "paged_decode(prefix)")
-            _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_q_start), _lib.ptr(self.d_active), _lib.ptr(self.d_priv_table),
-                           self.max_pages, _lib.ptr(self.d_priv_len), _lib.ptr(kc), _lib.ptr(vc),
-                           _lib.ptr(self.part_o[1]), _lib.ptr(self.part_ml[1]), B, c.num_heads, c.num_kv_heads,
-                           c.head_dim, seq_splits, scale, s), "paged_decode(private)")
-            n_src = 2
-            src_splits = [self.splits, seq_splits]
-        else:
-            _lib.check(dec(_lib.ptr(q), _lib.ptr(self.d_q_start), _lib.ptr(self.d_active), _lib.ptr(self.d_page_table),
-                           self.max_pages, _lib.ptr(self.d_len), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(self.part_o[0]),
-                           _lib.ptr(self.part_ml[0]), B, c.num_heads, c.num_kv_heads, c.head_dim, seq_splits, scale, s),
-                       "paged_decode")
-            n_src = 1
-            src_splits = [seq_splits]
-        o_ptrs = (ctypes.c_void_p * 4)(*[self.part_o[i].data_ptr() if i < n_src else 0 for i in range(4)])
-        ml_ptrs = (ctypes.c_void_p * 4)(*[self.part_ml[i].data_ptr() if i < n_src else 0 for i in range(4)])
-        sp = (ctypes.c_int * 4)(*[src_splits[i] if i < n_src else 0 for i in range(4)])
-        _lib.check(merge(o_ptrs, ml_ptrs, sp, n_src, _lib.ptr(out), None, B, c.num_heads, c.head_dim, s), "decode_merge")
+        out = torch.empty((B, c.num_heads, c.head_dim), device=self.device, dtype=torch.bfloat16)
+        if self._cascade_on():
+            return forest_decode_attention(q, kc, vc, self._forest_view(B), self.d_q_start, self.d_active,
+                                           self.d_priv_table, self.d_priv_len, self.part_o, self.part_ml, self.splits,
+                                           seq_splits, scale, out=out, n_nodes=self._group_bucket())
+        s = _lib.stream_ptr()
+        _lib.check(_fn("dec")(_lib.ptr(q), _lib.ptr(self.d_q_start), _lib.ptr(self.d_active), _lib.ptr(self.d_page_table),
+                              self.max_pages, _lib.ptr(self.d_len), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(self.part_o[0]),
+                              _lib.ptr(self.part_ml[0]), B, c.num_heads, c.num_kv_heads, c.head_dim, seq_splits, scale, s),
+                   "paged_decode")
+        o_ptrs = (ctypes.c_void_p * 4)(self.part_o[0].data_ptr(), 0, 0, 0)
+        ml_ptrs = (ctypes.c_void_p * 4)(self.part_ml[0].data_ptr(), 0, 0, 0)
+        sp = (ctypes.c_int * 4)(seq_splits, 0, 0, 0)
+        _lib.check(_fn("merge")(o_ptrs, ml_ptrs, sp, 1, None, _lib.ptr(out), None, B, c.num_heads, c.head_dim, s),
+                   "decode_merge")
         return out
 
+    def _cascade_on(self) -> bool:
+        """The shared-node pass runs on 128-row tensor-core tiles: head_dim 128 and a query-head group that divides
+        128.  Other shapes decode every sequence over its whole page table."""
+        c = self.cfg
+        R = c.num_heads // c.num_kv_heads
+        return bool(self.cascade and self.prefix_on_tensor_cores and c.head_dim == 128 and 128 % R == 0)
+
+    def _max_rows(self) -> int:
+        """Sequences per shared-node tile (their query heads of one KV head fill at most 128 rows)."""
+        return max(1, 128 // (self.cfg.num_heads // self.cfg.num_kv_heads))
+
+    def _forest_view(self, B: int):
+        from ..ops.forest_attention import ForestTables
+        return ForestTables(self.d_g_start, self.d_g_count, self.d_g_pages, self.d_g_len, self.d_g_level,
+                            self.d_row_mask, int(self.n_groups), int(self.n_levels),
+                            self.forest_stats["shared_tokens"], self.forest_stats["covered_tokens"])
+
     def _group_bucket(self) -> int:
-        """Number of prefix groups rounded up to a power of two: the grid of the shared-prefix pass (and the key of
-        the captured graph) changes only when the count crosses a bucket."""
+        """Rows of the node tables in use, rounded up to a power of two: the grid of the shared-node pass (and the
+        key of the captured graph) changes only when the count crosses a bucket."""
         n = max(1, int(self.n_groups))
-        return 1 << (n - 1).bit_length()
+        return min(self.n_node_rows, 1 << (n - 1).bit_length())
 
     @torch.no_grad()
     def _decode_step(self, B: int) -> None:
@@ -518,7 +495,7 @@ class SamplerEngine:
             for _ in range(n):
                 self._decode_step(B)
             return
-        key = (B, self._group_bucket() if self.cascade else 0, self._filter_on)
+        key = (B, self._group_bucket() if self._cascade_on() else 0, self.n_levels, self._filter_on)
         g = self._graphs.get(key)
         if g is None:
             # the first steps run eagerly (kernel attribute set-up, device binding, allocator warm-up)
@@ -571,42 +548,71 @@ class SamplerEngine:
             self.seed = int(sp.seed)
             self.d_step.zero_()            # a seeded call restarts the random stream
         results: List[Optional[dict]] = [None] * (len(prompts_np) * sp.n)
-        # work queue: one entry per prompt; a prompt's n rollouts are admitted together (one prefix group)
-        queue = list(range(len(prompts_np)))
+        # work queue: runs of prompts that start with the same (page-aligned) header; a run is admitted as a whole --
+        # its header is prefilled and stored once, every prompt's n rollouts form one prompt node below it
+        queue: List[Tuple[List[int], int]] = self._plan_runs(prompts_np) if self._cascade_on() else \
+            [([r], 0) for r in range(len(prompts_np))]
         slots_free = list(range(self.max_batch))
         live: Dict[int, _Seq] = {}
-        group_prompt_pages: Dict[int, np.ndarray] = {}
         group_members: Dict[int, List[int]] = {}
-        next_group = 0
+        root_members: Dict[int, List[int]] = {}
+        next_group = next_root = 0
         while queue or live:
-            # ---- admission: as many whole prompts as fit in slots and pages
-            admitted: List[Tuple[int, List[int]]] = []
-            while queue and len(slots_free) >= sp.n:
-                r = queue[0]
-                P = len(prompts_np[r])
-                n_full = P // PAGE
-                tail = P - n_full * PAGE
-                priv_pages = (tail + sp.max_tokens + PAGE - 1) // PAGE
-                need = n_full + sp.n * priv_pages
+            # ---- admission: as many whole runs as fit in slots and pages
+            admitted: List[dict] = []
+            while queue:
+                idxs, hlen = queue[0]
+                if len(idxs) > 1 and len(idxs) * sp.n > self.max_batch:
+                    # more sequences than the engine has slots: the run is cut in two (each half keeps the header)
+                    queue[0:1] = [(idxs[:len(idxs) // 2], hlen), (idxs[len(idxs) // 2:], hlen)]
+                    continue
+                if len(idxs) * sp.n > len(slots_free):
+                    break
+                n_hdr = hlen // PAGE
+                per_prompt = []
+                need = n_hdr
+                for r in idxs:
+                    P = len(prompts_np[r])
+                    n_full = (P - hlen) // PAGE
+                    priv_pages = (P % PAGE + sp.max_tokens + PAGE - 1) // PAGE
+                    per_prompt.append((r, P, n_full, priv_pages))
+                    need += n_full + sp.n * priv_pages
                 if self.pages.free_count() < need:
+                    if not live and not admitted and len(idxs) > 1:
+                        queue[0:1] = [(idxs[:len(idxs) // 2], hlen), (idxs[len(idxs) // 2:], hlen)]
+                        continue
                     break
                 queue.pop(0)
-                shared = self.pages.alloc(n_full)
-                gid = next_group
-                next_group += 1
-                group_prompt_pages[gid] = shared
-                mem = []
+                header = self.pages.alloc(n_hdr)
+                rid = -1
+                if n_hdr:
+                    rid = next_root
+                    next_root += 1
+                    root_members[rid] = []
+                run = {"root": rid, "header_len": hlen, "header_pages": header, "prompts": []}
                 slots_free.sort()
-                for si in range(sp.n):
-                    slot = slots_free.pop(0)
-                    priv = self.pages.alloc(priv_pages)
-                    if si > 0:
-                        self.pages.retain(shared)
-                    live[slot] = _Seq(req=r, sample=si, prompt_len=P, max_new=sp.max_tokens, shared_pages=shared,
-                                      private_pages=priv, group=gid)
-                    mem.append(slot)
-                group_members[gid] = mem
-                admitted.append((gid, mem))
+                first_of_run = True
+                for r, P, n_full, priv_pages in per_prompt:
+                    shared = self.pages.alloc(n_full)
+                    gid = next_group
+                    next_group += 1
+                    mem = []
+                    for si in range(sp.n):
+                        slot = slots_free.pop(0)
+                        priv = self.pages.alloc(priv_pages)
+                        if si > 0:
+                            self.pages.retain(shared)
+                        if not first_of_run:
+                            self.pages.retain(header)          # every sequence below the header holds a reference
+                        first_of_run = False
+                        live[slot] = _Seq(req=r, sample=si, prompt_len=P, max_new=sp.max_tokens, shared_pages=shared,
+                                          private_pages=priv, group=gid, header_pages=header, root=rid)
+                        mem.append(slot)
+                        if rid >= 0:
+                            root_members[rid].append(slot)
+                    group_members[gid] = mem
+                    run["prompts"].append((gid, mem))
+                admitted.append(run)
             if not admitted and not live:
                 raise RuntimeError("KV cache too small for a single prompt group; raise kv_cache_tokens")
             if admitted:
@@ -616,7 +622,7 @@ class SamplerEngine:
             bucket = next((b for b in (8, 16, 32, 64, 128, 256, 512, 1024) if b >= B), self.max_batch)
             bucket = min(bucket, self.max_batch)
             if B > 0:
-                self._set_groups(group_members, live)
+                self._set_groups(group_members, root_members, live)
                 self._run_steps(bucket, self.sync_interval)
             # ---- harvest
             fin = to_host(self.d_finished[:max(B, 1)]).numpy() if B else np.zeros(0, dtype=np.int32)
@@ -635,10 +641,14 @@ class SamplerEngine:
                         "prompt_len": sq.prompt_len, "prompt_index": sq.req, "text": None}
                     self.pages.release(sq.private_pages)
                     self.pages.release(sq.shared_pages)
+                    self.pages.release(sq.header_pages)
                     group_members[sq.group].remove(s)
                     if not group_members[sq.group]:
                         del group_members[sq.group]
-                        del group_prompt_pages[sq.group]
+                    if sq.root >= 0:
+                        root_members[sq.root].remove(s)
+                        if not root_members[sq.root]:
+                            del root_members[sq.root]
                     slots_free.append(s)
                     self.d_finished[s] = 0
                     self.d_len[s] = 0
@@ -646,31 +656,112 @@ class SamplerEngine:
         return results  # type: ignore[return-value]
 
     # ------------------------------------------------------------------ admission
+    def _plan_runs(self, prompts_np: List[np.ndarray]) -> List[Tuple[List[int], int]]:
+        """Prefix-tree discovery from the token ids: prompts are sorted so that common prefixes become neighbours, and
+        neighbours whose common prefix covers at least ``MIN_HEADER_PAGES`` pages form a run ``(prompt indices,
+        header length)``.  The header length is a multiple of the page size and leaves every prompt of the run at
+        least one token of its own (the position its first sampled token is predicted from).  Prompts without such
+        a neighbour are runs of one with header length 0.  Runs come back in order of their first prompt."""
+        n = len(prompts_np)
+        order = sorted(range(n), key=lambda i: prompts_np[i].tobytes())
+
+        def lcp(a: np.ndarray, b: np.ndarray) -> int:
+            m = min(len(a), len(b))
+            neq = np.flatnonzero(a[:m] != b[:m])
+            return int(neq[0]) if len(neq) else m
+
+        def header_of(common: int, shortest: int) -> int:
+            return (min(common, shortest - 1) // PAGE) * PAGE
+
+        runs: List[Tuple[List[int], int]] = []
+        cur, common, shortest = [order[0]] if n else [], 1 << 60, len(prompts_np[order[0]]) if n else 0
+        for k in range(1, n):
+            i, prev = order[k], order[k - 1]
+            c2 = min(common, lcp(prompts_np[prev], prompts_np[i]))
+            s2 = min(shortest, len(prompts_np[i]))
+            if header_of(c2, s2) >= MIN_HEADER_PAGES * PAGE:
+                cur.append(i)
+                common, shortest = c2, s2
+            else:
+                runs.append((cur, header_of(common, shortest) if len(cur) > 1 else 0))
+                cur, common, shortest = [i], 1 << 60, len(prompts_np[i])
+        if cur:
+            runs.append((cur, header_of(common, shortest) if len(cur) > 1 else 0))
+        runs = [(sorted(idxs), h) for idxs, h in runs]
+        runs.sort(key=lambda r: r[0][0])
+        return runs
+
     @torch.no_grad()
-    def _admit(self, admitted, prompts_np, live: Dict[int, _Seq], sp: SamplingParams,
+    def _prefill_runs(self, runs: List[dict], prompts_np, live: Dict[int, _Seq]) -> torch.Tensor:
+        """Packs the admitted runs -- every header once, then every prompt's remainder with the header as its fully
+        visible prefix -- runs the model over them, fills the KV pages and returns the final-norm hidden state of
+        every prompt's last token, in the order of ``runs[*]["prompts"]``."""
+        toks, pos, slots, segs, last = [], [], [], [], []
+        t = 0
+
+        def put(tokens: np.ndarray, p0: int, pages: np.ndarray):
+            nonlocal t
+            n = len(tokens)
+            toks.append(tokens)
+            ar = np.arange(n)
+            pos.append((p0 + ar).astype(np.int32))
+            slots.append((pages[ar // PAGE] * PAGE + ar % PAGE).astype(np.int32))
+            t += n
+
+        for run in runs:
+            hlen, hstart = run["header_len"], t
+            first = live[run["prompts"][0][1][0]]
+            if hlen:
+                put(prompts_np[first.req][:hlen], 0, run["header_pages"].astype(np.int64))
+                segs.append((hstart, hlen, 0, 0, hstart, hlen))
+            for _gid, mem in run["prompts"]:
+                s0 = live[mem[0]]
+                rem = prompts_np[s0.req][hlen:]
+                tail = s0.prompt_len % PAGE
+                pages = s0.shared_pages if tail == 0 else np.concatenate([s0.shared_pages, s0.private_pages[:1]])
+                q0 = t
+                put(rem, hlen, pages.astype(np.int64))
+                segs.append((q0, len(rem), hstart if hlen else 0, hlen, q0, len(rem)))
+                last.append(t - 1)
+        ids = to_device(torch.from_numpy(np.concatenate(toks).astype(np.int64)), self.device)
+        positions = to_device(torch.from_numpy(np.concatenate(pos)), self.device)
+        slot_t = to_device(torch.from_numpy(np.concatenate(slots)), self.device)
+        layout = AttnLayout(np.asarray(segs, dtype=np.int32), t)
+        scale = 1.0 / math.sqrt(self.cfg.head_dim)
+
+        def attn(li, q, k, v):
+            o, _ = attention_fwd_cuda(q, k, v.contiguous() if v.stride(1) != v.shape[2] else v, layout, scale,
+                                      need_lse=False)
+            return o
+
+        x = torch.nn.functional.embedding(ids, self.model.embed)
+        stream = None
+        for li in range(self.cfg.num_layers):
+            x, stream = self._block(li, x, stream, positions, slot_t, attn)
+        last_t = to_device(torch.from_numpy(np.asarray(last, dtype=np.int64)), self.device)
+        h, _ = norm.rmsnorm(x.index_select(0, last_t), self.model.final_norm, self.cfg.rms_norm_eps,
+                            stream.index_select(0, last_t))
+        return h
+
+    @torch.no_grad()
+    def _admit(self, admitted: List[dict], prompts_np, live: Dict[int, _Seq], sp: SamplingParams,
                token_budget: int = 32768) -> None:
-        """Prefills each admitted prompt ONCE, copies its partial tail page to every rollout's private
-        page, samples the first token of every rollout and initialises the slot state."""
+        """Prefills each admitted header and prompt ONCE, copies a prompt's partial tail page to every rollout's
+        private page, samples the first token of every rollout and initialises the slot state."""
         c = self.cfg
-        # batches of prompts under the token budget
-        batches: List[List[Tuple[int, List[int]]]] = [[]]
+        # batches of whole runs under the token budget (a prompt attends to its header inside one packed batch)
+        batches: List[List[dict]] = [[]]
         tok = 0
-        for gid, mem in admitted:
-            P = live[mem[0]].prompt_len
-            if batches[-1] and tok + P > token_budget:
+        for run in admitted:
+            n_tok = run["header_len"] + sum(live[mem[0]].prompt_len - run["header_len"] for _g, mem in run["prompts"])
+            if batches[-1] and tok + n_tok > token_budget:
                 batches.append([])
                 tok = 0
-            batches[-1].append((gid, mem))
-            tok += P
-        for batch in batches:
-            prompts, page_lists = [], []
-            for gid, mem in batch:
-                s0 = live[mem[0]]
-                tail = s0.prompt_len % PAGE
-                pl = s0.shared_pages if tail == 0 else np.concatenate([s0.shared_pages, s0.private_pages[:1]])
-                prompts.append(prompts_np[s0.req])
-                page_lists.append(pl.astype(np.int64))
-            h = self._prefill(prompts, page_lists)
+            batches[-1].append(run)
+            tok += n_tok
+        for runs in batches:
+            batch = [pm for run in runs for pm in run["prompts"]]
+            h = self._prefill_runs(runs, prompts_np, live)
             # tail page copies for rollouts 1..n-1
             src, dst = [], []
             for gid, mem in batch:
@@ -725,46 +816,47 @@ class SamplerEngine:
             sh = np.zeros(n, dtype=np.int32)
             for i, s in enumerate(slots):
                 sq = live[s]
-                allp = np.concatenate([sq.shared_pages, sq.private_pages])
+                allp = np.concatenate([sq.header_pages, sq.shared_pages, sq.private_pages])
                 pt[i, :len(allp)] = allp
                 pv[i, :len(sq.private_pages)] = sq.private_pages
-                sh[i] = len(sq.shared_pages) * PAGE
+                sh[i] = (len(sq.header_pages) + len(sq.shared_pages)) * PAGE
                 plen[i] = sq.prompt_len - sh[i] + 1
             self.d_page_table[st] = to_device(torch.from_numpy(pt), self.device)
             self.d_priv_table[st] = to_device(torch.from_numpy(pv), self.device)
             self.d_priv_len[st] = to_device(torch.from_numpy(plen), self.device)
             self.d_shared_tokens[st] = to_device(torch.from_numpy(sh), self.device)
 
-    def _set_groups(self, group_members: Dict[int, List[int]], live: Dict[int, _Seq]) -> None:
-        """Prefix-forest tables for cascade decode: runs of consecutive slots (at most 16) that share
-        one prompt become one query group over the prompt's shared pages."""
-        if not self.cascade:
+    def _set_groups(self, group_members: Dict[int, List[int]], root_members: Dict[int, List[int]],
+                    live: Dict[int, _Seq]) -> None:
+        """Node tables of the prefix forest for cascade decode: header nodes (level 0, when any is live) over all
+        sequences of their prompts, prompt nodes over the prompt's rollouts; runs of consecutive slots (one
+        tensor-core tile each) become table rows."""
+        if not self._cascade_on():
             return
-        B = self.max_batch
-        g_start = np.zeros(B, dtype=np.int32)
-        g_count = np.zeros(B, dtype=np.int32)
-        g_len = np.zeros(B, dtype=np.int32)
-        g_pages = np.zeros((B, self.max_pages), dtype=np.int32)
-        k = 0
+        nodes: List[ForestNode] = []
+        two = bool(root_members)
+        for rid, mem in root_members.items():
+            sq = live[mem[0]]
+            nodes.append(ForestNode(0, mem, sq.header_pages, len(sq.header_pages) * PAGE))
         for gid, mem in group_members.items():
-            mem = sorted(mem)
-            shared = live[mem[0]].shared_pages
-            i = 0
-            while i < len(mem):
-                j = i
-                while j + 1 < len(mem) and mem[j + 1] == mem[j] + 1 and j + 1 - i < MAX_NQ:
-                    j += 1
-                g_start[k] = mem[i]
-                g_count[k] = j - i + 1
-                g_len[k] = len(shared) * PAGE
-                g_pages[k, :len(shared)] = shared
-                k += 1
-                i = j + 1
-        self.n_groups = k
-        self.d_g_start.copy_(torch.from_numpy(g_start))
-        self.d_g_count.copy_(torch.from_numpy(g_count))
-        self.d_g_len.copy_(torch.from_numpy(g_len))
-        self.d_g_pages.copy_(torch.from_numpy(g_pages))
+            sq = live[mem[0]]
+            nodes.append(ForestNode(1 if two else 0, mem, sq.shared_pages, len(sq.shared_pages) * PAGE))
+        qs, qc, pg, ln, lv, mask, G, nl, shared, covered = plan_forest(
+            nodes, self.max_batch, self.max_pages, self._max_rows(), n_levels=2 if two else 1)
+        if G > self.n_node_rows:
+            raise RuntimeError(f"prefix forest needs {G} table rows, the engine holds {self.n_node_rows}")
+        self.n_groups, self.n_levels = G, nl
+        self.forest_stats = {"shared_tokens": shared, "covered_tokens": covered}
+
+        def fill(dst: torch.Tensor, arr: np.ndarray):
+            buf = np.zeros(tuple(dst.shape), dtype=arr.dtype)
+            buf[:len(arr)] = arr[:len(buf)]
+            dst.copy_(to_device(torch.from_numpy(buf), self.device))
+
+        for dst, arr in ((self.d_g_start, qs), (self.d_g_count, qc), (self.d_g_len, ln), (self.d_g_level, lv),
+                         (self.d_g_pages, pg)):
+            fill(dst, arr)
+        self.d_row_mask.copy_(to_device(torch.from_numpy(mask), self.device))
 
     # ------------------------------------------------------------------ weights / sleep / wake
     @torch.no_grad()

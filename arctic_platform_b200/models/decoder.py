@@ -254,9 +254,15 @@ class DecoderLM(nn.Module):
 
     # ------------------------------------------------------------------ init
     @torch.no_grad()
-    def init_weights(self, seed: int = 0, std: float = 0.02) -> "DecoderLM":
+    def init_weights(self, seed: int = 0, std: float = 0.02, on_device: Optional[bool] = None) -> "DecoderLM":
         """Deterministic normal(0, std) init keyed by parameter name, so the values do not depend on
-        how the model is later sharded (norm weights are ones)."""
+        how the model is later sharded (norm weights are ones).  ``on_device``: draw the numbers with the device's
+        own generator instead of the host's (same values on every GPU for one name and seed, different from the
+        host's stream).  Default: the device for CUDA models of more than 2^28 parameters -- drawing billions of
+        numbers on the host takes tens of seconds per model copy, and a colocated job builds three of them."""
+        if on_device is None:
+            first = next(self.parameters())
+            on_device = first.is_cuda and sum(p.numel() for p in self.parameters()) > (1 << 28)
         for name, p in self.named_parameters():
             if name.endswith("A_log") or name.endswith("dt_bias"):
                 p.copy_(torch.linspace(-1.0, 1.0, p.numel()).to(p.dtype))      # decays spread over the heads
@@ -265,13 +271,14 @@ class DecoderLM(nn.Module):
                 is_plain = name.endswith("norm_w") or not self.cfg.norm_one_plus
                 p.fill_(1.0 if is_plain else 0.0)                              # (1+w) norms store w - 1
                 continue
-            g = torch.Generator(device="cpu")
+            src = p.device if (on_device and p.is_cuda) else torch.device("cpu")
+            g = torch.Generator(device=src)
             g.manual_seed((hash_name(name) + seed) % (2 ** 31))
             chunk = 1 << 24
             flat = p.data.view(-1)
             for s in range(0, flat.numel(), chunk):
                 n = min(chunk, flat.numel() - s)
-                flat[s:s + n].copy_((torch.randn(n, generator=g, dtype=torch.float32) * std).to(p.dtype))
+                flat[s:s + n].copy_((torch.randn(n, generator=g, dtype=torch.float32, device=src) * std).to(p.dtype))
         return self
 
     def rope(self, device) -> Tuple[torch.Tensor, torch.Tensor]:

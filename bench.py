@@ -116,6 +116,7 @@ class ClockSampler(threading.Thread):
 
 
 def main():
+    t_start = time.perf_counter()
     args = parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -256,8 +257,12 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return [float(v) for v in t.tolist()]
 
+    if rank == 0:
+        print(f"[bench] engines ready after {time.perf_counter() - t_start:.1f} s", file=sys.stderr, flush=True)
     for _ in range(args.warmup):
         step_client()
+    if rank == 0:
+        print(f"[bench] warm-up done after {time.perf_counter() - t_start:.1f} s", file=sys.stderr, flush=True)
     marks.clear()
     sampler = ClockSampler(local_rank)
     sampler.start()

@@ -166,11 +166,24 @@ def test_cta_pair_kernel_all_operand_layouts(M, N, K):
     _pair(a, bt, out32, M, N, K, b_mn=True, epi=1)
     _lib.check_status("pair nn")
     _close(out32, ref, K)
-    at = a.t().contiguous()                                   # [K, M]: the weight-gradient form, accumulated
-    acc = torch.full((M, N), 2.0, device="cuda", dtype=torch.float32)
+    if M % 8 == 0:                                            # A stored [K, M]: rows of M elements, 16-byte aligned
+        at = a.t().contiguous()                               # the weight-gradient form, accumulated
+        acc = torch.full((M, N), 2.0, device="cuda", dtype=torch.float32)
+        _pair(at, bt, acc, M, N, K, a_mn=True, b_mn=True, epi=3)
+        _lib.check_status("pair tn acc")
+        _close(acc, ref + 2.0, K)
+
+
+def test_cta_pair_kernel_splits_long_k_accumulation():
+    """A weight-gradient shaped product (few output tiles, K = tokens) is cut along K by the kernel; the parts add
+    into the fp32 accumulator."""
+    from arctic_platform_b200.ops import _lib
+    M, N, K = 2560, 4096, 16384                               # 160 tiles: 2.2 waves of pairs without a split
+    at, bt = _rand((K, M)), _rand((K, N))
+    acc = torch.full((M, N), -1.0, device="cuda", dtype=torch.float32)
     _pair(at, bt, acc, M, N, K, a_mn=True, b_mn=True, epi=3)
-    _lib.check_status("pair tn acc")
-    _close(acc, ref + 2.0, K)
+    _lib.check_status("pair tn split")
+    _close(acc, at.float().t() @ bt.float() - 1.0, K)
 
 
 def test_cta_pair_kernel_swiglu_and_many_tiles_per_pair():

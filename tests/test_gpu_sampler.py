@@ -111,7 +111,7 @@ def test_paged_decode_mma_kernel_matches_reference_and_scalar_kernel(Hq, Hkv, nq
         o_ptrs = (ctypes.c_void_p * 4)(po.data_ptr(), 0, 0, 0)
         ml_ptrs = (ctypes.c_void_p * 4)(pml.data_ptr(), 0, 0, 0)
         sp = (ctypes.c_int * 4)(splits, 0, 0, 0)
-        _lib.check(_fn("merge")(o_ptrs, ml_ptrs, sp, 1, _lib.ptr(out), _lib.ptr(lse), Bq, Hq, D, _lib.stream_ptr()), "merge")
+        _lib.check(_fn("merge")(o_ptrs, ml_ptrs, sp, 1, None, _lib.ptr(out), _lib.ptr(lse), Bq, Hq, D, _lib.stream_ptr()), "merge")
         _lib.check_status("paged decode")
         return out.float(), lse
 
