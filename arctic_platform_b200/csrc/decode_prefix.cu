@@ -91,19 +91,24 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-  // chained launch: barriers and TMEM are set up; q and the newest KV rows come from the previous kernels
+  // chained launch: barriers and TMEM are set up.  The pages of a shared node are never written while its
+  // sequences decode (new tokens go to private pages), so the first ring-full of K/V tiles is requested BEFORE
+  // the wait for the previous kernel; q, which that kernel produces, is loaded after it.
   pdl_launch_dependents();
-  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0 && n_blocks > 0) {
-      mbar_expect_tx(q_full, kDpTile);
-      for (int c = 0; c < 2; ++c) tma_load_4d(smem_q + c * 16384, &tma_q, q_full, c * 64, 0, kvh, qs);
       bool ok = true;
+      const int early = min(kDpSlots, 2 * n_blocks);
       for (int n = 0; n < 2 * n_blocks && ok; ++n) {
+        if (n == early) {
+          pdl_wait();
+          mbar_expect_tx(q_full, kDpTile);
+          for (int c = 0; c < 2; ++c) tma_load_4d(smem_q + c * 16384, &tma_q, q_full, c * 64, 0, kvh, qs);
+        }
         const int slot = n % kDpSlots;
         const uint32_t phase = (n / kDpSlots) & 1;
-        if (!mbar_wait(&kv_empty[slot], phase ^ 1, p.status, kTimeoutEmpty)) {
+        if (n >= early && !mbar_wait(&kv_empty[slot], phase ^ 1, p.status, kTimeoutEmpty)) {
           ok = false;
           break;
         }
@@ -119,13 +124,21 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           for (int c = 0; c < 2; ++c) tma_load_2d(dst + c * 16384 + pg * 2048, map, &kv_full[slot], c * 64, row);
         }
       }
+      if (2 * n_blocks <= early) {         // every tile fitted into the first ring-full: q is still to come
+        pdl_wait();
+        mbar_expect_tx(q_full, kDpTile);
+        for (int c = 0; c < 2; ++c) tma_load_4d(smem_q + c * 16384, &tma_q, q_full, c * 64, 0, kvh, qs);
+      }
       if (!ok) {
         const uint64_t t0 = global_timer_ns();
         while (global_timer_ns() - t0 < 100000ull) {
         }
       }
+    } else {
+      pdl_wait();
     }
   } else if (warp == 1) {
+    pdl_wait();
     if (lane == 0 && n_blocks > 0) {
       const uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
       const uint32_t idesc_o = umma_idesc_bf16(128, D, 0, 1);
@@ -163,6 +176,7 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       }
     }
   } else {
+    pdl_wait();                    // the partial buffers may still be read by the previous step's merge
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;

@@ -60,7 +60,10 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x))
 
 // One output row, 32 consecutive accumulator columns starting at `col0` (raw fp32 bits in `r`).  Covers every
 // epilogue except the two lm-head ones, which keep running state across the chunks of a tile.
-__device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, int row, int col0, const uint32_t (&r)[32]) {
+// `ncols` (32, or 16 for the last chunk of a tile width that is not a multiple of 32) clips the chunk at the tile
+// edge; columns at or beyond p.N are never written either.
+__device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, int row, int col0, const uint32_t (&r)[32],
+                                                 int ncols = 32) {
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
@@ -73,7 +76,7 @@ __device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, int row, i
     __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      if (col0 + q * 8 < p.N) {
+      if (q * 8 < ncols && col0 + q * 8 < p.N) {
         uint4 o;
         o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
         o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
@@ -88,7 +91,7 @@ __device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, int row, i
         static_cast<__nv_bfloat16*>(p.C2) + static_cast<long long>(row) * p.ldc2 + (col0 >> 1);
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
-      if (col0 + q * 16 < p.N) {
+      if (q * 16 < ncols && col0 + q * 16 < p.N) {
         float a[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) a[j] = silu_f(v[q * 16 + 2 * j]) * v[q * 16 + 2 * j + 1];
@@ -104,7 +107,7 @@ __device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, int row, i
     float* dst = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      if (col0 + q * 4 < p.N) {
+      if (q * 4 < ncols && col0 + q * 4 < p.N) {
         float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
         if (p.epi == kEpiF32Accum) {
           const float4 old = *reinterpret_cast<const float4*>(dst + q * 4);
@@ -122,7 +125,7 @@ __device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, int row, i
                  static_cast<long long>(row - owner * p.rows_per_rank) * p.ldc + col0;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      if (col0 + q * 4 < p.N)
+      if (q * 4 < ncols && col0 + q * 4 < p.N)
         atomicAdd(reinterpret_cast<float4*>(dst + q * 4),
                   make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
     }
@@ -134,7 +137,7 @@ __device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, int row, i
       __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.c_peers[to.x]) + static_cast<long long>(to.y) * p.ldc + col0;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        if (col0 + q * 8 < p.N) {
+        if (q * 8 < ncols && col0 + q * 8 < p.N) {
           uint4 o;
           o.x = pack_bf16x2(v[q * 8 + 0], v[q * 8 + 1]);
           o.y = pack_bf16x2(v[q * 8 + 2], v[q * 8 + 3]);
@@ -148,7 +151,7 @@ __device__ __forceinline__ void gemm_store_chunk(const GemmParams& p, int row, i
     float* dst = static_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      if (col0 + q * 4 < p.N)
+      if (q * 4 < ncols && col0 + q * 4 < p.N)
         atomicAdd(reinterpret_cast<float4*>(dst + q * 4),
                   make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
     }

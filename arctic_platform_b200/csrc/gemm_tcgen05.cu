@@ -32,9 +32,13 @@ struct GemmCfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = ST ? ST : (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+  // deepest ring that fits: widths 144 and 208 (one wave of SMs for column counts such as 19456 or 151936 that
+  // 128- or 256-wide tiles cut into "one wave and a bit") are 16-column multiples between the power-of-two widths
+  static constexpr int kStages = ST ? ST : (BN == 256) ? 4 : (BN > 144) ? 5 : (BN > 64) ? 6 : 8;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
-  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kTmemCols = BN <= 64 ? 128 : (BN <= 128 ? 256 : 512);   // a power of two, two accumulators
+  static constexpr int kAccStride = kTmemCols / 2;
+  static constexpr int kChunks = (BN + 31) / 32;                                // 32-column epilogue chunks
 };
 
 template <int BN, int ST = 0>
@@ -209,7 +213,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
           break;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * BN;
+        const uint32_t tmem_d = tmem_base + buf * Cfg::kAccStride;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, p.status, kTimeoutFull)) {
             ok = false;
@@ -253,7 +257,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < m_end;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * Cfg::kAccStride;
       if (p.epi == kEpiLogprobPartial) {
         // BN == 128 here: one partial record per row and tile
         const float rs = p.alpha * ((p.row_scale && row_ok) ? p.row_scale[row] : 1.f);
@@ -341,14 +345,25 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
         continue;
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = 0; c < Cfg::kChunks; ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
+        const int ncols = min(32, BN - c * 32);   // 16 in the last chunk of a width that is not a multiple of 32
+        if (BN % 32 != 0 && ncols == 16) {
+          uint32_t h[16];
+          tmem_ld_32x16(taddr + c * 32, h);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = h[j];
+#pragma unroll
+          for (int j = 16; j < 32; ++j) r[j] = 0u;
+        } else {
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+        }
         if (!row_ok) continue;
-        gemm_store_chunk(p, row, col0, r);
+        gemm_store_chunk(p, row, col0, r, ncols);
       }
       tc_fence_before();
       __syncwarp();
@@ -493,7 +508,7 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   // of pairs, automatic tile choice, no grid cap.  APB_GEMM_PAIR=0 keeps everything on the one-CTA kernel.
   if (bn == 0 && splits == 1 && !tile_map && max_ctas <= 0 && pair_kernel_enabled() &&
       (epi == kEpiBf16 || epi == kEpiF32 || epi == kEpiF32Accum || epi == kEpiSwiGLU) &&
-      !(epi == kEpiBf16 && !C) &&
+      !(epi == kEpiBf16 && !C) && M >= 512 &&
       static_cast<long long>((M + 255) / 256) * ((N + 255) / 256) >= sm_count() / 2)
     return apb_gemm_bf16_pair(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, alpha, bias, C2, ldc2, stream);
   if (bn == 0) {
@@ -504,12 +519,30 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
     // skinny problems (decode): narrower tiles put more SMs on the weight stream
     if (bn == 128 && t128 * 10 < sm_count() * 7 && N >= 128) bn = 64;
     if (tile_map) bn = 128;
+    // one row tile (decode): the width that covers N in the fewest waves of SMs, then the fewest idle SMs
+    if (!tile_map && tm == 1 && splits == 1 && !b_mn && N >= 1024 && epi != kEpiLogprobPartial && epi != kEpiDlogits) {
+      const int cand[5] = {256, 208, 144, 128, 64};
+      long long best_cost = -1;
+      for (int i = 0; i < 5; ++i) {
+        const long long tiles = (N + cand[i] - 1) / cand[i];
+        const long long waves = (tiles + sm_count() - 1) / sm_count();
+        const long long cost = waves * cand[i];          // columns streamed by the busiest SM
+        if (best_cost < 0 || cost < best_cost) {
+          best_cost = cost;
+          bn = cand[i];
+        }
+      }
+    }
   }
   // bn = 1000 + width: the two-CTAs-per-SM variant (widths 64 and 128)
   const bool x2 = bn > 1000;
   if (x2) bn -= 1000;
-  if (bn != 64 && bn != 128 && bn != 256) return kBadArgument;
-  if (x2 && bn == 256) return kBadArgument;
+  if (bn != 64 && bn != 128 && bn != 144 && bn != 208 && bn != 256) return kBadArgument;
+  if (x2 && bn != 64 && bn != 128) return kBadArgument;
+  // the in-between widths exist for skinny NT products (decode); they do not take the transposed-B layout (its
+  // 64-column chunks), the tile table or the lm-head epilogues
+  if ((bn == 144 || bn == 208) && (b_mn || tile_map || epi == kEpiLogprobPartial || epi == kEpiDlogits))
+    return kBadArgument;
 
   CUtensorMap ta, tb;
   int rc;
@@ -549,6 +582,8 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   p.chained = chained_launch_on() ? 1 : 0;
   if (x2) return bn == 64 ? launch_gemm_x2<64>(ta, tb, p, stream) : launch_gemm_x2<128>(ta, tb, p, stream);
   if (bn == 64) return launch_gemm<64>(ta, tb, p, max_ctas, stream);
+  if (bn == 144) return launch_gemm<144>(ta, tb, p, max_ctas, stream);
+  if (bn == 208) return launch_gemm<208>(ta, tb, p, max_ctas, stream);
   return bn == 256 ? launch_gemm<256>(ta, tb, p, max_ctas, stream) : launch_gemm<128>(ta, tb, p, max_ctas, stream);
 }
 }
@@ -814,10 +849,15 @@ int apb_gemm_ag(void* const* a_ptrs, int world, int rows, const void* B, void* C
 // row into the fp32 accumulator of the rank that owns it (acc_ptrs[r]: [M/world, N] fp32, zero on entry),
 // straight from the GEMM epilogue over the NVLink peer mappings.  Follow with apb_tp_finalize.
 int apb_gemm_rs(const void* A, const void* B, void* const* acc_ptrs, int world, int M, int N, int K, long long lda,
-                long long ldb, long long ld_acc, int bn, cudaStream_t stream) {
+                long long ldb, long long ld_acc, int bn, int splits, cudaStream_t stream) {
   using namespace apb;
   if (world < 1 || world > 8 || M % world || (lda % 8) || (ldb % 8) || (ld_acc % 4) || (N % 8)) return kBadArgument;
   if (bn == 0) bn = 128;
+  // the epilogue adds into the owners' accumulators anyway, so the product may also be cut along K: skinny
+  // (decode) problems then put every SM on the weight stream
+  const int k_blocks = (K + kBK - 1) / kBK;
+  if (splits < 1) splits = 1;
+  if (splits > k_blocks) splits = k_blocks;
   CUtensorMap ta, tb;
   int rc = make_tmap_2d(&ta, A, 2, M, K, lda, 64, kBM);
   if (rc) return 1000 + rc;
@@ -828,8 +868,9 @@ int apb_gemm_rs(const void* A, const void* B, void* const* acc_ptrs, int world, 
   p.N = N;
   p.K = K;
   p.epi = kEpiF32AtomicPeer;
-  p.splits = 1;
+  p.splits = splits;
   p.ldc = ld_acc;
+  p.chained = chained_launch_on() ? 1 : 0;
   p.alpha = 1.f;
   p.status = status_device_ptr();
   p.rows_per_rank = M / world;

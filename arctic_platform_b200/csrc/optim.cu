@@ -24,6 +24,7 @@
 #include "common.cuh"
 #include "host_utils.cuh"
 #include "peer.cuh"
+#include <string.h>
 
 namespace apb {
 
@@ -516,6 +517,191 @@ int apb_quant_fp8_block128(const void* w, long long ldw, int rows, int cols, voi
   quant_fp8_block128_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(w), ldw, rows, cols,
                                                  static_cast<uint8_t*>(q), ldq, scales, (cols + 127) / 128);
   return static_cast<int>(cudaGetLastError());
+}
+}
+
+// ---------------------------------------------------------------------------
+// Table-driven weight synchronisation: gather + tensor-parallel reshard + cast / fp8 requantisation in one pass
+// ---------------------------------------------------------------------------
+namespace apb {
+
+// One rectangular slice of one trainer parameter and where it goes in the sampler.  The source parameter is a
+// row-major matrix (src_ld elements per row; a vector is one row) that lives at element `src_elem` of the full
+// parameter-major flat space; when `piece_len` > 0 the trainer keeps it ZeRO-3 sharded -- cut into equal flat
+// pieces, piece r on rank r at `shard_off` of that rank's shard buffer -- and every 16-byte vector is read from
+// the rank that owns it.  The slice [row0, row0 + rows) x [col0, col0 + cols) is written to the destination as a
+// dense [rows, dst_ld] matrix: bf16 at `dst_elem` of the bf16 buffer (dst_elem >= 0) and / or e4m3 at `q_off` of
+// the fp8 buffer with one fp32 scale per 128 x 128 block of THE SLICE at `scale_off` (fp8 != 0).
+struct SyncSeg {
+  long long src_elem;
+  long long piece_len;
+  long long shard_off;
+  long long dst_elem;    // < 0: no bf16 copy
+  long long q_off;       // fp8 bytes
+  long long scale_off;   // floats
+  long long tile_start;  // 128 x 128 tiles of all earlier segments
+  int src_ld, row0, col0, rows, cols, dst_ld, q_ld, scale_ld;
+  int fp8;
+  int tiles_c;           // ceil(cols / 128)
+};
+
+__device__ __forceinline__ const __nv_bfloat16* sync_src_ptr(const SyncSeg& sg, const PeerPtrs& src, int src_rank,
+                                                             long long e_in_param) {
+  if (sg.piece_len > 0) {
+    const int owner = static_cast<int>(e_in_param / sg.piece_len);
+    return static_cast<const __nv_bfloat16*>(src.p[owner]) + sg.shard_off + (e_in_param - owner * sg.piece_len);
+  }
+  return static_cast<const __nv_bfloat16*>(src.p[src_rank]) + sg.src_elem + e_in_param;
+}
+
+// One CTA per 128 x 128 tile of a segment (grid-stride over all tiles of the table).  A tile is read ONCE from the
+// source (local memory, or a peer's over NVLink) into registers: 256 threads x 8 vectors of 8 bf16.
+__global__ void __launch_bounds__(256)
+sync_weights_table_kernel(const SyncSeg* __restrict__ segs, int n_seg, long long total_tiles, PeerPtrs src,
+                          int src_rank, PeerPtrs flags, int rank, int world, int epoch,
+                          __nv_bfloat16* __restrict__ dst_bf16, uint8_t* __restrict__ dst_q,
+                          float* __restrict__ dst_scale, int* status) {
+  if (!epoch_barrier(flags, rank, world, epoch, status)) return;
+  __shared__ float red[8];
+  for (long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    int lo = 0, hi = n_seg - 1;             // last segment whose tile_start <= t
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (segs[mid].tile_start <= t) lo = mid; else hi = mid - 1;
+    }
+    const SyncSeg sg = segs[lo];
+    const long long lt = t - sg.tile_start;
+    const int rb = static_cast<int>(lt / sg.tiles_c), cb = static_cast<int>(lt % sg.tiles_c);
+    uint4 v[8];
+    float amax = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int i = threadIdx.x + k * 256;          // vector index inside the tile: 128 rows x 16 vectors
+      const int r = rb * 128 + (i >> 4), c = cb * 128 + (i & 15) * 8;
+      v[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (r < sg.rows && c < sg.cols) {
+        const long long e = static_cast<long long>(sg.row0 + r) * sg.src_ld + sg.col0 + c;
+        v[k] = *reinterpret_cast<const uint4*>(sync_src_ptr(sg, src, src_rank, e));
+        if (sg.dst_elem >= 0)
+          *reinterpret_cast<uint4*>(dst_bf16 + sg.dst_elem + static_cast<long long>(r) * sg.dst_ld + c) = v[k];
+        if (sg.fp8) {
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h2[j]);
+            amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+          }
+        }
+      }
+    }
+    if (sg.fp8) {                                   // uniform across the CTA
+      amax = warp_max(amax);
+      __syncthreads();                              // `red` of the previous tile has been read by everybody
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+      __syncthreads();
+      amax = red[0];
+#pragma unroll
+      for (int k = 1; k < 8; ++k) amax = fmaxf(amax, red[k]);
+      const float scale = amax > 0.f ? amax / 448.f : 1.f;
+      const float inv = 1.f / scale;
+      if (threadIdx.x == 0) dst_scale[sg.scale_off + static_cast<long long>(rb) * sg.scale_ld + cb] = scale;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int i = threadIdx.x + k * 256;
+        const int r = rb * 128 + (i >> 4), c = cb * 128 + (i & 15) * 8;
+        if (r < sg.rows && c < sg.cols) {
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
+          uint32_t out[2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const float2 a = __bfloat1622float2(h2[2 * j]);
+            const float2 b = __bfloat1622float2(h2[2 * j + 1]);
+            uint16_t lo16, hi16;
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo16) : "f"(a.y * inv), "f"(a.x * inv));
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi16) : "f"(b.y * inv), "f"(b.x * inv));
+            out[j] = static_cast<uint32_t>(lo16) | (static_cast<uint32_t>(hi16) << 16);
+          }
+          *reinterpret_cast<uint2*>(dst_q + sg.q_off + static_cast<long long>(r) * sg.q_ld + c) =
+              make_uint2(out[0], out[1]);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace apb
+
+extern "C" {
+
+// segs: DEVICE array of n_seg apb::SyncSeg records (tile_start filled, ascending); total_tiles = tiles of all
+// segments.  src_ptrs[n_src]: the trainer ranks' parameter buffers (full flat buffers, of which src_rank's is read,
+// or ZeRO-3 shard buffers, read by ownership) -- peer mappings of this process (symmetric memory or opened IPC
+// handles).  flag_ptrs / rank / world / epoch: optional epoch barrier among the ranks that launch this kernel
+// together (world <= 1: none).  dst_bf16 / dst_q / dst_scale: this sampler rank's buffers.
+int apb_sync_weights_table(const void* segs, int n_seg, long long total_tiles, void* const* src_ptrs, int n_src,
+                           int src_rank, void* const* flag_ptrs, int rank, int world, int epoch, void* dst_bf16,
+                           void* dst_q, float* dst_scale, int max_ctas, cudaStream_t s) {
+  using namespace apb;
+  if (n_seg <= 0 || total_tiles <= 0) return 0;
+  if (!segs || !src_ptrs || n_src < 1 || n_src > kMaxRanks || src_rank < 0 || src_rank >= n_src ||
+      world > kMaxRanks || (world > 1 && !flag_ptrs))
+    return kBadArgument;
+  for (int i = 0; i < n_src; ++i)
+    if (!src_ptrs[i]) return kBadArgument;
+  PeerPtrs fl;
+  for (int i = 0; i < kMaxRanks; ++i) fl.p[i] = (world > 1 && i < world) ? flag_ptrs[i] : nullptr;
+  const long long cap = max_ctas > 0 ? max_ctas : static_cast<long long>(sm_count()) * 8;
+  const int grid = static_cast<int>(total_tiles < cap ? total_tiles : cap);
+  sync_weights_table_kernel<<<grid, 256, 0, s>>>(static_cast<const SyncSeg*>(segs), n_seg, total_tiles,
+                                                 to_peers(src_ptrs, n_src), src_rank, fl, rank, world > 1 ? world : 1,
+                                                 epoch, static_cast<__nv_bfloat16*>(dst_bf16),
+                                                 static_cast<uint8_t*>(dst_q), dst_scale, status_device_ptr());
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Size of one table record, so that the host side can lay the records out without sharing a header.
+int apb_sync_seg_bytes() { return static_cast<int>(sizeof(apb::SyncSeg)); }
+
+// ---- device pointers shared between processes (split placement: the sampler's process reads the trainer's
+// parameter buffer over NVLink).  `handle` is an opaque 64-byte record to send to the other process.
+int apb_ipc_export(const void* ptr, void* handle64, long long* offset_out) {
+  if (!ptr || !handle64 || !offset_out) return apb::kBadArgument;
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  // the handle names the allocation; the pointer may sit inside it (a caching allocator's block)
+  typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static RangeFn range_fn = nullptr;
+  if (!range_fn) {
+    void* fp = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fp, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return -1;
+    range_fn = reinterpret_cast<RangeFn>(fp);
+  }
+  if (range_fn(&base, &size, reinterpret_cast<CUdeviceptr>(ptr)) != CUDA_SUCCESS) return -2;
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  memcpy(handle64, &h, sizeof(h));
+  *offset_out = static_cast<long long>(reinterpret_cast<CUdeviceptr>(ptr) - base);
+  return 0;
+}
+
+int apb_ipc_open(const void* handle64, long long offset, void** ptr_out) {
+  if (!handle64 || !ptr_out) return apb::kBadArgument;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* base = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  *ptr_out = static_cast<char*>(base) + offset;
+  return 0;
+}
+
+int apb_ipc_close(void* ptr, long long offset) {
+  if (!ptr) return 0;
+  return static_cast<int>(cudaIpcCloseMemHandle(static_cast<char*>(ptr) - offset));
 }
 }
 

@@ -156,14 +156,88 @@ def _fn(name: str):
     return _FN[name]
 
 
+class _TPDecode:
+    """Symmetric scratch and epoch state of one tensor-parallel replica's decode loop: two fp32 accumulators
+    (``[max_batch / tp, H]`` per rank, targets of the peers' GEMM epilogues), two bf16 activation buffers
+    (``[max_batch, H]`` per rank, targets of the owners' normalised rows), the flags of the in-kernel barriers and a
+    DEVICE epoch counter -- the kernels read ``*epoch + offset``, so a captured step can be replayed."""
+
+    def __init__(self, device, group, max_batch: int, hidden: int):
+        import torch.distributed as dist
+        from ..parallel.symm import EpochFlags, SymmetricBuffer
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device(device)
+        self.H = hidden
+        self.rows = max_batch // self.world
+        self.flags = EpochFlags(device, group)
+        self.acc = [SymmetricBuffer(self.rows * hidden, torch.float32, device, group) for _ in range(2)]
+        self.hbuf = [SymmetricBuffer(max_batch * hidden, torch.bfloat16, device, group) for _ in range(2)]
+        self.resid = torch.zeros((self.rows, hidden), device=device, dtype=torch.bfloat16)
+        self.epoch = torch.ones(1, device=device, dtype=torch.int32)      # 0 is what fresh flags hold
+        self.done = torch.zeros(1, device=device, dtype=torch.int32)
+        self._calls = 0
+        c = ctypes
+        vp, i, ll, f = c.c_void_p, c.c_int, c.c_longlong, c.c_float
+        self._rs = _lib.declare("apb_gemm_rs", [vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, vp])
+        self._na = _lib.declare("apb_tp_norm_allgather", [vp, i, i, vp, i, vp, vp, i, vp, f, vp, i, i, vp, vp])
+        self._adv = _lib.declare("apb_tp_epoch_advance", [vp, i, vp])
+
+    def begin_step(self) -> None:
+        self._calls = 0
+
+    def rs_norm_allgather(self, x: torch.Tensor, w_local: torch.Tensor, norm_w: torch.Tensor, eps: float, B: int,
+                          H: int, splits: int) -> torch.Tensor:
+        """``RMSNorm(residual += sum over ranks of x @ w_local^T) * norm_w`` for all ``B`` rows, on every rank."""
+        k = self._calls
+        self._calls += 1
+        acc, hb = self.acc[k & 1], self.hbuf[k & 1]
+        rl = B // self.world
+        s = _lib.stream_ptr()
+        _lib.check(self._rs(_lib.ptr(x), _lib.ptr(w_local), acc.ptr_table(), self.world, B, H, x.shape[1], x.stride(0),
+                            w_local.stride(0), H, 128, splits, s), "apb_gemm_rs")
+        _lib.check(self._na(self.flags.ptr_table(), self.rank, self.world, _lib.ptr(self.epoch), 2 * k,
+                            _lib.ptr(acc.tensor), _lib.ptr(self.resid), 1, _lib.ptr(norm_w), float(eps), hb.ptr_table(),
+                            rl, H, _lib.ptr(self.done), s), "apb_tp_norm_allgather")
+        return hb.tensor[:B * H].view(B, H)
+
+    def end_step(self) -> None:
+        if self._calls & 1:
+            raise RuntimeError("a decode step must use the accumulator pair an even number of times")
+        _lib.check(self._adv(_lib.ptr(self.epoch), 2 * self._calls, _lib.stream_ptr()), "apb_tp_epoch_advance")
+
+
 class SamplerEngine:
     def __init__(self, cfg: DecoderConfig, device="cuda", model: Optional[DecoderLM] = None,
                  kv_cache_tokens: int = 1 << 20, max_batch: int = 256, max_seq_len: int = 8192,
                  cascade: bool = True, sync_interval: int = 16, use_cuda_graph: bool = True, seed: int = 0,
                  eos_token_id: Optional[int] = None, prefix_on_tensor_cores: bool = True, split_k: bool = True,
-                 quantization: Optional[str] = None):
-        self.cfg = cfg
+                 quantization: Optional[str] = None, tp_group=None):
         self.device = torch.device(device)
+        # tensor-parallel replica: this engine is ONE rank of ``tp`` and holds the heads / columns of its shard
+        # (``vllm_config.tensor_parallel_size`` in the reference, arctic_platform/common/ray_server.py:375-404)
+        self.tp_group = tp_group
+        self.tp = 1
+        self.tp_rank = 0
+        self.full_cfg = cfg
+        if tp_group is not None:
+            import torch.distributed as dist
+            self.tp = dist.get_world_size(tp_group)
+            self.tp_rank = dist.get_rank(tp_group)
+        if self.tp > 1:
+            from ..parallel.tp_sampler import tp_config
+            if cfg.is_moe:
+                raise NotImplementedError("tensor-parallel replicas of the paged engine serve dense decoders")
+            if max_batch % self.tp:
+                raise ValueError(f"max_num_seqs={max_batch} must be a multiple of tensor_parallel_size={self.tp}")
+            cfg = tp_config(cfg, self.tp)
+            if model is not None and model.cfg.num_heads != cfg.num_heads:
+                full, model = model, DecoderLM(cfg, self.device, torch.bfloat16)
+                self.cfg, self.model = cfg, model
+                from ..models.hf_io import iter_hf_tensors
+                self.load_weights(iter_hf_tensors(full), notify=False)
+        self.cfg = cfg
         self.model = model if model is not None else DecoderLM(cfg, self.device, torch.bfloat16)
         self.max_batch = max_batch
         self.max_seq_len = max_seq_len
@@ -190,6 +264,8 @@ class SamplerEngine:
         self._step_count = 0
         self._asleep = False
         self._alloc_state()
+        self._tpd = _TPDecode(self.device, tp_group, max_batch, cfg.hidden_size) if self.tp > 1 else None
+        self._sync_plan = None           # table of the one-kernel weight hand-over (parallel/weight_sync.py)
 
     # ------------------------------------------------------------------ memory
     def _alloc_cache(self) -> None:
@@ -248,7 +324,7 @@ class SamplerEngine:
         self.acc_o = torch.zeros((B, c.hidden_size), **f32)
         self.acc_d = torch.zeros((B, c.hidden_size), **f32)
         self.acc_qkv = torch.zeros((B, c.qkv_size), **f32)
-        self.acc_gu = torch.zeros((B, 2 * c.intermediate_size), **f32) if not c.is_moe else None
+        self.acc_gu = torch.zeros((B, 2 * c.intermediate_size), **f32) if not c.is_moe else None   # split-K gate/up sums
         self.d_new_tok = torch.zeros(B, **i32)
         self.d_new_lp = torch.zeros(B, **f32)
         self.d_slots = torch.full((B,), -1, **i32)                              # cache slot of the token being fed
@@ -272,14 +348,22 @@ class SamplerEngine:
                               _lib.ptr(self.kcache[li]), _lib.ptr(self.vcache[li]), k.shape[0], c.num_kv_heads,
                               c.head_dim, _lib.stream_ptr()), "kv_cache_write")
         a = attn_fn(li, q, k, v)
-        o = gemm.matmul_nt(a.reshape(a.shape[0], -1), blk.wo)
+        o = self._tp_sum(gemm.matmul_nt(a.reshape(a.shape[0], -1), blk.wo))
         h2, stream = norm.rmsnorm(o, blk.ln2, c.rms_norm_eps, stream)
         if blk.mlp is not None:
             d = blk.mlp(h2)
         else:
             _, act = gemm.gate_up_swiglu(h2, blk.wgu, keep_gu=False)
-            d = gemm.matmul_nt(act, blk.wdown)
+            d = self._tp_sum(gemm.matmul_nt(act, blk.wdown))
         return d, stream
+
+    def _tp_sum(self, t: torch.Tensor) -> torch.Tensor:
+        """Prefill under tensor parallelism: the row-parallel projections' partial results are summed over the
+        replica with a library all-reduce (prefill runs once per prompt; decode uses the fused kernels)."""
+        if self.tp > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, group=self.tp_group)
+        return t
 
     @torch.no_grad()
     def weights_updated(self) -> None:
@@ -309,10 +393,10 @@ class SamplerEngine:
                               _lib.ptr(self.kcache[li]), _lib.ptr(self.vcache[li]), k.shape[0], c.num_kv_heads,
                               c.head_dim, _lib.stream_ptr()), "kv_cache_write")
         a = attn_fn(li, q, k, v)
-        o = fp8_linear(a.reshape(a.shape[0], -1).contiguous(), *w["wo"])
+        o = self._tp_sum(fp8_linear(a.reshape(a.shape[0], -1).contiguous(), *w["wo"]))
         h2, stream = norm.rmsnorm(o, blk.ln2, c.rms_norm_eps, stream)
         act = norm.swiglu(fp8_linear(h2, *w["wgu"]))
-        return fp8_linear(act, *w["wdown"]), stream
+        return self._tp_sum(fp8_linear(act, *w["wdown"])), stream
 
     # ------------------------------------------------------------------ decode step
     @torch.no_grad()
@@ -384,7 +468,9 @@ class SamplerEngine:
                                     _lib.stream_ptr()), "decode_begin")
             stream = None
             attn = lambda li, q, k, v: self._decode_attention(li, q, B)
-            if self.split_k and not c.is_moe and not self.fp8:
+            if self.tp > 1 and not self.fp8:
+                h = self._decode_layers_tp(x, positions, slots, B)
+            elif self.split_k and not c.is_moe and not self.fp8:
                 h = self._decode_layers_splitk(x, positions, slots, B)
             else:
                 for li in range(c.num_layers):
@@ -422,14 +508,12 @@ class SamplerEngine:
         return y, stream
 
     def _gate_up_bn(self, B: int) -> int:
-        """Tile choice of the gate/up projection in decode: when 128-wide tiles make between one and two waves of
-        SMs, run two CTAs per SM so that every tile streams its weights at the same time."""
+        """Tile width of the gate/up projection in decode.  0 lets the kernel pick the width that covers the
+        columns in one wave of SMs (144-wide tiles for 19456 columns: 136 tiles, where 128-wide ones would leave
+        four SMs with two tiles each and double the kernel's time)."""
         if os.environ.get("APB_GATE_UP_BN"):
             return int(os.environ["APB_GATE_UP_BN"])
-        if B > 128:
-            return 0
-        tiles = (2 * self.cfg.intermediate_size + 127) // 128
-        return gemm.BN_X2 + 128 if 148 < tiles <= 296 else 256
+        return 0
 
     def _decode_layers_splitk(self, x: torch.Tensor, positions, slots, B: int) -> torch.Tensor:
         """Decoder stack for one decode step.  The two projections with few output columns (o_proj, down_proj)
@@ -488,6 +572,56 @@ class SamplerEngine:
             gemm.gemm_raw(act, blk.wdown, acc_d, M=B, N=H, K=c.intermediate_size, epi=gemm.EPI_F32_ATOMIC, splits=sd,
                           bn=128)
         h, _ = self._norm_f32(acc_d, self.model.final_norm, stream)
+        return h
+
+    def _decode_layers_tp(self, x: torch.Tensor, positions, slots, B: int) -> torch.Tensor:
+        """Decoder stack of one decode step on one rank of a tensor-parallel replica.  Column-parallel projections
+        (qkv, gate/up) read the full activation from LOCAL memory; row-parallel ones (o, down) add their partial
+        rows into the owner rank's fp32 accumulator from the GEMM epilogue (``apb_gemm_rs``), and
+        ``apb_tp_norm_allgather`` turns the owner's sums into residual + RMSNorm and stores the normalised rows into
+        every rank's activation buffer -- two kernels per projection, no library collective in the loop."""
+        c, t = self.cfg, self._tpd
+        H, T = c.hidden_size, self.tp
+        if B % T:
+            raise ValueError(f"decode batch {B} is not a multiple of tensor_parallel_size {T}")
+        rl = B // T
+        tiles = (H + 127) // 128
+        so = max(1, min(148 // tiles, (c.q_size + 63) // 64))
+        sd = max(1, min(148 // tiles, (c.intermediate_size + 63) // 64))
+        qkv_tiles = (c.qkv_size + 127) // 128
+        sq = max(1, min(148 // qkv_tiles, (H + 63) // 64))
+        gu_tiles = (2 * c.intermediate_size + 255) // 256
+        sgu = max(1, min(148 // gu_tiles, 4))
+        acc_qkv = self.acc_qkv[:B]
+        acc_gu = self.acc_gu[:B]
+        cos_t, sin_t = self.model.rope(self.device)
+        t.begin_step()
+        # the residual stream is carried for this rank's rows only
+        t.resid[:rl].copy_(x[self.tp_rank * rl:(self.tp_rank + 1) * rl])
+        h, _ = norm.rmsnorm(x, self.model.blocks[0].ln1, c.rms_norm_eps, None)
+        for li in range(c.num_layers):
+            blk = self.model.blocks[li]
+            gemm.gemm_raw(h, blk.wqkv, acc_qkv, M=B, N=c.qkv_size, K=H, epi=gemm.EPI_F32_ATOMIC, splits=sq, bn=128)
+            q = torch.empty((B, c.num_heads, c.head_dim), device=self.device, dtype=torch.bfloat16)
+            _lib.check(_fn("qkv_post")(_lib.ptr(acc_qkv), acc_qkv.stride(0), _lib.ptr(blk.q_norm), _lib.ptr(blk.k_norm),
+                                       _lib.ptr(cos_t), _lib.ptr(sin_t), _lib.ptr(positions), _lib.ptr(slots),
+                                       _lib.ptr(q), _lib.ptr(self.kcache[li]), _lib.ptr(self.vcache[li]), B,
+                                       c.num_heads, c.num_kv_heads, c.head_dim, c.rms_norm_eps, _lib.stream_ptr()),
+                       "decode_qkv_post")
+            a = self._decode_attention(li, q, B).reshape(B, -1)
+            h2 = t.rs_norm_allgather(a, blk.wo, blk.ln2, c.rms_norm_eps, B, H, so)
+            act = torch.empty((B, c.intermediate_size), device=self.device, dtype=torch.bfloat16)
+            if sgu > 1:
+                gemm.gemm_raw(h2, blk.wgu, acc_gu, M=B, N=2 * c.intermediate_size, K=H, epi=gemm.EPI_F32_ATOMIC,
+                              splits=sgu, bn=256)
+                _lib.check(_fn("swiglu32")(_lib.ptr(acc_gu), _lib.ptr(act), B, c.intermediate_size, _lib.stream_ptr()),
+                           "swiglu_f32in")
+            else:
+                gemm.gemm_raw(h2, blk.wgu, None, M=B, N=2 * c.intermediate_size, K=H, epi=gemm.EPI_SWIGLU, out2=act,
+                              bn=self._gate_up_bn(B))
+            nxt = self.model.blocks[li + 1].ln1 if li + 1 < c.num_layers else self.model.final_norm
+            h = t.rs_norm_allgather(act, blk.wdown, nxt, c.rms_norm_eps, B, H, sd)
+        t.end_step()
         return h
 
     def _run_steps(self, B: int, n: int) -> None:
@@ -860,23 +994,42 @@ class SamplerEngine:
 
     # ------------------------------------------------------------------ weights / sleep / wake
     @torch.no_grad()
-    def load_weights(self, named_tensors) -> int:
-        """Copies ``(hf_name, tensor)`` pairs into the engine's fused parameters; returns the count."""
+    def load_weights(self, named_tensors, notify: bool = True) -> int:
+        """Copies ``(hf_name, tensor)`` pairs (FULL tensors) into the engine's fused parameters -- a tensor-parallel
+        rank keeps its slice of each; returns the count."""
         from ..models.hf_io import load_hf_tensor
         n = 0
+        if self.tp > 1:
+            from ..parallel.tp_sampler import tp_slice
         for name, t in named_tensors:
+            if self.tp > 1:
+                t = tp_slice(name, t, self.full_cfg, self.tp_rank, self.tp)
             load_hf_tensor(self.model, name, t)
             n += 1
-        self.weights_updated()
+        if notify:
+            self.weights_updated()
         return n
 
     def weight_norm(self) -> Dict[str, float]:
-        sq = torch.zeros((), dtype=torch.float64, device=self.device)
-        n = 0
-        for p in self.model.parameters():
-            sq += p.data.double().pow(2).sum()
-            n += p.numel()
-        return {"norm": float(sq.sqrt().item()), "sq_sum": float(sq.item()), "num_params": n}
+        """Norm and size of the WHOLE model (a tensor-parallel rank adds the other ranks' slices; replicated tensors
+        count once)."""
+        sq_s = torch.zeros((), dtype=torch.float64, device=self.device)
+        sq_r = torch.zeros((), dtype=torch.float64, device=self.device)
+        n_s = n_r = 0
+        for name, p in self.model.named_parameters():
+            sharded = self.tp > 1 and name.split(".")[-1] in ("wqkv", "wgate", "wo", "wgu", "wdown")
+            v = p.data.double().pow(2).sum()
+            if sharded:
+                sq_s, n_s = sq_s + v, n_s + p.numel()
+            else:
+                sq_r, n_r = sq_r + v, n_r + p.numel()
+        if self.tp > 1:
+            import torch.distributed as dist
+            t = torch.stack([sq_s, torch.tensor(float(n_s), dtype=torch.float64, device=self.device)])
+            dist.all_reduce(t, group=self.tp_group)
+            sq_s, n_s = t[0], int(t[1].item())
+        sq = sq_s + sq_r
+        return {"norm": float(sq.sqrt().item()), "sq_sum": float(sq.item()), "num_params": n_s + n_r}
 
     def reset_prefix_cache(self) -> None:
         """Pages are released at the end of every ``generate`` call, so nothing outlives a weight sync."""
@@ -890,6 +1043,7 @@ class SamplerEngine:
         if level >= 2:
             for p in self.model.parameters():
                 p.data = torch.empty(0, device=self.device, dtype=p.dtype)
+            self._sync_plan = None            # its destination buffer went with the weights
         self._asleep = True
         torch.cuda.empty_cache()
 

@@ -202,10 +202,24 @@ class EngineWorker:
         group = dist.new_group(list(range(first, first + tp)), use_local_synchronization=True)
         vc = dict(job_config.get("vllm_config") or {})
         full = model if model is not None else self._load_model(job_config, dtype, seed)
-        self.sampler = TensorParallelSampler(
-            self.model_cfg, self.device, model=full, tp_group=group, dtype=dtype,
-            max_batch=int(vc.get("max_num_seqs", 256)), max_seq_len=int(vc.get("max_model_len", 8192)), seed=seed,
-            eos_token_id=vc.get("eos_token_id"))
+        paged = (self.device.type == "cuda" and not self.model_cfg.is_moe and self.model_cfg.layer_types is None
+                 and self.model_cfg.head_dim == 128 and not vc.get("enable_return_routed_experts")
+                 and vc.get("tp_engine", "paged") == "paged")
+        if paged:
+            # dense decoders on GPUs: the paged CUDA engine with head shards of the KV cache and the fused
+            # GEMM -> reduce-scatter / norm -> all-gather kernels in its decode loop
+            from .sampler import SamplerEngine
+            self.sampler = SamplerEngine(
+                self.model_cfg, self.device, model=full, tp_group=group,
+                kv_cache_tokens=int(vc.get("kv_cache_tokens", 1 << 20)), max_batch=int(vc.get("max_num_seqs", 256)),
+                max_seq_len=int(vc.get("max_model_len", 8192)),
+                cascade=bool((job_config.get("arctic_inference_config") or {}).get("zorro_inference", {}).get("enable", True)),
+                seed=seed, eos_token_id=vc.get("eos_token_id"), quantization=vc.get("quantization"))
+        else:
+            self.sampler = TensorParallelSampler(
+                self.model_cfg, self.device, model=full, tp_group=group, dtype=dtype,
+                max_batch=int(vc.get("max_num_seqs", 256)), max_seq_len=int(vc.get("max_model_len", 8192)), seed=seed,
+                eos_token_id=vc.get("eos_token_id"))
         self.tp = tp
         del full                                                 # only the shard stays resident
         if self.device.type == "cuda":
@@ -648,7 +662,10 @@ class EngineWorker:
         their Hugging Face names.  Returns the number of tensors covered."""
         from ..models.hf_io import hf_param_names
         from ..parallel import weight_sync
-        if dst.sampler is not None and hasattr(dst.sampler, "tp"):
+        n_table = self._sync_by_table(dst)
+        if n_table is not None:
+            return n_table
+        if dst.sampler is not None and getattr(dst.sampler, "tp", 1) > 1:
             # tensor-parallel replica: a different layout per rank, so the tensors travel under their names
             return dst.sampler.load_weights((n, t.detach()) for n, t in self.engine.iter_hf_tensors())
         dst_model = dst.sampler.model if dst.sampler is not None else dst.engine.model
@@ -674,6 +691,38 @@ class EngineWorker:
                 dst.sampler.weights_updated()
             return n_names
         return weight_sync.sync_state_dict(((n, t.detach()) for n, t in self.engine.iter_hf_tensors()), dst_model)
+
+    def _sync_by_table(self, dst: "EngineWorker") -> Optional[int]:
+        """One kernel for a CUDA sampler of the same process whose layout differs from the trainer's: a
+        tensor-parallel shard (head / column slices) and / or block-scaled fp8 matrices.  The table names, for every
+        128 x 128 tile of the sampler's tensors, where it lives in the trainer (ZeRO-3 piece of which rank, or the
+        replicated buffer).  Returns the tensor count, or ``None`` when this route does not apply."""
+        from ..models.hf_io import hf_param_names
+        from ..parallel import weight_sync
+        sm = dst.sampler
+        if sm is None or not self.engine.on_cuda or not hasattr(sm, "_sync_plan"):
+            return None
+        tp, fp8 = int(getattr(sm, "tp", 1)), bool(getattr(sm, "fp8", False))
+        if tp == 1 and not fp8:
+            return None                         # same layout: the flat kernel below is the shortest path
+        if self.model_cfg.is_moe or any(u.local_only for u in self.engine.units):
+            return None
+        if next(sm.model.parameters()).device != self.device:
+            return None
+        layout = weight_sync.trainer_layout(self.engine)
+        key = (layout["total"], layout["world"], layout["zero3"] is not None, sm.tp_rank, tp, fp8, True)
+        plan = sm._sync_plan
+        if plan is None or plan.layout_key != key:
+            plan = weight_sync.build_sync_plan(layout, sm.model, full_cfg=sm.full_cfg, tp_rank=sm.tp_rank, tp=tp, fp8=fp8)
+            sm._sync_plan = plan
+        ptrs, src_rank = weight_sync.engine_source(self.engine)
+        weight_sync.run_sync_plan(plan, ptrs, src_rank)
+        if fp8:
+            # the block-scaled copies came out of the same pass: nothing to re-quantise before the next rollout
+            sm._fp8_w = [{n: plan.fp8[(li, n)] for n in weight_sync.FP8_MATRICES} for li in range(sm.cfg.num_layers)]
+            sm._graphs.clear()
+            sm._fp8_stale = False
+        return len(hf_param_names(self.model_cfg))
 
     def sleep_inference(self, level: int = 1) -> None:
         if self.sampler is not None:

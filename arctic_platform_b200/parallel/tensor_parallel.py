@@ -27,7 +27,7 @@ def _fns():
         c = ctypes
         vp, i, ll = c.c_void_p, c.c_int, c.c_longlong
         _FN["ag"] = _lib.declare("apb_gemm_ag", [vp, i, i, vp, vp, i, i, ll, ll, ll, i, vp])
-        _FN["rs"] = _lib.declare("apb_gemm_rs", [vp, vp, vp, i, i, i, i, ll, ll, ll, i, vp])
+        _FN["rs"] = _lib.declare("apb_gemm_rs", [vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, vp])
         _FN["fin"] = _lib.declare("apb_tp_finalize", [vp, i, i, i, vp, vp, ll, vp])
         _FN["wait"] = _lib.declare("apb_epoch_wait", [vp, i, i, i, vp])
     return _FN
@@ -79,7 +79,7 @@ def ag_gemm(ctx: TPContext, x_local: torch.Tensor, w_local: torch.Tensor, bn: in
     return out
 
 
-def gemm_rs(ctx: TPContext, x: torch.Tensor, w_local: torch.Tensor, bn: int = 0) -> torch.Tensor:
+def gemm_rs(ctx: TPContext, x: torch.Tensor, w_local: torch.Tensor, bn: int = 0, splits: int = 1) -> torch.Tensor:
     """``reduce_scatter(x @ w_local^T, dim 0)`` -> ``[M / world, N]``; ``x [M, K_local]``, ``w_local [N, K_local]``."""
     M, K = x.shape
     N = w_local.shape[0]
@@ -95,7 +95,7 @@ def gemm_rs(ctx: TPContext, x: torch.Tensor, w_local: torch.Tensor, bn: int = 0)
     f = _fns()
     s = _lib.stream_ptr()
     _lib.check(f["rs"](_lib.ptr(x), _lib.ptr(w_local), acc.ptr_table(), ctx.world, M, N, K, x.stride(0),
-                       w_local.stride(0), N, bn, s), "apb_gemm_rs")
+                       w_local.stride(0), N, bn, splits, s), "apb_gemm_rs")
     out = torch.empty((rows, N), device=x.device, dtype=torch.bfloat16)
     _lib.check(f["fin"](ctx.flags.ptr_table(), ctx.rank, ctx.world, ctx.flags.next(), _lib.ptr(acc.tensor), _lib.ptr(out),
                         rows * N, s), "apb_tp_finalize")

@@ -204,3 +204,28 @@ def test_cta_pair_kernel_swiglu_and_many_tiles_per_pair():
     _lib.check_status("pair vs one")
     assert torch.equal(auto, gu)
     assert (auto.float() - one.float()).abs().max().item() <= 2e-2 * ref_gu.abs().max().item()
+
+
+@pytest.mark.parametrize("bn", [144, 208])
+@pytest.mark.parametrize("M,N,K", [(128, 2880, 256), (100, 1160, 200), (128, 19456, 512), (300, 424, 64)])
+def test_in_between_tile_widths(M, N, K, bn):
+    """144- and 208-column tiles (16-column multiples between the power-of-two widths, used to cover decode-shaped
+    products in one wave of SMs): bf16 / fp32 outputs and the SwiGLU epilogue, with row, column and depth tails."""
+    from arctic_platform_b200.ops import _lib, gemm
+    a, b = _rand((M, K)), _rand((N, K), 0.2)
+    ref = a.float() @ b.float().t()
+    out = gemm.matmul_nt(a, b, bn=bn)
+    _lib.check_status("gemm bn")
+    _close(out, ref, K)
+    out32 = torch.full((M, N), 7.0, device="cuda", dtype=torch.float32)
+    gemm.matmul_nt(a, b, out=out32, bn=bn)
+    _lib.check_status("gemm bn f32")
+    _close(out32, ref, K)
+    if N % 16 == 0:
+        act = torch.empty((M, N // 2), device="cuda", dtype=torch.bfloat16)
+        gemm.gemm_raw(a, b, None, M=M, N=N, K=K, epi=gemm.EPI_SWIGLU, out2=act, bn=bn)
+        _lib.check_status("gemm bn swiglu")
+        _close(act, torch.nn.functional.silu(ref[:, 0::2]) * ref[:, 1::2], K)
+    auto = gemm.matmul_nt(a, b)                      # the automatic choice for one row tile may be one of these widths
+    _lib.check_status("gemm auto")
+    _close(auto, ref, K)

@@ -328,3 +328,80 @@ def test_expert_parallel_training_fused_matches_collective_on_two_gpus():
             assert all(abs(x - y) <= 3e-2 * abs(y) + 1e-4 for x, y in zip(r[other][1], r["collective"][1])), (other, r[other][1], r["collective"][1])
             assert (r[other][0] - r["collective"][0]).abs().mean() < 2e-4
             assert abs(r[other][2] - r["collective"][2]) <= 2e-3 * r["collective"][2]
+
+
+def _tp_paged_main(rank, world, port, out_dir):
+    """Tensor-parallel replica of the paged CUDA engine (head shards of the KV cache, GEMM -> reduce-scatter and
+    norm -> all-gather kernels in the decode loop) fed by the one-kernel weight hand-over from a ZeRO-3 trainer."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from arctic_platform_b200.engine.sampler import SamplerEngine
+        from arctic_platform_b200.engine.worker import EngineWorker
+        from arctic_platform_b200.models.config import PRESETS
+        from arctic_platform_b200.models.decoder import DecoderLM
+        from arctic_platform_b200.models.hf_io import iter_hf_tensors, load_hf_tensor
+        from arctic_platform_b200.ops import _lib
+        from arctic_platform_b200.parallel.tp_sampler import tp_config, tp_slice
+        cfg = PRESETS["qwen3-tiny-d128"]
+        job = {"model_name": "qwen3-tiny-d128", "seed": 5,
+               "ds_config": {"zero_optimization": {"stage": 3}, "optimizer": {"params": {"lr": 1e-3}}}}
+        tr, sm = EngineWorker(), EngineWorker()
+        tr.initialize({**job, "job_type": "training"})
+        sm.initialize({**job, "job_type": "sampling", "seed": 77,        # other weights: everything must arrive by the sync
+                       "vllm_config": {"kv_cache_tokens": 1 << 14, "max_num_seqs": 16, "max_model_len": 512,
+                                       "tensor_parallel_size": world}})
+        assert isinstance(sm.sampler, SamplerEngine) and sm.sampler.tp == world
+        n = tr.sync_weights_to(sm)
+        _lib.check_status("tp sync")
+        assert n > 0 and sm.sampler._sync_plan is not None
+        # exact bf16 equality with the name-based slices of the trainer's full tensors
+        ref = DecoderLM(tp_config(cfg, world), "cuda", torch.bfloat16)
+        for name, t in tr.engine.iter_hf_tensors():
+            load_hf_tensor(ref, name, tp_slice(name, t.detach(), cfg, rank, world))
+        for (n1, a), (_n2, b) in zip(sm.sampler.model.named_parameters(), ref.named_parameters()):
+            assert torch.equal(a, b), n1
+        assert tr.engine.weight_norm()["norm"] == pytest.approx(sm.sampler.weight_norm()["norm"], rel=1e-3)
+        # generation: the replica against a one-rank engine holding the same (full) weights
+        full = DecoderLM(cfg, "cuda", torch.bfloat16)
+        for name, t in tr.engine.iter_hf_tensors():
+            load_hf_tensor(full, name, t.detach())
+        one = SamplerEngine(cfg, "cuda", model=full, kv_cache_tokens=1 << 14, max_batch=16, max_seq_len=512)
+        g = torch.Generator().manual_seed(3)
+        prompts = [torch.randint(1, cfg.vocab_size, (n_tok,), generator=g).tolist() for n_tok in (40, 75, 33)]
+        sp = {"n": 4, "temperature": 0.0, "max_tokens": 24, "ignore_eos": True}
+        res = {}
+        for graph in (False, True):
+            sm.sampler.use_cuda_graph = graph
+            sm.sampler._graphs.clear()
+            res[graph] = sm.generate(prompts, sp)
+            _lib.check_status("tp generate")
+        res["one"] = one.generate(prompts, sp)
+        torch.save(res, os.path.join(out_dir, f"tp{rank}.pt"))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_tensor_parallel_paged_sampler_on_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_tp_paged_main, args=(2, _free_port(), d), nprocs=2, join=True)
+        r0 = torch.load(os.path.join(d, "tp0.pt"), weights_only=False)
+        r1 = torch.load(os.path.join(d, "tp1.pt"), weights_only=False)
+    for graph in (False, True):
+        # the ranks of a replica never diverge: identical activations, identical sampling decisions
+        assert [o["token_ids"] for o in r0[graph]] == [o["token_ids"] for o in r1[graph]]
+    assert [o["token_ids"] for o in r0[True]] == [o["token_ids"] for o in r0[False]]
+    # against one rank: same model, different summation order -- greedy tokens agree except where two logits tie
+    same = sum(a["token_ids"] == b["token_ids"] for a, b in zip(r0[False], r0["one"]))
+    assert same >= int(0.75 * len(r0["one"])), same
+    for a, b in zip(r0[False], r0["one"]):
+        k = next((i for i, (x, y) in enumerate(zip(a["token_ids"], b["token_ids"])) if x != y), len(a["token_ids"]))
+        assert a["logprobs"][:k] == pytest.approx(b["logprobs"][:k], abs=6e-2)
