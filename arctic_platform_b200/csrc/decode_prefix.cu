@@ -92,14 +92,14 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
   // chained launch: barriers and TMEM are set up.  The pages of a shared node are never written while its
-  // sequences decode (new tokens go to private pages), so the first ring-full of K/V tiles is requested BEFORE
+  // sequences decode (new tokens go to private pages), so the first K and V tiles are requested BEFORE
   // the wait for the previous kernel; q, which that kernel produces, is loaded after it.
   pdl_launch_dependents();
 
   if (warp == 0) {
     if (lane == 0 && n_blocks > 0) {
       bool ok = true;
-      const int early = min(kDpSlots, 2 * n_blocks);
+      const int early = min(2, 2 * n_blocks);       // the first K and V tiles; q must not queue behind a full ring
       for (int n = 0; n < 2 * n_blocks && ok; ++n) {
         if (n == early) {
           pdl_wait();

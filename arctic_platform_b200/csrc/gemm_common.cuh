@@ -36,7 +36,8 @@ struct GemmParams {
   float alpha;
   // Optional tile table for grouped problems: {m0, m_end, b_row_offset, n_tile}.
   const int4* tile_map;
-  int num_map_tiles;
+  int num_map_tiles;         // entries of tile_map (an upper bound when num_tiles_dev is set)
+  const int* num_tiles_dev;  // optional: the live entry count, written by a kernel (a routing plan built on the device)
   int* status;
   // log-prob epilogues
   const float* row_scale;  // [M] per-row multiplier of the logits (inverse temperature) or null

@@ -58,7 +58,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
 
   const int tiles_m = (p.M + kBM - 1) / kBM;
   const int tiles_n = (p.N + BN - 1) / BN;
-  const int mn_tiles = p.tile_map ? p.num_map_tiles : tiles_m * tiles_n;
+  const int mn_tiles = p.tile_map ? (p.num_tiles_dev ? min(*p.num_tiles_dev, p.num_map_tiles) : p.num_map_tiles)
+                                  : tiles_m * tiles_n;
   const int total_tiles = mn_tiles * p.splits;
   const int k_blocks = (p.K + kBK - 1) / kBK;
 
@@ -116,6 +117,14 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
     }
   };
 
+  // Skinny problems (one row tile: decode) have every CTA read the SAME activation tile for the same k-block at the
+  // same moment -- more than a hundred SMs queueing on the few L2 slices that hold those 16 KB.  Each output tile
+  // therefore walks its K range from a different starting block (sums are order independent up to rounding), which
+  // spreads the activation reads over the whole L2.
+  auto k_rotation = [&](int tile, int nkb) -> int {
+    return (tiles_m == 1 && !p.tile_map && nkb > 1) ? tile % nkb : 0;
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
@@ -129,15 +138,17 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
         int m0, m_end, b_row, n0, kb0, kb1;
         decode(blockIdx.x, m0, m_end, b_row, n0, kb0, kb1);
         prefetched = min(Cfg::kStages, kb1 - kb0);
+        const int rot = k_rotation(blockIdx.x, kb1 - kb0);
         for (int i = 0; i < prefetched; ++i) {
+          const int kb = kb0 + (i + rot) % (kb1 - kb0);
           uint8_t* sb = smem + i * Cfg::kStageBytes + Cfg::kABytes;
           mbar_expect_tx(&full_bar[i], Cfg::kStageBytes);
           if (!p.b_mn) {
-            tma_load_2d(sb, &tma_b, &full_bar[i], (kb0 + i) * kBK, b_row);
+            tma_load_2d(sb, &tma_b, &full_bar[i], kb * kBK, b_row);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sb + c * (64 * kBK * 2), &tma_b, &full_bar[i], b_row + c * 64, (kb0 + i) * kBK);
+              tma_load_2d(sb + c * (64 * kBK * 2), &tma_b, &full_bar[i], b_row + c * 64, kb * kBK);
           }
         }
       }
@@ -145,7 +156,9 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int m0, m_end, b_row, n0, kb0, kb1;
         decode(t, m0, m_end, b_row, n0, kb0, kb1);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        const int rot = k_rotation(t, kb1 - kb0);
+        for (int it = 0; it < kb1 - kb0; ++it) {
+          const int kb = kb0 + (it + rot) % (kb1 - kb0);
           const bool b_done = prefetched > 0;      // this stage's barrier is armed and its B tile requested already
           if (b_done) --prefetched;
           if (!b_done && !mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kTimeoutEmpty)) {
@@ -485,10 +498,10 @@ extern "C" {
 // per-group B row offsets (b_rows = total rows of the stacked B).
 // bn = 0 picks the tile width; splits > 1 needs an atomic fp32 epilogue.
 // max_ctas > 0 caps the grid (leaves SMs free for a concurrent kernel).
-int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
-                  long long ldc, int a_mn, int b_mn, int epi, int splits, float alpha, const void* bias,
-                  void* C2, long long ldc2, const void* tile_map, int num_map_tiles, long long b_rows, int bn,
-                  int max_ctas, cudaStream_t stream) {
+static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, int a_mn, int b_mn, int epi, int splits, float alpha, const void* bias,
+                         void* C2, long long ldc2, const void* tile_map, int num_map_tiles, const int* num_tiles_dev,
+                         long long b_rows, int bn, int max_ctas, cudaStream_t stream) {
   using namespace apb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (N % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
@@ -574,6 +587,7 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   p.alpha = alpha;
   p.tile_map = static_cast<const int4*>(tile_map);
   p.num_map_tiles = num_map_tiles;
+  p.num_tiles_dev = tile_map ? num_tiles_dev : nullptr;
   p.status = status_device_ptr();
   p.row_scale = nullptr;
   p.labels = nullptr;
@@ -585,6 +599,24 @@ int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, lo
   if (bn == 144) return launch_gemm<144>(ta, tb, p, max_ctas, stream);
   if (bn == 208) return launch_gemm<208>(ta, tb, p, max_ctas, stream);
   return bn == 256 ? launch_gemm<256>(ta, tb, p, max_ctas, stream) : launch_gemm<128>(ta, tb, p, max_ctas, stream);
+}
+
+int apb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                  long long ldc, int a_mn, int b_mn, int epi, int splits, float alpha, const void* bias,
+                  void* C2, long long ldc2, const void* tile_map, int num_map_tiles, long long b_rows, int bn,
+                  int max_ctas, cudaStream_t stream) {
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, splits, alpha, bias, C2, ldc2, tile_map,
+                        num_map_tiles, nullptr, b_rows, bn, max_ctas, stream);
+}
+
+// Grouped GEMM whose tile table was written by a kernel: `tile_map` has room for `max_tiles` entries, the number in
+// use is read from `*num_tiles_dev` when the GEMM runs (no host round trip between routing and the expert GEMMs).
+int apb_gemm_bf16_grouped_dev(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                              long long ldc, int epi, float alpha, void* C2, long long ldc2, const void* tile_map,
+                              int max_tiles, const int* num_tiles_dev, long long b_rows, cudaStream_t stream) {
+  if (!tile_map || !num_tiles_dev || max_tiles <= 0) return apb::kBadArgument;
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, 0, 0, epi, 1, alpha, nullptr, C2, ldc2, tile_map, max_tiles,
+                        num_tiles_dev, b_rows, 128, 0, stream);
 }
 }
 

@@ -498,6 +498,16 @@ class SamplerEngine:
         finally:
             _fn("chain")(prev_chain)
 
+    def _moe_graph_ok(self) -> bool:
+        """A mixture-of-experts step can be captured when routing, the expert histogram and the grouped-GEMM tile
+        tables are all built on the device (no expert parallelism, no group-limited routing, at most 512 experts)."""
+        if os.environ.get("APB_MOE_GRAPH", "1") == "0":
+            return False
+        c = self.cfg
+        if c.num_experts > 512 or getattr(c, "moe_n_group", 1) > 1 or getattr(c, "moe_activation", "swiglu") != "swiglu":
+            return False
+        return all(getattr(b.mlp, "ep", None) is None for b in self.model.blocks if b.mlp is not None)
+
     def _norm_f32(self, acc: torch.Tensor, w: torch.Tensor, res: torch.Tensor):
         """RMSNorm whose input is an fp32 split-K accumulator (reset to zero as it is read)."""
         T, H = acc.shape
@@ -625,7 +635,7 @@ class SamplerEngine:
         return h
 
     def _run_steps(self, B: int, n: int) -> None:
-        if not self.use_cuda_graph or self.cfg.is_moe:
+        if not self.use_cuda_graph or (self.cfg.is_moe and not self._moe_graph_ok()):
             for _ in range(n):
                 self._decode_step(B)
             return

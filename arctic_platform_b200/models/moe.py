@@ -63,13 +63,25 @@ def route_topk(logits: torch.Tensor, k: int, renorm: bool, score_func: str = "so
                 best = quality.topk(topk_group, dim=-1).indices
                 allowed = torch.zeros_like(quality, dtype=torch.bool).scatter_(1, best, True)
                 pick = grouped.masked_fill(~allowed[:, :, None], float("-inf")).view(T, E)
-            idx = torch.topk(pick, k, dim=-1).indices
+            if pick.is_cuda and n_group <= 1 and pick.shape[-1] <= 512:
+                # one kernel: scores, selection bias, k rounds of arg-max (no sort, no host round trip)
+                from ..ops.rl_ops import moe_route
+                idx = moe_route(x, k, score_func, expert_bias)
+            else:
+                idx = torch.topk(pick, k, dim=-1).indices
     w = scores.gather(-1, idx)
     if renorm:
         w = w / (w.sum(-1, keepdim=True) + 1e-20)
     if route_scale != 1.0:
         w = w * route_scale
     return w, idx
+
+
+def _expert_histogram(idx: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Tokens per expert ``[E]`` (int64) without ``torch.bincount``, which sizes its result from the data and therefore
+    synchronises with the host."""
+    flat = idx.reshape(-1).to(torch.int64)
+    return torch.zeros(num_experts, dtype=torch.int64, device=flat.device).scatter_add_(0, flat, torch.ones_like(flat))
 
 
 def build_group_tiles(counts: torch.Tensor, n_out: int, device, bn: int = 128) -> torch.Tensor:
@@ -89,20 +101,64 @@ def build_group_tiles(counts: torch.Tensor, n_out: int, device, bn: int = 128) -
     return torch.tensor(tiles, dtype=torch.int32).to(device)
 
 
+_GROUPED_DEV = {}
+
+
+def _grouped_dev_fns():
+    if not _GROUPED_DEV:
+        import ctypes as c
+        from ..ops import _lib
+        vp, i, ll, f = c.c_void_p, c.c_int, c.c_longlong, c.c_float
+        _GROUPED_DEV["tiles"] = _lib.declare("apb_moe_group_tiles", [vp, i, i, i, vp, vp, i, i, vp, vp, vp])
+        _GROUPED_DEV["gemm"] = _lib.declare("apb_gemm_bf16_grouped_dev",
+                                            [vp, vp, vp, i, i, i, ll, ll, ll, i, f, vp, ll, vp, i, vp, ll, vp])
+    return _GROUPED_DEV
+
+
+def device_group_tiles(counts: torch.Tensor, rows: int, n_out1: int, n_out2: int):
+    """Tile tables of the two grouped expert GEMMs built by a kernel from ``counts [E]`` (int32, on the GPU): no copy
+    of the histogram to the host.  Returns ``(tiles1, tiles2, n_tiles [2], max1, max2)``; the tables are sized for the
+    worst case (every expert may add one partial 128-row block) and ``n_tiles`` holds the live sizes on the device."""
+    from ..ops import _lib
+    E = counts.numel()
+    max_blocks = (rows + 127) // 128 + E
+    max1, max2 = max_blocks * ((n_out1 + 127) // 128), max_blocks * ((n_out2 + 127) // 128)
+    dev = counts.device
+    t1 = torch.empty((max1, 4), dtype=torch.int32, device=dev)
+    t2 = torch.empty((max2, 4), dtype=torch.int32, device=dev)
+    n_tiles = torch.empty(2, dtype=torch.int32, device=dev)
+    _lib.check(_grouped_dev_fns()["tiles"](_lib.ptr(counts), E, n_out1, n_out2, _lib.ptr(t1), _lib.ptr(t2), max1, max2,
+                                           _lib.ptr(n_tiles), None, _lib.stream_ptr()), "apb_moe_group_tiles")
+    return t1, t2, n_tiles, max1, max2
+
+
 class _GroupedFFNFn(torch.autograd.Function):
-    """y[r] = W_down[e(r)] (silu(W_g[e(r)] x[r]) * (W_u[e(r)] x[r])) for rows sorted by expert."""
+    """y[r] = W_down[e(r)] (silu(W_g[e(r)] x[r]) * (W_u[e(r)] x[r])) for rows sorted by expert.  ``counts`` on the
+    GPU (int32): the forward builds its tile tables with a kernel and never synchronises with the host; ``counts`` on
+    the host: tables built in Python (the expert-parallel path, which knows its row counts already)."""
 
     @staticmethod
     def forward(ctx, x, wgu, wdown, counts):
+        from ..ops import _lib
         E, I2, H = wgu.shape
         I = I2 // 2
         R = x.shape[0]
-        t1 = build_group_tiles(counts, I2, x.device)
-        t2 = build_group_tiles(counts, H, x.device)
         gu = torch.empty((R, I2), device=x.device, dtype=x.dtype)
         act = torch.empty((R, I), device=x.device, dtype=x.dtype)
         y = torch.empty((R, H), device=x.device, dtype=x.dtype)
-        if R > 0:
+        if R > 0 and counts.is_cuda:
+            t1, t2, n_tiles, max1, max2 = device_group_tiles(counts, R, I2, H)
+            fn = _grouped_dev_fns()["gemm"]
+            w1, w2 = wgu.view(E * I2, H), wdown.view(E * H, I)
+            _lib.check(fn(_lib.ptr(x), _lib.ptr(w1), _lib.ptr(gu), R, I2, H, x.stride(0), w1.stride(0), gu.stride(0),
+                          gemm.EPI_SWIGLU, 1.0, _lib.ptr(act), act.stride(0), _lib.ptr(t1), max1, _lib.ptr(n_tiles),
+                          E * I2, _lib.stream_ptr()), "grouped gate/up")
+            _lib.check(fn(_lib.ptr(act), _lib.ptr(w2), _lib.ptr(y), R, H, I, act.stride(0), w2.stride(0), y.stride(0),
+                          gemm.EPI_BF16, 1.0, None, 0, _lib.ptr(t2), max2, _lib.ptr(n_tiles[1:]), E * H,
+                          _lib.stream_ptr()), "grouped down")
+        elif R > 0:
+            t1 = build_group_tiles(counts, I2, x.device)
+            t2 = build_group_tiles(counts, H, x.device)
             gemm.gemm_raw(x, wgu.view(E * I2, H), gu, M=R, N=I2, K=H, epi=gemm.EPI_SWIGLU, out2=act, tile_map=t1,
                           b_rows=E * I2, bn=128)
             gemm.gemm_raw(act, wdown.view(E * H, I), y, M=R, N=H, K=I, tile_map=t2, b_rows=E * H, bn=128)
@@ -113,6 +169,7 @@ class _GroupedFFNFn(torch.autograd.Function):
     def backward(ctx, dy):
         from ..ops import _lib
         x, wgu, wdown, gu, act, counts = ctx.saved_tensors
+        counts = counts.cpu()                 # the per-expert loops below are driven from the host (one copy per layer)
         E, I2, H = wgu.shape
         I = I2 // 2
         R = x.shape[0]
@@ -158,6 +215,8 @@ def grouped_ffn(x_sorted: torch.Tensor, wgu: torch.Tensor, wdown: torch.Tensor, 
             outs.append((torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ wdown[e].t())
             row += c
         return torch.cat(outs) if outs else x_sorted.new_zeros((0, wdown.shape[1]))
+    if counts.is_cuda and counts.numel() <= 512:
+        return _GroupedFFNFn.apply(x_sorted.contiguous(), wgu, wdown, counts.to(torch.int32))
     return _GroupedFFNFn.apply(x_sorted.contiguous(), wgu, wdown, counts.cpu())
 
 
@@ -214,13 +273,13 @@ class MoEFeedForward(nn.Module):
         if self.routing_log is not None:                         # a sampler records what it routed, pass by pass
             self.routing_log.append(idx.detach())
         if self.tokens_per_expert is not None and self.training and self.replay_mode != "replay":
-            self.tokens_per_expert += torch.bincount(idx.reshape(-1), minlength=cfg.num_experts).to(self.tokens_per_expert.dtype)
+            self.tokens_per_expert += _expert_histogram(idx, cfg.num_experts).to(self.tokens_per_expert.dtype)
         if self.ep is not None:
             return self.ep.forward(self, x, w, idx)
         k = cfg.num_experts_per_tok
         flat_e = idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
-        counts = torch.bincount(flat_e, minlength=cfg.num_experts)
+        counts = _expert_histogram(flat_e, cfg.num_experts)
         self.last_tokens_per_expert = counts.detach()
         src_tok = torch.div(order, k, rounding_mode="floor")
         xs = x.index_select(0, src_tok)

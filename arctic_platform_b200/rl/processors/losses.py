@@ -62,6 +62,44 @@ def _token_views(model_outputs: dict, batch: dict, device):
     return packed, take, mask, seq_ids
 
 
+def _verl_grpo_fused(lp, old, adv, mask, take, actor, agg_mode, info, meta, model_outputs, packed, device):
+    """The token-mean objective on a GPU: ONE kernel produces the loss statistics and the gradient with respect to
+    the log-probs (``csrc/rl_ops.cu``) instead of some thirty element-wise kernels plus their autograd graph.  Returns
+    ``None`` when the configuration needs the general path (sequence-mean aggregation, an entropy bonus, sequence
+    parallelism, no global token count)."""
+    from ...ops import rl_ops
+    use_kl = bool(actor.get("use_kl_loss", False))
+    kl_kind = actor.get("kl_loss_type", "low_var_kl") if use_kl else None
+    if (model_outputs.get("owned") is not None or info.get("count_mask") is not None
+            or not rl_ops.fused_grpo_supported(lp, agg_mode, info.get("batch_num_tokens"), kl_kind,
+                                               model_outputs.get("entropy") is not None)):
+        return None
+    ref = take("ref_log_prob") if use_kl else None
+    if use_kl and ref is None:
+        raise KeyError("use_kl_loss needs batch['ref_log_prob']")
+    kl_coef = float(actor.get("kl_loss_coef", 0.001)) if use_kl else 0.0
+    is_w = meta.get("rollout_is_weights")
+    weight = packed.gather_from_grid(to_device(is_w, device)).float() if is_w is not None else None
+    scale = float(info["dp_size"]) / float(info["batch_num_tokens"])
+    loss, sums = rl_ops.grpo_token_loss(lp, old, adv, mask, scale, ref_lp=ref, kl_kind=kl_kind, kl_coef=kl_coef,
+                                        weight=weight, clip_low=0.2, clip_high=0.2, clip_c=3.0)
+    ntok, clip_s, kl_s, lower_s, pg_s, kld_s = to_host(sums).tolist()[:6]      # the one device->host sync of the loss
+    metrics: Dict[str, Any] = {}
+    for name, v in (("actor/pg_clipfrac", clip_s), ("actor/ppo_kl", kl_s), ("actor/pg_clipfrac_lower", lower_s),
+                    ("actor/pg_loss", pg_s)):
+        metrics[name + ".sum"] = v
+        metrics[name + ".tokens"] = ntok
+    loss_sum = pg_s
+    if use_kl:
+        metrics["kl_loss.sum"] = kld_s
+        metrics["kl_loss.tokens"] = ntok
+        metrics["kl_coef"] = kl_coef
+        loss_sum += kl_coef * kld_s
+    metrics["loss.sum"] = loss_sum
+    metrics["loss.tokens"] = ntok
+    return loss, metrics
+
+
 @register_loss_fn("verl_grpo")
 def verl_grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, device) -> Tuple[torch.Tensor, dict]:
     actor = meta.get("actor_config", {}) or {}
@@ -75,6 +113,9 @@ def verl_grpo_loss(model_outputs: dict, batch: dict, meta: dict, config: dict, d
     adv = take("advantages")
     if old is None or adv is None:
         raise KeyError("verl_grpo needs batch['old_log_probs'] and batch['advantages']")
+    fused = _verl_grpo_fused(lp, old, adv, mask, take, actor, agg_mode, info, meta, model_outputs, packed, device)
+    if fused is not None:
+        return fused
     # the clip constants are fixed in the reference implementation (0.2 / 0.2 / 3.0) whatever the config says
     tok_loss, neg_kl, clipped, lower = ppo_clip_token_loss(lp, old, adv, 0.2, 0.2, 3.0)
     is_w = meta.get("rollout_is_weights")

@@ -70,14 +70,20 @@ def test_fp8_sampler_takes_its_matrices_from_the_sync_pass():
     """A colocated fp8 sampler: after the worker-level hand-over the sampler serves from the block-scaled copies the
     sync kernel wrote (no separate quantisation pass), and generation runs."""
     from arctic_platform_b200.engine.worker import EngineWorker
+    from arctic_platform_b200.models.config import PRESETS
+    from arctic_platform_b200.models.decoder import DecoderLM
     from arctic_platform_b200.ops import _lib
+    # every projection's inner dimension a multiple of 128 (the fp8 GEMM's scale blocks)
+    cfg = dataclasses.replace(PRESETS["qwen3-tiny-d128"], hidden_size=256, intermediate_size=512, num_heads=4,
+                              num_kv_heads=2, num_layers=2)
     job = {"model_name": "qwen3-tiny-d128", "seed": 5,
            "ds_config": {"zero_optimization": {"stage": 1}, "optimizer": {"params": {"lr": 1e-3}}}}
     tr, sm = EngineWorker(), EngineWorker()
-    tr.initialize({**job, "job_type": "training"})
+    tr.initialize({**job, "job_type": "training"}, model=DecoderLM(cfg, "cuda", torch.bfloat16).init_weights(seed=5))
     sm.initialize({**job, "job_type": "sampling", "seed": 99,
                    "vllm_config": {"kv_cache_tokens": 1 << 13, "max_num_seqs": 8, "max_model_len": 256,
-                                   "quantization": "fp8"}})
+                                   "quantization": "fp8"}},
+                  model=DecoderLM(cfg, "cuda", torch.bfloat16).init_weights(seed=99))
     assert sm.sampler.fp8 and sm.sampler._fp8_stale
     n = tr.sync_weights_to(sm)
     assert n > 0 and sm.sampler._sync_plan is not None and not sm.sampler._fp8_stale
