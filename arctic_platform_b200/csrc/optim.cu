@@ -212,7 +212,11 @@ gather_unit_kernel(PeerPtrs shards, GatherTable t, int rank, int world, __nv_bfl
 // shard_off = destination offset, vec_start counts float4 groups.  One flag barrier per launch.
 __global__ void __launch_bounds__(256)
 zero3_reduce_unit_kernel(PeerPtrs grads, GatherTable t, PeerPtrs flags, int rank, int world, int epoch, float scale,
-                         float* __restrict__ reduced, double* __restrict__ sumsq, int* status) {
+                         float* __restrict__ reduced, double* __restrict__ sumsq, int accumulate, int* status) {
+  // accumulate = 1 (gradients reduced unit by unit DURING the backward pass): the sums are ADDED to this rank's
+  // shard accumulator and every source range is cleared after it has been read (each element is read by exactly one
+  // rank, its owner), so the staging slot is zero on all ranks when the kernel has ended everywhere; the squares
+  // for the gradient norm are then taken from the accumulator at the optimizer step.
   if (!epoch_barrier(flags, rank, world, epoch, status)) return;
   const long long total = t.vec_start[t.n];
   double acc = 0.0;
@@ -224,7 +228,9 @@ zero3_reduce_unit_kernel(PeerPtrs grads, GatherTable t, PeerPtrs flags, int rank
     float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = 0; r < world; ++r) {
       const int src = (rank + r) % world;
-      const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(grads.p[src]) + t.full_off[pc] + off);
+      float4* sp = reinterpret_cast<float4*>(static_cast<float*>(grads.p[src]) + t.full_off[pc] + off);
+      const float4 v = *sp;
+      if (accumulate) *sp = make_float4(0.f, 0.f, 0.f, 0.f);
       s4.x += v.x;
       s4.y += v.y;
       s4.z += v.z;
@@ -234,7 +240,15 @@ zero3_reduce_unit_kernel(PeerPtrs grads, GatherTable t, PeerPtrs flags, int rank
     s4.y *= scale;
     s4.z *= scale;
     s4.w *= scale;
-    *reinterpret_cast<float4*>(reduced + t.shard_off[pc] + off) = s4;
+    float4* dst = reinterpret_cast<float4*>(reduced + t.shard_off[pc] + off);
+    if (accumulate) {
+      const float4 old = *dst;
+      s4.x += old.x;
+      s4.y += old.y;
+      s4.z += old.z;
+      s4.w += old.w;
+    }
+    *dst = s4;
     acc += static_cast<double>(s4.x) * s4.x + static_cast<double>(s4.y) * s4.y + static_cast<double>(s4.z) * s4.z +
            static_cast<double>(s4.w) * s4.w;
   }
@@ -242,7 +256,7 @@ zero3_reduce_unit_kernel(PeerPtrs grads, GatherTable t, PeerPtrs flags, int rank
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && !accumulate && sumsq) {
     double tt = 0.0;
     for (int w = 0; w < blockDim.x / 32; ++w) tt += red[w];
     atomicAdd(sumsq, tt);
@@ -360,7 +374,7 @@ int apb_gather_unit(void* const* shard_ptrs, int rank, int world, const long lon
 // rank's piece of parameter i inside the unit; piece_len[i] (multiple of 4); dst_off[i]: offset inside `reduced`.
 int apb_zero3_reduce_unit(void* const* grad_ptrs, void* const* flag_ptrs, int rank, int world, int epoch,
                           const long long* src_off, const long long* piece_len, const long long* dst_off, int n_pieces,
-                          float scale, float* reduced, double* sumsq, cudaStream_t s) {
+                          float scale, float* reduced, double* sumsq, int accumulate, cudaStream_t s) {
   if (world > kMaxRanks || n_pieces < 1 || n_pieces > kMaxGatherPieces) return kBadArgument;
   GatherTable t;
   t.n = n_pieces;
@@ -376,7 +390,8 @@ int apb_zero3_reduce_unit(void* const* grad_ptrs, void* const* flag_ptrs, int ra
   t.vec_start[n_pieces] = acc;
   zero3_reduce_unit_kernel<<<grid_for(acc > 0 ? acc : 1), 256, 0, s>>>(to_peers(grad_ptrs, world), t,
                                                                        to_peers(flag_ptrs, world), rank, world, epoch,
-                                                                       scale, reduced, sumsq, status_device_ptr());
+                                                                       scale, reduced, sumsq, accumulate,
+                                                                       status_device_ptr());
   return static_cast<int>(cudaGetLastError());
 }
 

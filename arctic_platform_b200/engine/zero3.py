@@ -250,7 +250,7 @@ class Zero3State:
                 arr = ctypes.c_longlong * n
                 _lib.check(fn(gp, flags_tbl, r, W, e.flags.next(), arr(*[p[1] + r * p[2] for p in part]),
                               arr(*[p[2] for p in part]), arr(*[base + p[3] for p in part]), n, 1.0 / W,
-                              _lib.ptr(e.reduced), _lib.ptr(e.sumsq), s), "apb_zero3_reduce_unit")
+                              _lib.ptr(e.reduced), _lib.ptr(e.sumsq), 0, s), "apb_zero3_reduce_unit")
 
     def reduced_pieces_collective(self) -> List[torch.Tensor]:
         """Per unit: this rank's shard of the averaged gradient (shard layout)."""
@@ -279,7 +279,7 @@ def _fused_reduce():
         c = ctypes
         _REDUCE = _lib.declare("apb_zero3_reduce_unit", [c.c_void_p, c.c_void_p, c.c_int, c.c_int, c.c_int, c.c_void_p,
                                                           c.c_void_p, c.c_void_p, c.c_int, c.c_float, c.c_void_p,
-                                                          c.c_void_p, c.c_void_p])
+                                                          c.c_void_p, c.c_int, c.c_void_p])
     return _REDUCE
 
 

@@ -38,6 +38,7 @@ def main():
     cfg = Qwen3Config(vocab_size=151936, hidden_size=2560, intermediate_size=9728, num_hidden_layers=36,
                       num_attention_heads=32, num_key_value_heads=8, head_dim=128, max_position_embeddings=40960,
                       rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=True, dtype="bfloat16")
+    cfg.architectures = ["Qwen3ForCausalLM"]
     d = tempfile.mkdtemp(prefix="qwen3_4b_cfg_")
     cfg.save_pretrained(d)
     # vLLM wants a tokenizer even when only token ids go in and come out: a word-level one built here, no download
@@ -48,7 +49,7 @@ def main():
     tok.pre_tokenizer = pre_tokenizers.Whitespace()
     PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", eos_token="<eos>", pad_token="<eos>").save_pretrained(d)
     t0 = time.perf_counter()
-    llm = LLM(model=d, tokenizer=d, load_format="dummy", dtype="bfloat16", enable_prefix_caching=True,
+    llm = LLM(model=d, tokenizer=d, runner="generate", load_format="dummy", dtype="bfloat16", enable_prefix_caching=True,
               max_model_len=args.prompt_len + args.max_tokens + 16, max_num_seqs=args.prompts * args.samples,
               gpu_memory_utilization=args.gpu_memory_utilization, seed=0)
     t_init = time.perf_counter() - t0
