@@ -63,6 +63,10 @@ class EngineConfig:
     # blocks stay gathered from one optimizer step to the next when they take at most a tenth of the device memory,
     # otherwise two alternating slots); DeepSpeed's ``zero_optimization.stage3_max_live_parameters`` sets it.
     zero3_max_live_parameters: int = -1
+    # stage 3 on GPUs: reduce every decoder block's gradient right after its backward (side stream, overlapped with
+    # the next block's backward) into this rank's fp32 shard accumulator, keeping only three block-sized staging
+    # buffers of full gradients instead of a full-size buffer (DeepSpeed: ``zero_optimization.overlap_comm``)
+    zero3_overlap_comm: bool = True
 
     @staticmethod
     def from_ds_config(ds_config: Optional[dict], training_config: Optional[dict] = None) -> "EngineConfig":
@@ -109,6 +113,8 @@ class EngineConfig:
         cfg.offload_optimizer = (zero.get("offload_optimizer") or {}).get("device", "none") == "cpu"
         if zero.get("stage3_max_live_parameters") is not None:
             cfg.zero3_max_live_parameters = int(float(zero["stage3_max_live_parameters"]))
+        if zero.get("overlap_comm") is not None:
+            cfg.zero3_overlap_comm = bool(zero["overlap_comm"])
         cfg.impl = ds.get("b200_impl", "fused")
         if (zero.get("offload_param") or {}).get("device", "none") not in ("none", None):
             import logging
@@ -262,13 +268,20 @@ class TrainEngine:
         self.param_buf = self.zero3.shard_buf   # what peers can read of this rank's parameters
         if self.forward_only:
             return
-        self.grad_buf = (SymmetricBuffer(self.total, torch.float32, self.device, self.group) if use_symm
-                         else SymmetricBuffer(self.total, torch.float32, self.device, False))
-        gflat = self.grad_buf.tensor
-        for u in self.units:
-            for name, p in u.params:
-                o, n, shape = self.param_slices[name]
-                p.grad_f32 = gflat[o:o + n].view(shape)
+        self.grad_stage = None
+        partition = (use_symm and self.cfg.zero3_overlap_comm and not self.cfg.gradient_checkpointing
+                     and not self.opt_on_host and self.cfg.adam_w_mode
+                     and os.environ.get("APB_ZERO3_OVERLAP", "1") != "0" and sum(self.zero3.is_block) >= 3)
+        if partition:
+            self._build_partitioned_grads()
+        else:
+            self.grad_buf = (SymmetricBuffer(self.total, torch.float32, self.device, self.group) if use_symm
+                             else SymmetricBuffer(self.total, torch.float32, self.device, False))
+            gflat = self.grad_buf.tensor
+            for u in self.units:
+                for name, p in u.params:
+                    o, n, shape = self.param_slices[name]
+                    p.grad_f32 = gflat[o:o + n].view(shape)
         init = self._zero3_state_from_params()
         self.master = self._new_opt_state(init.numel())
         self.master.copy_(init)
@@ -276,8 +289,53 @@ class TrainEngine:
         self.exp_avg = self._new_opt_state(self.shard_total).zero_()
         self.exp_avg_sq = self._new_opt_state(self.shard_total).zero_()
         self._build_host_staging()
-        self.reduced = torch.empty(self.shard_total, dtype=torch.float32, device=self.device)
+        self.reduced = torch.zeros(self.shard_total, dtype=torch.float32, device=self.device)
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.device)
+
+    def _build_partitioned_grads(self) -> None:
+        """Stage 3 without a full-size gradient buffer: the weight-gradient GEMMs of decoder block ``k`` accumulate
+        into staging buffer ``k % 3`` (symmetric memory, one block long); ``Zero3State.reduce_block_async`` sums the
+        block over the ranks into ``reduced`` as soon as its backward has been queued.  Units that are touched at
+        both ends of every pass (embedding / lm-head, final norm) and expert-parallel units keep a buffer of their
+        own and are reduced at the optimizer step."""
+        z = self.zero3
+        stage_len = max(u.length for u, b in zip(self.units, z.is_block) if b)
+        self.grad_stage = [SymmetricBuffer(stage_len, torch.float32, self.device, self.group) for _ in range(3)]
+        res_len, self.grad_res_off = 0, {}
+        for ui, u in enumerate(self.units):
+            if not z.is_block[ui]:
+                self.grad_res_off[ui] = res_len
+                res_len += u.length
+        self.grad_res = SymmetricBuffer(max(res_len, 8), torch.float32, self.device, self.group)
+        self.grad_buf = None
+        for ui, u in enumerate(self.units):
+            if z.is_block[ui]:
+                base, buf = 0, self.grad_stage[z.block_rank[ui] % 3].tensor
+            else:
+                base, buf = self.grad_res_off[ui], self.grad_res.tensor
+            for name, p in u.params:
+                o, n, shape = self.param_slices[name]
+                p.grad_f32 = buf[base + o - u.offset:base + o - u.offset + n].view(shape)
+        z.enable_overlapped_reduce()
+
+    def unit_grad_table(self, ui: int):
+        """Per-rank base pointers of unit ``ui``'s full fp32 gradient (ctypes array) -- one slice of the full-size
+        buffer, a staging buffer, or the resident buffer."""
+        u = self.units[ui]
+        if self.grad_stage is None:
+            return self.grad_buf.ptr_table(u.offset * 4)
+        if self.zero3.is_block[ui]:
+            return self.grad_stage[self.zero3.block_rank[ui] % 3].ptr_table(0)
+        return self.grad_res.ptr_table(self.grad_res_off[ui] * 4)
+
+    def unit_grad_tensor(self, ui: int) -> torch.Tensor:
+        u = self.units[ui]
+        if getattr(self, "grad_stage", None) is None:
+            return self.grad_buf.tensor[u.offset:u.offset + u.length]
+        if self.zero3.is_block[ui]:
+            return self.grad_stage[self.zero3.block_rank[ui] % 3].tensor[:u.length]
+        o = self.grad_res_off[ui]
+        return self.grad_res.tensor[o:o + u.length]
 
     # ------------------------------------------------------------------ optimizer state on the host
     @property
@@ -349,7 +407,12 @@ class TrainEngine:
 
     # ------------------------------------------------------------------ training loop pieces
     def zero_grad(self) -> None:
-        self.grad_buf.tensor.zero_()
+        if getattr(self, "grad_stage", None) is not None:
+            # the staging buffers were cleared by the reductions that read them; the shard accumulator starts over
+            self.grad_res.tensor.zero_()
+            self.reduced.zero_()
+        else:
+            self.grad_buf.tensor.zero_()
         for p in self.model.parameters():
             p.grad = None
 
@@ -371,8 +434,12 @@ class TrainEngine:
 
     def backward(self, loss: torch.Tensor) -> None:
         self.require_awake("backward")
+        if self.zero3 is not None:
+            self.zero3.begin_backward()
         loss.backward()
         self.collect_autograd_grads()
+        if self.zero3 is not None:
+            self.zero3.finish_backward()
         self.micro_steps += 1
 
     def collect_autograd_grads(self) -> None:
@@ -460,7 +527,7 @@ class TrainEngine:
 
     def _local_unit_reduce(self, u: Unit, so: int, fn_r, flags_tbl, s) -> None:
         """Expert-parallel unit: the local gradient is the whole gradient; scale it like the data-parallel mean."""
-        own = (ctypes.c_void_p * 1)(self.grad_buf.tensor.data_ptr() + u.offset * 4)
+        own = (ctypes.c_void_p * 1)(self.unit_grad_tensor(self.units.index(u)).data_ptr())
         _lib.check(fn_r(own, ctypes.c_void_p(0), flags_tbl, 0, 1, 0, 0, u.length, 1.0 / self.world,
                         ctypes.c_void_p(self.reduced.data_ptr() + so * 4), _lib.ptr(self.sumsq), s), "apb_zero_reduce")
 
@@ -481,10 +548,17 @@ class TrainEngine:
         when they materialise a unit)."""
         cfg = self.cfg
         z = self.zero3
-        z.reduce_pieces_fused(fn_r, flags_tbl, s)
+        z.reduce_pieces_fused(fn_r, flags_tbl, s)        # overlapped mode: only the units not reduced during backward
         for ui, (u, so) in enumerate(zip(self.units, self.unit_shard_off)):
             if u.local_only:
                 self._local_unit_reduce(u, so, fn_r, flags_tbl, s)
+        if self.grad_stage is not None:
+            # squares of the block shards that the backward-time reductions accumulated
+            fn_sq = _fused_fns()["sumsq"]
+            for ui, so in enumerate(self.unit_shard_off):
+                if z.is_block[ui]:
+                    _lib.check(fn_sq(ctypes.c_void_p(self.reduced.data_ptr() + so * 4), z.unit_shard_len[ui],
+                                     _lib.ptr(self.sumsq), s), "apb_sumsq_f32")
         dist.all_reduce(self.sumsq, group=self.group)
         self._grad_norm_tensor = self.sumsq.sqrt().float().clone()
         own = (ctypes.c_void_p * 1)()
@@ -737,4 +811,5 @@ def _fused_fns():
                                        [vp, vp, vp, i, i, i, ll, ll, vp, vp, vp, vp, vp, f, f, f, f, f, f, f, f, vp])
         _FUSED["wait"] = _lib.declare("apb_epoch_wait", [vp, i, i, i, vp])
         _FUSED["gather"] = _lib.declare("apb_gather_shards", [vp, vp, i, i, i, ll, vp, vp])
+        _FUSED["sumsq"] = _lib.declare("apb_sumsq_f32", [vp, ll, vp, vp])
     return _FUSED

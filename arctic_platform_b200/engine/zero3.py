@@ -15,8 +15,14 @@ of the device memory): then every block has a slot of its own and is gathered ON
 once per micro-batch pass -- with 16 micro-batches per step that removes 31 of 32 gathers per block.  The embedding /
 lm-head and the final norm stay gathered (they are touched at both ends of every pass).
 
-Gradients stay full-size in fp32 (accumulated locally over micro-batches); at the step every piece is reduced from
-all ranks by ``zero_reduce_kernel`` straight into the owner's shard layout (reduce-scatter by P2P loads).
+Gradients.  On GPUs with the fused kernels (``overlap_comm``, the default) a decoder block's gradient is reduced
+over the ranks right after the block's backward has been queued: its weight-gradient GEMMs accumulate into one of
+three block-sized fp32 staging buffers in symmetric memory, a backward hook launches ``zero3_reduce_unit_kernel`` on a
+side stream (every rank pulls ITS shard range from all ranks' staging buffers, adds it to its fp32 shard accumulator
+and clears what it read), and the next block's backward runs meanwhile.  A rank therefore holds three blocks of full
+gradient plus its 1/world shard accumulator instead of a full-size buffer -- what lets the 32B recipes fit.  Without
+the overlap (CPU / gloo, the collective baseline, activation checkpointing) gradients stay full-size in fp32,
+accumulated locally over micro-batches, and are reduced piece by piece at the optimizer step.
 
 CPU / gloo runs use the same bookkeeping with ``all_gather`` / ``all_reduce``, which is what the equivalence test
 against stage 1 exercises.  The reference delegates all of this to DeepSpeed (``zero_optimization.stage: 3``,
@@ -108,6 +114,7 @@ class Zero3State:
         self.gather_ctas = int(os.environ.get("APB_ZERO3_GATHER_CTAS", "128"))   # SMs lent to a prefetch
         for ui in self.resident:
             self._gather(ui, self.resident[ui])
+        self.overlap = False               # set by enable_overlapped_reduce()
         self._install_hooks()
 
     def _choose_slot_count(self, block_lens: List[int], max_block: int, dt: torch.dtype) -> int:
@@ -223,15 +230,96 @@ class Zero3State:
         def bwd_pre(i):
             def hook(_mod, _grad_out):
                 ui = unit_of_block[i]
+                if self.overlap:
+                    self._before_block_backward(ui)
                 self.ensure(ui)
                 if i - 1 >= 0:
                     self.prefetch(unit_of_block[i - 1])
+            return hook
+
+        def bwd_post(i):
+            def hook(_mod, _grad_in, _grad_out):
+                if self.overlap:
+                    self.reduce_block_async(unit_of_block[i])
             return hook
 
         for i, blk in enumerate(blocks):
             blk.register_forward_pre_hook(fwd_pre(i))
             if not self.e.forward_only:
                 blk.register_full_backward_pre_hook(bwd_pre(i))
+                blk.register_full_backward_hook(bwd_post(i))
+
+    # ------------------------------------------------------------------ gradient reduction overlapped with backward
+    def enable_overlapped_reduce(self) -> None:
+        """Called by the engine once the staging buffers exist.  The reductions run on their own stream with their
+        own flag set: epochs are compared with ``>=``, so kernels of two streams must never share one counter."""
+        from ..parallel.symm import EpochFlags
+        e = self.e
+        self.overlap = True
+        self.side_r = torch.cuda.Stream(device=e.device)
+        self.flags_r = EpochFlags(e.device, e.group)
+        self.reduce_done: Dict[int, torch.cuda.Event] = {}       # block unit -> its reduction has finished here
+        self.pass_done: Optional[torch.cuda.Event] = None        # every rank finished the previous pass's reductions
+        self._unit_of_rank = {k: ui for ui, k in self.block_rank.items()}
+        self._wait_fn = None
+
+    def begin_backward(self) -> None:
+        if self.overlap:
+            self.reduce_done = {}
+
+    def _before_block_backward(self, ui: int) -> None:
+        """Block ``ui`` is about to accumulate into staging buffer ``rank % 3``.  Its previous user -- the block three
+        positions later in this pass, or a block of the previous pass -- has been read and cleared by ALL ranks once
+        this rank's reduction of the block TWO positions later has finished (every rank enters that kernel's barrier
+        only after its own earlier reductions), or, at the start of a pass, once the end-of-pass barrier has."""
+        main = torch.cuda.current_stream(self.e.device)
+        k = self.block_rank[ui]
+        ev = self.reduce_done.get(self._unit_of_rank.get(k + 2, -1))
+        if ev is not None:
+            main.wait_event(ev)
+        elif self.pass_done is not None:
+            main.wait_event(self.pass_done)
+
+    def reduce_block_async(self, ui: int) -> None:
+        e = self.e
+        W, r = e.world, e.rank
+        main = torch.cuda.current_stream(e.device)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        self.side_r.wait_event(ready)
+        fn = _fused_reduce()
+        base = e.unit_shard_off[ui]
+        rows = self.pieces[ui]
+        gp = e.unit_grad_table(ui)
+        with torch.cuda.stream(self.side_r):
+            s = _lib.stream_ptr(self.side_r)
+            for lo in range(0, len(rows), 24):
+                part = rows[lo:lo + 24]
+                n = len(part)
+                arr = ctypes.c_longlong * n
+                _lib.check(fn(gp, self.flags_r.ptr_table(), r, W, self.flags_r.next(),
+                              arr(*[p[1] + r * p[2] for p in part]), arr(*[p[2] for p in part]),
+                              arr(*[base + p[3] for p in part]), n, 1.0 / W, _lib.ptr(e.reduced), None, 1, s),
+                           "apb_zero3_reduce_unit")
+            done = torch.cuda.Event()
+            done.record(self.side_r)
+        self.reduce_done[ui] = done
+
+    def finish_backward(self) -> None:
+        """End of a backward pass: one more barrier on the reduction stream (all ranks have finished reading and
+        clearing every staging buffer), and the main stream joins it -- the optimizer step, or the next pass's first
+        blocks, must see the completed shard accumulator / cleared buffers."""
+        if not self.overlap:
+            return
+        e = self.e
+        from .trainer import _fused_fns
+        with torch.cuda.stream(self.side_r):
+            _lib.check(_fused_fns()["wait"](self.flags_r.ptr_table(), e.rank, e.world, self.flags_r.next(),
+                                            _lib.stream_ptr(self.side_r)), "apb_epoch_wait")
+            ev = torch.cuda.Event()
+            ev.record(self.side_r)
+        self.pass_done = ev
+        torch.cuda.current_stream(e.device).wait_event(ev)
 
     # ------------------------------------------------------------------ optimizer step
     def reduce_pieces_fused(self, fn_r, flags_tbl, s) -> None:
@@ -239,11 +327,11 @@ class Zero3State:
         W, r = e.world, e.rank
         fn = _fused_reduce()
         for ui, u in enumerate(e.units):
-            if u.local_only:
+            if u.local_only or (self.overlap and self.is_block[ui]):
                 continue
             base = e.unit_shard_off[ui]
             rows = self.pieces[ui]
-            gp = e.grad_buf.ptr_table(u.offset * 4)
+            gp = e.unit_grad_table(ui)
             for lo in range(0, len(rows), 24):                     # one launch (one flag barrier) per 24 parameters
                 part = rows[lo:lo + 24]
                 n = len(part)
@@ -256,10 +344,9 @@ class Zero3State:
         """Per unit: this rank's shard of the averaged gradient (shard layout)."""
         e = self.e
         W, r = e.world, e.rank
-        g = e.grad_buf.tensor
         out = []
         for ui, u in enumerate(e.units):
-            gu = g[u.offset:u.offset + u.length]
+            gu = e.unit_grad_tensor(ui)
             if u.local_only:
                 out.append(gu / W)               # complete on this rank
                 continue

@@ -180,9 +180,16 @@ def _zero3_main(rank, world, port, out_dir):
         mbs = [build_packed_batch(ids[m], mask[m], R).to("cuda")
                for m in (slice(sl.start, sl.start + half), slice(sl.start + half, sl.stop))]
         res = {}
-        for name, stage, impl in (("z1", 1, "fused"), ("z3", 3, "fused"), ("z3c", 3, "collective")):
-            model = DecoderLM(PRESETS["qwen3-tiny-d128"], "cuda", torch.bfloat16).init_weights(seed=11)
-            eng = TrainEngine(model, EngineConfig(lr=1e-3, weight_decay=0.01, max_grad_norm=0.5, impl=impl, zero_stage=stage))
+        import dataclasses
+        cfg5 = dataclasses.replace(PRESETS["qwen3-tiny-d128"], num_layers=5)   # enough blocks for the 3 staging buffers
+        for name, stage, impl, overlap in (("z1", 1, "fused", True), ("z3", 3, "fused", True), ("z3n", 3, "fused", False),
+                                           ("z3c", 3, "collective", True)):
+            model = DecoderLM(cfg5, "cuda", torch.bfloat16).init_weights(seed=11)
+            eng = TrainEngine(model, EngineConfig(lr=1e-3, weight_decay=0.01, max_grad_norm=0.5, impl=impl, zero_stage=stage,
+                                                  zero3_overlap_comm=overlap))
+            if stage == 3:
+                # gradients reduced block by block during backward (three staging buffers) vs one full-size buffer
+                assert (eng.grad_stage is not None) == (name == "z3")
             norms, losses = [], []
             for _step in range(2):
                 for i, pb in enumerate(mbs):                      # two micro-batches per step (slots are re-gathered)
@@ -218,7 +225,7 @@ def test_zero3_sharded_parameters_match_replicated_on_two_gpus():
         mp.spawn(_zero3_main, args=(2, _free_port(), d), nprocs=2, join=True)
         res = [torch.load(os.path.join(d, f"z{r}.pt"), weights_only=False) for r in range(2)]
     for r in res:
-        for other in ("z3", "z3c"):
+        for other in ("z3", "z3n", "z3c"):
             assert all(abs(a - b) <= 2e-2 * abs(b) + 1e-4 for a, b in zip(r[other][1], r["z1"][1])), (r[other][1], r["z1"][1])
             assert all(abs(a - b) <= 2e-2 * abs(b) + 2e-3 for a, b in zip(r[other][2], r["z1"][2]))
             assert (r[other][0] - r["z1"][0]).abs().max() < 2e-2
