@@ -194,7 +194,8 @@ def main(argv=None) -> None:
     if args.verbose:
         print(f"[server] cluster: {cluster}", flush=True)
     core = ArcticRLServerCore(training_gpus=args.training_gpus, sampling_gpus=args.sampling_gpus,
-                              log_prob_gpus=args.log_prob_gpus, colocate=args.colocate)
+                              log_prob_gpus=args.log_prob_gpus, colocate=args.colocate,
+                              log_prob_engine=args.log_prob_engine)
     if args.worker_watchdog_seconds > 0:
         core.start_worker_watchdog(args.worker_watchdog_seconds)
     uvicorn.run(create_app(core), host=args.host, port=args.port, log_level="info" if args.verbose else "warning")

@@ -169,8 +169,14 @@ def default_worker_factory(job_config: Dict[str, Any], rank: int, world: int):
 class ArcticRLServerCore:
     def __init__(self, worker_factory: Optional[Callable] = None, training_gpus: int = 0,
                  sampling_gpus: int = 0, log_prob_gpus: int = 0, colocate: bool = False,
-                 heartbeat_timeout: float = 0.0, master_port: Optional[int] = None):
+                 heartbeat_timeout: float = 0.0, master_port: Optional[int] = None,
+                 log_prob_engine: str = "deepspeed"):
         self.gpus = {"training": training_gpus, "sampling": sampling_gpus, "log_prob": log_prob_gpus}
+        # which engine serves log-prob jobs: "deepspeed" = a forward-only training engine (ZeRO shards, packed
+        # layout), "vllm" = the sampler's engine and weights layout (arctic_platform/common/ray_server.py:141-201)
+        if log_prob_engine not in ("deepspeed", "vllm"):
+            raise ValueError(f"log_prob_engine must be 'deepspeed' or 'vllm', got {log_prob_engine!r}")
+        self.log_prob_engine = log_prob_engine
         self.pool = None
         if worker_factory is None:
             ranks = max(int(training_gpus or 0), int(log_prob_gpus or 0))
@@ -204,6 +210,8 @@ class ArcticRLServerCore:
         job_type = job_config.get("job_type", "training")
         if job_type not in ("training", "sampling", "log_prob"):
             raise JobError(400, f"unknown job_type {job_type!r}")
+        if job_type == "log_prob":
+            job_config = {**job_config, "log_prob_engine": job_config.get("log_prob_engine") or self.log_prob_engine}
         n = int(job_config.get("num_devices") or self.gpus.get(job_type) or 1)
         tp = int((job_config.get("vllm_config") or {}).get("tensor_parallel_size", 1) or 1) if job_type == "sampling" else 1
         # (an SPMD launch -- one client and one in-process worker per rank -- forms its replicas over the launcher's
@@ -502,17 +510,34 @@ class ArcticRLServerCore:
             active = [(ws, idx) for ws, idx in zip(replicas, share) if idx]
             flat = [(w, idx) for ws, idx in active for w in ws]          # all ranks of a replica score the same share
             outs = call_all([w for w, _ in flat], "score_completions",
-                            [([prompts[i] for i in idx], [completions[i] for i in idx]) for _, idx in flat],
+                            [([prompts[i] for i in idx], [completions[i] for i in idx], int(top_k)) for _, idx in flat],
                             peer_grace_s=None)
             firsts, k = [], 0
             for ws, _idx in active:
                 firsts.append(outs[k])
                 k += len(ws)
             rows = [None] * len(prompts)
+            tops = [None] * len(prompts)
             for (_, idx), res in zip(active, firsts):
-                for i, r in zip(idx, res):
-                    rows[i] = r
-            return {"job_id": job.job_id, "log_probs": rows}
+                lp_rows, top_rows = (res["log_probs"], res["top_log_probs"]) if isinstance(res, dict) else (res, None)
+                for j, i in enumerate(idx):
+                    rows[i] = lp_rows[j]
+                    if top_rows is not None:
+                        tops[i] = top_rows[j]
+            out = {"job_id": job.job_id, "log_probs": rows}
+            if int(top_k) > 1:
+                out["top_log_probs"] = tops
+            return out
+        if int(top_k) > 1:
+            # the k most likely tokens per position need the whole distribution: one packed pass on every rank's share
+            share = [list(range(r, len(prompts), len(job.workers))) for r in range(len(job.workers))]
+            outs = call_all(job.workers, "score_completions",
+                            [([prompts[i] for i in idx], [completions[i] for i in idx], int(top_k)) for idx in share])
+            rows, tops = [None] * len(prompts), [None] * len(prompts)
+            for idx, res in zip(share, outs):
+                for j, i in enumerate(idx):
+                    rows[i], tops[i] = res["log_probs"][j], res["top_log_probs"][j]
+            return {"job_id": job.job_id, "log_probs": rows, "top_log_probs": tops}
         rows = []
         P = max(len(p) for p in prompts)
         R = max(len(c) for c in completions)

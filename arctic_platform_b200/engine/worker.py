@@ -43,6 +43,17 @@ def split_microbatches(batch: Dict[str, torch.Tensor], n: int) -> List[Dict[str,
     return outs
 
 
+class _ScoringView:
+    """What the forward-only pipeline needs of an engine -- the model -- for a log-prob job that is served by a
+    sampler's engine (``log_prob_engine = vllm``): no optimizer state, no gradient buffers."""
+
+    def __init__(self, model):
+        self.model = model
+
+    def backward(self, _loss):
+        raise RuntimeError("a log-prob job on the sampler's engine cannot train")
+
+
 def _loss_free_row(batch: Dict[str, Any]) -> Dict[str, Any]:
     """One row of ``batch`` that contributes nothing to the loss (masks and labels cleared), marked ``_dummy`` so that
     its outputs are dropped: a filler pass that keeps a rank in step with its peers' collectives."""
@@ -119,7 +130,9 @@ class EngineWorker:
             self._ensure_process_group(job_config)
         if self.job_type == "sampling" and tp > 1:
             return self._initialize_tp_sampler(job_config, model, tp, dtype, seed)
-        if self.job_type == "sampling":
+        scorer = (self.job_type == "log_prob" and job_config.get("log_prob_engine") == "vllm"
+                  and self.world == 1 and self.model_cfg.layer_types is None)
+        if self.job_type == "sampling" or scorer:
             from .sampler import SamplerEngine
             vc = dict(job_config.get("vllm_config") or {})
             m = model if model is not None else self._load_model(job_config, dtype, seed)
@@ -131,6 +144,11 @@ class EngineWorker:
                 from .hybrid_sampler import HybridSampler as SamplerEngine      # noqa: F811
             elif self.device.type != "cuda":
                 from .reference_sampler import ReferenceSampler as SamplerEngine   # noqa: F811  (CPU: recompute sampler)
+            if scorer:
+                # a log-prob job on the sampler's engine: it only scores (teacher-forced passes), so a token of KV
+                # cache is enough; it receives weights like a sampler does
+                vc.setdefault("kv_cache_tokens", 1024)
+                vc.setdefault("max_num_seqs", 8)
             self.sampler = SamplerEngine(
                 self.model_cfg, self.device, model=m,
                 kv_cache_tokens=int(vc.get("kv_cache_tokens", 1 << 20)), max_batch=int(vc.get("max_num_seqs", 256)),
@@ -290,7 +308,10 @@ class EngineWorker:
 
     # ------------------------------------------------------------------ forward / backward / step
     def _forward_maybe_backward(self, batch, meta, processing, backward: bool) -> Dict[str, Any]:
-        if self.engine is None:
+        engine = self.engine
+        if engine is None and self.sampler is not None and not backward and self.job_type == "log_prob":
+            engine = _ScoringView(self.sampler.model)      # log-prob job served by the sampler's engine and weights
+        if engine is None:
             raise RuntimeError("worker has no training/log-prob engine")
         t0 = time.perf_counter()
         row_order = None
@@ -315,7 +336,7 @@ class EngineWorker:
                     log_dp_shard_tokens(self.rank, f"{tag} micro-batch {i}", mb, meta)
                 offload = self.activation_offload if backward else None
                 with nvtx_range(f"{tag}/mb{i}", enabled=self._nvtx), (offload or contextlib.nullcontext()):
-                    r = run_pipeline(self.engine, mb, meta, processing, self.device, backward=backward, return_tensors=True)
+                    r = run_pipeline(engine, mb, meta, processing, self.device, backward=backward, return_tensors=True)
                 if offload is not None:
                     offload.release()
                 per_mb.append(r["metrics"])
@@ -457,10 +478,12 @@ class EngineWorker:
         return r["batch"]["log_probs"][:, 1:]
 
     @torch.no_grad()
-    def score_completions(self, prompts, completions) -> List[List[float]]:
+    def score_completions(self, prompts, completions, top_k: int = 1):
         """Log-probability of every completion token given its prompt, under this worker's CURRENT weights -- the
         sampler's when the worker hosts one (what the rollouts were drawn from), else the engine's.  One packed
-        pass; identical prompts are computed once."""
+        pass; identical prompts are computed once.  ``top_k`` > 1 also returns, per completion position, the ``k``
+        most likely tokens with their log-probs (``{"log_probs": rows, "top_log_probs": [[{token: lp}]]}``), which
+        the reference takes from its sampler's ``prompt_logprobs`` (arctic_platform/common/http_server.py:949)."""
         from ..models.decoder import token_logprobs
         from ..rl.zorro_train.layout import build_packed_batch
         model = self._target_model()
@@ -481,9 +504,31 @@ class EngineWorker:
         was_training = model.training
         model.eval()
         lp, _ = token_logprobs(model, pk, 1.0, with_entropy=False)
-        model.train(was_training)
         grid = pk.scatter_to_grid(lp.float()).cpu()
-        return [grid[i, :len(c)].tolist() for i, c in enumerate(completions)]
+        rows = [grid[i, :len(c)].tolist() for i, c in enumerate(completions)]
+        if int(top_k) <= 1:
+            model.train(was_training)
+            return rows
+        # the whole distribution at the prediction rows, a chunk of rows at a time
+        k = int(top_k)
+        h = model.forward_hidden(pk.input_ids, pk.positions, pk.layout).index_select(0, pk.pred_index)
+        W = model.output_weight
+        N = h.shape[0]
+        top_lp = torch.empty((N, k), dtype=torch.float32, device=h.device)
+        top_id = torch.empty((N, k), dtype=torch.int64, device=h.device)
+        for r0 in range(0, N, 2048):
+            z = torch.log_softmax((h[r0:r0 + 2048].float() @ W.float().t()), -1)
+            top_lp[r0:r0 + 2048], top_id[r0:r0 + 2048] = torch.topk(z, k, dim=-1)
+        model.train(was_training)
+        R_ = pk.response_length
+        lp_grid = torch.zeros((len(prompts) * R_, k), dtype=torch.float32)
+        id_grid = torch.zeros((len(prompts) * R_, k), dtype=torch.int64)
+        oi = pk.out_index.cpu()
+        lp_grid[oi], id_grid[oi] = top_lp.cpu(), top_id.cpu()
+        lp_grid, id_grid = lp_grid.view(len(prompts), R_, k), id_grid.view(len(prompts), R_, k)
+        tops = [[{int(t): float(v) for t, v in zip(id_grid[i, j].tolist(), lp_grid[i, j].tolist())}
+                 for j in range(len(c))] for i, c in enumerate(completions)]
+        return {"log_probs": rows, "top_log_probs": tops}
 
     # ------------------------------------------------------------------ rollout
     def _tokenizer_for(self):

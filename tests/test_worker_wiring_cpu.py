@@ -160,3 +160,29 @@ def test_sampler_worker_uses_the_tokenizer_that_ships_with_a_checkpoint(tmp_path
     assert (tmp_path / "export" / "tokenizer.json").exists() and (tmp_path / "export" / "config.json").exists()
     from transformers import AutoTokenizer
     assert AutoTokenizer.from_pretrained(str(tmp_path / "export"), local_files_only=True).encode("w5 w6", add_special_tokens=False) == [5, 6]
+
+
+def test_log_prob_top_k_and_scoring_engine_choice():
+    """``log_probs(top_k > 1)`` returns the k most likely tokens per completion position (the chosen token's own
+    log-prob stays in ``log_probs``), and the server hands ``log_prob_engine`` to its log-prob jobs."""
+    import torch
+    from arctic_platform_b200.common.server import ArcticRLServerCore
+    core = ArcticRLServerCore(log_prob_engine="vllm")
+    try:
+        jid = core.initialize({"model_name": "qwen3-tiny", "job_type": "log_prob", "seed": 3})["job_id"]
+        assert core.jobs[jid].config["log_prob_engine"] == "vllm"
+        prompts, completions = [[5, 6, 7, 8], [9, 10, 11]], [[12, 13, 14], [15, 16]]
+        one = core.log_probs(jid, prompts, completions)
+        top = core.log_probs(jid, prompts, completions, top_k=3)
+        assert "top_log_probs" not in one and len(top["top_log_probs"]) == 2
+        for rows, tops, comp in zip(top["log_probs"], top["top_log_probs"], completions):
+            assert len(rows) == len(tops) == len(comp)
+            for lp, cand, tok in zip(rows, tops, comp):
+                assert len(cand) == 3 and max(cand.values()) >= lp - 1e-4
+                if tok in cand:
+                    assert cand[tok] == pytest.approx(lp, abs=1e-4)
+        assert one["log_probs"][0] == pytest.approx(top["log_probs"][0], abs=1e-5)
+    finally:
+        core.destroy()
+    with pytest.raises(ValueError):
+        ArcticRLServerCore(log_prob_engine="other")
