@@ -178,6 +178,10 @@ class _TPDecode:
         self.epoch = torch.ones(1, device=device, dtype=torch.int32)      # 0 is what fresh flags hold
         self.done = torch.zeros(1, device=device, dtype=torch.int32)
         self._calls = 0
+        # APB_TP_DECODE=nccl: the library shape of the same step (local bf16 GEMM, NCCL all-reduce, residual + norm
+        # kernel on every rank) -- the twin the decode benchmark times the fused kernels against
+        self.library_twin = os.environ.get("APB_TP_DECODE", "fused") == "nccl"
+        self.twin_stream: Optional[torch.Tensor] = None
         c = ctypes
         vp, i, ll, f = c.c_void_p, c.c_int, c.c_longlong, c.c_float
         self._rs = _lib.declare("apb_gemm_rs", [vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, vp])
@@ -192,6 +196,12 @@ class _TPDecode:
         """``RMSNorm(residual += sum over ranks of x @ w_local^T) * norm_w`` for all ``B`` rows, on every rank."""
         k = self._calls
         self._calls += 1
+        if self.library_twin:
+            import torch.distributed as dist
+            y = gemm.matmul_nt(x, w_local)
+            dist.all_reduce(y, group=self.group)
+            h, self.twin_stream = norm.rmsnorm(y, norm_w, eps, self.twin_stream)
+            return h
         acc, hb = self.acc[k & 1], self.hbuf[k & 1]
         rl = B // self.world
         s = _lib.stream_ptr()
@@ -205,6 +215,8 @@ class _TPDecode:
     def end_step(self) -> None:
         if self._calls & 1:
             raise RuntimeError("a decode step must use the accumulator pair an even number of times")
+        if self.library_twin:
+            return
         _lib.check(self._adv(_lib.ptr(self.epoch), 2 * self._calls, _lib.stream_ptr()), "apb_tp_epoch_advance")
 
 
@@ -608,6 +620,7 @@ class SamplerEngine:
         t.begin_step()
         # the residual stream is carried for this rank's rows only
         t.resid[:rl].copy_(x[self.tp_rank * rl:(self.tp_rank + 1) * rl])
+        t.twin_stream = x
         h, _ = norm.rmsnorm(x, self.model.blocks[0].ln1, c.rms_norm_eps, None)
         for li in range(c.num_layers):
             blk = self.model.blocks[li]

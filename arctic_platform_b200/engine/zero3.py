@@ -15,14 +15,15 @@ of the device memory): then every block has a slot of its own and is gathered ON
 once per micro-batch pass -- with 16 micro-batches per step that removes 31 of 32 gathers per block.  The embedding /
 lm-head and the final norm stay gathered (they are touched at both ends of every pass).
 
-Gradients.  On GPUs with the fused kernels (``overlap_comm``, the default) a decoder block's gradient is reduced
-over the ranks right after the block's backward has been queued: its weight-gradient GEMMs accumulate into one of
+Gradients.  On GPUs with the fused kernels and ``overlap_comm`` (automatic: models whose full-size fp32 gradient
+buffer would take more than a tenth of the device memory) a decoder block's gradient is reduced over the ranks right after the block's backward has been queued: its weight-gradient GEMMs accumulate into one of
 three block-sized fp32 staging buffers in symmetric memory, a backward hook launches ``zero3_reduce_unit_kernel`` on a
 side stream (every rank pulls ITS shard range from all ranks' staging buffers, adds it to its fp32 shard accumulator
 and clears what it read), and the next block's backward runs meanwhile.  A rank therefore holds three blocks of full
 gradient plus its 1/world shard accumulator instead of a full-size buffer -- what lets the 32B recipes fit.  Without
-the overlap (CPU / gloo, the collective baseline, activation checkpointing) gradients stay full-size in fp32,
-accumulated locally over micro-batches, and are reduced piece by piece at the optimizer step.
+the overlap (small models, CPU / gloo, the collective baseline, activation checkpointing) gradients stay full-size
+in fp32, accumulated locally over micro-batches, and are reduced piece by piece at the optimizer step -- one
+reduction per step instead of one per micro-batch, which is the faster choice while the buffer fits.
 
 CPU / gloo runs use the same bookkeeping with ``all_gather`` / ``all_reduce``, which is what the equivalence test
 against stage 1 exercises.  The reference delegates all of this to DeepSpeed (``zero_optimization.stage: 3``,
