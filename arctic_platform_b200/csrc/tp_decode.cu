@@ -2,11 +2,15 @@
 // follows it and the all-gather of the normalised rows.
 //
 // In a tensor-parallel replica of T ranks the output projection and the down projection are split along their
-// input dimension, so every rank holds a partial [B, H] result.  apb_gemm_rs adds each partial row straight from
-// the GEMM epilogue into the fp32 accumulator of the rank that OWNS the row (rows are dealt out in T contiguous
-// blocks).  This kernel then runs on every rank, one CTA per owned row:
-//   1. epoch barrier A -- every rank has launched this kernel, i.e. every rank's GEMM has finished adding;
-//   2. row = accumulator (+ residual stream of the row), accumulator cleared for its next use;
+// input dimension, so every rank holds a partial [B, H] result, which its GEMM leaves in a LOCAL fp32 buffer in
+// symmetric memory (split-K partials meet there through local red.add).  Rows are dealt out to the ranks in T
+// contiguous blocks.  This kernel then runs on every rank, one CTA per owned row:
+//   0. the partial buffer of the PREVIOUS call (all of its readers passed that call's barrier B) is cleared for its
+//      next use while the ranks gather at barrier A;
+//   1. epoch barrier A -- every rank has launched this kernel, i.e. every rank's partial is complete;
+//   2. row = sum over ranks of their partial row, pulled with plain 16-byte peer loads (a reduce-scatter by
+//      reading: 1/T of every peer's buffer crosses NVLink once, as full-width loads instead of fp32 atomics, which
+//      measured ~25 us slower per projection at T = 8), plus the residual stream of the row;
 //   3. the new residual row stays local (bf16); RMSNorm(row) * w is stored as bf16 into the activation buffer of
 //      EVERY rank at the row's global position (plain peer stores over NVLink): the all-gather;
 //   4. the last CTA to finish announces epoch B to all ranks, and every CTA waits until all ranks have announced
@@ -26,16 +30,23 @@ constexpr int kTpNormThreads = 256;
 
 __global__ void __launch_bounds__(kTpNormThreads)
 tp_norm_allgather_kernel(PeerPtrs flags, int rank, int world, const int* __restrict__ epoch_base, int epoch_off,
-                         float* __restrict__ acc, __nv_bfloat16* __restrict__ resid, int has_resid,
+                         PeerPtrs part_ptrs, float4* __restrict__ clear_buf, long long clear_vec4,
+                         __nv_bfloat16* __restrict__ resid, int has_resid,
                          const __nv_bfloat16* __restrict__ w, float eps, PeerPtrs out_ptrs, int rows_local, int H,
                          int* __restrict__ done_counter, int* status) {
   pdl_entry();
+  if (clear_buf) {
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (long long i = static_cast<long long>(blockIdx.x) * kTpNormThreads + threadIdx.x; i < clear_vec4;
+         i += static_cast<long long>(gridDim.x) * kTpNormThreads)
+      clear_buf[i] = z;
+  }
   const int epoch_a = *epoch_base + epoch_off;
   if (!epoch_barrier(flags, rank, world, epoch_a, status)) return;
   __shared__ float red[kTpNormThreads / 32];
   __shared__ int last_s;
   const int row = blockIdx.x;  // gridDim.x == rows_local
-  float* a = acc + static_cast<long long>(row) * H;
+  const long long grow = static_cast<long long>(rank) * rows_local + row;
   __nv_bfloat16* rs = resid + static_cast<long long>(row) * H;
   // pass 1: x = acc (+ residual); keep x in registers (H <= 256 * 8 * 4)
   float x[4][8];
@@ -45,12 +56,17 @@ tp_norm_allgather_kernel(PeerPtrs flags, int rank, int world, const int* __restr
   for (int k = 0; k < 4; ++k) {
     const int v = threadIdx.x + k * kTpNormThreads;
     if (v < nv) {
-      const float4 p0 = *reinterpret_cast<const float4*>(a + v * 8);
-      const float4 p1 = *reinterpret_cast<const float4*>(a + v * 8 + 4);
-      x[k][0] = p0.x; x[k][1] = p0.y; x[k][2] = p0.z; x[k][3] = p0.w;
-      x[k][4] = p1.x; x[k][5] = p1.y; x[k][6] = p1.z; x[k][7] = p1.w;
-      *reinterpret_cast<float4*>(a + v * 8) = make_float4(0.f, 0.f, 0.f, 0.f);
-      *reinterpret_cast<float4*>(a + v * 8 + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[k][j] = 0.f;
+      // own partial first, then the peers in ring order so that the ranks do not all read the same peer at once
+      for (int i = 0; i < world; ++i) {
+        const int r = (rank + i) % world;
+        const float* a = static_cast<const float*>(part_ptrs.p[r]) + grow * H + v * 8;
+        const float4 p0 = *reinterpret_cast<const float4*>(a);
+        const float4 p1 = *reinterpret_cast<const float4*>(a + 4);
+        x[k][0] += p0.x; x[k][1] += p0.y; x[k][2] += p0.z; x[k][3] += p0.w;
+        x[k][4] += p1.x; x[k][5] += p1.y; x[k][6] += p1.z; x[k][7] += p1.w;
+      }
       if (has_resid) {
         const uint4 raw = *reinterpret_cast<const uint4*>(rs + v * 8);
         const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -86,7 +102,6 @@ tp_norm_allgather_kernel(PeerPtrs flags, int rank, int world, const int* __restr
   for (int i = 0; i < kTpNormThreads / 32; ++i) tot += red[i];
   const float rstd = rsqrtf(tot / static_cast<float>(H) + eps);
   // pass 2: normalised row to every rank's activation buffer
-  const long long grow = static_cast<long long>(rank) * rows_local + row;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const int v = threadIdx.x + k * kTpNormThreads;
@@ -146,26 +161,32 @@ __global__ void tp_epoch_advance_kernel(int* epoch_base, int by) {
 
 extern "C" {
 
-// acc [rows_local, H] fp32 (this rank's accumulator, cleared here), resid [rows_local, H] bf16 in/out (has_resid = 0:
-// the accumulator alone is the new residual), w [H] bf16, out_ptrs[world]: every rank's [world * rows_local, H] bf16
-// activation buffer.  epoch_base: device int; the kernel consumes epochs *epoch_base + epoch_off and + 1.
-// done_counter: device int, zero between launches.  H % 8 == 0, H <= 8192.
-int apb_tp_norm_allgather(void* const* flag_ptrs, int rank, int world, const int* epoch_base, int epoch_off, float* acc,
-                          void* resid, int has_resid, const void* w, float eps, void* const* out_ptrs, int rows_local,
-                          int H, int* done_counter, cudaStream_t s) {
+// part_ptrs[world]: every rank's [world * rows_local, H] fp32 partial of THIS call (read, never written here);
+// clear_buf / clear_elems: this rank's partial buffer of the previous call, zeroed here for its next use (null / 0:
+// nothing to clear; clear_elems % 4 == 0).  resid [rows_local, H] bf16 in/out (has_resid = 0: the sum alone is the new
+// residual), w [H] bf16, out_ptrs[world]: every rank's [world * rows_local, H] bf16 activation buffer.  epoch_base:
+// device int; the kernel consumes epochs *epoch_base + epoch_off and + 1.  done_counter: device int, zero between
+// launches.  H % 8 == 0, H <= 8192.
+int apb_tp_norm_allgather(void* const* flag_ptrs, int rank, int world, const int* epoch_base, int epoch_off,
+                          void* const* part_ptrs, float* clear_buf, long long clear_elems, void* resid, int has_resid,
+                          const void* w, float eps, void* const* out_ptrs, int rows_local, int H, int* done_counter,
+                          cudaStream_t s) {
   using namespace apb;
   if (rows_local <= 0) return 0;
-  if (world < 1 || world > kMaxRanks || (H % 8) || H > kTpNormThreads * 8 * 4 || !flag_ptrs || !epoch_base || !acc ||
-      !resid || !w || !out_ptrs || !done_counter)
+  if (world < 1 || world > kMaxRanks || (H % 8) || H > kTpNormThreads * 8 * 4 || !flag_ptrs || !epoch_base ||
+      !part_ptrs || !resid || !w || !out_ptrs || !done_counter || (clear_elems % 4) || clear_elems < 0 ||
+      (clear_buf && (reinterpret_cast<uintptr_t>(clear_buf) & 15)))
     return kBadArgument;
-  PeerPtrs f, o;
+  PeerPtrs f, o, pp;
   for (int i = 0; i < kMaxRanks; ++i) {
     f.p[i] = i < world ? flag_ptrs[i] : nullptr;
     o.p[i] = i < world ? out_ptrs[i] : nullptr;
-    if (i < world && (!f.p[i] || !o.p[i])) return kBadArgument;
+    pp.p[i] = i < world ? part_ptrs[i] : nullptr;
+    if (i < world && (!f.p[i] || !o.p[i] || !pp.p[i])) return kBadArgument;
   }
   return static_cast<int>(launch_kernel(tp_norm_allgather_kernel, dim3(rows_local), dim3(kTpNormThreads), 0, s, f, rank,
-                                        world, epoch_base, epoch_off, acc, static_cast<__nv_bfloat16*>(resid), has_resid,
+                                        world, epoch_base, epoch_off, pp, reinterpret_cast<float4*>(clear_buf),
+                                        clear_buf ? clear_elems / 4 : 0, static_cast<__nv_bfloat16*>(resid), has_resid,
                                         static_cast<const __nv_bfloat16*>(w), eps, o, rows_local, H, done_counter,
                                         status_device_ptr()));
 }

@@ -157,10 +157,11 @@ def _fn(name: str):
 
 
 class _TPDecode:
-    """Symmetric scratch and epoch state of one tensor-parallel replica's decode loop: two fp32 accumulators
-    (``[max_batch / tp, H]`` per rank, targets of the peers' GEMM epilogues), two bf16 activation buffers
-    (``[max_batch, H]`` per rank, targets of the owners' normalised rows), the flags of the in-kernel barriers and a
-    DEVICE epoch counter -- the kernels read ``*epoch + offset``, so a captured step can be replayed."""
+    """Symmetric scratch and epoch state of one tensor-parallel replica's decode loop: two fp32 partial buffers
+    (``[max_batch, H]`` per rank: the local GEMM adds its split-K partials there, the row owners pull their rows
+    from every rank), two bf16 activation buffers (``[max_batch, H]`` per rank, targets of the owners' normalised
+    rows), the flags of the in-kernel barriers and a DEVICE epoch counter -- the kernels read ``*epoch + offset``,
+    so a captured step can be replayed."""
 
     def __init__(self, device, group, max_batch: int, hidden: int):
         import torch.distributed as dist
@@ -172,7 +173,7 @@ class _TPDecode:
         self.H = hidden
         self.rows = max_batch // self.world
         self.flags = EpochFlags(device, group)
-        self.acc = [SymmetricBuffer(self.rows * hidden, torch.float32, device, group) for _ in range(2)]
+        self.acc = [SymmetricBuffer(max_batch * hidden, torch.float32, device, group) for _ in range(2)]
         self.hbuf = [SymmetricBuffer(max_batch * hidden, torch.bfloat16, device, group) for _ in range(2)]
         self.resid = torch.zeros((self.rows, hidden), device=device, dtype=torch.bfloat16)
         self.epoch = torch.ones(1, device=device, dtype=torch.int32)      # 0 is what fresh flags hold
@@ -184,8 +185,8 @@ class _TPDecode:
         self.twin_stream: Optional[torch.Tensor] = None
         c = ctypes
         vp, i, ll, f = c.c_void_p, c.c_int, c.c_longlong, c.c_float
-        self._rs = _lib.declare("apb_gemm_rs", [vp, vp, vp, i, i, i, i, ll, ll, ll, i, i, vp])
-        self._na = _lib.declare("apb_tp_norm_allgather", [vp, i, i, vp, i, vp, vp, i, vp, f, vp, i, i, vp, vp])
+        self._na = _lib.declare("apb_tp_norm_allgather",
+                                [vp, i, i, vp, i, vp, vp, ll, vp, i, vp, f, vp, i, i, vp, vp])
         self._adv = _lib.declare("apb_tp_epoch_advance", [vp, i, vp])
 
     def begin_step(self) -> None:
@@ -202,14 +203,17 @@ class _TPDecode:
             dist.all_reduce(y, group=self.group)
             h, self.twin_stream = norm.rmsnorm(y, norm_w, eps, self.twin_stream)
             return h
-        acc, hb = self.acc[k & 1], self.hbuf[k & 1]
+        acc, other, hb = self.acc[k & 1], self.acc[(k + 1) & 1], self.hbuf[k & 1]
         rl = B // self.world
         s = _lib.stream_ptr()
-        _lib.check(self._rs(_lib.ptr(x), _lib.ptr(w_local), acc.ptr_table(), self.world, B, H, x.shape[1], x.stride(0),
-                            w_local.stride(0), H, 128, splits, s), "apb_gemm_rs")
+        # this rank's partial [B, H] stays local (split-K partials meet through local red.add) ...
+        gemm.gemm_raw(x, w_local, acc.tensor[:B * H].view(B, H), M=B, N=H, K=x.shape[1], epi=gemm.EPI_F32_ATOMIC,
+                      splits=splits, bn=128)
+        # ... and the row owners pull, sum, normalise and hand the rows to everybody; the buffer of the previous
+        # call is cleared on the way (all of it: a later step may run with more rows than this one)
         _lib.check(self._na(self.flags.ptr_table(), self.rank, self.world, _lib.ptr(self.epoch), 2 * k,
-                            _lib.ptr(acc.tensor), _lib.ptr(self.resid), 1, _lib.ptr(norm_w), float(eps), hb.ptr_table(),
-                            rl, H, _lib.ptr(self.done), s), "apb_tp_norm_allgather")
+                            acc.ptr_table(), _lib.ptr(other.tensor), other.tensor.numel(), _lib.ptr(self.resid), 1, _lib.ptr(norm_w),
+                            float(eps), hb.ptr_table(), rl, H, _lib.ptr(self.done), s), "apb_tp_norm_allgather")
         return hb.tensor[:B * H].view(B, H)
 
     def end_step(self) -> None:
@@ -598,9 +602,9 @@ class SamplerEngine:
 
     def _decode_layers_tp(self, x: torch.Tensor, positions, slots, B: int) -> torch.Tensor:
         """Decoder stack of one decode step on one rank of a tensor-parallel replica.  Column-parallel projections
-        (qkv, gate/up) read the full activation from LOCAL memory; row-parallel ones (o, down) add their partial
-        rows into the owner rank's fp32 accumulator from the GEMM epilogue (``apb_gemm_rs``), and
-        ``apb_tp_norm_allgather`` turns the owner's sums into residual + RMSNorm and stores the normalised rows into
+        (qkv, gate/up) read the full activation from LOCAL memory; row-parallel ones (o, down) leave their partial
+        result in a local fp32 buffer, and ``apb_tp_norm_allgather`` on the rank that owns a row pulls the row's
+        partials from every rank (peer loads), adds the residual, applies RMSNorm and stores the normalised row into
         every rank's activation buffer -- two kernels per projection, no library collective in the loop."""
         c, t = self.cfg, self._tpd
         H, T = c.hidden_size, self.tp

@@ -439,9 +439,21 @@ class TrainEngine:
             raise RuntimeError(f"training engine is asleep ({', '.join(sorted(self._offloaded))} offloaded); "
                                f"call wake before {what}")
 
+    def align_ranks(self) -> None:
+        """Queues a one-element NCCL all-reduce on the current stream.  The in-kernel barriers of the fused paths wait
+        at most a second for their peers; ranks that ran for a long time without meeting (a whole rollout, sixteen
+        micro-batches with resident parameters) drift apart by more than that through clock differences alone, so the
+        first fused kernel after such a stretch is preceded by a collective that waits without a limit."""
+        if self.world > 1 and self.on_cuda and self.impl == "fused":
+            if getattr(self, "_align_buf", None) is None:
+                self._align_buf = torch.zeros(1, device=self.device, dtype=torch.float32)
+            dist.all_reduce(self._align_buf, group=self.group)
+
     def backward(self, loss: torch.Tensor) -> None:
         self.require_awake("backward")
         if self.zero3 is not None:
+            if self.zero3.overlap:
+                self.align_ranks()
             self.zero3.begin_backward()
         loss.backward()
         self.collect_autograd_grads()
@@ -470,6 +482,7 @@ class TrainEngine:
         bias2 = 1.0 - cfg.betas[1] ** t
         self.sumsq.zero_()
         if self.impl == "fused" and not self.opt_on_host and self.cfg.adam_w_mode:
+            self.align_ranks()
             self._step_fused(lr, bias1, bias2)
         else:
             self._step_collective(lr, bias1, bias2)

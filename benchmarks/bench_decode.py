@@ -89,6 +89,12 @@ def main():
                           "tensor_parallel": world, "tp_step": os.environ.get("APB_TP_DECODE", "fused") if world > 1 else None,
                           **res}), flush=True)
     if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        if os.environ.get("APB_TP_DECODE", "fused") == "nccl":
+            # NCCL collectives captured in CUDA graphs keep the communicator busy at teardown: leave without it
+            sys.stdout.flush()
+            os._exit(0)
         dist.destroy_process_group()
 
 
