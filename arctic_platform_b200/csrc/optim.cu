@@ -572,13 +572,17 @@ __device__ __forceinline__ const __nv_bfloat16* sync_src_ptr(const SyncSeg& sg, 
 // One CTA per 128 x 128 tile of a segment (grid-stride over all tiles of the table).  A tile is read ONCE from the
 // source (local memory, or a peer's over NVLink) into registers: 256 threads x 8 vectors of 8 bf16.
 __global__ void __launch_bounds__(256)
-sync_weights_table_kernel(const SyncSeg* __restrict__ segs, int n_seg, long long total_tiles, PeerPtrs src,
-                          int src_rank, PeerPtrs flags, int rank, int world, int epoch,
+sync_weights_table_kernel(const SyncSeg* __restrict__ segs, int n_seg, long long total_tiles, long long tile_rot,
+                          PeerPtrs src, int src_rank, PeerPtrs flags, int rank, int world, int epoch,
                           __nv_bfloat16* __restrict__ dst_bf16, uint8_t* __restrict__ dst_q,
                           float* __restrict__ dst_scale, int* status) {
   if (!epoch_barrier(flags, rank, world, epoch, status)) return;
   __shared__ float red[8];
-  for (long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+  for (long long t0 = blockIdx.x; t0 < total_tiles; t0 += gridDim.x) {
+    // every rank starts its walk at a different tile: the ranks would otherwise all pull the same stretch of a
+    // tensor -- one owner's NVLink port -- at the same moment
+    long long t = t0 + tile_rot;
+    if (t >= total_tiles) t -= total_tiles;
     int lo = 0, hi = n_seg - 1;             // last segment whose tile_start <= t
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
@@ -667,7 +671,8 @@ int apb_sync_weights_table(const void* segs, int n_seg, long long total_tiles, v
   for (int i = 0; i < kMaxRanks; ++i) fl.p[i] = (world > 1 && i < world) ? flag_ptrs[i] : nullptr;
   const long long cap = max_ctas > 0 ? max_ctas : static_cast<long long>(sm_count()) * 8;
   const int grid = static_cast<int>(total_tiles < cap ? total_tiles : cap);
-  sync_weights_table_kernel<<<grid, 256, 0, s>>>(static_cast<const SyncSeg*>(segs), n_seg, total_tiles,
+  const long long rot = n_src > 1 ? (total_tiles / n_src) * src_rank : 0;
+  sync_weights_table_kernel<<<grid, 256, 0, s>>>(static_cast<const SyncSeg*>(segs), n_seg, total_tiles, rot,
                                                  to_peers(src_ptrs, n_src), src_rank, fl, rank, world > 1 ? world : 1,
                                                  epoch, static_cast<__nv_bfloat16*>(dst_bf16),
                                                  static_cast<uint8_t*>(dst_q), dst_scale, status_device_ptr());
