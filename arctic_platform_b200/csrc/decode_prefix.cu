@@ -12,6 +12,12 @@
 // ArcticInference's forest cascade attention (`use_fca`, arctic_platform/common/utils/server_models.py:123-132).
 //
 // CTA = 192 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax (one row each).
+//
+// The KV blocks of a node are software-pipelined: tensor memory holds TWO score buffers and TWO output buffers, the
+// MMA warp issues Q K^T of block j+1 before it waits for the probabilities of block j, and the softmax warps fold the
+// output of block j-1 into their running accumulator after they have handed block j's probabilities over -- so the
+// tensor pipe works on P V (j-1) and Q K^T (j+1) while the softmax of block j runs, and neither side idles on the
+// other (one buffer of each made every block a serial chain of load, MMA, softmax, MMA, read-out).
 #include "common.cuh"
 #include "host_utils.cuh"
 
@@ -35,6 +41,7 @@ constexpr int kDpThreads = 192;
 constexpr int kDpSlots = 4;
 constexpr int kDpTile = 128 * 128 * 2;  // one Q / K / V tile (D = 128)
 constexpr int kDpSmem = kDpTile + kDpSlots * kDpTile + 1024 + 256;
+constexpr int kDpTmemCols = 512;        // S0 | S1 | O0 | O1, 128 fp32 columns each
 
 __global__ void __launch_bounds__(kDpThreads, 1)
 decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
@@ -48,10 +55,11 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   uint64_t* kv_full = bars;
   uint64_t* kv_empty = bars + kDpSlots;
   uint64_t* q_full = bars + 2 * kDpSlots;
-  uint64_t* s_full = q_full + 1;
-  uint64_t* p_full = s_full + 1;
-  uint64_t* o_full = p_full + 1;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_full + 1);
+  uint64_t* s_full = q_full + 1;    // [2] MMA -> softmax: scores of block j are in S[j & 1]
+  uint64_t* p_full = s_full + 2;    // [2] softmax -> MMA: probabilities of block j are in S[j & 1]
+  uint64_t* o_full = p_full + 2;    // [2] MMA -> softmax: P V of block j is in O[j & 1]
+  uint64_t* o_free = o_full + 2;    // [2] softmax -> MMA: O[j & 1] has been read
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_free + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = blockIdx.x / p.Hkv;
@@ -78,13 +86,16 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(q_full, 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
-    mbar_init(o_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&p_full[b], 128);
+      mbar_init(&o_full[b], 1);
+      mbar_init(&o_free[b], 128);
+    }
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_holder, 256);
+    tmem_alloc(tmem_holder, kDpTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -144,34 +155,45 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       const uint32_t idesc_o = umma_idesc_bf16(128, D, 0, 1);
       bool ok = mbar_wait(q_full, 0, p.status, kTimeoutFull);
       const uint32_t qa = smem_u32(smem_q);
-      for (int j = 0; j < n_blocks && ok; ++j) {
-        const int nk = 2 * j, nv = 2 * j + 1;
-        if (!mbar_wait(&kv_full[nk % kDpSlots], (nk / kDpSlots) & 1, p.status, kTimeoutFull)) {
-          ok = false;
-          break;
-        }
+      // S(j) = Q K(j)^T into score buffer j & 1
+      auto issue_qk = [&](int j) -> bool {
+        const int nk = 2 * j;
+        if (!mbar_wait(&kv_full[nk % kDpSlots], (nk / kDpSlots) & 1, p.status, kTimeoutFull)) return false;
         tc_fence_after();
         const uint32_t ka = smem_u32(smem_kv + (nk % kDpSlots) * kDpTile);
+        const uint32_t t_s = tmem_base + (j & 1) * 128;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k / 4) * 16384 + (k % 4) * 32;
-          umma_bf16_ss(tmem_base, umma_smem_desc(qa + off, 0, 1024), umma_smem_desc(ka + off, 0, 1024), idesc_s,
+          umma_bf16_ss(t_s, umma_smem_desc(qa + off, 0, 1024), umma_smem_desc(ka + off, 0, 1024), idesc_s,
                        k > 0 ? 1u : 0u);
         }
-        tc_commit(s_full);
+        tc_commit(&s_full[j & 1]);
         tc_commit(&kv_empty[nk % kDpSlots]);
+        return true;
+      };
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        // the scores of the NEXT block first: they are ready when the softmax warps finish this one.  Its buffer
+        // held the probabilities of block j-1, whose P V was issued before this point (the pipe runs in order).
+        if (j + 1 < n_blocks && !issue_qk(j + 1)) {
+          ok = false;
+          break;
+        }
+        const int nv = 2 * j + 1, b = j & 1;
         if (!mbar_wait(&kv_full[nv % kDpSlots], (nv / kDpSlots) & 1, p.status, kTimeoutFull) ||
-            !mbar_wait(p_full, j & 1, p.status, kTimeoutTmemEmpty)) {
+            !mbar_wait(&p_full[b], (j >> 1) & 1, p.status, kTimeoutTmemEmpty) ||
+            (j >= 2 && !mbar_wait(&o_free[b], ((j - 2) >> 1) & 1, p.status, kTimeoutTmemEmpty))) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t va = smem_u32(smem_kv + (nv % kDpSlots) * kDpTile);
+        const uint32_t t_p = tmem_base + b * 128, t_o = tmem_base + 256 + b * 128;
 #pragma unroll
         for (int k = 0; k < 128 / 16; ++k)
-          umma_bf16_ts(tmem_base + 128, tmem_base + k * 8, umma_smem_desc(va + k * 2048, 16384, 1024), idesc_o,
-                       k > 0 ? 1u : 0u);
-        tc_commit(o_full);
+          umma_bf16_ts(t_o, t_p + k * 8, umma_smem_desc(va + k * 2048, 16384, 1024), idesc_o, k > 0 ? 1u : 0u);
+        tc_commit(&o_full[b]);
         tc_commit(&kv_empty[nv % kDpSlots]);
       }
     }
@@ -180,19 +202,38 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_off;
-    const uint32_t t_o = tmem_base + lane_off + 128;
     float o_acc[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
+    float alpha_prev = 1.f;          // rescale factor that goes with the output block still to be folded in
     bool ok = true;
+    // o_acc = o_acc * alpha + O(j), then O[j & 1] is handed back to the MMA warp
+    auto fold_output = [&](int j, float alpha) -> bool {
+      const int b = j & 1;
+      if (!mbar_wait(&o_full[b], (j >> 1) & 1, p.status, kTimeoutTmemFull)) return false;
+      tc_fence_after();
+      const uint32_t t_o = tmem_base + lane_off + 256 + b * 128;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_o + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+      mbar_arrive(&o_free[b]);
+      return true;
+    };
     for (int j = 0; j < n_blocks; ++j) {
-      if (!mbar_wait(s_full, j & 1, p.status, kTimeoutTmemFull)) {
+      const int b = j & 1;
+      if (!mbar_wait(&s_full[b], (j >> 1) & 1, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      const uint32_t t_s = tmem_base + lane_off + b * 128;
       const int limit = max(0, min(128, len - (b0 + j) * 128));
       float mx = -INFINITY;
 #pragma unroll 1
@@ -227,24 +268,17 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[b]);
       l_run = l_run * alpha + rowsum;
       m_run = m_new;
-      if (!mbar_wait(o_full, j & 1, p.status, kTimeoutTmemFull)) {
+      // while the tensor pipe multiplies this block's probabilities, fold in the previous block's output
+      if (j > 0 && !fold_output(j - 1, alpha_prev)) {
         ok = false;
         break;
       }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_o + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
-      }
-      tc_fence_before();
+      alpha_prev = alpha;
     }
+    if (ok && n_blocks > 0) ok = fold_output(n_blocks - 1, alpha_prev);
     if (ok && row < nq * R) {
       const int seq = qs + row / R;
       const int head = kvh * R + row % R;
@@ -266,7 +300,7 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, kDpTmemCols);
   }
 }
 

@@ -38,6 +38,11 @@ struct GemmParams {
   const int4* tile_map;
   int num_map_tiles;         // entries of tile_map (an upper bound when num_tiles_dev is set)
   const int* num_tiles_dev;  // optional: the live entry count, written by a kernel (a routing plan built on the device)
+  // Optional second record per tile (grouped backward passes): {c_row_off, kb0, kb1, bk_off}.  The tile's output rows
+  // are written at row + c_row_off (per-group slabs of a stacked C), its K walk is the k-block range [kb0, kb1)
+  // (kb1 < 0: all of K; an empty range skips the tile -- a group without rows), and B's K coordinate is shifted
+  // by bk_off rows (per-group slabs of a stacked [K, N] B).
+  const int4* tile_ext;
   int* status;
   // log-prob epilogues
   const float* row_scale;  // [M] per-row multiplier of the logits (inverse temperature) or null

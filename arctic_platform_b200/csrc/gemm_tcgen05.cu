@@ -90,6 +90,8 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
 
   // Tile decode shared by all roles.  Consecutive tile ids walk 8 m-tiles of
   // one n-band before moving on, so CTAs running at the same time share B in L2.
+  // c_off / bk_off: see GemmParams::tile_ext (0 without it)
+  int c_off = 0, bk_off = 0;
   auto decode = [&](int t, int& m0, int& m_end, int& b_row, int& n0, int& kb0, int& kb1) {
     const int split = t / mn_tiles;
     const int tt = t - split * mn_tiles;
@@ -101,6 +103,16 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
       m_end = e.y;
       n0 = e.w * BN;
       b_row = e.z + n0;
+      if (p.tile_ext) {
+        const int4 x = p.tile_ext[tt];
+        c_off = x.x;
+        bk_off = x.w;
+        if (x.z >= 0) {
+          kb0 = max(0, x.y);
+          kb1 = min(k_blocks, x.z);
+          if (kb1 < kb0) kb1 = kb0;
+        }
+      }
     } else {
       constexpr int G = 8;
       const int per_group = G * tiles_n;
@@ -148,7 +160,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sb + c * (64 * kBK * 2), &tma_b, &full_bar[i], b_row + c * 64, kb * kBK);
+              tma_load_2d(sb + c * (64 * kBK * 2), &tma_b, &full_bar[i], b_row + c * 64, kb * kBK + bk_off);
           }
         }
       }
@@ -192,7 +204,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sb + c * (64 * kBK * 2), &tma_b, &full_bar[stage], b_row + c * 64, kb * kBK);
+              tma_load_2d(sb + c * (64 * kBK * 2), &tma_b, &full_bar[stage], b_row + c * 64, kb * kBK + bk_off);
           }
           if (++stage == Cfg::kStages) {
             stage = 0;
@@ -216,11 +228,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int m0, m_end, b_row, n0, kb0, kb1;
         decode(t, m0, m_end, b_row, n0, kb0, kb1);
+        if (kb1 <= kb0) continue;              // a group without rows: no loads, no accumulator, nothing stored
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        ++it;
         if (!mbar_wait(&tempty_bar[buf], acc_phase ^ 1, p.status, kTimeoutTmemEmpty)) {
           ok = false;
           break;
@@ -258,11 +272,13 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
     int it = 0;
     bool ok = true;
     pdl_wait();                    // the output buffer may still be read (or cleared) by the previous kernel
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int m0, m_end, b_row, n0, kb0, kb1;
       decode(t, m0, m_end, b_row, n0, kb0, kb1);
+      if (kb1 <= kb0) continue;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      ++it;
       if (!mbar_wait(&tfull_bar[buf], acc_phase, p.status, kTimeoutTmemFull)) {
         ok = false;
         break;
@@ -376,7 +392,7 @@ __device__ __forceinline__ void gemm_body(const CUtensorMap& tma_a, const CUtens
           tmem_ld_wait();
         }
         if (!row_ok) continue;
-        gemm_store_chunk(p, row, col0, r, ncols);
+        gemm_store_chunk(p, row + c_off, col0, r, ncols);
       }
       tc_fence_before();
       __syncwarp();
@@ -501,9 +517,11 @@ extern "C" {
 static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                          long long ldc, int a_mn, int b_mn, int epi, int splits, float alpha, const void* bias,
                          void* C2, long long ldc2, const void* tile_map, int num_map_tiles, const int* num_tiles_dev,
-                         long long b_rows, int bn, int max_ctas, cudaStream_t stream) {
+                         long long b_rows, int bn, int max_ctas, cudaStream_t stream, const void* tile_ext = nullptr,
+                         long long b_k_rows = 0) {
   using namespace apb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (tile_ext && (!tile_map || splits > 1)) return kBadArgument;
   if ((lda % 8) || (ldb % 8) || (N % 8) || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15))
     return kBadArgument;
@@ -568,7 +586,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   if (!b_mn)
     rc = make_tmap_2d(&tb, B, 2, brows, static_cast<uint64_t>(K), ldb, 64, bn);
   else
-    rc = make_tmap_2d(&tb, B, 2, static_cast<uint64_t>(K), brows, ldb, 64, 64);
+    rc = make_tmap_2d(&tb, B, 2, static_cast<uint64_t>(b_k_rows > 0 ? b_k_rows : K), brows, ldb, 64, 64);
   if (rc) return 2000 + rc;
 
   GemmParams p{};  // zero: the peer-mode fields must read 0 in the plain path
@@ -588,6 +606,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   p.tile_map = static_cast<const int4*>(tile_map);
   p.num_map_tiles = num_map_tiles;
   p.num_tiles_dev = tile_map ? num_tiles_dev : nullptr;
+  p.tile_ext = static_cast<const int4*>(tile_ext);
   p.status = status_device_ptr();
   p.row_scale = nullptr;
   p.labels = nullptr;
@@ -617,6 +636,23 @@ int apb_gemm_bf16_grouped_dev(const void* A, const void* B, void* C, int M, int 
   if (!tile_map || !num_tiles_dev || max_tiles <= 0) return apb::kBadArgument;
   return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, 0, 0, epi, 1, alpha, nullptr, C2, ldc2, tile_map, max_tiles,
                         num_tiles_dev, b_rows, 128, 0, stream);
+}
+
+// The grouped backward passes of an expert layer, tables written by a kernel (apb_moe_plan):
+//   data gradient    dX[rows of e] = dY[rows of e] @ W[e],  W stacked [E * K, N] (b_mn = 1, bk_off = e * K per tile);
+//   weight gradient  dW[e] (+)= dY[rows of e]^T @ X[rows of e]: a_mn = b_mn = 1, K = the row axis, every tile walks
+//                    the k-blocks of its expert's rows (64-row aligned, padding rows zero) and writes the e-th slab of
+//                    the stacked dW (c_row_off = e * M).
+// `tile_ext` holds one {c_row_off, kb0, kb1, bk_off} record per tile of `tile_map`.  b_k_rows: rows of the stacked
+// [K, N] B (0: K).  b_n_rows: rows of a stacked [N, K] B (0: N).  num_tiles_dev may be null (all max_tiles live).
+int apb_gemm_bf16_grouped_ext(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                              long long ldc, int a_mn, int b_mn, int epi, float alpha, const void* tile_map,
+                              const void* tile_ext, int max_tiles, const int* num_tiles_dev, long long b_n_rows,
+                              long long b_k_rows, cudaStream_t stream) {
+  if (!tile_map || !tile_ext || max_tiles <= 0) return apb::kBadArgument;
+  if (epi != apb::kEpiBf16 && epi != apb::kEpiF32 && epi != apb::kEpiF32Accum) return apb::kBadArgument;
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, 1, alpha, nullptr, nullptr, 0, tile_map,
+                        max_tiles, num_tiles_dev, b_n_rows, 128, 0, stream, tile_ext, b_k_rows);
 }
 }
 
@@ -915,9 +951,9 @@ int apb_gemm_rs(const void* A, const void* B, void* const* acc_ptrs, int world, 
 // Grouped GEMM whose output rows are scattered to other ranks: row m of the result goes to
 // out_ptrs[row_map[m].x] + row_map[m].y * ldc (bf16).  Used as the fused "expert GEMM 2 + combine" of
 // expert-parallel MoE.  tile_map as in apb_gemm_bf16.
-int apb_gemm_scatter(const void* A, const void* B, void* const* out_ptrs, int world, const void* row_map, int M, int N,
-                     int K, long long lda, long long ldb, long long ldc, const void* tile_map, int num_map_tiles,
-                     long long b_rows, cudaStream_t stream) {
+static int gemm_scatter_impl(const void* A, const void* B, void* const* out_ptrs, int world, const void* row_map, int M,
+                             int N, int K, long long lda, long long ldb, long long ldc, const void* tile_map,
+                             int num_map_tiles, const int* num_tiles_dev, long long b_rows, cudaStream_t stream) {
   using namespace apb;
   if (M <= 0) return 0;
   if (world < 1 || world > 8 || (lda % 8) || (ldb % 8) || (ldc % 8) || (N % 8)) return kBadArgument;
@@ -936,11 +972,29 @@ int apb_gemm_scatter(const void* A, const void* B, void* const* out_ptrs, int wo
   p.alpha = 1.f;
   p.tile_map = static_cast<const int4*>(tile_map);
   p.num_map_tiles = num_map_tiles;
+  p.num_tiles_dev = num_tiles_dev;
   p.status = status_device_ptr();
   p.row_map = static_cast<const int2*>(row_map);
   p.world = world;
   for (int r = 0; r < 8; ++r) p.c_peers[r] = r < world ? out_ptrs[r] : nullptr;
   return launch_gemm<128>(ta, tb, p, 0, stream);
+}
+
+int apb_gemm_scatter(const void* A, const void* B, void* const* out_ptrs, int world, const void* row_map, int M, int N,
+                     int K, long long lda, long long ldb, long long ldc, const void* tile_map, int num_map_tiles,
+                     long long b_rows, cudaStream_t stream) {
+  return gemm_scatter_impl(A, B, out_ptrs, world, row_map, M, N, K, lda, ldb, ldc, tile_map, num_map_tiles, nullptr,
+                           b_rows, stream);
+}
+
+// The same with a tile table written by a kernel: room for `max_tiles` records, the live count read from
+// `*num_tiles_dev` when the GEMM runs.
+int apb_gemm_scatter_dev(const void* A, const void* B, void* const* out_ptrs, int world, const void* row_map, int M,
+                         int N, int K, long long lda, long long ldb, long long ldc, const void* tile_map, int max_tiles,
+                         const int* num_tiles_dev, long long b_rows, cudaStream_t stream) {
+  if (!tile_map || !num_tiles_dev || max_tiles <= 0) return apb::kBadArgument;
+  return gemm_scatter_impl(A, B, out_ptrs, world, row_map, M, N, K, lda, ldb, ldc, tile_map, max_tiles, num_tiles_dev,
+                           b_rows, stream);
 }
 
 int apb_tp_finalize(void* const* flag_ptrs, int rank, int world, int epoch, float* acc, void* out, long long n,

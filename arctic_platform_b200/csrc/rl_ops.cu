@@ -211,9 +211,108 @@ moe_group_tiles_kernel(const int* __restrict__ counts, int E, int n_out1, int n_
   }
 }
 
+// Routing plan of an expert layer whose rows are laid out expert-major with every expert's segment padded to a
+// multiple of 64 rows (padding rows hold zeros), from the tokens-per-expert histogram, on the device.  Writes
+//   seg_start [E + 1]: first padded row of every expert (seg_start[E] = rows in use);
+//   row-block tables {m0, m_end, b_row_offset, n_tile} (+ extension records {c_row_off, kb0, kb1, bk_off}) for the
+//   four GEMMs that walk 128-row blocks of the segments:
+//     0 gate/up forward   (N = 2I, B = Wgu  stacked [E * 2I, H], b_row_offset = e * 2I)
+//     1 down forward      (N = H,  B = Wdn  stacked [E * H, I],  b_row_offset = e * H)
+//     2 d act = dY @ Wdn  (N = I,  B stacked [E * H, I] read K-major, bk_off = e * H)
+//     3 d x = dGU @ Wgu   (N = H,  B stacked [E * 2I, H] read K-major, bk_off = e * 2I)
+//   and the two weight-gradient tables, whose tile COUNT is static (every expert x every 128 x 128 block of its weight)
+//   and whose K walk is the expert's 64-row blocks:
+//     4 dWdn[e] [H, I]  += dY[seg]^T  @ act[seg]      5 dWgu[e] [2I, H] += dGU[seg]^T @ x[seg]
+// n_tiles [4]: live sizes of tables 0-3.  One block; the prefix sums are serial over E <= 512 experts.
+struct MoePlanOut {
+  int4* map[6];
+  int4* ext[6];
+  int max_tiles[4];
+};
+
+__global__ void __launch_bounds__(256)
+moe_plan_kernel(const int* __restrict__ counts, int E, int H, int I, MoePlanOut out, int* __restrict__ seg_start,
+                int* __restrict__ n_tiles) {
+  __shared__ int row_off[513];
+  __shared__ int blk_off[513];
+  if (threadIdx.x == 0) {
+    int r = 0, b = 0;
+    for (int e = 0; e < E; ++e) {
+      row_off[e] = r;
+      blk_off[e] = b;
+      const int padded = (max(counts[e], 0) + 63) / 64 * 64;
+      r += padded;
+      b += (padded + 127) / 128;
+    }
+    row_off[E] = r;
+    blk_off[E] = b;
+  }
+  __syncthreads();
+  const int I2 = 2 * I;
+  const int nt[4] = {(I2 + 127) / 128, (H + 127) / 128, (I + 127) / 128, (H + 127) / 128};
+  const int b_off_mul[4] = {I2, H, 0, 0};      // b_row_offset = e * this
+  const int bk_mul[4] = {0, 0, H, I2};         // bk_off = e * this
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) seg_start[e] = row_off[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int r0 = row_off[e], r1 = row_off[e + 1];
+    int b = blk_off[e];
+    for (int m0 = r0; m0 < r1; m0 += 128, ++b) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        for (int t = 0; t < nt[g]; ++t) {
+          const int i = b * nt[g] + t;
+          if (i < out.max_tiles[g]) {
+            out.map[g][i] = make_int4(m0, r1, e * b_off_mul[g], t);
+            out.ext[g][i] = make_int4(0, 0, -1, e * bk_mul[g]);
+          }
+        }
+      }
+    }
+    // weight gradients: tile (e, mt, nt) at a fixed position
+    const int kb0 = r0 / 64, kb1 = r1 / 64;
+    const int mt_dn = (H + 127) / 128, nt_dn = (I + 127) / 128;
+    for (int mt = 0; mt < mt_dn; ++mt)
+      for (int t = 0; t < nt_dn; ++t) {
+        const int i = (e * mt_dn + mt) * nt_dn + t;
+        out.map[4][i] = make_int4(mt * 128, H, 0, t);
+        out.ext[4][i] = make_int4(e * H, kb0, kb1, 0);
+      }
+    const int mt_gu = (I2 + 127) / 128, nt_gu = (H + 127) / 128;
+    for (int mt = 0; mt < mt_gu; ++mt)
+      for (int t = 0; t < nt_gu; ++t) {
+        const int i = (e * mt_gu + mt) * nt_gu + t;
+        out.map[5][i] = make_int4(mt * 128, I2, 0, t);
+        out.ext[5][i] = make_int4(e * I2, kb0, kb1, 0);
+      }
+  }
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) n_tiles[g] = min(blk_off[E] * nt[g], out.max_tiles[g]);
+  }
+}
+
 }  // namespace apb
 
 extern "C" {
+
+// counts [E] int32 on the device (E <= 512), hidden size H, expert width I.  maps / exts: 6 device tables each (see
+// moe_plan_kernel); max_tiles [4]: capacity of tables 0-3 (tables 4 and 5 hold E * ceil(H/128) * ceil(I/128) and
+// E * ceil(2I/128) * ceil(H/128) records).  seg_start [E + 1], n_tiles [4]: device outputs.
+int apb_moe_plan(const int* counts, int E, int H, int I, void* const* maps, void* const* exts, const int* max_tiles,
+                 int* seg_start, int* n_tiles, cudaStream_t s) {
+  using namespace apb;
+  if (!counts || !maps || !exts || !max_tiles || !seg_start || !n_tiles || E < 1 || E > 512 || H < 1 || I < 1)
+    return kBadArgument;
+  MoePlanOut o;
+  for (int g = 0; g < 6; ++g) {
+    if (!maps[g] || !exts[g]) return kBadArgument;
+    o.map[g] = static_cast<int4*>(maps[g]);
+    o.ext[g] = static_cast<int4*>(exts[g]);
+  }
+  for (int g = 0; g < 4; ++g) o.max_tiles[g] = max_tiles[g];
+  moe_plan_kernel<<<1, 256, 0, s>>>(counts, E, H, I, o, seg_start, n_tiles);
+  return static_cast<int>(cudaGetLastError());
+}
 
 // counts [E] int32 (E <= 512) -> tile tables of the gate/up (n_out1 columns per expert) and down (n_out2) grouped
 // GEMMs, their live sizes n_tiles[2] and, optionally, the row offset of every expert (offsets [E + 1]).

@@ -257,6 +257,8 @@ class SamplerEngine:
         self.model = model if model is not None else DecoderLM(cfg, self.device, torch.bfloat16)
         self.max_batch = max_batch
         self.max_seq_len = max_seq_len
+        self._sm_count = (torch.cuda.get_device_properties(self.device).multi_processor_count
+                          if self.device.type == "cuda" else 1)
         self.cascade = cascade
         self.sync_interval = sync_interval
         self.use_cuda_graph = use_cuda_graph
@@ -290,6 +292,13 @@ class SamplerEngine:
         # zero-filled: the unwritten tail of a last page is multiplied by probability 0 and must be finite
         self.kcache = torch.zeros(shape, device=self.device, dtype=torch.bfloat16)
         self.vcache = torch.zeros(shape, device=self.device, dtype=torch.bfloat16)
+        if self.device.type == "cuda":
+            from ..utils import memory_budget
+            memory_budget.set_kv_resident(self.device, self.kv_bytes())
+
+    def kv_bytes(self) -> int:
+        c = self.cfg
+        return 2 * c.num_layers * self.num_pages * c.num_kv_heads * PAGE * c.head_dim * 2
 
     def _alloc_state(self) -> None:
         B, dev, c = self.max_batch, self.device, self.cfg
@@ -427,9 +436,12 @@ class SamplerEngine:
             seq_splits = max(1, min(self.splits, int(os.environ["APB_DECODE_SEQ_SPLITS"])))
         out = torch.empty((B, c.num_heads, c.head_dim), device=self.device, dtype=torch.bfloat16)
         if self._cascade_on():
+            # shared pass: as many KV splits as keep all its CTAs (nodes x KV heads x splits) within one wave of SMs
+            nodes = self._group_bucket()
+            node_splits = max(1, min(self.splits, self._sm_count // max(1, nodes * c.num_kv_heads)))
             return forest_decode_attention(q, kc, vc, self._forest_view(B), self.d_q_start, self.d_active,
-                                           self.d_priv_table, self.d_priv_len, self.part_o, self.part_ml, self.splits,
-                                           seq_splits, scale, out=out, n_nodes=self._group_bucket())
+                                           self.d_priv_table, self.d_priv_len, self.part_o, self.part_ml, node_splits,
+                                           seq_splits, scale, out=out, n_nodes=nodes)
         s = _lib.stream_ptr()
         _lib.check(_fn("dec")(_lib.ptr(q), _lib.ptr(self.d_q_start), _lib.ptr(self.d_active), _lib.ptr(self.d_page_table),
                               self.max_pages, _lib.ptr(self.d_len), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(self.part_o[0]),
@@ -1063,10 +1075,22 @@ class SamplerEngine:
         return None
 
     def sleep(self, level: int = 1) -> None:
-        """Level 1 frees the KV cache and the captured graphs; level 2 also drops the weights (they come
-        back with the next weight sync)."""
+        """Level 1 frees the KV cache and the captured graphs -- unless the trainer that shares the GPU has shown
+        that it runs with room to spare for the cache (``utils/memory_budget.py``): then cache and graphs stay and the
+        next wake costs nothing.  Level 2 always frees them and also drops the weights (they come back with the next
+        weight sync)."""
+        keep = False
+        if level < 2 and self.kcache is not None and self.device.type == "cuda":
+            from ..utils import memory_budget
+            keep = memory_budget.kv_may_stay(self.device, self.kv_bytes())
+        if keep:
+            self._asleep = True
+            return
         self._graphs.clear()
         self.kcache = self.vcache = None
+        if self.device.type == "cuda":
+            from ..utils import memory_budget
+            memory_budget.set_kv_resident(self.device, 0)
         if level >= 2:
             for p in self.model.parameters():
                 p.data = torch.empty(0, device=self.device, dtype=p.dtype)
@@ -1076,6 +1100,7 @@ class SamplerEngine:
 
     def wake(self, tags: Optional[Sequence[str]] = None) -> None:
         tags = set(tags or ("weights", "kv_cache"))
-        if "kv_cache" in tags and self.kcache is None:
-            self._alloc_cache()
+        if "kv_cache" in tags:
+            if self.kcache is None:
+                self._alloc_cache()
             self._asleep = False

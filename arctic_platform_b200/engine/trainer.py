@@ -489,6 +489,9 @@ class TrainEngine:
         self.global_steps += 1
         self.zero_grad()
         self.last_lr = lr
+        if self.on_cuda:
+            from ..utils import memory_budget
+            memory_budget.note_training_peak(self.device)      # a colocated sampler decides from this what it may keep
         if getattr(self.model.cfg, "moe_expert_bias", False):
             # aux-loss-free load balancing: one nudge of every router's selection bias per optimizer step, from the
             # expert loads of all data-parallel ranks

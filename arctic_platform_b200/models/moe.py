@@ -13,6 +13,7 @@ execution (experts sharded over ranks, dispatch/combine over NVLink) lives in
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -130,6 +131,139 @@ def device_group_tiles(counts: torch.Tensor, rows: int, n_out1: int, n_out2: int
     _lib.check(_grouped_dev_fns()["tiles"](_lib.ptr(counts), E, n_out1, n_out2, _lib.ptr(t1), _lib.ptr(t2), max1, max2,
                                            _lib.ptr(n_tiles), None, _lib.stream_ptr()), "apb_moe_group_tiles")
     return t1, t2, n_tiles, max1, max2
+
+
+class MoEPlan:
+    """Device-side plan of one expert-layer call in the PADDED expert-major row layout: expert ``e`` owns rows
+    ``[seg_start[e], seg_start[e + 1])``, a multiple of 64 of them, the rows past its ``counts[e]`` tokens holding
+    zeros.  Padding makes every expert's rows a whole number of 64-row K blocks, which is what lets the weight
+    gradients run as ONE grouped GEMM per weight (each tile walks the K blocks of its expert) instead of a host loop
+    over experts.  Everything here is written by ``moe_plan_kernel`` from the histogram on the GPU: no number of it
+    ever reaches the host.  ``rows_cap`` (host) bounds the rows in use: pairs + 63 per expert, rounded to 128."""
+
+    def __init__(self, counts: torch.Tensor, num_pairs: int, H: int, I: int, rows_cap: Optional[int] = None):
+        from ..ops import _lib
+        import ctypes as c
+        E = counts.numel()
+        dev = counts.device
+        self.E, self.H, self.I = E, H, I
+        self.counts = counts
+        self.rows_cap = (num_pairs + 63 * E + 127) // 128 * 128 if rows_cap is None else int(rows_cap)
+        blocks = self.rows_cap // 128 + E
+        I2 = 2 * I
+        t = lambda n: (n + 127) // 128
+        self.max_tiles = [blocks * t(I2), blocks * t(H), blocks * t(I), blocks * t(H)]
+        sizes = self.max_tiles + [E * t(H) * t(I), E * t(I2) * t(H)]
+        self.wgrad_tiles = sizes[4:]
+        self.maps = [torch.empty((n, 4), dtype=torch.int32, device=dev) for n in sizes]
+        self.exts = [torch.empty((n, 4), dtype=torch.int32, device=dev) for n in sizes]
+        self.seg_start = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        self.n_tiles = torch.empty(4, dtype=torch.int32, device=dev)
+        fn = _plan_fns()["plan"]
+        arr = c.c_void_p * 6
+        _lib.check(fn(_lib.ptr(counts), E, H, I, arr(*[m.data_ptr() for m in self.maps]),
+                      arr(*[x.data_ptr() for x in self.exts]), (c.c_int * 4)(*self.max_tiles), _lib.ptr(self.seg_start),
+                      _lib.ptr(self.n_tiles), _lib.stream_ptr()), "apb_moe_plan")
+
+    def padded_rows(self, sorted_expert: torch.Tensor) -> torch.Tensor:
+        """Padded row of every pair of an expert-sorted list (``sorted_expert [P]`` int64, ascending)."""
+        c64 = self.counts.to(torch.int64)
+        first = c64.cumsum(0) - c64
+        P = sorted_expert.numel()
+        within = torch.arange(P, device=sorted_expert.device) - first[sorted_expert]
+        return self.seg_start.to(torch.int64)[sorted_expert] + within
+
+
+_PLAN_FNS = {}
+
+
+def _plan_fns():
+    if not _PLAN_FNS:
+        import ctypes as c
+        from ..ops import _lib
+        vp, i, ll, f = c.c_void_p, c.c_int, c.c_longlong, c.c_float
+        _PLAN_FNS["plan"] = _lib.declare("apb_moe_plan", [vp, i, i, i, vp, vp, vp, vp, vp, vp])
+        _PLAN_FNS["gemm"] = _lib.declare("apb_gemm_bf16_grouped_ext",
+                                         [vp, vp, vp, i, i, i, ll, ll, ll, i, i, i, f, vp, vp, i, vp, ll, ll, vp])
+    return _PLAN_FNS
+
+
+def _grouped_ext(A, B, C, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, plan: MoEPlan, g: int, b_n_rows=0, b_k_rows=0):
+    from ..ops import _lib
+    live = g < 4
+    _lib.check(_plan_fns()["gemm"](_lib.ptr(A), _lib.ptr(B), _lib.ptr(C), M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, 1.0,
+                                   _lib.ptr(plan.maps[g]), _lib.ptr(plan.exts[g]),
+                                   plan.max_tiles[g] if live else plan.wgrad_tiles[g - 4],
+                                   _lib.ptr(plan.n_tiles[g:]) if live else None, b_n_rows, b_k_rows,
+                                   _lib.stream_ptr()), f"grouped expert GEMM {g}")
+
+
+class _GroupedFFNPaddedFn(torch.autograd.Function):
+    """Expert FFN over the padded expert-major layout of :class:`MoEPlan`, forward AND backward as grouped tcgen05
+    GEMMs driven by device tables: two forward GEMMs (gate/up with the SwiGLU epilogue, down), two data-gradient
+    GEMMs against the K-major view of the stacked weights and two weight-gradient GEMMs whose tiles walk the rows of
+    their expert -- six launches and one SwiGLU-backward kernel per layer, none of them sized on the host."""
+
+    @staticmethod
+    def forward(ctx, x_pad, wgu, wdown, plan: MoEPlan):
+        from ..ops import _lib
+        E, I2, H = wgu.shape
+        I = I2 // 2
+        R = x_pad.shape[0]
+        gu = torch.empty((R, I2), device=x_pad.device, dtype=x_pad.dtype)
+        act = torch.empty((R, I), device=x_pad.device, dtype=x_pad.dtype)
+        y = torch.empty((R, H), device=x_pad.device, dtype=x_pad.dtype)
+        fn = _grouped_dev_fns()["gemm"]
+        w1, w2 = wgu.view(E * I2, H), wdown.view(E * H, I)
+        _lib.check(fn(_lib.ptr(x_pad), _lib.ptr(w1), _lib.ptr(gu), R, I2, H, x_pad.stride(0), w1.stride(0), gu.stride(0),
+                      gemm.EPI_SWIGLU, 1.0, _lib.ptr(act), act.stride(0), _lib.ptr(plan.maps[0]), plan.max_tiles[0],
+                      _lib.ptr(plan.n_tiles), E * I2, _lib.stream_ptr()), "grouped gate/up")
+        _lib.check(fn(_lib.ptr(act), _lib.ptr(w2), _lib.ptr(y), R, H, I, act.stride(0), w2.stride(0), y.stride(0),
+                      gemm.EPI_BF16, 1.0, None, 0, _lib.ptr(plan.maps[1]), plan.max_tiles[1], _lib.ptr(plan.n_tiles[1:]),
+                      E * H, _lib.stream_ptr()), "grouped down")
+        ctx.save_for_backward(x_pad, wgu, wdown, gu, act)
+        ctx.plan = plan
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import _lib
+        x_pad, wgu, wdown, gu, act = ctx.saved_tensors
+        plan = ctx.plan
+        E, I2, H = wgu.shape
+        I = I2 // 2
+        R = x_pad.shape[0]
+        dy = dy.contiguous()
+        dev = x_pad.device
+        acc_gu = getattr(wgu, "grad_f32", None)
+        acc_dn = getattr(wdown, "grad_f32", None)
+        dwgu = acc_gu if acc_gu is not None else torch.zeros(wgu.shape, device=dev, dtype=torch.float32)
+        dwdn = acc_dn if acc_dn is not None else torch.zeros(wdown.shape, device=dev, dtype=torch.float32)
+        w1, w2 = wgu.view(E * I2, H), wdown.view(E * H, I)
+        dact = torch.empty_like(act)
+        dgu = torch.empty_like(gu)
+        dx = torch.empty_like(x_pad)
+        # d act = dY @ Wdown[e]: the stacked [E * H, I] weight read K-major, K offset e * H per tile
+        _grouped_ext(dy, w2, dact, R, I, H, dy.stride(0), w2.stride(0), dact.stride(0), 0, 1, gemm.EPI_BF16, plan, 2,
+                     b_k_rows=E * H)
+        # dWdown[e] += dY[rows of e]^T @ act[rows of e]
+        _grouped_ext(dy, act, dwdn.view(E * H, I), H, I, R, dy.stride(0), act.stride(0), I, 1, 1, gemm.EPI_F32_ACCUM,
+                     plan, 4)
+        _lib.check(_lib.cuda_lib().apb_swiglu_bwd(_lib.ptr(gu), _lib.ptr(dact), _lib.ptr(dgu), R, I, _lib.stream_ptr()),
+                   "swiglu_bwd")
+        _grouped_ext(dgu, w1, dx, R, H, I2, dgu.stride(0), w1.stride(0), dx.stride(0), 0, 1, gemm.EPI_BF16, plan, 3,
+                     b_k_rows=E * I2)
+        _grouped_ext(dgu, x_pad, dwgu.view(E * I2, H), I2, H, R, dgu.stride(0), x_pad.stride(0), H, 1, 1,
+                     gemm.EPI_F32_ACCUM, plan, 5)
+        return (dx, None if acc_gu is not None else dwgu.to(wgu.dtype),
+                None if acc_dn is not None else dwdn.to(wdown.dtype), None)
+
+
+def padded_plan_supported(x: torch.Tensor, wgu: torch.Tensor) -> bool:
+    """The padded device-planned path needs the GPU, bf16 and at most 512 experts (one block builds the plan)."""
+    E, I2, H = wgu.shape
+    return (x.is_cuda and x.dtype == torch.bfloat16 and E <= 512 and H % 8 == 0 and (I2 // 2) % 8 == 0
+            and os.environ.get("APB_MOE_PADDED", "1") != "0")
 
 
 class _GroupedFFNFn(torch.autograd.Function):
@@ -282,8 +416,16 @@ class MoEFeedForward(nn.Module):
         counts = _expert_histogram(flat_e, cfg.num_experts)
         self.last_tokens_per_expert = counts.detach()
         src_tok = torch.div(order, k, rounding_mode="floor")
-        xs = x.index_select(0, src_tok)
-        ys = grouped_ffn(xs, self.wgu, self.wdown, counts)
+        if torch.is_grad_enabled() and padded_plan_supported(x, self.wgu):
+            # training: padded expert-major rows, forward and backward as grouped GEMMs planned on the device
+            plan = MoEPlan(counts.to(torch.int32), flat_e.numel(), H, self.wgu.shape[1] // 2)
+            pos = plan.padded_rows(flat_e.index_select(0, order))
+            x_pad = torch.zeros((plan.rows_cap, H), device=x.device, dtype=x.dtype).index_copy(
+                0, pos, x.index_select(0, src_tok))
+            ys = _GroupedFFNPaddedFn.apply(x_pad, self.wgu, self.wdown, plan).index_select(0, pos)
+        else:
+            xs = x.index_select(0, src_tok)
+            ys = grouped_ffn(xs, self.wgu, self.wdown, counts)
         wflat = w.reshape(-1).index_select(0, order).to(ys.dtype)
         out = torch.zeros((T, H), device=x.device, dtype=torch.float32 if x.is_cuda else x.dtype)
         out.index_add_(0, src_tok, (ys * wflat[:, None]).to(out.dtype))

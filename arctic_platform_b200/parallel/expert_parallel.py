@@ -4,11 +4,15 @@ Experts are sharded over the ranks of a group (rank ``d`` owns experts ``[d*El, 
 
 1. routing (fp32 softmax + top-k) and an all-gather of the per-expert pair counts (``[W, E]`` int64 -- the only
    library collective, 8 * E bytes; the reference all-reduces a chunk count there,
-   arctic_platform/model/implementations/qwen35/models/layers/moe.py:451-454);
+   arctic_platform/model/implementations/qwen35/models/layers/moe.py:451-454).  The count matrix STAYS ON THE
+   GPU: every offset, the owner's padded expert-major row layout and the tile tables of the grouped GEMMs are
+   derived from it by device code (``plan_routing_device``, ``models.moe.MoEPlan``), and the receive buffers are
+   sized for a fixed capacity (``max_recv_rows``), so a layer call never synchronises with the host;
 2. **dispatch**: every routed (token, expert) pair is written by ``ep_scatter_rows_kernel`` straight into the
    owner rank's receive buffer at its final, expert-sorted row (offsets are computed identically on every
    rank from the count matrix, so no second exchange is needed), together with a ``(source rank, pair)`` tag;
-3. the owner runs the grouped tcgen05 GEMMs over its rows (``models/moe.py``);
+3. the owner runs the grouped tcgen05 GEMMs over its rows (``models/moe.py``: forward, data gradients and weight
+   gradients from device tables);
 4. **combine**: in inference the second expert GEMM stores each output row directly into the source rank's
    combine buffer from its epilogue (``apb_gemm_scatter`` -- compute and all-to-all in one kernel); in training
    the rows go back through the same scatter kernel so that every stage has an exact transpose for autograd;
@@ -38,7 +42,8 @@ def _fns():
         c = ctypes
         vp, i, ll = c.c_void_p, c.c_int, c.c_longlong
         _FN["scatter"] = _lib.declare("apb_ep_scatter_rows", [vp, ll, vp, vp, vp, vp, vp, ll, vp, i, i, i, i, vp])
-        _FN["gscatter"] = _lib.declare("apb_gemm_scatter", [vp, vp, vp, i, vp, i, i, i, ll, ll, ll, vp, i, ll, vp])
+        _FN["gscatter"] = _lib.declare("apb_gemm_scatter_dev",
+                                       [vp, vp, vp, i, vp, i, i, i, ll, ll, ll, vp, i, vp, ll, vp])
         _FN["wait"] = _lib.declare("apb_epoch_wait", [vp, i, i, i, vp])
     return _FN
 
@@ -94,6 +99,58 @@ def plan_routing(idx: torch.Tensor, num_experts: int, world: int, rank: int, gro
     return routing
 
 
+@dataclass
+class DeviceRouting:
+    """The fused path's plan: nothing here was computed on the host except ``num_pairs`` and the capacity."""
+    order: torch.Tensor        # [P] pair indices sorted by expert
+    src_tok: torch.Tensor      # [P] token of each sorted pair (int32)
+    dst_rank: torch.Tensor     # [P] owner rank of each sorted pair (int32; -1 = dropped: capacity exceeded)
+    dst_row: torch.Tensor      # [P] padded row in the owner's receive buffer (int32)
+    recv_counts: torch.Tensor  # [El] rows per local expert on THIS rank (int32, GPU)
+    valid: torch.Tensor        # [cap] bool: the receive-buffer row holds a routed pair (not padding)
+    plan: object               # models.moe.MoEPlan of this rank's experts
+    recv_rows: int             # = capacity (host)
+    num_pairs: int
+
+
+def plan_routing_device(idx: torch.Tensor, num_experts: int, world: int, rank: int, group, cap: int, hidden: int,
+                        expert_width: int, overflow: torch.Tensor) -> DeviceRouting:
+    """Like :func:`plan_routing`, for the padded layout of :class:`models.moe.MoEPlan` (every expert's rows on its
+    owner start at a multiple of 64) and without a device->host copy.  ``overflow`` (int32 [1], GPU) is raised when
+    a rank would receive more rows than ``cap``; such pairs are dropped instead of written out of bounds."""
+    from ..models.moe import MoEPlan, _expert_histogram
+    P = idx.numel()
+    k = idx.shape[1]
+    El = num_experts // world
+    flat = idx.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = _expert_histogram(flat, num_experts)
+    allc = torch.empty((world, num_experts), dtype=counts.dtype, device=counts.device)
+    dist.all_gather_into_tensor(allc.view(-1), counts.contiguous(), group=group)
+    tot = allc.sum(0)                                              # pairs per expert over all ranks
+    padded = (tot + 63) // 64 * 64
+    blk = padded.view(world, El)
+    base = (blk.cumsum(1) - blk).reshape(-1)                       # padded start of each expert on its owner
+    before_me = allc[:rank].sum(0) if rank > 0 else torch.zeros_like(tot)
+    start = base + before_me
+    sorted_e = flat[order]
+    first = counts.cumsum(0) - counts
+    dst_row = start[sorted_e] + (torch.arange(P, device=idx.device) - first[sorted_e])
+    used = blk.sum(1)                                              # padded rows in use on every rank
+    overflow |= (used.max() > cap).to(overflow.dtype)
+    dst_rank = torch.div(sorted_e, El, rounding_mode="floor")
+    dst_rank = torch.where(dst_row < cap, dst_rank, torch.full_like(dst_rank, -1)).to(torch.int32)
+    mine = tot[rank * El:(rank + 1) * El].to(torch.int32)
+    plan = MoEPlan(mine, 0, hidden, expert_width, rows_cap=cap)
+    rows = torch.arange(cap, device=idx.device)
+    seg = plan.seg_start.to(torch.int64)
+    e_of = torch.searchsorted(seg[1:].contiguous(), rows, right=True).clamp_(max=El - 1)
+    valid = (rows - seg[e_of]) < mine.to(torch.int64)[e_of]
+    valid &= rows < seg[El]
+    return DeviceRouting(order, torch.div(order, k, rounding_mode="floor").to(torch.int32), dst_rank,
+                         dst_row.to(torch.int32), mine, valid, plan, cap, P)
+
+
 class ExpertParallel:
     def __init__(self, hidden: int, num_experts: int, group=None, device="cuda", max_recv_rows: int = 1 << 16,
                  max_pairs: int = 1 << 16, impl: str = "fused"):
@@ -109,7 +166,16 @@ class ExpertParallel:
             self.recv = SymmetricBuffer(max_recv_rows * hidden, torch.bfloat16, device, group)
             self.meta = SymmetricBuffer(max_recv_rows * 2, torch.int32, device, group)
             self.comb = SymmetricBuffer(max_pairs * hidden, torch.bfloat16, device, group)
-        self.max_recv_rows, self.max_pairs = max_recv_rows, max_pairs
+            self.overflow = torch.zeros(1, dtype=torch.int32, device=device)
+        self.max_recv_rows, self.max_pairs = max_recv_rows // 128 * 128, max_pairs
+
+    def raise_if_overflowed(self) -> None:
+        """One host read: did any layer call since the last check receive more rows than the buffers hold?  (The
+        pairs beyond the capacity were dropped, not written.)  The training engine asks once per optimizer step."""
+        if self.impl == "fused" and int(self.overflow.item()) != 0:
+            self.overflow.zero_()
+            raise ValueError(f"expert-parallel receive capacity ({self.max_recv_rows} rows) exceeded; "
+                             "raise max_recv_rows")
 
     # ------------------------------------------------------------------ exchange primitives
     def _barrier(self) -> None:
@@ -130,7 +196,12 @@ class ExpertParallel:
                                      self.meta.ptr_table(), self.rank, self.world, r.num_pairs, H, _lib.stream_ptr()),
                    "apb_ep_scatter_rows")
         self._barrier()
-        return self.recv.tensor[: r.recv_rows * H].view(r.recv_rows, H).clone()
+        got = self.recv.tensor[: r.recv_rows * H].view(r.recv_rows, H)
+        if not torch.is_grad_enabled():
+            return got          # read in place: the layer's closing barrier comes before the next dispatch lands here
+        # padding rows of the layout still hold rows of an earlier call: they must read as zeros (the weight-gradient
+        # GEMMs walk whole 64-row blocks)
+        return torch.where(r.valid[:, None], got, torch.zeros((), dtype=got.dtype, device=got.device))
 
     def _to_sources(self, rows: torch.Tensor, r: Routing) -> torch.Tensor:
         """This rank's processed rows -> the source ranks' combine buffers (pair order); returns ``[P, H]``."""
@@ -143,7 +214,7 @@ class ExpertParallel:
         meta = self.meta.tensor[: r.recv_rows * 2].view(r.recv_rows, 2)
         src_row = torch.arange(r.recv_rows, device=rows.device, dtype=torch.int32)
         # named tensors: a temporary handed to ptr() would be freed (and its block reused) before the launch
-        to_rank = meta[:, 0].contiguous()
+        to_rank = torch.where(r.valid, meta[:, 0], torch.full_like(meta[:, 0], -1))      # padding rows go nowhere
         to_row = meta[:, 1].contiguous()
         _lib.check(_fns()["scatter"](_lib.ptr(rows), rows.stride(0), _lib.ptr(src_row), _lib.ptr(to_rank),
                                      _lib.ptr(to_row), None, self.comb.ptr_table(), H, None, self.rank,
@@ -156,33 +227,48 @@ class ExpertParallel:
         from ..models.moe import grouped_ffn
         T, H = x.shape
         k = idx.shape[1]
+        if self.impl == "fused":
+            from ..models.moe import _GroupedFFNPaddedFn
+            if idx.numel() > self.max_pairs:
+                raise ValueError("expert-parallel scratch too small for this batch")
+            r = plan_routing_device(idx, self.num_experts, self.world, self.rank, self.group, self.max_recv_rows, H,
+                                    moe.wgu.shape[1] // 2, self.overflow)
+            moe.last_tokens_per_expert = r.recv_counts
+            x_recv = _DispatchFn.apply(x, self, r)
+            if not torch.is_grad_enabled():
+                y_pairs = self._ffn_with_fused_combine(moe, x_recv, r)
+            else:
+                y_recv = _GroupedFFNPaddedFn.apply(x_recv, moe.wgu, moe.wdown, r.plan)
+                y_pairs = _CombineFn.apply(y_recv, self, r)
+            return (y_pairs.view(T, k, H).float() * w[..., None]).sum(1).to(x.dtype)
         r = plan_routing(idx, self.num_experts, self.world, self.rank, self.group)
         moe.last_tokens_per_expert = r.recv_counts
         x_recv = _DispatchFn.apply(x, self, r)
-        if self.impl == "fused" and not torch.is_grad_enabled():
-            y_pairs = self._ffn_with_fused_combine(moe, x_recv, r)
-        else:
-            y_recv = grouped_ffn(x_recv, moe.wgu, moe.wdown, r.recv_counts)
-            y_pairs = _CombineFn.apply(y_recv, self, r)
+        y_recv = grouped_ffn(x_recv, moe.wgu, moe.wdown, r.recv_counts)
+        y_pairs = _CombineFn.apply(y_recv, self, r)
         return (y_pairs.view(T, k, H).float() * w[..., None]).sum(1).to(x.dtype)
 
     def _ffn_with_fused_combine(self, moe, x_recv: torch.Tensor, r: Routing) -> torch.Tensor:
         """Inference path: GEMM 1 with the SwiGLU epilogue, GEMM 2 whose epilogue stores every output row into
         the source rank's combine buffer (no separate combine kernel)."""
-        from ..models.moe import build_group_tiles
+        from ..models.moe import _grouped_dev_fns
         from ..ops import gemm
         El, I2, H = moe.wgu.shape
-        rows = r.recv_rows
-        if rows > 0:
-            t1 = build_group_tiles(r.recv_counts, I2, x_recv.device)
-            t2 = build_group_tiles(r.recv_counts, H, x_recv.device)
-            act = torch.empty((rows, I2 // 2), device=x_recv.device, dtype=x_recv.dtype)
-            gemm.gemm_raw(x_recv, moe.wgu.view(El * I2, H), None, M=rows, N=I2, K=H, epi=gemm.EPI_SWIGLU, out2=act,
-                          tile_map=t1, b_rows=El * I2, bn=128)
-            meta = self.meta.tensor[: rows * 2]
-            _lib.check(_fns()["gscatter"](_lib.ptr(act), _lib.ptr(moe.wdown.view(El * H, I2 // 2)), self.comb.ptr_table(),
-                                          self.world, _lib.ptr(meta), rows, H, I2 // 2, act.stride(0), I2 // 2, H,
-                                          _lib.ptr(t2), t2.shape[0], El * H, _lib.stream_ptr()), "apb_gemm_scatter")
+        rows, plan = r.recv_rows, r.plan
+        w1 = moe.wgu.view(El * I2, H)
+        act = torch.empty((rows, I2 // 2), device=x_recv.device, dtype=x_recv.dtype)
+        _lib.check(_grouped_dev_fns()["gemm"](_lib.ptr(x_recv), _lib.ptr(w1), None, rows, I2, H, x_recv.stride(0),
+                                              w1.stride(0), 0, gemm.EPI_SWIGLU, 1.0, _lib.ptr(act), act.stride(0),
+                                              _lib.ptr(plan.maps[0]), plan.max_tiles[0], _lib.ptr(plan.n_tiles),
+                                              El * I2, _lib.stream_ptr()), "grouped gate/up")
+        # (rank, row) of every receive-buffer row; padding rows are dropped by the epilogue (rank -1)
+        meta = self.meta.tensor[: rows * 2].view(rows, 2)
+        row_map = torch.where(r.valid[:, None], meta, torch.tensor([-1, 0], dtype=meta.dtype, device=meta.device))
+        row_map = row_map.contiguous()
+        _lib.check(_fns()["gscatter"](_lib.ptr(act), _lib.ptr(moe.wdown.view(El * H, I2 // 2)), self.comb.ptr_table(),
+                                      self.world, _lib.ptr(row_map), rows, H, I2 // 2, act.stride(0), I2 // 2, H,
+                                      _lib.ptr(plan.maps[1]), plan.max_tiles[1], _lib.ptr(plan.n_tiles[1:]), El * H,
+                                      _lib.stream_ptr()), "apb_gemm_scatter_dev")
         self._barrier()
         return self.comb.tensor[: r.num_pairs * H].view(r.num_pairs, H).clone()
 

@@ -95,3 +95,55 @@ def test_moe_layer_forward_and_backward_with_device_built_tiles():
     ref.pow(2).sum().backward()
     assert (y.float() - ref).abs().max() < 3e-2 * ref.abs().max() + 1e-3
     assert (x.grad.float() - xr.grad).abs().max() < 5e-2 * xr.grad.abs().max() + 1e-3
+
+
+@pytest.mark.parametrize("tokens,experts,top_k", [(300, 16, 4), (37, 8, 2), (1024, 64, 8)])
+def test_moe_layer_padded_plan_backward_matches_per_expert_fp32(tokens, experts, top_k):
+    """Training path of the expert layer: padded expert-major rows, forward, data gradients and weight gradients as
+    grouped GEMMs planned by a kernel (no expert count reaches the host) against an fp32 per-expert loop; skewed
+    routing leaves some experts without tokens."""
+    import dataclasses
+    from arctic_platform_b200.models.config import PRESETS
+    from arctic_platform_b200.models.moe import MoEFeedForward
+    from arctic_platform_b200.ops import _lib
+    cfg = dataclasses.replace(PRESETS["qwen3-moe-tiny"], hidden_size=256, moe_intermediate_size=192, num_experts=experts,
+                              num_experts_per_tok=top_k, shared_expert_intermediate_size=0)
+    torch.manual_seed(1)
+    moe = MoEFeedForward(cfg, "cuda", torch.bfloat16)
+    for p in moe.parameters():
+        p.data.normal_(0, 0.05)
+    moe.router.data[experts // 2:] -= 1.0                          # starve the upper half of the experts
+    x = (torch.randn(tokens, 256, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    from arctic_platform_b200.models.moe import route_topk
+    route = lambda lg, forced: route_topk(lg, top_k, cfg.norm_topk_prob, cfg.moe_score_func, cfg.moe_route_scale, None,
+                                          forced, cfg.moe_n_group, cfg.moe_topk_group)
+    with torch.no_grad():
+        _, idx = route((x.float() @ moe.router.float().t()), None)
+    moe.routed_experts = idx                                       # both sides route identically
+    y = moe(x)
+    (y.float() * torch.linspace(-1, 1, 256, device="cuda")).sum().backward()
+    _lib.check_status("moe padded plan")
+    # oracle: same routing decision, fp32 math (the routing weights carry gradient to x through the router)
+    xr = x.detach().float().requires_grad_(True)
+    wgu = moe.wgu.detach().float().requires_grad_(True)
+    wdn = moe.wdown.detach().float().requires_grad_(True)
+    w, _ = route(xr @ moe.router.detach().float().t(), idx)
+    out = torch.zeros(tokens, 256, device="cuda")
+    for e in range(experts):
+        tok, slot = (idx == e).nonzero(as_tuple=True)
+        if tok.numel() == 0:
+            continue
+        gu = xr[tok] @ wgu[e].t()
+        ye = (torch.nn.functional.silu(gu[:, 0::2]) * gu[:, 1::2]) @ wdn[e].t()
+        out = out.index_add(0, tok, ye * w[tok, slot, None].float())
+    (out * torch.linspace(-1, 1, 256, device="cuda")).sum().backward()
+    tol = lambda ref: 4e-2 * ref.abs().max() + 1e-3
+    assert (y.float() - out).abs().max() < tol(out)
+    assert (x.grad.float() - xr.grad).abs().max() < tol(xr.grad)
+    g_gu = moe.wgu.grad_f32 if getattr(moe.wgu, "grad_f32", None) is not None else moe.wgu.grad.float()
+    g_dn = moe.wdown.grad_f32 if getattr(moe.wdown, "grad_f32", None) is not None else moe.wdown.grad.float()
+    assert (g_gu - wgu.grad).abs().max() < tol(wgu.grad)
+    assert (g_dn - wdn.grad).abs().max() < tol(wdn.grad)
+    starved = (torch.bincount(idx.reshape(-1), minlength=experts) == 0).nonzero().flatten().tolist()
+    for e in starved:                                              # experts without tokens: exactly zero gradient
+        assert float(g_gu[e].abs().max()) == 0.0 and float(g_dn[e].abs().max()) == 0.0
