@@ -78,3 +78,27 @@ def test_swiglu_fwd_bwd():
     ar.backward(d.float())
     assert torch.allclose(act.float(), ar.detach(), atol=3e-2, rtol=2e-2)
     assert torch.allclose(gu.grad.float(), gr.grad, atol=5e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("T,H,Dk,Dv", [(200, 4, 128, 128), (64, 2, 32, 48), (1000, 3, 64, 128)])
+def test_delta_rule_scan_kernel_matches_the_token_by_token_recurrence(T, H, Dk, Dv):
+    """The chunk recurrence of the gated delta rule as one kernel (no-grad passes) against the token-by-token oracle
+    and against the differentiable PyTorch loop, with and without a carried-in state."""
+    from arctic_platform_b200.models.linear_attention import gated_delta_rule_chunked, gated_delta_rule_recurrent
+    from arctic_platform_b200.ops import _lib
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn(T, H, Dk, device="cuda", generator=g)
+    k = torch.randn(T, H, Dk, device="cuda", generator=g)
+    v = torch.randn(T, H, Dv, device="cuda", generator=g)
+    gate = -torch.rand(T, H, device="cuda", generator=g) * 0.3
+    beta = torch.rand(T, H, device="cuda", generator=g)
+    S0 = torch.randn(H, Dk, Dv, device="cuda", generator=g) * 0.1
+    for state in (None, S0):
+        want_o, want_S = gated_delta_rule_recurrent(q, k, v, gate, beta, state)
+        with torch.no_grad():
+            got_o, got_S = gated_delta_rule_chunked(q, k, v, gate, beta, state)            # kernel
+        _lib.check_status("delta rule scan")
+        with torch.enable_grad():
+            loop_o, loop_S = gated_delta_rule_chunked(q, k, v, gate, beta, state)          # PyTorch loop
+        for a, b in ((got_o, want_o), (got_S, want_S), (got_o, loop_o), (got_S, loop_S)):
+            assert (a - b).abs().max() < 2e-3 * b.abs().max() + 1e-4
