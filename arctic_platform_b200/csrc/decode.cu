@@ -267,25 +267,12 @@ __device__ __forceinline__ void decode_issue_page(uint32_t stage_addr, const __n
   }
 }
 
-// Optional tail of the per-sequence pass: when it runs unsplit (one CTA sees a sequence's whole private context) it
-// can finish the cascade itself -- join its result with the partials the shared-node pass left for the row
-// (log-sum-exp merge over up to three shared levels) and write the normalised bf16 output, instead of storing its own
-// partial for a separate merge launch.  out == null: off.
-struct FusedMerge {
-  const float* o[3];      // per shared level: [Bq, Hq, splits_l, D]
-  const float* ml[3];     // per shared level: [Bq, Hq, splits_l, 2]
-  int splits[3];
-  int n;                  // shared levels
-  const int* row_mask;    // [Bq] bit l: the row has a node at level l (null: every level applies to every row)
-  __nv_bfloat16* out;     // [Bq, Hq, D]
-};
-
 __global__ void __launch_bounds__(kDecThreads)
 paged_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const int* __restrict__ q_start,
                         const int* __restrict__ q_count, const int* __restrict__ pages, int max_pages,
                         const int* __restrict__ kv_len, const __nv_bfloat16* __restrict__ kcache,
                         const __nv_bfloat16* __restrict__ vcache, float* __restrict__ out_o, float* __restrict__ out_ml,
-                        int Hq, int Hkv, int splits, float scale_log2, const FusedMerge fm) {
+                        int Hq, int Hkv, int splits, float scale_log2) {
   pdl_entry();
   constexpr int D = 128;
   extern __shared__ __align__(128) uint8_t dec_smem[];
@@ -305,12 +292,6 @@ paged_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const int* __restri
   const int n_my = (p1 - p0 - warp + 3) / 4;  // pages p0 + warp, p0 + warp + 4, ... (<= 0: none)
   const int q_per_pass = 16 / R;              // queries whose R heads fit the 16 MMA rows
   const int quad_row = lane >> 2, quad_col = (lane & 3) * 2;
-  if (fm.out != nullptr && nq <= 0) {
-    // an idle slot: nobody else writes its output row, and what follows (projections, norms) should see finite data
-    for (int i = threadIdx.x; i < R * D; i += kDecThreads)
-      fm.out[(static_cast<long long>(qs) * Hq + kvh * R) * D + i] = __float2bfloat16(0.f);
-    return;
-  }
 
   for (int q0 = 0; q0 < nq; q0 += q_per_pass) {
     const int rows_valid = min(q_per_pass, nq - q0) * R;
@@ -465,30 +446,6 @@ paged_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const int* __restri
         ll += red_l[w * 16 + rr] * scw;
       }
       const long long qrow = qs + q0 + rr / R;
-      if (fm.out != nullptr) {
-        // join with the shared levels of this row and finish: (mm, ll, ov) is the private pass's partial
-        const long long rh = qrow * Hq + kvh * R + rr % R;
-        const int valid = fm.row_mask ? fm.row_mask[qrow] : 0x7;
-        float gm = mm;
-        for (int l = 0; l < fm.n; ++l) {
-          if (!((valid >> l) & 1)) continue;
-          for (int k = 0; k < fm.splits[l]; ++k) gm = fmaxf(gm, fm.ml[l][(rh * fm.splits[l] + k) * 2]);
-        }
-        const float s0 = (mm == -INFINITY) ? 0.f : exp2f(mm - gm);
-        float acc = ov * s0, lsum = ll * s0;
-        for (int l = 0; l < fm.n; ++l) {
-          if (!((valid >> l) & 1)) continue;
-          for (int k = 0; k < fm.splits[l]; ++k) {
-            const long long b = rh * fm.splits[l] + k;
-            const float m = fm.ml[l][b * 2];
-            const float sc = (m == -INFINITY) ? 0.f : exp2f(m - gm);
-            lsum += fm.ml[l][b * 2 + 1] * sc;
-            acc += fm.o[l][b * D + d] * sc;
-          }
-        }
-        fm.out[rh * D + d] = __float2bfloat16(lsum > 0.f ? acc / lsum : 0.f);
-        continue;
-      }
       const long long base = ((qrow * Hq + kvh * R + rr % R) * splits + split);
       out_o[base * D + d] = ov;
       if (d == 0) {
@@ -1021,7 +978,7 @@ int apb_paged_decode_partial(const void* q, const int* q_start, const int* q_cou
                                           static_cast<const __nv_bfloat16*>(q), q_start, q_count, pages, max_pages,
                                           kv_len, static_cast<const __nv_bfloat16*>(kcache),
                                           static_cast<const __nv_bfloat16*>(vcache), out_o, out_ml, Hq, Hkv, splits,
-                                          sl2, FusedMerge{}));
+                                          sl2));
   }
 #define APB_DEC(RR)                                                                                           \
   paged_decode_kernel<RR, 128><<<grid, kDecThreads, 0, s>>>(                                                  \
@@ -1035,44 +992,6 @@ int apb_paged_decode_partial(const void* q, const int* q_start, const int* q_cou
   else return kBadArgument;
 #undef APB_DEC
   return static_cast<int>(cudaGetLastError());
-}
-
-// Per-sequence pass that also finishes the cascade (see FusedMerge): unsplit, tensor-core form only (16 % R == 0).
-// shared_o / shared_ml / shared_splits: the partials of `n_shared` (0..3) shared levels as the shared-node pass wrote
-// them; row_mask as in apb_decode_merge; out [Bq, Hq, D] bf16.  Rows of groups with q_count == 0 are not written.
-int apb_paged_decode_merge_fused(const void* q, const int* q_start, const int* q_count, const int* pages, int max_pages,
-                                 const int* kv_len, const void* kcache, const void* vcache, int G, int Hq, int Hkv, int D,
-                                 float scale, const float* const* shared_o, const float* const* shared_ml,
-                                 const int* shared_splits, int n_shared, const int* row_mask, void* out,
-                                 cudaStream_t s) {
-  if (G <= 0) return 0;
-  if (D != 128 || Hq % Hkv || !out || n_shared < 0 || n_shared > 3) return kBadArgument;
-  const int R = Hq / Hkv;
-  if (16 % R != 0 || g_decode_scalar) return kBadArgument;
-  FusedMerge fm{};
-  for (int l = 0; l < n_shared; ++l) {
-    if (!shared_o || !shared_ml || !shared_splits || !shared_o[l] || !shared_ml[l] || shared_splits[l] < 1)
-      return kBadArgument;
-    fm.o[l] = shared_o[l];
-    fm.ml[l] = shared_ml[l];
-    fm.splits[l] = shared_splits[l];
-  }
-  fm.n = n_shared;
-  fm.row_mask = row_mask;
-  fm.out = static_cast<__nv_bfloat16*>(out);
-  static bool configured[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!configured[dev & 63]) {
-    cudaError_t e = cudaFuncSetAttribute(paged_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMmaSmem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured[dev & 63] = true;
-  }
-  return static_cast<int>(launch_kernel(paged_decode_mma_kernel, dim3(G * Hkv, 1), dim3(kDecThreads), kMmaSmem, s,
-                                        static_cast<const __nv_bfloat16*>(q), q_start, q_count, pages, max_pages, kv_len,
-                                        static_cast<const __nv_bfloat16*>(kcache),
-                                        static_cast<const __nv_bfloat16*>(vcache), static_cast<float*>(nullptr),
-                                        static_cast<float*>(nullptr), Hq, Hkv, 1, scale * 1.4426950408889634f, fm));
 }
 
 // Merges up to 4 partial sets into out [rows, Hq, D] bf16 (+ optional natural-log LSE [rows, Hq]).

@@ -18,7 +18,6 @@ from __future__ import annotations
 
 import ctypes
 import math
-import os
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
@@ -39,8 +38,6 @@ def _fn(name: str):
         vp, i, ll, f = c.c_void_p, c.c_int, c.c_longlong, c.c_float
         _FN["dec"] = _lib.declare("apb_paged_decode_partial", [vp, vp, vp, vp, i, vp, vp, vp, vp, vp, i, i, i, i, i, f, vp])
         _FN["merge"] = _lib.declare("apb_decode_merge", [vp, vp, vp, i, vp, vp, vp, i, i, i, vp])
-        _FN["dec_fused"] = _lib.declare("apb_paged_decode_merge_fused",
-                                        [vp, vp, vp, vp, i, vp, vp, vp, i, i, i, i, f, vp, vp, vp, i, vp, vp, vp])
         _FN["prefix_tc"] = _lib.declare("apb_decode_prefix_tc",
                                         [vp, i, vp, vp, vp, i, vp, vp, vp, vp, ll, vp, vp, i, i, i, i, i, i, f, vp])
     return _FN[name]
@@ -147,19 +144,6 @@ def forest_decode_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch
                                     _lib.ptr(forest.pages), forest.pages.shape[1], _lib.ptr(forest.kv_len),
                                     _lib.ptr(forest.level), _lib.ptr(kcache), _lib.ptr(vcache), num_pages, o_lv, ml_lv,
                                     nl, G, Hq, Hkv, D, splits, scale, s), "decode_prefix_tc")
-    R = Hq // Hkv
-    if seq_splits == 1 and 16 % R == 0 and os.environ.get("APB_DECODE_FUSED_MERGE", "1") != "0":
-        # the per-sequence pass sees each sequence's whole private context in one CTA: it joins the shared levels'
-        # partials itself and writes the final rows (no partial round trip, no merge launch)
-        n_sh = nl if G > 0 else 0
-        so = (ctypes.c_void_p * 3)(*[part_o[i].data_ptr() if i < n_sh else 0 for i in range(3)])
-        sml = (ctypes.c_void_p * 3)(*[part_ml[i].data_ptr() if i < n_sh else 0 for i in range(3)])
-        ssp = (ctypes.c_int * 3)(*[splits if i < n_sh else 0 for i in range(3)])
-        _lib.check(_fn("dec_fused")(_lib.ptr(q), _lib.ptr(priv_start), _lib.ptr(priv_active), _lib.ptr(priv_table),
-                                    max_pages, _lib.ptr(priv_len), _lib.ptr(kcache), _lib.ptr(vcache), B, Hq, Hkv, D,
-                                    scale, so, sml, ssp, n_sh, _lib.ptr(forest.row_mask), _lib.ptr(out), s),
-                   "paged_decode(private + merge)")
-        return out
     _lib.check(_fn("dec")(_lib.ptr(q), _lib.ptr(priv_start), _lib.ptr(priv_active), _lib.ptr(priv_table), max_pages,
                           _lib.ptr(priv_len), _lib.ptr(kcache), _lib.ptr(vcache), _lib.ptr(part_o[nl]),
                           _lib.ptr(part_ml[nl]), B, Hq, Hkv, D, seq_splits, scale, s), "paged_decode(private)")

@@ -15,12 +15,10 @@ def _scratch(B, Hq, D, splits):
             [torch.empty((B, Hq, splits, 2), **f32) for _ in range(4)])
 
 
-@pytest.mark.parametrize("seq_splits", [1, 2])
 @pytest.mark.parametrize("Hq,Hkv", [(32, 8), (16, 8), (8, 8)])
-def test_three_level_forest_matches_dense_attention(Hq, Hkv, seq_splits):
+def test_three_level_forest_matches_dense_attention(Hq, Hkv):
     """Headers shared by several prompts, prompts shared by their rollouts, private tails; one sequence without a
-    header, one prompt node whose slots are not consecutive, and a header with more sequences than one tile holds.
-    ``seq_splits`` 1: the per-sequence pass joins the levels itself; 2: partials + the separate merge kernel."""
+    header, one prompt node whose slots are not consecutive, and a header with more sequences than one tile holds."""
     from arctic_platform_b200.ops import _lib
     from arctic_platform_b200.ops import forest_attention as fa
     D, splits = 128, 4
@@ -76,8 +74,7 @@ def test_three_level_forest_matches_dense_attention(Hq, Hkv, seq_splits):
     for buf in po + pml:
         buf.fill_(float("nan"))                                            # stale partials must never be merged
     out = fa.forest_decode_attention(q, kc, vc, forest, torch.arange(B, **i32), torch.ones(B, **i32),
-                                     torch.from_numpy(priv).cuda(), torch.from_numpy(plen).cuda(), po, pml, splits,
-                                     seq_splits)
+                                     torch.from_numpy(priv).cuda(), torch.from_numpy(plen).cuda(), po, pml, splits, 1)
     _lib.check_status("forest")
     ref = fa.forest_decode_reference(q, kc, vc, ctx)
     assert torch.isfinite(out.float()).all()
