@@ -108,58 +108,39 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   pdl_launch_dependents();
 
   if (warp == 0) {
-    if (n_blocks > 0) {
-      // The whole warp runs the producer loop: lane 0 waits and issues the copies, all lanes together hold the page
-      // numbers of the next 32 pages (one coalesced read per four KV blocks, the following group already in flight)
-      // -- a look-up per page by the issuing thread was a dependent global load in front of every tile and set the
-      // pace of the whole kernel.
-      auto load_pages = [&](int chunk) -> int {
-        const int pi = min(b0 * 8 + chunk * 32 + lane, last_page);   // past the end: the node's last page (masked)
-        return p.pages[static_cast<long long>(g) * p.max_pages + pi];
-      };
-      int cur = load_pages(0), nxt = load_pages(1), cur_chunk = 0;
+    if (lane == 0 && n_blocks > 0) {
       bool ok = true;
       const int early = min(2, 2 * n_blocks);       // the first K and V tiles; q must not queue behind a full ring
       for (int n = 0; n < 2 * n_blocks && ok; ++n) {
         if (n == early) {
           pdl_wait();
-          if (lane == 0) {
-            mbar_expect_tx(q_full, kDpTile);
-            for (int c = 0; c < 2; ++c) tma_load_4d(smem_q + c * 16384, &tma_q, q_full, c * 64, 0, kvh, qs);
-          }
-        }
-        const int slot = n % kDpSlots;
-        const uint32_t phase = (n / kDpSlots) & 1;
-        const int j = n >> 1;                       // block of this tile, relative to b0
-        if ((j >> 2) != cur_chunk) {
-          cur = nxt;
-          cur_chunk = j >> 2;
-          nxt = load_pages(cur_chunk + 1);
-        }
-        int fine = 1;
-        if (lane == 0 && n >= early && !mbar_wait(&kv_empty[slot], phase ^ 1, p.status, kTimeoutEmpty)) fine = 0;
-        ok = __shfl_sync(0xffffffffu, fine, 0) != 0;
-        if (!ok) break;
-        uint8_t* dst = smem_kv + slot * kDpTile;
-        if (lane == 0) mbar_expect_tx(&kv_full[slot], kDpTile);
-        const CUtensorMap* map = (n & 1) ? &tma_v : &tma_k;
-#pragma unroll
-        for (int pg = 0; pg < 8; ++pg) {
-          const int page = __shfl_sync(0xffffffffu, cur, (j & 3) * 8 + pg);
-          if (lane == 0) {
-            const int row = (page * p.Hkv + kvh) * 16;
-            for (int c = 0; c < 2; ++c) tma_load_2d(dst + c * 16384 + pg * 2048, map, &kv_full[slot], c * 64, row);
-          }
-        }
-      }
-      if (ok && 2 * n_blocks <= early) {   // every tile fitted into the first ring-full: q is still to come
-        pdl_wait();
-        if (lane == 0) {
           mbar_expect_tx(q_full, kDpTile);
           for (int c = 0; c < 2; ++c) tma_load_4d(smem_q + c * 16384, &tma_q, q_full, c * 64, 0, kvh, qs);
         }
+        const int slot = n % kDpSlots;
+        const uint32_t phase = (n / kDpSlots) & 1;
+        if (n >= early && !mbar_wait(&kv_empty[slot], phase ^ 1, p.status, kTimeoutEmpty)) {
+          ok = false;
+          break;
+        }
+        const int b = b0 + (n >> 1);
+        uint8_t* dst = smem_kv + slot * kDpTile;
+        mbar_expect_tx(&kv_full[slot], kDpTile);
+        const CUtensorMap* map = (n & 1) ? &tma_v : &tma_k;
+        for (int pg = 0; pg < 8; ++pg) {
+          // pages past the end of the node are replaced by its last page: finite data, masked by `limit`
+          const int pi = min(b * 8 + pg, last_page);
+          const int page = p.pages[static_cast<long long>(g) * p.max_pages + pi];
+          const int row = (page * p.Hkv + kvh) * 16;
+          for (int c = 0; c < 2; ++c) tma_load_2d(dst + c * 16384 + pg * 2048, map, &kv_full[slot], c * 64, row);
+        }
       }
-      if (!ok && lane == 0) {
+      if (2 * n_blocks <= early) {         // every tile fitted into the first ring-full: q is still to come
+        pdl_wait();
+        mbar_expect_tx(q_full, kDpTile);
+        for (int c = 0; c < 2; ++c) tma_load_4d(smem_q + c * 16384, &tma_q, q_full, c * 64, 0, kvh, qs);
+      }
+      if (!ok) {
         const uint64_t t0 = global_timer_ns();
         while (global_timer_ns() - t0 < 100000ull) {
         }
