@@ -108,7 +108,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 // dx = rstd * (g - xhat * mean(g * xhat)) [+ dres], g = dy * w ; dw += sum_t dy * xhat
 // NV = 8-element vectors per thread (registers scale with it, so narrow rows keep more CTAs per SM).
 template <int NV>
-__global__ void __launch_bounds__(kNormThreads, NV <= 2 ? 3 : 1)
+__global__ void __launch_bounds__(kNormThreads, NV <= 1 ? 3 : (NV <= 2 ? 2 : 1))
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
@@ -134,8 +134,10 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
     const size_t base = static_cast<size_t>(row) * H;
     const float rstd = rstd_in[row];
-    float g[kNormMaxVec][8], xh[kNormMaxVec][8];
+    float g[kNormMaxVec][8], xh[kNormMaxVec][8], rr[kNormMaxVec][8];
     float dot = 0.f;
+    // all three inputs of the row are requested before the block-wide reduction: the upstream residual gradient
+    // used to be loaded after it, a second full memory latency per row
 #pragma unroll
     for (int i = 0; i < kNormMaxVec; ++i) {
       const int v = threadIdx.x + i * kNormThreads;
@@ -143,6 +145,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         float d[8];
         load8(dy + base + v * 8, d);
         load8(x + base + v * 8, xh[i]);
+        if (dres) load8(dres + base + v * 8, rr[i]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] *= rstd;
@@ -159,13 +162,7 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
       if (v < nvec) {
         float o[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * dot);
-        if (dres) {
-          float r[8];
-          load8(dres + base + v * 8, r);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += r[j];
-        }
+        for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * dot) + (dres ? rr[i][j] : 0.f);
         store8(dx + base + v * 8, o);
       }
     }
@@ -279,8 +276,13 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_qkv,
 
 // Backward of the above: dq/dk (post-rotary grads) -> d(raw q/k) written into
 // dqkv rows (same layout as qkv), dwq/dwk accumulated in fp32.
+// D / 16 lanes share one (token, head) item, so a warp works on 32 / (D / 16) items at a time with 16-byte loads
+// (8 elements of each half of the head per lane): four times the bytes in flight per warp of a one-item-per-warp
+// walk, whose 4-byte loads and position -> cos/sin load chain left the kernel at an eighth of the memory bandwidth.
+// Weight gradients are summed over the lane groups, then over the CTA in shared memory, before one atomic per
+// element and CTA.
 template <int D>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_qkv,
                        const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
                        const float* __restrict__ cos_t, const float* __restrict__ sin_t,
@@ -288,95 +290,122 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld_qkv,
                        const __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dqkv, long long ld_dqkv,
                        float* __restrict__ dwq, float* __restrict__ dwk, int T, int Hq, int Hkv, int rot,
                        float eps) {
-  constexpr int E2 = D / 64;  // elements per lane in each half of the head
+  constexpr int LPI = D / 16;       // lanes per item
+  constexpr int IPW = 32 / LPI;     // items per warp and pass
+  __shared__ float dw_s[2][D];
   const int lane = threadIdx.x & 31;
+  const int sub = lane % LPI, grp = lane / LPI;
   const int heads = Hq + Hkv;
   const long long nwarps_total = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  // Every warp walks (token, head) pairs of BOTH classes (q heads and k heads) so the work is balanced whatever
-  // the GQA ratio; the two weight-gradient accumulators live in registers side by side.
-  float dwa[2][E2], dwb[2][E2];
-  float wa[2][E2], wb[2][E2];
-#pragma unroll
-  for (int c = 0; c < 2; ++c) {
-    const __nv_bfloat16* w = c == 0 ? wq : wk;
-#pragma unroll
-    for (int j = 0; j < E2; ++j) {
-      dwa[c][j] = dwb[c][j] = 0.f;
-      wa[c][j] = w ? __bfloat162float(w[lane * E2 + j]) : 1.f;
-      wb[c][j] = w ? __bfloat162float(w[D / 2 + lane * E2 + j]) : 1.f;
-    }
-  }
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) (&dw_s[0][0])[i] = 0.f;
+  __syncthreads();
   const bool has_w = wq != nullptr;
   const long long gw = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
-  const long long items = static_cast<long long>(T) * heads;
   const int half = rot / 2;
-  for (long long it = gw; it < items; it += nwarps_total) {
-    const int t = static_cast<int>(it / heads);
-    const int h = static_cast<int>(it % heads);
-    const bool is_q = h < Hq;
-    const __nv_bfloat16* src = qkv + t * ld_qkv + static_cast<long long>(h) * D;
-    const __nv_bfloat16* g = is_q ? dq + (static_cast<long long>(t) * Hq + h) * D
-                                  : dk + (static_cast<long long>(t) * Hkv + (h - Hq)) * D;
-    __nv_bfloat16* dst = dqkv + t * ld_dqkv + static_cast<long long>(h) * D;
-    const int p = pos[t];
-    float ga[E2], gb[E2], xa[E2], xb[E2];
-    load_vec<E2>(g + lane * E2, ga);
-    load_vec<E2>(g + D / 2 + lane * E2, gb);
-    load_vec<E2>(src + lane * E2, xa);
-    load_vec<E2>(src + D / 2 + lane * E2, xb);
-    if (rot == D) {
+  auto group_sum = [&](float v) {
 #pragma unroll
-      for (int j = 0; j < E2; ++j) {
-        const int i = lane * E2 + j;
-        const float c = cos_t[static_cast<long long>(p) * half + i], sn = sin_t[static_cast<long long>(p) * half + i];
-        const float da = ga[j], db = gb[j];
-        ga[j] = da * c + db * sn;  // transpose of the rotation
-        gb[j] = db * c - da * sn;
+    for (int o = LPI / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+  };
+  // The q heads first, then the k heads: each pass spreads its own items evenly over all warps (balanced whatever
+  // the GQA ratio) and needs only its own weight and weight-gradient registers.
+#pragma unroll 1
+  for (int c = 0; c < 2; ++c) {
+    const int nh = c == 0 ? Hq : Hkv;
+    const int h0 = c == 0 ? 0 : Hq;
+    const __nv_bfloat16* w = c == 0 ? wq : wk;
+    const __nv_bfloat16* gsrc = c == 0 ? dq : dk;
+    float dwa[8], dwb[8], wa[8], wb[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      dwa[j] = dwb[j] = 0.f;
+      wa[j] = wb[j] = 1.f;
+    }
+    if (w) {
+      load8(w + sub * 8, wa);
+      load8(w + D / 2 + sub * 8, wb);
+    }
+    const long long items = static_cast<long long>(T) * nh;
+    for (long long base = gw * IPW; base < items; base += nwarps_total * IPW) {
+      const long long it = base + grp;
+      const bool valid = it < items;                     // the shuffles below need every lane of the warp
+      const long long itc = valid ? it : items - 1;
+      const int t = static_cast<int>(itc / nh);
+      const int h = static_cast<int>(itc % nh);
+      const __nv_bfloat16* src = qkv + t * ld_qkv + static_cast<long long>(h0 + h) * D;
+      const __nv_bfloat16* g = gsrc + (static_cast<long long>(t) * nh + h) * D;
+      __nv_bfloat16* dst = dqkv + t * ld_dqkv + static_cast<long long>(h0 + h) * D;
+      const int p = pos[t];
+      float ga[8], gb[8], xa[8], xb[8];
+      load8(g + sub * 8, ga);
+      load8(g + D / 2 + sub * 8, gb);
+      load8(src + sub * 8, xa);
+      load8(src + D / 2 + sub * 8, xb);
+      if (rot == D) {
+        const float4* cp = reinterpret_cast<const float4*>(cos_t + static_cast<long long>(p) * half + sub * 8);
+        const float4* sp = reinterpret_cast<const float4*>(sin_t + static_cast<long long>(p) * half + sub * 8);
+        const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+        const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float da = ga[j], db = gb[j];
+          ga[j] = da * cs[j] + db * sn[j];  // transpose of the rotation
+          gb[j] = db * cs[j] - da * sn[j];
+        }
+      }
+      if (has_w) {
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += xa[j] * xa[j] + xb[j] * xb[j];
+        ss = group_sum(ss);
+        const float rstd = rsqrtf(ss / D + eps);
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xa[j] *= rstd;
+          xb[j] *= rstd;
+          if (valid) {
+            dwa[j] += ga[j] * xa[j];
+            dwb[j] += gb[j] * xb[j];
+          }
+          ga[j] *= wa[j];
+          gb[j] *= wb[j];
+          dot += ga[j] * xa[j] + gb[j] * xb[j];
+        }
+        dot = group_sum(dot) / D;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          ga[j] = rstd * (ga[j] - xa[j] * dot);
+          gb[j] = rstd * (gb[j] - xb[j] * dot);
+        }
+      }
+      if (valid) {
+        store8(dst + sub * 8, ga);
+        store8(dst + D / 2 + sub * 8, gb);
       }
     }
     if (has_w) {
-      float ss = 0.f;
 #pragma unroll
-      for (int j = 0; j < E2; ++j) ss += xa[j] * xa[j] + xb[j] * xb[j];
-      ss = warp_sum(ss);
-      const float rstd = rsqrtf(ss / D + eps);
-      float dot = 0.f;
+      for (int j = 0; j < 8; ++j) {
+        float a = dwa[j], b2 = dwb[j];
 #pragma unroll
-      for (int j = 0; j < E2; ++j) {
-        xa[j] *= rstd;
-        xb[j] *= rstd;
-        const float pa = ga[j] * xa[j], pb = gb[j] * xb[j];
-        if (is_q) {
-          dwa[0][j] += pa;
-          dwb[0][j] += pb;
-        } else {
-          dwa[1][j] += pa;
-          dwb[1][j] += pb;
+        for (int o = LPI; o < 32; o <<= 1) {             // over the lane groups of the warp
+          a += __shfl_xor_sync(0xffffffffu, a, o);
+          b2 += __shfl_xor_sync(0xffffffffu, b2, o);
         }
-        ga[j] *= is_q ? wa[0][j] : wa[1][j];
-        gb[j] *= is_q ? wb[0][j] : wb[1][j];
-        dot += ga[j] * xa[j] + gb[j] * xb[j];
-      }
-      dot = warp_sum(dot) / D;
-#pragma unroll
-      for (int j = 0; j < E2; ++j) {
-        ga[j] = rstd * (ga[j] - xa[j] * dot);
-        gb[j] = rstd * (gb[j] - xb[j] * dot);
+        if (grp == 0) {
+          atomicAdd(&dw_s[c][sub * 8 + j], a);
+          atomicAdd(&dw_s[c][D / 2 + sub * 8 + j], b2);
+        }
       }
     }
-    store_vec<E2>(dst + lane * E2, ga);
-    store_vec<E2>(dst + D / 2 + lane * E2, gb);
   }
   if (has_w) {
-#pragma unroll
-    for (int c = 0; c < 2; ++c) {
-      float* dwp = c == 0 ? dwq : dwk;
-      if (!dwp) continue;
-#pragma unroll
-      for (int j = 0; j < E2; ++j) {
-        atomicAdd(dwp + lane * E2 + j, dwa[c][j]);
-        atomicAdd(dwp + D / 2 + lane * E2 + j, dwb[c][j]);
-      }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
+      float* dwp = i < D ? dwq : dwk;
+      if (dwp) atomicAdd(dwp + (i % D), (&dw_s[0][0])[i]);
     }
   }
 }
@@ -483,7 +512,7 @@ int apb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
   if (T <= 0) return 0;
   if (H % 8 || H > kNormThreads * 8 * kNormMaxVec) return kBadArgument;
   const int nv = (H / 8 + kNormThreads - 1) / kNormThreads;
-  const int per_sm = nv <= 2 ? 3 : 1;
+  const int per_sm = nv <= 1 ? 3 : (nv <= 2 ? 2 : 1);
   const int grid = T < 148 * per_sm ? T : 148 * per_sm;
 #define APB_NORM_BWD(NV)                                                                                     \
   rmsnorm_bwd_kernel<NV><<<grid, kNormThreads, 0, s>>>(                                                       \
@@ -525,7 +554,7 @@ int apb_qknorm_rope_bwd(const void* qkv, long long ld_qkv, const void* wq, const
                         float eps, cudaStream_t s) {
   if (T <= 0) return 0;
   if (rot != 0 && rot != D) return kBadArgument;
-  const int grid = 148 * 8;
+  const int grid = 148 * 2;       // two resident CTAs per SM, each walks its share of the items
 #define APB_LAUNCH_QKB(DD)                                                                                  \
   qknorm_rope_bwd_kernel<DD><<<grid, 256, 0, s>>>(                                                          \
       static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<const __nv_bfloat16*>(wq),               \
