@@ -111,6 +111,10 @@ class DeviceRouting:
     plan: object               # models.moe.MoEPlan of this rank's experts
     recv_rows: int             # = capacity (host)
     num_pairs: int
+    # training pass: received rows are copied out of the symmetric buffer with the padding rows zeroed (they are
+    # saved for backward and read by the weight-gradient GEMMs); inference reads the buffer in place.  Decided by
+    # the layer, not from the autograd mode inside the exchange (a Function's forward always runs without it).
+    materialize: bool = True
 
 
 def plan_routing_device(idx: torch.Tensor, num_experts: int, world: int, rank: int, group, cap: int, hidden: int,
@@ -197,7 +201,7 @@ class ExpertParallel:
                    "apb_ep_scatter_rows")
         self._barrier()
         got = self.recv.tensor[: r.recv_rows * H].view(r.recv_rows, H)
-        if not torch.is_grad_enabled():
+        if not getattr(r, "materialize", True):
             return got          # read in place: the layer's closing barrier comes before the next dispatch lands here
         # padding rows of the layout still hold rows of an earlier call: they must read as zeros (the weight-gradient
         # GEMMs walk whole 64-row blocks)
@@ -234,6 +238,7 @@ class ExpertParallel:
             r = plan_routing_device(idx, self.num_experts, self.world, self.rank, self.group, self.max_recv_rows, H,
                                     moe.wgu.shape[1] // 2, self.overflow)
             moe.last_tokens_per_expert = r.recv_counts
+            r.materialize = torch.is_grad_enabled()
             x_recv = _DispatchFn.apply(x, self, r)
             if not torch.is_grad_enabled():
                 y_pairs = self._ffn_with_fused_combine(moe, x_recv, r)

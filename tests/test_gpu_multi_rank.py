@@ -136,6 +136,12 @@ def _tp_ep_main(rank, world, port, out_dir):
         dist.all_reduce(gfull)
         res["ep_dw"] = float((ep_moe.wdown.grad.float() - gfull[rank * El:(rank + 1) * El]).abs().max())
         res["ep_dw_scale"] = float(gfull.abs().max())
+        # the gate/up gradient reads the rows RECEIVED in the forward (saved for backward): they must not alias the
+        # receive buffer, which the backward's own exchange overwrites
+        gfull_gu = full.wgu.grad.float().clone()
+        dist.all_reduce(gfull_gu)
+        res["ep_dwgu"] = float((ep_moe.wgu.grad.float() - gfull_gu[rank * El:(rank + 1) * El]).abs().max())
+        res["ep_dwgu_scale"] = float(gfull_gu.abs().max())
         _lib.check_status("tp/ep")
         torch.save(res, os.path.join(out_dir, f"t{rank}.pt"))
     finally:
@@ -158,6 +164,7 @@ def test_tensor_parallel_and_expert_parallel_fused_kernels():
         assert r["ep_inf"] < 0.03 * r["ep_scale"] + 0.02, r
         assert r["ep_dx"] < 0.05, r
         assert r["ep_dw"] < 0.03 * r["ep_dw_scale"] + 0.02, r
+        assert r["ep_dwgu"] < 0.03 * r["ep_dwgu_scale"] + 0.02, r
 
 
 def _zero3_main(rank, world, port, out_dir):
