@@ -43,7 +43,12 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="qwen3-4b")
     ap.add_argument("--layers", type=int, default=8, help="decoder blocks of the model used for the engine cases")
+    ap.add_argument("--cases", default="step,tp,ep", help="comma list of case groups: step (trainer step, ZeRO-3 gather, "
+                    "weight sync), tp (tensor-parallel GEMMs), ep (expert-parallel MoE layer)")
+    ap.add_argument("--peak-tflops", type=float, default=1635.6,
+                    help="bf16 GEMM peak of the machine (denominator of the compute side of the roofline)")
     args = ap.parse_args()
+    cases = set(args.cases.split(","))
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -54,8 +59,7 @@ def main():
     from arctic_platform_b200.ops import _lib
     from arctic_platform_b200.parallel import tensor_parallel as tp
     from arctic_platform_b200.parallel.weight_sync import flatten_like, sync_flat
-    peaks_file = Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
-    peak_tflops = json.loads(peaks_file.read_text())["bf16_tflops"] if peaks_file.exists() else 1590.0
+    peak_tflops = args.peak_tflops
     cfg = dataclasses.replace(PRESETS[args.model], num_layers=args.layers)
     out = []
 
@@ -69,7 +73,8 @@ def main():
         out.append(rec)
 
     # ---- trainer step: fused vs collectives (stage 1: RS + AdamW + AG), and stage 3 (RS + local AdamW)
-    for name, stage, impl in (("step_fused_zero1", 1, "fused"), ("step_nccl_zero1", 1, "collective"), ("step_fused_zero3", 3, "fused")):
+    step_cases = (("step_fused_zero1", 1, "fused"), ("step_nccl_zero1", 1, "collective"), ("step_fused_zero3", 3, "fused"))
+    for name, stage, impl in (step_cases if "step" in cases else ()):
         model = DecoderLM(cfg, dev, torch.bfloat16).init_weights(seed=1)
         eng = TrainEngine(model, EngineConfig(lr=1e-6, max_grad_norm=1.0, impl=impl, zero_stage=stage))
         eng.grad_buf.tensor.normal_(0, 1e-3)
@@ -102,7 +107,7 @@ def main():
         torch.cuda.empty_cache()
 
     # ---- sampler tensor parallelism at decode shapes (128 sequences)
-    if world > 1:
+    if world > 1 and "tp" in cases:
         H, Q, I = PRESETS[args.model].hidden_size, PRESETS[args.model].q_size, PRESETS[args.model].intermediate_size
         ctx = tp.TPContext(dev, None, max_rows=128, max_cols=max(2 * I, Q))
         rows = 128 // world
@@ -141,6 +146,7 @@ def main():
             emit(f"tp_gemm_rs_{label}_nccl", timed(base, iters=20), nvlink_bytes=nv, flops=flops)
         _lib.check_status("tp")
 
+    if world > 1 and "ep" in cases:
         # ---- expert-parallel MoE layer (Qwen3-30B-A3B layer shape), 4096 tokens per rank
         from arctic_platform_b200.models.moe import MoEFeedForward
         from arctic_platform_b200.parallel.expert_parallel import ExpertParallel
@@ -163,6 +169,17 @@ def main():
                 nv = 2 * pairs * mcfg.hidden_size * 2 * (world - 1) / world          # dispatch + combine
                 flops = 2.0 * pairs * 3 * mcfg.hidden_size * mcfg.moe_intermediate_size
                 emit(f"ep_moe_layer_infer_{impl}", ms, nvlink_bytes=nv, flops=flops, tokens=T)
+                # training: forward + backward (data and weight gradients), dispatch and combine in both directions
+                xg = x.clone().requires_grad_(True)
+                gy = torch.randn_like(x)
+
+                def train_pass():
+                    moe.wgu.grad = moe.wdown.grad = moe.router.grad = None
+                    moe(xg).backward(gy)
+                ms = timed(train_pass, iters=5)
+                emit(f"ep_moe_layer_train_{impl}", ms, nvlink_bytes=2 * nv, flops=3 * flops, tokens=T)
+                del moe
+                torch.cuda.empty_cache()
             _lib.check_status("ep")
     dist.barrier()
     dist.destroy_process_group()
