@@ -259,6 +259,8 @@ class SamplerEngine:
         self.max_seq_len = max_seq_len
         self._sm_count = (torch.cuda.get_device_properties(self.device).multi_processor_count
                           if self.device.type == "cuda" else 1)
+        from ..utils import memory_budget
+        memory_budget.register("sampler", self.device)
         self.cascade = cascade
         self.sync_interval = sync_interval
         self.use_cuda_graph = use_cuda_graph
@@ -400,6 +402,7 @@ class SamplerEngine:
         from ..parallel.weight_sync import quantize_fp8_block128
         self._fp8_w = []
         self._graphs.clear()             # captured graphs hold pointers to the previous copies
+        self._parked_graphs = None
         for blk in self.model.blocks:
             self._fp8_w.append({n: quantize_fp8_block128(getattr(blk, n).data) for n in ("wqkv", "wo", "wgu", "wdown")})
         self._fp8_stale = False
@@ -717,6 +720,7 @@ class SamplerEngine:
             self.d_out_tokens = torch.zeros((self.max_batch, self.out_cap), device=self.device, dtype=torch.int32)
             self.d_out_lps = torch.zeros((self.max_batch, self.out_cap), device=self.device, dtype=torch.float32)
             self._graphs.clear()
+            self._parked_graphs = None
         if sp.seed is not None:
             self.seed = int(sp.seed)
             self.d_step.zero_()            # a seeded call restarts the random stream
@@ -1086,7 +1090,13 @@ class SamplerEngine:
         if keep:
             self._asleep = True
             return
-        self._graphs.clear()
+        # the captured decode graphs hold the cache's addresses: they are parked, and come back if the next cache
+        # lands on the same addresses (the usual case when the blocks only went back to the shared allocator)
+        if level < 2 and self.kcache is not None and self._graphs:
+            self._parked_graphs = (self.kcache.data_ptr(), self.vcache.data_ptr(), self._graphs)
+        else:
+            self._parked_graphs = None
+        self._graphs = {}
         self.kcache = self.vcache = None
         if self.device.type == "cuda":
             from ..utils import memory_budget
@@ -1096,11 +1106,17 @@ class SamplerEngine:
                 p.data = torch.empty(0, device=self.device, dtype=p.dtype)
             self._sync_plan = None            # its destination buffer went with the weights
         self._asleep = True
-        torch.cuda.empty_cache()
+        from ..utils import memory_budget
+        if level >= 2 or not memory_budget.shares_allocator(self.device):
+            torch.cuda.empty_cache()      # engines in other processes can only get the memory through the driver
 
     def wake(self, tags: Optional[Sequence[str]] = None) -> None:
         tags = set(tags or ("weights", "kv_cache"))
         if "kv_cache" in tags:
             if self.kcache is None:
                 self._alloc_cache()
+                parked = getattr(self, "_parked_graphs", None)
+                if parked is not None and parked[0] == self.kcache.data_ptr() and parked[1] == self.vcache.data_ptr():
+                    self._graphs = parked[2]
+                self._parked_graphs = None
             self._asleep = False

@@ -193,6 +193,9 @@ class TrainEngine:
         self.device = p0.device
         self.param_dtype = p0.dtype
         self.on_cuda = self.device.type == "cuda"
+        if self.on_cuda and not forward_only:
+            from ..utils import memory_budget
+            memory_budget.register("trainer", self.device)
         self.impl = cfg.impl if self.on_cuda else "collective"
         self.global_steps = 0
         self.micro_steps = 0

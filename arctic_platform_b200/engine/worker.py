@@ -800,11 +800,16 @@ class EngineWorker:
         if self.engine is not None:
             self.engine.reload_states()
 
-    def empty_cache(self) -> None:
+    def empty_cache(self, force: bool = False) -> None:
+        """Returns the allocator's cached blocks to the driver -- what a sampler in ANOTHER process needs before it
+        wakes.  A sampler in this process takes the freed blocks from the shared allocator directly, so the call is
+        skipped then (``force`` overrides)."""
         if self.device.type == "cuda":
             import gc
+            from ..utils import memory_budget
             gc.collect()
-            torch.cuda.empty_cache()
+            if force or not memory_budget.shares_allocator(self.device):
+                torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoint(self, path: str, tag: Optional[str] = None, export_hf: bool = False) -> Dict[str, Any]:

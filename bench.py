@@ -322,6 +322,7 @@ def main():
             "phases_ms": {n: round(v, 1) for n, v in zip(PHASES, per_phase)},
             "gpu_launches": launches,
             "peak_device_memory_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1),
+            "reserved_device_memory_gb": round(torch.cuda.memory_reserved(dev) / 2 ** 30, 1),
             "rollout_tokens_per_step": B * R * world,
         }
         print(json.dumps(line), flush=True)
