@@ -224,28 +224,77 @@ class ArcticRLClientWrapper:
 
     def update_actor(self, data: Dict[str, Any]) -> Dict[str, float]:
         """``ppo_epochs`` passes over the batch, each cut into mini-batches of ``ppo_mini_batch_size * rollout_n``
-        samples (whole prompt groups stay together); one ``fwd_bwd`` + ``step`` per mini-batch."""
+        samples (whole prompt groups stay together); one ``fwd_bwd`` + ``step`` per mini-batch.  Returns the reduced
+        metrics (see ``update_actor_detailed`` for the loss and the token counts as well)."""
+        return self.update_actor_detailed(data)["metrics"]
+
+    # how a metric is folded over the mini-batches of one update; everything else is averaged
+    METRIC_REDUCTION = {"actor/pg_clipfrac_lower": "mean", "actor/pg_clipfrac": "mean", "actor/pg_loss": "mean",
+                        "actor/ppo_kl": "mean", "grad_norm": "mean", "kl_coef": "mean", "kl_loss": "mean",
+                        "perf/max_memory_allocated_gb": "max", "global_tokens": "sum"}
+
+    @staticmethod
+    def _plain(obj: Any) -> Dict[str, Any]:
+        """A config object as JSON-safe dict (values that do not serialise become None)."""
+        import json
+        if obj is None:
+            return {}
+        src = _to_plain(obj) if not hasattr(obj, "__dict__") or isinstance(obj, dict) else vars(obj)
+        return json.loads(json.dumps(src, default=lambda o: None))
+
+    def update_actor_detailed(self, data: Dict[str, Any]) -> Dict[str, Any]:
+        """The update with everything verl's trainer reads back: ``{"loss", "metrics", "global_token_num"}``
+        (arctic_platform/integrations/verl/adapter.py:268-397).  Per mini-batch the meta carries the global batch
+        size of one optimizer step, the number of loss tokens in the chunk, the chunk's slice of the rollout
+        importance weights, and the actor / policy-loss sections of the config."""
         batch, P, R = prepare_padded_batch(data, self.pad_token_id)
         for k in ("advantages", "old_log_probs", "ref_log_prob", "response_mask", "rollout_log_probs"):
             if k in data:
                 batch[k] = data[k]
         batch.setdefault("response_mask", batch["attention_mask"][:, -R:])
         B = batch["input_ids"].shape[0]
-        mini = int(cfg_get(self.config, "actor_rollout_ref.actor.ppo_mini_batch_size", max(1, B // self.rollout_n))) * self.rollout_n
-        mini = max(1, min(mini, B))
+        per_step = int(cfg_get(self.config, "actor_rollout_ref.actor.ppo_mini_batch_size",
+                               max(1, B // self.rollout_n))) * self.rollout_n
+        mini = max(1, min(per_step, B))
         n_mini = math.ceil(B / mini)
-        metrics: Dict[str, List[float]] = {}
+        actor_cfg = cfg_get(self.config, "actor_rollout_ref.actor", None)
+        shared_meta = {"response_length": R, "max_prompt_len": P, "max_response_len": R, "rollout_n": self.rollout_n,
+                       "pad_token_id": self.pad_token_id,
+                       "calculate_entropy": bool(cfg_get(self.config, "actor_rollout_ref.actor.calculate_entropy", False)),
+                       "max_token_len_per_gpu": cfg_get(self.config, "actor_rollout_ref.actor.ppo_max_token_len_per_gpu", None),
+                       "actor_config": self._plain(actor_cfg),
+                       "policy_loss_config": self._plain(cfg_get(self.config, "actor_rollout_ref.actor.policy_loss", None))}
+        is_w = data.get("rollout_is_weights")
+        token_counts = batch["attention_mask"].sum(-1).tolist()
+        series: Dict[str, List[float]] = {}
+        losses: List[float] = []
+        last_lr = None
         for _epoch in range(self.ppo_epochs):
             for i in range(n_mini):
                 sl = slice(i * mini, min(B, (i + 1) * mini))
                 mb = {k: v[sl] for k, v in batch.items()}
-                out = self._call("fwd_bwd", {"batch": mb, "meta": self._meta({"response_length": R})})
+                meta = self._meta({**shared_meta, "global_batch_size": per_step,
+                                   "batch_num_tokens": int(mb["response_mask"].sum()),
+                                   "rollout_is_weights": is_w[sl] if isinstance(is_w, torch.Tensor) else is_w})
+                out = self._call("fwd_bwd", {"batch": mb, "meta": meta})
                 st = self._call("step")
-                for k, v in {**out.get("metrics", {}), **st.get("metrics", {})}.items():
-                    if isinstance(v, (int, float)):
-                        metrics.setdefault(k, []).append(float(v))
+                merged = {**out.get("metrics", {}), **st.get("metrics", {})}
+                if isinstance(out.get("avg_loss"), (int, float)):
+                    losses.append(float(out["avg_loss"]))
+                elif isinstance(merged.get("loss"), (int, float)):
+                    losses.append(float(merged["loss"]))
+                if isinstance(merged.get("last_lr"), (int, float)):
+                    last_lr = float(merged["last_lr"])
+                for k, v in merged.items():
+                    if k not in ("loss",) and isinstance(v, (int, float)):
+                        series.setdefault(k, []).append(float(v))
         self.global_steps += 1
-        return {k: sum(v) / len(v) for k, v in metrics.items()}
+        fold = {"mean": lambda v: sum(v) / len(v), "max": max, "min": min, "sum": sum}
+        metrics = {k: fold[self.METRIC_REDUCTION.get(k, "mean")](v) for k, v in series.items()}
+        if last_lr is not None:
+            metrics["lr"] = last_lr
+        loss = sum(losses) / len(losses) if losses else float("nan")
+        return {"loss": loss, "metrics": metrics, "global_token_num": token_counts}
 
     def generate(self, prompt_ids: Sequence[Sequence[int]], sampling_params: Optional[dict] = None, routing_key=None) -> List[dict]:
         sp = {"temperature": self.temperature, "n": 1,

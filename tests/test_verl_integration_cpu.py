@@ -152,3 +152,77 @@ def test_real_update_through_local_client(tmp_path):
     from arctic_platform_b200.models.config import PRESETS
     assert estimate_flops_per_token(PRESETS["qwen3-4b"], 4096) > 6 * 3.5e9
     worker.wrapper.destroy()
+
+
+def test_rollout_endpoint_protocol_details():
+    """Token budget resolution, log-prob flag, verl's stop vocabulary, per-mode sleep / wake and the hybrid weight
+    hand-over order."""
+    from arctic_platform_b200.integrations.verl.rollout import (RolloutServerConfig, resolve_max_tokens,
+                                                                verl_stop_reason)
+    cfg = RolloutServerConfig(max_model_len=16, prompt_length=8, response_length=6)
+    assert resolve_max_tokens({"max_tokens": 100}, 4, cfg) == 12          # clamped to the context space
+    assert resolve_max_tokens({"max_new_tokens": 3}, 4, cfg) == 3
+    assert resolve_max_tokens({}, 4, cfg) == 10                           # response + prompt budget - prompt
+    with pytest.raises(ValueError, match="exceeds the model's maximum context length"):
+        resolve_max_tokens({}, 17, cfg)
+    assert resolve_max_tokens({}, 4, RolloutServerConfig()) == -1         # nothing configured: engine default
+    assert [verl_stop_reason(r) for r in ("abort", "stop", "length", "other", None)] == \
+        ["aborted", "completed", "completed", "other", None]
+    assert RolloutServerConfig.from_verl({"response_length": 5, "free_cache_engine": False}).free_cache_engine is False
+
+    fake = _FakeClient()
+    w = ArcticRLClientWrapper(_config(), client=fake)
+    rep = asyncio.run(ArcticReplica(0, w, RolloutMode.COLOCATED, config=cfg, nnodes=2).init())
+    assert len(rep.servers) == 2 and not rep.rollout_worker_use_gpu()
+    srv = rep.server_handle.use_verl_stop_reasons()
+    out = asyncio.run(srv.generate([1, 2, 3], {"logprobs": True}, request_id="a"))
+    sent = fake.calls[-1][1][1]
+    assert sent["max_tokens"] == 11 and sent["logprobs"] == 0 and out.stop_reason == "completed"
+    assert out.finish_reason == "length" and out.extra["global_steps"] == 0
+    # colocated: sleep, then wake restores weights + cache and resets cached prefixes; node 1 never touches the engine
+    n0 = len(fake.calls)
+    asyncio.run(rep.servers[1].sleep())
+    asyncio.run(rep.servers[1].wake_up())
+    assert len(fake.calls) == n0
+    asyncio.run(srv.sleep())
+    asyncio.run(srv.wake_up())
+    assert [c[0] for c in fake.calls[n0:]] == ["sleep_inference", "wake_inference", "reset_prefix_cache"]
+    assert fake.calls[n0 + 1][1][0] == ["kv_cache", "weights"]
+    # hybrid hand-over: weights while asleep, then the cache, then the prefix reset
+    hyb = asyncio.run(ArcticReplica(1, w, RolloutMode.HYBRID).init()).server_handle
+    asyncio.run(hyb.sleep())
+    n1 = len(fake.calls)
+    asyncio.run(hyb.update_weights(global_steps=7))
+    assert [c[0] for c in fake.calls[n1:]] == ["sync_weights", "wake_inference", "reset_prefix_cache"]
+    assert fake.calls[n1 + 1][1][0] == ["kv_cache"] and hyb.global_steps == 7
+    # standalone and free_cache_engine=False: sleep / wake are no-ops
+    n2 = len(fake.calls)
+    alone = ArcticLLMServer(w, RolloutMode.STANDALONE)
+    keep = ArcticLLMServer(w, RolloutMode.HYBRID, config=RolloutServerConfig(free_cache_engine=False))
+    for s_ in (alone, keep):
+        asyncio.run(s_.sleep())
+        asyncio.run(s_.wake_up())
+    assert len(fake.calls) == n2
+    assert asyncio.run(rep.abort_request("a"))["aborted"] is False
+
+
+def test_update_actor_detailed_meta_and_reductions():
+    fake = _FakeClient()
+    w = ArcticRLClientWrapper(_config(), client=fake)
+    ids, mask, R = make_grpo_batch(n_prompts=4, n_samples=2)
+    data = {"input_ids": ids, "attention_mask": mask, "responses": ids[:, -R:], "advantages": torch.randn(8, R),
+            "old_log_probs": torch.zeros(8, R), "rollout_is_weights": torch.arange(8.0)[:, None].expand(8, R)}
+    out = w.update_actor_detailed(data)
+    assert set(out) == {"loss", "metrics", "global_token_num"} and len(out["global_token_num"]) == 8
+    assert out["global_token_num"] == mask.sum(-1).tolist()
+    first = fake.calls[0][1][0]["meta"]
+    assert first["global_batch_size"] == 4 and first["batch_num_tokens"] == int(first_mask_tokens(fake))
+    assert first["rollout_is_weights"].shape[0] == 4 and float(first["rollout_is_weights"][3, 0]) == 3.0
+    second = [c for c in fake.calls if c[0] == "fwd_bwd"][1][1][0]["meta"]
+    assert float(second["rollout_is_weights"][0, 0]) == 4.0          # the chunk's own slice
+    assert isinstance(first["actor_config"], dict) and first["actor_config"].get("ppo_epochs") == 2
+    assert out["metrics"]["actor/pg_loss"] == 0.5 and "lr" not in out["metrics"] or isinstance(out["metrics"]["lr"], float)
+
+
+def first_mask_tokens(fake):
+    return fake.calls[0][1][0]["batch"]["response_mask"].sum()
