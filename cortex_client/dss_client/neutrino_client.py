@@ -254,6 +254,113 @@ class NeutrinoClient:
                 raise NeutrinoError(f"request {request_id} failed: {ev.get('message')}")
         raise NeutrinoError(f"request {request_id} ended without a result")
 
+    # ------------------------------------------------------------------ requests: status, polling, cancelling
+    @staticmethod
+    def _normalize_request_status(status) -> str:
+        """The service reports request states in several spellings; callers see one upper-case word."""
+        word = str(status or "").strip().upper().replace("-", "_")
+        return {"DONE": "COMPLETED", "SUCCESS": "COMPLETED", "SUCCEEDED": "COMPLETED", "FINISHED": "COMPLETED",
+                "ERROR": "FAILED", "CANCELED": "CANCELLED", "IN_PROGRESS": "RUNNING", "QUEUED": "PENDING"}.get(word, word)
+
+    def get_request_status(self, job_id: str, request_id: str, max_events: Optional[int] = None,
+                           cursor: Optional[str] = None) -> dict:
+        """One look at an asynchronous request: ``{"status", "events", "next_cursor", ...}``."""
+        params = {}
+        if max_events is not None:
+            params["max_events"] = max_events
+        if cursor:
+            params["cursor"] = cursor
+        return self._send("GET", f"/jobs/{job_id}/requests/{request_id}", params=params or None).json()
+
+    def poll_request(self, job_id: str, request_id: str, timeout: Optional[float] = None) -> dict:
+        """Polls the request's status page until it completes and returns its result (chunked results are put back
+        together); raises on FAILED / CANCELLED or when ``timeout`` (default: the client's request timeout) passes.
+        The interval grows by half per empty poll up to ten times the base interval."""
+        deadline = time.time() + (self.request_timeout if timeout is None else timeout)
+        delay, cursor, chunks = self.poll_interval, None, []
+        while time.time() < deadline:
+            page = self.get_request_status(job_id, request_id, cursor=cursor)
+            cursor = page.get("next_cursor", cursor)
+            progressed = False
+            for ev in page.get("events") or []:
+                progressed = True
+                if ev.get("type") == "result_chunk":
+                    chunks.append(base64.b64decode(ev["data"]))
+            state = self._normalize_request_status(page.get("status"))
+            if state == "COMPLETED":
+                if chunks:
+                    return wire.decode_result_chunks(chunks)
+                data = page.get("result")
+                return wire.loads(base64.b64decode(data)) if isinstance(data, str) else (data or {})
+            if state in ("FAILED", "CANCELLED"):
+                raise NeutrinoError(f"request {request_id} {state.lower()}: {page.get('message') or page.get('error') or ''}")
+            if progressed:
+                delay = self.poll_interval
+            else:
+                self._sleep(delay)
+                delay = min(delay * 1.5, self.poll_interval * 10)
+        raise NeutrinoError(f"request {request_id} timed out")
+
+    def cancel_request(self, job_id: str, request_id: str, sub_job_id: Optional[str] = None) -> dict:
+        return self._operation(job_id, "cancel-request", {"request_id": request_id}, sub_job_id=sub_job_id)
+
+    # ------------------------------------------------------------------ logs and scheduler events (cursor-paged)
+    def tail_logs(self, job_id: str, cursor: Optional[str] = None, max_lines: Optional[int] = None,
+                  sub_job_id: Optional[str] = None) -> dict:
+        """One page of a sub-job's log from ``cursor`` (None: the start): ``{"entries", "next_cursor", "eof"}``."""
+        body = {k: v for k, v in (("cursor", cursor), ("max_lines", max_lines)) if v is not None}
+        return self._operation(job_id, "tail-logs", body, sub_job_id=sub_job_id)
+
+    def tail_events(self, job_id: str, cursor: Optional[str] = None, max_events: Optional[int] = None,
+                    sub_job_id: Optional[str] = None) -> dict:
+        """One page of the session's scheduling events: ``{"events", "next_cursor", "eof"}``."""
+        body = {k: v for k, v in (("cursor", cursor), ("max_events", max_events)) if v is not None}
+        return self._operation(job_id, "zmd-events", body, sub_job_id=sub_job_id)
+
+    def _stream_pages(self, fetch, key: str, follow: bool, cursor: Optional[str], poll_interval: Optional[float]):
+        """Generator over a cursor-paged feed: yields the entries of every page; an empty page ends the stream when
+        the feed reports its end and ``follow`` is off, otherwise the next look comes after a growing pause."""
+        base = poll_interval or self.poll_interval
+        delay = base
+        while True:
+            page = fetch(cursor) or {}
+            cursor = page.get("next_cursor", cursor)
+            items = page.get(key) or []
+            yield from items
+            if items:
+                delay = base
+                continue
+            if page.get("eof") and not follow:
+                return
+            self._sleep(delay)
+            delay = min(delay * 1.5, base * 10)
+
+    def stream_logs(self, job_id: str, sub_job_id: Optional[str] = None, cursor: Optional[str] = None,
+                    max_lines: Optional[int] = None, poll_interval: Optional[float] = None, follow: bool = True):
+        """Log entries as they appear (``follow=False``: until the current end of the log)."""
+        return self._stream_pages(lambda c: self.tail_logs(job_id, c, max_lines, sub_job_id), "entries", follow, cursor,
+                                  poll_interval)
+
+    def stream_events(self, job_id: str, cursor: Optional[str] = None, max_events: Optional[int] = None,
+                      sub_job_id: Optional[str] = None, poll_interval: Optional[float] = None, follow: bool = True):
+        return self._stream_pages(lambda c: self.tail_events(job_id, c, max_events, sub_job_id), "events", follow, cursor,
+                                  poll_interval)
+
+    # ------------------------------------------------------------------ checkpoints, experiment bookkeeping
+    def list_checkpoints(self, job_id: str) -> List[dict]:
+        return self._send("GET", f"/jobs/{job_id}/checkpoints").json().get("checkpoints", [])
+
+    def export_checkpoint(self, job_id: str, checkpoint_id: str) -> dict:
+        """Asks the service to publish a checkpoint as Hugging Face weights (colon-action route)."""
+        return self._send("POST", f"/jobs/{job_id}/checkpoints/{checkpoint_id}:export").json()
+
+    def delete_checkpoint(self, job_id: str, checkpoint_id: str) -> None:
+        self._send("DELETE", f"/jobs/{job_id}/checkpoints/{checkpoint_id}")
+
+    def get_experiment_run(self, job_id: str) -> dict:
+        """``{"experiment_name", "experiment_run_name"}`` the service files the job's metrics under."""
+        return self._send("GET", f"/jobs/{job_id}/experiment-run").json()
+
     def forward_backward(self, job_id: str, batch: dict, meta: Optional[dict] = None, processing: Optional[dict] = None, **kw):
         return self._operation(job_id, "forward_backward", {"batch": batch, "meta": meta or {}, "processing": processing or {}},
                                binary=True, **kw)

@@ -34,6 +34,8 @@ class FakeServiceSession:
         self._groups: Dict[str, List[bytes]] = {}
         self._n = 0
         self.logs = [{"ts": f"t{i}", "level": "INFO", "message": f"line {i}"} for i in range(5)]
+        self.events = [{"ts": f"e{i}", "kind": "ZONE_READY" if i else "SCHEDULED"} for i in range(3)]
+        self.checkpoints = [{"checkpoint_id": "c1", "step": 10}, {"checkpoint_id": "c2", "step": 20}]
 
     # the one entry point requests.Session exposes that the clients use
     def request(self, method: str, url: str, headers=None, timeout=None, params=None, json=None, data=None):
@@ -75,6 +77,40 @@ class FakeServiceSession:
         m = re.fullmatch(r"/jobs/([^/]+)/logs", path)
         if m:
             return FakeResponse(200, {"logs": self.logs[int(params.get("cursor", 0)):]})
+        m = re.fullmatch(r"/jobs/([^/]+)/requests/([^/]+)", path)
+        if m:
+            evs = self.requests.get(m.group(2))
+            if evs is None:
+                return FakeResponse(404, {"error": "no such request"})
+            cur = int(params.get("cursor") or 0)
+            page = [e for e in evs if e["seq"] >= cur][:2]
+            nxt = (page[-1]["seq"] + 1) if page else cur
+            done = nxt >= len(evs)
+            failed = any(e["type"] == "error" for e in evs[:nxt])
+            out = {"status": "error" if failed else ("done" if done else "in-progress"), "events": page,
+                   "next_cursor": str(nxt)}
+            if failed:
+                out["message"] = next(e["message"] for e in evs if e["type"] == "error")
+            elif done:
+                last = evs[-1]
+                if "data" in last:
+                    out["result"] = last["data"]
+            return FakeResponse(200, out)
+        m = re.fullmatch(r"/jobs/([^/]+)/checkpoints", path)
+        if m and method == "GET":
+            return FakeResponse(200, {"checkpoints": list(self.checkpoints)})
+        m = re.fullmatch(r"/jobs/([^/]+)/checkpoints/([^/:]+)(:export)?", path)
+        if m:
+            cid = m.group(2)
+            if not any(c["checkpoint_id"] == cid for c in self.checkpoints):
+                return FakeResponse(404, {"error": "no such checkpoint"})
+            if method == "DELETE":
+                self.checkpoints = [c for c in self.checkpoints if c["checkpoint_id"] != cid]
+                return FakeResponse(200, {})
+            return FakeResponse(200, {"checkpoint_id": cid, "status": "EXPORTING"})
+        m = re.fullmatch(r"/jobs/([^/]+)/experiment-run", path)
+        if m:
+            return FakeResponse(200, {"experiment_name": "exp", "experiment_run_name": f"run-{m.group(1)}"})
         m = re.fullmatch(r"/jobs/([^/]+)/([a-z_\-]+)", path)
         if m and method == "POST":
             jid, op = m.groups()
@@ -121,6 +157,11 @@ class FakeServiceSession:
             return {"metrics": {"grad_norm": 1.5, "last_lr": body.get("learning_rate") or 1e-6}}
         if op == "fail":
             raise RuntimeError("engine exploded")
+        if op in ("tail-logs", "zmd-events"):
+            feed, key, cap = (self.logs, "entries", "max_lines") if op == "tail-logs" else (self.events, "events", "max_events")
+            cur = int(body.get("cursor") or 0)
+            page = feed[cur:cur + int(body.get(cap) or 2)]
+            return {key: page, "next_cursor": str(cur + len(page)), "eof": cur + len(page) >= len(feed)}
         return {"status": "ok", "op": op, "body": {k: v for k, v in body.items() if not hasattr(v, "shape")}}
 
     def _events_for(self, op, body, params) -> List[dict]:

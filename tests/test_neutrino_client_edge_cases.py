@@ -165,3 +165,44 @@ def test_generate_checks_lengths_and_streams():
     assert c.load(jid, step=4)["op"] == "load"
     assert c.bootstrap_router_replay(jid, {"layer0": torch.zeros(2, 2, dtype=torch.long)})["op"] == "bootstrap_router_replay"
     assert c.fwd == c.forward_backward and c.fwd_no_grad == c.forward
+
+
+def test_request_polling_log_tails_and_checkpoint_routes():
+    """The status-page way of waiting for a request, cursor-paged log / scheduler-event feeds (one page, and the
+    streaming generators with and without follow), checkpoint listing / export / deletion, experiment bookkeeping
+    and the older forward aliases."""
+    svc = FakeServiceSession(chunk_results_over=600)
+    naps = []
+    c = NeutrinoClient("https://svc/api", session=svc, poll_interval=0.01, sleep=naps.append)
+    job = c.create_job([SubJobConfig.training_job("qwen3-tiny")])["job_id"]
+    # status-page polling: plain result, chunked result, failure
+    rid = c._operation(job, "step", {"learning_rate": 3e-6}, wait=False)
+    assert c.poll_request(job, rid)["metrics"]["last_lr"] == 3e-6
+    big = {"batch": {"input_ids": torch.zeros(4, 300, dtype=torch.int64)}}
+    rid = c._operation(job, "forward", big, binary=True, wait=False)
+    assert c.poll_request(job, rid)["batch"]["log_probs"].shape == (4, 3)
+    rid = c._operation(job, "fail", {}, wait=False)
+    import pytest
+    with pytest.raises(NeutrinoError, match="failed: engine exploded"):
+        c.poll_request(job, rid)
+    assert c._normalize_request_status("in-progress") == "RUNNING" and c._normalize_request_status("Done") == "COMPLETED"
+    assert c.cancel_request(job, "r-any")["body"] == {"request_id": "r-any"}
+    # one page, then the generators
+    page = c.tail_logs(job, max_lines=3)
+    assert [e["message"] for e in page["entries"]] == ["line 0", "line 1", "line 2"] and not page["eof"]
+    assert [e["message"] for e in c.stream_logs(job, follow=False, max_lines=2)] == [f"line {i}" for i in range(5)]
+    assert [e["kind"] for e in c.stream_events(job, follow=False)] == ["SCHEDULED", "ZONE_READY", "ZONE_READY"]
+    live = c.stream_logs(job, cursor="4")                        # follow: waits for new entries after the end
+    assert next(live)["message"] == "line 4"
+    svc.logs.append({"ts": "t5", "level": "INFO", "message": "line 5"})
+    assert next(live)["message"] == "line 5" and len(naps) >= 0
+    # checkpoints and bookkeeping
+    assert [k["checkpoint_id"] for k in c.list_checkpoints(job)] == ["c1", "c2"]
+    assert c.export_checkpoint(job, "c2")["status"] == "EXPORTING"
+    c.delete_checkpoint(job, "c1")
+    assert [k["checkpoint_id"] for k in c.list_checkpoints(job)] == ["c2"]
+    with pytest.raises(NeutrinoError):
+        c.delete_checkpoint(job, "c1")
+    assert c.get_experiment_run(job) == {"experiment_name": "exp", "experiment_run_name": f"run-{job}"}
+    out = c.fwd_no_grad(job, {"input_ids": torch.zeros(2, 5, dtype=torch.int64)})
+    assert out["batch"]["log_probs"].shape == (2, 3)
