@@ -13,11 +13,14 @@
 //
 // CTA = 192 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax (one row each).
 //
-// The KV blocks of a node are software-pipelined: tensor memory holds TWO score buffers and TWO output buffers, the
-// MMA warp issues Q K^T of block j+1 before it waits for the probabilities of block j, and the softmax warps fold the
-// output of block j-1 into their running accumulator after they have handed block j's probabilities over -- so the
-// tensor pipe works on P V (j-1) and Q K^T (j+1) while the softmax of block j runs, and neither side idles on the
-// other (one buffer of each made every block a serial chain of load, MMA, softmax, MMA, read-out).
+// The KV blocks of a node are software-pipelined: tensor memory holds TWO score buffers, the MMA warp issues Q K^T of
+// block j+1 before it waits for the probabilities of block j, and P V accumulates over all blocks in ONE output
+// buffer in tensor memory that the softmax warps read only once, at the end.  The running maximum is therefore a
+// REFERENCE maximum: a row rescales its output (read, multiply, write back -- after the previous P V has landed)
+// only when its true maximum has moved more than 2^8 above the reference; otherwise the probabilities are taken
+// against the stale reference (at most 256, harmless in bf16 / fp32) and nothing is rescaled.  Per block a softmax
+// thread thus reads its 128 scores once, takes 128 exponentials and writes 64 packed words -- the per-block read-out
+// and fold of the output (and the second pass over the scores) of the earlier versions set the pace of the kernel.
 #include "common.cuh"
 #include "host_utils.cuh"
 
@@ -41,7 +44,8 @@ constexpr int kDpThreads = 192;
 constexpr int kDpSlots = 4;
 constexpr int kDpTile = 128 * 128 * 2;  // one Q / K / V tile (D = 128)
 constexpr int kDpSmem = kDpTile + kDpSlots * kDpTile + 1024 + 256;
-constexpr int kDpTmemCols = 512;        // S0 | S1 | O0 | O1, 128 fp32 columns each
+constexpr int kDpTmemCols = 512;        // S0 | S1 | O (128 fp32 columns each); 384 used, the allocation is a power of 2
+constexpr float kDpRescaleSlack = 8.f;  // log2 units the true row maximum may exceed the reference before a rescale
 
 __global__ void __launch_bounds__(kDpThreads, 1)
 decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
@@ -57,9 +61,8 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   uint64_t* q_full = bars + 2 * kDpSlots;
   uint64_t* s_full = q_full + 1;    // [2] MMA -> softmax: scores of block j are in S[j & 1]
   uint64_t* p_full = s_full + 2;    // [2] softmax -> MMA: probabilities of block j are in S[j & 1]
-  uint64_t* o_full = p_full + 2;    // [2] MMA -> softmax: P V of block j is in O[j & 1]
-  uint64_t* o_free = o_full + 2;    // [2] softmax -> MMA: O[j & 1] has been read
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_free + 2);
+  uint64_t* o_full = p_full + 2;    // [1] MMA -> softmax: P V of block j has been added to O (one phase per block)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(o_full + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = blockIdx.x / p.Hkv;
@@ -90,7 +93,6 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       mbar_init(&s_full[b], 1);
       mbar_init(&p_full[b], 128);
       mbar_init(&o_full[b], 1);
-      mbar_init(&o_free[b], 128);
     }
     mbar_fence_init();
   }
@@ -182,18 +184,18 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         }
         const int nv = 2 * j + 1, b = j & 1;
         if (!mbar_wait(&kv_full[nv % kDpSlots], (nv / kDpSlots) & 1, p.status, kTimeoutFull) ||
-            !mbar_wait(&p_full[b], (j >> 1) & 1, p.status, kTimeoutTmemEmpty) ||
-            (j >= 2 && !mbar_wait(&o_free[b], ((j - 2) >> 1) & 1, p.status, kTimeoutTmemEmpty))) {
+            !mbar_wait(&p_full[b], (j >> 1) & 1, p.status, kTimeoutTmemEmpty)) {
           ok = false;
           break;
         }
         tc_fence_after();
         const uint32_t va = smem_u32(smem_kv + (nv % kDpSlots) * kDpTile);
-        const uint32_t t_p = tmem_base + b * 128, t_o = tmem_base + 256 + b * 128;
+        const uint32_t t_p = tmem_base + b * 128, t_o = tmem_base + 256;
 #pragma unroll
         for (int k = 0; k < 128 / 16; ++k)
-          umma_bf16_ts(t_o, t_p + k * 8, umma_smem_desc(va + k * 2048, 16384, 1024), idesc_o, k > 0 ? 1u : 0u);
-        tc_commit(&o_full[b]);
+          umma_bf16_ts(t_o, t_p + k * 8, umma_smem_desc(va + k * 2048, 16384, 1024), idesc_o,
+                       (j > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&o_full[0]);
         tc_commit(&kv_empty[nv % kDpSlots]);
       }
     }
@@ -202,30 +204,10 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
-    float o_acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
-    float alpha_prev = 1.f;          // rescale factor that goes with the output block still to be folded in
+    // m_ref: the maximum the exponentials are taken against (see the header); l_run: row sum in the same units
+    float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
-    // o_acc = o_acc * alpha + O(j), then O[j & 1] is handed back to the MMA warp
-    auto fold_output = [&](int j, float alpha) -> bool {
-      const int b = j & 1;
-      if (!mbar_wait(&o_full[b], (j >> 1) & 1, p.status, kTimeoutTmemFull)) return false;
-      tc_fence_after();
-      const uint32_t t_o = tmem_base + lane_off + 256 + b * 128;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_o + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = o_acc[c * 32 + i] * alpha + __uint_as_float(r[i]);
-      }
-      tc_fence_before();
-      mbar_arrive(&o_free[b]);
-      return true;
-    };
+    const uint32_t t_o = tmem_base + lane_off + 256;
     for (int j = 0; j < n_blocks; ++j) {
       const int b = j & 1;
       if (!mbar_wait(&s_full[b], (j >> 1) & 1, p.status, kTimeoutTmemFull)) {
@@ -235,30 +217,49 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       tc_fence_after();
       const uint32_t t_s = tmem_base + lane_off + b * 128;
       const int limit = max(0, min(128, len - (b0 + j) * 128));
+      uint32_t sc[4][32];
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_s + c * 32, r);
-        tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sc[c]);
+      tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          if (c * 32 + i < limit) mx = fmaxf(mx, __uint_as_float(r[i]));
-      }
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);
-      float rowsum = 0.f;
+          if (c * 32 + i < limit) mx = fmaxf(mx, __uint_as_float(sc[c][i]));
+      const float m_new = fmaxf(m_ref, mx * p.scale_log2);
+      if (m_new > m_ref + kDpRescaleSlack || m_ref == -INFINITY) {
+        // move the reference.  Everything accumulated so far is in the old units: the row sum here, the output
+        // row in tensor memory (once the previous block's P V has landed; block 0 has nothing to rescale)
+        const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
+        if (j > 0) {
+          if (!mbar_wait(&o_full[0], (j - 1) & 1, p.status, kTimeoutTmemFull)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
 #pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_o + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(t_o + c * 32, r);
+          }
+        }
+        l_run *= alpha;
+        m_ref = m_new;
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      float rowsum = 0.f;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_s + c * 32, r);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float p0 = exp2f(__uint_as_float(r[2 * i]) * p.scale_log2 - m_use);
-          float p1 = exp2f(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m_use);
+          float p0 = exp2f(__uint_as_float(sc[c][2 * i]) * p.scale_log2 - m_use);
+          float p1 = exp2f(__uint_as_float(sc[c][2 * i + 1]) * p.scale_log2 - m_use);
           if (c * 32 + 2 * i >= limit) p0 = 0.f;
           if (c * 32 + 2 * i + 1 >= limit) p1 = 0.f;
           rowsum += p0 + p1;
@@ -269,16 +270,29 @@ decode_prefix_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_full[b]);
-      l_run = l_run * alpha + rowsum;
-      m_run = m_new;
-      // while the tensor pipe multiplies this block's probabilities, fold in the previous block's output
-      if (j > 0 && !fold_output(j - 1, alpha_prev)) {
-        ok = false;
-        break;
-      }
-      alpha_prev = alpha;
+      l_run += rowsum;
     }
-    if (ok && n_blocks > 0) ok = fold_output(n_blocks - 1, alpha_prev);
+    // the output row: one read after the last P V
+    float o_acc[D];
+    if (ok && n_blocks > 0) {
+      ok = mbar_wait(&o_full[0], (n_blocks - 1) & 1, p.status, kTimeoutTmemFull);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_o + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] = __uint_as_float(r[i]);
+        }
+        tc_fence_before();
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
+    }
+    const float m_run = m_ref;
     if (ok && row < nq * R) {
       const int seq = qs + row / R;
       const int head = kvh * R + row % R;
