@@ -17,10 +17,10 @@ def make_transport(config: ArcticRLClientConfig, server_state: Any = None) -> Tr
     if config.backend.protocol == "http":
         from .transports.onprem import HttpTransport
         return HttpTransport(config)
+    if config.backend.protocol == "ray":
+        from .transports.ray_actor import RayTransport
+        return RayTransport(config, server_state)
     from .transports.onprem import CoreTransport
-    if config.backend.protocol == "ray" and server_state is None:
-        from ..rl.ray_client import create_arctic_rl_ray_server_state
-        server_state = create_arctic_rl_ray_server_state(colocate=config.backend.colocate)
     return CoreTransport(config, server_state)
 
 
