@@ -12,6 +12,7 @@ from __future__ import annotations
 import contextlib
 import os
 import time
+import logging
 from typing import Any, Dict, Iterable, List, Optional
 
 import torch
@@ -23,6 +24,8 @@ from ..models.config import DecoderConfig, resolve_config
 from ..models.decoder import DecoderLM
 from ..rl.processors.pipeline import run_pipeline
 from .trainer import EngineConfig, TrainEngine
+
+logger = logging.getLogger(__name__)
 
 
 def split_microbatches(batch: Dict[str, torch.Tensor], n: int) -> List[Dict[str, torch.Tensor]]:
@@ -144,6 +147,14 @@ class EngineWorker:
                 from .hybrid_sampler import HybridSampler as SamplerEngine      # noqa: F811
             elif self.device.type != "cuda":
                 from .reference_sampler import ReferenceSampler as SamplerEngine   # noqa: F811  (CPU: recompute sampler)
+            spec = self._speculative_setup(job_config, vc, dtype, seed) if not scorer else None
+            if spec is not None:
+                from .speculative import SpeculativeSampler
+                self.sampler = SpeculativeSampler(self.model_cfg, self.device, model=m, draft_model=spec["draft"],
+                                                  num_speculative_tokens=spec["k"],
+                                                  max_seq_len=int(vc.get("max_model_len", 8192)), seed=seed,
+                                                  eos_token_id=vc.get("eos_token_id"))
+                return True
             if scorer:
                 # a log-prob job on the sampler's engine: it only scores (teacher-forced passes), so a token of KV
                 # cache is enough; it receives weights like a sampler does
@@ -276,6 +287,32 @@ class EngineWorker:
             dist.init_process_group("gloo", rank=self.rank, world_size=self.world, timeout=timeout)
         _PG["created_here"], _PG["users"] = True, 1
         self._owns_process_group = True
+
+    def _speculative_setup(self, job_config, vc: dict, dtype, seed) -> Optional[dict]:
+        """``arctic_inference_config.speculative_decoding = {model, num_speculative_tokens}`` (or ``vllm_config.spec_model``)
+        names a draft model.  The tensor-op engine drafts and verifies with it (CPU runs; on a GPU when
+        ``vllm_config.speculative_engine = "tensor_op"`` asks for that engine); the paged CUDA engine does not
+        speculate, so there the setting is reported and ignored.  Hybrid (recurrent-state) models are not drafted for."""
+        sd = dict((job_config.get("arctic_inference_config") or {}).get("speculative_decoding") or {})
+        name = (sd.get("model") or vc.get("spec_model") or "").strip()
+        if not name:
+            return None
+        tensor_op = self.device.type != "cuda" or vc.get("speculative_engine") == "tensor_op"
+        if not tensor_op or self.model_cfg.layer_types is not None:
+            logger.warning("speculative decoding (%s) is not available on this sampler engine; decoding without it", name)
+            return None
+        from pathlib import Path
+        from ..models.config import resolve_config
+        from ..models.conversion_cache import load_through_cache
+        dcfg = resolve_config(name)
+        draft = DecoderLM(dcfg, self.device, dtype)
+        path = Path(name)
+        if path.is_dir() and any(path.glob("*.safetensors")):
+            load_through_cache(draft, path, cache_dir=job_config.get("weight_conversion_cache_dir"))
+        else:
+            draft.init_weights(seed=seed + 1)
+        draft.eval()
+        return {"draft": draft, "k": int(sd.get("num_speculative_tokens") or vc.get("num_speculative_tokens") or 4)}
 
     def _load_model(self, job_config, dtype, seed) -> DecoderLM:
         from pathlib import Path
