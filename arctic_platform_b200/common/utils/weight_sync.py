@@ -3,6 +3,9 @@
 * ``sync_weights_in_process``  -- source and target workers live in this process on the same GPU: one kernel copies
   (stages 0-2) or gathers (stage 3) the flat parameter buffer into the sampler's buffer.  This is what the
   reference's zero-copy CUDA-IPC path (``sync_weights_cuda_ipc``) achieves for colocated engines.
+* ``sync_weights_cuda_ipc``    -- different processes on one node (split placement): the trainer exports an IPC handle
+  of its flat parameter buffer, the sampler maps it and runs the same one-kernel hand-over on it over NVLink (with its
+  tensor-parallel slicing and fp8 requantisation); no tensor travels through the server.
 * ``sync_weights_bulk``        -- different processes: one RPC returns every tensor, one RPC loads them.
 * ``sync_weights_low_mem``     -- different processes, bounded peak memory: buckets of at most ``bucket_bytes``
   (the reference's ``sync_weights_cuda_ipc_low_mem`` streams one parameter per round trip).
@@ -39,6 +42,24 @@ def load_staged(dst, weights) -> int:
 
 def sync_weights_in_process(src, dst) -> int:
     return src.obj.sync_weights_to(dst.obj)
+
+
+def sync_weights_cuda_ipc(src, dst, staged: bool = True) -> Optional[int]:
+    """``None`` when the source cannot export its storage (sharded or symmetric-memory buffers) or the target is not
+    the paged CUDA sampler: the caller then picks another strategy."""
+    try:
+        info = src.call("export_ipc_source")
+    except Exception:
+        info = None
+    if not info:
+        return None
+
+    def run():
+        return dst.call("sync_from_ipc", [info])
+    try:
+        return _staged(dst, run) if staged else run()
+    except RuntimeError:
+        return None
 
 
 def sync_weights_bulk(src, dst, staged: bool = False) -> int:
@@ -83,6 +104,10 @@ def sync_pair(src, dst, cuda_ipc: Optional[bool] = None, low_memory: Optional[bo
     if same_rank_process(src, dst) and cuda_ipc is not False:
         # both engines live in the same spawned rank process: the in-process kernel runs there
         return {"strategy": "in_process", "num_tensors": src.sync_to(dst)}
+    if cuda_ipc is True and hasattr(src, "call") and hasattr(dst, "call"):
+        n = sync_weights_cuda_ipc(src, dst)
+        if n is not None:
+            return {"strategy": "cuda_ipc", "num_tensors": n}
     if via_file:
         return {"strategy": "cpu_file", "num_tensors": sync_weights_cpu_file(src, dst)}
     if low_memory:

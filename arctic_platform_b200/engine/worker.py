@@ -665,9 +665,9 @@ class EngineWorker:
         return out
 
     def release_ipc_handles(self) -> int:
-        """Nothing to release: engines of one GPU share a process and hand weights over with a kernel, so no
-        inter-process memory handles are ever exported (the reference frees its CUDA-IPC handles here)."""
-        return 0
+        """Unmaps the trainer buffers a split-placement sampler opened through CUDA IPC (``sync_from_ipc``); engines
+        that share a process hand weights over with a kernel and hold none.  Returns how many were released."""
+        return self.release_ipc()
 
     def weight_norm(self) -> Dict[str, float]:
         return self.sampler.weight_norm() if self.sampler is not None else self.engine.weight_norm()
@@ -805,6 +805,70 @@ class EngineWorker:
             sm._graphs.clear()
             sm._fp8_stale = False
         return len(hf_param_names(self.model_cfg))
+
+    # ------------------------------------------------------------------ split placement: hand-over through CUDA IPC
+    def export_ipc_source(self) -> Optional[Dict[str, Any]]:
+        """Trainer side of the split-placement hand-over: an IPC handle of this rank's flat bf16 parameter buffer
+        plus its layout, for a sampler in ANOTHER process of the node to map and read over NVLink
+        (``sync_from_ipc``).  ``None`` when the storage cannot be exported that way -- ZeRO-3 shards and the
+        symmetric-memory buffers of multi-rank fused engines are not legacy-IPC allocations -- and the caller falls
+        back to shipping tensors.  The reference's counterpart is ``sync_weights_cuda_ipc``
+        (arctic_platform/common/utils/weight_sync.py:47-142)."""
+        from ..parallel import weight_sync
+        eng = self.engine
+        if eng is None or not eng.on_cuda or getattr(eng, "zero3", None) is not None:
+            return None
+        if any(u.local_only for u in eng.units):
+            return None
+        try:
+            handle, offset = weight_sync.export_ipc(eng.param_buf.tensor)
+        except Exception:
+            return None
+        torch.cuda.synchronize(self.device)               # the optimizer step that wrote the buffer has finished
+        return {"handle": handle, "offset": offset, "layout": weight_sync.trainer_layout(eng),
+                "device": int(self.device.index or 0)}
+
+    def sync_from_ipc(self, sources: List[Dict[str, Any]]) -> int:
+        """Sampler side: maps the trainer buffers named by ``sources`` (once per handle), builds the tile table for
+        this replica's layout (tensor-parallel shard, fp8 copies) and runs the one hand-over kernel on them.  Returns
+        the number of tensors covered."""
+        from ..models.hf_io import hf_param_names
+        from ..parallel import weight_sync
+        sm = self.sampler
+        if sm is None or self.device.type != "cuda" or not hasattr(sm, "_sync_plan"):
+            raise RuntimeError("sync_from_ipc needs the paged CUDA sampler")
+        maps = self.__dict__.setdefault("_ipc_maps", {})
+        ptrs = []
+        for src in sources:
+            key = bytes(src["handle"])
+            if key not in maps:
+                maps[key] = (weight_sync.open_ipc(key, int(src["offset"])), int(src["offset"]))
+            ptrs.append(maps[key][0])
+        layout = sources[0]["layout"]
+        tp, fp8 = int(getattr(sm, "tp", 1)), bool(getattr(sm, "fp8", False))
+        key = (layout["total"], layout["world"], layout["zero3"] is not None, sm.tp_rank, tp, fp8, "ipc")
+        plan = sm._sync_plan
+        if plan is None or plan.layout_key != key:
+            plan = weight_sync.build_sync_plan(layout, sm.model, full_cfg=sm.full_cfg, tp_rank=sm.tp_rank, tp=tp, fp8=fp8)
+            plan.layout_key = key
+            sm._sync_plan = plan
+        weight_sync.run_sync_plan(plan, ptrs, 0)
+        torch.cuda.synchronize(self.device)               # the trainer may write its buffer again after this returns
+        if fp8:
+            sm._fp8_w = [{n: plan.fp8[(li, n)] for n in weight_sync.FP8_MATRICES} for li in range(sm.cfg.num_layers)]
+            sm._graphs.clear()
+            sm._fp8_stale = False
+        elif hasattr(sm, "weights_updated"):
+            sm.weights_updated()
+        return len(hf_param_names(self.model_cfg))
+
+    def release_ipc(self) -> int:
+        """Unmaps every trainer buffer this worker has opened (before the trainer frees them)."""
+        from ..parallel import weight_sync
+        maps = self.__dict__.pop("_ipc_maps", {})
+        for addr, off in maps.values():
+            weight_sync.close_ipc(addr, off)
+        return len(maps)
 
     def sleep_inference(self, level: int = 1) -> None:
         if self.sampler is not None:

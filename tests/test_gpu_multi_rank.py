@@ -419,3 +419,73 @@ def test_tensor_parallel_paged_sampler_on_two_gpus():
     for a, b in zip(r0[False], r0["one"]):
         k = next((i for i, (x, y) in enumerate(zip(a["token_ids"], b["token_ids"])) if x != y), len(a["token_ids"]))
         assert a["logprobs"][:k] == pytest.approx(b["logprobs"][:k], abs=6e-2)
+
+
+def _ipc_trainer(q_out, q_in, port):
+    """Process A (cuda:0): a one-rank trainer that takes one optimizer step, exports its buffer and waits."""
+    try:
+        torch.cuda.set_device(0)
+        from arctic_platform_b200.engine.worker import EngineWorker
+        w = EngineWorker("cuda:0")
+        w.initialize({"model_name": "qwen3-tiny-d128", "job_type": "training", "seed": 5,
+                      "ds_config": {"zero_optimization": {"stage": 1}, "optimizer": {"params": {"lr": 1e-2}}}})
+        info = w.export_ipc_source()
+        assert info is not None and len(info["handle"]) == 64
+        ref = {n: t.detach().float().cpu() for n, t in w.engine.iter_hf_tensors()}
+        q_out.put((info, ref, w.weight_norm()["norm"]))
+        assert q_in.get(timeout=120) == "done"               # keep the buffer alive while the reader has it mapped
+    except Exception as exc:                                 # pragma: no cover - surfaced by the parent
+        q_out.put(("error", repr(exc), None))
+        raise
+
+
+def _ipc_sampler(q_out, q_src, fp8):
+    """Process B (cuda:1): a sampler that maps the trainer's buffer and runs the hand-over kernel on it."""
+    try:
+        torch.cuda.set_device(1)
+        from arctic_platform_b200.engine.worker import EngineWorker
+        from arctic_platform_b200.ops import _lib
+        w = EngineWorker("cuda:1")
+        vc = {"max_model_len": 256, "kv_cache_tokens": 4096, "max_num_seqs": 8}
+        if fp8:
+            vc["quantization"] = "fp8"
+        w.initialize({"model_name": "qwen3-tiny-d128", "job_type": "sampling", "seed": 99, "vllm_config": vc})
+        info, ref, norm = q_src.get(timeout=120)
+        n = w.sync_from_ipc([info])
+        _lib.check_status("ipc sync")
+        got = {n_: t.detach().float().cpu() for n_, t in w.sampler.model.named_parameters()}
+        out = w.generate([[3, 4, 5, 6]], {"temperature": 0.0, "max_tokens": 4})
+        released = w.release_ipc_handles()
+        q_out.put((n, w.weight_norm()["norm"], norm, released, len(out[0]["token_ids"]),
+                   {k: float(v.abs().sum()) for k, v in got.items()}))
+    except Exception as exc:                                 # pragma: no cover
+        q_out.put(("error", repr(exc)))
+        raise
+
+
+@pytest.mark.timeout(300)
+def test_split_placement_hand_over_through_cuda_ipc(fp8=False):
+    """Trainer and sampler in DIFFERENT processes on different GPUs: the sampler maps the trainer's flat buffer
+    through a CUDA IPC handle and the table kernel pulls the weights over NVLink."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    a_out, a_in, b_out = ctx.Queue(), ctx.Queue(), ctx.Queue()
+    pa = ctx.Process(target=_ipc_trainer, args=(a_out, a_in, _free_port()))
+    pa.start()
+    first = a_out.get(timeout=180)
+    assert first[0] != "error", first
+    relay = ctx.Queue()
+    relay.put(first)
+    pb = ctx.Process(target=_ipc_sampler, args=(b_out, relay, fp8))
+    pb.start()
+    res = b_out.get(timeout=180)
+    a_in.put("done")
+    pa.join(60)
+    pb.join(60)
+    assert res[0] != "error", res
+    n, got_norm, want_norm, released, n_tok, _sums = res
+    assert n > 0 and released == 1 and n_tok == 4
+    assert got_norm == pytest.approx(want_norm, rel=1e-3)
+    assert pa.exitcode == 0 and pb.exitcode == 0

@@ -83,3 +83,54 @@ def test_worker_export_helpers(tmp_path):
     assert out["num_tensors"] == len(sizes) and out["bytes"] == sum(sizes.values())
     assert set(dict(read_safetensors(tmp_path / "w.safetensors"))) == set(sizes)
     assert w.release_ipc_handles() == 0
+
+
+def test_cuda_ipc_strategy_is_tried_first_and_falls_back():
+    """``cuda_ipc=True`` between workers of different processes: the source is asked for an IPC handle of its flat
+    buffer and the target runs the hand-over kernel on it; a source that cannot export (CPU engine, sharded or
+    symmetric-memory storage) or a target without the paged CUDA sampler falls back to shipping tensors."""
+    calls = []
+
+    class Src:
+        def __init__(self, info):
+            self.info = info
+
+        def call(self, name, *a):
+            calls.append(("src", name))
+            if name == "export_ipc_source":
+                return self.info
+            if name == "get_weights":
+                return [("w", torch.zeros(2))]
+            raise AssertionError(name)
+
+    class Dst:
+        def __init__(self, ok=True):
+            self.ok = ok
+
+        def call(self, name, *a):
+            calls.append(("dst", name))
+            if name == "has_sampler":
+                return True
+            if name == "sync_from_ipc":
+                if not self.ok:
+                    raise RuntimeError("sync_from_ipc needs the paged CUDA sampler")
+                assert a[0][0]["handle"] == b"h" * 64
+                return 7
+            if name == "load_weights":
+                return len(a[0])
+            return None
+
+    info = {"handle": b"h" * 64, "offset": 0, "layout": {}, "device": 0}
+    r = ws.sync_pair(Src(info), Dst(), cuda_ipc=True)
+    assert r == {"strategy": "cuda_ipc", "num_tensors": 7}
+    order = [c for c in calls if c[0] == "dst"]
+    assert [c[1] for c in order] == ["has_sampler", "wake_inference", "sync_from_ipc", "wake_inference", "reset_prefix_cache"]
+    calls.clear()
+    assert ws.sync_pair(Src(None), Dst(), cuda_ipc=True)["strategy"] == "bulk"          # nothing to export
+    assert ws.sync_pair(Src(info), Dst(ok=False), cuda_ipc=True)["strategy"] == "bulk"  # target cannot map
+    assert ws.sync_pair(Src(info), Dst())["strategy"] == "bulk"                         # not asked for
+    # a CPU trainer has nothing to export
+    from arctic_platform_b200.engine.worker import EngineWorker
+    w = EngineWorker("cpu")
+    w.initialize({"model_name": "qwen3-tiny", "job_type": "training", "ds_config": {"zero_optimization": {"stage": 1}}})
+    assert w.export_ipc_source() is None and w.release_ipc_handles() == 0
