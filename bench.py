@@ -57,6 +57,11 @@ def parse_args():
                     help="file with a same-box anchor {'grpo_step_tokens_per_s_per_gpu': x, 'what': ...}; default "
                          "benchmarks/anchors_1gpu.json when present (vs_baseline = value / (x * gpus))")
     ap.add_argument("--lr", type=float, default=1e-6)
+    ap.add_argument("--wall-limit-s", type=float, default=830.0,
+                    help="safety net for callers that end the process after a fixed wall time: when the next timed "
+                         "step would end later than this many seconds after the process started, the timed loop "
+                         "stops (all ranks together, never before 5 steps) and the line reports the steps it timed "
+                         "in 'steps' and the request in 'steps_requested'; 0 = no limit")
     return ap.parse_args()
 
 
@@ -113,6 +118,17 @@ class ClockSampler(threading.Thread):
         busy = sorted(sm)[len(sm) // 4:] if sm else []
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(self.samples)}
+
+
+MIN_TIMED_STEPS = 5
+
+
+def stop_for_wall_limit(done: int, age_s: float, s_per_step: float, limit_s: float) -> bool:
+    """Whether the timed loop should end after ``done`` steps: the next step (3 % slack, 5 s to report and leave) would
+    finish later than ``limit_s`` seconds after the process started.  Never before ``MIN_TIMED_STEPS``."""
+    if limit_s <= 0 or done < MIN_TIMED_STEPS:
+        return False
+    return age_s + 1.03 * s_per_step + 5.0 > limit_s
 
 
 def main():
@@ -257,6 +273,25 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return [float(v) for v in t.tolist()]
 
+    def process_age():
+        try:
+            import psutil
+            return time.time() - psutil.Process().create_time()
+        except Exception:
+            return time.perf_counter() - t_start + 30.0      # imports happened before t_start: assume the worst
+
+    def out_of_time(done, s_per_step):
+        """True on every rank when any rank expects the next step to end after the wall limit."""
+        late = stop_for_wall_limit(done, process_age(), s_per_step, args.wall_limit_s)
+        if world > 1:
+            t = torch.tensor([1.0 if late else 0.0], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            late = bool(t.item() > 0)
+        if late and rank == 0:
+            print(f"[bench] wall limit {args.wall_limit_s:.0f} s: stopping after {done} of {args.steps} timed steps",
+                  file=sys.stderr, flush=True)
+        return late
+
     if rank == 0:
         print(f"[bench] engines ready after {time.perf_counter() - t_start:.1f} s", file=sys.stderr, flush=True)
     for _ in range(args.warmup):
@@ -271,8 +306,13 @@ def main():
     l0 = _lib.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
+    t_timed = time.time()
+    steps_done = 0
     for _ in range(args.steps):
         loss, gnorm = step_client()
+        steps_done += 1
+        if steps_done < args.steps and out_of_time(steps_done, (time.time() - t_timed) / steps_done):
+            break
     ev1.record()
     barrier()
     launches = _lib.launch_count() - l0
@@ -286,7 +326,7 @@ def main():
     for step_marks in marks:
         for name, e0, e1 in step_marks:
             phase_ms[name] += e0.elapsed_time(e1)
-    K = args.steps
+    K = steps_done
     red = reduce_max([ev0.elapsed_time(ev1) / K, sum(phase_ms.values()) / K] + [phase_ms[n] / K for n in PHASES])
     ms_e2e, ms_dev, per_phase = red[0], red[1], red[2:]
     if rank == 0:
@@ -304,7 +344,7 @@ def main():
         stage_label = f"zero{args.zero_stage}-fused" if world > 1 else "single-rank fused clip+AdamW (no sharding)"
         line = {
             "metric": "grpo_step_tokens_per_s", "value": value, "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
+            "n_gpus": world, "steps": K, "steps_requested": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": vs, "dtype": "bf16", "data": "synthetic",
             "impl": "ours",
             "config": {"model": args.model, "global_batch": B * world, "prompts": NP * world, "samples_per_prompt": NS,
