@@ -35,6 +35,62 @@ class NeutrinoError(RuntimeError):
         self.detail = detail or {}
 
 
+class ChunkGroupError(NeutrinoError):
+    """A chunked upload that the service refused for a reason that concerns the whole group; ``detail`` is the
+    service's error object (``code``, ``message``, ``chunk_group_id``, ...)."""
+
+
+class ChunkGroupRestartError(ChunkGroupError):
+    """The service lost an incomplete group and the bounded number of replays did not get it through either."""
+
+
+class ChunkGroupConflictError(ChunkGroupError):
+    """One group identity was used for different contents, or the group was closed with chunks missing."""
+
+
+CHUNK_GROUP_RESTART_CODES = {"chunk_group_restart_required", "chunk_group_restart"}
+CHUNK_GROUP_CONFLICT_CODES = {"chunk_group_conflict", "chunk_group_missing_chunks"}
+MAX_GROUP_REPLAYS = 2
+
+
+def find_chunk_group_error(body: Any, _depth: int = 0) -> Optional[dict]:
+    """The chunk-group error object inside an error reply, or None.  Gateways wrap the service's JSON reply in their
+    own (``{"message": "upstream said: {...}"}``), sometimes more than once, so the search descends into dicts,
+    lists and JSON objects embedded in strings.  The returned dict always carries ``code``."""
+    if _depth > 8:
+        return None
+    if isinstance(body, dict):
+        code = body.get("code") or body.get("error")
+        if isinstance(code, str) and code in CHUNK_GROUP_RESTART_CODES | CHUNK_GROUP_CONFLICT_CODES:
+            return {**body, "code": code}
+        if body.get("chunk_group_id") and str(body.get("message", "")).endswith("missing chunks"):
+            return {**body, "code": "chunk_group_missing_chunks"}
+        children = list(body.values())
+    elif isinstance(body, list):
+        children = body
+    elif isinstance(body, str) and ("{" in body or "[" in body):
+        import json
+        dec, children, i = json.JSONDecoder(), [], 0
+        while i < len(body):
+            if body[i] in "{[":
+                try:
+                    obj, end = dec.raw_decode(body, i)
+                except ValueError:
+                    i += 1
+                    continue
+                children.append(obj)
+                i = end
+            else:
+                i += 1
+    else:
+        return None
+    for child in children:
+        hit = find_chunk_group_error(child, _depth + 1)
+        if hit is not None:
+            return hit
+    return None
+
+
 class JobType(str, Enum):
     TRAINING = "training"
     SAMPLING = "sampling"
@@ -142,9 +198,12 @@ class NeutrinoClient:
                     detail = resp.json()
                 except Exception:
                     pass
-                if resp.status_code not in TRANSIENT:
+                if not isinstance(detail, dict):
+                    detail = {"body": detail}
+                # a chunk-group verdict is about the group, not this attempt: repeating the same chunk cannot help
+                if resp.status_code not in TRANSIENT or (kw.get("data") is not None and find_chunk_group_error(detail)):
                     raise NeutrinoError(f"{method} {path} -> {resp.status_code}: {getattr(resp, 'text', '')[:300]}",
-                                        resp.status_code, detail if isinstance(detail, dict) else {})
+                                        resp.status_code, detail)
                 last = NeutrinoError(f"{method} {path} -> {resp.status_code}", resp.status_code)
             if attempt < self.max_retries:
                 self._sleep(delay * (0.5 + random.random()))
@@ -198,23 +257,39 @@ class NeutrinoClient:
 
     # ------------------------------------------------------------------ ops
     def _post_octet_request_chunks(self, path: str, op: str, frame: bytes, params: Optional[dict]) -> str:
-        for attempt in range(3):
+        """Uploads one frame as a group of chunks and returns the request id the last chunk is answered with.  A
+        group the service lost half-way is replayed from its first chunk under a new identity, at most
+        ``MAX_GROUP_REPLAYS`` times (``ChunkGroupRestartError`` after that); an identity conflict or a group closed
+        with chunks missing is not retried (``ChunkGroupConflictError``)."""
+        for attempt in range(MAX_GROUP_REPLAYS + 1):
             gid = str(uuid.uuid4())
             chunks = wire.encode_byte_chunks(frame, kind="request", operation=op, max_bytes=MAX_CHUNK_BYTES,
                                              chunk_group_id=gid)
             rid = None
             try:
-                for c in chunks:
-                    rid = self._send("POST", path, params=params, data=c,
-                                     headers={"Content-Type": "application/octet-stream"}).json().get("request_id", rid)
-            except NeutrinoError as exc:
-                if exc.detail.get("error") == "chunk_group_restart" and attempt < 2:
-                    continue                                      # the server lost the group: resend under a new id
+                for i, c in enumerate(chunks):
+                    body = self._send("POST", path, params=params, data=c,
+                                      headers={"Content-Type": "application/octet-stream"}).json()
+                    got = body.get("request_id") if isinstance(body, dict) else None
+                    if got and i < len(chunks) - 1:
+                        raise NeutrinoError(f"{op}: chunk {i} of {len(chunks)} was answered with a request id")
+                    rid = got or rid
+            except ChunkGroupError:
                 raise
+            except NeutrinoError as exc:
+                detail = find_chunk_group_error(exc.detail)
+                if detail is None:
+                    raise
+                if detail["code"] in CHUNK_GROUP_RESTART_CODES:
+                    if attempt < MAX_GROUP_REPLAYS:
+                        continue                                  # the server lost the group: resend under a new id
+                    raise ChunkGroupRestartError(f"{op}: chunk group kept restarting: {detail.get('message') or detail['code']}",
+                                                 exc.status, detail) from exc
+                raise ChunkGroupConflictError(f"{op}: {detail.get('message') or detail['code']}", exc.status, detail) from exc
             if rid is None:
                 raise NeutrinoError("server did not return a request_id")
             return rid
-        raise NeutrinoError("chunk upload kept restarting")
+        raise AssertionError("unreachable")
 
     def _operation(self, job_id: str, op: str, body: Optional[dict] = None, binary: bool = False,
                    sub_job_id: Optional[str] = None, wait: bool = True):
@@ -371,6 +446,31 @@ class NeutrinoClient:
     fwd = forward_backward
     fwd_no_grad = forward
 
+    def sampling_max_seq_len(self, job_id: str) -> Optional[int]:
+        """The sequence limit of the job's sampling sub-job (``max_seq_len`` of its inference config, else
+        ``vllm_config.max_model_len``), cached per job.  A job without a sampling sub-job caches ``None``; a failed
+        look-up caches nothing, so the next call asks again."""
+        cache = self.__dict__.setdefault("_max_seq_len_cache", {})
+        if job_id in cache:
+            return cache[job_id]
+        try:
+            job = self.get_job(job_id)
+        except Exception:
+            return None
+        found = None
+        for sub in job.get("sub_jobs") or []:
+            if not isinstance(sub, dict):
+                continue
+            for holder, key in ((sub.get("inference_config"), "max_seq_len"), (sub.get("vllm_config"), "max_model_len")):
+                raw = holder.get(key) if isinstance(holder, dict) else None
+                if isinstance(raw, (int, float)) and not isinstance(raw, bool) and raw > 0:
+                    found = int(raw)
+                    break
+            if found:
+                break
+        cache[job_id] = found
+        return found
+
     def _check_prompt_lengths(self, prompts: Sequence[Sequence[int]], max_tokens: int, max_seq_len: Optional[int]) -> None:
         if max_seq_len is None:
             return
@@ -382,6 +482,8 @@ class NeutrinoClient:
     def generate(self, job_id: str, prompts: Sequence[Sequence[int]], sampling_params: Optional[dict] = None,
                  max_seq_len: Optional[int] = None, **kw):
         sp = dict(sampling_params or {})
+        if max_seq_len is None and kw.pop("validate_lengths", False):
+            max_seq_len = self.sampling_max_seq_len(job_id)
         self._check_prompt_lengths(prompts, int(sp.get("max_tokens", 16)), max_seq_len)
         return self._operation(job_id, "generate", {"prompts": [list(map(int, p)) for p in prompts], "sampling_params": sp}, **kw)
 
@@ -416,8 +518,21 @@ class NeutrinoClient:
 
 
 class NeutrinoTrainingEngine:
-    """``engine(batch)`` = forward + backward on the service, ``engine.step()`` = optimizer step: the shape of a local
-    ``nn.Module`` + optimizer loop, so existing training scripts change two lines."""
+    """A training job of the hosted service in the shape of a local engine.  Two call styles:
+
+    * ``loss = engine(batch)`` runs forward + backward at once (forward only after ``engine.eval()``);
+    * ``handle = engine.forward(**batch); loss = engine.backward(handle)`` -- the DeepSpeed-engine shape, where the
+      forward call only remembers the batch and ``backward`` does the work on the service.
+
+    ``step()`` applies the accumulated gradients; ``lr_scheduler.get_last_lr()`` reports the rate the service used.
+    ``from_sub_job`` creates the job, waits until it runs and wraps it; ``destroy`` cancels it."""
+
+    class _LastLR:
+        def __init__(self) -> None:
+            self.last_lr: List[float] = [-1.0]
+
+        def get_last_lr(self) -> List[float]:
+            return list(self.last_lr)
 
     def __init__(self, client: NeutrinoClient, job_id: str, loss_fn: str = "sft", meta: Optional[dict] = None):
         self.client = client
@@ -426,6 +541,18 @@ class NeutrinoTrainingEngine:
         self.meta = dict(meta or {})
         self.global_steps = 0
         self.training = True
+        self.module = None
+        self.optimizer = None
+        self.training_dataloader = None
+        self.lr_scheduler = self._LastLR()
+        self._pending: Optional[dict] = None
+
+    @classmethod
+    def from_sub_job(cls, client: NeutrinoClient, sub_job: "SubJobConfig", name: Optional[str] = None, **kw):
+        job = client.create_job([sub_job], name=name)
+        job_id = job["job_id"] if isinstance(job, dict) else job
+        client.wait_for_job(job_id)
+        return cls(client, job_id, **kw)
 
     def train(self, mode: bool = True):
         self.training = mode
@@ -440,13 +567,57 @@ class NeutrinoTrainingEngine:
         out = self.client.forward_backward(self.job_id, batch, {**self.meta, **meta}, {"loss_fn": self.loss_fn})
         return float(out.get("avg_loss", 0.0))
 
+    def forward(self, *args, **kwargs) -> dict:
+        if self._pending is not None:
+            raise RuntimeError("forward() was called twice without backward() in between")
+        if args:
+            if len(args) != 1 or not isinstance(args[0], dict) or kwargs:
+                raise TypeError("pass the batch as keyword tensors or as one dict")
+            kwargs = args[0]
+        self._pending = dict(kwargs)
+        return self._pending
+
+    def backward(self, *_args, **_kwargs) -> float:
+        if self._pending is None:
+            raise RuntimeError("backward() without a batch: call forward() first")
+        batch, self._pending = self._pending, None
+        return self(batch)
+
+    def is_gradient_accumulation_boundary(self) -> bool:
+        return True
+
     def step(self, learning_rate: Optional[float] = None) -> dict:
         out = self.client.step(self.job_id, learning_rate)
-        self.global_steps += 1
-        return out.get("metrics", out)
+        self.global_steps = int(out.get("global_steps", self.global_steps + 1))
+        metrics = out.get("metrics", out)
+        lr = out.get("last_lr", metrics.get("last_lr") if isinstance(metrics, dict) else None)
+        if lr is not None:
+            self.lr_scheduler.last_lr = list(lr) if isinstance(lr, (list, tuple)) else [float(lr)]
+        return metrics
 
     def save(self, path: Optional[str] = None, export_hf: bool = False) -> dict:
         return self.client.save(self.job_id, path, self.global_steps, export_hf)
 
     def load(self, path: Optional[str] = None, step: Optional[int] = None) -> dict:
         return self.client.load(self.job_id, path, step)
+
+    def save_checkpoint(self, *_args, checkpoint_type: Optional[str] = None, **_kwargs) -> dict:
+        """Server-side save; positional arguments of a local engine's ``save_checkpoint(dir, tag)`` are accepted and
+        ignored (the service decides where checkpoints live)."""
+        extra = {"checkpoint_type": checkpoint_type} if checkpoint_type else {}
+        return self.client._operation(self.job_id, "save", {"step": self.global_steps, **extra})
+
+    def load_checkpoint(self, checkpoint_id: str, *, source_job_id: Optional[str] = None,
+                        target_sub_job_id: Optional[str] = None) -> dict:
+        """Loads a checkpoint of this job -- or of ``source_job_id`` -- into the (``target_sub_job_id``) training
+        sub-job.  Loading across data-parallel sizes needs a job created without optimizer-state loading."""
+        body = {"checkpoint_id": checkpoint_id}
+        if source_job_id:
+            body["source_job_id"] = source_job_id
+        return self.client._operation(self.job_id, "load", body, sub_job_id=target_sub_job_id)
+
+    def destroy(self) -> None:
+        try:
+            self.client.cancel_job(self.job_id)
+        except NeutrinoError:
+            pass                                   # already finished or cancelled

@@ -29,6 +29,7 @@ class FakeServiceSession:
         self.calls: List[tuple] = []
         self.fail_next: List[int] = []
         self.restart_chunk_groups = 0
+        self.chunk_group_reply = None          # (status, body) answered once to the next chunk upload
         self.ready_after = ready_after
         self.chunk_results_over = chunk_results_over
         self._groups: Dict[str, List[bytes]] = {}
@@ -119,6 +120,10 @@ class FakeServiceSession:
             if data is not None:
                 hdr = wire.read_byte_chunk_metadata(data)
                 gid = hdr["chunk_group_id"] if hdr else self._new_id("g")
+                if self.chunk_group_reply is not None:
+                    status, reply = self.chunk_group_reply
+                    self.chunk_group_reply = None
+                    return FakeResponse(status, reply)
                 if self.restart_chunk_groups > 0:
                     self.restart_chunk_groups -= 1
                     self._groups.pop(gid, None)

@@ -206,3 +206,75 @@ def test_request_polling_log_tails_and_checkpoint_routes():
     assert c.get_experiment_run(job) == {"experiment_name": "exp", "experiment_run_name": f"run-{job}"}
     out = c.fwd_no_grad(job, {"input_ids": torch.zeros(2, 5, dtype=torch.int64)})
     assert out["batch"]["log_probs"].shape == (2, 3)
+
+
+def test_chunk_group_verdicts_become_structured_errors(monkeypatch):
+    from cortex_client.dss_client.neutrino_client import (ChunkGroupConflictError, ChunkGroupRestartError,
+                                                          find_chunk_group_error)
+    monkeypatch.setattr(nc, "MAX_CHUNK_BYTES", 16384)
+    c, _ = _client()
+    jid = _job(c)
+    batch = {"input_ids": torch.arange(6000).view(4, 1500)}
+    # the verdict may sit inside a gateway's wrapper, as JSON embedded in a string, on a status that is otherwise retried
+    wrapped = {"message": 'upstream error: {"error": {"code": "chunk_group_conflict", "message": "group g reused", '
+                          '"chunk_group_id": "g"}} (request 77)'}
+    c.session.chunk_group_reply = (503, wrapped)
+    n0 = len(c.session.calls)
+    with pytest.raises(ChunkGroupConflictError, match="group g reused") as e:
+        c.forward_backward(jid, batch)
+    assert e.value.detail["code"] == "chunk_group_conflict" and e.value.status == 503
+    assert len(c.session.calls) == n0 + 1                          # not retried, not replayed
+    c.session.chunk_group_reply = (400, {"chunk_group_id": "g", "message": "request chunk group is missing chunks"})
+    with pytest.raises(ChunkGroupConflictError) as e:
+        c.forward_backward(jid, batch)
+    assert e.value.detail["code"] == "chunk_group_missing_chunks"
+    # a restart verdict is replayed; when the replays run out the error says so
+    c.session.chunk_group_reply = (409, {"code": "chunk_group_restart_required", "message": "state lost"})
+    assert c.forward_backward(jid, batch)["metrics"]["n"] == 4
+    c.session.restart_chunk_groups = 10
+    with pytest.raises(ChunkGroupRestartError):
+        c.forward_backward(jid, batch)
+    assert isinstance(ChunkGroupRestartError("x"), NeutrinoError)
+    assert find_chunk_group_error({"a": [1, "text {not json} more", {"b": "{}"}]}) is None
+    assert find_chunk_group_error("[[[[[[[[[[[[[[[[") is None
+
+
+def test_sampling_limit_is_read_from_the_job_and_cached():
+    c, _ = _client()
+    jid = _job(c)
+    c.session.jobs[jid]["sub_jobs"] = [{"sub_job_type": "training"},
+                                       {"sub_job_type": "sampling", "inference_config": {"max_seq_len": 64.0}}]
+    assert c.sampling_max_seq_len(jid) == 64
+    n0 = len(c.session.calls)
+    assert c.sampling_max_seq_len(jid) == 64 and len(c.session.calls) == n0          # cached
+    with pytest.raises(ValueError, match="max_seq_len 64"):
+        c.generate(jid, [[1] * 60], {"max_tokens": 8}, validate_lengths=True)
+    assert c.sampling_max_seq_len("missing-job") is None                             # failed look-up: not cached
+    assert "missing-job" not in c._max_seq_len_cache
+
+
+def test_training_engine_deepspeed_call_shape_and_lifecycle():
+    from cortex_client.dss_client import NeutrinoTrainingEngine, SubJobConfig
+    c, _ = _client()
+    eng = NeutrinoTrainingEngine.from_sub_job(c, SubJobConfig.training_job("qwen3-4b", num_gpus=2), name="t", loss_fn="sft_ce")
+    assert c.session.jobs[eng.job_id]["status"] == "RUNNING" and eng.module is None and eng.optimizer is None
+    assert eng.lr_scheduler.get_last_lr() == [-1.0] and eng.is_gradient_accumulation_boundary()
+    handle = eng.forward(input_ids=torch.ones(2, 8, dtype=torch.long))
+    with pytest.raises(RuntimeError, match="twice"):
+        eng.forward(input_ids=torch.ones(1, 8, dtype=torch.long))
+    assert eng.backward(handle) == 0.25
+    with pytest.raises(RuntimeError, match="forward"):
+        eng.backward()
+    assert eng.forward({"input_ids": torch.ones(3, 8, dtype=torch.long)})["input_ids"].shape[0] == 3
+    eng.backward()
+    eng.step(2e-5)
+    assert eng.global_steps == 1 and eng.lr_scheduler.get_last_lr() == [2e-5]
+    saved = eng.save_checkpoint("/ignored/dir", "tag", checkpoint_type="full")
+    assert saved["op"] == "save" and saved["body"] == {"step": 1, "checkpoint_type": "full"}
+    loaded = eng.load_checkpoint("ck-7", source_job_id="job-old", target_sub_job_id=f"{eng.job_id}:training:0")
+    assert loaded["body"] == {"checkpoint_id": "ck-7", "source_job_id": "job-old"}
+    posts = [x for x in c.session.calls if x[0] == "POST" and x[1].endswith("/load")]
+    assert posts[-1][2] == {"sub_job_id": f"{eng.job_id}:training:0"}
+    eng.destroy()
+    assert c.session.jobs[eng.job_id]["status"] == "CANCELLED"
+    eng.destroy()                                                       # a second cancel is not an error for the caller
