@@ -482,10 +482,16 @@ class NeutrinoClient:
     def generate(self, job_id: str, prompts: Sequence[Sequence[int]], sampling_params: Optional[dict] = None,
                  max_seq_len: Optional[int] = None, **kw):
         sp = dict(sampling_params or {})
-        if max_seq_len is None and kw.pop("validate_lengths", False):
+        validate = kw.pop("validate_lengths", False)
+        if max_seq_len is None and validate:
             max_seq_len = self.sampling_max_seq_len(job_id)
         self._check_prompt_lengths(prompts, int(sp.get("max_tokens", 16)), max_seq_len)
-        return self._operation(job_id, "generate", {"prompts": [list(map(int, p)) for p in prompts], "sampling_params": sp}, **kw)
+        body = {"prompts": [list(map(int, p)) for p in prompts], "sampling_params": sp}
+        for key in ("routing_key", "strict"):
+            if kw.get(key) is not None:
+                body[key] = kw[key]
+            kw.pop(key, None)
+        return self._operation(job_id, "generate", body, **kw)
 
     def generate_stream(self, job_id: str, prompts: Sequence[Sequence[int]], sampling_params: Optional[dict] = None) -> Iterator[dict]:
         rid = self.generate(job_id, prompts, {**(sampling_params or {}), "stream": True}, wait=False)
@@ -498,14 +504,38 @@ class NeutrinoClient:
     def step(self, job_id: str, learning_rate: Optional[float] = None, **kw):
         return self._operation(job_id, "step", {"learning_rate": learning_rate} if learning_rate is not None else {}, **kw)
 
-    def save(self, job_id: str, path: Optional[str] = None, step: Optional[int] = None, export_hf: bool = False, **kw):
-        return self._operation(job_id, "save", {"path": path, "step": step, "export_hf": export_hf}, **kw)
+    def save(self, job_id: str, path: Optional[str] = None, step: Optional[int] = None, export_hf: bool = False,
+             checkpoint_type: Optional[str] = None, **kw):
+        body = {"path": path, "step": step, "export_hf": export_hf}
+        if checkpoint_type:
+            body["checkpoint_type"] = checkpoint_type
+        return self._operation(job_id, "save", body, **kw)
 
-    def load(self, job_id: str, path: Optional[str] = None, step: Optional[int] = None, **kw):
-        return self._operation(job_id, "load", {"path": path, "step": step}, **kw)
+    def load(self, job_id: str, path: Optional[str] = None, step: Optional[int] = None, *,
+             checkpoint_id: Optional[str] = None, source_job_id: Optional[str] = None,
+             target_sub_job_id: Optional[str] = None, **kw):
+        """By ``path`` / ``step`` (a directory the job can read) or by ``checkpoint_id`` of a server-side save --
+        of this job or of ``source_job_id`` -- routed to ``target_sub_job_id`` when the job has several trainers."""
+        if checkpoint_id is None:
+            body = {"path": path, "step": step}
+        else:
+            body = {"checkpoint_id": checkpoint_id}
+            if source_job_id:
+                body["source_job_id"] = source_job_id
+        if target_sub_job_id:
+            kw.setdefault("sub_job_id", target_sub_job_id)
+        return self._operation(job_id, "load", body, **kw)
 
-    def weight_sync(self, job_id: str, **kw):
-        return self._operation(job_id, "weight_sync", {}, **kw)
+    def weight_sync(self, job_id: str, source_sub_job_id: Optional[str] = None,
+                    target_sub_job_ids: Optional[Sequence[str]] = None, weight_format: Optional[str] = None, **kw):
+        """Trainer -> sampler hand-over.  Without arguments: the job's first trainer to its first sampler."""
+        body: Dict[str, Any] = {}
+        if source_sub_job_id or target_sub_job_ids:
+            body = {"source_sub_job_id": source_sub_job_id or f"{job_id}:training:0",
+                    "target_sub_job_ids": list(target_sub_job_ids or [f"{job_id}:sampling:0"])}
+        if weight_format:
+            body["weight_format"] = weight_format
+        return self._operation(job_id, "weight_sync", body, **kw)
 
     def reset_prefix_cache(self, job_id: str, **kw):
         return self._operation(job_id, "reset_prefix_cache", {}, **kw)
