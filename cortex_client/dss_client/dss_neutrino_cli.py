@@ -5,6 +5,7 @@
     dss-neutrino jobs create --model qwen3-4b --training-gpus 8 --sampling-gpus 8
     dss-neutrino logs JOB [--follow]            # plain-text tail with an on-disk cursor cache
     dss-neutrino tui jobs | tui logs JOB [-f]   # the log viewer (cached entries + cursor, filters)
+    dss-neutrino tui app                        # full-screen job browser and log viewer
     dss-neutrino login | logout | whoami        # connection settings kept in a 0600 file
     dss-neutrino step JOB [--lr 1e-6] | save JOB [--path P] | sync JOB | capacity
     dss-neutrino submit job.json|- [--job-id ID] [--dry-run] [--wait]      # a whole create-job body

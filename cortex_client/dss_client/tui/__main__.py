@@ -1,4 +1,5 @@
-"""``python -m dss_client.tui [jobs | logs JOB]``: list jobs, or view / follow one job's log through the cache."""
+"""``python -m dss_client.tui [app | jobs | logs JOB]``: the full-screen browser, or plain output: list jobs, view /
+follow one job's log through the cache."""
 from __future__ import annotations
 
 import argparse
@@ -11,8 +12,10 @@ from .viewer import LogViewer
 def main(argv: Optional[List[str]] = None, client=None, out=None) -> int:
     ap = argparse.ArgumentParser(prog="neutrino-tui")
     ap.add_argument("--url")
+    ap.add_argument("--config")
     ap.add_argument("--no-color", action="store_true")
     sub = ap.add_subparsers(dest="cmd", required=True)
+    sub.add_parser("app")
     j = sub.add_parser("jobs")
     j.add_argument("--filter", default="")
     j.add_argument("--status")
@@ -27,6 +30,9 @@ def main(argv: Optional[List[str]] = None, client=None, out=None) -> int:
     if client is None:
         from ..dss_neutrino_cli import _client
         client = _client(args)
+    if args.cmd == "app":
+        from .app import main as app_main
+        return app_main(client)
     viewer = LogViewer(client, out=out, color=False if args.no_color else None)
     if args.cmd == "jobs":
         viewer.list_jobs(args.filter, args.status)

@@ -32,6 +32,20 @@ def format_log_entry(entry: Any) -> str:
     return f"{head}[{_level(entry)}] {where}{msg}".rstrip()
 
 
+def format_event(ev: Any) -> str:
+    """``<timestamp> KIND [sub-job] detail`` for a scheduling event (placement, zone ready, restarts, ...)."""
+    if not isinstance(ev, dict):
+        return str(ev)
+    ts = ev.get("ts") or ev.get("timestamp") or ev.get("time") or ""
+    kind = ev.get("kind") or ev.get("type") or ev.get("event") or "EVENT"
+    where = ev.get("sub_job_id") or ev.get("source") or ""
+    detail = ev.get("message") or ev.get("reason") or ev.get("detail") or ""
+    if isinstance(detail, (dict, list)):
+        import json
+        detail = json.dumps(detail, sort_keys=True)
+    return " ".join(str(x) for x in (ts, kind, f"[{where}]" if where else "", detail) if x not in ("", None))
+
+
 def wrap_log_line(text: Any, width: int) -> List[str]:
     """Hard wrap at ``width`` columns keeping every character (log lines hold stack traces and JSON: nothing is
     dropped, continuation lines are indented by two spaces)."""
@@ -79,21 +93,31 @@ def sort_jobs(jobs: Any) -> list:
     return sorted(list(jobs or []), key=lambda j: (not is_active_status(j.get("status")), -_created_epoch(j.get("created_at"))))
 
 
+def _submitted(job: Any) -> dict:
+    """The body the job was created with, when the service echoes it inside the record."""
+    body = job.get("body") if isinstance(job, dict) else None
+    return body if isinstance(body, dict) else {}
+
+
 def format_job_config(job: Any) -> str:
     parts = []
-    for sj in (job.get("sub_jobs") or []):
+    subs = job.get("sub_jobs") or _submitted(job).get("sub_jobs") or _submitted(job).get("sub_job_configs") or []
+    for sj in subs:
+        if not isinstance(sj, dict):
+            continue
         cfg = sj.get("config") or sj
-        bits = [str(sj.get("type") or sj.get("job_type") or "?")]
+        bits = [str(sj.get("type") or sj.get("sub_job_type") or sj.get("job_type") or "?")]
         if cfg.get("model_name"):
             bits.append(str(cfg["model_name"]))
-        if cfg.get("num_gpus") or cfg.get("gpus"):
-            bits.append(f"{cfg.get('num_gpus') or cfg.get('gpus')}g")
+        gpus = next((cfg[k] for k in ("num_gpus", "gpus", "num_devices", "n_gpus") if cfg.get(k)), None)
+        if gpus:
+            bits.append(f"{gpus}g")
         parts.append(":".join(bits))
     return " + ".join(parts)
 
 
 def format_job_row(job: Any) -> str:
-    name = job.get("name") or ""
+    name = job.get("name") or _submitted(job).get("name") or ""
     return (f"{str(job.get('job_id') or job.get('id') or '?'):<14} {str(job.get('status') or '?'):<10} "
             f"{format_created_at(job.get('created_at')):<16} {name} {format_job_config(job)}").rstrip()
 
