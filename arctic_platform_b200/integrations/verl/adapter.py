@@ -87,6 +87,20 @@ def prepare_padded_batch(data: Dict[str, Any], pad_token_id: int, drop_position_
     """Dense wire batch from a verl batch that is either already dense (``input_ids [B, S]``, ``responses [B, R]``)
     or jagged (``input_ids`` 1-D values with ``prompt_lens`` / ``response_lens``)."""
     ids = data["input_ids"]
+    if getattr(ids, "is_nested", False) or (ids.dim() == 1 and "prompt_lens" not in data and "prompts" in data):
+        # verl's padding-free layout: nested rows of prompt || response (or their flat values next to dense
+        # prompts / responses + mask)
+        from .nested import nested_to_padded, prompt_response_lengths
+        pl, rl, P, R = prompt_response_lengths(data)
+        out = {"input_ids": nested_to_padded(ids, pl, rl, P, R, pad_token_id)}
+        mask = data.get("attention_mask")
+        if mask is None or getattr(mask, "is_nested", False):
+            vals = ids.values() if getattr(ids, "is_nested", False) else ids
+            mask = nested_to_padded(torch.ones_like(vals), pl, rl, P, R, 0)
+        out["attention_mask"] = mask
+        if not drop_position_ids and "position_ids" in data:
+            out["position_ids"] = nested_to_padded(data["position_ids"], pl, rl, P, R, 0)
+        return out, P, R
     if ids.dim() == 2:
         R = data["responses"].shape[1] if "responses" in data else int(data["max_response_len"])
         out = {"input_ids": ids, "attention_mask": data["attention_mask"]}

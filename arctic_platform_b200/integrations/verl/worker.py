@@ -59,7 +59,12 @@ class ArcticRLActorRolloutRefWorker:
 
     def _throughput(self, data: Dict[str, Any], seconds: float, training: bool) -> Dict[str, float]:
         mask = data.get("attention_mask")
-        tokens = float(mask.sum()) if torch.is_tensor(mask) and mask.dim() == 2 else float(data["input_ids"].numel())
+        ids = data["input_ids"]
+        if getattr(ids, "is_nested", False):
+            ids = ids.values().reshape(1, -1)             # padding-free: every stored token is a real token
+            mask = None
+            data = {**data, "input_ids": ids}
+        tokens = float(mask.sum()) if torch.is_tensor(mask) and not mask.is_nested and mask.dim() == 2 else float(ids.numel())
         out = {"perf/tokens_per_s": tokens / max(seconds, 1e-9), "perf/seconds": seconds}
         if self._model_cfg is not None:
             seq = tokens / max(1, data["input_ids"].shape[0]) if data["input_ids"].dim() == 2 else tokens
@@ -70,16 +75,51 @@ class ArcticRLActorRolloutRefWorker:
                 out["perf/mfu"] = out["perf/tflops"] / (self.peak_tflops * n)
         return out
 
+    @staticmethod
+    def _nested_like_input(data: Dict[str, Any], out: Dict[str, Any]) -> Dict[str, Any]:
+        """A padding-free batch (nested ``input_ids``) gets its per-token outputs back in the same layout: nested rows
+        of ``prompt + response`` positions, each value stored on the token that predicts it.  The grids come back
+        aligned with the response tokens, which is what both training modes of the platform produce."""
+        from .nested import is_nested, make_njt
+        if not is_nested(data.get("input_ids")):
+            return out
+        return {k: (make_njt(data, v, "predict_next") if torch.is_tensor(v) and v.dim() == 2 else v) for k, v in out.items()}
+
     @dispatch("ONE_TO_ALL")
     def compute_log_prob(self, data: Dict[str, Any]) -> Dict[str, Any]:
         t0 = time.perf_counter()
         out = self.wrapper.compute_log_prob(data, calculate_entropy=bool(data.get("calculate_entropy", False)))
+        out = self._nested_like_input(data, out)
         out["metrics"] = self._throughput(data, time.perf_counter() - t0, training=False)
         return out
 
     @dispatch("ONE_TO_ALL")
     def compute_ref_log_prob(self, data: Dict[str, Any]) -> Dict[str, Any]:
-        return self.wrapper.compute_ref_log_prob(data)
+        return self._nested_like_input(data, self.wrapper.compute_ref_log_prob(data))
+
+    # calls verl makes on every worker that mean nothing for a forwarder: the platform owns device placement, the loss
+    # function travels with each call, and engine state lives on the server
+    @dispatch("ONE_TO_ALL")
+    def to(self, device=None, model: bool = True, optimizer: bool = True, grad: bool = True) -> None:
+        return None
+
+    @dispatch("ONE_TO_ALL")
+    def set_loss_fn(self, loss_fn=None) -> None:
+        return None
+
+    @dispatch("ONE_TO_ALL")
+    def reset(self) -> None:
+        return None
+
+    @dispatch("ONE_TO_ALL", blocking=False)
+    def sleep_replicas(self) -> None:
+        return None
+
+    @dispatch("ONE_TO_ALL")
+    def destroy(self) -> None:
+        if self.wrapper is not None:
+            self.wrapper.destroy()
+            self.wrapper = None
 
     @dispatch("ONE_TO_ALL")
     def update_actor(self, data: Dict[str, Any]) -> Dict[str, Any]:

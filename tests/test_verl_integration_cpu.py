@@ -146,12 +146,31 @@ def test_real_update_through_local_client(tmp_path):
     data["old_log_probs"] = lp["old_log_probs"]
     out = worker.update_actor(data)["metrics"]
     assert out["grad_norm"] > 0 and "actor/pg_loss" in out and out["perf/tflops"] > 0 and "perf/mfu" in out
+    # the same batch in verl's padding-free layout: nested rows in, nested rows out, each value on its predicting token
+    lens = mask.sum(1)
+    P = ids.shape[1] - R
+    rows = [ids[b][mask[b].bool()] for b in range(4)]
+    pl = mask[:, :P].sum(1)
+    nested = {"input_ids": torch.nested.nested_tensor(rows, layout=torch.jagged),
+              "prompts": torch.nested.nested_tensor([r[:int(p)] for r, p in zip(rows, pl)], layout=torch.jagged),
+              "responses": torch.nested.nested_tensor([r[int(p):] for r, p in zip(rows, pl)], layout=torch.jagged),
+              "max_prompt_len": P, "max_response_len": R}
+    dense_ref = worker.compute_ref_log_prob(data)["ref_log_prob"]
+    got = worker.compute_ref_log_prob(nested)["ref_log_prob"]
+    assert got.is_nested and torch.equal(got.offsets().diff(), lens)
+    for b, row in enumerate(got.unbind()):
+        p, r = int(pl[b]), int(lens[b] - pl[b])
+        torch.testing.assert_close(row[p - 1:p - 1 + r], dense_ref[b, :r], rtol=1e-4, atol=1e-5)
+        assert float(row[:p - 1].abs().sum()) == 0.0
+    assert worker.compute_log_prob(nested)["metrics"]["perf/tokens_per_s"] > 0
+    assert worker.to("cpu") is None and worker.set_loss_fn(None) is None and worker.reset() is None
     handle = worker.reconnect_handle()
     again = ArcticRLClientWrapper.from_config(cfg, handle={**handle})   # attaches: no new jobs
     assert again.client_config.training_job_id == handle["job_ids"]["training"]
     from arctic_platform_b200.models.config import PRESETS
     assert estimate_flops_per_token(PRESETS["qwen3-4b"], 4096) > 6 * 3.5e9
-    worker.wrapper.destroy()
+    worker.destroy()
+    assert worker.wrapper is None
 
 
 def test_rollout_endpoint_protocol_details():
