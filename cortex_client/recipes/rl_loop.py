@@ -3,18 +3,88 @@ per prompt, scores them with a user reward function, takes one policy update and
 
     python -m cortex_client.recipes.rl_loop --url https://... --model Qwen/Qwen3-8B --prompts prompts.jsonl
 
-``--prompts`` is a jsonl file of ``{"prompt_ids": [...], "answer": ...}`` rows; the default reward is 1 when the decoded
-answer tokens (``answer_ids``) appear in the rollout, else 0 -- replace ``reward_fn`` for real tasks.
+    python -m cortex_client.recipes.rl_loop config=conn.json model_name=Qwen/Qwen3-8B prompts=math.jsonl lora_rank=32 \
+        training_gpus=4 sampling_gpus=4 max_tokens=512 eval_prompts=math500.jsonl eval_every=10 log_path=/tmp/rl
+
+``--prompts`` is a jsonl file of token rows ``{"prompt_ids": [...], "answer_ids": [...]}`` (reward 1 when the answer
+tokens appear in the rollout) or of text rows ``{"prompt": "..." | "messages": [...], "answer": "..."}``, which are
+rendered through the chat template and scored by the boxed-answer math reward on the decoded rollout -- replace
+``reward_fn`` for other tasks.  With ``eval_prompts`` a held-out set is sampled greedily every ``eval_every`` steps and
+its mean reward logged as ``eval/reward_mean``.  The second calling form takes ``key=value`` settings
+(``RLSettings``) and writes ``config.json`` + ``metrics.jsonl`` under ``log_path``.
 Counterpart of cortex-client/recipes/rl_loop.py in the reference."""
 from __future__ import annotations
 
 import argparse
+import dataclasses
 import json
-from typing import Callable, List, Optional, Sequence
+from typing import Any, Callable, List, Optional, Sequence
 
 import torch
 
 from ..dss_client import NeutrinoClient, SubJobConfig
+from .common import MetricsLogger, apply_overrides, client_from_settings, math_reward
+
+
+@dataclasses.dataclass
+class RLSettings:
+    config: Optional[str] = None
+    url: Optional[str] = None
+    model_name: str = "Qwen/Qwen3-8B"
+    prompts: str = "prompts.jsonl"
+    eval_prompts: Optional[str] = None
+    tokenizer: Optional[str] = None
+    steps: int = 50
+    prompts_per_step: int = 16
+    group_size: int = 8
+    max_tokens: int = 512
+    max_seq_len: int = 2048
+    training_gpus: int = 4
+    sampling_gpus: int = 4
+    learning_rate: float = 1e-6
+    lora_rank: int = 0
+    eval_every: int = 10
+    log_path: Optional[str] = None
+    wandb_project: Optional[str] = None
+    wandb_name: Optional[str] = None
+    job_id: Optional[str] = None
+
+
+def read_rows(path: str) -> List[dict]:
+    with open(path, encoding="utf-8") as f:
+        return [json.loads(ln) for ln in f if ln.strip()]
+
+
+def prepare_rows(rows: List[dict], tokenizer: Any = None) -> List[dict]:
+    """Text rows get ``prompt_ids`` (chat template + generation prompt); token rows pass through."""
+    out = []
+    for r in rows:
+        if "prompt_ids" in r:
+            out.append(r)
+            continue
+        if tokenizer is None:
+            raise ValueError("text prompts need a tokenizer")
+        msgs = r.get("messages") or [{"role": "user", "content": r["prompt"]}]
+        ids = tokenizer.apply_chat_template(msgs, tokenize=True, add_generation_prompt=True)
+        out.append({**r, "prompt_ids": list(ids["input_ids"] if isinstance(ids, dict) else ids)})
+    return out
+
+
+def make_reward(tokenizer: Any = None) -> Callable[[Sequence[int], dict], float]:
+    """Token rows: the answer tokens appear in the rollout.  Text rows: boxed answer of the decoded rollout."""
+    def reward(rollout_ids: Sequence[int], row: dict) -> float:
+        if "answer" in row and tokenizer is not None:
+            return math_reward(tokenizer.decode(list(rollout_ids), skip_special_tokens=True), str(row["answer"]))
+        return contains_answer(rollout_ids, row)
+    return reward
+
+
+def evaluate(client: NeutrinoClient, job_id: str, rows: List[dict], reward_fn, max_tokens: int) -> dict:
+    """Greedy, one sample per held-out prompt."""
+    prompts = [list(r["prompt_ids"]) for r in rows]
+    outs = client.generate(job_id, prompts, {"n": 1, "max_tokens": max_tokens, "temperature": 0.0})["results"]
+    scores = [reward_fn(o["token_ids"], rows[o["prompt_index"]]) for o in outs]
+    return {"eval/reward_mean": sum(scores) / max(1, len(scores)), "eval/prompts": len(scores)}
 
 
 def contains_answer(rollout_ids: Sequence[int], row: dict) -> float:
@@ -43,11 +113,15 @@ def build_batch(prompts: List[List[int]], outs: List[dict], max_tokens: int, rew
 
 def run(client: NeutrinoClient, model: str, rows: List[dict], steps: int = 3, prompts_per_step: int = 4, n: int = 4,
         max_tokens: int = 64, gpus: int = 1, lr: float = 1e-6, reward_fn: Callable[[Sequence[int], dict], float] = contains_answer,
-        job_id: Optional[str] = None, log=print) -> List[dict]:
+        job_id: Optional[str] = None, log=print, sampling_gpus: Optional[int] = None, extra: Optional[dict] = None,
+        max_seq_len: Optional[int] = None, eval_rows: Optional[List[dict]] = None, eval_every: int = 0,
+        logger: Optional[MetricsLogger] = None) -> List[dict]:
     own = job_id is None
     if own:
-        job = client.create_job([SubJobConfig.training_job(model, num_gpus=gpus, learning_rate=lr),
-                                 SubJobConfig.sampling_job(model, num_gpus=gpus)])
+        tkw = {"max_seq_len": max_seq_len} if max_seq_len else {}
+        skw = {"max_model_len": max_seq_len} if max_seq_len else {}
+        job = client.create_job([SubJobConfig.training_job(model, num_gpus=gpus, learning_rate=lr, extra=dict(extra or {}), **tkw),
+                                 SubJobConfig.sampling_job(model, num_gpus=sampling_gpus or gpus, **skw)])
         job_id = job["job_id"]
         client.wait_for_job(job_id)
     history = []
@@ -65,17 +139,52 @@ def run(client: NeutrinoClient, model: str, rows: List[dict], steps: int = 3, pr
             out = client.forward_backward(job_id, batch, meta, {"loss_fn": "verl_grpo"})
             st = client.step(job_id)
             client.weight_sync(job_id)
+            solved = (rewards.view(-1, n) > 0).any(1).float().mean()
             rec = {"step": step, "reward_mean": float(rewards.mean()), "loss": out.get("avg_loss"),
-                   "grad_norm": (st.get("metrics") or {}).get("grad_norm")}
+                   "grad_norm": (st.get("metrics") or {}).get("grad_norm"), "prompts_solved": float(solved),
+                   "response_tokens_mean": sum(len(o["token_ids"]) for o in outs) / max(1, len(outs))}
+            if eval_rows and eval_every and (step + 1) % eval_every == 0:
+                rec.update(evaluate(client, job_id, eval_rows, reward_fn, max_tokens))     # on the weights just synced
             history.append(rec)
-            log(json.dumps(rec))
+            if logger is not None:
+                logger.log(step, {k: v for k, v in rec.items() if k != "step"})
+            else:
+                log(json.dumps(rec))
     finally:
         if own:
             client.cancel_job(job_id)
     return history
 
 
+def run_settings(st: RLSettings, client: Optional[NeutrinoClient] = None, tokenizer: Any = None, echo=print) -> List[dict]:
+    client = client or client_from_settings(st.config, st.url)
+    rows, eval_rows = read_rows(st.prompts), (read_rows(st.eval_prompts) if st.eval_prompts else None)
+    needs_text = any("prompt_ids" not in r or "answer" in r for r in rows + (eval_rows or []))
+    if tokenizer is None and needs_text:
+        from transformers import AutoTokenizer
+        tokenizer = AutoTokenizer.from_pretrained(st.tokenizer or st.model_name)
+    rows = prepare_rows(rows, tokenizer)
+    eval_rows = prepare_rows(eval_rows, tokenizer) if eval_rows else None
+    too_long = [i for i, r in enumerate(rows) if len(r["prompt_ids"]) + st.max_tokens > st.max_seq_len]
+    if too_long:
+        raise ValueError(f"{len(too_long)} prompt(s) do not fit max_seq_len={st.max_seq_len} with max_tokens={st.max_tokens} "
+                         f"(first: row {too_long[0]})")
+    logger = MetricsLogger(st.log_path, dataclasses.asdict(st), st.wandb_project, st.wandb_name, echo=echo)
+    try:
+        return run(client, st.model_name, rows, st.steps, st.prompts_per_step, st.group_size, st.max_tokens,
+                   st.training_gpus, st.learning_rate, make_reward(tokenizer), st.job_id,
+                   sampling_gpus=st.sampling_gpus, extra={"lora_rank": st.lora_rank} if st.lora_rank > 0 else None,
+                   max_seq_len=st.max_seq_len, eval_rows=eval_rows, eval_every=st.eval_every, logger=logger)
+    finally:
+        logger.close()
+
+
 def main(argv=None, client: Optional[NeutrinoClient] = None) -> int:
+    import sys
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and all("=" in a and not a.startswith("-") for a in argv):       # key=value settings
+        run_settings(apply_overrides(RLSettings(), argv), client)
+        return 0
     ap = argparse.ArgumentParser(description="GRPO loop against the hosted training service")
     ap.add_argument("--url")
     ap.add_argument("--model", required=True)
