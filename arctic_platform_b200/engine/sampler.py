@@ -998,6 +998,10 @@ class SamplerEngine:
                 pv[i, :len(sq.private_pages)] = sq.private_pages
                 sh[i] = (len(sq.header_pages) + len(sq.shared_pages)) * PAGE
                 plen[i] = sq.prompt_len - sh[i] + 1
+            from ..utils import checked
+            if checked.enabled():                   # host arrays: no synchronisation involved
+                checked.check_page_table("page_table", pt, plen + sh - 1, self.num_pages, PAGE)
+                checked.check_page_table("priv_table", pv, plen - 1, self.num_pages, PAGE)
             self.d_page_table[st] = to_device(torch.from_numpy(pt), self.device)
             self.d_priv_table[st] = to_device(torch.from_numpy(pv), self.device)
             self.d_priv_len[st] = to_device(torch.from_numpy(plen), self.device)

@@ -164,6 +164,16 @@ class MoEPlan:
         _lib.check(fn(_lib.ptr(counts), E, H, I, arr(*[m.data_ptr() for m in self.maps]),
                       arr(*[x.data_ptr() for x in self.exts]), (c.c_int * 4)(*self.max_tiles), _lib.ptr(self.seg_start),
                       _lib.ptr(self.n_tiles), _lib.stream_ptr()), "apb_moe_plan")
+        from ..utils import checked
+        if checked.active_for(counts):
+            seg = self.seg_start.to(torch.int64)
+            checked.check_cu_seqlens(seg, name="moe_plan.seg_start")
+            checked.check_range("moe_plan.seg_start", seg, 0, self.rows_cap + 1)
+            if bool((seg % 64 != 0).any()):
+                raise checked.TableError("moe_plan.seg_start: an expert's rows do not start at a multiple of 64")
+            cap = torch.tensor(self.max_tiles, dtype=torch.int64, device=self.n_tiles.device)
+            if bool((self.n_tiles.to(torch.int64) > cap).any()):
+                raise checked.TableError(f"moe_plan: tile counts {self.n_tiles.tolist()} exceed the tables {self.max_tiles}")
 
     def padded_rows(self, sorted_expert: torch.Tensor) -> torch.Tensor:
         """Padded row of every pair of an expert-sorted list (``sorted_expert [P]`` int64, ascending)."""

@@ -48,6 +48,9 @@ class AttnLayout:
     @staticmethod
     def from_cu_seqlens(cu_seqlens) -> "AttnLayout":
         cu = np.asarray(cu_seqlens, dtype=np.int64)
+        from ..utils import checked
+        if checked.enabled():
+            checked.check_cu_seqlens(cu)
         starts, lens = cu[:-1], cu[1:] - cu[:-1]
         segs = np.stack([starts, lens, np.zeros_like(starts), np.zeros_like(starts), starts, lens], 1)
         return AttnLayout(segs[lens > 0], int(cu[-1]))

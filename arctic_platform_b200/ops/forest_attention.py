@@ -111,6 +111,9 @@ def build_forest_tables(nodes: Sequence[ForestNode], num_slots: int, max_pages: 
                         n_levels: Optional[int] = None) -> ForestTables:
     from ..utils.transfer_stats import to_device
     qs, qc, pg, ln, lv, mask, G, nl, shared, covered = plan_forest(nodes, num_slots, max_pages, max_rows, n_levels)
+    from ..utils import checked
+    if checked.enabled():                           # host arrays: no synchronisation involved
+        checked.check_forest(qs, qc, pg, ln, lv, num_slots, np.iinfo(np.int32).max, nl, max_rows, PAGE)
     t = lambda a: to_device(torch.from_numpy(a), device)
     return ForestTables(t(qs), t(qc), t(pg), t(ln), t(lv), t(mask), G, nl, shared, covered)
 
@@ -137,6 +140,13 @@ def forest_decode_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch
     G = forest.n_nodes if n_nodes is None else int(n_nodes)
     if out is None:
         out = torch.empty((B, Hq, D), device=q.device, dtype=torch.bfloat16)
+    from ..utils import checked
+    if checked.active_for(q):
+        if G > 0:
+            checked.check_forest(forest.q_start[:G], forest.q_count[:G], forest.pages[:G], forest.kv_len[:G],
+                                 forest.level[:G], B, num_pages, nl, 128, PAGE)
+        checked.check_range("priv_start", priv_start, 0, max(1, B), priv_active)
+        checked.check_page_table("priv_table", priv_table, priv_len, num_pages, PAGE, priv_active)
     if G > 0:
         o_lv = (ctypes.c_void_p * 3)(*[part_o[min(i, nl - 1)].data_ptr() for i in range(3)])
         ml_lv = (ctypes.c_void_p * 3)(*[part_ml[min(i, nl - 1)].data_ptr() for i in range(3)])

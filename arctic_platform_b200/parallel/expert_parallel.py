@@ -239,6 +239,10 @@ class ExpertParallel:
                                     moe.wgu.shape[1] // 2, self.overflow)
             moe.last_tokens_per_expert = r.recv_counts
             r.materialize = torch.is_grad_enabled()
+            from ..utils import checked
+            if checked.active_for(x):
+                checked.check_routing(r.dst_rank, r.dst_row, self.world, self.max_recv_rows, "expert_parallel")
+                checked.check_range("expert_parallel.src_tok", r.src_tok, 0, max(1, T))
             x_recv = _DispatchFn.apply(x, self, r)
             if not torch.is_grad_enabled():
                 y_pairs = self._ffn_with_fused_combine(moe, x_recv, r)

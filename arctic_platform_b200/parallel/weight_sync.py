@@ -303,6 +303,15 @@ def build_sync_plan(layout: Dict[str, Any], model, full_cfg=None, tp_rank: int =
         if rows_seen != expect_rows:
             raise ValueError(f"{name}: slices cover {rows_seen} rows, the sampler's tensor has {expect_rows}")
     n = len(segs)
+    from ..utils import checked
+    if checked.enabled():                       # host records: extents of every slice inside source and destination
+        for i, sg in enumerate(segs):
+            last_src = sg.src_elem + (sg.row0 + sg.rows - 1) * sg.src_ld + sg.col0 + sg.cols
+            if sg.src_elem < 0 or last_src > layout["total"]:
+                raise checked.TableError(f"sync segment {i}: source elements up to {last_src} of {layout['total']}")
+        live = [sg for sg in segs if sg.dst_elem >= 0]
+        checked.check_copy_table("sync plan", [0] * len(live), [sg.dst_elem for sg in live],
+                                 [(sg.rows - 1) * sg.dst_ld + sg.cols for sg in live], 1 << 62, flat.numel())
     if _fns()["seg_bytes"]() != ctypes.sizeof(_SyncSeg):
         raise RuntimeError("sync table record layout differs between the library and its Python mirror")
     arr = (_SyncSeg * n)(*segs)
