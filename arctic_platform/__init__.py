@@ -23,6 +23,19 @@ _MOVED = {
     "rl.zorro_train.zorro_train": "rl.zorro_train.layout",
     "model.loader": "models.factory",
     "model.patch": "models.factory",
+    # the reference's own back-compat shims under rl/ (its code moved to common/)
+    "rl.server": "common.server",
+    "rl.ray_cluster": "common.ray_cluster",
+    "rl.ray_server": "rl.ray_client",
+    "common.ray_server": "rl.ray_client",
+    "rl.deepspeed_worker": "engine.worker",
+    "rl.utils": "common.utils",
+    "rl.utils.batch": "common.utils.batch",
+    "rl.utils.cuda_ipc": "common.utils.cuda_ipc",
+    "rl.utils.ray_pg": "common.utils.ray_pg",
+    "rl.utils.server_models": "common.utils.server_models",
+    "rl.utils.debug": "utils.debug",
+    "rl.utils.record_replay": "utils.record_replay",
 }
 
 

@@ -66,3 +66,7 @@ class ArcticSFTClient:
 
     def __exit__(self, *exc) -> None:
         self.shutdown()
+
+
+def create_arctic_sft_client(config: ArcticSFTClientConfig, server_state: Any = None) -> ArcticSFTClient:
+    return ArcticSFTClient(config, server_state)

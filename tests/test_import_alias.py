@@ -30,3 +30,69 @@ def test_reference_import_paths_resolve_to_the_same_modules():
                                                      sampling_gpus=1, log_prob_gpus=0, vllm_config={"max_model_len": 32}))
     assert len(c.call("generate", [[3, 4]], {"n": 1, "max_tokens": 2})) == 1
     c.call("shutdown")
+
+
+def test_reference_shim_paths_and_ipc_merge():
+    # the reference keeps back-compat shims under rl/ for code that moved to common/: both spellings work here too
+    from arctic_platform.rl.server import ArcticRLServerCore
+    from arctic_platform_b200.common.server import ArcticRLServerCore as Real
+    assert ArcticRLServerCore is Real
+    assert importlib.import_module("arctic_platform.rl.ray_cluster") is importlib.import_module("arctic_platform_b200.common.ray_cluster")
+    assert importlib.import_module("arctic_platform.rl.deepspeed_worker") is importlib.import_module("arctic_platform_b200.engine.worker")
+    for leaf, real in (("batch", "common.utils.batch"), ("ray_pg", "common.utils.ray_pg"), ("server_models", "common.utils.server_models"),
+                       ("debug", "utils.debug"), ("record_replay", "utils.record_replay"), ("cuda_ipc", "common.utils.cuda_ipc")):
+        assert importlib.import_module(f"arctic_platform.rl.utils.{leaf}") is importlib.import_module(f"arctic_platform_b200.{real}")
+    from arctic_platform.common.ray_server import create_arctic_rl_ray_server_state
+    assert callable(create_arctic_rl_ray_server_state)
+
+    from arctic_platform.common.utils.cuda_ipc import merge_cuda_ipc_payloads, merge_ipc_sources
+    layout = {"total": 100, "world": 2, "zero3": None, "params": {"a": (0, 10, (10,))}}
+    srcs = [{"handle": b"h0", "offset": 0, "layout": layout, "device": 0}, {"handle": b"h1", "offset": 0, "layout": layout, "device": 1}]
+    merged = merge_ipc_sources(srcs)
+    assert [s["device"] for s in merged] == [0, 1] and merged[0] is not srcs[0]
+    assert merge_ipc_sources([srcs[0], None]) is None and merge_ipc_sources([]) is None
+    assert merge_cuda_ipc_payloads(srcs) == {"sources": merged, "num_ranks": 2, "num_params": 1}
+    assert merge_cuda_ipc_payloads([None, None])["sources"] is None
+    with pytest.raises(ValueError, match="same buffer"):
+        merge_ipc_sources([srcs[0], dict(srcs[0])])
+    with pytest.raises(ValueError, match="another parameter layout"):
+        merge_ipc_sources([srcs[0], {**srcs[1], "layout": {**layout, "total": 99}}])
+    with pytest.raises(ValueError, match="2 trainer ranks"):
+        merge_ipc_sources([srcs[0]])
+    with pytest.raises(ValueError, match="offset"):
+        merge_ipc_sources([{"handle": b"x", "layout": layout}, srcs[1]])
+
+
+def test_package_level_names_of_the_reference_resolve(tmp_path):
+    import arctic_platform.rl as rl
+    import arctic_platform.rl.processors as proc
+    import arctic_platform.sft as sft
+    from arctic_platform_b200.common import registry
+    for name in ("create_arctic_rl_client", "ArcticRLClientConfig", "WeightSyncConfig", "WeightSyncCoordinator", "run_pipeline",
+                 "run_sft_pipeline", "register_loss_fn", "register_post_processor", "grpo_loss", "sft_loss", "pack_sequences",
+                 "unpack_sequences"):
+        assert getattr(rl, name) is not None, name
+    assert rl.register_loss_fn is registry.register_loss_fn and rl.run_sft_pipeline is sft.run_sft_pipeline
+    for name in ("POST_PROCESSORS", "LOSS_FNS", "register_post_processor", "register_loss_fn", "run_pipeline", "pack_sequences",
+                 "unpack_sequences", "pad_packed_for_model", "DEFAULT_MAX_TOKENS_PER_MB", "MicroBatchSpec",
+                 "split_padded_tensor_dict_into_mb_list", "DistributedStatsTracker", "ReduceType", "DEFAULT_TRACKER",
+                 "denominator", "stat", "scalar", "scope", "export", "masked_normalization", "agg_loss", "kl_penalty",
+                 "ppo_actor_loss_fn", "sapo_loss_fn", "grpo_loss", "verl_grpo_loss", "sft_loss", "sft_ce_loss"):
+        assert getattr(proc, name) is not None, name
+    assert {"verl_grpo", "grpo", "sft", "sft_ce"} <= set(proc.LOSS_FNS) and proc.LOSS_FNS is registry.LOSS_FNS
+    assert "compute_entropy_and_logprobs" in proc.POST_PROCESSORS
+    with pytest.raises(AttributeError):
+        proc.no_such_name
+    with pytest.raises(AttributeError):
+        rl.no_such_name
+    for name in ("ArcticSFTClient", "ArcticSFTClientConfig", "LOGIT_LOSS_FNS", "SFT_LOSS_FNS", "create_arctic_sft_client",
+                 "run_sft_pipeline", "sft_ce_loss", "sft_loss"):
+        assert getattr(sft, name) is not None, name
+    c = sft.create_arctic_sft_client(sft.ArcticSFTClientConfig(comm_protocol="local", model_name="qwen3-tiny", training_gpus=1,
+                                                               checkpoint_path=str(tmp_path)))
+    try:
+        import torch
+        out = c.fwd_bwd({"input_ids": torch.randint(1, 100, (2, 8)), "attention_mask": torch.ones(2, 8, dtype=torch.long)})
+        assert "avg_loss" in out
+    finally:
+        c.shutdown()
