@@ -62,7 +62,8 @@ def _generate_request(jobs, prompts, sampling_params=None, routing_key=None, str
 
 
 def _log_probs_request(jobs, prompts, completions=None, top_k=1) -> Request:
-    jt = "log_prob" if jobs.log_prob is not None else "training"
+    # the scorer: the log-prob job, else the trainer, else (a sampling-only client) the sampler's own replicas
+    jt = next((k for k in ("log_prob", "training", "sampling") if getattr(jobs, k, None) is not None), "log_prob")
     return Request("log-probs", jobs.require(jt), {"prompts": prompts, "completions": completions or [], "top_k": top_k})
 
 

@@ -177,7 +177,8 @@ class ArcticRLHttpClient:
         return self._octet("/generate", self._need("sampling"), {"prompts": prompts, "sampling_params": sampling_params})["results"]
 
     async def log_probs(self, prompts, completions, top_k: int = 1):
-        kind = "log_prob" if self.job_ids.get("log_prob") is not None else "training"
+        # the scorer: the log-prob job, else the trainer, else (a sampling-only client) the sampler's own replicas
+        kind = next((k for k in ("log_prob", "training", "sampling") if self.job_ids.get(k) is not None), "log_prob")
         return self._json("/log-probs", {"job_id": self._need(kind)},
                           {"prompts": prompts, "completions": completions, "top_k": top_k})
 

@@ -126,7 +126,8 @@ class ArcticRLLocalClient:
         return self.server.generate(self._need("sampling"), prompts, sampling_params)["results"]
 
     async def log_probs(self, prompts, completions, top_k: int = 1) -> Dict[str, Any]:
-        kind = "log_prob" if self.job_ids.get("log_prob") is not None else "training"
+        # the scorer: the log-prob job, else the trainer, else (a sampling-only client) the sampler's own replicas
+        kind = next((k for k in ("log_prob", "training", "sampling") if self.job_ids.get(k) is not None), "log_prob")
         return self.server.log_probs(self._need(kind), prompts, completions, top_k)
 
     async def sleep_inference(self, level: int = 1) -> Dict[str, Any]:

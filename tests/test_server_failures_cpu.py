@@ -186,11 +186,11 @@ def test_watchdog_marks_a_job_failed_when_a_worker_process_is_gone():
         assert job.status == "RUNNING"
         job.workers[0]._proc.terminate()                         # the exact child created above
         job.workers[0]._proc.join(10)
-        deadline = time.time() + 60.0                            # generous: a loaded CI box schedules the watchdog late
+        deadline = time.time() + 180.0                           # generous: a loaded CI box schedules the watchdog late
         while job.status != "FAILED" and time.time() < deadline:
             time.sleep(0.05)
         assert job.status == "FAILED" and "do not answer" in job.info["failure"]
-        job.workers[1]._proc.join(60)                            # teardown follows the state change
+        job.workers[1]._proc.join(180)                           # teardown follows the state change
         assert not job.workers[1]._proc.is_alive()               # the peer was stopped with it
     finally:
         core.stop_worker_watchdog()
