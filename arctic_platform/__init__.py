@@ -21,8 +21,51 @@ _MOVED = {
     "common.utils.sft_profile": "utils.sft_profile",
     "common.utils.record_replay": "utils.record_replay",
     "rl.zorro_train.zorro_train": "rl.zorro_train.layout",
+    "model": "models",
+    "model.config": "models.factory",
+    "model.factory": "models.factory",
     "model.loader": "models.factory",
     "model.patch": "models.factory",
+    "model.loaders": "models",
+    "model.loaders.huggingface": "models.hf_io",
+    "model.loaders.qwen3_5_moe": "models.loader_options",
+    "model.patches": "models",
+    "model.patches.liger": "ops.norm",
+    "model.patches.zorro_train": "rl.zorro_train.layout",
+    "model.patches.gradient_checkpointing": "models.decoder",
+    "model.implementations": "models",
+    "model.implementations.qwen35": "models",
+    "model.implementations.qwen35.config": "models.config",
+    "model.implementations.qwen35.config_validation": "models.config",
+    "model.implementations.qwen35.conversion_cache": "models.conversion_cache",
+    "model.implementations.qwen35.deepspeed_integration": "engine.trainer",
+    "model.implementations.qwen35.distributed": "parallel",
+    "model.implementations.qwen35.distributed.deepep": "parallel.expert_parallel",
+    "model.implementations.qwen35.distributed.expert_parallel": "parallel.expert_parallel",
+    "model.implementations.qwen35.gpu": "utils",
+    "model.implementations.qwen35.gpu.action_masks": "utils.action_masks",
+    "model.implementations.qwen35.gpu.activation_offload": "utils.activation_offload",
+    "model.implementations.qwen35.gpu.debug": "utils.debug",
+    "model.implementations.qwen35.gpu.router_replay_recompute": "models.moe",
+    "model.implementations.qwen35.gpu.tiled_mlp": "models.tiled_mlp",
+    "model.implementations.qwen35.logging_utils": "utils.debug",
+    "model.implementations.qwen35.model_builder": "models.factory",
+    "model.implementations.qwen35.parallel_dims": "parallel.parallel_dims",
+    "model.implementations.qwen35.sequence_parallel": "parallel.ulysses",
+    "model.implementations.qwen35.vlm": "models.vlm",
+    "model.implementations.qwen35.weights": "models.hf_io",
+    "model.implementations.qwen35.world": "parallel.world",
+    "rl.processors.grpo": "rl.processors.losses",
+    "rl.processors.sft": "sft.processor",
+    "rl.processors.verl_grpo": "rl.processors.losses",
+    "rl.zorro_train.module_patcher": "rl.zorro_train.layout",
+    "rl.zorro_train.qwen_attention_patcher": "rl.zorro_train.layout",
+    "rl.zorro_train.qwen_model_patcher": "rl.zorro_train.layout",
+    "client.sft_client": "sft.client",
+    "client.sft_config": "sft.config",
+    "client.transports.onprem_http": "client.transports.onprem",
+    "client.transports.onprem_ray": "client.transports.ray_actor",
+    "common.utils.tiled_logits": "ops.logprob",
     # the reference's own back-compat shims under rl/ (its code moved to common/)
     "rl.server": "common.server",
     "rl.ray_cluster": "common.ray_cluster",

@@ -124,6 +124,30 @@ def register_loader(name: str, matches: Optional[Callable[[LoaderContext], bool]
     return deco
 
 
+def is_registered_loader(name: str) -> bool:
+    return name in _LOADERS
+
+
+def select_loader(ctx: LoaderContext) -> Callable:
+    """The loader function ``build_model`` would call for this context (explicit ``spec.loader``, else the one
+    loader whose ``matches`` accepts the context, else the default)."""
+    return _LOADERS[resolve_loader_name(ctx)][0]
+
+
+# user patches: callables ``patch(model, ctx)`` that run after the built-in switches, in registration order, when the
+# spec asks for them (``ModelSpec.loader_options["patches"] = [name, ...]``) -- arctic_platform/model/patch.py:40-49
+_USER_PATCHES: Dict[str, Callable] = {}
+
+
+def register_patch(name: str):
+    def deco(fn):
+        if name in PATCH_ORDER or name in _USER_PATCHES:
+            raise ValueError(f"patch {name!r} is already registered")
+        _USER_PATCHES[name] = fn
+        return fn
+    return deco
+
+
 def get_loader_options_model(name: str):
     """The options schema registered for a loader, or ``None``."""
     if name not in _LOADERS:
@@ -223,6 +247,13 @@ def build_model(spec: ModelSpec, parallel_groups: Optional[dict] = None, device=
     opts = schema.from_dict(spec.loader_options) if schema is not None else None     # raises on unknown / bad options
     model = fn(ctx, device, seed)
     applied = apply_patches(model, spec.patches)
+    for pname in getattr(opts, "patches", None) or []:
+        if pname not in _USER_PATCHES:
+            raise KeyError(f"unknown patch {pname!r} (registered: {sorted(_USER_PATCHES)})")
+        if pname not in applied:
+            _USER_PATCHES[pname](model, ctx)
+            applied.append(pname)
+            model._applied_patches = applied
     ac = getattr(opts, "ac_config", None)
     if ac is not None:
         model.set_activation_checkpointing(ac.mode, ac.targets, ac.freq)

@@ -98,8 +98,11 @@ class LoaderOptions:
     weight_conversion_cache_dir: Optional[str] = None
     ac_config: Any = None
     debug: Any = None
+    patches: Optional[list] = None         # names registered with ``models.factory.register_patch``, applied in this order
 
     def __post_init__(self) -> None:
+        if self.patches is not None and not (isinstance(self.patches, (list, tuple)) and all(isinstance(p, str) for p in self.patches)):
+            raise ValueError("loader_options.patches: expected a list of patch names")
         _literal(self.ep_comm_backend, ("deepep",), "loader_options.ep_comm_backend")
         _literal(self.optimization_dtype, ("bfloat16", "float32"), "loader_options.optimization_dtype")
         _literal(self.reduce_dtype, ("bfloat16", "float32"), "loader_options.reduce_dtype")

@@ -96,3 +96,35 @@ def test_package_level_names_of_the_reference_resolve(tmp_path):
         assert "avg_loss" in out
     finally:
         c.shutdown()
+
+
+def test_model_package_paths_and_patch_registry():
+    import arctic_platform
+    for path in arctic_platform._MOVED:                                   # every declared move resolves
+        assert importlib.import_module(f"arctic_platform.{path}") is not None, path
+    from arctic_platform.model import (LoadedModel, LoaderContext, ModelSpec, Patches, build_model, register_patch,
+                                       select_loader)
+    from arctic_platform.model.loader import is_registered_loader
+    from arctic_platform.model.implementations.qwen35.parallel_dims import ParallelDims
+    from arctic_platform_b200.parallel.parallel_dims import ParallelDims as Real
+    assert ParallelDims is Real and is_registered_loader("dense") and not is_registered_loader("nope")
+    seen = []
+
+    @register_patch("count_blocks_for_test")
+    def _count(model, ctx):
+        seen.append((len(model.blocks), ctx.spec.model_path_or_name))
+
+    with pytest.raises(ValueError):
+        register_patch("count_blocks_for_test")(lambda m, c: None)
+    with pytest.raises(ValueError):
+        register_patch("liger")(lambda m, c: None)
+    spec = ModelSpec("qwen3-tiny", patches=Patches(gradient_checkpointing=True),
+                     loader_options={"patches": ["count_blocks_for_test"]})
+    assert callable(select_loader(LoaderContext(spec)))
+    loaded = build_model(spec)
+    assert isinstance(loaded, LoadedModel) and seen and seen[0][1] == "qwen3-tiny"
+    assert loaded.applied_patches[-1] == "count_blocks_for_test" and "gradient_checkpointing" in loaded.applied_patches
+    with pytest.raises(KeyError, match="unknown patch"):
+        build_model(ModelSpec("qwen3-tiny", loader_options={"patches": ["missing"]}))
+    with pytest.raises(ValueError, match="patches"):
+        build_model(ModelSpec("qwen3-tiny", loader_options={"patches": "count_blocks_for_test"}))
