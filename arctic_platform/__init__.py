@@ -58,6 +58,9 @@ _MOVED = {
     "rl.processors.grpo": "rl.processors.losses",
     "rl.processors.sft": "sft.processor",
     "rl.processors.verl_grpo": "rl.processors.losses",
+    "rl.zorro_train.demo": "rl.zorro_train.harness",
+    "rl.zorro_train.tests": "rl.zorro_train.harness",
+    "rl.zorro_train.test_perf": "rl.zorro_train.harness",
     "rl.zorro_train.module_patcher": "rl.zorro_train.layout",
     "rl.zorro_train.qwen_attention_patcher": "rl.zorro_train.layout",
     "rl.zorro_train.qwen_model_patcher": "rl.zorro_train.layout",
