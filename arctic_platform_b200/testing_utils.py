@@ -245,3 +245,174 @@ def execute_subprocess_async(cmd, env=None, stdin=None, timeout: float = 180, qu
     if not result.stdout and not result.stderr:
         raise RuntimeError(f"'{' '.join(cmd)}' produced no output.")
     return result
+
+
+# ------------------------------------------------------------------------------------------------- environment flags
+def parse_flag_from_env(key: str, default: bool = False) -> bool:
+    """``yes/true/1/on`` and ``no/false/0/off`` (any case); anything else is an error, not a silent default."""
+    raw = os.environ.get(key)
+    if raw is None:
+        return default
+    word = raw.strip().lower()
+    if word in ("1", "true", "yes", "y", "on"):
+        return True
+    if word in ("0", "false", "no", "n", "off", ""):
+        return False
+    raise ValueError(f"{key}={raw!r}: expected yes or no")
+
+
+def parse_int_from_env(key: str, default: Optional[int] = None) -> Optional[int]:
+    raw = os.environ.get(key)
+    if raw is None:
+        return default
+    try:
+        return int(raw)
+    except ValueError as exc:
+        raise ValueError(f"{key}={raw!r}: expected an integer") from exc
+
+
+def is_torch_available() -> bool:
+    return True
+
+
+def is_deepspeed_available() -> bool:
+    return importlib.util.find_spec("deepspeed") is not None
+
+
+def get_gpu_count() -> int:
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+# ------------------------------------------------------------------------------------------------- more decorators
+def require_torch(fn):
+    return fn
+
+
+def require_torch_no_gpus(fn):
+    return _skip_unless(get_gpu_count() == 0, "test requires a machine without GPUs")(fn)
+
+
+def require_torch_non_multi_gpu(fn):
+    return _skip_unless(get_gpu_count() < 2, "test requires zero or one GPU")(fn)
+
+
+def require_torch_up_to_2_gpus(fn):
+    return _skip_unless(get_gpu_count() < 3, "test requires at most two GPUs")(fn)
+
+
+require_deepspeed = require_module("deepspeed")
+require_flash_attn = require_module("flash_attn")
+require_flash_attn_3 = require_module("flash_attn_interface")
+
+
+# ------------------------------------------------------------------------------------------------- paths and files
+def get_tests_dir(append_path: Optional[str] = None) -> str:
+    """The ``tests`` directory of the checkout this module was imported from (``append_path`` joined onto it)."""
+    root = Path(__file__).resolve().parents[1] / "tests"
+    return str(root / append_path) if append_path else str(root)
+
+
+@contextlib.contextmanager
+def ExtendSysPath(path) -> Iterator[None]:
+    """``sys.path`` with ``path`` in front for the duration of the block."""
+    path = os.fspath(path)
+    sys.path.insert(0, path)
+    try:
+        yield
+    finally:
+        try:
+            sys.path.remove(path)
+        except ValueError:
+            pass
+
+
+def write_file(file, content: str) -> None:
+    Path(file).parent.mkdir(parents=True, exist_ok=True)
+    Path(file).write_text(content, encoding="utf-8")
+
+
+def read_json_file(file):
+    import json
+    return json.loads(Path(file).read_text(encoding="utf-8"))
+
+
+def replace_str_in_file(file, text_to_search: str, replacement_text: str) -> int:
+    """Replaces every occurrence in place; returns how many there were."""
+    p = Path(file)
+    text = p.read_text(encoding="utf-8")
+    n = text.count(text_to_search)
+    if n:
+        p.write_text(text.replace(text_to_search, replacement_text), encoding="utf-8")
+    return n
+
+
+class CaptureLogger:
+    """Collects what a ``logging`` logger emits inside the block: ``with CaptureLogger(log) as cl: ...; cl.out``."""
+
+    def __init__(self, logger):
+        import logging
+        self.logger = logger
+        self.io = io.StringIO()
+        self.handler = logging.StreamHandler(self.io)
+        self.out = ""
+
+    def __enter__(self):
+        self.logger.addHandler(self.handler)
+        return self
+
+    def __exit__(self, *exc):
+        self.logger.removeHandler(self.handler)
+        self.out = self.io.getvalue()
+
+    def __repr__(self):
+        return f"captured: {self.out}\n"
+
+
+# ------------------------------------------------------------------------------------------------- pytest-xdist
+def get_xdist_worker_id() -> int:
+    """0 outside pytest-xdist, else the numeric part of ``gw<N>``."""
+    worker = os.environ.get("PYTEST_XDIST_WORKER", "gw0")
+    digits = "".join(c for c in worker if c.isdigit())
+    return int(digits) if digits else 0
+
+
+def get_xdist_worker_count() -> int:
+    return parse_int_from_env("PYTEST_XDIST_WORKER_COUNT", 1) or 1
+
+
+# ------------------------------------------------------------------------------------------------- pytest reports
+def pytest_addoption_shared(parser) -> None:
+    """``--make-reports=<id>``: write the terminal report's sections to ``reports/<id>/*.txt`` (call from a
+    ``conftest.py``'s ``pytest_addoption``)."""
+    try:
+        parser.addoption("--make-reports", action="store", default=False,
+                         help="write report files under reports/<id>/ (durations, failures, summary)")
+    except ValueError:
+        pass                                    # already added by another conftest
+
+
+def pytest_terminal_summary_main(tr, id: str, root: Optional[str] = None) -> Dict[str, str]:
+    """Writes ``durations.txt`` (slowest first), ``failures_line.txt`` (one line per failure), ``failures_long.txt``
+    (tracebacks), ``passes.txt``, ``skipped.txt`` and ``stats.txt`` for a finished run.  ``tr`` is pytest's terminal
+    reporter.  Returns ``{name: path}``."""
+    out_dir = Path(root or "reports") / str(id)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    stats = getattr(tr, "stats", {})
+    files: Dict[str, str] = {}
+
+    def emit(name: str, lines) -> None:
+        path = out_dir / f"{name}.txt"
+        path.write_text("".join(f"{ln}\n" for ln in lines), encoding="utf-8")
+        files[name] = str(path)
+
+    timed = [r for reps in stats.values() for r in reps if hasattr(r, "duration") and getattr(r, "when", "") == "call"]
+    timed.sort(key=lambda r: r.duration, reverse=True)
+    emit("durations", [f"{r.duration:9.3f}s {r.nodeid}" for r in timed if r.duration >= 0.005])
+    failed = list(stats.get("failed", [])) + list(stats.get("error", []))
+    emit("failures_line", [f"{r.nodeid}: {str(getattr(r, 'longreprtext', '')).strip().splitlines()[-1] if getattr(r, 'longreprtext', '') else ''}"
+                           for r in failed])
+    emit("failures_long", [f"==== {r.nodeid}\n{getattr(r, 'longreprtext', '')}" for r in failed])
+    emit("passes", [r.nodeid for r in stats.get("passed", []) if getattr(r, "when", "call") == "call"])
+    emit("skipped", [f"{r.nodeid}: {r.longrepr[-1] if isinstance(r.longrepr, tuple) else r.longrepr}" for r in stats.get("skipped", [])])
+    emit("stats", [f"{k or 'other'}: {len(v)}" for k, v in sorted(stats.items(), key=lambda kv: str(kv[0]))])
+    return files

@@ -22,3 +22,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_addoption(parser):
+    from arctic_platform_b200.testing_utils import pytest_addoption_shared
+    pytest_addoption_shared(parser)
+
+
+def pytest_terminal_summary(terminalreporter):
+    make_reports = terminalreporter.config.getoption("--make-reports", default=False)
+    if make_reports:
+        from arctic_platform_b200.testing_utils import pytest_terminal_summary_main
+        pytest_terminal_summary_main(terminalreporter, id=make_reports, root=str(ROOT / "reports"))
