@@ -72,8 +72,7 @@ _MOVED = {
     # the reference's own back-compat shims under rl/ (its code moved to common/)
     "rl.server": "common.server",
     "rl.ray_cluster": "common.ray_cluster",
-    "rl.ray_server": "rl.ray_client",
-    "common.ray_server": "rl.ray_client",
+    "rl.ray_server": "common.ray_server",
     "rl.deepspeed_worker": "engine.worker",
     "rl.utils": "common.utils",
     "rl.utils.batch": "common.utils.batch",

@@ -40,13 +40,8 @@ class _RayCoreProxy:
 
 def create_arctic_rl_ray_server_state(**kwargs):
     """Server state hosted in a detached 0-GPU actor (Ray) or in-process (no Ray)."""
-    if not ray_available():
-        return ArcticRLServerCore(**kwargs)
-    import ray
-    if not ray.is_initialized():
-        ray.init(ignore_reinit_error=True)
-    actor_cls = ray.remote(num_gpus=0)(ArcticRLServerCore)
-    return _RayCoreProxy(actor_cls.remote(**kwargs))
+    from ..common.ray_server import create_arctic_rl_ray_server_state as create
+    return create(**kwargs)
 
 
 class ArcticRLRayClient(ArcticRLLocalClient):
