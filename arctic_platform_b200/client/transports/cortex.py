@@ -24,8 +24,20 @@ TRANSIENT = {408, 425, 429, 500, 502, 503, 504}
 MAX_CHUNK_BYTES = 8 * 1024 * 1024
 
 
+MAX_GROUP_REPLAYS = 2
+
+
 class CortexError(RuntimeError):
-    pass
+    def __init__(self, message: str, status: Optional[int] = None, detail: Optional[dict] = None):
+        super().__init__(message)
+        self.status = status
+        self.detail = detail or {}
+
+
+class ChunkGroupError(CortexError):
+    """The service refused a chunked upload for a reason that concerns the whole group (``detail["code"]``):
+    the group kept getting lost after the bounded replays, its identity was reused for other contents, or it was
+    closed with chunks missing."""
 
 
 class CortexTransport(Transport):
@@ -59,11 +71,19 @@ class CortexTransport(Transport):
             try:
                 resp = self.session.request(method, self.base + path, headers={**self.headers, **extra_headers},
                                             timeout=self.config.request_timeout, **kw)
-                if resp.status_code not in TRANSIENT:
-                    if resp.status_code >= 400:
-                        raise CortexError(f"{method} {path} -> {resp.status_code}: {getattr(resp, 'text', '')[:200]}")
+                if resp.status_code < 400:
                     return resp
-                last = CortexError(f"{method} {path} -> {resp.status_code}")
+                try:
+                    detail = resp.json()
+                except Exception:
+                    detail = None
+                detail = detail if isinstance(detail, dict) else {"body": detail}
+                # a verdict on the chunk group is final for this attempt whatever the status code says
+                verdict = wire.find_chunk_group_error(detail) if kw.get("data") is not None else None
+                if resp.status_code not in TRANSIENT or verdict is not None:
+                    raise CortexError(f"{method} {path} -> {resp.status_code}: {getattr(resp, 'text', '')[:200]}",
+                                      resp.status_code, detail)
+                last = CortexError(f"{method} {path} -> {resp.status_code}", resp.status_code)
             except CortexError:
                 raise
             except Exception as exc:      # connection errors are transient
@@ -99,23 +119,26 @@ class CortexTransport(Transport):
         if not request.binary:
             return self._http("POST", path, params=params, json=request.body).json()["request_id"]
         frame = wire.dumps(request.body)
-        chunks = wire.encode_byte_chunks(frame, kind="request", operation=request.op, max_bytes=MAX_CHUNK_BYTES,
-                                         chunk_group_id=str(uuid.uuid4()))
-        for attempt in range(2):         # a failed chunk upload restarts the whole group under a new id
+        for attempt in range(MAX_GROUP_REPLAYS + 1):
+            # every attempt is a new group identity: the service may still hold fragments of the lost one
+            chunks = wire.encode_byte_chunks(frame, kind="request", operation=request.op, max_bytes=MAX_CHUNK_BYTES,
+                                             chunk_group_id=str(uuid.uuid4()))
             try:
                 rid = None
                 for c in chunks:
                     rid = self._http("POST", path, params=params, data=c,
                                      headers={"Content-Type": "application/octet-stream"}).json().get("request_id", rid)
-                if rid is None:
-                    raise CortexError("server did not return a request_id")
-                return rid
-            except CortexError:
-                if attempt == 1:
-                    raise
-                chunks = wire.encode_byte_chunks(frame, kind="request", operation=request.op,
-                                                 max_bytes=MAX_CHUNK_BYTES, chunk_group_id=str(uuid.uuid4()))
-        raise CortexError("unreachable")
+            except CortexError as exc:
+                verdict = wire.find_chunk_group_error(exc.detail)
+                if verdict is None:
+                    raise                                         # not about the group: replaying cannot help
+                if verdict["code"] in wire.CHUNK_GROUP_RESTART_CODES and attempt < MAX_GROUP_REPLAYS:
+                    continue
+                raise ChunkGroupError(f"{request.op}: {verdict.get('message') or verdict['code']}", exc.status, verdict) from exc
+            if rid is None:
+                raise CortexError("server did not return a request_id")
+            return rid
+        raise AssertionError("unreachable")
 
     def _poll(self, request_id: str) -> dict:
         cursor = 0

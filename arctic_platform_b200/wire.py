@@ -374,3 +374,46 @@ def encode_result_chunks(result: Any, *, max_bytes: int = 0) -> List[bytes]:
 
 def decode_result_chunks(chunks: List[bytes]) -> Any:
     return loads(decode_byte_chunks(chunks, kind="result"))
+
+
+# ------------------------------------------------------------------ chunk-group verdicts in error replies
+CHUNK_GROUP_RESTART_CODES = {"chunk_group_restart_required", "chunk_group_restart"}
+CHUNK_GROUP_CONFLICT_CODES = {"chunk_group_conflict", "chunk_group_missing_chunks"}
+
+
+def find_chunk_group_error(body: Any, _depth: int = 0) -> Optional[dict]:
+    """The chunk-group error object inside an error reply, or None.  Gateways wrap the service's JSON reply in their
+    own (``{"message": "upstream said: {...}"}``), sometimes more than once, so the search descends into dicts,
+    lists and JSON objects embedded in strings.  The returned dict always carries ``code``."""
+    if _depth > 8:
+        return None
+    if isinstance(body, dict):
+        code = body.get("code") or body.get("error")
+        if isinstance(code, str) and code in CHUNK_GROUP_RESTART_CODES | CHUNK_GROUP_CONFLICT_CODES:
+            return {**body, "code": code}
+        if body.get("chunk_group_id") and str(body.get("message", "")).endswith("missing chunks"):
+            return {**body, "code": "chunk_group_missing_chunks"}
+        children = list(body.values())
+    elif isinstance(body, list):
+        children = body
+    elif isinstance(body, str) and ("{" in body or "[" in body):
+        import json
+        dec, children, i = json.JSONDecoder(), [], 0
+        while i < len(body):
+            if body[i] in "{[":
+                try:
+                    obj, end = dec.raw_decode(body, i)
+                except ValueError:
+                    i += 1
+                    continue
+                children.append(obj)
+                i = end
+            else:
+                i += 1
+    else:
+        return None
+    for child in children:
+        hit = find_chunk_group_error(child, _depth + 1)
+        if hit is not None:
+            return hit
+    return None

@@ -48,47 +48,10 @@ class ChunkGroupConflictError(ChunkGroupError):
     """One group identity was used for different contents, or the group was closed with chunks missing."""
 
 
-CHUNK_GROUP_RESTART_CODES = {"chunk_group_restart_required", "chunk_group_restart"}
-CHUNK_GROUP_CONFLICT_CODES = {"chunk_group_conflict", "chunk_group_missing_chunks"}
+from arctic_platform_b200.wire import (CHUNK_GROUP_CONFLICT_CODES, CHUNK_GROUP_RESTART_CODES,  # noqa: E402,F401
+                                       find_chunk_group_error)
+
 MAX_GROUP_REPLAYS = 2
-
-
-def find_chunk_group_error(body: Any, _depth: int = 0) -> Optional[dict]:
-    """The chunk-group error object inside an error reply, or None.  Gateways wrap the service's JSON reply in their
-    own (``{"message": "upstream said: {...}"}``), sometimes more than once, so the search descends into dicts,
-    lists and JSON objects embedded in strings.  The returned dict always carries ``code``."""
-    if _depth > 8:
-        return None
-    if isinstance(body, dict):
-        code = body.get("code") or body.get("error")
-        if isinstance(code, str) and code in CHUNK_GROUP_RESTART_CODES | CHUNK_GROUP_CONFLICT_CODES:
-            return {**body, "code": code}
-        if body.get("chunk_group_id") and str(body.get("message", "")).endswith("missing chunks"):
-            return {**body, "code": "chunk_group_missing_chunks"}
-        children = list(body.values())
-    elif isinstance(body, list):
-        children = body
-    elif isinstance(body, str) and ("{" in body or "[" in body):
-        import json
-        dec, children, i = json.JSONDecoder(), [], 0
-        while i < len(body):
-            if body[i] in "{[":
-                try:
-                    obj, end = dec.raw_decode(body, i)
-                except ValueError:
-                    i += 1
-                    continue
-                children.append(obj)
-                i = end
-            else:
-                i += 1
-    else:
-        return None
-    for child in children:
-        hit = find_chunk_group_error(child, _depth + 1)
-        if hit is not None:
-            return hit
-    return None
 
 
 class JobType(str, Enum):

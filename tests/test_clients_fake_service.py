@@ -125,6 +125,26 @@ def test_cortex_transport_submit_poll_chunks_and_retries(monkeypatch):
     with pytest.raises(CortexError, match="failed after 4 attempts"):
         tr.call(Request("step", jobs.training, {}))
     s.fail_next = []
+    # verdicts on a chunk group: a conflict is final at once (even on a status that is otherwise retried, even wrapped by
+    # a gateway), a refusal that is not about the group is not replayed, a group that keeps getting lost gives up
+    from arctic_platform_b200.client.transports.cortex import ChunkGroupError
+    big = Request("forward", jobs.log_prob, {"batch": {"input_ids": ids}}, binary=True)
+    s.chunk_group_reply = (503, {"message": 'gateway: {"code": "chunk_group_conflict", "message": "group reused"}'})
+    n0 = len(s.calls)
+    with pytest.raises(ChunkGroupError, match="group reused") as e:
+        tr.call(big)
+    assert len(s.calls) == n0 + 1 and e.value.detail["code"] == "chunk_group_conflict" and e.value.status == 503
+    s.chunk_group_reply = (400, {"detail": "malformed frame"})
+    n0 = len(s.calls)
+    with pytest.raises(CortexError, match="400") as e:
+        tr.call(big)
+    assert not isinstance(e.value, ChunkGroupError) and len(s.calls) == n0 + 1
+    s.restart_chunk_groups = 10
+    with pytest.raises(ChunkGroupError) as e:
+        tr.call(big)
+    assert e.value.detail["code"] == "chunk_group_restart"
+    s.restart_chunk_groups = 0
+    assert tr.call(big)["batch"]["log_probs"].shape == (4, 3)
     tr.shutdown()
     assert list(s.jobs.values())[0]["status"] == "CANCELLED"
 
