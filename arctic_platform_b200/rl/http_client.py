@@ -122,6 +122,19 @@ class ArcticRLHttpClient:
                 detail = resp.text
             raise RuntimeError(f"server returned {resp.status_code}: {detail}")
 
+    # job ids as attributes (arctic_platform/rl/http_client.py:323-341 in the reference)
+    @property
+    def training_job_id(self) -> Optional[int]:
+        return self.job_ids.get("training")
+
+    @property
+    def sampling_job_id(self) -> Optional[int]:
+        return self.job_ids.get("sampling")
+
+    @property
+    def log_prob_job_id(self) -> Optional[int]:
+        return self.job_ids.get("log_prob")
+
     def _need(self, kind: str) -> int:
         jid = self.job_ids.get(kind)
         if jid is None:

@@ -63,6 +63,19 @@ class ArcticRLLocalClient:
                 self.job_ids[kind] = info["job_id"]
 
     # ------------------------------------------------------------------ helpers
+    # job ids as attributes (arctic_platform/rl/http_client.py:323-341 in the reference)
+    @property
+    def training_job_id(self) -> Optional[int]:
+        return self.job_ids.get("training")
+
+    @property
+    def sampling_job_id(self) -> Optional[int]:
+        return self.job_ids.get("sampling")
+
+    @property
+    def log_prob_job_id(self) -> Optional[int]:
+        return self.job_ids.get("log_prob")
+
     def _need(self, kind: str) -> int:
         jid = self.job_ids.get(kind)
         if jid is None:
