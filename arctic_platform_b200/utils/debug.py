@@ -254,3 +254,114 @@ def drop_stale_nccl_topo_file() -> Optional[str]:
         os.environ.pop("NCCL_TOPO_FILE", None)
         return topo
     return None
+
+
+# ------------------------------------------------------------------------------------------------- more accessors
+def get_rank() -> int:
+    return dist.get_rank() if dist.is_available() and dist.is_initialized() else int(os.environ.get("RANK", 0))
+
+
+def get_device_id() -> int:
+    """The physical index of this process's current device: ``CUDA_VISIBLE_DEVICES`` maps logical to physical ids,
+    which is what NVML and ``nvidia-smi`` number by."""
+    if not torch.cuda.is_available():
+        return 0
+    logical = torch.cuda.current_device()
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES", "").strip()
+    if visible:
+        ids = [v.strip() for v in visible.split(",") if v.strip()]
+        if logical < len(ids) and ids[logical].isdigit():
+            return int(ids[logical])
+    return logical
+
+
+def get_nvml_mem() -> Dict[str, float]:
+    """Device memory as the driver sees it (every process on the GPU counted), in GiB; ``{}`` without a GPU.
+    Read through ``torch.cuda.mem_get_info`` -- the same figures NVML reports, no second library handle."""
+    if not torch.cuda.is_available():
+        return {}
+    free, total = torch.cuda.mem_get_info()
+    gib = 2 ** 30
+    return {"used_gib": (total - free) / gib, "free_gib": free / gib, "total_gib": total / gib}
+
+
+def gc_empty_accelerator_cache() -> None:
+    """Python garbage first (drops tensors that only cycles keep alive), then the allocator's cached blocks."""
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
+
+
+def print_rank(*msg, force: bool = True, ranks=None, **kwargs) -> None:
+    """``pr`` limited to ``ranks`` (None = every rank)."""
+    if ranks is not None and get_rank() not in ranks:
+        return
+    pr(*msg, force=force, **kwargs)
+
+
+def print_rank0(*msg, force: bool = True, **kwargs) -> None:
+    print_rank(*msg, force=force, ranks=(0,), **kwargs)
+
+
+class SynchronizedWallClockTimerSimple(SynchronizedWallClockTimer):
+    """Timers for step loops: ``timers(name).start()`` / ``.stop()`` handles, and ``log(names)`` that prints one line
+    with the mean milliseconds of each named timer since the last ``log`` and resets them."""
+
+    class _Handle:
+        def __init__(self, owner: "SynchronizedWallClockTimerSimple", name: str):
+            self.owner, self.name = owner, name
+
+        def start(self):
+            self.owner.start(self.name)
+            return self
+
+        def stop(self, record: bool = True) -> float:
+            return self.owner.stop(self.name)
+
+        def elapsed(self, reset: bool = True) -> float:
+            ms = self.owner.elapsed_ms.get(self.name, 0.0)
+            if reset:
+                self.owner.elapsed_ms.pop(self.name, None)
+                self.owner.counts.pop(self.name, None)
+            return ms
+
+    def __call__(self, name: str) -> "_Handle":
+        return self._Handle(self, name)
+
+    def means(self, names=None, reset: bool = True) -> Dict[str, float]:
+        names = list(names) if names is not None else list(self.elapsed_ms)
+        out = {n: self.elapsed_ms[n] / max(1, self.counts.get(n, 1)) for n in names if n in self.elapsed_ms}
+        if reset:
+            for n in out:
+                self.elapsed_ms.pop(n, None)
+                self.counts.pop(n, None)
+        return out
+
+    def log(self, names=None, reset: bool = True, ranks=(0,)) -> str:
+        line = " | ".join(f"{n}: {ms:.2f}" for n, ms in self.means(names, reset).items())
+        if line and self.enabled:
+            print_rank(f"time (ms) | {line}", ranks=ranks)
+        return line
+
+
+class SynchronizedWallClockTimerSimpleDummy:
+    """No-op twin: ``timers(name).start()`` and friends cost nothing."""
+
+    class _Handle:
+        def start(self):
+            return self
+
+        def stop(self, record: bool = True) -> float:
+            return 0.0
+
+        def elapsed(self, reset: bool = True) -> float:
+            return 0.0
+
+    def __call__(self, name: str) -> "_Handle":
+        return self._Handle()
+
+    def log(self, *a, **k) -> str:
+        return ""
+
+    def means(self, *a, **k) -> Dict[str, float]:
+        return {}
