@@ -9,6 +9,7 @@ Contract of arctic_platform/common/utils/batch.py:39-492 in the reference.
 """
 from __future__ import annotations
 
+import os
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
@@ -154,3 +155,47 @@ def split_batch_for_ranks(batch, meta: Dict[str, Any], n: int) -> Tuple[List[Any
         from ...rl.zorro_train.seqlen_balancing import reorg_global_batch
         batch, order = reorg_global_batch(batch, meta, n)
     return split_dict(batch, n), order
+
+
+# ------------------------------------------------------------------ the rest of the reference's helper names
+def unpack_batch(payload: Dict[str, Any]) -> Tuple[dict, Any, Dict[str, Any], Optional[dict]]:
+    """``(args, batch, meta, processing)`` of a call payload (``args`` is always empty: calls take keyword data)."""
+    return {}, payload["batch"], payload.get("meta") or {}, payload.get("processing")
+
+
+def http_split_batch(frame: bytes, num_workers: int) -> Tuple[List[Dict[str, Any]], Optional[torch.Tensor]]:
+    """One DSSST1 request frame -> per-rank payloads (same ``meta`` and ``processing`` on every rank, the batch split
+    by ``split_batch_for_ranks``) and the permutation that was applied to the rows, if any."""
+    from ... import wire
+    _args, batch, meta, processing = unpack_batch(wire.loads(frame))
+    meta = dict(meta)
+    shards, order = split_batch_for_ranks(batch, meta, num_workers)
+    return [{"batch": s, "meta": dict(meta), "processing": processing} for s in shards], order
+
+
+def get_reverse_idx(idx_map) -> List[int]:
+    """The inverse permutation: ``out[idx_map[i]] = i``."""
+    out = [0] * len(idx_map)
+    for i, j in enumerate(idx_map):
+        out[int(j)] = i
+    return out
+
+
+def dump_dict_payload(payload: Dict[str, Any], tag: str, out=None) -> None:
+    """One line per entry (tensors by shape / dtype, everything else by value) when ``ARL_DUMP_PAYLOADS`` is set;
+    silent otherwise."""
+    if not os.environ.get("ARL_DUMP_PAYLOADS"):
+        return
+    import sys
+    out = out or sys.stderr
+    for k, v in payload.items():
+        what = f"tensor{tuple(v.shape)} {v.dtype}" if torch.is_tensor(v) else repr(v)[:200]
+        out.write(f"{tag}: {k} = {what}\n")
+
+
+def __getattr__(name: str):
+    # metric reducers live in ``metrics.py``; the reference reaches them through this module
+    if name in ("combine_metric_shards", "combine_metric_microbatches", "finalize_fwd_bwd_metrics"):
+        from . import metrics
+        return getattr(metrics, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -153,3 +153,28 @@ def test_subprocess_runner_and_small_helpers(monkeypatch):
     assert not tu.gpu_partitioning_active()
     with tu.gpu_serial_lock("apb-test-lock"):
         pass
+
+
+def test_request_frame_split_and_small_batch_helpers(monkeypatch):
+    import io
+
+    from arctic_platform_b200 import wire
+    from arctic_platform_b200.common.utils import batch as b
+    frame = wire.dumps({"batch": {"input_ids": torch.arange(12).view(4, 3), "response_mask": torch.ones(4, 2)},
+                        "meta": {"temperature": 1.0}, "processing": {"loss_fn": "sft"}})
+    shards, order = b.http_split_batch(frame, 2)
+    assert len(shards) == 2 and order is None and shards[0]["batch"]["input_ids"].shape == (2, 3)
+    assert shards[1]["meta"]["dp_size"] == 2 and shards[0]["meta"]["batch_num_tokens"] == 8.0
+    assert shards[0]["processing"] == {"loss_fn": "sft"} and shards[0]["meta"] is not shards[1]["meta"]
+    assert b.get_reverse_idx([2, 0, 1]) == [1, 2, 0]
+    assert b.unpack_batch({"batch": 1, "meta": {"a": 1}, "processing": None}) == ({}, 1, {"a": 1}, None)
+    buf = io.StringIO()
+    monkeypatch.delenv("ARL_DUMP_PAYLOADS", raising=False)
+    b.dump_dict_payload({"x": torch.zeros(2, 3)}, "t", buf)
+    assert buf.getvalue() == ""
+    monkeypatch.setenv("ARL_DUMP_PAYLOADS", "1")
+    b.dump_dict_payload({"x": torch.zeros(2, 3), "y": 5}, "t", buf)
+    assert "t: x = tensor(2, 3) torch.float32" in buf.getvalue() and "t: y = 5" in buf.getvalue()
+    from arctic_platform_b200.common.utils.batch import combine_metric_shards, finalize_fwd_bwd_metrics
+    from arctic_platform_b200.common.utils import metrics
+    assert finalize_fwd_bwd_metrics is metrics.finalize_fwd_bwd_metrics and combine_metric_shards is metrics.combine_metric_shards
