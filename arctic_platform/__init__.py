@@ -68,7 +68,6 @@ _MOVED = {
     "client.sft_config": "sft.config",
     "client.transports.onprem_http": "client.transports.onprem",
     "client.transports.onprem_ray": "client.transports.ray_actor",
-    "common.utils.tiled_logits": "ops.logprob",
     # the reference's own back-compat shims under rl/ (its code moved to common/)
     "rl.server": "common.server",
     "rl.ray_cluster": "common.ray_cluster",
