@@ -21,7 +21,9 @@ class ReplayMiss(RuntimeError):
 
 def _settings():
     d = os.environ.get("REPLAY_GENERATION_DIR")
-    mode = os.environ.get("REPLAY_GENERATION_MODE", "")
+    mode = os.environ.get("REPLAY_GENERATION_MODE", "").lower()
+    if mode == "load":                                   # the reference's word for replay
+        mode = "replay"
     if os.environ.get("REPLAY_GENERATION") == "1" and not mode:
         mode = "replay"
     start = int(os.environ.get("REPLAY_START_RECORD", "0") or 0)
@@ -78,3 +80,60 @@ def record_replay_generation(fn: Callable) -> Callable:
         return _after(d, i, fn(*args, **kwargs))
     wrapper._replay_counter = counter
     return wrapper
+
+
+class RecordReplay:
+    """Tape of whole batch dicts (tensors included), for loops that record what they fed the trainer rather than what
+    the sampler returned: ``save_record(i, batch)`` in record mode, ``load_record(i)`` in load mode, ``skip_record(i)``
+    for the leading records a replay should pass over.  Switches, read when the object is made:
+    ``REPLAY_GENERATION=1`` (on), ``REPLAY_GENERATION_DIR``, ``REPLAY_GENERATION_MODE`` = ``record`` (default) |
+    ``load``, ``REPLAY_START_RECORD``.  Records are DSSST1 frames (``generate-<i>.dssst1``): loading one parses
+    tensors and JSON, it never runs code -- the reference stores pickles
+    (arctic_platform/common/utils/record_replay.py:60-105)."""
+
+    def __init__(self):
+        self.enabled = os.environ.get("REPLAY_GENERATION", "").lower() in ("1", "true", "yes", "on")
+        d = os.environ.get("REPLAY_GENERATION_DIR")
+        self.dir = Path(d) if d else None
+        self.mode = os.environ.get("REPLAY_GENERATION_MODE", "record").lower()
+        if self.mode == "replay":
+            self.mode = "load"
+        if self.mode not in ("record", "load"):
+            raise ValueError(f"REPLAY_GENERATION_MODE={self.mode!r}: expected record or load")
+        try:
+            self.start_record = max(0, int(os.environ.get("REPLAY_START_RECORD", "0") or 0))
+        except ValueError:
+            self.start_record = 0
+        if self.is_record_mode():
+            self.dir.mkdir(parents=True, exist_ok=True)
+        elif self.is_replay_mode() and not self.dir.exists():
+            raise FileNotFoundError(f"load mode needs the directory {self.dir}")
+
+    def is_enabled(self) -> bool:
+        return self.enabled and self.dir is not None
+
+    def is_record_mode(self) -> bool:
+        return self.is_enabled() and self.mode == "record"
+
+    def is_replay_mode(self) -> bool:
+        return self.is_enabled() and self.mode == "load"
+
+    def skip_record(self, record_index: int) -> bool:
+        return self.is_replay_mode() and record_index <= self.start_record
+
+    def _path(self, record_index: int) -> Path:
+        return self.dir / f"generate-{record_index}.dssst1"
+
+    def save_record(self, record_index: int, batch_dict: dict) -> None:
+        if self.is_record_mode():
+            from .. import wire
+            self._path(record_index).write_bytes(wire.dumps(batch_dict))
+
+    def load_record(self, record_index: int):
+        if not self.is_replay_mode():
+            return None
+        p = self._path(record_index)
+        if not p.exists():
+            raise FileNotFoundError(f"no record {record_index} under {self.dir}")
+        from .. import wire
+        return wire.loads(p.read_bytes())
