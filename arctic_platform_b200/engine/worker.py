@@ -362,12 +362,15 @@ class EngineWorker:
         meta = self._with_sft_global_tokens(mbs, meta, processing)
         meta = self._with_rl_global_counts(mbs, meta, processing)
         per_mb, outs = [], []
-        from ..utils.debug import ProfilerContext, nvtx_range, see_memory_usage
+        from ..utils.debug import MemoryHistory, ProfilerContext, nvtx_range, see_memory_usage
         tag = "fwd_bwd" if backward else "fwd"
         self._calls = getattr(self, "_calls", 0) + 1
         prof_type = os.environ.get("APB_PROFILER", "none") if self._calls == int(os.environ.get("APB_PROFILER_CALL", "2")) else "none"
         see_memory_usage(f"{tag} start")
-        with ProfilerContext(prof_type, os.environ.get("APB_PROFILER_DIR", "/tmp/apb-prof"), f"{tag}-rank{self.rank}") as prof:
+        mem_hist = MemoryHistory(prof_type == "none" and os.environ.get("APB_MEMORY_HISTORY") == "1"
+                                 and self._calls == int(os.environ.get("APB_PROFILER_CALL", "2")),
+                                 os.environ.get("APB_PROFILER_DIR", "/tmp/apb-prof"), f"{tag}-memory-rank{self.rank}")
+        with mem_hist, ProfilerContext(prof_type, os.environ.get("APB_PROFILER_DIR", "/tmp/apb-prof"), f"{tag}-rank{self.rank}") as prof:
             for i, mb in enumerate(mbs):
                 if isinstance(mb, dict):
                     log_dp_shard_tokens(self.rank, f"{tag} micro-batch {i}", mb, meta)
@@ -381,6 +384,8 @@ class EngineWorker:
                     outs.append(r)                           # a filler pass has no rows of the caller's batch
         if prof.report and self.rank == 0:
             print(f"[profile] {tag}: {prof.report}", flush=True)
+        if mem_hist.path:
+            print(f"[profile] {tag}: allocator history in {mem_hist.path}", flush=True)
         see_memory_usage(f"{tag} end")
         metrics = combine_metric_microbatches(per_mb)
         result: Dict[str, Any] = {"metrics": metrics, "avg_loss": sum(o["avg_loss"] for o in outs)}

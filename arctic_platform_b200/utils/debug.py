@@ -188,6 +188,33 @@ class ProfilerContext:
         return False
 
 
+class MemoryHistory:
+    """Allocator history of the block as a snapshot file (open it at pytorch.org/memory_viz): every allocation and
+    free with its stack while the block runs, then one ``<out_dir>/<name>.pickle``.  ``enabled=False`` or no GPU: does
+    nothing.  The reference has this as a hard-coded switch around one training call
+    (arctic_platform/common/deepspeed_worker.py:374-378, 522-529)."""
+
+    def __init__(self, enabled: bool, out_dir: str = "/tmp/apb-mem-prof", name: str = "rank-0", max_entries: int = 100_000):
+        self.enabled = bool(enabled) and torch.cuda.is_available()
+        self.out_dir, self.name, self.max_entries = out_dir, name, max_entries
+        self.path: Optional[str] = None
+
+    def __enter__(self):
+        if self.enabled:
+            torch.cuda.memory._record_memory_history(max_entries=self.max_entries)
+        return self
+
+    def __exit__(self, *exc):
+        if self.enabled:
+            try:
+                os.makedirs(self.out_dir, exist_ok=True)
+                self.path = os.path.join(self.out_dir, f"{self.name}.pickle")
+                torch.cuda.memory._dump_snapshot(self.path)
+            finally:
+                torch.cuda.memory._record_memory_history(enabled=None)
+        return False
+
+
 def enable_full_determinism(seed: int, warn_only: bool = True) -> None:
     """Seeds every RNG and switches PyTorch to deterministic algorithms."""
     random.seed(seed)

@@ -33,3 +33,14 @@ def test_step_loop_timers(capsys):
     assert t.means() == {} and t("fwd").elapsed() == 0.0                      # log() reset what it reported
     d = debug.SynchronizedWallClockTimerSimpleDummy()
     assert d("x").start().stop() == 0.0 and d.log() == "" and d.means() == {} and d("x").elapsed() == 0.0
+
+
+def test_memory_history_is_inert_without_a_gpu(tmp_path):
+    import torch
+    with debug.MemoryHistory(True, str(tmp_path), "r0") as mh:
+        x = torch.zeros(4)
+    if not torch.cuda.is_available():
+        assert mh.path is None and not mh.enabled and list(tmp_path.iterdir()) == []
+    with debug.MemoryHistory(False, str(tmp_path)) as off:
+        pass
+    assert off.path is None and x.sum() == 0
