@@ -87,7 +87,7 @@ class SpawnedActor:
             raise ActorDied(f"actor pid {self._proc.pid} exited (code {self._proc.exitcode})") from exc
 
     def call(self, method: str, *args, timeout: Optional[float] = None, **kwargs):
-        if not self._proc.is_alive():
+        if not self.alive():
             raise ActorDied(f"actor pid {self._proc.pid} is not running (code {self._proc.exitcode})")
         with self._lock:
             try:
@@ -100,8 +100,15 @@ class SpawnedActor:
         return payload
 
     def alive(self) -> bool:
-        """Whether the process exists -- never blocks, also while a long call is in flight."""
-        return self._proc.is_alive()
+        """Whether the process exists -- never blocks, also while a long call is in flight.  Decided from the process
+        sentinel (readable once the process has exited), not from ``Process.is_alive()``: that one reaps the child
+        with ``waitpid``, and when two threads ask at the same moment (the watchdog and a caller that is tearing the
+        job down) the loser of the race is told "no such child" and reports a dead process as alive."""
+        from multiprocessing.connection import wait
+        try:
+            return not wait([self._proc.sentinel], timeout=0)
+        except (ValueError, OSError):            # closed process object
+            return False
 
     def heartbeat(self, timeout: float = 5.0) -> bool:
         try:
@@ -123,16 +130,16 @@ class SpawnedActor:
 
     def kill(self, grace_s: float = 2.0) -> None:
         try:
-            if self._proc.is_alive() and grace_s > 0:
+            if self.alive() and grace_s > 0:
                 try:
                     self._conn.send(None)
                 except Exception:
                     pass
                 self._proc.join(grace_s)
-            if self._proc.is_alive():
+            if self.alive():
                 self._proc.terminate()
                 self._proc.join(5.0)
-            if self._proc.is_alive():
+            if self.alive():                     # the sentinel, not is_alive(): never signal a pid that was reaped
                 self._proc.kill()
         finally:
             self._conn.close()

@@ -20,16 +20,36 @@ class SkyRLArcticBackend:
     def __init__(self, model: str, training_gpus: int = 1, sampling_gpus: int = 1, log_prob_gpus: int = 1,
                  colocate: bool = True, comm_protocol: str = "local", host: Optional[str] = None,
                  port: Optional[int] = None, lr: float = 1e-6, zero_stage: int = 3, zorro: bool = True,
-                 max_model_len: int = 8192, loss_fn: str = "verl_grpo", kl_loss_coef: float = 0.001):
+                 max_model_len: int = 8192, loss_fn: str = "verl_grpo", kl_loss_coef: float = 0.001,
+                 sampler_tp: int = 1, sequence_parallel: int = 1, offload_optimizer: bool = False):
         self.zorro = zorro
         self.loss_fn = loss_fn
         self.kl_loss_coef = kl_loss_coef
-        self.client = create_arctic_rl_client(ArcticRLClientConfig(
-            comm_protocol=comm_protocol, host=host, port=port, model_name=model, training_gpus=training_gpus,
-            sampling_gpus=sampling_gpus, log_prob_gpus=log_prob_gpus, colocate=colocate,
-            ds_config={"zero_optimization": {"stage": zero_stage}, "gradient_clipping": 1.0,
-                       "optimizer": {"type": "AdamW", "params": {"lr": lr}}},
-            ds_worker_config={"zorro_train": {"enable": zorro}}, vllm_config={"max_model_len": max_model_len}))
+        self.client = create_arctic_rl_client(self.client_config(
+            model, training_gpus, sampling_gpus, log_prob_gpus, colocate, comm_protocol, host, port, lr, zero_stage, zorro,
+            max_model_len, sampler_tp, sequence_parallel, offload_optimizer))
+
+    @staticmethod
+    def client_config(model, training_gpus=1, sampling_gpus=1, log_prob_gpus=1, colocate=True, comm_protocol="local",
+                      host=None, port=None, lr=1e-6, zero_stage=3, zorro=True, max_model_len=8192, sampler_tp=1,
+                      sequence_parallel=1, offload_optimizer=False) -> ArcticRLClientConfig:
+        """The platform configuration a launcher's flags stand for (kept apart so that it can be inspected without
+        starting engines)."""
+        zero: Dict[str, Any] = {"stage": zero_stage}
+        if offload_optimizer:
+            zero["offload_optimizer"] = {"device": "cpu", "pin_memory": True}
+        worker: Dict[str, Any] = {"zorro_train": {"enable": zorro}}
+        if sequence_parallel > 1:
+            worker["sequence_parallel"] = int(sequence_parallel)
+        vllm: Dict[str, Any] = {"max_model_len": max_model_len}
+        if sampler_tp > 1:
+            vllm["tensor_parallel_size"] = int(sampler_tp)
+        kw = {"host": host, "port": port} if comm_protocol != "local" else {}
+        return ArcticRLClientConfig(
+            comm_protocol=comm_protocol, model_name=model, training_gpus=training_gpus, sampling_gpus=sampling_gpus,
+            log_prob_gpus=log_prob_gpus, colocate=colocate,
+            ds_config={"zero_optimization": zero, "gradient_clipping": 1.0, "optimizer": {"type": "AdamW", "params": {"lr": lr}}},
+            ds_worker_config=worker, vllm_config=vllm, **kw)
 
     def generate(self, prompts: Sequence[Sequence[int]], n: int = 1, max_tokens: int = 1024, temperature: float = 1.0,
                  **extra) -> List[dict]:

@@ -82,7 +82,8 @@ def run(args, backend: Optional[SkyRLArcticBackend] = None, log=print) -> List[D
     backend = backend or SkyRLArcticBackend(
         args.model, training_gpus=args.training_gpus, sampling_gpus=args.sampling_gpus, log_prob_gpus=args.log_prob_gpus,
         lr=args.lr, zero_stage=args.zero_stage, zorro=not args.no_zorro, max_model_len=args.max_prompt_tokens + args.max_tokens,
-        kl_loss_coef=args.kl_loss_coef)
+        kl_loss_coef=args.kl_loss_coef, sampler_tp=getattr(args, "sampler_tp", 1),
+        sequence_parallel=getattr(args, "sequence_parallel", 1), offload_optimizer=getattr(args, "offload_optimizer", False))
     history = []
     try:
         backend.client.call("sync_weights")
@@ -137,6 +138,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--no-zorro", action="store_true")
     ap.add_argument("--epochs", type=int, default=1)
     ap.add_argument("--max-steps", type=int, default=0)
+    ap.add_argument("--sampler-tp", type=int, default=1, help="tensor-parallel width of each sampler replica")
+    ap.add_argument("--sequence-parallel", type=int, default=1, help="Ulysses degree of the trainer (long prompts)")
+    ap.add_argument("--offload-optimizer", action="store_true", help="fp32 master weights and Adam moments in host memory")
     return ap
 
 

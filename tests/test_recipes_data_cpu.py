@@ -92,3 +92,21 @@ def test_launchers_are_valid_shell():
                 "verl/txt2sql/run_qwen3_32b_bird_grpo_baseline.sh",
                 "verl/long_context_qa/run_qwen3_32b_loongrl_grpo_baseline.sh"):
         subprocess.run(["bash", "-n", os.path.join(root, rel)], check=True)
+
+
+def test_skyrl_launcher_flags_become_platform_config():
+    from recipes.rl.skyrl.arctic_backend import SkyRLArcticBackend
+    from recipes.rl.skyrl.run_loop import build_parser
+    a = build_parser().parse_args(["--data", "d", "--env", "e", "--sampler-tp", "4", "--sequence-parallel", "4", "--offload-optimizer"])
+    assert (a.sampler_tp, a.sequence_parallel, a.offload_optimizer) == (4, 4, True)
+    cfg = SkyRLArcticBackend.client_config("qwen3-32b", 32, 32, 32, sampler_tp=4, sequence_parallel=4, offload_optimizer=True,
+                                           max_model_len=36864)
+    assert cfg.ds_config["zero_optimization"] == {"stage": 3, "offload_optimizer": {"device": "cpu", "pin_memory": True}}
+    assert cfg.ds_worker_config == {"zorro_train": {"enable": True}, "sequence_parallel": 4}
+    assert cfg.vllm_config == {"max_model_len": 36864, "tensor_parallel_size": 4}
+    plain = SkyRLArcticBackend.client_config("qwen3-tiny")
+    assert "sequence_parallel" not in plain.ds_worker_config and "tensor_parallel_size" not in plain.vllm_config
+    import subprocess
+    root = os.path.join(os.path.dirname(__file__), "..", "recipes", "rl", "skyrl")
+    for rel in ("txt2sql/run_qwen3_32b_bird_grpo_4node.sh", "long_context_qa/run_qwen3_32b_loongrl_grpo_4node.sh"):
+        subprocess.run(["bash", "-n", os.path.join(root, rel)], check=True)

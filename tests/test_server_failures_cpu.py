@@ -190,8 +190,12 @@ def test_watchdog_marks_a_job_failed_when_a_worker_process_is_gone():
         while job.status != "FAILED" and time.time() < deadline:
             time.sleep(0.05)
         assert job.status == "FAILED" and "do not answer" in job.info["failure"]
-        job.workers[1]._proc.join(180)                           # teardown follows the state change
-        assert not job.workers[1]._proc.is_alive()               # the peer was stopped with it
+        # teardown follows the state change.  The watchdog thread is joining that process right now, so this thread
+        # must not join it too (two joiners race for the one waitpid): it watches the worker's own liveness probe
+        deadline = time.time() + 180.0
+        while job.workers[1].alive() and time.time() < deadline:
+            time.sleep(0.05)
+        assert not job.workers[1].alive()                        # the peer was stopped with it
     finally:
         core.stop_worker_watchdog()
         core.destroy()
