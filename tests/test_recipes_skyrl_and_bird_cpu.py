@@ -95,3 +95,24 @@ def test_dataset_loop_runs_on_the_tiny_preset(tmp_path):
     hist = run_loop.run(args, log=logs.append)
     assert len(hist) == 2 and len(logs) == 2 and all(h["grad_norm"] >= 0 for h in hist)
     assert json.loads(logs[0])["step"] == 0
+
+
+def test_entrypoint_runs_in_process_and_reattaches(tmp_path, capsys):
+    from arctic_platform_b200.common.ray_server import create_arctic_rl_ray_server_state
+    from recipes.rl.skyrl import entrypoint
+    rows = [{"prompt": [{"role": "user", "content": f"What is {a}+{a}?"}], "reward_model": {"ground_truth": str(2 * a)}}
+            for a in range(1, 5)]
+    data = tmp_path / "p.jsonl"
+    data.write_text("\n".join(json.dumps(r) for r in rows))
+    argv = ["--data", str(data), "--env", "gsm8k_arctic", "--model", "qwen3-tiny", "--batch-prompts", "2", "--n", "2",
+            "--max-tokens", "4", "--max-steps", "1", "--max-prompt-tokens", "64", "--zero-stage", "1", "--log-prob-gpus", "0",
+            "--kl-loss-coef", "0"]
+    assert entrypoint.main(argv) == 0
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["step"] == 0
+    # a server state handed in by the caller hosts the engines; the loop leaves them to their owner
+    state = create_arctic_rl_ray_server_state(colocate=True)
+    hist = entrypoint.skyrl_entrypoint(argv, server_state=state)
+    assert len(hist) == 1 and len(state.get_jobs()) == 2
+    state.destroy()
+    assert entrypoint.main(["--as-ray-task"] + argv) == 2                    # no Ray on this machine: says so, no traceback
+    import recipes.rl.skyrl.sitecustomize  # noqa: F401  (importable, and harmless without skyrl_gym)
