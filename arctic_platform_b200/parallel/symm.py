@@ -53,7 +53,17 @@ class SymmetricBuffer:
         self.multicast_ptr = 0
         self._handle = None
         dev = torch.device(device)
-        if self.world > 1 and dev.type == "cuda":
+        if self.world > 1 and dev.type == "cuda" and os.environ.get("APB_SYMM", "torch") == "vmm" and not multimem_enabled():
+            # this package's own allocation + descriptor exchange (parallel/vmm.py); opt-in
+            from .vmm import VmmSymmetricMemory
+            self._handle = VmmSymmetricMemory(numel, dtype, dev, group)
+            self.tensor = self._handle.tensor
+            if zero:
+                self.tensor.zero_()
+            self.peer_ptrs = [int(p) for p in self._handle.peer_ptrs]
+            torch.cuda.synchronize(dev)
+            dist.barrier(group=group)
+        elif self.world > 1 and dev.type == "cuda":
             _keep_rendezvous_off_multicast()
             import torch.distributed._symmetric_memory as symm_mem
 
