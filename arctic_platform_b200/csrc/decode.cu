@@ -925,7 +925,7 @@ int apb_kv_cache_write(const void* k, long long ldk, const void* v, long long ld
   if (T <= 0) return 0;
   if ((D % 8) || (ldk % 8) || (ldv % 8)) return kBadArgument;
   const long long n = static_cast<long long>(T) * Hkv * D / 8;
-  const int grid = static_cast<int>((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  const int grid = static_cast<int>((n + 255) / 256 < apb::sm_count() * 8 ? (n + 255) / 256 : apb::sm_count() * 8);
   return static_cast<int>(launch_kernel(kv_cache_write_kernel, dim3(grid), dim3(256), 0, s,
                                         static_cast<const __nv_bfloat16*>(k), ldk, static_cast<const __nv_bfloat16*>(v),
                                         ldv, slots, static_cast<__nv_bfloat16*>(kcache),

@@ -484,7 +484,7 @@ int apb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void
                     int H, float eps, float w_offset, cudaStream_t s) {
   if (T <= 0) return 0;
   if (H % 8 || H > kNormThreads * 8 * kNormMaxVec) return kBadArgument;
-  const int grid = T < 148 * 8 ? T : 148 * 8;
+  const int grid = T < apb::sm_count() * 8 ? T : apb::sm_count() * 8;
   return static_cast<int>(launch_kernel(rmsnorm_fwd_kernel, dim3(grid), dim3(kNormThreads), 0, s,
                                         static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
                                         static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y),
@@ -498,7 +498,7 @@ int apb_rmsnorm_fwd_f32in(float* x_f32, const void* res, const void* w, void* y,
                           float w_offset, cudaStream_t s) {
   if (T <= 0) return 0;
   if (H % 8 || H > kNormThreads * 8 * kNormMaxVec || !res_out) return kBadArgument;
-  const int grid = T < 148 * 8 ? T : 148 * 8;
+  const int grid = T < apb::sm_count() * 8 ? T : apb::sm_count() * 8;
   return static_cast<int>(launch_kernel(rmsnorm_fwd_kernel, dim3(grid), dim3(kNormThreads), 0, s,
                                         static_cast<const __nv_bfloat16*>(nullptr),
                                         static_cast<const __nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(w),
@@ -513,7 +513,7 @@ int apb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
   if (H % 8 || H > kNormThreads * 8 * kNormMaxVec) return kBadArgument;
   const int nv = (H / 8 + kNormThreads - 1) / kNormThreads;
   const int per_sm = nv <= 1 ? 3 : (nv <= 2 ? 2 : 1);
-  const int grid = T < 148 * per_sm ? T : 148 * per_sm;
+  const int grid = T < apb::sm_count() * per_sm ? T : apb::sm_count() * per_sm;
 #define APB_NORM_BWD(NV)                                                                                     \
   rmsnorm_bwd_kernel<NV><<<grid, kNormThreads, 0, s>>>(                                                       \
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),                            \
@@ -554,7 +554,7 @@ int apb_qknorm_rope_bwd(const void* qkv, long long ld_qkv, const void* wq, const
                         float eps, cudaStream_t s) {
   if (T <= 0) return 0;
   if (rot != 0 && rot != D) return kBadArgument;
-  const int grid = 148 * 2;       // two resident CTAs per SM, each walks its share of the items
+  const int grid = apb::sm_count() * 2;       // two resident CTAs per SM, each walks its share of the items
 #define APB_LAUNCH_QKB(DD)                                                                                  \
   qknorm_rope_bwd_kernel<DD><<<grid, 256, 0, s>>>(                                                          \
       static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<const __nv_bfloat16*>(wq),               \
@@ -573,7 +573,7 @@ int apb_swiglu_f32in(float* acc, void* act, long long T, long long I, cudaStream
   if (I % 4) return kBadArgument;
   const long long n = T * I / 4;
   if (n <= 0) return 0;
-  const int grid = static_cast<int>(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);
+  const int grid = static_cast<int>(n / 256 + 1 < apb::sm_count() * 16 ? n / 256 + 1 : apb::sm_count() * 16);
   return static_cast<int>(launch_kernel(swiglu_f32in_kernel, dim3(grid), dim3(256), 0, s, acc,
                                         static_cast<__nv_bfloat16*>(act), n));
 }
@@ -581,7 +581,7 @@ int apb_swiglu_fwd(const void* gu, void* act, long long T, long long I, cudaStre
   if (I % 8) return kBadArgument;
   const long long n = T * I / 8;
   if (n <= 0) return 0;
-  const int grid = static_cast<int>(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);
+  const int grid = static_cast<int>(n / 256 + 1 < apb::sm_count() * 16 ? n / 256 + 1 : apb::sm_count() * 16);
   swiglu_fwd_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(act), n);
   return static_cast<int>(cudaGetLastError());
 }
@@ -589,7 +589,7 @@ int apb_swiglu_bwd(const void* gu, const void* dact, void* dgu, long long T, lon
   if (I % 8) return kBadArgument;
   const long long n = T * I / 8;
   if (n <= 0) return 0;
-  const int grid = static_cast<int>(n / 256 + 1 < 148 * 16 ? n / 256 + 1 : 148 * 16);
+  const int grid = static_cast<int>(n / 256 + 1 < apb::sm_count() * 16 ? n / 256 + 1 : apb::sm_count() * 16);
   swiglu_bwd_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(gu),
                                          static_cast<const __nv_bfloat16*>(dact),
                                          static_cast<__nv_bfloat16*>(dgu), n);

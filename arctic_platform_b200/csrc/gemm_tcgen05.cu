@@ -1005,7 +1005,8 @@ int apb_tp_finalize(void* const* flag_ptrs, int rank, int world, int epoch, floa
   PeerPtrs f;
   for (int i = 0; i < kMaxRanks; ++i) f.p[i] = i < world ? flag_ptrs[i] : nullptr;
   long long g = (n / 8 + 255) / 256;
-  const int grid = static_cast<int>(g < 1 ? 1 : (g < 148 * 8 ? g : 148 * 8));
+  const long long cap = static_cast<long long>(sm_count()) * 8;
+  const int grid = static_cast<int>(g < 1 ? 1 : (g < cap ? g : cap));
   tp_finalize_kernel<<<grid, 256, 0, stream>>>(f, rank, world, epoch, acc, static_cast<__nv_bfloat16*>(out), n,
                                                status_device_ptr());
   return static_cast<int>(cudaGetLastError());

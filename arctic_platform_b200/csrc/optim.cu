@@ -292,7 +292,8 @@ static PeerPtrs to_peers(void* const* ptrs, int world) {
 static int grid_for(long long work_items) {
   long long g = (work_items + 255) / 256;
   if (g < 1) g = 1;
-  return static_cast<int>(g < 148 * 8 ? g : 148 * 8);
+  const long long cap = static_cast<long long>(sm_count()) * 8;
+  return static_cast<int>(g < cap ? g : cap);
 }
 
 // Phase A.  grad_ptrs[world]: every rank's fp32 bucket base (peer-mapped); flag_ptrs[world]: every rank's
@@ -770,7 +771,8 @@ int apb_ep_scatter_rows(const void* src, long long ld_src, const int* src_row, c
   PeerPtrs meta;
   for (int i = 0; i < kMaxRanks; ++i) meta.p[i] = (meta_ptrs && i < world) ? meta_ptrs[i] : nullptr;
   const long long g = (static_cast<long long>(n_pairs) * 32 + 255) / 256;
-  const int grid = static_cast<int>(g < 148 * 16 ? g : 148 * 16);
+  const long long cap = static_cast<long long>(sm_count()) * 16;
+  const int grid = static_cast<int>(g < cap ? g : cap);
   ep_scatter_rows_kernel<<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src), ld_src, src_row, dst_rank, dst_row,
                                               tag, to_peers(dst_ptrs, world), ld_dst, meta, rank, world, n_pairs, H,
                                               status_device_ptr());
