@@ -11,6 +11,11 @@ GROUPS: Dict[str, List[str]] = {
     "ray": ["ray"],
     "hf": ["transformers", "safetensors"],
     "testing": ["pytest"],
+    # the reference's group names: what a training-only server, the full RL stack, the verl glue and development need
+    "sft": ["torch", "numpy", "pydantic", "fastapi", "uvicorn", "requests", "safetensors"],
+    "rl": ["torch", "numpy", "pydantic", "fastapi", "uvicorn", "requests", "safetensors", "pyarrow"],
+    "verl": ["torch", "numpy", "pydantic", "omegaconf"],
+    "dev": ["torch", "numpy", "pydantic", "pytest"],
 }
 
 
