@@ -416,3 +416,43 @@ def pytest_terminal_summary_main(tr, id: str, root: Optional[str] = None) -> Dic
     emit("skipped", [f"{r.nodeid}: {r.longrepr[-1] if isinstance(r.longrepr, tuple) else r.longrepr}" for r in stats.get("skipped", [])])
     emit("stats", [f"{k or 'other'}: {len(v)}" for k, v in sorted(stats.items(), key=lambda kv: str(kv[0]))])
     return files
+
+
+# ------------------------------------------------------------------------------------------------- GPUs under pytest-xdist
+def gpu_slice_for_worker(worker_id: int, n_workers: int, gpu_ids):
+    """The GPUs one pytest-xdist worker may see: the list is cut into ``n_workers`` contiguous slices of equal size
+    (the remainder stays unused so that every worker has the same number of devices); with more workers than GPUs,
+    workers share round-robin, one GPU each."""
+    ids = [str(g) for g in gpu_ids]
+    if not ids or n_workers <= 1:
+        return ids
+    if n_workers >= len(ids):
+        return [ids[worker_id % len(ids)]]
+    per = len(ids) // n_workers
+    return ids[worker_id * per:(worker_id + 1) * per]
+
+
+def visible_gpu_ids():
+    """GPU ids this process could use, WITHOUT initialising CUDA: ``CUDA_VISIBLE_DEVICES`` when set, else the device
+    nodes the driver created."""
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if visible is not None:
+        return [v.strip() for v in visible.split(",") if v.strip()]
+    import glob
+    import re
+    return sorted((re.sub(r"\\D", "", p) for p in glob.glob("/dev/nvidia[0-9]*")), key=int)
+
+
+def partition_gpus_for_xdist() -> Optional[str]:
+    """Call before anything initialises CUDA (top of ``conftest.py``): under pytest-xdist, narrows
+    ``CUDA_VISIBLE_DEVICES`` to this worker's slice and sets ``ARL_GPU_PARTITIONED=1``; returns the new value, or
+    None when nothing was changed (no xdist, no GPUs, or already partitioned)."""
+    if "PYTEST_XDIST_WORKER" not in os.environ or os.environ.get("ARL_GPU_PARTITIONED"):
+        return None
+    ids = visible_gpu_ids()
+    if not ids:
+        return None
+    mine = gpu_slice_for_worker(get_xdist_worker_id(), get_xdist_worker_count(), ids)
+    os.environ["CUDA_VISIBLE_DEVICES"] = ",".join(mine)
+    os.environ["ARL_GPU_PARTITIONED"] = "1"
+    return os.environ["CUDA_VISIBLE_DEVICES"]

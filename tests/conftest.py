@@ -8,6 +8,11 @@ ROOT = Path(__file__).resolve().parents[1]
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
+# under pytest-xdist every worker gets its own slice of the GPUs (before anything initialises CUDA)
+from arctic_platform_b200.testing_utils import partition_gpus_for_xdist  # noqa: E402
+
+partition_gpus_for_xdist()
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: test needs a CUDA device (B200)")

@@ -100,3 +100,22 @@ def test_report_files(tmp_path):
     tu.pytest_addoption_shared(p)
     tu.pytest_addoption_shared(p)                       # a second conftest asking for the same option is fine
     assert p.opts == [("--make-reports",)]
+
+
+def test_gpu_partitioning_for_xdist_workers(monkeypatch):
+    ids = list(range(8))
+    assert [tu.gpu_slice_for_worker(w, 4, ids) for w in range(4)] == [["0", "1"], ["2", "3"], ["4", "5"], ["6", "7"]]
+    assert [tu.gpu_slice_for_worker(w, 3, ids) for w in range(3)] == [["0", "1"], ["2", "3"], ["4", "5"]]     # equal slices
+    assert [tu.gpu_slice_for_worker(w, 4, [0, 1]) for w in range(4)] == [["0"], ["1"], ["0"], ["1"]]            # sharing
+    assert tu.gpu_slice_for_worker(0, 1, ids) == [str(i) for i in ids] and tu.gpu_slice_for_worker(2, 4, []) == []
+    for k in ("PYTEST_XDIST_WORKER", "PYTEST_XDIST_WORKER_COUNT", "ARL_GPU_PARTITIONED", "CUDA_VISIBLE_DEVICES"):
+        monkeypatch.delenv(k, raising=False)
+    assert tu.partition_gpus_for_xdist() is None                                   # not under xdist
+    monkeypatch.setenv("PYTEST_XDIST_WORKER", "gw1")
+    monkeypatch.setenv("PYTEST_XDIST_WORKER_COUNT", "2")
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "4,5,6,7")
+    assert tu.visible_gpu_ids() == ["4", "5", "6", "7"]
+    assert tu.partition_gpus_for_xdist() == "6,7" and tu.partition_gpus_for_xdist() is None    # once per process
+    monkeypatch.delenv("ARL_GPU_PARTITIONED")
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    assert tu.partition_gpus_for_xdist() is None                                   # a CPU-only run stays CPU-only
