@@ -139,3 +139,34 @@ def test_jobs_model_survives_a_failing_service_and_long_lists(tmp_path):
     assert "refresh failed" in draw_jobs(m, 80, 10, None)[-1]
     m.set_query("no such job")
     assert m.selected() is None and draw_jobs(m, 80, 10, None)[0].startswith("jobs: 0 of 30")
+
+
+def test_terminal_reads_keys_from_a_pseudo_terminal():
+    import io
+    import os
+    import pty
+
+    from cortex_client.dss_client.tui.app import Terminal
+    master, slave = pty.openpty()
+    out = io.StringIO()
+    with os.fdopen(slave, "rb", buffering=0) as tty_in:
+        with Terminal(stdin=tty_in, stdout=out) as term:
+            assert term.read_key(0.05) is None                                   # nothing typed
+            os.write(master, b"j")
+            assert term.read_key(1.0) == "j"
+            os.write(master, b"\x1b[A")
+            assert term.read_key(1.0) == "up"
+            os.write(master, b"\x1b[6~")
+            assert term.read_key(1.0) == "pgdn"
+            os.write(master, b"\r")
+            assert term.read_key(1.0) == "enter"
+            os.write(master, b"\x1b")
+            assert term.read_key(1.0) == "esc"                                   # a lone escape, after the short wait
+            os.write(master, b"\x7f")
+            assert term.read_key(1.0) == "backspace"
+            term.draw(["ab", "cd"])
+            w, h = term.size()
+            assert w > 0 and h > 0
+        text = out.getvalue()
+        assert text.startswith("\x1b[?1049h\x1b[?25l") and "\x1b[Hab\r\ncd" in text and text.endswith("\x1b[?25h\x1b[?1049l")
+    os.close(master)
