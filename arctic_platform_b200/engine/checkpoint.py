@@ -31,6 +31,22 @@ import torch.distributed as dist
 DS_VERSION = "0.19.2+b200"
 
 
+
+def _load_pt(path):
+    """Reads a checkpoint file as DATA: tensors, numbers, strings and containers only (``weights_only=True``), which
+    is all this engine writes.  A file that needs arbitrary unpickling (e.g. written by another framework with
+    custom classes inside) is refused unless ``APB_TRUST_CHECKPOINT_PICKLES=1`` says the file is trusted -- loading a
+    pickle runs whatever code it names."""
+    import os
+    import pickle
+    try:
+        return torch.load(path, map_location="cpu", weights_only=True)
+    except pickle.UnpicklingError as exc:
+        if os.environ.get("APB_TRUST_CHECKPOINT_PICKLES") == "1":
+            return torch.load(path, map_location="cpu", weights_only=False)
+        raise RuntimeError(f"{path} holds objects beyond tensors and plain containers ({exc}); set "
+                           f"APB_TRUST_CHECKPOINT_PICKLES=1 to load it if you trust its origin") from exc
+
 def _barrier(engine) -> None:
     if engine.world > 1 and dist.is_initialized():
         dist.barrier(group=engine.group)
@@ -146,7 +162,7 @@ def load_checkpoint(engine, load_dir: str, tag: Optional[str] = None, strict: bo
     ms = d / "mp_rank_00_model_states.pt"
     if not ms.exists():
         raise FileNotFoundError(f"{ms} not found")
-    state = torch.load(ms, map_location="cpu", weights_only=False)
+    state = _load_pt(ms)
     if state.get("dp_world_size", 1) != engine.world and not engine.forward_only:
         raise ValueError(f"checkpoint was written with {state.get('dp_world_size')} data-parallel ranks, this job has "
                          f"{engine.world}; use the hf/ export to change the world size")
@@ -186,7 +202,7 @@ def load_checkpoint(engine, load_dir: str, tag: Optional[str] = None, strict: bo
     engine.micro_steps = int(state.get("micro_steps", 0))
     if not engine.forward_only:
         f = d / f"bf16_zero_pp_rank_{engine.rank}_mp_rank_00_optim_states.pt"
-        osd = torch.load(f, map_location="cpu", weights_only=False)["optimizer_state_dict"]
+        osd = _load_pt(f)["optimizer_state_dict"]
         base = osd["base_optimizer_state"]["state"][0]
         part = osd["single_partition_of_fp32_groups"][0]
         if part.numel() != engine.master.numel():

@@ -124,3 +124,25 @@ def test_load_rejects_a_layout_mismatch_and_accepts_a_tag_directory(tmp_path):
     _t.save(st, f)
     with pytest.raises(ValueError, match="layout"):
         load_checkpoint(b, str(tmp_path))
+
+
+class _CustomForPickleTest:
+    pass
+
+
+def test_checkpoint_files_are_read_as_data_only(tmp_path, monkeypatch):
+    """A checkpoint file that needs arbitrary unpickling is refused unless the caller says it is trusted."""
+    import torch
+
+    from arctic_platform_b200.engine import checkpoint as ck
+
+    Custom = _CustomForPickleTest                          # stands for "some class another framework pickled"
+    good, bad = tmp_path / "good.pt", tmp_path / "bad.pt"
+    torch.save({"w": torch.ones(2), "step": 3, "names": ["a"]}, good)
+    torch.save({"w": torch.ones(2), "obj": Custom()}, bad)
+    assert ck._load_pt(good)["step"] == 3
+    monkeypatch.delenv("APB_TRUST_CHECKPOINT_PICKLES", raising=False)
+    with pytest.raises(RuntimeError, match="APB_TRUST_CHECKPOINT_PICKLES"):
+        ck._load_pt(bad)
+    monkeypatch.setenv("APB_TRUST_CHECKPOINT_PICKLES", "1")
+    assert isinstance(ck._load_pt(bad)["obj"], Custom)
