@@ -15,6 +15,9 @@ loss) back:
   * ``value``: the device time of the engine phases inside the SAME steps (sync_weights, rollout, reference
                log-probs, forward/backward, optimizer), each bracketed by CUDA events, host batch building excluded.
 Bytes copied per step are counted where the copies are issued (``utils/transfer_stats.py``).
+``--wall-limit-s`` (default 830 s after process start) is a safety net for callers that end the process after a fixed
+wall time: when the next timed step would end past it, all ranks stop together (never before 5 timed steps) and the
+line reports the steps actually timed in ``steps`` with the request in ``steps_requested``.
 
     python bench.py [--gpus N --steps K --warmup W]          # N > 1 under torch.distributed.run
     python bench.py --impl reference                          # the reference's own stack, if installable
