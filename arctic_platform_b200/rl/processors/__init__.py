@@ -17,8 +17,13 @@ _EXPORTS = {
                       "export"),
     "functional": ("masked_sum", "masked_mean", "masked_normalization", "agg_loss", "kl_penalty", "kl_penalty_forward",
                    "ppo_clip_token_loss", "ppo_actor_loss_fn", "sapo_loss_fn", "m2po_mask", "proximal_logp_approximations",
-                   "resolve_proximal_logp", "sequence_level_ratio_and_advantages"),
+                   "resolve_proximal_logp", "sequence_level_ratio_and_advantages", "ProxLogpMethod", "ProxApproxMethod",
+                   "PROX_LOGP_METHOD_RECOMPUTE", "PROX_LOGP_METHOD_LOGLINEAR", "PROX_LOGP_METHOD_METRICS",
+                   "PROX_APPROX_METHOD_LOGLINEAR", "PROX_APPROX_METHOD_LINEAR", "PROX_APPROX_METHOD_ROLLOUT",
+                   "PROX_APPROX_METHODS_ALL", "compute_prox_logp_approximations", "_resolve_proximal_logp",
+                   "_compute_sequence_level_ratio_and_advantages"),
     "losses": ("verl_grpo_loss", "grpo_loss", "sft_loss", "sft_ce_loss", "SFT_LOSS_FNS"),
+    "../../sft/processor": ("LOGIT_LOSS_FNS", "run_sft_pipeline"),
 }
 _REGISTRY = ("LOSS_FNS", "POST_PROCESSORS", "register_loss_fn", "register_post_processor", "resolve_fn")
 _WHERE = {name: mod for mod, names in _EXPORTS.items() for name in names}
@@ -34,7 +39,10 @@ def __getattr__(name: str) -> Any:
             importlib.import_module(f"{__name__}.pipeline")
         value = getattr(registry, name)
     elif name in _WHERE:
-        value = getattr(importlib.import_module(f"{__name__}.{_WHERE[name]}"), name)
+        where = _WHERE[name]
+        mod = importlib.import_module("...sft.processor", __name__) if where.startswith("../") else \
+            importlib.import_module(f"{__name__}.{where}")
+        value = getattr(mod, name)
     else:
         raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
     globals()[name] = value

@@ -291,3 +291,34 @@ def sapo_loss_fn(logprobs, old_logprobs, advantages, tau_pos: float, tau_neg: fl
             "clip_mask": none, "dual_clip_mask": none, "sapo_soft_gate": gate.detach(),
             "sapo_scaled_gate_pos": gate_pos.detach(), "sapo_scaled_gate_neg": gate_neg.detach()}
     return loss, stat
+
+
+# ------------------------------------------------------------------ names of the proximal-policy options
+from enum import Enum  # noqa: E402
+
+
+class ProxLogpMethod(str, Enum):
+    """Where the proximal policy's log-probs come from (``processing.loss_kwargs.prox_logp_method``)."""
+    RECOMPUTE = "recompute"      # the client sent them (an extra forward pass), or the data is on-policy
+    LOGLINEAR = "loglinear"      # interpolated from behaviour and current log-probs by staleness, no extra pass
+    METRICS = "metrics"          # client-sent values are required; approximations are computed for metrics only
+
+
+class ProxApproxMethod(str, Enum):
+    LOGLINEAR = "loglinear"      # interpolate log-probs
+    LINEAR = "linear"            # interpolate probabilities
+    ROLLOUT = "rollout"          # keep the behaviour policy's values
+
+
+PROX_LOGP_METHOD_RECOMPUTE = ProxLogpMethod.RECOMPUTE.value
+PROX_LOGP_METHOD_LOGLINEAR = ProxLogpMethod.LOGLINEAR.value
+PROX_LOGP_METHOD_METRICS = ProxLogpMethod.METRICS.value
+PROX_APPROX_METHOD_LOGLINEAR = ProxApproxMethod.LOGLINEAR.value
+PROX_APPROX_METHOD_LINEAR = ProxApproxMethod.LINEAR.value
+PROX_APPROX_METHOD_ROLLOUT = ProxApproxMethod.ROLLOUT.value
+PROX_APPROX_METHODS_ALL = [m.value for m in ProxApproxMethod]
+
+# the reference's spellings of three helpers
+compute_prox_logp_approximations = proximal_logp_approximations
+_resolve_proximal_logp = resolve_proximal_logp
+_compute_sequence_level_ratio_and_advantages = sequence_level_ratio_and_advantages

@@ -77,7 +77,12 @@ def test_package_level_names_of_the_reference_resolve(tmp_path):
                  "unpack_sequences", "pad_packed_for_model", "DEFAULT_MAX_TOKENS_PER_MB", "MicroBatchSpec",
                  "split_padded_tensor_dict_into_mb_list", "DistributedStatsTracker", "ReduceType", "DEFAULT_TRACKER",
                  "denominator", "stat", "scalar", "scope", "export", "masked_normalization", "agg_loss", "kl_penalty",
-                 "ppo_actor_loss_fn", "sapo_loss_fn", "grpo_loss", "verl_grpo_loss", "sft_loss", "sft_ce_loss"):
+                 "ppo_actor_loss_fn", "sapo_loss_fn", "grpo_loss", "verl_grpo_loss", "sft_loss", "sft_ce_loss",
+                 "ProxLogpMethod", "ProxApproxMethod", "PROX_LOGP_METHOD_RECOMPUTE", "PROX_LOGP_METHOD_LOGLINEAR",
+                 "PROX_LOGP_METHOD_METRICS", "PROX_APPROX_METHOD_LOGLINEAR", "PROX_APPROX_METHOD_LINEAR",
+                 "PROX_APPROX_METHOD_ROLLOUT", "PROX_APPROX_METHODS_ALL", "compute_prox_logp_approximations",
+                 "_resolve_proximal_logp", "_compute_sequence_level_ratio_and_advantages", "LOGIT_LOSS_FNS", "SFT_LOSS_FNS",
+                 "run_sft_pipeline"):
         assert getattr(proc, name) is not None, name
     assert {"verl_grpo", "grpo", "sft", "sft_ce"} <= set(proc.LOSS_FNS) and proc.LOSS_FNS is registry.LOSS_FNS
     assert "compute_entropy_and_logprobs" in proc.POST_PROCESSORS
