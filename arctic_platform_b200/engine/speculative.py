@@ -17,7 +17,10 @@ One round for a sequence ``s``:
    from ``p_k``.  Greedy decoding (temperature 0) accepts exactly the tokens the target would have produced and
    replaces the first mismatch by the target's arg-max, so its output equals plain greedy decoding token for token.
 
-Every round therefore emits between 1 and ``k + 1`` tokens for ``k`` draft passes and one target pass.  Requests with
+Every round therefore emits between 1 and ``k + 1`` tokens for ``k`` draft passes and one target pass.  All sequences
+of a request (``n`` samples of every prompt) advance together: a draft step, and the verifying target pass, is ONE
+packed forward over all sequences that are still running, so the number of model passes per round does not grow with
+the number of sequences.  Requests with
 distribution shaping that depends on the tokens emitted so far (penalties, ``min_tokens``, ``logit_bias``, ``min_p``)
 fall back to plain decoding.
 """
@@ -56,12 +59,18 @@ class SpeculativeSampler(ReferenceSampler):
         return self.stats["accepted"] / max(1, self.stats["proposed"])
 
     # ------------------------------------------------------------------ model passes
+    def _logits_packed(self, model: DecoderLM, seqs: Sequence[Sequence[int]], lasts: Sequence[int]) -> List[torch.Tensor]:
+        """fp32 logits of the last ``lasts[i]`` positions of every sequence, from one packed recompute pass."""
+        lens = [len(s) for s in seqs]
+        ids = torch.tensor([t for s in seqs for t in s], dtype=torch.int64, device=self.device)
+        pos = torch.cat([torch.arange(n, device=self.device) for n in lens])
+        cu = np.concatenate([[0], np.cumsum(lens)])
+        h = model.forward_hidden(ids, pos, AttnLayout.from_cu_seqlens(cu))
+        rows = torch.cat([torch.arange(int(cu[i + 1]) - int(lasts[i]), int(cu[i + 1]), device=self.device) for i in range(len(seqs))])
+        return list(model.logits(h[rows]).float().split([int(x) for x in lasts]))
+
     def _logits(self, model: DecoderLM, seq: Sequence[int], last: int) -> torch.Tensor:
-        """fp32 logits of the last ``last`` positions of ``seq`` (one recompute pass)."""
-        ids = torch.tensor(list(seq), dtype=torch.int64, device=self.device)
-        layout = AttnLayout.from_cu_seqlens(np.array([0, len(seq)]))
-        h = model.forward_hidden(ids, torch.arange(len(seq), device=self.device), layout)[-last:]
-        return model.logits(h).float()
+        return self._logits_packed(model, [seq], [last])[0]
 
     @staticmethod
     def _dist(logits: torch.Tensor, sp: SamplingParams) -> torch.Tensor:
@@ -83,60 +92,76 @@ class SpeculativeSampler(ReferenceSampler):
         if self.eos is not None and not sp.ignore_eos:
             stops.add(int(self.eos))
         greedy = not (sp.temperature and sp.temperature > 0)
-        results: List[dict] = []
+        states: List[dict] = []
         for pi, prompt in enumerate(prompts):
             if len(prompt) == 0:
                 raise ValueError("empty prompt")
             if len(prompt) + sp.max_tokens > self.max_seq_len:
                 raise ValueError(f"prompt ({len(prompt)}) + max_tokens ({sp.max_tokens}) exceeds max_seq_len {self.max_seq_len}")
             for _ in range(sp.n):
-                seq = list(map(int, prompt))
-                out: List[int] = []
-                lps: List[float] = []
-                reason = "length"
-                while len(out) < sp.max_tokens and reason == "length":
-                    k = min(self.k, sp.max_tokens - len(out))
-                    new_tokens, new_lps = self._round(seq, k, sp, greedy)
-                    for tok, lp in zip(new_tokens, new_lps):
-                        out.append(tok)
-                        lps.append(lp)
-                        seq.append(tok)
-                        if tok in stops:
-                            reason = "stop"
-                            break
-                        if len(out) >= sp.max_tokens:
-                            break
-                results.append({"token_ids": out, "logprobs": lps, "finish_reason": reason, "prompt_len": len(prompt),
-                                "prompt_index": pi, "text": None})
-        return results
+                states.append({"seq": list(map(int, prompt)), "out": [], "lps": [], "reason": "length", "pi": pi,
+                               "prompt_len": len(prompt)})
+        running = [st for st in states if sp.max_tokens > 0]
+        while running:
+            ks = [min(self.k, sp.max_tokens - len(st["out"])) for st in running]
+            emitted = self._rounds([st["seq"] for st in running], ks, sp, greedy)
+            still = []
+            for st, (toks, tok_lps) in zip(running, emitted):
+                for tok, lp in zip(toks, tok_lps):
+                    st["out"].append(tok)
+                    st["lps"].append(lp)
+                    st["seq"].append(tok)
+                    if tok in stops:
+                        st["reason"] = "stop"
+                        break
+                    if len(st["out"]) >= sp.max_tokens:
+                        break
+                if st["reason"] == "length" and len(st["out"]) < sp.max_tokens:
+                    still.append(st)
+            running = still
+        return [{"token_ids": st["out"], "logprobs": st["lps"], "finish_reason": st["reason"], "prompt_len": st["prompt_len"],
+                 "prompt_index": st["pi"], "text": None} for st in states]
 
     def _draw(self, probs: torch.Tensor) -> int:
         return int(torch.multinomial(probs.cpu(), 1, generator=self.gen))
 
     def _round(self, seq: List[int], k: int, sp: SamplingParams, greedy: bool):
-        """One draft-and-verify round after ``seq``: returns the emitted tokens (1 .. k + 1) and their log-probs under
-        the target's unfiltered (temperature-scaled) policy."""
-        # 1. draft k tokens
-        draft_tokens: List[int] = []
-        draft_probs: List[torch.Tensor] = []
-        ext = list(seq)
-        for _ in range(k):
-            lg = self._logits(self.draft, ext, 1)[0]
-            if greedy:
-                tok = int(lg.argmax())
-                draft_probs.append(lg)                               # unused in greedy mode
-            else:
-                q = self._dist(lg, sp)
-                tok = self._draw(q)
-                draft_probs.append(q)
-            draft_tokens.append(tok)
-            ext.append(tok)
-        # 2. one target pass over seq + drafts: distributions at the k + 1 positions that follow seq[-1], x_1, ..., x_k
-        tl = self._logits(self.model, ext, k + 1)
-        self.stats["rounds"] += 1
+        """One draft-and-verify round after ``seq``: the emitted tokens (1 .. k + 1) and their log-probs under the
+        target's unfiltered (temperature-scaled) policy."""
+        return self._rounds([seq], [k], sp, greedy)[0]
+
+    def _rounds(self, seqs: Sequence[List[int]], ks: Sequence[int], sp: SamplingParams, greedy: bool):
+        """One round for every sequence at once (``ks[i]`` draft tokens for sequence ``i``): ``max(ks)`` packed draft
+        passes and one packed target pass.  Returns ``[(tokens, log-probs)]`` in the order of ``seqs``."""
+        n = len(seqs)
+        exts = [list(s) for s in seqs]
+        draft_tokens: List[List[int]] = [[] for _ in range(n)]
+        draft_probs: List[List[torch.Tensor]] = [[] for _ in range(n)]
+        # 1. draft: step j extends every sequence that still has draft tokens to produce
+        for j in range(max(ks)):
+            idx = [i for i in range(n) if j < ks[i]]
+            for i, lg in zip(idx, self._logits_packed(self.draft, [exts[i] for i in idx], [1] * len(idx))):
+                lg = lg[0]
+                if greedy:
+                    tok = int(lg.argmax())
+                    draft_probs[i].append(lg)                          # unused in greedy mode
+                else:
+                    q = self._dist(lg, sp)
+                    tok = self._draw(q)
+                    draft_probs[i].append(q)
+                draft_tokens[i].append(tok)
+                exts[i].append(tok)
+        # 2. one target pass over every seq + drafts: distributions at the k + 1 positions after seq[-1], x_1, ..., x_k
+        target = self._logits_packed(self.model, exts, [k + 1 for k in ks])
+        self.stats["rounds"] += n
         self.stats["target_passes"] += 1
-        self.stats["proposed"] += k
+        self.stats["proposed"] += int(sum(ks))
         scale = sp.temperature if not greedy else 1.0
+        # 3. accept / resample, sequence by sequence
+        return [self._verify(target[i], draft_tokens[i], draft_probs[i], ks[i], sp, greedy, scale) for i in range(n)]
+
+    def _verify(self, tl: torch.Tensor, drafts: List[int], qs: List[torch.Tensor], k: int, sp: SamplingParams, greedy: bool,
+                scale: float):
         emitted: List[int] = []
         emitted_lps: List[float] = []
 
@@ -144,8 +169,7 @@ class SpeculativeSampler(ReferenceSampler):
             emitted.append(tok)
             emitted_lps.append(float(torch.log_softmax(tl[pos] / scale, -1)[tok]))
 
-        # 3. accept / resample
-        for i, x in enumerate(draft_tokens):
+        for i, x in enumerate(drafts):
             if greedy:
                 best = int(tl[i].argmax())
                 if best == x:
@@ -154,7 +178,7 @@ class SpeculativeSampler(ReferenceSampler):
                     continue
                 emit(best, i)
                 return emitted, emitted_lps
-            p, q = self._dist(tl[i], sp), draft_probs[i]
+            p, q = self._dist(tl[i], sp), qs[i]
             ratio = float(p[x]) / max(float(q[x]), 1e-30)
             if float(torch.rand((), generator=self.gen)) < min(1.0, ratio):
                 emit(x, i)

@@ -87,3 +87,28 @@ def test_worker_builds_the_speculative_engine_from_the_job_config():
     assert w.sampler.stats == before
     with pytest.raises(ValueError, match="needs a draft model"):
         SpeculativeSampler(PRESETS["qwen3-tiny"], "cpu", model=w.sampler.model, draft_model=None)
+
+
+def test_sequences_of_a_request_advance_in_packed_passes():
+    """Model passes per round do not grow with the number of sequences, and a batch of ragged prompts (one of which
+    stops early) gives each sequence exactly what it gets alone."""
+    cfg, target, draft = _models()
+    prompts = [[3, 9, 27, 5], [11, 2], [7, 7, 7, 7, 7, 7, 1]]
+    plain = ReferenceSampler(cfg, "cpu", model=target, max_seq_len=64)
+    want = plain.generate(prompts, {"temperature": 0.0, "max_tokens": 9, "n": 2})
+    stop = want[2]["token_ids"][3]                                       # ends prompt 1 (or another one) early
+    want = plain.generate(prompts, {"temperature": 0.0, "max_tokens": 9, "n": 2, "stop_token_ids": [stop]})
+    spec = SpeculativeSampler(cfg, "cpu", model=target, draft_model=draft, num_speculative_tokens=3, max_seq_len=64)
+    got = spec.generate(prompts, {"temperature": 0.0, "max_tokens": 9, "n": 2, "stop_token_ids": [stop]})
+    assert [(g["prompt_index"], g["token_ids"], g["finish_reason"]) for g in got] == \
+        [(w["prompt_index"], w["token_ids"], w["finish_reason"]) for w in want]
+    assert any(g["finish_reason"] == "stop" for g in got) and any(g["finish_reason"] == "length" for g in got)
+    passes_six = spec.stats["target_passes"]
+    alone = SpeculativeSampler(cfg, "cpu", model=target, draft_model=draft, num_speculative_tokens=3, max_seq_len=64)
+    alone.generate(prompts[:1], {"temperature": 0.0, "max_tokens": 9})
+    assert passes_six <= 9 and passes_six < 6 * alone.stats["target_passes"]      # six sequences share the passes
+    assert spec.stats["rounds"] >= passes_six                                     # rounds are counted per sequence
+    # the packed helper returns exactly the rows asked for
+    lg = spec._logits_packed(target, [[1, 2, 3], [4, 5]], [2, 1])
+    assert [t.shape[0] for t in lg] == [2, 1]
+    torch.testing.assert_close(lg[1][0], spec._logits(target, [4, 5], 1)[0], rtol=1e-5, atol=1e-5)
