@@ -52,7 +52,20 @@ _MOVED = {
     "model.implementations.qwen35.model_builder": "models.factory",
     "model.implementations.qwen35.parallel_dims": "parallel.parallel_dims",
     "model.implementations.qwen35.sequence_parallel": "parallel.ulysses",
+    "model.implementations.qwen35.models": "models",
+    "model.implementations.qwen35.models.base": "models.decoder",
+    "model.implementations.qwen35.models.layers": "models",
+    "model.implementations.qwen35.models.layers.checkpointing": "models.decoder",
+    "model.implementations.qwen35.models.layers.lm_head": "ops.logprob",
+    "model.implementations.qwen35.models.layers.moe": "models.moe",
+    "model.implementations.qwen35.models.layers.rotary_emb": "models.decoder",
+    "model.implementations.qwen35.models.qwen3_5_moe": "models",
+    "model.implementations.qwen35.models.qwen3_5_moe.configuration_qwen3_5_moe": "models.config",
+    "model.implementations.qwen35.models.qwen3_5_moe.converting_qwen3_5_moe": "models.hf_io",
+    "model.implementations.qwen35.models.qwen3_5_moe.modeling_qwen3_5_moe": "models.decoder",
     "model.implementations.qwen35.vlm": "models.vlm",
+    "client.examples": "sft.examples",
+    "client.examples.sft_example": "sft.examples.sft_example",
     "model.implementations.qwen35.weights": "models.hf_io",
     "model.implementations.qwen35.world": "parallel.world",
     "rl.processors.grpo": "rl.processors.losses",
@@ -84,8 +97,9 @@ _MOVED = {
 
 
 class _AliasLoader(importlib.abc.Loader):
-    def __init__(self, real_name: str):
+    def __init__(self, real_name: str, alias_path: str = ""):
         self.real_name = real_name
+        self.alias_path = alias_path
 
     def create_module(self, spec):
         mod = importlib.import_module(self.real_name)
@@ -96,6 +110,10 @@ class _AliasLoader(importlib.abc.Loader):
         # already executed under its real name; the import machinery has just stamped the alias spec on it -- put the
         # real one back, the module's own relative imports go by it
         module.__spec__ = self._real_spec
+        from ._names import COMPAT_NAMES
+        for name, (where, attr) in COMPAT_NAMES.get(self.alias_path, {}).items():
+            if name not in vars(module):
+                setattr(module, name, getattr(importlib.import_module(f"{_TARGET}.{where}"), attr))
 
 
 class _AliasFinder(importlib.abc.MetaPathFinder):
@@ -110,7 +128,7 @@ class _AliasFinder(importlib.abc.MetaPathFinder):
         except (ImportError, ValueError):
             return None
         mod = importlib.import_module(real)
-        return importlib.util.spec_from_loader(fullname, _AliasLoader(real), is_package=hasattr(mod, "__path__"))
+        return importlib.util.spec_from_loader(fullname, _AliasLoader(real, rest), is_package=hasattr(mod, "__path__"))
 
 
 if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):

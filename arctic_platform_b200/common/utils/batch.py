@@ -163,14 +163,20 @@ def unpack_batch(payload: Dict[str, Any]) -> Tuple[dict, Any, Dict[str, Any], Op
     return {}, payload["batch"], payload.get("meta") or {}, payload.get("processing")
 
 
-def http_split_batch(frame: bytes, num_workers: int) -> Tuple[List[Dict[str, Any]], Optional[torch.Tensor]]:
-    """One DSSST1 request frame -> per-rank payloads (same ``meta`` and ``processing`` on every rank, the batch split
-    by ``split_batch_for_ranks``) and the permutation that was applied to the rows, if any."""
-    from ... import wire
-    _args, batch, meta, processing = unpack_batch(wire.loads(frame))
+def ray_split_batch(payload: Dict[str, Any], num_workers: int) -> Tuple[List[Dict[str, Any]], Optional[torch.Tensor]]:
+    """A decoded call payload (``{"batch", "meta", "processing"}``) -> per-rank payloads (same ``meta`` and
+    ``processing`` on every rank, the batch split by ``split_batch_for_ranks``) and the permutation that was applied
+    to the rows, if any."""
+    _args, batch, meta, processing = unpack_batch(payload)
     meta = dict(meta)
     shards, order = split_batch_for_ranks(batch, meta, num_workers)
     return [{"batch": s, "meta": dict(meta), "processing": processing} for s in shards], order
+
+
+def http_split_batch(frame: bytes, num_workers: int) -> Tuple[List[Dict[str, Any]], Optional[torch.Tensor]]:
+    """The same for one DSSST1 request frame as it arrives over HTTP."""
+    from ... import wire
+    return ray_split_batch(wire.loads(frame), num_workers)
 
 
 def get_reverse_idx(idx_map) -> List[int]:

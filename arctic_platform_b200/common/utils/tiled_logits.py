@@ -69,6 +69,38 @@ def logprobs_entropy_from_flat_logits(flat_logits: torch.Tensor, flat_labels: to
     return lp, ent
 
 
+def logprobs_from_logits(logits: torch.Tensor, labels: torch.Tensor, inplace_backward: bool = True) -> torch.Tensor:
+    """Log-prob of ``labels`` under ``logits [..., V]`` for callers that already hold logits (an external model);
+    ``logit[label] - logsumexp`` in fp32, so no ``[..., V]`` softmax copy is made.  ``inplace_backward`` is accepted
+    for call compatibility (arctic_platform/rl/processors/pipeline.py:620-647 uses it for a library CE kernel)."""
+    lead = logits.shape[:-1]
+    flat = logits.reshape(-1, logits.shape[-1]).float()
+    picked = flat.gather(-1, labels.reshape(-1, 1).long()).squeeze(-1)
+    return (picked - torch.logsumexp(flat, dim=-1)).view(*lead)
+
+
+def fast_logprobs_and_entropy_from_logits(logits: torch.Tensor, labels: torch.Tensor, calculate_entropy: bool = True):
+    """``logits [..., V]`` -> ``(logprobs [...], entropy [...] or None)`` in one pass."""
+    lead = logits.shape[:-1]
+    lp, ent = logprobs_entropy_from_flat_logits(logits.reshape(-1, logits.shape[-1]), labels.reshape(-1), calculate_entropy)
+    return lp.view(*lead), (ent.view(*lead) if ent is not None else None)
+
+
+def chunked_logprobs_and_entropy_from_logits(logits: torch.Tensor, labels: torch.Tensor, calculate_entropy: bool = True,
+                                             peak_mem_gib: float = 4.0):
+    """Same result, walking the rows in blocks whose fp32 softmax fits in ``peak_mem_gib`` GiB."""
+    flat, y = logits.reshape(-1, logits.shape[-1]), labels.reshape(-1)
+    rows = logits_chunk_rows(flat.shape[-1], peak_mem_gib)
+    parts = [logprobs_entropy_from_flat_logits(flat[i:i + rows], y[i:i + rows], calculate_entropy)
+             for i in range(0, flat.shape[0], rows)]
+    if not parts:
+        empty = flat.new_zeros(labels.shape, dtype=torch.float32)
+        return empty, (empty.clone() if calculate_entropy else None)
+    lp = torch.cat([p[0] for p in parts]).view_as(labels)
+    ent = torch.cat([p[1] for p in parts]).view_as(labels) if calculate_entropy else None
+    return lp, ent
+
+
 def _from_hidden(model, hidden_states, labels, temperature, calculate_entropy, chunk_rows, fp32_inputs):
     w = _weight(model)
     lead = hidden_states.shape[:-1]

@@ -366,3 +366,24 @@ def token_logprobs(model: DecoderLM, packed, inv_temperature=1.0, with_entropy: 
         from ..utils.action_masks import masked_logprobs
         return masked_logprobs(pred, model.output_weight, packed.labels, action_masks, inv_temperature, with_entropy)
     return lm_head_logprobs(pred, model.output_weight, packed.labels, inv_temperature, with_entropy)
+
+
+# ----------------------------------------------------------------------------- selective checkpointing, per block
+def get_supported_targets(layer: "DecoderBlock") -> frozenset:
+    """Parts of ``layer`` that selective activation checkpointing can name."""
+    return layer.supported_ac_targets()
+
+
+def supports_selective_activation_checkpointing(layer) -> bool:
+    return isinstance(layer, DecoderBlock)
+
+
+def set_selective_activation_checkpointing(layer: "DecoderBlock", targets) -> None:
+    """Puts the named parts of ONE block under activation checkpointing (``DecoderLM.enable_activation_checkpointing``
+    does this for every block).  Unknown names raise; names of parts the block does not have are ignored, as in
+    arctic_platform/model/implementations/qwen35/models/layers/checkpointing.py:118-146."""
+    chosen = tuple(dict.fromkeys(targets))
+    unknown = set(chosen) - set(SELECTIVE_AC_TARGETS)
+    if unknown:
+        raise ValueError(f"Unsupported selective activation checkpoint targets: {sorted(unknown)}")
+    layer.ac_targets = tuple(t for t in chosen if t in layer.supported_ac_targets())

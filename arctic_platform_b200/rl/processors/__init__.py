@@ -12,9 +12,14 @@ from typing import Any
 _EXPORTS = {
     "pipeline": ("run_pipeline", "DEFAULT_PROCESSING", "pack_for_model", "response_length_of", "action_masks_of"),
     "packing": ("pack_sequences", "unpack_sequences", "pad_packed_for_model"),
-    "microbatch": ("DEFAULT_MAX_TOKENS_PER_MB", "MicroBatchSpec", "ffd_allocate", "split_padded_tensor_dict_into_mb_list"),
+    "padding": ("padded_tensor_2d_to_unpadded_tensor_1d", "padded_tensor_2d_dict_to_unpadded_tensor_1d_dict",
+                "unpadded_tensor_1d_to_padded_tensor_2d", "unpadded_tensor_1d_dict_to_padded_tensor_2d_dict",
+                "padded_tensor_2d_full_to_unpadded_tensor_1d_response", "unpadded_tensor_1d_response_to_padded_tensor_2d_full",
+                "unpadded_tensor_1d_response_dict_to_padded_tensor_2d_full_dict", "compute_packing_info_for_batch"),
+    "microbatch": ("DEFAULT_MAX_TOKENS_PER_MB", "MicroBatchSpec", "MicroBatchList", "ffd_allocate",
+                   "split_padded_tensor_dict_into_mb_list"),
     "stats_tracker": ("DistributedStatsTracker", "ReduceType", "DEFAULT_TRACKER", "denominator", "stat", "scalar", "scope",
-                      "export"),
+                      "export", "export_all", "get", "record_timing", "TRACKERS"),
     "functional": ("masked_sum", "masked_mean", "masked_normalization", "agg_loss", "kl_penalty", "kl_penalty_forward",
                    "ppo_clip_token_loss", "ppo_actor_loss_fn", "sapo_loss_fn", "m2po_mask", "proximal_logp_approximations",
                    "resolve_proximal_logp", "sequence_level_ratio_and_advantages", "ProxLogpMethod", "ProxApproxMethod",

@@ -23,6 +23,30 @@ class MicroBatchSpec:
     n_mbs_divisor: int = 1         # the count is rounded up to a multiple of this
 
 
+@dataclass
+class MicroBatchList:
+    """What the split returns: the micro-batches with the bookkeeping to put per-row results back in input order.
+    ``forward_indices[j]`` is the input row that sits at position ``j`` of the concatenated micro-batches,
+    ``backward_indices`` its inverse (``concat(results)[backward_indices]`` is in input order), ``group_lens`` the
+    token count of every micro-batch.  Unpacks as ``(mbs, groups)`` too."""
+    data: dict
+    mb_spec: MicroBatchSpec
+    mbs: list
+    group_lens: list
+    forward_indices: Optional[list] = None
+    backward_indices: Optional[list] = None
+    groups: Optional[list] = None
+
+    def __len__(self) -> int:
+        return len(self.mbs)
+
+    def __iter__(self):
+        return iter((self.mbs, self.groups))
+
+    def __getitem__(self, i):
+        return (self.mbs, self.groups)[i]
+
+
 def ffd_allocate(sizes, capacity: int, min_groups: int = 1, divisor: int = 1) -> List[List[int]]:
     """Groups of item indices; every group's total size is within ``capacity``.  Raises when an item alone
     exceeds the capacity.  Trailing empty groups appear when ``min_groups`` / ``divisor`` ask for more
@@ -41,7 +65,7 @@ def ffd_allocate(sizes, capacity: int, min_groups: int = 1, divisor: int = 1) ->
 
 
 def split_padded_tensor_dict_into_mb_list(batch: Dict[str, torch.Tensor], spec: MicroBatchSpec, group=None
-                                          ) -> Tuple[List[Dict[str, torch.Tensor]], List[List[int]]]:
+                                          ) -> MicroBatchList:
     """Splits along dim 0 by token budget (``attention_mask`` row sums).  With a process group the number
     of micro-batches is raised to the maximum over ranks so every rank runs the same number of steps."""
     lens = batch["attention_mask"].sum(-1).tolist()
@@ -58,4 +82,9 @@ def split_padded_tensor_dict_into_mb_list(batch: Dict[str, torch.Tensor], spec: 
         idx = torch.tensor(g, dtype=torch.long)
         mbs.append({k: (v[idx] if torch.is_tensor(v) and v.dim() > 0 and v.shape[0] == len(lens) else v)
                     for k, v in batch.items()})
-    return mbs, groups
+    forward = [i for g in groups for i in g]
+    backward = [0] * len(forward)
+    for pos, row in enumerate(forward):
+        backward[row] = pos
+    return MicroBatchList(data=batch, mb_spec=spec, mbs=mbs, group_lens=[int(sum(lens[i] for i in g)) for g in groups],
+                          forward_indices=forward, backward_indices=backward, groups=groups)

@@ -22,6 +22,10 @@ from ...common.registry import LOSS_FNS, POST_PROCESSORS, register_post_processo
 from ...models.decoder import token_logprobs
 from ..zorro_train.layout import PackedBatch, build_packed_batch, build_plain_packed
 from . import losses as _losses  # noqa: F401  (registers the built-in losses)
+from .padding import *  # noqa: F401,F403  (padded grid <-> packed row helpers, importable from here as well)
+from ...common.utils.batch import dump_dict_payload  # noqa: F401
+from ...common.utils.tiled_logits import (chunked_logprobs_and_entropy_from_logits,  # noqa: F401
+                                          fast_logprobs_and_entropy_from_logits, logprobs_from_logits)
 
 DEFAULT_PROCESSING = {"pre": [], "post": ["compute_entropy_and_logprobs"], "loss_fn": "verl_grpo", "loss_kwargs": {}}
 

@@ -5,6 +5,7 @@ Python floats (token-weighted means across ranks when a process group is given).
 from __future__ import annotations
 
 import contextlib
+import time
 from enum import Enum
 from typing import Dict, List, Optional
 
@@ -64,6 +65,15 @@ class DistributedStatsTracker:
             self.stats.setdefault(key, []).append(float(v))
             self.reduce_types[key] = ReduceType.SCALAR
 
+    @contextlib.contextmanager
+    def record_timing(self, key: str):
+        """Wall time of the block in seconds, recorded as the scalar ``key`` (under the current scope)."""
+        t0 = time.perf_counter()
+        try:
+            yield
+        finally:
+            self.scalar(**{key: time.perf_counter() - t0})
+
     def export(self, key: Optional[str] = None, reduce_group=None, reset: bool = True) -> Dict[str, float]:
         out: Dict[str, float] = {}
         do_reduce = dist.is_initialized() and reduce_group is not False and dist.get_world_size(reduce_group) > 1
@@ -122,3 +132,21 @@ stat = DEFAULT_TRACKER.stat
 scalar = DEFAULT_TRACKER.scalar
 scope = DEFAULT_TRACKER.scope
 export = DEFAULT_TRACKER.export
+record_timing = DEFAULT_TRACKER.record_timing
+
+TRACKERS: Dict[str, DistributedStatsTracker] = {}
+
+
+def get(name: str) -> DistributedStatsTracker:
+    """The named tracker, made on first use (one per subsystem that wants its own scope tree)."""
+    if name not in TRACKERS:
+        TRACKERS[name] = DistributedStatsTracker(name)
+    return TRACKERS[name]
+
+
+def export_all(reduce_group=None, reset: bool = True) -> Dict[str, float]:
+    """The default tracker's export merged with every named tracker's."""
+    out = DEFAULT_TRACKER.export(reduce_group=reduce_group, reset=reset)
+    for tracker in TRACKERS.values():
+        out.update(tracker.export(reduce_group=reduce_group, reset=reset))
+    return out

@@ -87,6 +87,24 @@ def get_seqlen_balanced_partitions(seqlens: Sequence[int], k_partitions: int, eq
     return parts
 
 
+def ceildiv(a: int, b: int) -> int:
+    return -(a // -b)
+
+
+def roundup_divisible(a: int, b: int) -> int:
+    """``a`` rounded up to a multiple of ``b``."""
+    return ceildiv(a, b) * b
+
+
+def compute_variation(costs: Sequence[float]) -> Tuple[float, float, float]:
+    """How uneven a list of costs is: ``(max, max / min, (max - median) / median)``; the last is 0 when the largest
+    item is typical and grows with a heavy outlier."""
+    import statistics
+    ordered = sorted(costs)
+    med = statistics.median(ordered)
+    return ordered[-1], (ordered[-1] / ordered[0] if ordered[0] else float("inf")), ((ordered[-1] - med) / med if med else 0.0)
+
+
 def log_seqlen_unbalance(seqlens: Sequence[int], partitions: List[List[int]], prefix: str = "") -> Dict[str, float]:
     loads = [sum(seqlens[i] for i in p) for p in partitions]
     return {f"{prefix}/min": float(min(loads)), f"{prefix}/max": float(max(loads)),

@@ -9,7 +9,7 @@ from typing import Any, Dict, Optional
 import torch
 import torch.distributed as dist
 
-from ..rl.processors.losses import SFT_LOSS_FNS  # noqa: F401
+from ..rl.processors.losses import SFT_LOSS_FNS, sft_ce_loss, sft_loss  # noqa: F401
 from ..rl.processors.pipeline import run_pipeline
 
 LOGIT_LOSS_FNS = {"sft_ce"}
@@ -46,6 +46,37 @@ def count_loss_tokens(batch: Dict[str, Any]) -> int:
         elif torch.is_tensor(pos) and pos.numel() == ids.numel():
             first = first | (pos.reshape(1, -1) == 0)
     return int((sel & ~first).sum())
+
+
+def count_valid_target_tokens(batch: Any) -> Optional[int]:
+    """Next-token targets the loss is taken over, for one micro-batch dict or a list of them (a gradient-accumulation
+    step).  ``None`` when nothing carries ``labels`` (the caller then skips the global-token normalisation); ``0``
+    when every position is masked.  Same contract as arctic_platform/sft/processor.py:60-73, counted by
+    ``count_loss_tokens`` so packed rows and left padding are handled too."""
+    if isinstance(batch, (list, tuple)):
+        counts = [count_valid_target_tokens(mb) for mb in batch]
+        counts = [c for c in counts if c is not None]
+        return sum(counts) if counts else None
+    if not isinstance(batch, dict) or batch.get("labels") is None:
+        return None
+    return count_loss_tokens(batch)
+
+
+def sft_ce_sum_from_hidden(model, hidden: torch.Tensor, labels: torch.Tensor, *, mode: str = "memory",
+                           peak_mem_gib: float = 4.0):
+    """Summed next-token cross entropy from the last hidden states ``[B, S, H]`` and ``labels [B, S]`` (``-100`` =
+    ignored) without a ``[B, S, V]`` logits tensor -> ``(ce_sum, number of valid targets)``.  ``hidden[:, :-1]``
+    predicts ``labels[:, 1:]``.  Both modes of the reference (``compute`` / ``memory``,
+    arctic_platform/sft/processor.py:169-238) run the lm-head kernel that produces log-probs in its epilogue;
+    ``peak_mem_gib`` sizes the row chunk of its backward recompute."""
+    if mode not in ("compute", "memory"):
+        raise ValueError(f"sft_ce_sum_from_hidden: mode must be 'compute' or 'memory', got {mode!r}")
+    from ..common.utils.tiled_logits import chunked_logprobs_entropy_from_hidden
+    targets = labels[:, 1:]
+    valid = targets != -100
+    logprobs, _ = chunked_logprobs_entropy_from_hidden(model, hidden[:, :-1, :].contiguous(), targets.clamp_min(0).contiguous(),
+                                                       temperature=1.0, calculate_entropy=False, peak_mem_gib=peak_mem_gib)
+    return -(logprobs * valid.to(logprobs.dtype)).sum(), int(valid.sum())
 
 
 def inject_sft_global_token_meta(batch: Dict[str, Any], meta: Dict[str, Any], group=None) -> None:

@@ -70,6 +70,13 @@ def torch_assert_safetensors_close(path_a, path_b, rtol: float = 1e-5, atol: flo
         torch.testing.assert_close(a[k].float(), b[k].float(), rtol=rtol, atol=atol, msg=lambda m: f"{k}: {m}")
 
 
+def apply_print_resets(buf: str) -> str:
+    """What a terminal would show: on every line, whatever precedes the last carriage return is dropped (progress
+    bars rewrite their line)."""
+    import re
+    return re.sub(r"^.*\r", "", buf, flags=re.M)
+
+
 class CaptureStd:
     """Context manager capturing stdout and/or stderr into ``.out`` / ``.err``."""
 

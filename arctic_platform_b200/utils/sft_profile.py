@@ -6,7 +6,7 @@ from __future__ import annotations
 import contextlib
 import os
 import time
-from typing import Dict
+from typing import Dict, Optional
 
 BUCKETS = ("serialize", "rpc", "h2d", "fwd", "bwd", "loss", "step")
 _acc: Dict[str, float] = {}
@@ -56,6 +56,35 @@ def merge_into(metrics: dict, reset: bool = True) -> dict:
     return metrics
 
 
-def format_line(profile_ms: Dict[str, float]) -> str:
+def format_line(prefix_or_buckets, buckets: Optional[Dict[str, float]] = None) -> str:
+    """``format_line(buckets)`` -> the buckets by share, largest first; ``format_line(prefix, buckets)`` -> the same
+    behind ``[ARL_SFT_PROFILE] prefix:`` (the line the reference prints)."""
+    profile_ms = prefix_or_buckets if buckets is None else buckets
     total = sum(profile_ms.values()) or 1.0
-    return " ".join(f"{k}={v:.1f}ms({100 * v / total:.0f}%)" for k, v in sorted(profile_ms.items(), key=lambda kv: -kv[1]))
+    body = " ".join(f"{k}={v:.1f}ms({100 * v / total:.0f}%)" for k, v in sorted(profile_ms.items(), key=lambda kv: -kv[1]))
+    return body if buckets is None else f"[ARL_SFT_PROFILE] {prefix_or_buckets}: {body}"
+
+
+def take_last() -> Dict[str, float]:
+    """The buckets accumulated since the last call, cleared (empty when profiling is off)."""
+    return snapshot(reset=True) if enabled() else {}
+
+
+def merge_into_metrics(metrics: Optional[dict], extra: Optional[Dict[str, float]] = None) -> dict:
+    """A copy of ``metrics`` with ``_profile_ms`` (the last step's buckets plus ``extra``) attached for the wire."""
+    out = dict(metrics or {})
+    if not enabled():
+        return out
+    prof = take_last()
+    prof.update(extra or {})
+    if prof:
+        out["_profile_ms"] = {k: round(v, 3) for k, v in sorted(prof.items())}
+    return out
+
+
+def maybe_print(prefix: str, buckets: Optional[Dict[str, float]] = None) -> None:
+    if not enabled():
+        return
+    data = buckets if buckets is not None else snapshot(reset=False)
+    if data:
+        print(format_line(prefix, data), flush=True)

@@ -133,3 +133,58 @@ def test_model_package_paths_and_patch_registry():
         build_model(ModelSpec("qwen3-tiny", loader_options={"patches": ["missing"]}))
     with pytest.raises(ValueError, match="patches"):
         build_model(ModelSpec("qwen3-tiny", loader_options={"patches": "count_blocks_for_test"}))
+
+
+# every module path the reference package has (files under its package directory), as import names below the package
+_ALL_REFERENCE_MODULES = """
+_dependency_groups client client.client client.config client.examples client.examples.sft_example client.sft_client
+client.sft_config client.transport client.transports client.transports.cortex client.transports.onprem
+client.transports.onprem_http client.transports.onprem_ray common common.deepspeed_worker common.http_server
+common.ray_cluster common.ray_server common.registry common.server common.utils common.utils.batch
+common.utils.checkpoint common.utils.cuda_ipc common.utils.debug common.utils.ray_pg common.utils.record_replay
+common.utils.server_models common.utils.sft_profile common.utils.tiled_logits common.utils.weight_sync integrations
+integrations.verl integrations.verl.adapter integrations.verl.grpo_loss integrations.verl.register
+integrations.verl.rollout integrations.verl.worker model model.config model.factory model.implementations
+model.implementations.qwen35 model.implementations.qwen35.config model.implementations.qwen35.config_validation
+model.implementations.qwen35.conversion_cache model.implementations.qwen35.deepspeed_integration
+model.implementations.qwen35.distributed model.implementations.qwen35.distributed.deepep
+model.implementations.qwen35.distributed.expert_parallel model.implementations.qwen35.gpu
+model.implementations.qwen35.gpu.action_masks model.implementations.qwen35.gpu.activation_offload
+model.implementations.qwen35.gpu.debug model.implementations.qwen35.gpu.router_replay_recompute
+model.implementations.qwen35.gpu.tiled_mlp model.implementations.qwen35.logging_utils
+model.implementations.qwen35.model_builder model.implementations.qwen35.models
+model.implementations.qwen35.models.base model.implementations.qwen35.models.layers
+model.implementations.qwen35.models.layers.checkpointing model.implementations.qwen35.models.layers.lm_head
+model.implementations.qwen35.models.layers.moe model.implementations.qwen35.models.layers.rotary_emb
+model.implementations.qwen35.models.qwen3_5_moe
+model.implementations.qwen35.models.qwen3_5_moe.configuration_qwen3_5_moe
+model.implementations.qwen35.models.qwen3_5_moe.converting_qwen3_5_moe
+model.implementations.qwen35.models.qwen3_5_moe.modeling_qwen3_5_moe model.implementations.qwen35.parallel_dims
+model.implementations.qwen35.sequence_parallel model.implementations.qwen35.vlm
+model.implementations.qwen35.weights model.implementations.qwen35.world model.loader model.loaders
+model.loaders.huggingface model.loaders.qwen3_5_moe model.patch model.patches model.patches.gradient_checkpointing
+model.patches.liger model.patches.zorro_train rl rl.client rl.config rl.deepspeed_worker
+rl.examples.inference_example rl.examples.local_server_example rl.examples.weight_sync_example rl.http_client
+rl.http_server rl.processors rl.processors.functional rl.processors.grpo rl.processors.microbatch
+rl.processors.packing rl.processors.pipeline rl.processors.sft rl.processors.stats_tracker rl.processors.verl_grpo
+rl.ray_client rl.ray_cluster rl.ray_server rl.server rl.utils rl.utils.batch rl.utils.cuda_ipc rl.utils.debug
+rl.utils.ray_pg rl.utils.record_replay rl.utils.server_models rl.weight_sync rl.zorro_train rl.zorro_train.actor
+rl.zorro_train.demo rl.zorro_train.module_patcher rl.zorro_train.qwen_attention_patcher
+rl.zorro_train.qwen_model_patcher rl.zorro_train.seqlen_balancing rl.zorro_train.test_perf rl.zorro_train.tests
+rl.zorro_train.zorro_train sft sft.client sft.config sft.examples sft.examples.run_sft_ckpt_resume_demo
+sft.examples.run_sft_generate_demo sft.examples.run_sft_http_demo sft.examples.sft_example sft.processor
+testing_utils wire
+""".split()
+
+
+def test_every_module_path_of_the_reference_package_imports():
+    import importlib
+
+    missing = []
+    for name in _ALL_REFERENCE_MODULES:
+        try:
+            importlib.import_module("arctic_platform." + name)
+        except ImportError as exc:
+            missing.append(f"{name}: {exc}")
+    assert not missing, missing
+    assert len(_ALL_REFERENCE_MODULES) == 135
