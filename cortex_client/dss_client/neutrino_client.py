@@ -614,3 +614,11 @@ class NeutrinoTrainingEngine:
             self.client.cancel_job(self.job_id)
         except NeutrinoError:
             pass                                   # already finished or cancelled
+
+
+def __getattr__(name: str):
+    # the reference keeps the JSON batch-description helpers in this module; here they live in ``batch_spec``
+    if name in ("build_forward_backward_kwargs", "serialize_forward_backward_args", "build_forward_backward_payload"):
+        from . import batch_spec
+        return getattr(batch_spec, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

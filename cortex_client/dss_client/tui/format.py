@@ -46,6 +46,23 @@ def format_event(ev: Any) -> str:
     return " ".join(str(x) for x in (ts, kind, f"[{where}]" if where else "", detail) if x not in ("", None))
 
 
+def source_label(source: Any) -> str:
+    """Side-panel label of a log source (a sub-job: its id string or ``{"sub_job_id", "job_type"}``):
+    ``"<type> #<index>"``, the type taken from ``job_type`` or else from the middle of ``<uuid>:<type>:<index>``."""
+    if isinstance(source, dict):
+        sid = str(source.get("sub_job_id") or source.get("id") or source.get("source_id") or "")
+        kind = source.get("job_type") or source.get("type")
+    else:
+        sid, kind = str(source), None
+    parts = sid.split(":")
+    if kind is None and len(parts) >= 3:
+        kind = parts[-2]
+    index = parts[-1] if len(parts) >= 2 and parts[-1].isdigit() else None
+    if kind and index is not None:
+        return f"{kind} #{index}"
+    return str(kind or sid or "?")
+
+
 def wrap_log_line(text: Any, width: int) -> List[str]:
     """Hard wrap at ``width`` columns keeping every character (log lines hold stack traces and JSON: nothing is
     dropped, continuation lines are indented by two spaces)."""

@@ -192,3 +192,19 @@ def cached_pages(fetch: Callable[[Optional[str]], Dict[str, Any]], cache: LogCac
         if not entries:
             sleep(wait)
             wait = min(wait * POLL_BACKOFF, POLL_MAX_INTERVAL)
+
+
+def cached_log_pages(cache: LogCache, client: Any, job_id: str, sub_job_id: str, *, follow: bool = False,
+                     poll_interval: float = 1.0, replay_limit: Optional[int] = 2000, tail_lines: Optional[int] = 2000,
+                     sleep: Callable[[float], None] = time.sleep, max_polls: Optional[int] = None) -> Iterator[List[Any]]:
+    """``cached_pages`` over ``client.tail_logs`` for one sub-job (the cache is keyed by ``sub_job_id``).  The very
+    first request of a sub-job (no saved cursor) asks only for the last ``tail_lines`` lines: a job that has run for
+    hours is not read from its first line.  Later requests continue from the saved cursor and send no line limit."""
+    def fetch(cursor: Optional[str]) -> Dict[str, Any]:
+        kw: Dict[str, Any] = {"cursor": cursor, "sub_job_id": sub_job_id}
+        if cursor is None and tail_lines:
+            kw["max_lines"] = int(tail_lines)
+        return client.tail_logs(job_id, **kw)
+
+    return cached_pages(fetch, cache, sub_job_id, follow=follow, sleep=sleep, poll_interval=poll_interval,
+                        max_polls=max_polls, replay_limit=replay_limit)
