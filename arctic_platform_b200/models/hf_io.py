@@ -344,6 +344,73 @@ def save_hf_checkpoint(model, out_dir, max_shard_bytes: int = 4 << 30, tensors=N
     return files
 
 
+# ----------------------------------------------------------------------------- plain state dicts in a directory
+def get_max_layer_num(state_dict, layer_prefix: str = "model.layers.") -> int:
+    """Number of layers named in ``state_dict`` (highest ``<prefix><n>.`` + 1; 0 when there is none).  Works on any
+    iterable of names."""
+    top = -1
+    for key in state_dict:
+        if key.startswith(layer_prefix):
+            head = key[len(layer_prefix):].split(".", 1)[0]
+            if head.isdigit():
+                top = max(top, int(head))
+    return top + 1
+
+
+def safetensors_keys(path) -> List[str]:
+    """Tensor names of one ``.safetensors`` file, from its header only."""
+    with open(path, "rb") as f:
+        (hlen,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(hlen))
+    return [k for k in header if k != "__metadata__"]
+
+
+def load_state_dict_keys(save_dir) -> List[str]:
+    """Names of every tensor in the ``*.safetensors`` files of a directory; no tensor data is read."""
+    return [k for p in sorted(Path(save_dir).glob("*.safetensors")) for k in safetensors_keys(p)]
+
+
+def load_state_dict(save_dir) -> Dict[str, torch.Tensor]:
+    """Every tensor of the ``*.safetensors`` files of a directory, on the CPU."""
+    return {k: t for p in sorted(Path(save_dir).glob("*.safetensors")) for k, t in read_safetensors(p)}
+
+
+def save_state_dict(state_dict: Dict[str, torch.Tensor], save_dir, save_format: str = "safetensors",
+                    save_sharded: bool = True, max_shard_bytes: int = 5 << 30) -> List[str]:
+    """Writes a name -> tensor mapping as ``model.safetensors`` (or ``model-XXXXX-of-YYYYY.safetensors`` plus
+    ``model.safetensors.index.json`` when it exceeds ``max_shard_bytes`` and ``save_sharded``); ``save_format="torch"``
+    writes ``pytorch_model.bin``.  Returns the file names.  Same call as
+    arctic_platform/model/implementations/qwen35/weights.py:59-103."""
+    out = Path(save_dir)
+    out.mkdir(parents=True, exist_ok=True)
+    if save_format == "torch":
+        torch.save({k: v.detach().to("cpu") for k, v in state_dict.items()}, out / "pytorch_model.bin")
+        return ["pytorch_model.bin"]
+    if save_format != "safetensors":
+        raise ValueError(f"save_format {save_format!r}: expected 'safetensors' or 'torch'")
+    shards: List[Dict[str, torch.Tensor]] = [{}]
+    size = 0
+    for name, t in state_dict.items():
+        n = t.numel() * t.element_size()
+        if save_sharded and size + n > max_shard_bytes and shards[-1]:
+            shards.append({})
+            size = 0
+        shards[-1][name] = t.detach().to("cpu").contiguous()
+        size += n
+    files, weight_map, total = [], {}, 0
+    for i, sh in enumerate(shards):
+        fn = "model.safetensors" if len(shards) == 1 else f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors"
+        write_safetensors(out / fn, sh, {"format": "pt"})
+        files.append(fn)
+        for k, t in sh.items():
+            weight_map[k] = fn
+            total += t.numel() * t.element_size()
+    if len(shards) > 1:
+        (out / "model.safetensors.index.json").write_text(json.dumps({"metadata": {"total_size": total},
+                                                                       "weight_map": weight_map}))
+    return files
+
+
 TOKENIZER_FILES = ("tokenizer.json", "tokenizer_config.json", "tokenizer.model", "special_tokens_map.json", "vocab.json",
                    "merges.txt", "added_tokens.json", "generation_config.json", "chat_template.jinja", "chat_template.json")
 

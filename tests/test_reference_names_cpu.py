@@ -253,3 +253,30 @@ def test_small_helpers_under_their_reference_names():
     assert blk.ac_targets == ("norm",)
     with pytest.raises(ValueError, match="Unsupported"):
         set_selective_activation_checkpointing(blk, ["everything"])
+
+
+def test_state_dict_directory_helpers(tmp_path):
+    from arctic_platform_b200.models.hf_io import (get_max_layer_num, load_state_dict, load_state_dict_keys,
+                                                   save_state_dict)
+
+    sd = {"model.embed_tokens.weight": torch.randn(6, 4), "model.layers.0.w": torch.randn(4, 4).to(torch.bfloat16),
+          "model.layers.11.w": torch.arange(8, dtype=torch.int64), "lm_head.weight": torch.randn(6, 4)}
+    assert get_max_layer_num(sd) == 12 and get_max_layer_num({"x": 1}) == 0
+    assert get_max_layer_num(sd, layer_prefix="model.language_model.layers.") == 0
+
+    one = save_state_dict(sd, tmp_path / "one")
+    assert one == ["model.safetensors"] and sorted(load_state_dict_keys(tmp_path / "one")) == sorted(sd)
+    many = save_state_dict(sd, tmp_path / "many", max_shard_bytes=100)
+    assert len(many) > 1 and (tmp_path / "many" / "model.safetensors.index.json").is_file()
+    assert save_state_dict(sd, tmp_path / "flat", save_sharded=False, max_shard_bytes=100) == ["model.safetensors"]
+    for d in ("one", "many", "flat"):
+        back = load_state_dict(tmp_path / d)
+        assert set(back) == set(sd) and all(torch.equal(back[k], sd[k]) and back[k].dtype == sd[k].dtype for k in sd)
+    import json
+    index = json.loads((tmp_path / "many" / "model.safetensors.index.json").read_text())
+    assert set(index["weight_map"]) == set(sd) and set(index["weight_map"].values()) == set(many)
+
+    assert save_state_dict(sd, tmp_path / "pt", save_format="torch") == ["pytorch_model.bin"]
+    assert set(torch.load(tmp_path / "pt" / "pytorch_model.bin", weights_only=True)) == set(sd)
+    with pytest.raises(ValueError, match="save_format"):
+        save_state_dict(sd, tmp_path / "x", save_format="npz")
